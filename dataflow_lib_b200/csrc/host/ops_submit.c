@@ -1,0 +1,99 @@
+/*
+ * submit_* wrappers: build an Op on the stack (skeleton + pointers to the argument values)
+ * and hand it to handle->submit_op. Argument order per op is the one fixed by
+ * als244/dataflow_lib (src/dataflow_ops/src/norm_ops.c:17-24,52-60,85-91, attn_misc_ops.c:17-24,
+ * mlp_misc_ops.c:15-19,46-52, loss_misc_ops.c:19-22,47-50), because plug-ins index op_args by
+ * position. Every wrapper returns 0 on success and -1 on failure.
+ */
+#include "dataflow_api.h"
+
+static int submit(Dataflow_Handle * handle, Op * op, int stream_id, const char * what) {
+	if (!handle || !handle->submit_op) { fprintf(stderr, "Error: %s submitted to an uninitialised handle\n", what); return -1; }
+	if (handle->submit_op(handle, op, stream_id)) { fprintf(stderr, "Error: failed to submit %s op...\n", what); return -1; }
+	return 0;
+}
+
+/* ARGS(op, a, b, ...) stores &a, &b, ... into op.op_args in order. */
+#define ARGS(op, ...) do { void * args_[] = {__VA_ARGS__}; for (unsigned i_ = 0; i_ < sizeof(args_) / sizeof(args_[0]); i_++) (op).op_args[i_] = args_[i_]; } while (0)
+
+int submit_rms_norm(Dataflow_Handle * handle, int stream_id, DataflowDatatype fwd_dt, int n_rows, int n_cols, float eps,
+                    void * rms_weight, void * X, void * out, float * weighted_sums, float * rms_vals) {
+	Op op;
+	set_native_rms_norm_skeleton(&op.op_skeleton, fwd_dt);
+	ARGS(op, &n_rows, &n_cols, &eps, &rms_weight, &X, &out, &weighted_sums, &rms_vals);
+	return submit(handle, &op, stream_id, "rms norm");
+}
+
+int submit_rms_norm_bwd_x(Dataflow_Handle * handle, int stream_id, DataflowDatatype fwd_dt, DataflowDatatype bwd_dt,
+                          int n_rows, int n_cols, float eps, float * fwd_weighted_sums, float * fwd_rms_vals,
+                          void * rms_weight, void * X_inp, void * upstream_dX, void * dX) {
+	Op op;
+	set_native_rms_norm_bwd_x_skeleton(&op.op_skeleton, fwd_dt, bwd_dt);
+	ARGS(op, &n_rows, &n_cols, &eps, &fwd_weighted_sums, &fwd_rms_vals, &rms_weight, &X_inp, &upstream_dX, &dX);
+	return submit(handle, &op, stream_id, "rms norm bwd x");
+}
+
+int submit_rms_norm_bwd_w(Dataflow_Handle * handle, int stream_id, DataflowDatatype fwd_dt, DataflowDatatype bwd_dt,
+                          int n_rows, int n_cols, float eps, float * fwd_rms_vals, void * X_inp, void * upstream_dX, void * dW) {
+	Op op;
+	set_native_rms_norm_bwd_w_skeleton(&op.op_skeleton, fwd_dt, bwd_dt);
+	ARGS(op, &n_rows, &n_cols, &eps, &fwd_rms_vals, &X_inp, &upstream_dX, &dW);
+	return submit(handle, &op, stream_id, "rms norm bwd w");
+}
+
+int submit_rope(Dataflow_Handle * handle, int stream_id, DataflowDatatype fwd_dt, uint64_t N, int model_dim, int head_dim,
+                int num_kv_heads, int theta, int * seq_positions, void * X_q, void * X_k) {
+	Op op;
+	set_native_rope_skeleton(&op.op_skeleton, fwd_dt);
+	ARGS(op, &N, &model_dim, &head_dim, &num_kv_heads, &theta, &seq_positions, &X_q, &X_k);
+	return submit(handle, &op, stream_id, "rope");
+}
+
+int submit_rope_bwd_x(Dataflow_Handle * handle, int stream_id, DataflowDatatype bwd_dt, uint64_t N, int model_dim, int head_dim,
+                      int num_kv_heads, int theta, int * seq_positions, void * dX_q, void * dX_k) {
+	Op op;
+	set_native_rope_bwd_x_skeleton(&op.op_skeleton, bwd_dt);
+	ARGS(op, &N, &model_dim, &head_dim, &num_kv_heads, &theta, &seq_positions, &dX_q, &dX_k);
+	return submit(handle, &op, stream_id, "rope bwd x");
+}
+
+int submit_swiglu(Dataflow_Handle * handle, int stream_id, DataflowDatatype fwd_dt, int num_rows, int num_cols,
+                  void * x_w1, void * x_w3, void * out) {
+	Op op;
+	set_native_swiglu_skeleton(&op.op_skeleton, fwd_dt);
+	ARGS(op, &num_rows, &num_cols, &x_w1, &x_w3, &out);
+	return submit(handle, &op, stream_id, "swiglu");
+}
+
+int submit_swiglu_bwd_x(Dataflow_Handle * handle, int stream_id, DataflowDatatype fwd_dt, DataflowDatatype bwd_dt,
+                        int num_rows, int num_cols, void * x_w1, void * x_w3, void * upstream_dX, void * dX_w1, void * dX_w3) {
+	Op op;
+	set_native_swiglu_bwd_x_skeleton(&op.op_skeleton, fwd_dt, bwd_dt);
+	ARGS(op, &num_rows, &num_cols, &x_w1, &x_w3, &upstream_dX, &dX_w1, &dX_w3);
+	return submit(handle, &op, stream_id, "swiglu bwd x");
+}
+
+int submit_softmax(Dataflow_Handle * handle, int stream_id, DataflowDatatype fwd_dt, DataflowDatatype bwd_dt,
+                   int n_rows, int n_cols, void * X, void * out) {
+	Op op;
+	set_native_softmax_skeleton(&op.op_skeleton, fwd_dt, bwd_dt);
+	ARGS(op, &n_rows, &n_cols, &X, &out);
+	return submit(handle, &op, stream_id, "softmax");
+}
+
+int submit_cross_entropy_loss(Dataflow_Handle * handle, int stream_id, DataflowDatatype bwd_dt, int n_rows, int n_cols,
+                              void * pred_logits, uint32_t * labels) {
+	Op op;
+	set_native_cross_entropy_loss_skeleton(&op.op_skeleton, bwd_dt);
+	ARGS(op, &n_rows, &n_cols, &pred_logits, &labels);
+	return submit(handle, &op, stream_id, "cross entropy loss");
+}
+
+int submit_softmax_cross_entropy(Dataflow_Handle * handle, int stream_id, DataflowDatatype fwd_dt, DataflowDatatype bwd_dt,
+                                 int n_rows, int n_cols, void * logits, uint32_t * labels, void * dlogits,
+                                 float * row_loss, float * loss_sum) {
+	Op op;
+	set_native_softmax_cross_entropy_skeleton(&op.op_skeleton, fwd_dt, bwd_dt);
+	ARGS(op, &n_rows, &n_cols, &logits, &labels, &dlogits, &row_loss, &loss_sum);
+	return submit(handle, &op, stream_id, "softmax cross entropy");
+}

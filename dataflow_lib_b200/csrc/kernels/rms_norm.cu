@@ -1,0 +1,436 @@
+// RMSNorm forward, backward-x and backward-w.
+//
+// Layout: X, out, dY, dX are [n_rows, n_cols] row-major; a row is split into chunks of 8
+// elements and thread t of a CTA owns chunks t, t+T, t+2T, ... (VPT of them, compile time),
+// so a warp reads 32 consecutive 128-bit packets per request and the thread's slice of the
+// weight vector stays in registers for every row the CTA processes. CTAs are persistent and
+// walk rows blockIdx.x, blockIdx.x + gridDim.x, ... ; the packets of the next row are
+// requested before the current row is reduced, so each thread keeps 2*VPT (fwd), up to 6*VPT
+// (bwd_x) loads in flight.
+#include "common.cuh"
+
+namespace dfb200 {
+
+constexpr int E = 8;                 // elements per chunk
+constexpr int MAX_VPT = 8;
+// CTA width limit per VPT: rows up to 128*VPT chunks use <= 128 threads; only VPT == MAX_VPT grows wider.
+constexpr int max_threads_for(int vpt) { return vpt < MAX_VPT ? 128 : 512; }
+constexpr int MAX_COLS = MAX_VPT * 512 * E;
+
+template <typename T> struct RawChunk { uint32_t w[E / Word<T>::EPW]; };
+
+template <typename T>
+__device__ __forceinline__ void ld_raw(const void * base, uint64_t elem_idx, RawChunk<T> & c) {
+	ld_words<E / Word<T>::EPW, Hint::STREAM>(reinterpret_cast<const char *>(base) + elem_idx * (4 / Word<T>::EPW), c.w);
+}
+template <typename T>
+__device__ __forceinline__ void to_f32(const RawChunk<T> & c, float (&f)[E]) {
+	#pragma unroll
+	for (int i = 0; i < E / Word<T>::EPW; i++) Word<T>::unpack(c.w[i], &f[i * Word<T>::EPW]);
+}
+
+// Sum `a` and `b` over the CTA; every thread gets both totals. `slot` must alternate between
+// consecutive calls (two smem buffers make one barrier per call enough).
+__device__ __forceinline__ void block_sum2(float & a, float & b, float (*smem)[2][32], int slot) {
+	a = warp_sum(a);
+	b = warp_sum(b);
+	const int n_warps = blockDim.x >> 5;
+	if (n_warps == 1) return;
+	const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+	if (lane == 0) { smem[slot][0][warp] = a; smem[slot][1][warp] = b; }
+	__syncthreads();
+	float x = lane < n_warps ? smem[slot][0][lane] : 0.0f;
+	float y = lane < n_warps ? smem[slot][1][lane] : 0.0f;
+	a = warp_sum(x);
+	b = warp_sum(y);
+}
+
+// ----------------------------------------------------------------------------------------
+// forward:  out = T( (x * r) * w ),  r = rsqrt(sum x^2 / n + eps)   (fp32, one rounding)
+// follows src/ops/nvidia/norm/rms_norm.cu:339-406
+// ----------------------------------------------------------------------------------------
+template <typename T, int VPT>
+__global__ void __launch_bounds__(max_threads_for(VPT))
+rms_norm_fwd_kernel(int n_rows, int n_cols, float eps, const void * __restrict__ weight, const void * __restrict__ X,
+                    void * __restrict__ out, float * __restrict__ weighted_sums, float * __restrict__ rms_vals) {
+	__shared__ float red[2][2][32];
+	const int n_chunks = n_cols / E;
+	const int tid = threadIdx.x, nthr = blockDim.x;
+
+	RawChunk<T> wr[VPT], cur[VPT], nxt[VPT];     // packed: 4 registers per chunk for 16-bit types
+	#pragma unroll
+	for (int v = 0; v < VPT; v++) {
+		const int c = tid + v * nthr;
+		if (c < n_chunks) ld_words<E / Word<T>::EPW, Hint::KEEP>(reinterpret_cast<const char *>(weight) + (size_t) c * E * (4 / Word<T>::EPW), wr[v].w);
+	}
+	int row = blockIdx.x;
+	if (row < n_rows) {
+		#pragma unroll
+		for (int v = 0; v < VPT; v++) {
+			const int c = tid + v * nthr;
+			if (c < n_chunks) ld_raw<T>(X, (uint64_t) row * n_cols + (uint64_t) c * E, cur[v]);
+		}
+	}
+	int slot = 0;
+	for (; row < n_rows; row += gridDim.x, slot ^= 1) {
+		const int next_row = row + gridDim.x;
+		if (next_row < n_rows) {
+			#pragma unroll
+			for (int v = 0; v < VPT; v++) {
+				const int c = tid + v * nthr;
+				if (c < n_chunks) ld_raw<T>(X, (uint64_t) next_row * n_cols + (uint64_t) c * E, nxt[v]);
+			}
+		}
+		float ss = 0.0f, ws = 0.0f;
+		#pragma unroll
+		for (int v = 0; v < VPT; v++) {
+			const int c = tid + v * nthr;
+			if (c < n_chunks) {
+				float x[E], w[E];
+				to_f32<T>(cur[v], x); to_f32<T>(wr[v], w);
+				#pragma unroll
+				for (int i = 0; i < E; i++) { ws = fmaf(w[i], x[i], ws); ss = fmaf(x[i], x[i], ss); }
+			}
+		}
+		block_sum2(ss, ws, red, slot);
+		const float r = rsqrtf(ss / (float) n_cols + eps);
+		if (tid == 0) {
+			if (weighted_sums) weighted_sums[row] = ws;
+			if (rms_vals) rms_vals[row] = r;
+		}
+		#pragma unroll
+		for (int v = 0; v < VPT; v++) {
+			const int c = tid + v * nthr;
+			if (c < n_chunks) {
+				float x[E], w[E], o[E];
+				to_f32<T>(cur[v], x); to_f32<T>(wr[v], w);
+				#pragma unroll
+				for (int i = 0; i < E; i++) o[i] = (x[i] * r) * w[i];
+				store_elems<T, E>(out, (uint64_t) row * n_cols + (uint64_t) c * E, o);
+			}
+		}
+		#pragma unroll
+		for (int v = 0; v < VPT; v++) cur[v] = nxt[v];
+	}
+}
+
+// ----------------------------------------------------------------------------------------
+// backward-x:  dX += dY * B( w*r - ((x*r^3)/n) * ws )   follows
+// src/ops/nvidia/norm/rms_norm_bwd_x.cu:243-252 : the derivative is formed in fp32, rounded to
+// the backward type B, multiplied by dY in B (one rounding) and added to dX in B (one rounding).
+// For B = fp32 the multiply-add is a single fused fma, which is what nvcc makes of the
+// reference's `dX += dY * deriv`.
+// ----------------------------------------------------------------------------------------
+template <typename B> __device__ __forceinline__ float accumulate_dx(float dx, float dy, float deriv) {
+	return round_to<B>(dx + round_to<B>(dy * round_to<B>(deriv)));
+}
+template <> __device__ __forceinline__ float accumulate_dx<f32_t>(float dx, float dy, float deriv) {
+	return fmaf(dy, deriv, dx);
+}
+
+template <typename F, typename B, int VPT>
+__global__ void __launch_bounds__(max_threads_for(VPT))
+rms_norm_bwd_x_kernel(int n_rows, int n_cols, const float * __restrict__ fwd_weighted_sums, const float * __restrict__ fwd_rms_vals,
+                      const void * __restrict__ weight, const void * __restrict__ X, const void * __restrict__ dY, void * dX) {
+	const int n_chunks = n_cols / E;
+	const int tid = threadIdx.x, nthr = blockDim.x;
+	const float n_cols_f = (float) n_cols;
+
+	RawChunk<F> wr[VPT];
+	#pragma unroll
+	for (int v = 0; v < VPT; v++) {
+		const int c = tid + v * nthr;
+		if (c < n_chunks) ld_words<E / Word<F>::EPW, Hint::KEEP>(reinterpret_cast<const char *>(weight) + (size_t) c * E * (4 / Word<F>::EPW), wr[v].w);
+	}
+
+	for (int row = blockIdx.x; row < n_rows; row += gridDim.x) {
+		RawChunk<F> xr[VPT];
+		RawChunk<B> gr[VPT], dr[VPT];
+		#pragma unroll
+		for (int v = 0; v < VPT; v++) {
+			const int c = tid + v * nthr;
+			if (c < n_chunks) {
+				const uint64_t off = (uint64_t) row * n_cols + (uint64_t) c * E;
+				ld_raw<F>(X, off, xr[v]);
+				ld_raw<B>(dY, off, gr[v]);
+				ld_raw<B>(dX, off, dr[v]);
+			}
+		}
+		const float r = __ldg(fwd_rms_vals + row);
+		const float ws = __ldg(fwd_weighted_sums + row);
+		const float r3 = r * r * r;
+		#pragma unroll
+		for (int v = 0; v < VPT; v++) {
+			const int c = tid + v * nthr;
+			if (c < n_chunks) {
+				float x[E], g[E], d[E], w[E];
+				to_f32<F>(xr[v], x); to_f32<B>(gr[v], g); to_f32<B>(dr[v], d); to_f32<F>(wr[v], w);
+				#pragma unroll
+				for (int i = 0; i < E; i++) {
+					const float deriv = (w[i] * r) - (__fdividef(x[i] * r3, n_cols_f) * ws);
+					d[i] = accumulate_dx<B>(d[i], g[i], deriv);
+				}
+				store_elems<B, E>(dX, (uint64_t) row * n_cols + (uint64_t) c * E, d);
+			}
+		}
+	}
+}
+
+// ----------------------------------------------------------------------------------------
+// backward-w, stage 1: every CTA reduces dY*x*r over its rows into fp32 column sums.
+// The CTA is GROUPS row-groups of `group_threads` threads; group g takes rows
+// blockIdx.x*GROUPS + g, + gridDim.x*GROUPS, ... ; the groups are then summed through shared
+// memory in group order and the CTA writes one fp32 row [n_cols] of partial sums.
+// The arithmetic per term follows src/ops/nvidia/norm/rms_norm_bwd_w.cu:295 (f32(dY)*f32(x)*r).
+// ----------------------------------------------------------------------------------------
+template <typename F, typename B, int VPT>
+__global__ void __launch_bounds__(512)
+rms_norm_bwd_w_partial_kernel(int n_rows, int n_cols, int group_threads, const float * __restrict__ fwd_rms_vals,
+                              const void * __restrict__ X, const void * __restrict__ dY, float * __restrict__ partials) {
+	extern __shared__ float group_sums[];      // [groups - 1][n_cols]
+	const int n_chunks = n_cols / E;
+	const int groups = blockDim.x / group_threads;
+	const int g = threadIdx.x / group_threads;
+	const int tid = threadIdx.x - g * group_threads;
+
+	float acc[VPT][E];
+	#pragma unroll
+	for (int v = 0; v < VPT; v++)
+		#pragma unroll
+		for (int i = 0; i < E; i++) acc[v][i] = 0.0f;
+
+	const int row_stride = gridDim.x * groups;
+	for (int row = blockIdx.x * groups + g; row < n_rows; row += row_stride) {
+		RawChunk<F> xr[VPT];
+		RawChunk<B> gr[VPT];
+		#pragma unroll
+		for (int v = 0; v < VPT; v++) {
+			const int c = tid + v * group_threads;
+			if (c < n_chunks) {
+				const uint64_t off = (uint64_t) row * n_cols + (uint64_t) c * E;
+				ld_raw<F>(X, off, xr[v]);
+				ld_raw<B>(dY, off, gr[v]);
+			}
+		}
+		const float r = __ldg(fwd_rms_vals + row);
+		#pragma unroll
+		for (int v = 0; v < VPT; v++) {
+			const int c = tid + v * group_threads;
+			if (c < n_chunks) {
+				float x[E], gy[E];
+				to_f32<F>(xr[v], x); to_f32<B>(gr[v], gy);
+				#pragma unroll
+				for (int i = 0; i < E; i++) acc[v][i] += gy[i] * x[i] * r;
+			}
+		}
+	}
+
+	if (g > 0) {
+		#pragma unroll
+		for (int v = 0; v < VPT; v++) {
+			const int c = tid + v * group_threads;
+			if (c < n_chunks) {
+				float4 * dst = reinterpret_cast<float4 *>(group_sums + (size_t) (g - 1) * n_cols + (size_t) c * E);
+				dst[0] = make_float4(acc[v][0], acc[v][1], acc[v][2], acc[v][3]);
+				dst[1] = make_float4(acc[v][4], acc[v][5], acc[v][6], acc[v][7]);
+			}
+		}
+	}
+	__syncthreads();
+	if (g == 0) {
+		#pragma unroll
+		for (int v = 0; v < VPT; v++) {
+			const int c = tid + v * group_threads;
+			if (c < n_chunks) {
+				for (int o = 0; o < groups - 1; o++) {
+					const float4 * src = reinterpret_cast<const float4 *>(group_sums + (size_t) o * n_cols + (size_t) c * E);
+					const float4 a = src[0], b = src[1];
+					acc[v][0] += a.x; acc[v][1] += a.y; acc[v][2] += a.z; acc[v][3] += a.w;
+					acc[v][4] += b.x; acc[v][5] += b.y; acc[v][6] += b.z; acc[v][7] += b.w;
+				}
+				float4 * dst = reinterpret_cast<float4 *>(partials + (size_t) blockIdx.x * n_cols + (size_t) c * E);
+				dst[0] = make_float4(acc[v][0], acc[v][1], acc[v][2], acc[v][3]);
+				dst[1] = make_float4(acc[v][4], acc[v][5], acc[v][6], acc[v][7]);
+			}
+		}
+	}
+}
+
+// backward-w, stage 2: dW[c] = B( f32(dW[c]) + sum_p partials[p][c] ). A CTA covers 32
+// columns with 8 slices of the partial rows; slices are combined in slice order.
+template <typename B>
+__global__ void __launch_bounds__(256)
+rms_norm_bwd_w_final_kernel(int n_cols, int n_partials, const float * __restrict__ partials, void * dW) {
+	__shared__ float slice_sum[8][32];
+	const int lane = threadIdx.x & 31, slice = threadIdx.x >> 5;
+	const int col = blockIdx.x * 32 + lane;
+	float s = 0.0f;
+	if (col < n_cols)
+		for (int p = slice; p < n_partials; p += 8) s += partials[(size_t) p * n_cols + col];
+	slice_sum[slice][lane] = s;
+	__syncthreads();
+	if (slice == 0 && col < n_cols) {
+		float total = slice_sum[0][lane];
+		#pragma unroll
+		for (int k = 1; k < 8; k++) total += slice_sum[k][lane];
+		// element-wise read-modify-write of dW in its own type
+		if constexpr (Word<B>::EPW == 1) {
+			float * p = reinterpret_cast<float *>(dW) + col;
+			*p = *p + total;
+		} else {
+			static_assert(Word<B>::EPW == 2, "backward datatypes are fp32, fp16 or bf16");
+			uint16_t * p = reinterpret_cast<uint16_t *>(dW) + col;
+			float pair[2];
+			Word<B>::unpack((uint32_t) *p, pair);
+			pair[0] += total; pair[1] = 0.0f;
+			*p = (uint16_t) (Word<B>::pack(pair) & 0xffffu);
+		}
+	}
+}
+
+// ----------------------------------------------------------------------------------------
+// host side
+// ----------------------------------------------------------------------------------------
+
+struct RowGeometry { int vpt; int threads; };
+
+// Pick the chunks-per-thread (1,2,4,8) and the CTA width (multiple of 32) for a row of
+// n_chunks chunks: about 128 threads per row, wider only once VPT has reached its maximum.
+static bool row_geometry(int n_chunks, RowGeometry * geo) {
+	int vpt = 1;
+	while (vpt < MAX_VPT && (n_chunks + vpt - 1) / vpt > 128) vpt *= 2;
+	int threads = (n_chunks + vpt - 1) / vpt;
+	threads = (threads + 31) / 32 * 32;
+	if (threads > max_threads_for(vpt)) return false;
+	geo->vpt = vpt; geo->threads = threads;
+	return true;
+}
+
+static int check_rows(const char * op, int n_rows, int n_cols, RowGeometry * geo) {
+	if (n_rows < 0 || n_cols <= 0) return set_error(DFB200_ERR_ARG, "%s: bad shape %d x %d", op, n_rows, n_cols);
+	if (n_cols % E) return set_error(DFB200_ERR_ARG, "%s: n_cols = %d is not a multiple of %d", op, n_cols, E);
+	if (!row_geometry(n_cols / E, geo))
+		return set_error(DFB200_ERR_ARG, "%s: n_cols = %d exceeds the supported maximum of %d", op, n_cols, MAX_COLS);
+	return DFB200_OK;
+}
+
+#define DFB200_DISPATCH_VPT(vpt, VPT, ...)                  \
+	switch (vpt) {                                          \
+		case 1:  { constexpr int VPT = 1;  __VA_ARGS__; break; } \
+		case 2:  { constexpr int VPT = 2;  __VA_ARGS__; break; } \
+		case 4:  { constexpr int VPT = 4;  __VA_ARGS__; break; } \
+		default: { constexpr int VPT = 8;  __VA_ARGS__; break; } \
+	}
+
+// Grid of a persistent row kernel: every SM filled to the occupancy the kernel reaches.
+template <typename K> static int persistent_grid(K kernel, int n_rows, int threads) {
+	int per_sm = 0;
+	if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, threads, 0) != cudaSuccess || per_sm < 1) { cudaGetLastError(); per_sm = 1; }
+	long long g = (long long) sm_count() * per_sm;
+	if (g > n_rows) g = n_rows;
+	return g < 1 ? 1 : (int) g;
+}
+
+}  // namespace dfb200
+
+using namespace dfb200;
+
+extern "C" int dfb200_rms_norm(int fwd_dt, int n_rows, int n_cols, float eps, const void * rms_weight, const void * X, void * out,
+                               float * weighted_sums, float * rms_vals, void * stream) {
+	if (!dtype_size(fwd_dt)) return set_error(DFB200_ERR_DTYPE, "rms_norm: unsupported datatype %d", fwd_dt);
+	RowGeometry geo;
+	int rc = check_rows("rms_norm", n_rows, n_cols, &geo);
+	if (rc) return rc;
+	if (n_rows == 0) return DFB200_OK;
+	if (!rms_weight || !X || !out) return set_error(DFB200_ERR_ARG, "rms_norm: NULL tensor argument");
+	if (!aligned16(rms_weight) || !aligned16(X) || !aligned16(out)) return set_error(DFB200_ERR_ARG, "rms_norm: tensors must be 16-byte aligned");
+	DFB200_DISPATCH_DTYPE(fwd_dt, T, DFB200_DISPATCH_VPT(geo.vpt, VPT, {
+		auto kernel = rms_norm_fwd_kernel<T, VPT>;
+		const int grid = persistent_grid(kernel, n_rows, geo.threads);
+		kernel<<<grid, geo.threads, 0, (cudaStream_t) stream>>>(n_rows, n_cols, eps, rms_weight, X, out, weighted_sums, rms_vals);
+	}));
+	return check_launch("rms_norm");
+}
+
+extern "C" int dfb200_rms_norm_bwd_x(int fwd_dt, int bwd_dt, int n_rows, int n_cols, float eps, const float * fwd_weighted_sums,
+                                     const float * fwd_rms_vals, const void * rms_weight, const void * X_inp, const void * upstream_dX,
+                                     void * dX, void * stream) {
+	(void) eps;
+	if (!valid_fwd_bwd_pair(fwd_dt, bwd_dt)) return set_error(DFB200_ERR_DTYPE, "rms_norm_bwd_x: unsupported datatype pair (%d, %d)", fwd_dt, bwd_dt);
+	RowGeometry geo;
+	int rc = check_rows("rms_norm_bwd_x", n_rows, n_cols, &geo);
+	if (rc) return rc;
+	if (n_rows == 0) return DFB200_OK;
+	if (!fwd_weighted_sums || !fwd_rms_vals || !rms_weight || !X_inp || !upstream_dX || !dX)
+		return set_error(DFB200_ERR_ARG, "rms_norm_bwd_x: NULL tensor argument");
+	if (!aligned16(rms_weight) || !aligned16(X_inp) || !aligned16(upstream_dX) || !aligned16(dX))
+		return set_error(DFB200_ERR_ARG, "rms_norm_bwd_x: tensors must be 16-byte aligned");
+	DFB200_DISPATCH_PAIR(fwd_dt, bwd_dt, F, B, DFB200_DISPATCH_VPT(geo.vpt, VPT, {
+		auto kernel = rms_norm_bwd_x_kernel<F, B, VPT>;
+		const int grid = persistent_grid(kernel, n_rows, geo.threads);
+		kernel<<<grid, geo.threads, 0, (cudaStream_t) stream>>>(n_rows, n_cols, fwd_weighted_sums, fwd_rms_vals, rms_weight, X_inp, upstream_dX, dX);
+	}));
+	return check_launch("rms_norm_bwd_x");
+}
+
+// Stage-1 geometry of backward-w: one CTA of up to 512 threads per SM, split into row groups.
+// The 8*VPT fp32 accumulators per thread make VPT <= 4 the register-friendly choice, so wide rows
+// get wider groups before they get more packets per thread.
+static void bwd_w_geometry(int n_rows, int n_chunks, RowGeometry * geo, int * groups, int * grid) {
+	int vpt = 1;
+	while (vpt < 4 && (n_chunks + vpt - 1) / vpt > 128) vpt *= 2;
+	if ((n_chunks + vpt - 1) / vpt > 512) vpt = 8;
+	int threads = ((n_chunks + vpt - 1) / vpt + 31) / 32 * 32;
+	geo->vpt = vpt; geo->threads = threads;          // threads <= 512 because n_cols <= MAX_COLS
+	int g = 512 / threads;
+	if (g < 1) g = 1;
+	if (g > 8) g = 8;
+	while (g > 1 && g > n_rows) g /= 2;
+	long long ctas = sm_count();
+	const long long needed = ((long long) n_rows + g - 1) / g;
+	if (ctas > needed) ctas = needed;
+	if (ctas < 1) ctas = 1;
+	*groups = g;
+	*grid = (int) ctas;
+}
+
+extern "C" uint64_t dfb200_rms_norm_bwd_w_workspace_bytes(int n_rows, int n_cols) {
+	(void) n_rows;
+	if (n_cols <= 0) return 0;
+	int sms = sm_count();
+	if (sms <= 0) sms = 148;
+	return (uint64_t) sms * (uint64_t) n_cols * sizeof(float);
+}
+
+extern "C" int dfb200_rms_norm_bwd_w(int fwd_dt, int bwd_dt, int n_rows, int n_cols, float eps, const float * fwd_rms_vals,
+                                     const void * X_inp, const void * upstream_dX, void * dW, void * workspace, uint64_t workspace_bytes,
+                                     void * stream) {
+	(void) eps;
+	if (!valid_fwd_bwd_pair(fwd_dt, bwd_dt)) return set_error(DFB200_ERR_DTYPE, "rms_norm_bwd_w: unsupported datatype pair (%d, %d)", fwd_dt, bwd_dt);
+	RowGeometry geo;
+	int rc = check_rows("rms_norm_bwd_w", n_rows, n_cols, &geo);
+	if (rc) return rc;
+	if (n_rows == 0) return DFB200_OK;
+	if (!fwd_rms_vals || !X_inp || !upstream_dX || !dW) return set_error(DFB200_ERR_ARG, "rms_norm_bwd_w: NULL tensor argument");
+	if (!aligned16(X_inp) || !aligned16(upstream_dX)) return set_error(DFB200_ERR_ARG, "rms_norm_bwd_w: tensors must be 16-byte aligned");
+	int groups, grid;
+	bwd_w_geometry(n_rows, n_cols / E, &geo, &groups, &grid);
+	const uint64_t need = (uint64_t) grid * (uint64_t) n_cols * sizeof(float);
+	if (!workspace || workspace_bytes < need || !aligned16(workspace))
+		return set_error(DFB200_ERR_WORKSPACE, "rms_norm_bwd_w: needs %llu bytes of 16-byte aligned workspace, got %llu",
+		                 (unsigned long long) need, (unsigned long long) workspace_bytes);
+	const size_t smem = (size_t) (groups - 1) * n_cols * sizeof(float);
+	if (smem > 200 * 1024) return set_error(DFB200_ERR_ARG, "rms_norm_bwd_w: n_cols = %d too large", n_cols);
+	cudaStream_t s = (cudaStream_t) stream;
+	float * partials = reinterpret_cast<float *>(workspace);
+	DFB200_DISPATCH_PAIR(fwd_dt, bwd_dt, F, B, DFB200_DISPATCH_VPT(geo.vpt, VPT, {
+		auto kernel = rms_norm_bwd_w_partial_kernel<F, B, VPT>;
+		if (smem > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem);
+		kernel<<<grid, groups * geo.threads, smem, s>>>(n_rows, n_cols, geo.threads, fwd_rms_vals, X_inp, upstream_dX, partials);
+	}));
+	rc = check_launch("rms_norm_bwd_w (partial sums)");
+	if (rc) return rc;
+	DFB200_DISPATCH_PAIR(fwd_dt, bwd_dt, F, B,
+		(rms_norm_bwd_w_final_kernel<B><<<(n_cols + 31) / 32, 256, 0, s>>>(n_cols, grid, partials, dW)));
+	return check_launch("rms_norm_bwd_w (final sum)");
+}

@@ -1,0 +1,332 @@
+// Row softmax, the cross-entropy gradient step, and the two fused into one pass.
+//
+// A row lives in REGISTERS: a thread-block cluster of 1, 2, 4 or 8 CTAs owns one row, every
+// thread requests its (up to CPT) 128-bit packets up front, and the three phases of the
+// reference kernel (max, sum of exponentials, normalise; src/ops/nvidia/loss/softmax.cu:311-405)
+// run on the register copy. The row is read from HBM once and written once; the reference
+// reads it three times. Cross-CTA exchange of the maxima and partial sums goes through
+// distributed shared memory with the hardware cluster barrier (no spinning on memory).
+//
+// Rounding points kept from the reference (W = the output/"backward" datatype, which is also
+// the type the reference holds its shared-memory scratch in):
+//   * max is taken over W values (exact), x - max is rounded to W before the exponential,
+//   * the row is split into 32 interleaved partial sums: element j belongs to partial
+//     (j / 32) % 32 -- the reference's 32 warps striding over 32-element groups -- each
+//     accumulated in fp32 and rounded to W; the 32 rounded values are added in fp32 in the
+//     shuffle-tree order and the total is rounded to W again,
+//   * out = W( exp(W(x - max)) / total ).
+// Within a partial sum the fp32 addition order differs from the reference's (it cannot be
+// reproduced by a different thread layout); that changes a partial by a few fp32 ulps before
+// its rounding to W.
+#include "common.cuh"
+
+#include <cooperative_groups.h>
+#include <math_constants.h>
+
+namespace cg = cooperative_groups;
+
+namespace dfb200 {
+
+constexpr int E = 8;                       // elements per chunk
+constexpr int SLICE_ALIGN_CHUNKS = 128;    // slices start on a multiple of 1024 elements so that a thread's partial index is fixed
+constexpr int SOFTMAX_MAX_CLUSTER = 8;
+constexpr int SOFTMAX_MAX_THREADS = 512;
+constexpr int SOFTMAX_MAX_CPT = 8;
+
+template <typename F, typename B, int CPT, bool FUSE_CE>
+__global__ void __launch_bounds__(SOFTMAX_MAX_THREADS)
+softmax_rows_kernel(int n_rows, int n_cols, int slice_chunks, const void * __restrict__ X, void * __restrict__ out,
+                    const uint32_t * __restrict__ labels, float * __restrict__ row_loss) {
+	constexpr int FW = E / Word<F>::EPW;
+	__shared__ float s_warp_max[32];
+	__shared__ float s_warp_part[16][8];
+	__shared__ float s_cta_max;
+	__shared__ float s_cta_part[32];
+	__shared__ float s_row[2];              // row max, row total
+
+	cg::cluster_group cluster = cg::this_cluster();
+	const unsigned csize = cluster.num_blocks();
+	const unsigned crank = cluster.block_rank();
+	const int row = blockIdx.x / csize;
+	const int tid = threadIdx.x, nthr = blockDim.x;
+	const int warp = tid >> 5, lane = tid & 31, n_warps = nthr >> 5;
+
+	const int n_chunks = n_cols / E;
+	const int c_begin = crank * slice_chunks;
+	const int c_end = min(n_chunks, c_begin + slice_chunks);
+	const uint64_t row_elem = (uint64_t) row * (uint64_t) n_cols;
+
+	// ---- load: every packet of the slice is requested before anything is consumed
+	uint32_t raw[CPT][FW];
+	#pragma unroll
+	for (int k = 0; k < CPT; k++) {
+		const int c = c_begin + tid + k * nthr;
+		if (c < c_end) ld_words<FW, Hint::STREAM>(reinterpret_cast<const char *>(X) + (row_elem + (uint64_t) c * E) * (4 / Word<F>::EPW), raw[k]);
+	}
+
+	// ---- phase 1: row maximum
+	float m = -CUDART_INF_F;
+	#pragma unroll
+	for (int k = 0; k < CPT; k++) {
+		const int c = c_begin + tid + k * nthr;
+		if (c < c_end) {
+			float x[E];
+			#pragma unroll
+			for (int i = 0; i < FW; i++) Word<F>::unpack(raw[k][i], &x[i * Word<F>::EPW]);
+			#pragma unroll
+			for (int i = 0; i < E; i++) m = fmaxf(m, x[i]);
+		}
+	}
+	m = warp_max(m);
+	if (lane == 0) s_warp_max[warp] = m;
+	__syncthreads();
+	if (warp == 0) {
+		float v = lane < n_warps ? s_warp_max[lane] : -CUDART_INF_F;
+		v = warp_max(v);
+		if (lane == 0) s_cta_max = v;
+	}
+	if (csize > 1) {
+		cluster.sync();                     // also orders the s_cta_max write before the remote reads
+		if (warp == 0) {
+			float v = lane < csize ? *cluster.map_shared_rank(&s_cta_max, lane) : -CUDART_INF_F;
+			v = warp_max(v);
+			if (lane == 0) s_row[0] = v;
+		}
+	} else {
+		if (tid == 0) s_row[0] = s_cta_max; // same thread wrote it
+	}
+	__syncthreads();
+	const float row_max = s_row[0];
+
+	// ---- phase 2: 32 interleaved partial sums of exp(W(x - max))
+	float part = 0.0f;
+	#pragma unroll
+	for (int k = 0; k < CPT; k++) {
+		const int c = c_begin + tid + k * nthr;
+		if (c < c_end) {
+			float x[E];
+			#pragma unroll
+			for (int i = 0; i < FW; i++) Word<F>::unpack(raw[k][i], &x[i * Word<F>::EPW]);
+			#pragma unroll
+			for (int i = 0; i < E; i++) part += __expf(round_to<B>(x[i] - row_max));
+		}
+	}
+	// chunk c covers elements 8c..8c+7, so its partial index is (c / 4) % 32; c = tid + k*nthr with
+	// nthr % 128 == 0 and c_begin % 128 == 0 makes that (tid / 4) % 32 for every k.
+	part += __shfl_xor_sync(0xffffffffu, part, 1);
+	part += __shfl_xor_sync(0xffffffffu, part, 2);
+	if ((lane & 3) == 0) s_warp_part[warp][lane >> 2] = part;
+	__syncthreads();
+	if (warp == 0) {
+		// partial `lane` was produced by warps w with w % 4 == lane / 8 (8 partials per warp)
+		float v = 0.0f;
+		for (int w = lane >> 3; w < n_warps; w += 4) v += s_warp_part[w][lane & 7];
+		s_cta_part[lane] = v;
+	}
+	if (csize > 1) {
+		cluster.sync();
+		if (warp == 0) {
+			float v = 0.0f;
+			for (unsigned r = 0; r < csize; r++) v += cluster.map_shared_rank(s_cta_part, r)[lane];
+			v = round_to<B>(v);
+			v = warp_sum(v);
+			if (lane == 0) s_row[1] = round_to<B>(v);
+		}
+		cluster.barrier_arrive();           // remote reads done; matched by barrier_wait before exit
+	} else {
+		if (warp == 0) {
+			float v = round_to<B>(s_cta_part[lane]);   // written by this same lane
+			v = warp_sum(v);
+			if (lane == 0) s_row[1] = round_to<B>(v);
+		}
+	}
+	__syncthreads();
+	const float total = s_row[1];
+
+	// ---- phase 3: normalise, optional cross-entropy step, store
+	uint32_t label = 0xffffffffu;
+	if constexpr (FUSE_CE) label = __ldg(labels + row);
+	#pragma unroll
+	for (int k = 0; k < CPT; k++) {
+		const int c = c_begin + tid + k * nthr;
+		if (c < c_end) {
+			float x[E], o[E];
+			#pragma unroll
+			for (int i = 0; i < FW; i++) Word<F>::unpack(raw[k][i], &x[i * Word<F>::EPW]);
+			#pragma unroll
+			for (int i = 0; i < E; i++) o[i] = __fdividef(__expf(round_to<B>(x[i] - row_max)), total);
+			if constexpr (FUSE_CE) {
+				const uint32_t first = (uint32_t) c * E;
+				if (label >= first && label < first + E) {
+					#pragma unroll
+					for (int i = 0; i < E; i++) {
+						if (first + i == label) {
+							// the separate kernel reads the stored W probability and subtracts one in W
+							o[i] = round_to<B>(o[i]) - 1.0f;
+							if (row_loss) row_loss[row] = logf(total) - round_to<B>(x[i] - row_max);
+						}
+					}
+				}
+			}
+			store_elems<B, E>(out, row_elem + (uint64_t) c * E, o);
+		}
+	}
+	if constexpr (FUSE_CE) {
+		if (row_loss && label >= (uint32_t) n_cols && crank == 0 && tid == 0) row_loss[row] = 0.0f;
+	}
+	if (csize > 1) cluster.barrier_wait();  // no CTA leaves while a peer may still read its shared memory
+}
+
+// pred[r, labels[r]] -= 1 in the tensor's own type (intended semantics of
+// src/ops/nvidia/loss/cross_entropy.cu:33-44, whose row index is always 0 as written).
+template <typename B>
+__global__ void cross_entropy_step_kernel(int n_rows, int n_cols, void * pred, const uint32_t * __restrict__ labels) {
+	const int row = blockIdx.x * blockDim.x + threadIdx.x;
+	if (row >= n_rows) return;
+	const uint32_t label = labels[row];
+	if (label >= (uint32_t) n_cols) return;
+	const uint64_t idx = (uint64_t) row * (uint64_t) n_cols + label;
+	if constexpr (Word<B>::EPW == 1) {
+		float * p = reinterpret_cast<float *>(pred) + idx;
+		*p = *p - 1.0f;
+	} else {
+		uint16_t * p = reinterpret_cast<uint16_t *>(pred) + idx;
+		float pair[2];
+		Word<B>::unpack((uint32_t) *p, pair);
+		pair[0] -= 1.0f; pair[1] = 0.0f;
+		*p = (uint16_t) (Word<B>::pack(pair) & 0xffffu);
+	}
+}
+
+// loss_sum[0] = sum of row_loss over rows with a valid label (fp64, fixed order), loss_sum[1] = their count.
+__global__ void __launch_bounds__(1024)
+loss_sum_kernel(int n_rows, int n_cols, const float * __restrict__ row_loss, const uint32_t * __restrict__ labels, float * loss_sum) {
+	__shared__ double s_sum[1024];
+	__shared__ unsigned s_cnt[1024];
+	double acc = 0.0;
+	unsigned cnt = 0;
+	for (int r = threadIdx.x; r < n_rows; r += 1024) {
+		if (labels[r] < (uint32_t) n_cols) { acc += (double) row_loss[r]; cnt++; }
+	}
+	s_sum[threadIdx.x] = acc; s_cnt[threadIdx.x] = cnt;
+	__syncthreads();
+	for (int o = 512; o > 0; o >>= 1) {
+		if (threadIdx.x < o) { s_sum[threadIdx.x] += s_sum[threadIdx.x + o]; s_cnt[threadIdx.x] += s_cnt[threadIdx.x + o]; }
+		__syncthreads();
+	}
+	if (threadIdx.x == 0) { loss_sum[0] = (float) s_sum[0]; loss_sum[1] = (float) s_cnt[0]; }
+}
+
+struct SoftmaxGeometry { int cluster, threads, cpt, slice_chunks; };
+
+static bool softmax_geometry(int n_chunks, SoftmaxGeometry * g) {
+	// smallest cluster whose CTAs (<= 512 threads, <= 8 packets per thread) cover the row
+	int cluster = 1;
+	while (cluster < SOFTMAX_MAX_CLUSTER && (long long) cluster * SOFTMAX_MAX_THREADS * SOFTMAX_MAX_CPT < n_chunks) cluster *= 2;
+	int slice = (n_chunks + cluster - 1) / cluster;
+	slice = (slice + SLICE_ALIGN_CHUNKS - 1) / SLICE_ALIGN_CHUNKS * SLICE_ALIGN_CHUNKS;
+	if (slice > SOFTMAX_MAX_THREADS * SOFTMAX_MAX_CPT) return false;
+	// (cluster > 1 implies slices of more than 2048 chunks, so the 128-chunk alignment never leaves a CTA without work)
+	// threads: multiple of 128; packets per thread: power of two, as few as keep the CTA <= 512 threads
+	int cpt = 1;
+	while (cpt < SOFTMAX_MAX_CPT && (slice + cpt - 1) / cpt > SOFTMAX_MAX_THREADS) cpt *= 2;
+	// prefer >= 4 packets in flight per thread once the row is long enough to fill 128 threads with them
+	while (cpt < 4 && slice / (cpt * 2) >= 128) cpt *= 2;
+	int threads = (slice + cpt - 1) / cpt;
+	threads = (threads + 127) / 128 * 128;
+	if (threads > SOFTMAX_MAX_THREADS) return false;
+	g->cluster = cluster; g->threads = threads; g->cpt = cpt; g->slice_chunks = slice;
+	return true;
+}
+
+template <typename F, typename B, bool FUSE_CE>
+static int launch_softmax_rows(const SoftmaxGeometry & g, int n_rows, int n_cols, const void * X, void * out, const uint32_t * labels,
+                               float * row_loss, cudaStream_t stream) {
+	cudaLaunchConfig_t cfg = {};
+	cfg.gridDim = dim3((unsigned) n_rows * g.cluster, 1, 1);
+	cfg.blockDim = dim3(g.threads, 1, 1);
+	cfg.dynamicSmemBytes = 0;
+	cfg.stream = stream;
+	cudaLaunchAttribute attr[1];
+	attr[0].id = cudaLaunchAttributeClusterDimension;
+	attr[0].val.clusterDim.x = g.cluster; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+	cfg.attrs = attr; cfg.numAttrs = 1;
+	cudaError_t e;
+	switch (g.cpt) {
+		case 1:  e = cudaLaunchKernelEx(&cfg, softmax_rows_kernel<F, B, 1, FUSE_CE>, n_rows, n_cols, g.slice_chunks, X, out, labels, row_loss); break;
+		case 2:  e = cudaLaunchKernelEx(&cfg, softmax_rows_kernel<F, B, 2, FUSE_CE>, n_rows, n_cols, g.slice_chunks, X, out, labels, row_loss); break;
+		case 4:  e = cudaLaunchKernelEx(&cfg, softmax_rows_kernel<F, B, 4, FUSE_CE>, n_rows, n_cols, g.slice_chunks, X, out, labels, row_loss); break;
+		default: e = cudaLaunchKernelEx(&cfg, softmax_rows_kernel<F, B, 8, FUSE_CE>, n_rows, n_cols, g.slice_chunks, X, out, labels, row_loss); break;
+	}
+	if (e != cudaSuccess) { cudaGetLastError(); return set_error(DFB200_ERR_CUDA, "softmax launch: %s", cudaGetErrorString(e)); }
+	return DFB200_OK;
+}
+
+static int check_softmax(const char * op, int fwd_dt, int bwd_dt, int n_rows, int n_cols, const void * X, const void * out, SoftmaxGeometry * g) {
+	if (!valid_fwd_bwd_pair(fwd_dt, bwd_dt)) return set_error(DFB200_ERR_DTYPE, "%s: unsupported datatype pair (%d, %d)", op, fwd_dt, bwd_dt);
+	if (n_rows < 0 || n_cols <= 0) return set_error(DFB200_ERR_ARG, "%s: bad shape %d x %d", op, n_rows, n_cols);
+	if (n_cols % E) return set_error(DFB200_ERR_ARG, "%s: n_cols = %d is not a multiple of %d", op, n_cols, E);
+	if ((long long) n_rows * SOFTMAX_MAX_CLUSTER > 0x7fffffffLL) return set_error(DFB200_ERR_ARG, "%s: too many rows", op);
+	if (!softmax_geometry(n_cols / E, g))
+		return set_error(DFB200_ERR_ARG, "%s: n_cols = %d exceeds the supported maximum of %d", op, n_cols,
+		                 SOFTMAX_MAX_CLUSTER * SOFTMAX_MAX_THREADS * SOFTMAX_MAX_CPT * E);
+	if (n_rows && (!X || !out)) return set_error(DFB200_ERR_ARG, "%s: NULL tensor argument", op);
+	if (!aligned16(X) || !aligned16(out)) return set_error(DFB200_ERR_ARG, "%s: tensors must be 16-byte aligned", op);
+	return DFB200_OK;
+}
+
+}  // namespace dfb200
+
+using namespace dfb200;
+
+extern "C" int dfb200_softmax(int fwd_dt, int bwd_dt, int n_rows, int n_cols, const void * X, void * out, void * stream) {
+	SoftmaxGeometry g;
+	int rc = check_softmax("softmax", fwd_dt, bwd_dt, n_rows, n_cols, X, out, &g);
+	if (rc || n_rows == 0) return rc;
+	rc = DFB200_ERR_DTYPE;
+	DFB200_DISPATCH_PAIR(fwd_dt, bwd_dt, F, B,
+		rc = (launch_softmax_rows<F, B, false>(g, n_rows, n_cols, X, out, nullptr, nullptr, (cudaStream_t) stream)));
+	return rc;
+}
+
+extern "C" int dfb200_cross_entropy_loss(int bwd_dt, int n_rows, int n_cols, void * pred_logits, const uint32_t * labels, void * stream) {
+	if (!(bwd_dt == DATAFLOW_FP32 || bwd_dt == DATAFLOW_FP16 || bwd_dt == DATAFLOW_BF16))
+		return set_error(DFB200_ERR_DTYPE, "cross_entropy_loss: unsupported datatype %d", bwd_dt);
+	if (n_rows < 0 || n_cols <= 0) return set_error(DFB200_ERR_ARG, "cross_entropy_loss: bad shape %d x %d", n_rows, n_cols);
+	if (n_rows == 0) return DFB200_OK;
+	if (!pred_logits || !labels) return set_error(DFB200_ERR_ARG, "cross_entropy_loss: NULL tensor argument");
+	const int blocks = (n_rows + 255) / 256;
+	DFB200_DISPATCH_PAIR(bwd_dt, bwd_dt, F, B,
+		(cross_entropy_step_kernel<B><<<blocks, 256, 0, (cudaStream_t) stream>>>(n_rows, n_cols, pred_logits, labels)));
+	return check_launch("cross_entropy_loss");
+}
+
+extern "C" uint64_t dfb200_softmax_cross_entropy_workspace_bytes(int n_rows, int n_cols) {
+	(void) n_cols;
+	return n_rows > 0 ? (uint64_t) n_rows * sizeof(float) : 0;
+}
+
+extern "C" int dfb200_softmax_cross_entropy(int fwd_dt, int bwd_dt, int n_rows, int n_cols, const void * logits, const uint32_t * labels,
+                                            void * dlogits, float * row_loss, float * loss_sum, void * workspace, uint64_t workspace_bytes,
+                                            void * stream) {
+	SoftmaxGeometry g;
+	int rc = check_softmax("softmax_cross_entropy", fwd_dt, bwd_dt, n_rows, n_cols, logits, dlogits, &g);
+	if (rc || n_rows == 0) return rc;
+	if (!labels) return set_error(DFB200_ERR_ARG, "softmax_cross_entropy: NULL labels");
+	float * losses = row_loss;
+	if (!losses && loss_sum) {
+		if (!workspace || workspace_bytes < (uint64_t) n_rows * sizeof(float))
+			return set_error(DFB200_ERR_WORKSPACE, "softmax_cross_entropy: needs %llu bytes of workspace, got %llu",
+			                 (unsigned long long) n_rows * sizeof(float), (unsigned long long) workspace_bytes);
+		losses = reinterpret_cast<float *>(workspace);
+	}
+	rc = DFB200_ERR_DTYPE;
+	DFB200_DISPATCH_PAIR(fwd_dt, bwd_dt, F, B,
+		rc = (launch_softmax_rows<F, B, true>(g, n_rows, n_cols, logits, dlogits, labels, losses, (cudaStream_t) stream)));
+	if (rc) return rc;
+	if (loss_sum) {
+		loss_sum_kernel<<<1, 1024, 0, (cudaStream_t) stream>>>(n_rows, n_cols, losses, labels, loss_sum);
+		return check_launch("softmax_cross_entropy (loss sum)");
+	}
+	return DFB200_OK;
+}

@@ -1,0 +1,125 @@
+// SwiGLU forward and backward: pure streaming kernels (3 resp. 5 tensors, each touched once).
+// Every thread owns UNROLL chunks of 8 consecutive elements; all loads of a thread are issued
+// before the first use so that 2*UNROLL (fwd) / 3*UNROLL (bwd) 128-bit requests are in flight
+// per thread. The row structure is irrelevant (tensors are contiguous), so the kernels index
+// the flat element range.
+#include "common.cuh"
+
+namespace dfb200 {
+
+constexpr int SWIGLU_THREADS = 256;
+constexpr int E = 8;                       // elements per chunk
+
+// exp and divide are the approximate hardware forms (ex2.approx / rcp.approx based), the same
+// ones the reference build selects with --use_fast_math (src/ops/nvidia/Makefile:3-5).
+__device__ __forceinline__ float silu_and_e(float x, float & e) {
+	e = __expf(-x);
+	return __fdividef(x, 1.0f + e);
+}
+
+template <typename F, int UNROLL>
+__global__ void __launch_bounds__(SWIGLU_THREADS)
+swiglu_fwd_kernel(uint64_t n_chunks, const void * __restrict__ x_w1, const void * __restrict__ x_w3, void * __restrict__ out) {
+	const uint64_t first = (uint64_t) blockIdx.x * (SWIGLU_THREADS * UNROLL) + threadIdx.x;
+	float a[UNROLL][E], b[UNROLL][E];
+	#pragma unroll
+	for (int u = 0; u < UNROLL; u++) {
+		const uint64_t c = first + (uint64_t) u * SWIGLU_THREADS;
+		if (c < n_chunks) {
+			load_elems<F, E>(x_w1, c * E, a[u]);
+			load_elems<F, E>(x_w3, c * E, b[u]);
+		}
+	}
+	#pragma unroll
+	for (int u = 0; u < UNROLL; u++) {
+		const uint64_t c = first + (uint64_t) u * SWIGLU_THREADS;
+		if (c < n_chunks) {
+			float o[E];
+			#pragma unroll
+			for (int i = 0; i < E; i++) { float e; o[i] = silu_and_e(a[u][i], e) * b[u][i]; }
+			store_elems<F, E>(out, c * E, o);
+		}
+	}
+}
+
+// Reference arithmetic (src/ops/nvidia/activations/swiglu_bwd_x.cu:68-77), kept term for term:
+//   dX_w3 = dY * silu(x1);   dX_w1 = dY * ( (x3 * (1 + e + x1*e)) / ((1+e)*(1+e)) ),  e = exp(-x1)
+template <typename F, typename B, int UNROLL>
+__global__ void __launch_bounds__(SWIGLU_THREADS)
+swiglu_bwd_x_kernel(uint64_t n_chunks, const void * __restrict__ x_w1, const void * __restrict__ x_w3,
+                    const void * __restrict__ upstream_dX, void * __restrict__ dX_w1, void * __restrict__ dX_w3) {
+	const uint64_t first = (uint64_t) blockIdx.x * (SWIGLU_THREADS * UNROLL) + threadIdx.x;
+	float a[UNROLL][E], b[UNROLL][E], g[UNROLL][E];
+	#pragma unroll
+	for (int u = 0; u < UNROLL; u++) {
+		const uint64_t c = first + (uint64_t) u * SWIGLU_THREADS;
+		if (c < n_chunks) {
+			load_elems<F, E>(x_w1, c * E, a[u]);
+			load_elems<F, E>(x_w3, c * E, b[u]);
+			load_elems<B, E>(upstream_dX, c * E, g[u]);
+		}
+	}
+	#pragma unroll
+	for (int u = 0; u < UNROLL; u++) {
+		const uint64_t c = first + (uint64_t) u * SWIGLU_THREADS;
+		if (c < n_chunks) {
+			float d1[E], d3[E];
+			#pragma unroll
+			for (int i = 0; i < E; i++) {
+				float e;
+				const float x1 = a[u][i];
+				const float s = silu_and_e(x1, e);
+				const float ope = 1.0f + e;
+				d3[i] = g[u][i] * s;
+				d1[i] = g[u][i] * __fdividef(b[u][i] * (ope + x1 * e), ope * ope);
+			}
+			store_elems<B, E>(dX_w1, c * E, d1);
+			store_elems<B, E>(dX_w3, c * E, d3);
+		}
+	}
+}
+
+static int check_elementwise(const char * op, int num_rows, int num_cols, uint64_t * n_chunks, int n_ptrs, const void * const * ptrs) {
+	if (num_rows < 0 || num_cols < 0) return set_error(DFB200_ERR_ARG, "%s: negative shape %d x %d", op, num_rows, num_cols);
+	const uint64_t n = (uint64_t) num_rows * (uint64_t) num_cols;
+	if (n % E) return set_error(DFB200_ERR_ARG, "%s: num_rows*num_cols = %llu is not a multiple of %d", op, (unsigned long long) n, E);
+	for (int i = 0; i < n_ptrs; i++) {
+		if (n && !ptrs[i]) return set_error(DFB200_ERR_ARG, "%s: NULL tensor argument %d", op, i);
+		if (!aligned16(ptrs[i])) return set_error(DFB200_ERR_ARG, "%s: tensor argument %d is not 16-byte aligned", op, i);
+	}
+	*n_chunks = n / E;
+	return DFB200_OK;
+}
+
+}  // namespace dfb200
+
+using namespace dfb200;
+
+extern "C" int dfb200_swiglu(int fwd_dt, int num_rows, int num_cols, const void * x_w1, const void * x_w3, void * out, void * stream) {
+	if (!dtype_size(fwd_dt)) return set_error(DFB200_ERR_DTYPE, "swiglu: unsupported datatype %d", fwd_dt);
+	uint64_t n_chunks;
+	const void * ptrs[3] = {x_w1, x_w3, out};
+	int rc = check_elementwise("swiglu", num_rows, num_cols, &n_chunks, 3, ptrs);
+	if (rc || n_chunks == 0) return rc;
+	constexpr int UNROLL = 4;
+	const uint64_t blocks = (n_chunks + SWIGLU_THREADS * UNROLL - 1) / (SWIGLU_THREADS * UNROLL);
+	if (blocks > 0x7fffffffull) return set_error(DFB200_ERR_ARG, "swiglu: tensor too large");
+	DFB200_DISPATCH_DTYPE(fwd_dt, F,
+		(swiglu_fwd_kernel<F, UNROLL><<<(unsigned) blocks, SWIGLU_THREADS, 0, (cudaStream_t) stream>>>(n_chunks, x_w1, x_w3, out)));
+	return check_launch("swiglu");
+}
+
+extern "C" int dfb200_swiglu_bwd_x(int fwd_dt, int bwd_dt, int num_rows, int num_cols, const void * x_w1, const void * x_w3,
+                                   const void * upstream_dX, void * dX_w1, void * dX_w3, void * stream) {
+	if (!valid_fwd_bwd_pair(fwd_dt, bwd_dt)) return set_error(DFB200_ERR_DTYPE, "swiglu_bwd_x: unsupported datatype pair (%d, %d)", fwd_dt, bwd_dt);
+	uint64_t n_chunks;
+	const void * ptrs[5] = {x_w1, x_w3, upstream_dX, dX_w1, dX_w3};
+	int rc = check_elementwise("swiglu_bwd_x", num_rows, num_cols, &n_chunks, 5, ptrs);
+	if (rc || n_chunks == 0) return rc;
+	constexpr int UNROLL = 2;
+	const uint64_t blocks = (n_chunks + SWIGLU_THREADS * UNROLL - 1) / (SWIGLU_THREADS * UNROLL);
+	if (blocks > 0x7fffffffull) return set_error(DFB200_ERR_ARG, "swiglu_bwd_x: tensor too large");
+	DFB200_DISPATCH_PAIR(fwd_dt, bwd_dt, F, B,
+		(swiglu_bwd_x_kernel<F, B, UNROLL><<<(unsigned) blocks, SWIGLU_THREADS, 0, (cudaStream_t) stream>>>(n_chunks, x_w1, x_w3, upstream_dX, dX_w1, dX_w3)));
+	return check_launch("swiglu_bwd_x");
+}

@@ -1,0 +1,110 @@
+"""The C-ABI kernel launchers (include/dataflow_b200_kernels.h) on torch CUDA tensors.
+
+Function names and argument order mirror the reference's submit_* wrappers
+(src/dataflow_ops/include/dataflow_ops.h:146-215) minus the handle: tensors in place of device
+pointers, the current torch stream (or `stream=`) in place of a stream id. Nothing here computes:
+every call goes to the shared object and raises RuntimeError with the library's message on failure.
+"""
+import torch
+
+from . import _lib
+from .abi import DataflowDatatype as DT
+
+_lib_ = _lib.lib
+
+TORCH_TO_DT = {
+    torch.float32: DT.FP32, torch.float16: DT.FP16, torch.bfloat16: DT.BF16,
+    torch.float8_e4m3fn: DT.FP8E4M3, torch.float8_e5m2: DT.FP8E5M2,
+}
+
+
+def dt_of(t: torch.Tensor) -> int:
+    return int(TORCH_TO_DT[t.dtype])
+
+
+def _ptr(t):
+    if t is None:
+        return None
+    if not t.is_cuda:
+        raise ValueError("dataflow_lib_b200.ops works on CUDA tensors only (there is no CPU path)")
+    if not t.is_contiguous():
+        raise ValueError("tensor must be contiguous")
+    return t.data_ptr()
+
+
+def _stream(stream):
+    if stream is None:
+        return torch.cuda.current_stream().cuda_stream
+    return stream.cuda_stream if hasattr(stream, "cuda_stream") else int(stream)
+
+
+def _check(rc, what):
+    if rc != 0:
+        raise RuntimeError(f"{what} failed ({rc}): {_lib.last_error()}")
+
+
+_workspaces = {}
+
+
+def _workspace(device, nbytes):
+    """Per-device scratch that only grows (the C-ABI leaves allocation to the caller)."""
+    key = (device.type, device.index)
+    ws = _workspaces.get(key)
+    if ws is None or ws.numel() < nbytes:
+        ws = torch.empty(max(int(nbytes), 1 << 20), dtype=torch.uint8, device=device)
+        _workspaces[key] = ws
+    return ws
+
+
+def rms_norm(n_rows, n_cols, eps, rms_weight, X, out, weighted_sums=None, rms_vals=None, stream=None):
+    _check(_lib_.dfb200_rms_norm(dt_of(X), n_rows, n_cols, eps, _ptr(rms_weight), _ptr(X), _ptr(out),
+                                 _ptr(weighted_sums), _ptr(rms_vals), _stream(stream)), "rms_norm")
+
+
+def rms_norm_bwd_x(n_rows, n_cols, eps, fwd_weighted_sums, fwd_rms_vals, rms_weight, X_inp, upstream_dX, dX, stream=None):
+    _check(_lib_.dfb200_rms_norm_bwd_x(dt_of(X_inp), dt_of(dX), n_rows, n_cols, eps, _ptr(fwd_weighted_sums), _ptr(fwd_rms_vals),
+                                       _ptr(rms_weight), _ptr(X_inp), _ptr(upstream_dX), _ptr(dX), _stream(stream)), "rms_norm_bwd_x")
+
+
+def rms_norm_bwd_w(n_rows, n_cols, eps, fwd_rms_vals, X_inp, upstream_dX, dW, stream=None, workspace=None):
+    need = _lib_.dfb200_rms_norm_bwd_w_workspace_bytes(n_rows, n_cols)
+    ws = workspace if workspace is not None else _workspace(X_inp.device, need)
+    _check(_lib_.dfb200_rms_norm_bwd_w(dt_of(X_inp), dt_of(dW), n_rows, n_cols, eps, _ptr(fwd_rms_vals), _ptr(X_inp),
+                                       _ptr(upstream_dX), _ptr(dW), _ptr(ws), ws.numel() * ws.element_size(), _stream(stream)),
+           "rms_norm_bwd_w")
+
+
+def rope(N, model_dim, head_dim, num_kv_heads, theta, seq_positions, X_q, X_k, stream=None):
+    _check(_lib_.dfb200_rope(dt_of(X_q), N, model_dim, head_dim, num_kv_heads, theta, _ptr(seq_positions), _ptr(X_q), _ptr(X_k),
+                             _stream(stream)), "rope")
+
+
+def rope_bwd_x(N, model_dim, head_dim, num_kv_heads, theta, seq_positions, dX_q, dX_k, stream=None):
+    _check(_lib_.dfb200_rope_bwd_x(dt_of(dX_q), N, model_dim, head_dim, num_kv_heads, theta, _ptr(seq_positions), _ptr(dX_q),
+                                   _ptr(dX_k), _stream(stream)), "rope_bwd_x")
+
+
+def swiglu(num_rows, num_cols, x_w1, x_w3, out, stream=None):
+    _check(_lib_.dfb200_swiglu(dt_of(x_w1), num_rows, num_cols, _ptr(x_w1), _ptr(x_w3), _ptr(out), _stream(stream)), "swiglu")
+
+
+def swiglu_bwd_x(num_rows, num_cols, x_w1, x_w3, upstream_dX, dX_w1, dX_w3, stream=None):
+    _check(_lib_.dfb200_swiglu_bwd_x(dt_of(x_w1), dt_of(upstream_dX), num_rows, num_cols, _ptr(x_w1), _ptr(x_w3), _ptr(upstream_dX),
+                                     _ptr(dX_w1), _ptr(dX_w3), _stream(stream)), "swiglu_bwd_x")
+
+
+def softmax(n_rows, n_cols, X, out, stream=None):
+    _check(_lib_.dfb200_softmax(dt_of(X), dt_of(out), n_rows, n_cols, _ptr(X), _ptr(out), _stream(stream)), "softmax")
+
+
+def cross_entropy_loss(n_rows, n_cols, pred_logits, labels, stream=None):
+    _check(_lib_.dfb200_cross_entropy_loss(dt_of(pred_logits), n_rows, n_cols, _ptr(pred_logits), _ptr(labels), _stream(stream)),
+           "cross_entropy_loss")
+
+
+def softmax_cross_entropy(n_rows, n_cols, logits, labels, dlogits, row_loss=None, loss_sum=None, stream=None, workspace=None):
+    need = _lib_.dfb200_softmax_cross_entropy_workspace_bytes(n_rows, n_cols)
+    ws = workspace if workspace is not None else _workspace(logits.device, need)
+    _check(_lib_.dfb200_softmax_cross_entropy(dt_of(logits), dt_of(dlogits), n_rows, n_cols, _ptr(logits), _ptr(labels), _ptr(dlogits),
+                                              _ptr(row_loss), _ptr(loss_sum), _ptr(ws), ws.numel() * ws.element_size(),
+                                              _stream(stream)), "softmax_cross_entropy")

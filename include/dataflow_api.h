@@ -1,0 +1,126 @@
+/*
+ * dataflow_api.h -- host entry points of the library, with the names, argument meaning and
+ * return conventions of als244/dataflow_lib (int 0 = ok, -1 = error with a message on stderr;
+ * register_* return the number of functions added or -1; alloc_mem returns NULL on failure).
+ *
+ *   datatype helpers        src/datatype/include/dataflow_datatype.h:42-46, solo_conversion.h:6-16
+ *   fingerprints            src/fingerprint/include/fingerprint.h:12-30
+ *   hash table              src/table/include/table.h:73-102
+ *   handle                  src/dataflow_handle/nvidia/include/cuda_dataflow_handle.h:65-67
+ *   skeleton builders       src/set_ops/include/set_native_op_skeletons.h:11-32
+ *   submit_* wrappers       src/dataflow_ops/include/dataflow_ops.h:146-215
+ */
+#ifndef DATAFLOW_API_H
+#define DATAFLOW_API_H
+
+#include <stdio.h>
+#include "dataflow_abi.h"
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- datatypes ------------------------------------------------------------------------ */
+size_t dataflow_sizeof_element(DataflowDatatype arr_dtype);      /* 0 for scalar/none kinds */
+char * dataflow_datatype_as_string(DataflowDatatype dtype);      /* "BF16", ... ; "UNKNOWN" otherwise */
+/* fp32/fp16/bf16 array conversion on `num_threads` host threads; round-to-nearest-even. */
+int dataflow_convert_datatype(void * to, void * from, DataflowDatatype to_dt, DataflowDatatype from_dt, long n, int num_threads);
+float solo_bf16_to_fp32(uint16_t a);
+uint16_t solo_fp32_to_bf16(float f);
+float solo_fp16_to_fp32(uint16_t h);
+uint16_t solo_fp32_to_fp16(float f);
+uint16_t solo_fp16_to_bf16(uint16_t h);
+uint16_t solo_bf16_to_fp16(uint16_t a);
+
+/* ---- fingerprints --------------------------------------------------------------------- */
+typedef enum fingerprint_type {
+	SHA256_HASH = 0, SHA512_HASH = 1, SHA1_HASH = 2, MD5_HASH = 3, BLAKE3_HASH = 4
+} FingerprintType;
+
+void dataflow_sha256(const void * data, uint64_t num_bytes, uint8_t digest[32]);
+void do_fingerprinting(void * data, uint64_t num_bytes, uint8_t * ret_fingerprint, FingerprintType fingerprint_type);
+uint64_t fingerprint_to_least_sig64(uint8_t * fingerprint, int fingerprint_num_bytes);
+uint8_t get_fingerprint_num_bytes(FingerprintType fingerprint_type);
+char * get_fingerprint_type_name(FingerprintType fingerprint_type);
+void print_hex(uint8_t * fingerprint, int num_bytes);
+void print_sha256(uint8_t * fingerprint);
+
+/* ---- hash table ----------------------------------------------------------------------- */
+int init_table(Table * table, Hash_Func hash_func, uint64_t key_size_bytes, uint64_t value_size_bytes,
+               uint64_t min_table_size, uint64_t max_table_size, float load_factor, float shrink_factor);
+void destroy_table(Table * table);
+int insert_table(Table * table, void * key, void * value);
+/* Returns the slot index or -1. to_copy_value: the value is copied INTO the buffer `ret_value`
+ * points to; otherwise *ret_value is set to the value's address inside the table. */
+long find_table(Table * table, void * key, bool to_copy_value, void ** ret_value);
+int remove_table(Table * table, void * key, void * ret_value);
+
+/* ---- handle --------------------------------------------------------------------------- */
+/* Binds the handle to device `device_id`, creates `num_streams` non-blocking streams with one
+ * event each and an empty op table, and fills the function-pointer table. The handle uses the
+ * device's PRIMARY context (ctx_flags are applied to it when it is not yet active), so memory
+ * and streams are interchangeable with CUDA-runtime code in the same process. */
+int init_cuda_dataflow_handle(Dataflow_Handle * dataflow_handle, ComputeType compute_type, int device_id,
+                              int ctx_id, unsigned int ctx_flags,
+                              int num_streams, int * opt_stream_prios, char ** opt_stream_names);
+/* Not in the reference: releases streams, events, modules and the op table. */
+void destroy_cuda_dataflow_handle(Dataflow_Handle * dataflow_handle);
+
+/* ---- op skeletons and registration ---------------------------------------------------- */
+/* Registers the 54 (op x datatype) identities of the reference's native op set, plus this
+ * library's fused ops, on the handle. `native_function_code_filename` names the shared object
+ * that exports the ops (this library; NULL = the library containing this function);
+ * `native_function_config_filename` is accepted for source compatibility and ignored.
+ * Returns the number of ops registered. */
+int register_native_ops(Dataflow_Handle * dataflow_handle, char * native_function_code_filename, char * native_function_config_filename);
+int set_native_op_skeleton(Op_Skeleton * skeleton, char * op_name, DataflowDatatype fwd_dt, DataflowDatatype bwd_dt);
+void set_native_embedding_skeleton(Op_Skeleton * skeleton, DataflowDatatype fwd_datatype);
+void set_native_rms_norm_skeleton(Op_Skeleton * skeleton, DataflowDatatype fwd_datatype);
+void set_native_rms_norm_bwd_x_skeleton(Op_Skeleton * skeleton, DataflowDatatype fwd_datatype, DataflowDatatype bwd_datatype);
+void set_native_rms_norm_bwd_w_skeleton(Op_Skeleton * skeleton, DataflowDatatype fwd_datatype, DataflowDatatype bwd_datatype);
+void set_native_rope_skeleton(Op_Skeleton * skeleton, DataflowDatatype fwd_datatype);
+void set_native_rope_bwd_x_skeleton(Op_Skeleton * skeleton, DataflowDatatype bwd_datatype);
+void set_native_copy_to_seq_context_skeleton(Op_Skeleton * skeleton, DataflowDatatype fwd_datatype);
+void set_native_swiglu_skeleton(Op_Skeleton * skeleton, DataflowDatatype fwd_datatype);
+void set_native_swiglu_bwd_x_skeleton(Op_Skeleton * skeleton, DataflowDatatype fwd_datatype, DataflowDatatype bwd_datatype);
+void set_native_softmax_skeleton(Op_Skeleton * skeleton, DataflowDatatype fwd_datatype, DataflowDatatype bwd_datatype);
+void set_native_cross_entropy_loss_skeleton(Op_Skeleton * skeleton, DataflowDatatype bwd_datatype);
+/* Not in the reference: the fused softmax + cross-entropy op ("softmax_cross_entropy_<F>_<B>"). */
+void set_native_softmax_cross_entropy_skeleton(Op_Skeleton * skeleton, DataflowDatatype fwd_datatype, DataflowDatatype bwd_datatype);
+
+/* ---- op submission -------------------------------------------------------------------- */
+int submit_rms_norm(Dataflow_Handle * handle, int stream_id, DataflowDatatype fwd_dt,
+                    int n_rows, int n_cols, float eps,
+                    void * rms_weight, void * X, void * out, float * weighted_sums, float * rms_vals);
+int submit_rms_norm_bwd_x(Dataflow_Handle * handle, int stream_id, DataflowDatatype fwd_dt, DataflowDatatype bwd_dt,
+                          int n_rows, int n_cols, float eps,
+                          float * fwd_weighted_sums, float * fwd_rms_vals,
+                          void * rms_weight, void * X_inp, void * upstream_dX, void * dX);
+int submit_rms_norm_bwd_w(Dataflow_Handle * handle, int stream_id, DataflowDatatype fwd_dt, DataflowDatatype bwd_dt,
+                          int n_rows, int n_cols, float eps,
+                          float * fwd_rms_vals, void * X_inp, void * upstream_dX, void * dW);
+int submit_rope(Dataflow_Handle * handle, int stream_id, DataflowDatatype fwd_dt,
+                uint64_t N, int model_dim, int head_dim, int num_kv_heads, int theta,
+                int * seq_positions, void * X_q, void * X_k);
+int submit_rope_bwd_x(Dataflow_Handle * handle, int stream_id, DataflowDatatype bwd_dt,
+                      uint64_t N, int model_dim, int head_dim, int num_kv_heads, int theta,
+                      int * seq_positions, void * dX_q, void * dX_k);
+int submit_swiglu(Dataflow_Handle * handle, int stream_id, DataflowDatatype fwd_dt,
+                  int num_rows, int num_cols, void * x_w1, void * x_w3, void * out);
+int submit_swiglu_bwd_x(Dataflow_Handle * handle, int stream_id, DataflowDatatype fwd_dt, DataflowDatatype bwd_dt,
+                        int num_rows, int num_cols,
+                        void * x_w1, void * x_w3, void * upstream_dX, void * dX_w1, void * dX_w3);
+int submit_softmax(Dataflow_Handle * handle, int stream_id, DataflowDatatype fwd_dt, DataflowDatatype bwd_dt,
+                   int n_rows, int n_cols, void * X, void * out);
+int submit_cross_entropy_loss(Dataflow_Handle * handle, int stream_id, DataflowDatatype bwd_dt,
+                              int n_rows, int n_cols, void * pred_logits, uint32_t * labels);
+/* Not in the reference: one pass producing dlogits = softmax - onehot, per-row losses and
+ * {loss sum, valid-row count} (row_loss and loss_sum are optional device pointers). */
+int submit_softmax_cross_entropy(Dataflow_Handle * handle, int stream_id, DataflowDatatype fwd_dt, DataflowDatatype bwd_dt,
+                                 int n_rows, int n_cols, void * logits, uint32_t * labels, void * dlogits,
+                                 float * row_loss, float * loss_sum);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

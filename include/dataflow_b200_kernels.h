@@ -1,0 +1,119 @@
+/*
+ * dataflow_b200_kernels.h -- the C-ABI between host C code and the sm_100a kernels.
+ *
+ * Plain pointers and sizes only. Every function enqueues work on `stream` (a CUstream /
+ * cudaStream_t passed as void *, NULL = the legacy default stream) of the CURRENT device and
+ * returns without synchronising. Datatypes are DataflowDatatype values (dataflow_abi.h).
+ * Return value: DFB200_OK, or a negative DFB200_ERR_* code; dfb200_last_error() gives the
+ * message of the last failure on the calling thread. Nothing here falls back to the CPU.
+ *
+ * Each entry point replaces one family of `<op>_<dtype>_kernel` symbols of the reference's
+ * cubin together with its `<op>_set_launch_config` host function; the argument order after
+ * the datatypes is the reference kernel's parameter order.
+ *
+ * Alignment contract (checked, DFB200_ERR_ARG otherwise): tensor base pointers are 16-byte
+ * aligned and row lengths are multiples of 8 elements, so that every 8-element packet of a
+ * row (128 bits for 16-bit types, 2 x 128 for fp32, 64 for fp8) is naturally aligned.
+ */
+#ifndef DATAFLOW_B200_KERNELS_H
+#define DATAFLOW_B200_KERNELS_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define DFB200_OK             0
+#define DFB200_ERR_ARG       -1   /* NULL / misaligned pointer, bad size */
+#define DFB200_ERR_DTYPE     -2   /* datatype combination the op does not have */
+#define DFB200_ERR_CUDA      -3   /* launch or runtime error (message holds cudaGetErrorString) */
+#define DFB200_ERR_WORKSPACE -4   /* workspace missing or too small */
+
+const char * dfb200_last_error(void);
+
+/* Library build info: "sm_100a", and the SM count of the current device (0 if no device). */
+const char * dfb200_target_arch(void);
+int dfb200_sm_count(void);
+
+/* ---- RMSNorm ----------------------------------------------------------------------------
+ * Replaces rms_norm_<dt>_kernel (src/ops/nvidia/norm/rms_norm.cu:4,143,280,415,539) and
+ * rms_norm_set_launch_config / rms_norm_set_attribute_config (src/ops/nvidia/norm/rms_norm_config.c:3-79).
+ * out[r,i] = T( (f32(X[r,i]) * rms[r]) * f32(w[i]) ),  rms[r] = rsqrt(mean_i X[r,i]^2 + eps);
+ * weighted_sums[r] = sum_i w[i]*X[r,i] and rms_vals[r] = rms[r] are written when non-NULL. */
+int dfb200_rms_norm(int fwd_dt, int n_rows, int n_cols, float eps,
+                    const void * rms_weight, const void * X, void * out,
+                    float * weighted_sums, float * rms_vals, void * stream);
+
+/* Replaces rms_norm_bwd_x_<fwd>_<bwd>_kernel (src/ops/nvidia/norm/rms_norm_bwd_x.cu:4-590) and
+ * rms_norm_bwd_x_set_launch_config (src/ops/nvidia/norm/rms_norm_config.c:81-151).
+ * dX[r,i] += dY[r,i] * B( w[i]*rms[r] - (X[r,i]*rms[r]^3 / n_cols) * weighted_sums[r] )
+ * with the product and the sum each rounded to the bwd datatype B (the reference's formula,
+ * which accumulates into dX). */
+int dfb200_rms_norm_bwd_x(int fwd_dt, int bwd_dt, int n_rows, int n_cols, float eps,
+                          const float * fwd_weighted_sums, const float * fwd_rms_vals,
+                          const void * rms_weight, const void * X_inp,
+                          const void * upstream_dX, void * dX, void * stream);
+
+/* Replaces rms_norm_bwd_w_<fwd>_<bwd>_kernel (src/ops/nvidia/norm/rms_norm_bwd_w.cu:4-700) and
+ * rms_norm_bwd_w_set_launch_config (src/ops/nvidia/norm/rms_norm_config.c:154-222).
+ * dW[c] = B( f32(dW[c]) + sum_r f32(dY[r,c]) * f32(X[r,c]) * rms[r] ), reduced in fp32 in a
+ * fixed order (two launches, no atomics). Needs dfb200_rms_norm_bwd_w_workspace_bytes() bytes
+ * of 16-byte aligned device scratch; its contents on entry do not matter. */
+uint64_t dfb200_rms_norm_bwd_w_workspace_bytes(int n_rows, int n_cols);
+int dfb200_rms_norm_bwd_w(int fwd_dt, int bwd_dt, int n_rows, int n_cols, float eps,
+                          const float * fwd_rms_vals, const void * X_inp,
+                          const void * upstream_dX, void * dW,
+                          void * workspace, uint64_t workspace_bytes, void * stream);
+
+/* ---- RoPE -------------------------------------------------------------------------------
+ * Replaces rope_<dt>_kernel (src/ops/nvidia/attention/rope.cu:3,60,123,183,243), rope_bwd_x_<dt>_kernel
+ * (src/ops/nvidia/attention/rope_bwd_x.cu:3,62,120) and their launch configs
+ * (src/ops/nvidia/attention/attn_misc_config.c:3-53). N = tokens * model_dim. In place on
+ * X_q [tokens, model_dim] and X_k [tokens, num_kv_heads*head_dim]; interleaved pairs (2j, 2j+1)
+ * of each head are rotated by angle pos * theta^(-2j/head_dim); bwd applies the transpose. */
+int dfb200_rope(int fwd_dt, uint64_t N, int model_dim, int head_dim, int num_kv_heads, int theta,
+                const int * seq_positions, void * X_q, void * X_k, void * stream);
+int dfb200_rope_bwd_x(int bwd_dt, uint64_t N, int model_dim, int head_dim, int num_kv_heads, int theta,
+                      const int * seq_positions, void * dX_q, void * dX_k, void * stream);
+
+/* ---- SwiGLU -----------------------------------------------------------------------------
+ * Replaces swiglu_<dt>_kernel (src/ops/nvidia/activations/swiglu.cu:4-112), swiglu_bwd_x_<f>_<b>_kernel
+ * (src/ops/nvidia/activations/swiglu_bwd_x.cu:4-185) and src/ops/nvidia/activations/swiglu_config.c:4-50.
+ * out = silu(x_w1) * x_w3;  dX_w3 = dY*silu(x_w1);  dX_w1 = dY * x_w3 * dsilu(x_w1). */
+int dfb200_swiglu(int fwd_dt, int num_rows, int num_cols,
+                  const void * x_w1, const void * x_w3, void * out, void * stream);
+int dfb200_swiglu_bwd_x(int fwd_dt, int bwd_dt, int num_rows, int num_cols,
+                        const void * x_w1, const void * x_w3, const void * upstream_dX,
+                        void * dX_w1, void * dX_w3, void * stream);
+
+/* ---- softmax / cross entropy ------------------------------------------------------------
+ * dfb200_softmax replaces softmax_<f>_<b>_kernel (src/ops/nvidia/loss/softmax.cu:3-960) and
+ * softmax_set_launch_config (src/ops/nvidia/loss/loss_misc_config.c:3-26): row softmax with the
+ * reference's rounding points (max and x-max in the input type, 32 interleaved partial sums
+ * and the row total rounded to the input type). One HBM read and one write per element.
+ * dfb200_cross_entropy_loss replaces cross_entropy_loss_<dt>_kernel
+ * (src/ops/nvidia/loss/cross_entropy.cu:5,19,33) with its intended semantics:
+ * pred[r, labels[r]] -= 1 for every row r; rows whose label is >= n_cols are left untouched. */
+int dfb200_softmax(int fwd_dt, int bwd_dt, int n_rows, int n_cols,
+                   const void * X, void * out, void * stream);
+int dfb200_cross_entropy_loss(int bwd_dt, int n_rows, int n_cols,
+                              void * pred_logits, const uint32_t * labels, void * stream);
+
+/* Fused softmax + cross entropy, forward and backward in one pass over the logits (no
+ * counterpart in the reference, which runs the two kernels above back to back and never
+ * computes the loss value). dlogits = softmax(logits) - onehot(labels), bit-identical to
+ * dfb200_softmax followed by dfb200_cross_entropy_loss; row_loss[r] = log(sum_r) - (x[r,label]-max_r)
+ * in fp32 (optional); loss_sum[0] = sum_r row_loss[r] accumulated in fp64 in a fixed order and
+ * stored as fp32, loss_sum[1] = number of rows with a valid label (both optional, 2 floats).
+ * workspace: dfb200_softmax_cross_entropy_workspace_bytes() bytes of device scratch. */
+uint64_t dfb200_softmax_cross_entropy_workspace_bytes(int n_rows, int n_cols);
+int dfb200_softmax_cross_entropy(int fwd_dt, int bwd_dt, int n_rows, int n_cols,
+                                 const void * logits, const uint32_t * labels, void * dlogits,
+                                 float * row_loss, float * loss_sum,
+                                 void * workspace, uint64_t workspace_bytes, void * stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

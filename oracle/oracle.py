@@ -1,0 +1,150 @@
+"""numpy-level binding of oracle/liboracle.so -- the CPU restatement of the reference kernels' arithmetic
+(oracle/oracle.c). TEST INFRASTRUCTURE: imported only by tests/, __graft_entry__.smoke() and bench.py's
+CPU-baseline / reference arm.
+
+Arrays of 16-bit floats are numpy uint16 (raw bits), fp8 arrays numpy uint8, fp32 numpy float32.
+Datatype arguments are DataflowDatatype values (3 fp32, 4 fp16, 5 bf16, 6 e4m3, 7 e5m2)."""
+import ctypes as C
+import os
+import subprocess
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "liboracle.so")
+
+FP32, FP16, BF16, E4M3, E5M2 = 3, 4, 5, 6, 7
+NP_OF = {FP32: np.float32, FP16: np.uint16, BF16: np.uint16, E4M3: np.uint8, E5M2: np.uint8}
+
+
+def build():
+    subprocess.check_call(["make", "-s", "-C", _HERE, "all"])
+
+
+if not os.path.exists(LIB_PATH):
+    build()
+_lib = C.CDLL(LIB_PATH)
+
+_vp, _i, _f, _u64, _l = C.c_void_p, C.c_int, C.c_float, C.c_uint64, C.c_long
+_sig = {
+    "oracle_convert": (None, [_i, _vp, _i, _vp, _l]),
+    "oracle_rms_norm": (None, [_i, _i, _i, _f, _vp, _vp, _vp, _vp, _vp, _i]),
+    "oracle_rms_norm_bwd_x": (None, [_i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i]),
+    "oracle_rms_norm_bwd_w": (None, [_i, _i, _i, _i, _vp, _vp, _vp, _vp, _i, _i]),
+    "oracle_rope": (None, [_i, _u64, _i, _i, _i, _i, _vp, _vp, _vp, _i, _i]),
+    "oracle_swiglu": (None, [_i, _i, _i, _vp, _vp, _vp, _i]),
+    "oracle_swiglu_bwd_x": (None, [_i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _i]),
+    "oracle_softmax": (None, [_i, _i, _i, _i, _vp, _vp, _i]),
+    "oracle_cross_entropy_loss": (None, [_i, _i, _i, _vp, _vp]),
+    "oracle_softmax_cross_entropy": (None, [_i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _i]),
+    "oracle_fill_normal": (None, [_i, _vp, _l, _l, _u64, _f, _f, _i]),
+    "oracle_fill_labels": (None, [_vp, _l, _u64, C.c_uint32]),
+}
+for _n, (_r, _a) in _sig.items():
+    getattr(_lib, _n).restype = _r
+    getattr(_lib, _n).argtypes = _a
+
+N_THREADS = os.cpu_count() or 1
+
+
+def _p(a):
+    if a is None:
+        return None
+    assert a.flags["C_CONTIGUOUS"]
+    return a.ctypes.data
+
+
+def convert(to_dt, src, from_dt):
+    out = np.empty(src.shape, NP_OF[to_dt])
+    _lib.oracle_convert(to_dt, _p(out), from_dt, _p(src), src.size)
+    return out
+
+
+def to_f32(a, dt):
+    return a.astype(np.float32) if dt == FP32 else convert(FP32, a, dt)
+
+
+def from_f32(a, dt):
+    return np.ascontiguousarray(a, np.float32) if dt == FP32 else convert(dt, np.ascontiguousarray(a, np.float32), FP32)
+
+
+def fill_normal(dt, shape, seed, mean=0.0, std=1.0, threads=None):
+    """T(mean + std*z), z ~ N(0,1) a pure function of (seed, flat index)."""
+    shape = tuple(shape) if hasattr(shape, "__len__") else (shape,)
+    out = np.empty(shape, NP_OF[dt])
+    rows = shape[0] if len(shape) > 1 else 1
+    per = out.size // max(rows, 1)
+    _lib.oracle_fill_normal(dt, _p(out), rows, per, seed, mean, std, threads or N_THREADS)
+    return out
+
+
+def fill_labels(n, seed, n_classes):
+    out = np.empty(n, np.uint32)
+    _lib.oracle_fill_labels(_p(out), n, seed, n_classes)
+    return out
+
+
+def rms_norm(dt, eps, w, X, threads=None):
+    n_rows, n_cols = X.shape
+    out = np.empty_like(X)
+    ws = np.empty(n_rows, np.float32)
+    rms = np.empty(n_rows, np.float32)
+    _lib.oracle_rms_norm(dt, n_rows, n_cols, eps, _p(w), _p(X), _p(out), _p(ws), _p(rms), threads or N_THREADS)
+    return out, ws, rms
+
+
+def rms_norm_bwd_x(fwd_dt, bwd_dt, ws, rms, w, X, dY, dX, fused=False, threads=None):
+    """Returns the updated dX (dX is accumulated into; the input array is not modified)."""
+    n_rows, n_cols = X.shape
+    out = dX.copy()
+    _lib.oracle_rms_norm_bwd_x(fwd_dt, bwd_dt, n_rows, n_cols, _p(ws), _p(rms), _p(w), _p(X), _p(dY), _p(out), int(fused), threads or N_THREADS)
+    return out
+
+
+def rms_norm_bwd_w(fwd_dt, bwd_dt, rms, X, dY, dW, n_blocks=0, threads=None):
+    n_rows, n_cols = X.shape
+    out = dW.copy()
+    _lib.oracle_rms_norm_bwd_w(fwd_dt, bwd_dt, n_rows, n_cols, _p(rms), _p(X), _p(dY), _p(out), n_blocks, threads or N_THREADS)
+    return out
+
+
+def rope(dt, model_dim, head_dim, num_kv_heads, theta, pos, Xq, Xk, bwd=False, threads=None):
+    q, k = Xq.copy(), Xk.copy()
+    N = q.shape[0] * model_dim
+    _lib.oracle_rope(dt, N, model_dim, head_dim, num_kv_heads, theta, _p(np.ascontiguousarray(pos, np.int32)), _p(q), _p(k), int(bwd), threads or N_THREADS)
+    return q, k
+
+
+def swiglu(dt, x1, x3, threads=None):
+    out = np.empty_like(x1)
+    _lib.oracle_swiglu(dt, x1.shape[0], x1.shape[1], _p(x1), _p(x3), _p(out), threads or N_THREADS)
+    return out
+
+
+def swiglu_bwd_x(fwd_dt, bwd_dt, x1, x3, dY, threads=None):
+    d1, d3 = np.empty_like(dY), np.empty_like(dY)
+    _lib.oracle_swiglu_bwd_x(fwd_dt, bwd_dt, x1.shape[0], x1.shape[1], _p(x1), _p(x3), _p(dY), _p(d1), _p(d3), threads or N_THREADS)
+    return d1, d3
+
+
+def softmax(fwd_dt, bwd_dt, X, threads=None):
+    out = np.empty(X.shape, NP_OF[bwd_dt])
+    _lib.oracle_softmax(fwd_dt, bwd_dt, X.shape[0], X.shape[1], _p(X), _p(out), threads or N_THREADS)
+    return out
+
+
+def cross_entropy_loss(bwd_dt, pred, labels):
+    out = pred.copy()
+    _lib.oracle_cross_entropy_loss(bwd_dt, pred.shape[0], pred.shape[1], _p(out), _p(np.ascontiguousarray(labels, np.uint32)))
+    return out
+
+
+def softmax_cross_entropy(fwd_dt, bwd_dt, logits, labels, threads=None):
+    """Returns (dlogits, row_loss[n_rows] fp32, loss_sum[2] fp32 = {sum, valid rows})."""
+    n_rows, n_cols = logits.shape
+    dl = np.empty(logits.shape, NP_OF[bwd_dt])
+    row_loss = np.empty(n_rows, np.float32)
+    loss_sum = np.zeros(2, np.float32)
+    _lib.oracle_softmax_cross_entropy(fwd_dt, bwd_dt, n_rows, n_cols, _p(logits), _p(np.ascontiguousarray(labels, np.uint32)), _p(dl),
+                                      _p(row_loss), _p(loss_sum), threads or N_THREADS)
+    return dl, row_loss, loss_sum

@@ -1,0 +1,203 @@
+"""CPU tests of the host layer: the C-ABI library loads without a GPU and exports every declared symbol,
+the registry reproduces the reference's fingerprints (tests/golden/fingerprints.json, generated from the
+reference's own host sources), SHA-256 known answers, the hash table, datatype helpers, and the error
+behaviour of the handle API when no device is present."""
+import ctypes as C
+import json
+import os
+import re
+import subprocess
+
+import numpy as np
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+GOLDEN = json.load(open(os.path.join(ROOT, "tests", "golden", "fingerprints.json")))
+
+
+@pytest.fixture(scope="module")
+def L():
+    from dataflow_lib_b200 import _lib
+    return _lib.lib
+
+
+def test_library_exports_every_declared_symbol(L):
+    """Every function prototype in include/*.h must resolve in the shared object."""
+    declared = set()
+    for hdr in ("dataflow_b200_kernels.h", "dataflow_api.h"):
+        text = open(os.path.join(ROOT, "include", hdr)).read()
+        text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+        text = re.sub(r"typedef[^;]*;", "", text)
+        declared |= set(re.findall(r"\b([a-z_][a-z0-9_]*)\s*\([^;{]*\)\s*;", text))
+    declared -= {"defined"}
+    assert len(declared) > 60
+    missing = [n for n in sorted(declared) if not hasattr(L, n)]
+    assert not missing, f"declared in include/*.h but not exported: {missing}"
+    from dataflow_lib_b200 import _lib
+    bound = set(_lib.KERNEL_ABI) | set(_lib.HOST_ABI)
+    assert declared <= bound, f"no ctypes signature for {sorted(declared - bound)}"
+    assert L.dfb200_target_arch() == b"sm_100a"
+
+
+def test_library_has_no_undefined_cuda_driver_dependency():
+    """The library must load on a machine without libcuda (driver entry points are resolved lazily)."""
+    from dataflow_lib_b200 import _lib
+    out = subprocess.run(["ldd", _lib.LIB_PATH], capture_output=True, text=True).stdout
+    assert "libcuda.so" not in out and "libcudart" not in out and "not found" not in out, out
+
+
+def test_struct_layouts_match_reference(tmp_path):
+    """sizeof/offsetof of every ABI struct: include/dataflow_abi.h against the reference's headers (golden)."""
+    exe = str(tmp_path / "abi_layout")
+    subprocess.check_call(["gcc", f"-I{ROOT}/include", os.path.join(ROOT, "tests", "golden", "abi_layout.c"), "-o", exe])
+    mine = json.loads(subprocess.check_output([exe]))
+    assert mine == GOLDEN["layout"]
+    assert mine["sizeof(Op_Skeleton_Header)"] == 388 and mine["sizeof(Op_Skeleton)"] == 420 and mine["sizeof(Op)"] == 680
+    from dataflow_lib_b200 import abi           # the ctypes mirror used by the Python tests
+    assert C.sizeof(abi.OpSkeletonHeader) == 388 and C.sizeof(abi.OpSkeleton) == 420 and C.sizeof(abi.Op) == 680
+    assert C.sizeof(abi.Table) == mine["sizeof(Table)"] and C.sizeof(abi.CudaDeviceInfo) == mine["sizeof(Cuda_Device_Info)"]
+    assert C.sizeof(abi.CudaFunction) == mine["sizeof(Cuda_Function)"] and C.sizeof(abi.DataflowHandleStruct) == mine["sizeof(Dataflow_Handle)"]
+    assert abi.DataflowHandleStruct.op_table.offset == mine["offsetof(Dataflow_Handle,op_table)"]
+    assert abi.DataflowHandleStruct.submit_op.offset == mine["offsetof(Dataflow_Handle,submit_op)"]
+    assert abi.CudaFunction.op_skeleton.offset == mine["offsetof(Cuda_Function,op_skeleton)"]
+
+
+def test_sha256_known_answers(L):
+    """FIPS 180-4 example digests plus boundary lengths cross-checked against hashlib."""
+    import hashlib
+    out = (C.c_uint8 * 32)()
+    L.dataflow_sha256(b"abc", 3, out)
+    assert bytes(out).hex() == "ba7816bf8f01cfea414140de5dae2223b00361a396177a9cb410ff61f20015ad"
+    L.dataflow_sha256(b"", 0, out)
+    assert bytes(out).hex() == "e3b0c44298fc1c149afbf4c8996fb92427ae41e4649b934ca495991b7852b855"
+    rng = np.random.default_rng(0)
+    for n in (1, 55, 56, 57, 63, 64, 65, 119, 120, 127, 128, 388, 1000):
+        msg = rng.integers(0, 256, n, dtype=np.uint8).tobytes()
+        L.do_fingerprinting(msg, n, out, 0)
+        assert bytes(out) == hashlib.sha256(msg).digest(), n
+    fp = bytes(range(32))
+    assert L.fingerprint_to_least_sig64(fp, 32) == int.from_bytes(fp[24:], "big")
+    assert L.get_fingerprint_num_bytes(0) == 32 and L.get_fingerprint_type_name(0) == b"SHA256"
+
+
+def test_datatype_names_and_sizes_match_reference(L):
+    for k, name in GOLDEN["datatype_names"].items():
+        assert L.dataflow_datatype_as_string(int(k)).decode() == name, k
+    for k, size in GOLDEN["datatype_sizes"].items():
+        assert L.dataflow_sizeof_element(int(k)) == size, k
+
+
+def test_skeleton_fingerprints_match_reference(L):
+    """Every (op, datatype) identity of the reference: nickname, argument list and SHA-256 are bit-identical."""
+    from dataflow_lib_b200 import abi
+    assert len(GOLDEN["skeletons"]) == 59
+    seen = set()
+    for rec in GOLDEN["skeletons"]:
+        sk = abi.OpSkeleton()
+        C.memset(C.byref(sk), 0xCD, C.sizeof(sk))
+        assert L.set_native_op_skeleton(C.byref(sk), rec["op"].encode(), rec["fwd_dt"], rec["bwd_dt"]) == 0
+        assert sk.header.op_nickname.decode() == rec["nickname"]
+        assert sk.header.num_args == rec["num_args"]
+        assert list(sk.header.arg_dtypes) == rec["arg_dtypes"]
+        assert bytes(sk.identifier.fingerprint).hex() == rec["fingerprint"], rec["nickname"]
+        seen.add(rec["fingerprint"])
+    assert len(seen) == 59
+    # spot values quoted in the survey of the reference
+    by_nick = {r["nickname"]: r["fingerprint"] for r in GOLDEN["skeletons"]}
+    assert by_nick["rms_norm_BF16"] == "f1b2adb5a53567728addb01da4e7e41fbe1cf74ce1dc68feb65eb76628d8d5ad"
+    assert by_nick["swiglu_bwd_x_FP8E4M3_BF16"] == "32d7bf510467c9646f2f96c7c2af5c57df11a1cb364ae8b4dd561f1e5c95f904"
+    sk = abi.OpSkeleton()
+    assert L.set_native_op_skeleton(C.byref(sk), b"no_such_op", 3, 3) == -1
+    # the fused op has its own identity, distinct from every reference op
+    L.set_native_softmax_cross_entropy_skeleton(C.byref(sk), 5, 5)
+    assert sk.header.op_nickname == b"softmax_cross_entropy_BF16_BF16" and bytes(sk.identifier.fingerprint).hex() not in seen
+
+
+def test_hash_table(L):
+    """insert / find / duplicate / remove with collisions, growth and wrap-around."""
+    from dataflow_lib_b200 import abi
+    HASH = C.CFUNCTYPE(C.c_uint64, C.c_void_p, C.c_uint64)
+    hash_fn = HASH(lambda key, size: C.cast(key, C.POINTER(C.c_uint64))[0] % 7 % size)     # heavy collisions
+    t = abi.Table()
+    assert L.init_table(C.byref(t), C.cast(hash_fn, C.c_void_p), 8, 16, 8, 64, 0.5, 0.25) == 0
+    val = lambda k: (C.c_uint64 * 2)(k * 3, k * 5)
+    keys = list(range(100, 140))
+    for k in keys:
+        assert L.insert_table(C.byref(t), C.byref(C.c_uint64(k)), val(k)) == 0
+    assert t.cnt == 40 and t.size == 64
+    assert L.insert_table(C.byref(t), C.byref(C.c_uint64(105)), val(105)) == -1        # duplicate
+    ret = C.c_void_p()
+    for k in keys:
+        idx = L.find_table(C.byref(t), C.byref(C.c_uint64(k)), False, C.byref(ret))
+        assert idx >= 0 and C.cast(ret, C.POINTER(C.c_uint64))[0] == k * 3
+    buf = (C.c_uint64 * 2)()
+    assert L.find_table(C.byref(t), C.byref(C.c_uint64(117)), True, buf) >= 0 and list(buf) == [351, 585]
+    assert L.find_table(C.byref(t), C.byref(C.c_uint64(999)), False, C.byref(ret)) == -1 and not ret.value
+    for k in keys[::2]:
+        assert L.remove_table(C.byref(t), C.byref(C.c_uint64(k)), buf) == 0 and buf[0] == k * 3
+    assert L.remove_table(C.byref(t), C.byref(C.c_uint64(100)), buf) == -1
+    for k in keys:
+        found = L.find_table(C.byref(t), C.byref(C.c_uint64(k)), False, C.byref(ret)) >= 0
+        assert found == (k in keys[1::2]), k
+    assert t.cnt == 20
+    for k in range(200, 244):
+        assert L.insert_table(C.byref(t), C.byref(C.c_uint64(k)), val(k)) == 0
+    assert t.cnt == 64 and L.insert_table(C.byref(t), C.byref(C.c_uint64(500)), val(500)) == -1   # full at max size
+    L.destroy_table(C.byref(t))
+    assert not t.items
+
+
+def test_host_datatype_conversion(L):
+    """fp32 <-> bf16/fp16 round-to-nearest-even, against the oracle's converters (themselves checked against torch)."""
+    import oracle as O
+    import torch
+    rng = np.random.default_rng(1)
+    f = (rng.standard_normal(200000) * np.exp(rng.standard_normal(200000) * 6)).astype(np.float32)
+    f[:8] = [0.0, -0.0, np.inf, -np.inf, 65504.0, 65520.0, 1e-8, 6e-8]
+    for dt, tdt in ((5, torch.bfloat16), (4, torch.float16)):
+        out = np.empty(f.size, np.uint16)
+        assert L.dataflow_convert_datatype(out.ctypes.data, f.ctypes.data, dt, 3, f.size, 4) == 0
+        assert np.array_equal(out, O.from_f32(f, dt))
+        assert np.array_equal(out, torch.from_numpy(f).to(tdt).view(torch.int16).numpy().view(np.uint16))
+        back = np.empty(f.size, np.float32)
+        assert L.dataflow_convert_datatype(back.ctypes.data, out.ctypes.data, 3, dt, f.size, 3) == 0
+        assert np.array_equal(back.view(np.uint32), O.to_f32(out, dt).view(np.uint32))
+    assert L.solo_fp32_to_bf16(1.0) == 0x3F80 and L.solo_bf16_to_fp32(0x3F80) == 1.0
+    assert L.solo_fp32_to_fp16(1.0) == 0x3C00 and L.solo_fp16_to_fp32(0x3C00) == 1.0
+    assert L.solo_fp16_to_bf16(0x3C00) == 0x3F80 and L.solo_bf16_to_fp16(0x3F80) == 0x3C00
+    assert L.dataflow_convert_datatype(back.ctypes.data, out.ctypes.data, 6, 3, 4, 1) == -1    # no fp8 on the host, as in the reference
+
+
+def test_reference_host_conversion_agrees_where_it_is_rne():
+    """The reference's own converter (AVX-512 path, RNE) gives the same bf16/fp16 bits as this library's."""
+    ref_path = os.path.join(ROOT, "oracle", "_ref", "libref_host.so")
+    flags = open("/proc/cpuinfo").read()
+    if not os.path.exists(ref_path) or "avx512_bf16" not in flags or "avx512_fp16" not in flags:
+        pytest.skip("reference host library or AVX-512 bf16/fp16 not available here")
+    from dataflow_lib_b200 import _lib
+    ref = C.CDLL(ref_path)
+    ref.dataflow_convert_datatype.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_long, C.c_int]
+    f = (np.random.default_rng(2).standard_normal(1 << 16) * 3).astype(np.float32)
+    for dt in (5, 4):
+        a, b = np.empty(f.size, np.uint16), np.empty(f.size, np.uint16)
+        assert ref.dataflow_convert_datatype(a.ctypes.data, f.ctypes.data, dt, 3, f.size, 2) == 0
+        assert _lib.lib.dataflow_convert_datatype(b.ctypes.data, f.ctypes.data, dt, 3, f.size, 2) == 0
+        assert np.array_equal(a, b)
+
+
+def test_handle_api_fails_cleanly_without_a_device(L, capfd):
+    """No GPU here: init reports -1 (message on stderr) instead of crashing; submit on a dead handle is -1."""
+    import torch
+    if torch.cuda.is_available():
+        pytest.skip("a device is present")
+    from dataflow_lib_b200 import abi
+    h = abi.DataflowHandleStruct()
+    assert L.init_cuda_dataflow_handle(C.byref(h), abi.COMPUTE_CUDA, 0, 0, 0, 2, None, None) == -1
+    assert "Error" in capfd.readouterr().err
+    assert L.init_cuda_dataflow_handle(C.byref(h), abi.COMPUTE_CUDA, 0, 0, 0, 9999, None, None) == -1
+    assert L.submit_swiglu(C.byref(abi.DataflowHandleStruct()), 0, 5, 1, 8, None, None, None) == -1
+    assert L.register_native_ops(C.byref(abi.DataflowHandleStruct()), None, None) == -1
+    # the kernel launchers validate arguments before touching CUDA
+    assert L.dfb200_swiglu(5, 1, 7, None, None, None, None) == -1
+    assert b"multiple of 8" in L.dfb200_last_error()
+    assert L.dfb200_rms_norm(1, 1, 8, 1e-5, None, None, None, None, None, None) == -2
