@@ -1,0 +1,350 @@
+#!/usr/bin/env python
+"""Benchmark of the hot path: the Llama-3-8B-shaped elementwise op chain, forward + backward, bf16.
+
+    python bench.py --gpus N --steps K --warmup W            this library on N B200s (torchrun for N > 1)
+    python bench.py --impl reference --steps K --warmup W    the CPU arm: the reference has no host implementation
+                                                             of these ops, so the arm times the oracle port of its
+                                                             kernels' arithmetic on all host threads
+
+One step = one pass over one batch of 8192 tokens per GPU (weak scaling, token-sharded, no data-path collective;
+the RMSNorm weight gradient is all-reduced over NCCL at N > 1):
+    fwd  RMSNorm(d=4096) -> RoPE on Q [32 x 128] and K [8 x 128], theta 500000, positions 0..8191 -> SwiGLU [8192 x 14336]
+    bwd  SwiGLU bwd_x -> RoPE bwd_x -> RMSNorm bwd_x -> RMSNorm bwd_w
+submitted through the Dataflow_Handle API (submit_* -> registry lookup -> external op -> C-ABI launcher -> kernel).
+Synthetic seeded inputs (N(0,1); weight N(1, 0.02)). The working set of a step (1.7 GiB) is 13x the 126 MB L2.
+
+`value`   tokens/s with inputs resident in HBM, CUDA events on the handle's stream, max over ranks.
+`e2e`     the same chain with HOST buffers: every step copies its inputs from pinned host memory through
+          handle->submit_inbound_transfer, runs the ops, and reads the weight gradient and the per-row statistics
+          back through submit_outbound_transfer.
+`roofline` the dominant kernel (swiglu_bwd_x: 5 tensors x 14336 x 2 B per token), timed with events around each launch.
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+TOKENS, D_MODEL, N_HEADS, N_KV, HEAD_DIM, FFN, THETA, EPS = 8192, 4096, 32, 8, 128, 14336, 500000, 1e-5
+WORKLOAD = "llama3-8b layer elementwise chain fwd+bwd (RMSNorm d=4096 -> RoPE 32q/8kv x128 -> SwiGLU 14336), bf16, 8192 tokens/GPU"
+METRIC, UNIT = "tokens_per_s_op_chain", "tokens/s"
+
+# algorithmic HBM bytes per token of each op (bf16): what the op must read and write once
+BYTES_PER_TOKEN = {
+    "rms_norm": 2 * D_MODEL * 2 + 8, "rope": 2 * (N_HEADS + N_KV) * HEAD_DIM * 2 + 4, "swiglu": 3 * FFN * 2,
+    "swiglu_bwd_x": 5 * FFN * 2, "rope_bwd_x": 2 * (N_HEADS + N_KV) * HEAD_DIM * 2 + 4,
+    "rms_norm_bwd_x": 4 * D_MODEL * 2 + 8, "rms_norm_bwd_w": 2 * D_MODEL * 2 + 4,
+}
+KERNEL_LAUNCHES_PER_STEP = 8          # 7 ops; rms_norm_bwd_w is two launches
+DOMINANT = "swiglu_bwd_x"
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel from the ncu capture summarised in
+# profiles/ (None until a capture has been made)
+DOMINANT_DRAM_TRAFFIC_BYTES = None
+
+
+def measured_peak_hbm():
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured (MEASURED_PEAKS.json hbm_gbs)"
+    except Exception:
+        return 6650.0, "fallback (earlier measurement on this pool)"
+
+
+# ----------------------------------------------------------------------------------------------- CPU arm
+
+def cpu_chain_tokens_per_s(sample_tokens, threads):
+    """The oracle port of the chain on `sample_tokens` tokens; returns (tokens/s, seconds)."""
+    import numpy as np
+    import oracle as O
+    T = sample_tokens
+    X, w, dY = O.fill_normal(O.BF16, (T, D_MODEL), 1), O.fill_normal(O.BF16, (D_MODEL,), 2, 1.0, 0.02), O.fill_normal(O.BF16, (T, D_MODEL), 3)
+    Q, K = O.fill_normal(O.BF16, (T, N_HEADS * HEAD_DIM), 4), O.fill_normal(O.BF16, (T, N_KV * HEAD_DIM), 5)
+    g, u, dS = O.fill_normal(O.BF16, (T, FFN), 6), O.fill_normal(O.BF16, (T, FFN), 7), O.fill_normal(O.BF16, (T, FFN), 8)
+    pos = np.arange(T, dtype=np.int32)
+    dX, dW = np.zeros_like(X), np.zeros_like(w)
+    t0 = time.perf_counter()
+    _, ws, rms = O.rms_norm(O.BF16, EPS, w, X, threads=threads)
+    q, k = O.rope(O.BF16, N_HEADS * HEAD_DIM, HEAD_DIM, N_KV, THETA, pos, Q, K, threads=threads)
+    O.swiglu(O.BF16, g, u, threads=threads)
+    O.swiglu_bwd_x(O.BF16, O.BF16, g, u, dS, threads=threads)
+    O.rope(O.BF16, N_HEADS * HEAD_DIM, HEAD_DIM, N_KV, THETA, pos, q, k, bwd=True, threads=threads)
+    O.rms_norm_bwd_x(O.BF16, O.BF16, ws, rms, w, X, dY, dX, threads=threads)
+    O.rms_norm_bwd_w(O.BF16, O.BF16, rms, X, dY, dW, threads=threads)
+    dt = time.perf_counter() - t0
+    return T / dt, dt
+
+
+def cpu_baseline(target_seconds=12.0):
+    threads = os.cpu_count() or 1
+    rate, _ = cpu_chain_tokens_per_s(64, threads)                       # calibration
+    sample = int(min(TOKENS, max(64, rate * target_seconds)))
+    sample -= sample % 64
+    rate, secs = cpu_chain_tokens_per_s(sample, threads)
+    return {"value": rate, "unit": UNIT, "cores": threads, "kind": "port",
+            "sample": f"{sample} of {TOKENS} tokens of the same chain, oracle/oracle.c on {threads} threads, {secs:.1f} s"}
+
+
+def run_reference_arm(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    threads = os.cpu_count() or 1
+    rate, _ = cpu_chain_tokens_per_s(64, threads)
+    # a step is a bounded sample of the workload: about min(1 s, 150 s / K) of CPU work
+    sample = int(max(64, min(TOKENS, rate * min(1.0, 150.0 / max(args.steps, 1)))))
+    sample -= sample % 64
+    for _ in range(args.warmup):
+        cpu_chain_tokens_per_s(sample, threads)
+    times = []
+    for _ in range(args.steps):
+        _, secs = cpu_chain_tokens_per_s(sample, threads)
+        times.append(secs)
+    total = sum(times)
+    value = sample * args.steps / total
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": 1e3 * total / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic", "config": {"workload": WORKLOAD, "note": "the reference ships these ops only as CUDA kernels; this arm is the CPU port "
+                                        "of their arithmetic (oracle/oracle.c), each step a bounded sample of the workload (see cpu_baseline.sample)"},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": "port", "sample": f"{sample} tokens per step on {threads} threads"},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ----------------------------------------------------------------------------------------------- GPU arm
+
+class ClockSampler:
+    """nvidia-smi sampling of SM clock and throttle reasons while the timed regions run."""
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, uuid):
+        self.proc = None
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={uuid}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except Exception:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except Exception:
+            self.proc.kill()
+            out = ""
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in out.strip().splitlines():
+            p = [x.strip() for x in ln.split(",")]
+            if len(p) < 8:
+                continue
+            try:
+                sm.append(float(p[0])); mx.append(float(p[1]))
+            except ValueError:
+                continue
+            for name, v in zip(names, p[4:8]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        # idle samples (before/after the kernels) would drag the median down: keep the upper half
+        busy = sorted(sm)[len(sm) // 2:] if sm else []
+        return {"sm_mhz": statistics.median(busy) if busy else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def run_gpu_arm(args):
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+
+    import oracle as O   # input generation only (seeded fills); the timed path never touches it
+    from dataflow_lib_b200 import DataflowHandle
+    from dataflow_lib_b200.abi import DataflowDatatype as DT
+
+    rank, world, local = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1")), int(os.environ.get("LOCAL_RANK", "0"))
+    assert world == args.gpus, f"--gpus {args.gpus} but WORLD_SIZE={world} (launch N > 1 with torchrun)"
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+
+    h = DataflowHandle(device_id=local, num_streams=2)
+    stream = torch.cuda.ExternalStream(h.stream_ptr(0), device=torch.device("cuda", local))
+    BF, S0 = int(DT.BF16), 0
+    T = TOKENS
+
+    # ---- host inputs (seed 0 + rank for data, identical weights on all ranks), pinned through the handle
+    seed = 1000 * rank
+    host = {
+        "X": O.fill_normal(O.BF16, (T, D_MODEL), seed + 1), "w": O.fill_normal(O.BF16, (D_MODEL,), 2, 1.0, 0.02),
+        "dY": O.fill_normal(O.BF16, (T, D_MODEL), seed + 3), "Q": O.fill_normal(O.BF16, (T, N_HEADS * HEAD_DIM), seed + 4),
+        "K": O.fill_normal(O.BF16, (T, N_KV * HEAD_DIM), seed + 5), "gate": O.fill_normal(O.BF16, (T, FFN), seed + 6),
+        "up": O.fill_normal(O.BF16, (T, FFN), seed + 7), "dS": O.fill_normal(O.BF16, (T, FFN), seed + 8),
+        "pos": np.arange(T, dtype=np.int32),
+    }
+    for a in host.values():
+        assert h.enable_access_to_host_mem(a.ctypes.data, a.nbytes, 0) == 0
+    out_host = {"dW": np.zeros(D_MODEL, np.uint16), "rms": np.zeros(T, np.float32), "ws": np.zeros(T, np.float32)}
+    for a in out_host.values():
+        assert h.enable_access_to_host_mem(a.ctypes.data, a.nbytes, 0) == 0
+
+    dev = {k: torch.empty(v.shape, dtype=torch.int32 if k == "pos" else torch.bfloat16, device="cuda") for k, v in host.items()}
+    Y, dX = torch.empty_like(dev["X"]), torch.zeros_like(dev["X"])
+    S, d1, d3 = torch.empty_like(dev["gate"]), torch.empty_like(dev["gate"]), torch.empty_like(dev["gate"])
+    dW = torch.zeros(D_MODEL, dtype=torch.bfloat16, device="cuda")
+    ws, rms = torch.empty(T, device="cuda"), torch.empty(T, device="cuda")
+
+    def upload():
+        for k, a in host.items():
+            assert h.submit_inbound_transfer(S0, dev[k], a.ctypes.data, a.nbytes) == 0
+
+    op_names = ["rms_norm", "rope", "swiglu", "swiglu_bwd_x", "rope_bwd_x", "rms_norm_bwd_x", "rms_norm_bwd_w"]
+
+    DOM = op_names.index(DOMINANT)
+
+    def chain(events=None, only=None):
+        """One step. `events[i] = (start, end)` are recorded around op i (all ops, or just op `only`)."""
+        N = T * N_HEADS * HEAD_DIM
+        calls = [
+            lambda: h.submit_rms_norm(S0, BF, T, D_MODEL, EPS, dev["w"], dev["X"], Y, ws, rms),
+            lambda: h.submit_rope(S0, BF, N, N_HEADS * HEAD_DIM, HEAD_DIM, N_KV, THETA, dev["pos"], dev["Q"], dev["K"]),
+            lambda: h.submit_swiglu(S0, BF, T, FFN, dev["gate"], dev["up"], S),
+            lambda: h.submit_swiglu_bwd_x(S0, BF, BF, T, FFN, dev["gate"], dev["up"], dev["dS"], d1, d3),
+            lambda: h.submit_rope_bwd_x(S0, BF, N, N_HEADS * HEAD_DIM, HEAD_DIM, N_KV, THETA, dev["pos"], dev["Q"], dev["K"]),
+            lambda: h.submit_rms_norm_bwd_x(S0, BF, BF, T, D_MODEL, EPS, ws, rms, dev["w"], dev["X"], dev["dY"], dX),
+            lambda: h.submit_rms_norm_bwd_w(S0, BF, BF, T, D_MODEL, EPS, rms, dev["X"], dev["dY"], dW),
+        ]
+        for i, call in enumerate(calls):
+            timed = events is not None and (only is None or only == i)
+            if timed:
+                events[i][0].record(stream)
+            rc = call()
+            if timed:
+                events[i][1].record(stream)
+            if rc != 0:
+                raise RuntimeError(f"submit of {op_names[i]} failed")
+        if world > 1:
+            with torch.cuda.stream(stream):
+                dist.all_reduce(dW)                      # the data-parallel exchange: weight gradient, 8 KB
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    upload()
+    h.sync_stream(S0)
+    for _ in range(max(args.warmup, 3)):
+        chain()
+    barrier()
+
+    sampler = ClockSampler("GPU-" + str(torch.cuda.get_device_properties(local).uuid)) if rank == 0 else None
+
+    # ---- timed region 1: inputs resident in HBM. Only the dominant kernel is bracketed by events here (an event
+    # pair costs a few microseconds of stream serialisation, which seven pairs per 0.4 ms step would distort).
+    new_events = lambda: [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in op_names]
+    ev = [new_events() for _ in range(args.steps)]
+    t_begin, t_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    t_begin.record(stream)
+    for s in range(args.steps):
+        chain(ev[s], only=DOM)
+    t_end.record(stream)
+    barrier()
+    ms_total = t_begin.elapsed_time(t_end)
+    dom_ms = statistics.mean(ev[s][DOM][0].elapsed_time(ev[s][DOM][1]) for s in range(args.steps))
+
+    # ---- untimed pass: every op bracketed, for the per-op table (event-to-event times include launch latency)
+    prof_steps = min(args.steps, 50)
+    evp = [new_events() for _ in range(prof_steps)]
+    for s in range(prof_steps):
+        chain(evp[s])
+    barrier()
+    per_op_ms = {name: statistics.mean(evp[s][i][0].elapsed_time(evp[s][i][1]) for s in range(prof_steps)) for i, name in enumerate(op_names)}
+
+    # ---- timed region 2: end to end with host buffers through the handle's transfer calls
+    e2e_steps = max(3, min(args.steps, 10))
+    h2d = sum(a.nbytes for a in host.values())
+    d2h = sum(a.nbytes for a in out_host.values())
+
+    def e2e_step():
+        upload()
+        chain()
+        assert h.submit_outbound_transfer(S0, out_host["dW"].ctypes.data, dW, out_host["dW"].nbytes) == 0
+        assert h.submit_outbound_transfer(S0, out_host["rms"].ctypes.data, rms, out_host["rms"].nbytes) == 0
+        assert h.submit_outbound_transfer(S0, out_host["ws"].ctypes.data, ws, out_host["ws"].nbytes) == 0
+        h.sync_stream(S0)                                # the host consumes the result every step
+
+    e2e_step()
+    e_begin, e_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e_begin.record(stream)
+    for _ in range(e2e_steps):
+        e2e_step()
+    e_end.record(stream)
+    barrier()
+    ms_e2e = e_begin.elapsed_time(e_end)
+
+    clocks = sampler.stop() if sampler else None
+
+    times = torch.tensor([ms_total, ms_e2e], device="cuda", dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(times, op=dist.ReduceOp.MAX)
+    ms_total, ms_e2e = times.tolist()
+
+    if rank == 0:
+        peak, peak_src = measured_peak_hbm()
+        dom_bytes = BYTES_PER_TOKEN[DOMINANT] * T
+        achieved = dom_bytes / (dom_ms * 1e-3) / 1e9
+        ops_report = {name: {"ms": per_op_ms[name], "GB/s": BYTES_PER_TOKEN[name] * T / (per_op_ms[name] * 1e-3) / 1e9,
+                             "frac_of_peak": BYTES_PER_TOKEN[name] * T / (per_op_ms[name] * 1e-3) / 1e9 / peak} for name in op_names}
+        cpu = cpu_baseline() if world == 1 else None
+        line = {
+            "metric": METRIC, "value": world * T * args.steps / (ms_total * 1e-3), "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": ms_total / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": WORKLOAD, "tokens_per_gpu": T, "l2": "inputs larger than L2 (1.7 GiB touched per step vs 126 MB)",
+                       "parallelism": f"token-sharded x{world}" + (", NCCL all-reduce of the RMSNorm weight gradient" if world > 1 else "")},
+            "roofline": {"bound": "hbm", "kernel": DOMINANT, "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                         "traffic": DOMINANT_DRAM_TRAFFIC_BYTES, "algorithmic_bytes": dom_bytes, "peak_source": peak_src,
+                         "frac_of_nominal_8000": achieved / 8000.0},
+            "ops_event_bracketed": ops_report,
+            "e2e": {"value": world * T * e2e_steps / (ms_e2e * 1e-3), "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                    "steps": e2e_steps, "ms_per_step": ms_e2e / e2e_steps},
+            "gpu_launches": KERNEL_LAUNCHES_PER_STEP * args.steps,
+            "clocks": clocks,
+        }
+        if cpu is not None:
+            line["cpu_baseline"] = cpu
+        print(json.dumps(line), flush=True)
+
+    for a in list(host.values()) + list(out_host.values()):
+        h.disable_access_to_host_mem(a.ctypes.data)
+    h.close()
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference_arm(args)
+    else:
+        run_gpu_arm(args)
+
+
+if __name__ == "__main__":
+    main()

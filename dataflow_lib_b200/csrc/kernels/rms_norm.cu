@@ -13,9 +13,15 @@ namespace dfb200 {
 
 constexpr int E = 8;                 // elements per chunk
 constexpr int MAX_VPT = 8;
-// CTA width limit per VPT: rows up to 128*VPT chunks use <= 128 threads; only VPT == MAX_VPT grows wider.
-constexpr int max_threads_for(int vpt) { return vpt < MAX_VPT ? 128 : 512; }
 constexpr int MAX_COLS = MAX_VPT * 512 * E;
+// Threads that share one row, chosen by measurement on B200 (8192 x 4096 bf16, persistent grids):
+// forward 128 x 4 chunks (6.5 TB/s; 256 x 2: 5.9, 512 x 1: 4.7), backward-x 256 x 2 chunks (6.5 TB/s),
+// backward-w row groups of 256 x 2 chunks, four groups per CTA (5.5 TB/s for the partial sums).
+constexpr int FWD_ROW_THREADS = 128, BWD_X_ROW_THREADS = 256, BWD_W_ROW_THREADS = 256;
+// CTA width limits (launch bounds): a row uses ROW_THREADS threads until VPT reaches its maximum, then up to 512.
+constexpr int fwd_max_threads(int vpt) { return vpt < MAX_VPT ? FWD_ROW_THREADS : 512; }
+constexpr int bwd_x_max_threads(int vpt) { return vpt < MAX_VPT ? BWD_X_ROW_THREADS : 512; }
+constexpr int bwd_w_max_threads(int vpt) { return vpt <= 2 ? 1024 : 512; }
 
 template <typename T> struct RawChunk { uint32_t w[E / Word<T>::EPW]; };
 
@@ -50,7 +56,7 @@ __device__ __forceinline__ void block_sum2(float & a, float & b, float (*smem)[2
 // follows src/ops/nvidia/norm/rms_norm.cu:339-406
 // ----------------------------------------------------------------------------------------
 template <typename T, int VPT>
-__global__ void __launch_bounds__(max_threads_for(VPT))
+__global__ void __launch_bounds__(fwd_max_threads(VPT))
 rms_norm_fwd_kernel(int n_rows, int n_cols, float eps, const void * __restrict__ weight, const void * __restrict__ X,
                     void * __restrict__ out, float * __restrict__ weighted_sums, float * __restrict__ rms_vals) {
 	__shared__ float red[2][2][32];
@@ -116,22 +122,38 @@ rms_norm_fwd_kernel(int n_rows, int n_cols, float eps, const void * __restrict__
 
 // ----------------------------------------------------------------------------------------
 // backward-x:  dX += dY * B( w*r - ((x*r^3)/n) * ws )   follows
-// src/ops/nvidia/norm/rms_norm_bwd_x.cu:243-252 : the derivative is formed in fp32, rounded to
-// the backward type B, multiplied by dY in B (one rounding) and added to dX in B (one rounding).
-// For B = fp32 the multiply-add is a single fused fma, which is what nvcc makes of the
-// reference's `dX += dY * deriv`.
+// src/ops/nvidia/norm/rms_norm_bwd_x.cu:243-252 : the derivative is formed in fp32 and rounded
+// to the backward type B; the update dX + dY*B(deriv) is ONE fused multiply-add in B (a single
+// rounding), which is what the reference's `dX += dY * deriv` compiles to (fma.rn.bf16x2 /
+// fma.rn.f16x2 / fma.rn.f32) -- the reference kernels' outputs confirm it bit for bit.
+// 16-bit types stay packed: dY and dX words go straight into the paired fma.
 // ----------------------------------------------------------------------------------------
-template <typename B> __device__ __forceinline__ float accumulate_dx(float dx, float dy, float deriv) {
-	return round_to<B>(dx + round_to<B>(dy * round_to<B>(deriv)));
-}
-template <> __device__ __forceinline__ float accumulate_dx<f32_t>(float dx, float dy, float deriv) {
-	return fmaf(dy, deriv, dx);
-}
+template <typename B> struct FusedUpdate;
+template <> struct FusedUpdate<f32_t> {
+	static __device__ __forceinline__ uint32_t apply(uint32_t dx, uint32_t dy, const float * deriv) {
+		return __float_as_uint(fmaf(__uint_as_float(dy), deriv[0], __uint_as_float(dx)));
+	}
+};
+template <> struct FusedUpdate<bf16_t> {
+	static __device__ __forceinline__ uint32_t apply(uint32_t dx, uint32_t dy, const float * deriv) {
+		const __nv_bfloat162 d = __floats2bfloat162_rn(deriv[0], deriv[1]);
+		const __nv_bfloat162 r = __hfma2(*reinterpret_cast<const __nv_bfloat162 *>(&dy), d, *reinterpret_cast<const __nv_bfloat162 *>(&dx));
+		return *reinterpret_cast<const uint32_t *>(&r);
+	}
+};
+template <> struct FusedUpdate<f16_t> {
+	static __device__ __forceinline__ uint32_t apply(uint32_t dx, uint32_t dy, const float * deriv) {
+		const __half2 d = __floats2half2_rn(deriv[0], deriv[1]);
+		const __half2 r = __hfma2(*reinterpret_cast<const __half2 *>(&dy), d, *reinterpret_cast<const __half2 *>(&dx));
+		return *reinterpret_cast<const uint32_t *>(&r);
+	}
+};
 
 template <typename F, typename B, int VPT>
-__global__ void __launch_bounds__(max_threads_for(VPT))
+__global__ void __launch_bounds__(bwd_x_max_threads(VPT))
 rms_norm_bwd_x_kernel(int n_rows, int n_cols, const float * __restrict__ fwd_weighted_sums, const float * __restrict__ fwd_rms_vals,
                       const void * __restrict__ weight, const void * __restrict__ X, const void * __restrict__ dY, void * dX) {
+	constexpr int BEPW = Word<B>::EPW, BW = E / BEPW;
 	const int n_chunks = n_cols / E;
 	const int tid = threadIdx.x, nthr = blockDim.x;
 	const float n_cols_f = (float) n_cols;
@@ -163,14 +185,14 @@ rms_norm_bwd_x_kernel(int n_rows, int n_cols, const float * __restrict__ fwd_wei
 		for (int v = 0; v < VPT; v++) {
 			const int c = tid + v * nthr;
 			if (c < n_chunks) {
-				float x[E], g[E], d[E], w[E];
-				to_f32<F>(xr[v], x); to_f32<B>(gr[v], g); to_f32<B>(dr[v], d); to_f32<F>(wr[v], w);
+				float x[E], w[E], deriv[E];
+				to_f32<F>(xr[v], x); to_f32<F>(wr[v], w);
 				#pragma unroll
-				for (int i = 0; i < E; i++) {
-					const float deriv = (w[i] * r) - (__fdividef(x[i] * r3, n_cols_f) * ws);
-					d[i] = accumulate_dx<B>(d[i], g[i], deriv);
-				}
-				store_elems<B, E>(dX, (uint64_t) row * n_cols + (uint64_t) c * E, d);
+				for (int i = 0; i < E; i++) deriv[i] = (w[i] * r) - (__fdividef(x[i] * r3, n_cols_f) * ws);
+				uint32_t o[BW];
+				#pragma unroll
+				for (int k = 0; k < BW; k++) o[k] = FusedUpdate<B>::apply(dr[v].w[k], gr[v].w[k], &deriv[k * BEPW]);
+				st_words<BW>(reinterpret_cast<char *>(dX) + ((uint64_t) row * n_cols + (uint64_t) c * E) * (4 / BEPW), o);
 			}
 		}
 	}
@@ -184,7 +206,7 @@ rms_norm_bwd_x_kernel(int n_rows, int n_cols, const float * __restrict__ fwd_wei
 // The arithmetic per term follows src/ops/nvidia/norm/rms_norm_bwd_w.cu:295 (f32(dY)*f32(x)*r).
 // ----------------------------------------------------------------------------------------
 template <typename F, typename B, int VPT>
-__global__ void __launch_bounds__(512)
+__global__ void __launch_bounds__(bwd_w_max_threads(VPT))
 rms_norm_bwd_w_partial_kernel(int n_rows, int n_cols, int group_threads, const float * __restrict__ fwd_rms_vals,
                               const void * __restrict__ X, const void * __restrict__ dY, float * __restrict__ partials) {
 	extern __shared__ float group_sums[];      // [groups - 1][n_cols]
@@ -200,9 +222,10 @@ rms_norm_bwd_w_partial_kernel(int n_rows, int n_cols, int group_threads, const f
 		for (int i = 0; i < E; i++) acc[v][i] = 0.0f;
 
 	const int row_stride = gridDim.x * groups;
-	for (int row = blockIdx.x * groups + g; row < n_rows; row += row_stride) {
-		RawChunk<F> xr[VPT];
-		RawChunk<B> gr[VPT];
+	RawChunk<F> xr[VPT], xn[VPT];
+	RawChunk<B> gr[VPT], gn[VPT];
+	int row = blockIdx.x * groups + g;
+	if (row < n_rows) {
 		#pragma unroll
 		for (int v = 0; v < VPT; v++) {
 			const int c = tid + v * group_threads;
@@ -210,6 +233,20 @@ rms_norm_bwd_w_partial_kernel(int n_rows, int n_cols, int group_threads, const f
 				const uint64_t off = (uint64_t) row * n_cols + (uint64_t) c * E;
 				ld_raw<F>(X, off, xr[v]);
 				ld_raw<B>(dY, off, gr[v]);
+			}
+		}
+	}
+	for (; row < n_rows; row += row_stride) {
+		const int next_row = row + row_stride;
+		if (next_row < n_rows) {                     // next row's packets are requested before this row is consumed
+			#pragma unroll
+			for (int v = 0; v < VPT; v++) {
+				const int c = tid + v * group_threads;
+				if (c < n_chunks) {
+					const uint64_t off = (uint64_t) next_row * n_cols + (uint64_t) c * E;
+					ld_raw<F>(X, off, xn[v]);
+					ld_raw<B>(dY, off, gn[v]);
+				}
 			}
 		}
 		const float r = __ldg(fwd_rms_vals + row);
@@ -223,7 +260,10 @@ rms_norm_bwd_w_partial_kernel(int n_rows, int n_cols, int group_threads, const f
 				for (int i = 0; i < E; i++) acc[v][i] += gy[i] * x[i] * r;
 			}
 		}
+		#pragma unroll
+		for (int v = 0; v < VPT; v++) { xr[v] = xn[v]; gr[v] = gn[v]; }
 	}
+	cudaTriggerProgrammaticLaunchCompletion();       // the dependent (stage 2) may start being scheduled
 
 	if (g > 0) {
 		#pragma unroll
@@ -257,22 +297,28 @@ rms_norm_bwd_w_partial_kernel(int n_rows, int n_cols, int group_threads, const f
 }
 
 // backward-w, stage 2: dW[c] = B( f32(dW[c]) + sum_p partials[p][c] ). A CTA covers 32
-// columns with 8 slices of the partial rows; slices are combined in slice order.
+// columns with 32 slices of the partial rows (every thread a handful of independent loads);
+// slices are combined in slice order. Launched as a programmatic dependent of stage 1: its CTAs
+// are scheduled while stage 1 drains and block in cudaGridDependencySynchronize() until stage 1
+// has completed and its partial sums are visible, which hides the launch latency.
 template <typename B>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(1024)
 rms_norm_bwd_w_final_kernel(int n_cols, int n_partials, const float * __restrict__ partials, void * dW) {
-	__shared__ float slice_sum[8][32];
+	__shared__ float slice_sum[32][33];
 	const int lane = threadIdx.x & 31, slice = threadIdx.x >> 5;
 	const int col = blockIdx.x * 32 + lane;
+	cudaGridDependencySynchronize();
 	float s = 0.0f;
-	if (col < n_cols)
-		for (int p = slice; p < n_partials; p += 8) s += partials[(size_t) p * n_cols + col];
+	if (col < n_cols) {
+		#pragma unroll 4
+		for (int p = slice; p < n_partials; p += 32) s += partials[(size_t) p * n_cols + col];
+	}
 	slice_sum[slice][lane] = s;
 	__syncthreads();
 	if (slice == 0 && col < n_cols) {
 		float total = slice_sum[0][lane];
 		#pragma unroll
-		for (int k = 1; k < 8; k++) total += slice_sum[k][lane];
+		for (int k = 1; k < 32; k++) total += slice_sum[k][lane];
 		// element-wise read-modify-write of dW in its own type
 		if constexpr (Word<B>::EPW == 1) {
 			float * p = reinterpret_cast<float *>(dW) + col;
@@ -295,21 +341,22 @@ rms_norm_bwd_w_final_kernel(int n_cols, int n_partials, const float * __restrict
 struct RowGeometry { int vpt; int threads; };
 
 // Pick the chunks-per-thread (1,2,4,8) and the CTA width (multiple of 32) for a row of
-// n_chunks chunks: about 128 threads per row, wider only once VPT has reached its maximum.
-static bool row_geometry(int n_chunks, RowGeometry * geo) {
+// n_chunks chunks: about `row_threads` threads per row, wider (up to 512) only once VPT has
+// reached its maximum.
+static bool row_geometry(int n_chunks, int row_threads, RowGeometry * geo) {
 	int vpt = 1;
-	while (vpt < MAX_VPT && (n_chunks + vpt - 1) / vpt > 128) vpt *= 2;
+	while (vpt < MAX_VPT && (n_chunks + vpt - 1) / vpt > row_threads) vpt *= 2;
 	int threads = (n_chunks + vpt - 1) / vpt;
 	threads = (threads + 31) / 32 * 32;
-	if (threads > max_threads_for(vpt)) return false;
+	if (threads > (vpt < MAX_VPT ? row_threads : 512)) return false;
 	geo->vpt = vpt; geo->threads = threads;
 	return true;
 }
 
-static int check_rows(const char * op, int n_rows, int n_cols, RowGeometry * geo) {
+static int check_rows(const char * op, int n_rows, int n_cols, int row_threads, RowGeometry * geo) {
 	if (n_rows < 0 || n_cols <= 0) return set_error(DFB200_ERR_ARG, "%s: bad shape %d x %d", op, n_rows, n_cols);
 	if (n_cols % E) return set_error(DFB200_ERR_ARG, "%s: n_cols = %d is not a multiple of %d", op, n_cols, E);
-	if (!row_geometry(n_cols / E, geo))
+	if (!row_geometry(n_cols / E, row_threads, geo))
 		return set_error(DFB200_ERR_ARG, "%s: n_cols = %d exceeds the supported maximum of %d", op, n_cols, MAX_COLS);
 	return DFB200_OK;
 }
@@ -339,7 +386,7 @@ extern "C" int dfb200_rms_norm(int fwd_dt, int n_rows, int n_cols, float eps, co
                                float * weighted_sums, float * rms_vals, void * stream) {
 	if (!dtype_size(fwd_dt)) return set_error(DFB200_ERR_DTYPE, "rms_norm: unsupported datatype %d", fwd_dt);
 	RowGeometry geo;
-	int rc = check_rows("rms_norm", n_rows, n_cols, &geo);
+	int rc = check_rows("rms_norm", n_rows, n_cols, FWD_ROW_THREADS, &geo);
 	if (rc) return rc;
 	if (n_rows == 0) return DFB200_OK;
 	if (!rms_weight || !X || !out) return set_error(DFB200_ERR_ARG, "rms_norm: NULL tensor argument");
@@ -358,7 +405,7 @@ extern "C" int dfb200_rms_norm_bwd_x(int fwd_dt, int bwd_dt, int n_rows, int n_c
 	(void) eps;
 	if (!valid_fwd_bwd_pair(fwd_dt, bwd_dt)) return set_error(DFB200_ERR_DTYPE, "rms_norm_bwd_x: unsupported datatype pair (%d, %d)", fwd_dt, bwd_dt);
 	RowGeometry geo;
-	int rc = check_rows("rms_norm_bwd_x", n_rows, n_cols, &geo);
+	int rc = check_rows("rms_norm_bwd_x", n_rows, n_cols, BWD_X_ROW_THREADS, &geo);
 	if (rc) return rc;
 	if (n_rows == 0) return DFB200_OK;
 	if (!fwd_weighted_sums || !fwd_rms_vals || !rms_weight || !X_inp || !upstream_dX || !dX)
@@ -373,16 +420,10 @@ extern "C" int dfb200_rms_norm_bwd_x(int fwd_dt, int bwd_dt, int n_rows, int n_c
 	return check_launch("rms_norm_bwd_x");
 }
 
-// Stage-1 geometry of backward-w: one CTA of up to 512 threads per SM, split into row groups.
-// The 8*VPT fp32 accumulators per thread make VPT <= 4 the register-friendly choice, so wide rows
-// get wider groups before they get more packets per thread.
-static void bwd_w_geometry(int n_rows, int n_chunks, RowGeometry * geo, int * groups, int * grid) {
-	int vpt = 1;
-	while (vpt < 4 && (n_chunks + vpt - 1) / vpt > 128) vpt *= 2;
-	if ((n_chunks + vpt - 1) / vpt > 512) vpt = 8;
-	int threads = ((n_chunks + vpt - 1) / vpt + 31) / 32 * 32;
-	geo->vpt = vpt; geo->threads = threads;          // threads <= 512 because n_cols <= MAX_COLS
-	int g = 512 / threads;
+// Stage-1 geometry of backward-w: one CTA per SM, split into row groups of geo.threads threads.
+// The 8*VPT fp32 accumulators per thread limit the CTA to 1024 threads for VPT <= 2 and 512 beyond.
+static void bwd_w_geometry(int n_rows, const RowGeometry & geo, int * groups, int * grid) {
+	int g = bwd_w_max_threads(geo.vpt) / geo.threads;
 	if (g < 1) g = 1;
 	if (g > 8) g = 8;
 	while (g > 1 && g > n_rows) g /= 2;
@@ -408,13 +449,13 @@ extern "C" int dfb200_rms_norm_bwd_w(int fwd_dt, int bwd_dt, int n_rows, int n_c
 	(void) eps;
 	if (!valid_fwd_bwd_pair(fwd_dt, bwd_dt)) return set_error(DFB200_ERR_DTYPE, "rms_norm_bwd_w: unsupported datatype pair (%d, %d)", fwd_dt, bwd_dt);
 	RowGeometry geo;
-	int rc = check_rows("rms_norm_bwd_w", n_rows, n_cols, &geo);
+	int rc = check_rows("rms_norm_bwd_w", n_rows, n_cols, BWD_W_ROW_THREADS, &geo);
 	if (rc) return rc;
 	if (n_rows == 0) return DFB200_OK;
 	if (!fwd_rms_vals || !X_inp || !upstream_dX || !dW) return set_error(DFB200_ERR_ARG, "rms_norm_bwd_w: NULL tensor argument");
 	if (!aligned16(X_inp) || !aligned16(upstream_dX)) return set_error(DFB200_ERR_ARG, "rms_norm_bwd_w: tensors must be 16-byte aligned");
 	int groups, grid;
-	bwd_w_geometry(n_rows, n_cols / E, &geo, &groups, &grid);
+	bwd_w_geometry(n_rows, geo, &groups, &grid);
 	const uint64_t need = (uint64_t) grid * (uint64_t) n_cols * sizeof(float);
 	if (!workspace || workspace_bytes < need || !aligned16(workspace))
 		return set_error(DFB200_ERR_WORKSPACE, "rms_norm_bwd_w: needs %llu bytes of 16-byte aligned workspace, got %llu",
@@ -430,7 +471,20 @@ extern "C" int dfb200_rms_norm_bwd_w(int fwd_dt, int bwd_dt, int n_rows, int n_c
 	}));
 	rc = check_launch("rms_norm_bwd_w (partial sums)");
 	if (rc) return rc;
-	DFB200_DISPATCH_PAIR(fwd_dt, bwd_dt, F, B,
-		(rms_norm_bwd_w_final_kernel<B><<<(n_cols + 31) / 32, 256, 0, s>>>(n_cols, grid, partials, dW)));
-	return check_launch("rms_norm_bwd_w (final sum)");
+	{
+		cudaLaunchConfig_t cfg = {};
+		cfg.gridDim = dim3((n_cols + 31) / 32, 1, 1);
+		cfg.blockDim = dim3(1024, 1, 1);
+		cfg.stream = s;
+		cudaLaunchAttribute attr[1];
+		attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+		attr[0].val.programmaticStreamSerializationAllowed = 1;
+		cfg.attrs = attr; cfg.numAttrs = 1;
+		const float * cpartials = partials;
+		cudaError_t e = cudaErrorInvalidValue;
+		DFB200_DISPATCH_PAIR(fwd_dt, bwd_dt, F, B,
+			e = (cudaLaunchKernelEx(&cfg, rms_norm_bwd_w_final_kernel<B>, n_cols, grid, cpartials, dW)));
+		if (e != cudaSuccess) { cudaGetLastError(); return set_error(DFB200_ERR_CUDA, "rms_norm_bwd_w (final sum): %s", cudaGetErrorString(e)); }
+	}
+	return DFB200_OK;
 }

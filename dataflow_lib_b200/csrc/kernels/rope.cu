@@ -6,15 +6,32 @@
 // (token, frequency) for 32+8 heads. Here a CTA keeps the head_dim/2 inverse frequencies in
 // shared memory for its whole life, builds the (cos, sin) table of TOK tokens per iteration
 // (one sincosf per (token, frequency)), and then streams the TOK rows of Q and K through
-// registers in 128-bit packets, 4 packets in flight per thread. HBM traffic is one read and
-// one write of Q and K plus the positions.
+// registers in 128-bit packets. HBM traffic is one read and one write of Q and K plus the positions.
+//
+// Two kernels share that scheme:
+//   rope_staged_kernel  rows are staged through shared memory by bulk asynchronous copies (TMA
+//                       unit): the Q rows of TOK consecutive tokens are one contiguous block, so a
+//                       stage is two copies (Q block, K block) into a 4-deep ring; threads rotate
+//                       the pairs in place in shared memory and one thread writes the stage back
+//                       with a bulk store. Two to three stages (40-60 KB) are in flight per CTA
+//                       whatever the register budget, which an in-place register kernel cannot
+//                       reach (it cannot hoist a load above the previous store to the same tensor).
+//   rope_kernel         the register path, for shapes whose rows are not 16-byte multiples or do
+//                       not fit the ring.
 #include "common.cuh"
+#include "tma.cuh"
 
 namespace dfb200 {
 
 constexpr int E = 8;
-constexpr int ROPE_THREADS = 256;
-constexpr int ROPE_UNROLL = 4;
+#ifndef DFB200_ROPE_THREADS
+#define DFB200_ROPE_THREADS 512      /* measured on B200, 8192 tokens x (4096 + 1024): 512 x 1 = 5.7 TB/s, 256 x 4 = 5.1 TB/s */
+#define DFB200_ROPE_UNROLL 1
+#define DFB200_ROPE_MAX_TOK 8
+#endif
+constexpr int ROPE_THREADS = DFB200_ROPE_THREADS;
+constexpr int ROPE_UNROLL = DFB200_ROPE_UNROLL;
+constexpr int ROPE_MAX_TOK = DFB200_ROPE_MAX_TOK;       // tokens whose (cos, sin) table a CTA builds per iteration
 constexpr int ROPE_MAX_TABLE = 2048;       // (cos, sin) entries per buffer: TOK * head_dim / 2
 
 template <typename T, bool BWD>
@@ -99,6 +116,129 @@ rope_kernel(int tokens, int model_dim, int kv_dim, int head_dim, int tok_per_ite
 	}
 }
 
+// ----------------------------------------------------------------------------------------
+// staged kernel
+// ----------------------------------------------------------------------------------------
+constexpr int ROPE_STAGES = 4;
+constexpr int ROPE_STAGED_THREADS = 256;
+
+template <typename T, bool BWD>
+__global__ void __launch_bounds__(ROPE_STAGED_THREADS)
+rope_staged_kernel(int tokens, int model_dim, int kv_dim, int head_dim, int tok_per_stage, float theta,
+                   const int * __restrict__ seq_positions, void * X_q, void * X_k, unsigned int * status) {
+	constexpr int ESIZE = 4 / Word<T>::EPW;              // bytes per element
+	constexpr int CW = E / Word<T>::EPW;                 // 32-bit words per chunk
+	extern __shared__ __align__(128) unsigned char smem[];
+	const int half = head_dim >> 1;
+	const uint32_t q_stage_bytes = (uint32_t) tok_per_stage * model_dim * ESIZE;
+	const uint32_t k_stage_bytes = (uint32_t) tok_per_stage * kv_dim * ESIZE;
+	const uint32_t stage_bytes = (q_stage_bytes + k_stage_bytes + 127u) & ~127u;
+	unsigned char * ring = smem;                                                        // [STAGES][stage_bytes]
+	float2 * table = reinterpret_cast<float2 *>(smem + ROPE_STAGES * stage_bytes);      // [tok_per_stage * half]
+	float * inv_freq = reinterpret_cast<float *>(table + tok_per_stage * half);         // [half]
+	uint64_t * full = reinterpret_cast<uint64_t *>(inv_freq + ((half + 3) & ~3));       // [STAGES]
+	const int tid = threadIdx.x;
+
+	if (tid == 0) {
+		for (int s = 0; s < ROPE_STAGES; s++) mbar_init(&full[s], 1);
+		mbar_fence_init();
+	}
+	for (int j = tid; j < half; j += ROPE_STAGED_THREADS) {
+		const float expo = -1.0f * ((float) (2 * j) / (float) head_dim);
+		inv_freq[j] = (float) pow((double) theta, (double) expo);
+	}
+	__syncthreads();
+
+	// this CTA's iterations: token blocks blockIdx.x, + gridDim.x, ...
+	const int n_blocks = (tokens + tok_per_stage - 1) / tok_per_stage;
+	const int my_iters = blockIdx.x < n_blocks ? (n_blocks - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+	auto tok0_of = [&](int it) { return (blockIdx.x + it * (int) gridDim.x) * tok_per_stage; };
+	auto issue_load = [&](int it) {          // thread 0 only
+		const int s = it % ROPE_STAGES, tok0 = tok0_of(it), n_tok = min(tok_per_stage, tokens - tok0);
+		const uint32_t qb = (uint32_t) n_tok * model_dim * ESIZE, kb = (uint32_t) n_tok * kv_dim * ESIZE;
+		unsigned char * dst = ring + (size_t) s * stage_bytes;
+		mbar_arrive_expect_tx(&full[s], qb + kb);
+		bulk_load(dst, reinterpret_cast<const unsigned char *>(X_q) + (size_t) tok0 * model_dim * ESIZE, qb, &full[s]);
+		if (kb) bulk_load(dst + q_stage_bytes, reinterpret_cast<const unsigned char *>(X_k) + (size_t) tok0 * kv_dim * ESIZE, kb, &full[s]);
+	};
+	if (tid == 0)
+		for (int it = 0; it < ROPE_STAGES - 1 && it < my_iters; it++) issue_load(it);
+
+	const int q_chunks = model_dim / E, k_chunks = kv_dim / E, row_chunks = q_chunks + k_chunks;
+	const int chunks_per_head = head_dim / E;
+	const int head_mask = (chunks_per_head & (chunks_per_head - 1)) == 0 ? chunks_per_head - 1 : -1;
+	bool ok = true;
+	for (int it = 0; it < my_iters && ok; it++) {
+		const int s = it % ROPE_STAGES, tok0 = tok0_of(it), n_tok = min(tok_per_stage, tokens - tok0);
+		// (cos, sin) of this stage's tokens, while the copy is still in flight
+		for (int e = tid; e < n_tok * half; e += ROPE_STAGED_THREADS) {
+			const int t = e / half, j = e - t * half;
+			float sn, cs;
+			sincosf((float) __ldg(seq_positions + tok0 + t) * inv_freq[j], &sn, &cs);
+			table[e] = make_float2(cs, BWD ? -sn : sn);
+		}
+		ok = mbar_wait_bounded(&full[s], (uint32_t) (it / ROPE_STAGES) & 1u, status, 0x100u + (unsigned) s);
+		ok = __syncthreads_and(ok);            // table visible; everyone agrees on whether to go on
+		if (!ok) break;
+
+		// Rotate in place in shared memory. Token-major outer loop, chunk-strided inner loop: a chunk's
+		// slot in the (cos, sin) table depends only on its position inside its head, which for Q and K
+		// alike is (c mod chunks_per_head) because both sections hold whole heads -- no division in the
+		// inner loop when chunks_per_head is a power of two.
+		unsigned char * stage = ring + (size_t) s * stage_bytes;
+		for (int t = 0; t < n_tok; t++) {
+			unsigned char * q_row = stage + (size_t) t * model_dim * ESIZE;
+			unsigned char * k_row = stage + q_stage_bytes + (size_t) t * kv_dim * ESIZE - (size_t) q_chunks * E * ESIZE;
+			const float2 * tab_t = table + t * half;
+			for (int c = tid; c < row_chunks; c += ROPE_STAGED_THREADS) {
+				uint32_t * p = reinterpret_cast<uint32_t *>((c < q_chunks ? q_row : k_row) + (size_t) c * E * ESIZE);
+				const int in_head = head_mask >= 0 ? (c & head_mask) : (c % chunks_per_head);
+				uint32_t w[CW];
+				if constexpr (CW == 2) { const uint2 v = *reinterpret_cast<const uint2 *>(p); w[0] = v.x; w[1] = v.y; }
+				else {
+					#pragma unroll
+					for (int k = 0; k < CW; k += 4) { const uint4 v = *reinterpret_cast<const uint4 *>(p + k); w[k] = v.x; w[k + 1] = v.y; w[k + 2] = v.z; w[k + 3] = v.w; }
+				}
+				float x[E], o[E];
+				#pragma unroll
+				for (int k = 0; k < CW; k++) Word<T>::unpack(w[k], &x[k * Word<T>::EPW]);
+				const float4 * cs = reinterpret_cast<const float4 *>(tab_t + in_head * (E / 2));
+				const float4 cs01 = cs[0], cs23 = cs[1];
+				const float cv[4] = {cs01.x, cs01.z, cs23.x, cs23.z};
+				const float sv[4] = {cs01.y, cs01.w, cs23.y, cs23.w};
+				#pragma unroll
+				for (int q = 0; q < 4; q++) {
+					// one product rounded, the other fused into the sum: the contraction nvcc applies to the
+					// reference's `c*e - s*o` and `c*o + s*e`
+					o[2 * q]     = fmaf(cv[q], x[2 * q],     -__fmul_rn(sv[q], x[2 * q + 1]));
+					o[2 * q + 1] = fmaf(cv[q], x[2 * q + 1],  __fmul_rn(sv[q], x[2 * q]));
+				}
+				#pragma unroll
+				for (int k = 0; k < CW; k++) w[k] = Word<T>::pack(&o[k * Word<T>::EPW]);
+				if constexpr (CW == 2) *reinterpret_cast<uint2 *>(p) = make_uint2(w[0], w[1]);
+				else {
+					#pragma unroll
+					for (int k = 0; k < CW; k += 4) *reinterpret_cast<uint4 *>(p + k) = make_uint4(w[k], w[k + 1], w[k + 2], w[k + 3]);
+				}
+			}
+		}
+		fence_async_smem();                    // rotated values must be visible to the bulk store
+		__syncthreads();
+		if (tid == 0) {
+			const uint32_t qb = (uint32_t) n_tok * model_dim * ESIZE, kb = (uint32_t) n_tok * kv_dim * ESIZE;
+			bulk_store(reinterpret_cast<unsigned char *>(X_q) + (size_t) tok0 * model_dim * ESIZE, stage, qb);
+			if (kb) bulk_store(reinterpret_cast<unsigned char *>(X_k) + (size_t) tok0 * kv_dim * ESIZE, stage + q_stage_bytes, kb);
+			bulk_commit();
+			const int next = it + ROPE_STAGES - 1;       // refills the stage written back in the previous iteration
+			if (next < my_iters) {
+				bulk_wait_read<1>();                     // ... once that write-back no longer reads it
+				issue_load(next);
+			}
+		}
+	}
+	if (tid == 0) bulk_wait_all<0>();          // shared memory must outlive the write-backs
+}
+
 template <bool BWD>
 static int launch_rope(const char * op, int dt, uint64_t N, int model_dim, int head_dim, int num_kv_heads, int theta,
                        const int * seq_positions, void * X_q, void * X_k, void * stream) {
@@ -118,9 +258,40 @@ static int launch_rope(const char * op, int dt, uint64_t N, int model_dim, int h
 	if (!aligned16(X_q) || !aligned16(X_k)) return set_error(DFB200_ERR_ARG, "%s: tensors must be 16-byte aligned", op);
 	const int half = head_dim / 2;
 	if (half > ROPE_MAX_TABLE) return set_error(DFB200_ERR_ARG, "%s: head_dim %d too large", op, head_dim);
+
+	// staged path: rows must be 16-byte multiples (bulk copies) and four stages of at least one token must fit
+	{
+		const size_t esize = (size_t) dtype_size(dt);
+		const size_t row_bytes = ((size_t) model_dim + kv_dim) * esize;
+		const bool copyable = (model_dim * esize) % 16 == 0 && (kv_dim * esize) % 16 == 0;
+		int tok = (int) (24576 / row_bytes);
+		if (tok > 8) tok = 8;
+		if (tok > tokens) tok = tokens;
+		unsigned int * status = kernel_status_word(STATUS_ROPE);
+		if (copyable && tok >= 1 && status) {
+			const size_t stage_bytes = ((size_t) tok * row_bytes + 127) & ~(size_t) 127;
+			const size_t smem = ROPE_STAGES * stage_bytes + (size_t) tok * half * sizeof(float2) + (((size_t) half + 3) & ~(size_t) 3) * sizeof(float)
+			                    + ROPE_STAGES * sizeof(uint64_t);
+			int rc = DFB200_ERR_DTYPE;
+			DFB200_DISPATCH_DTYPE(dt, T, {
+				auto kernel = rope_staged_kernel<T, BWD>;
+				cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem);
+				int per_sm = 0;
+				if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, ROPE_STAGED_THREADS, smem) != cudaSuccess || per_sm < 1) { cudaGetLastError(); per_sm = 1; }
+				long long g = (long long) sm_count() * per_sm;
+				const long long blocks = ((long long) tokens + tok - 1) / tok;
+				if (g > blocks) g = blocks;
+				kernel<<<(int) (g < 1 ? 1 : g), ROPE_STAGED_THREADS, smem, (cudaStream_t) stream>>>(tokens, model_dim, kv_dim, head_dim, tok, (float) theta,
+				                                                                                  seq_positions, X_q, X_k, status);
+				rc = check_launch(op);
+			});
+			return rc;
+		}
+	}
+
 	int tok_per_iter = ROPE_THREADS / half;
 	if (tok_per_iter < 1) tok_per_iter = 1;
-	if (tok_per_iter > 8) tok_per_iter = 8;
+	if (tok_per_iter > ROPE_MAX_TOK) tok_per_iter = ROPE_MAX_TOK;
 	const size_t smem = (((size_t) half + 3) & ~(size_t) 3) * sizeof(float) + 2 * (size_t) tok_per_iter * half * sizeof(float2);
 	int grid = 0;
 	DFB200_DISPATCH_DTYPE(dt, T, {

@@ -1,6 +1,7 @@
 // Host-side support shared by all launchers: thread-local error text, cached device
 // properties, launch checking.
 #include "common.cuh"
+#include "tma.cuh"
 
 #include <stdarg.h>
 #include <string.h>
@@ -36,7 +37,36 @@ int check_launch(const char * what) {
 	return DFB200_OK;
 }
 
+static __device__ unsigned int g_kernel_status[STATUS_SLOTS];
+
+unsigned int * kernel_status_word(int slot) {
+	static unsigned int * base[64];          // per device
+	int dev = 0;
+	if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) { cudaGetLastError(); return nullptr; }
+	if (!base[dev]) {
+		void * p = nullptr;
+		if (cudaGetSymbolAddress(&p, g_kernel_status) != cudaSuccess) { cudaGetLastError(); return nullptr; }
+		base[dev] = static_cast<unsigned int *>(p);
+	}
+	return base[dev] + slot;
+}
+
 }  // namespace dfb200
+
+// Synchronises `stream`, returns the OR-free maximum of the kernels' status words (0 = every bounded
+// wait completed) and clears them. A non-zero value means a kernel gave up waiting for an
+// asynchronous copy or a peer; the value identifies the wait.
+extern "C" int dfb200_read_kernel_status(void * stream, unsigned int * status_words, int n_words) {
+	unsigned int host[dfb200::STATUS_SLOTS];
+	cudaError_t e = cudaStreamSynchronize((cudaStream_t) stream);
+	if (e == cudaSuccess) e = cudaMemcpyFromSymbol(host, dfb200::g_kernel_status, sizeof(host));
+	if (e != cudaSuccess) return dfb200::set_error(DFB200_ERR_CUDA, "read_kernel_status: %s", cudaGetErrorString(e));
+	unsigned int zero[dfb200::STATUS_SLOTS] = {0};
+	unsigned int worst = 0;
+	for (int i = 0; i < dfb200::STATUS_SLOTS; i++) { if (host[i] > worst) worst = host[i]; if (status_words && i < n_words) status_words[i] = host[i]; }
+	if (worst) cudaMemcpyToSymbol(dfb200::g_kernel_status, zero, sizeof(zero));
+	return (int) worst;
+}
 
 extern "C" const char * dfb200_last_error(void) { return dfb200::g_err; }
 extern "C" const char * dfb200_target_arch(void) { return "sm_100a"; }

@@ -32,6 +32,12 @@ extern "C" {
 
 const char * dfb200_last_error(void);
 
+/* Synchronises `stream` and returns the kernels' status: 0 when every bounded device-side wait
+ * (for an asynchronous copy) completed, otherwise a positive code naming the wait that gave up
+ * (also copied per kernel family into status_words[0..n_words) when non-NULL); negative on a
+ * CUDA error. The status words are cleared when non-zero. */
+int dfb200_read_kernel_status(void * stream, unsigned int * status_words, int n_words);
+
 /* Library build info: "sm_100a", and the SM count of the current device (0 if no device). */
 const char * dfb200_target_arch(void);
 int dfb200_sm_count(void);
@@ -48,8 +54,8 @@ int dfb200_rms_norm(int fwd_dt, int n_rows, int n_cols, float eps,
 /* Replaces rms_norm_bwd_x_<fwd>_<bwd>_kernel (src/ops/nvidia/norm/rms_norm_bwd_x.cu:4-590) and
  * rms_norm_bwd_x_set_launch_config (src/ops/nvidia/norm/rms_norm_config.c:81-151).
  * dX[r,i] += dY[r,i] * B( w[i]*rms[r] - (X[r,i]*rms[r]^3 / n_cols) * weighted_sums[r] )
- * with the product and the sum each rounded to the bwd datatype B (the reference's formula,
- * which accumulates into dX). */
+ * with the multiply-add done as one fused operation in the bwd datatype B, as the reference
+ * binary does (the reference's formula, which accumulates into dX). */
 int dfb200_rms_norm_bwd_x(int fwd_dt, int bwd_dt, int n_rows, int n_cols, float eps,
                           const float * fwd_weighted_sums, const float * fwd_rms_vals,
                           const void * rms_weight, const void * X_inp,

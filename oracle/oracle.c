@@ -219,8 +219,9 @@ void oracle_rms_norm(int dt, int n_rows, int n_cols, float eps, const void * w, 
  * RMSNorm backward-x -- src/ops/nvidia/norm/rms_norm_bwd_x.cu:243-252
  *   deriv = (w*r) - (((x*r^3)/n) * ws)          fp32
  *   dX   += dY * B(deriv)                        in the backward type B
- * fused == 0: product and sum are rounded to B separately (mul.bf16 then add.bf16);
- * fused == 1: one rounding of dX + dY*B(deriv) (what an fma.bf16 contraction gives).
+ * fused == 1: one rounding of dX + dY*B(deriv) -- the fma.rn.bf16x2 / f16x2 the reference binary executes (its outputs
+ *             in tests/golden/reference_vectors.npz match this variant bit for bit);
+ * fused == 0: product and sum rounded to B separately (the C++ expression read literally), kept for comparison.
  * For B = fp32 the update is a single fmaf either way.
  * ---------------------------------------------------------------------------------------- */
 

@@ -93,8 +93,9 @@ def rms_norm(dt, eps, w, X, threads=None):
     return out, ws, rms
 
 
-def rms_norm_bwd_x(fwd_dt, bwd_dt, ws, rms, w, X, dY, dX, fused=False, threads=None):
-    """Returns the updated dX (dX is accumulated into; the input array is not modified)."""
+def rms_norm_bwd_x(fwd_dt, bwd_dt, ws, rms, w, X, dY, dX, fused=True, threads=None):
+    """Returns the updated dX (dX is accumulated into; the input array is not modified). fused=True is the single-rounding
+    multiply-add the reference binary executes; fused=False rounds product and sum separately."""
     n_rows, n_cols = X.shape
     out = dX.copy()
     _lib.oracle_rms_norm_bwd_x(fwd_dt, bwd_dt, n_rows, n_cols, _p(ws), _p(rms), _p(w), _p(X), _p(dY), _p(out), int(fused), threads or N_THREADS)

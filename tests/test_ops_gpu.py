@@ -69,15 +69,14 @@ def test_rms_norm_bwd_x(ops, pair, shape, zero_dx):
     dY = fill(bdt, shape, 3)
     dX0 = np.zeros(shape, O.NP_OF[bdt]) if zero_dx else fill(bdt, shape, 4)
     _, ws, rms = O.rms_norm(fdt, 1e-5, w, X)
-    ref = O.rms_norm_bwd_x(fdt, bdt, ws, rms, w, X, dY, dX0, fused=False)
-    ref_fused = O.rms_norm_bwd_x(fdt, bdt, ws, rms, w, X, dY, dX0, fused=True)
+    ref = O.rms_norm_bwd_x(fdt, bdt, ws, rms, w, X, dY, dX0, fused=True)
     dX = to_dev(dX0, bdt)
     ops.rms_norm_bwd_x(n_rows, n_cols, 1e-5, torch.from_numpy(ws).cuda(), torch.from_numpy(rms).cuda(), to_dev(w, fdt), to_dev(X, fdt),
                        to_dev(dY, bdt), dX)
     torch.cuda.synchronize()
     got = to_host(dX, bdt)
-    check_lowp(got, ref, bdt, "rms_norm_bwd_x dX", rel=rel_for(bdt))
-    check_lowp(got, ref_fused, bdt, "rms_norm_bwd_x dX (fused-rounding variant)", rel=rel_for(bdt))
+    frac = check_lowp(got, ref, bdt, "rms_norm_bwd_x dX", rel=rel_for(bdt))
+    assert bdt == O.FP32 or frac > 0.99, f"only {frac:.4f} of dX bit-identical to the oracle"
 
 
 @pytest.mark.parametrize("pair", PAIRS, ids=lambda p: f"{DT_NAME[p[0]]}_{DT_NAME[p[1]]}")
@@ -182,7 +181,7 @@ def test_softmax(ops, pair, shape):
     torch.cuda.synchronize()
     # probabilities span many decades: the floor is the smallest normal step the type resolves near 1/n_cols
     frac = check_lowp(to_host(out, bdt), ref, bdt, "softmax out", rel=rel_for(bdt) if bdt != O.FP32 else 1e-4, scale=1.0 / shape[1])
-    assert frac > 0.9, f"only {frac:.3f} of the probabilities are bit-identical to the oracle"
+    assert bdt == O.FP32 or frac > 0.9, f"only {frac:.3f} of the probabilities are bit-identical to the oracle"
 
 
 @pytest.mark.parametrize("bdt", BWD_DTS, ids=lambda d: DT_NAME[d])
@@ -260,3 +259,12 @@ def test_bad_arguments_are_rejected(ops):
     with pytest.raises(RuntimeError, match="workspace"):
         ops.rms_norm_bwd_w(4, 64, 1e-5, torch.ones(4, device="cuda"), x, x, w.clone(), workspace=torch.empty(16, dtype=torch.uint8, device="cuda"))
     torch.cuda.synchronize()
+
+
+def test_no_bounded_wait_gave_up(ops):
+    """Kernels that wait on asynchronous copies record a status word when a wait runs out; after all the tests above it is 0."""
+    from dataflow_lib_b200 import _lib
+    import ctypes
+    words = (ctypes.c_uint * 8)()
+    rc = _lib.lib.dfb200_read_kernel_status(None, words, 8)
+    assert rc == 0, (rc, list(words), _lib.last_error())
