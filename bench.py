@@ -210,18 +210,26 @@ def run_gpu_arm(args):
 
     DOM = op_names.index(DOMINANT)
 
+    # The submissions of one step, bound once: the C entry points (submit_* of include/dataflow_api.h) with plain
+    # integer pointers, so that the per-step host work is the C path (skeleton + SHA-256 + table lookup + launch)
+    # and not Python argument marshalling.
+    import ctypes as C
+    from dataflow_lib_b200 import _lib as _dl
+    L, hp = _dl.lib, C.byref(h.h)
+    P = {k: v.data_ptr() for k, v in dev.items()}
+    N = T * N_HEADS * HEAD_DIM
+    calls = [
+        lambda: L.submit_rms_norm(hp, S0, BF, T, D_MODEL, EPS, P["w"], P["X"], Y.data_ptr(), ws.data_ptr(), rms.data_ptr()),
+        lambda: L.submit_rope(hp, S0, BF, N, N_HEADS * HEAD_DIM, HEAD_DIM, N_KV, THETA, P["pos"], P["Q"], P["K"]),
+        lambda: L.submit_swiglu(hp, S0, BF, T, FFN, P["gate"], P["up"], S.data_ptr()),
+        lambda: L.submit_swiglu_bwd_x(hp, S0, BF, BF, T, FFN, P["gate"], P["up"], P["dS"], d1.data_ptr(), d3.data_ptr()),
+        lambda: L.submit_rope_bwd_x(hp, S0, BF, N, N_HEADS * HEAD_DIM, HEAD_DIM, N_KV, THETA, P["pos"], P["Q"], P["K"]),
+        lambda: L.submit_rms_norm_bwd_x(hp, S0, BF, BF, T, D_MODEL, EPS, ws.data_ptr(), rms.data_ptr(), P["w"], P["X"], P["dY"], dX.data_ptr()),
+        lambda: L.submit_rms_norm_bwd_w(hp, S0, BF, BF, T, D_MODEL, EPS, rms.data_ptr(), P["X"], P["dY"], dW.data_ptr()),
+    ]
+
     def chain(events=None, only=None):
         """One step. `events[i] = (start, end)` are recorded around op i (all ops, or just op `only`)."""
-        N = T * N_HEADS * HEAD_DIM
-        calls = [
-            lambda: h.submit_rms_norm(S0, BF, T, D_MODEL, EPS, dev["w"], dev["X"], Y, ws, rms),
-            lambda: h.submit_rope(S0, BF, N, N_HEADS * HEAD_DIM, HEAD_DIM, N_KV, THETA, dev["pos"], dev["Q"], dev["K"]),
-            lambda: h.submit_swiglu(S0, BF, T, FFN, dev["gate"], dev["up"], S),
-            lambda: h.submit_swiglu_bwd_x(S0, BF, BF, T, FFN, dev["gate"], dev["up"], dev["dS"], d1, d3),
-            lambda: h.submit_rope_bwd_x(S0, BF, N, N_HEADS * HEAD_DIM, HEAD_DIM, N_KV, THETA, dev["pos"], dev["Q"], dev["K"]),
-            lambda: h.submit_rms_norm_bwd_x(S0, BF, BF, T, D_MODEL, EPS, ws, rms, dev["w"], dev["X"], dev["dY"], dX),
-            lambda: h.submit_rms_norm_bwd_w(S0, BF, BF, T, D_MODEL, EPS, rms, dev["X"], dev["dY"], dW),
-        ]
         for i, call in enumerate(calls):
             timed = events is not None and (only is None or only == i)
             if timed:
@@ -254,10 +262,12 @@ def run_gpu_arm(args):
     ev = [new_events() for _ in range(args.steps)]
     t_begin, t_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
+    host_t0 = time.perf_counter()
     t_begin.record(stream)
     for s in range(args.steps):
         chain(ev[s], only=DOM)
     t_end.record(stream)
+    host_enqueue_ms = 1e3 * (time.perf_counter() - host_t0) / args.steps      # host time to submit one step (no sync)
     barrier()
     ms_total = t_begin.elapsed_time(t_end)
     dom_ms = statistics.mean(ev[s][DOM][0].elapsed_time(ev[s][DOM][1]) for s in range(args.steps))
@@ -320,6 +330,7 @@ def run_gpu_arm(args):
             "e2e": {"value": world * T * e2e_steps / (ms_e2e * 1e-3), "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "steps": e2e_steps, "ms_per_step": ms_e2e / e2e_steps},
             "gpu_launches": KERNEL_LAUNCHES_PER_STEP * args.steps,
+            "host_enqueue_ms_per_step": host_enqueue_ms,
             "clocks": clocks,
         }
         if cpu is not None:

@@ -22,6 +22,11 @@ namespace dfb200 {
 int set_error(int code, const char * fmt, ...);     // stores a thread-local message, returns code
 int sm_count();                                      // SMs of the current device (cached per device)
 int check_launch(const char * what);                 // cudaGetLastError -> DFB200_ERR_CUDA or OK
+// Resident CTAs per SM of `kernel` at this launch shape on the current device (>= 1); the driver query is made
+// once per (kernel, threads, shared memory, device) and remembered.
+int ctas_per_sm(const void * kernel, int threads, size_t dyn_smem);
+// Opts `kernel` in to `dyn_smem` bytes of dynamic shared memory (needed above 48 KB); remembered per kernel and device.
+void allow_dyn_smem(const void * kernel, size_t dyn_smem);
 
 static inline bool aligned16(const void * p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 

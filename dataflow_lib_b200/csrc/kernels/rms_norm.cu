@@ -371,8 +371,7 @@ static int check_rows(const char * op, int n_rows, int n_cols, int row_threads, 
 
 // Grid of a persistent row kernel: every SM filled to the occupancy the kernel reaches.
 template <typename K> static int persistent_grid(K kernel, int n_rows, int threads) {
-	int per_sm = 0;
-	if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, threads, 0) != cudaSuccess || per_sm < 1) { cudaGetLastError(); per_sm = 1; }
+	const int per_sm = ctas_per_sm(reinterpret_cast<const void *>(kernel), threads, 0);
 	long long g = (long long) sm_count() * per_sm;
 	if (g > n_rows) g = n_rows;
 	return g < 1 ? 1 : (int) g;
@@ -466,7 +465,7 @@ extern "C" int dfb200_rms_norm_bwd_w(int fwd_dt, int bwd_dt, int n_rows, int n_c
 	float * partials = reinterpret_cast<float *>(workspace);
 	DFB200_DISPATCH_PAIR(fwd_dt, bwd_dt, F, B, DFB200_DISPATCH_VPT(geo.vpt, VPT, {
 		auto kernel = rms_norm_bwd_w_partial_kernel<F, B, VPT>;
-		if (smem > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem);
+		allow_dyn_smem(reinterpret_cast<const void *>(kernel), smem);
 		kernel<<<grid, groups * geo.threads, smem, s>>>(n_rows, n_cols, geo.threads, fwd_rms_vals, X_inp, upstream_dX, partials);
 	}));
 	rc = check_launch("rms_norm_bwd_w (partial sums)");

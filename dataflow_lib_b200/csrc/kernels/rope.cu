@@ -275,9 +275,8 @@ static int launch_rope(const char * op, int dt, uint64_t N, int model_dim, int h
 			int rc = DFB200_ERR_DTYPE;
 			DFB200_DISPATCH_DTYPE(dt, T, {
 				auto kernel = rope_staged_kernel<T, BWD>;
-				cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem);
-				int per_sm = 0;
-				if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, ROPE_STAGED_THREADS, smem) != cudaSuccess || per_sm < 1) { cudaGetLastError(); per_sm = 1; }
+				allow_dyn_smem(reinterpret_cast<const void *>(kernel), smem);
+				const int per_sm = ctas_per_sm(reinterpret_cast<const void *>(kernel), ROPE_STAGED_THREADS, smem);
 				long long g = (long long) sm_count() * per_sm;
 				const long long blocks = ((long long) tokens + tok - 1) / tok;
 				if (g > blocks) g = blocks;
@@ -296,8 +295,7 @@ static int launch_rope(const char * op, int dt, uint64_t N, int model_dim, int h
 	int grid = 0;
 	DFB200_DISPATCH_DTYPE(dt, T, {
 		auto kernel = rope_kernel<T, BWD>;
-		int per_sm = 0;
-		if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, ROPE_THREADS, smem) != cudaSuccess || per_sm < 1) { cudaGetLastError(); per_sm = 1; }
+		const int per_sm = ctas_per_sm(reinterpret_cast<const void *>(kernel), ROPE_THREADS, smem);
 		long long g = (long long) sm_count() * per_sm;
 		const long long iters = ((long long) tokens + tok_per_iter - 1) / tok_per_iter;
 		if (g > iters) g = iters;

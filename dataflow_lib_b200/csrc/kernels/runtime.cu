@@ -3,6 +3,7 @@
 #include "common.cuh"
 #include "tma.cuh"
 
+#include <pthread.h>
 #include <stdarg.h>
 #include <string.h>
 
@@ -29,6 +30,46 @@ int sm_count() {
 		cached[dev] = n;
 	}
 	return cached[dev];
+}
+
+namespace {
+struct LaunchMemo { const void * kernel; int device, threads; size_t smem; int value; };
+constexpr int MEMO_SLOTS = 256;
+LaunchMemo g_occ[MEMO_SLOTS];      // written under g_memo_lock; entries are immutable once published
+LaunchMemo g_smem[MEMO_SLOTS];
+int g_occ_n = 0, g_smem_n = 0;
+pthread_mutex_t g_memo_lock = PTHREAD_MUTEX_INITIALIZER;
+}
+
+int ctas_per_sm(const void * kernel, int threads, size_t dyn_smem) {
+	int dev = 0;
+	cudaGetDevice(&dev);
+	pthread_mutex_lock(&g_memo_lock);
+	for (int i = 0; i < g_occ_n; i++) {
+		const LaunchMemo & m = g_occ[i];
+		if (m.kernel == kernel && m.device == dev && m.threads == threads && m.smem == dyn_smem) { const int v = m.value; pthread_mutex_unlock(&g_memo_lock); return v; }
+	}
+	int per_sm = 0;
+	if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, threads, dyn_smem) != cudaSuccess || per_sm < 1) { cudaGetLastError(); per_sm = 1; }
+	if (g_occ_n < MEMO_SLOTS) g_occ[g_occ_n++] = LaunchMemo{kernel, dev, threads, dyn_smem, per_sm};
+	pthread_mutex_unlock(&g_memo_lock);
+	return per_sm;
+}
+
+void allow_dyn_smem(const void * kernel, size_t dyn_smem) {
+	if (dyn_smem <= 48 * 1024) return;
+	int dev = 0;
+	cudaGetDevice(&dev);
+	pthread_mutex_lock(&g_memo_lock);
+	LaunchMemo * slot = nullptr;
+	for (int i = 0; i < g_smem_n; i++)
+		if (g_smem[i].kernel == kernel && g_smem[i].device == dev) { slot = &g_smem[i]; break; }
+	if (!slot || slot->smem < dyn_smem) {
+		if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) dyn_smem) != cudaSuccess) cudaGetLastError();
+		if (slot) slot->smem = dyn_smem;
+		else if (g_smem_n < MEMO_SLOTS) g_smem[g_smem_n++] = LaunchMemo{kernel, dev, 0, dyn_smem, 0};
+	}
+	pthread_mutex_unlock(&g_memo_lock);
 }
 
 int check_launch(const char * what) {
