@@ -169,6 +169,7 @@ def run_gpu_arm(args):
     import oracle as O   # input generation only (seeded fills); the timed path never touches it
     from dataflow_lib_b200 import DataflowHandle
     from dataflow_lib_b200.abi import DataflowDatatype as DT
+    from dataflow_lib_b200.sharding import allreduce_step
 
     rank, world, local = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1")), int(os.environ.get("LOCAL_RANK", "0"))
     assert world == args.gpus, f"--gpus {args.gpus} but WORLD_SIZE={world} (launch N > 1 with torchrun)"
@@ -201,6 +202,7 @@ def run_gpu_arm(args):
     S, d1, d3 = torch.empty_like(dev["gate"]), torch.empty_like(dev["gate"]), torch.empty_like(dev["gate"])
     dW = torch.zeros(D_MODEL, dtype=torch.bfloat16, device="cuda")
     ws, rms = torch.empty(T, device="cuda"), torch.empty(T, device="cuda")
+    step_loss = torch.zeros(2, device="cuda")            # [loss sum, valid rows]: unused by this chain, part of the packed exchange
 
     def upload():
         for k, a in host.items():
@@ -241,7 +243,7 @@ def run_gpu_arm(args):
                 raise RuntimeError(f"submit of {op_names[i]} failed")
         if world > 1:
             with torch.cuda.stream(stream):
-                dist.all_reduce(dW)                      # the data-parallel exchange: weight gradient, 8 KB
+                allreduce_step(step_loss, [dW])          # the data-parallel exchange: one packed fp32 all-reduce (16 KB)
 
     def barrier():
         if world > 1:

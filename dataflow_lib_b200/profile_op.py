@@ -1,0 +1,69 @@
+"""Runs ONE op a few times on synthetic data, for profilers (ncu) and quick timing:
+
+    python -m dataflow_lib_b200.profile_op swiglu_bwd_x --tokens 2048 --iters 3
+    ncu --set full --clock-control none -k regex:swiglu_bwd_x -c 3 -o prof python -m dataflow_lib_b200.profile_op swiglu_bwd_x --tokens 2048
+
+Shapes are the Llama-3-8B layer's (d_model 4096, 32 q / 8 kv heads x 128, ffn 14336, vocab 128256); --tokens sets the rows.
+Prints the event-timed mean of the launches after the first (the first one warms up)."""
+import argparse
+
+import torch
+
+from . import ops
+
+D, NH, NKV, HD, F, V = 4096, 32, 8, 128, 14336, 128256
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("op", choices=["rms_norm", "rms_norm_bwd_x", "rms_norm_bwd_w", "rope", "rope_bwd_x", "swiglu", "swiglu_bwd_x",
+                                   "softmax", "softmax_cross_entropy"])
+    ap.add_argument("--tokens", type=int, default=2048)
+    ap.add_argument("--iters", type=int, default=3)
+    ap.add_argument("--dtype", default="bf16", choices=["bf16", "fp16", "fp32"])
+    a = ap.parse_args()
+    dt = {"bf16": torch.bfloat16, "fp16": torch.float16, "fp32": torch.float32}[a.dtype]
+    T = a.tokens
+    g = torch.Generator(device="cuda").manual_seed(0)
+    rn = lambda *s: torch.randn(*s, device="cuda", generator=g).to(dt)
+    es = torch.empty(0, dtype=dt).element_size()
+    if a.op.startswith("rms_norm"):
+        X, w, dY, dX = rn(T, D), (1 + 0.02 * torch.randn(D, device="cuda", generator=g)).to(dt), rn(T, D), torch.zeros(T, D, device="cuda", dtype=dt)
+        Y, dW = torch.empty_like(X), torch.zeros(D, device="cuda", dtype=dt)
+        ws, rms = torch.empty(T, device="cuda"), torch.empty(T, device="cuda")
+        ops.rms_norm(T, D, 1e-5, w, X, Y, ws, rms)
+        fn = {"rms_norm": lambda: ops.rms_norm(T, D, 1e-5, w, X, Y, ws, rms),
+              "rms_norm_bwd_x": lambda: ops.rms_norm_bwd_x(T, D, 1e-5, ws, rms, w, X, dY, dX),
+              "rms_norm_bwd_w": lambda: ops.rms_norm_bwd_w(T, D, 1e-5, rms, X, dY, dW)}[a.op]
+        nbytes = T * D * es * {"rms_norm": 2, "rms_norm_bwd_x": 4, "rms_norm_bwd_w": 2}[a.op]
+    elif a.op.startswith("rope"):
+        Q, K, pos = rn(T, NH * HD), rn(T, NKV * HD), torch.arange(T, device="cuda", dtype=torch.int32)
+        f = ops.rope if a.op == "rope" else ops.rope_bwd_x
+        fn = lambda: f(T * NH * HD, NH * HD, HD, NKV, 500000, pos, Q, K)
+        nbytes = 2 * T * (NH + NKV) * HD * es
+    elif a.op.startswith("swiglu"):
+        x1, x3, dY = rn(T, F), rn(T, F), rn(T, F)
+        out, d1, d3 = torch.empty_like(x1), torch.empty_like(x1), torch.empty_like(x1)
+        fn = (lambda: ops.swiglu(T, F, x1, x3, out)) if a.op == "swiglu" else (lambda: ops.swiglu_bwd_x(T, F, x1, x3, dY, d1, d3))
+        nbytes = T * F * es * (3 if a.op == "swiglu" else 5)
+    else:
+        L = (2 * torch.randn(T, V, device="cuda", generator=g)).to(dt)
+        out = torch.empty_like(L)
+        labels = torch.randint(0, V, (T,), device="cuda", generator=g, dtype=torch.int32)
+        loss = torch.zeros(2, device="cuda")
+        fn = (lambda: ops.softmax(T, V, L, out)) if a.op == "softmax" else (lambda: ops.softmax_cross_entropy(T, V, L, labels, out, None, loss))
+        nbytes = 2 * T * V * es
+    fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(a.iters):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / a.iters
+    print(f"{a.op} {a.dtype} tokens={T}: {ms * 1e3:.1f} us/launch back to back, {nbytes / (ms * 1e-3) / 1e9:.0f} GB/s algorithmic ({nbytes / 2**20:.0f} MiB)")
+
+
+if __name__ == "__main__":
+    main()
