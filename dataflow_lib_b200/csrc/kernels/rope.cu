@@ -120,7 +120,7 @@ rope_kernel(int tokens, int model_dim, int kv_dim, int head_dim, int tok_per_ite
 // staged kernel
 // ----------------------------------------------------------------------------------------
 constexpr int ROPE_STAGES = 4;
-constexpr int ROPE_STAGED_THREADS = 256;
+constexpr int ROPE_STAGED_THREADS = 512;
 
 template <typename T, bool BWD>
 __global__ void __launch_bounds__(ROPE_STAGED_THREADS)
@@ -134,8 +134,11 @@ rope_staged_kernel(int tokens, int model_dim, int kv_dim, int head_dim, int tok_
 	const uint32_t k_stage_bytes = (uint32_t) tok_per_stage * kv_dim * ESIZE;
 	const uint32_t stage_bytes = (q_stage_bytes + k_stage_bytes + 127u) & ~127u;
 	unsigned char * ring = smem;                                                        // [STAGES][stage_bytes]
-	float2 * table = reinterpret_cast<float2 *>(smem + ROPE_STAGES * stage_bytes);      // [tok_per_stage * half]
-	float * inv_freq = reinterpret_cast<float *>(table + tok_per_stage * half);         // [half]
+	// cos and sin in separate arrays: a thread reads 4 consecutive cos and 4 consecutive sin (two 16-byte loads),
+	// and consecutive threads read consecutive 16-byte slots, which is free of bank conflicts
+	float * tab_cos = reinterpret_cast<float *>(smem + ROPE_STAGES * stage_bytes);      // [tok_per_stage * half]
+	float * tab_sin = tab_cos + tok_per_stage * half;                                   // [tok_per_stage * half]
+	float * inv_freq = tab_sin + tok_per_stage * half;                                  // [half]
 	uint64_t * full = reinterpret_cast<uint64_t *>(inv_freq + ((half + 3) & ~3));       // [STAGES]
 	const int tid = threadIdx.x;
 
@@ -175,7 +178,8 @@ rope_staged_kernel(int tokens, int model_dim, int kv_dim, int head_dim, int tok_
 			const int t = e / half, j = e - t * half;
 			float sn, cs;
 			sincosf((float) __ldg(seq_positions + tok0 + t) * inv_freq[j], &sn, &cs);
-			table[e] = make_float2(cs, BWD ? -sn : sn);
+			tab_cos[e] = cs;
+			tab_sin[e] = BWD ? -sn : sn;
 		}
 		ok = mbar_wait_bounded(&full[s], (uint32_t) (it / ROPE_STAGES) & 1u, status, 0x100u + (unsigned) s);
 		ok = __syncthreads_and(ok);            // table visible; everyone agrees on whether to go on
@@ -189,7 +193,7 @@ rope_staged_kernel(int tokens, int model_dim, int kv_dim, int head_dim, int tok_
 		for (int t = 0; t < n_tok; t++) {
 			unsigned char * q_row = stage + (size_t) t * model_dim * ESIZE;
 			unsigned char * k_row = stage + q_stage_bytes + (size_t) t * kv_dim * ESIZE - (size_t) q_chunks * E * ESIZE;
-			const float2 * tab_t = table + t * half;
+			const float * cos_t = tab_cos + t * half, * sin_t = tab_sin + t * half;
 			for (int c = tid; c < row_chunks; c += ROPE_STAGED_THREADS) {
 				uint32_t * p = reinterpret_cast<uint32_t *>((c < q_chunks ? q_row : k_row) + (size_t) c * E * ESIZE);
 				const int in_head = head_mask >= 0 ? (c & head_mask) : (c % chunks_per_head);
@@ -202,10 +206,10 @@ rope_staged_kernel(int tokens, int model_dim, int kv_dim, int head_dim, int tok_
 				float x[E], o[E];
 				#pragma unroll
 				for (int k = 0; k < CW; k++) Word<T>::unpack(w[k], &x[k * Word<T>::EPW]);
-				const float4 * cs = reinterpret_cast<const float4 *>(tab_t + in_head * (E / 2));
-				const float4 cs01 = cs[0], cs23 = cs[1];
-				const float cv[4] = {cs01.x, cs01.z, cs23.x, cs23.z};
-				const float sv[4] = {cs01.y, cs01.w, cs23.y, cs23.w};
+				const float4 c4 = *reinterpret_cast<const float4 *>(cos_t + in_head * (E / 2));
+				const float4 s4 = *reinterpret_cast<const float4 *>(sin_t + in_head * (E / 2));
+				const float cv[4] = {c4.x, c4.y, c4.z, c4.w};
+				const float sv[4] = {s4.x, s4.y, s4.z, s4.w};
 				#pragma unroll
 				for (int q = 0; q < 4; q++) {
 					// one product rounded, the other fused into the sum: the contraction nvcc applies to the
