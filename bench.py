@@ -42,9 +42,10 @@ BYTES_PER_TOKEN = {
 }
 KERNEL_LAUNCHES_PER_STEP = 8          # 7 ops; rms_norm_bwd_w is two launches
 DOMINANT = "swiglu_bwd_x"
-# dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel from the ncu capture summarised in
-# profiles/ (None until a capture has been made)
-DOMINANT_DRAM_TRAFFIC_BYTES = None
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from the ncu capture summarised in
+# profiles/swiglu_bwd_x_bf16_2048x14336.md: reads scale with the rows and equal the algorithmic 704.6 MB; DRAM writes are
+# the algorithmic 469.8 MB minus ~41.6 MB that is still dirty in L2 when the kernel ends (size-independent residue).
+DOMINANT_DRAM_TRAFFIC_BYTES = 1_132_800_000
 
 
 def measured_peak_hbm():
