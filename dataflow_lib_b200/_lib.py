@@ -27,6 +27,7 @@ KERNEL_ABI = {
     "dfb200_rms_norm_bwd_x": (_i, [_i, _i, _i, _i, _f, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
     "dfb200_rms_norm_bwd_w_workspace_bytes": (_u64, [_i, _i]),
     "dfb200_rms_norm_bwd_w": (_i, [_i, _i, _i, _i, _f, _vp, _vp, _vp, _vp, _vp, _u64, _vp]),
+    "dfb200_rms_norm_bwd_w_static": (_i, [_i, _i, _i, _i, _f, _vp, _vp, _vp, _vp, _vp]),
     "dfb200_rope": (_i, [_i, _u64, _i, _i, _i, _i, _vp, _vp, _vp, _vp]),
     "dfb200_rope_bwd_x": (_i, [_i, _u64, _i, _i, _i, _i, _vp, _vp, _vp, _vp]),
     "dfb200_swiglu": (_i, [_i, _i, _i, _vp, _vp, _vp, _vp]),

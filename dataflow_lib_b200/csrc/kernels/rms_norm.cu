@@ -487,3 +487,45 @@ extern "C" int dfb200_rms_norm_bwd_w(int fwd_dt, int bwd_dt, int n_rows, int n_c
 	}
 	return DFB200_OK;
 }
+
+// ----------------------------------------------------------------------------------------
+// rms_norm_bwd_w for callers that must not allocate
+// ----------------------------------------------------------------------------------------
+// Some callers cannot give this op a workspace: programs that handed the whole device to their own arena with
+// one bulk alloc_mem() at start-up (the memory model the handle interface is built around) and have nothing left
+// to carve scratch from, and code running where cudaMalloc is off limits because it synchronises the whole device
+// (a latency-critical step loop, other streams mid-flight). For them the partial column sums live in this
+// fixed array, which every GPU that loads the library holds from load until exit.
+constexpr int STATIC_SCRATCH_FLOATS = 160 * 8192;      // 5 MiB: n_SM * n_cols must fit, e.g. 8192 columns on up to 160 SMs
+static __device__ __align__(256) float g_bwd_w_static_scratch[STATIC_SCRATCH_FLOATS];
+
+// Same arithmetic, kernels and results as dfb200_rms_norm_bwd_w, with the scratch taken from the array above instead
+// of a caller workspace. It calls no cudaMalloc, cudaFree or allocating library routine.
+//  * The first call on each device looks up the array's device address (cudaGetSymbolAddress, with that device
+//    current) and remembers it; make that first call outside any stream capture.
+//  * Limit: n_SM * n_cols <= 1,310,720 floats (n_cols <= 8192 on a 148-SM B200); larger shapes are rejected
+//    with DFB200_ERR_WORKSPACE and a message, never truncated.
+//  * All calls on a device share the one array and it keeps the previous call's contents. Nothing in it has to
+//    start at zero (stage 1 overwrites every partial row that stage 2 reads), but two calls that overlap on the
+//    GPU (different streams, no dependency between them) race on it: order them.
+extern "C" int dfb200_rms_norm_bwd_w_static(int fwd_dt, int bwd_dt, int n_rows, int n_cols, float eps, const float * fwd_rms_vals,
+                                            const void * X_inp, const void * upstream_dX, void * dW, void * stream) {
+	static float * scratch_of_device[64];          // device address of g_bwd_w_static_scratch, per device
+	int dev = -1;
+	cudaError_t e = cudaGetDevice(&dev);
+	if (e != cudaSuccess || dev < 0 || dev >= 64) { cudaGetLastError(); return set_error(DFB200_ERR_CUDA, "rms_norm_bwd_w_static: no current device (%s)", cudaGetErrorString(e)); }
+	if (!scratch_of_device[dev]) {
+		void * p = nullptr;
+		// in host code the array's name is only a handle for the runtime, not a device address: ask for the address
+		e = cudaGetSymbolAddress(&p, g_bwd_w_static_scratch);
+		if (e != cudaSuccess || !p) { cudaGetLastError(); return set_error(DFB200_ERR_CUDA, "rms_norm_bwd_w_static: cudaGetSymbolAddress failed: %s", cudaGetErrorString(e)); }
+		scratch_of_device[dev] = static_cast<float *>(p);
+	}
+	const uint64_t capacity = (uint64_t) STATIC_SCRATCH_FLOATS * sizeof(float);
+	const uint64_t need = dfb200_rms_norm_bwd_w_workspace_bytes(n_rows, n_cols);
+	if (need > capacity)
+		return set_error(DFB200_ERR_WORKSPACE, "rms_norm_bwd_w_static: n_cols = %d needs %llu bytes of scratch on this device, the built-in array holds %llu "
+		                 "(n_SM * n_cols <= %d); use dfb200_rms_norm_bwd_w with a caller workspace", n_cols, (unsigned long long) need,
+		                 (unsigned long long) capacity, STATIC_SCRATCH_FLOATS);
+	return dfb200_rms_norm_bwd_w(fwd_dt, bwd_dt, n_rows, n_cols, eps, fwd_rms_vals, X_inp, upstream_dX, dW, scratch_of_device[dev], capacity, stream);
+}

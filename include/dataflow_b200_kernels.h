@@ -72,6 +72,17 @@ int dfb200_rms_norm_bwd_w(int fwd_dt, int bwd_dt, int n_rows, int n_cols, float 
                           const void * upstream_dX, void * dW,
                           void * workspace, uint64_t workspace_bytes, void * stream);
 
+/* No counterpart in the reference. rms_norm_bwd_w for callers that cannot allocate device memory or pass a
+ * workspace: a program whose own arena already owns the whole device (one bulk alloc_mem at start-up), or a step
+ * loop that must not hit cudaMalloc's device-wide synchronisation. Same results as dfb200_rms_norm_bwd_w; the
+ * partial sums go to a 5 MiB array built into the library (held by every GPU that loads it until exit), so
+ * n_SM * n_cols must be <= 1,310,720 (n_cols <= 8192 on a 148-SM B200) or the call fails with
+ * DFB200_ERR_WORKSPACE. The first call on a device resolves the array's address: issue it before any stream
+ * capture. Calls share the array: calls that overlap on the GPU race, so keep them ordered. */
+int dfb200_rms_norm_bwd_w_static(int fwd_dt, int bwd_dt, int n_rows, int n_cols, float eps,
+                                 const float * fwd_rms_vals, const void * X_inp,
+                                 const void * upstream_dX, void * dW, void * stream);
+
 /* ---- RoPE -------------------------------------------------------------------------------
  * Replaces rope_<dt>_kernel (src/ops/nvidia/attention/rope.cu:3,60,123,183,243), rope_bwd_x_<dt>_kernel
  * (src/ops/nvidia/attention/rope_bwd_x.cu:3,62,120) and their launch configs
