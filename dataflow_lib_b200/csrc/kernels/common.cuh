@@ -169,6 +169,24 @@ __device__ __forceinline__ void store_elems(void * base, uint64_t idx, const flo
 }
 
 // ---------------------------------------------------------------------------------------
+// fast math: the approximate, flush-to-zero hardware forms that the reference build selects with
+// --use_fast_math (expf -> ex2.approx.ftz(x * log2 e), a / b -> a * rcp.approx.ftz(b)). Written as PTX because the
+// CUDA intrinsics without the global -ftz flag wrap the same instructions in denormal fix-ups (3 extra
+// instructions per call), which matters in the instruction-bound softmax.
+// ---------------------------------------------------------------------------------------
+__device__ __forceinline__ float fast_exp(float x) {
+	float t, y;
+	asm("mul.ftz.f32 %0, %1, 0f3FB8AA3B;" : "=f"(t) : "f"(x));      // log2(e)
+	asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(t));
+	return y;
+}
+__device__ __forceinline__ float fast_rcp(float x) {
+	float y;
+	asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+	return y;
+}
+
+// ---------------------------------------------------------------------------------------
 // reductions
 // ---------------------------------------------------------------------------------------
 

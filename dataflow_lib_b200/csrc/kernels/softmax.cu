@@ -31,7 +31,80 @@ constexpr int E = 8;                       // elements per chunk
 constexpr int SLICE_ALIGN_CHUNKS = 128;    // slices start on a multiple of 1024 elements so that a thread's partial index is fixed
 constexpr int SOFTMAX_MAX_CLUSTER = 8;
 constexpr int SOFTMAX_MAX_THREADS = 512;
-constexpr int SOFTMAX_MAX_CPT = 8;
+#ifndef DFB200_SOFTMAX_MAX_CPT
+#define DFB200_SOFTMAX_MAX_CPT 8
+#endif
+constexpr int SOFTMAX_MAX_CPT = DFB200_SOFTMAX_MAX_CPT;
+
+// Per-chunk arithmetic. The softmax is instruction-bound before it is memory-bound (two exponentials per element
+// plus the rounding of x - max to the working type): at 6.5 TB/s an SM has about 22 issue slots per element, and
+// the conversion/transcendental pipe only 4 per element. The same-type 16-bit cases therefore work on PACKED pairs:
+// the maximum with max.bf16x2 / max.f16x2 and x - max with sub.bf16x2 / sub.f16x2 -- which is also literally the
+// reference's operation (one rounding of the exact difference, src/ops/nvidia/loss/softmax.cu:359) -- so that no
+// float->bf16 conversion is left in the inner loops. Other type pairs take the generic fp32 path.
+template <typename F, typename B> struct RowMath {
+	static constexpr int FW = E / Word<F>::EPW;
+	struct Max { float m; };
+	static __device__ __forceinline__ Max max_init() { return Max{-CUDART_INF_F}; }
+	static __device__ __forceinline__ void max_chunk(Max & acc, const uint32_t (&raw)[FW]) {
+		float x[E];
+		#pragma unroll
+		for (int i = 0; i < FW; i++) Word<F>::unpack(raw[i], &x[i * Word<F>::EPW]);
+		#pragma unroll
+		for (int i = 0; i < E; i++) acc.m = fmaxf(acc.m, x[i]);
+	}
+	static __device__ __forceinline__ float max_value(const Max & acc) { return acc.m; }
+	struct Shift { float m; };
+	static __device__ __forceinline__ Shift shift_of(float row_max) { return Shift{row_max}; }
+	// d[i] = W(x[i] - max) as fp32
+	static __device__ __forceinline__ void shifted(const Shift & sh, const uint32_t (&raw)[FW], float (&d)[E]) {
+		float x[E];
+		#pragma unroll
+		for (int i = 0; i < FW; i++) Word<F>::unpack(raw[i], &x[i * Word<F>::EPW]);
+		#pragma unroll
+		for (int i = 0; i < E; i++) d[i] = round_to<B>(x[i] - sh.m);
+	}
+};
+
+template <> struct RowMath<bf16_t, bf16_t> {
+	static constexpr int FW = 4;
+	struct Max { __nv_bfloat162 m; };
+	static __device__ __forceinline__ Max max_init() { Max a; a.m = __float2bfloat162_rn(-CUDART_INF_F); return a; }
+	static __device__ __forceinline__ void max_chunk(Max & acc, const uint32_t (&raw)[FW]) {
+		#pragma unroll
+		for (int i = 0; i < FW; i++) acc.m = __hmax2(acc.m, *reinterpret_cast<const __nv_bfloat162 *>(&raw[i]));
+	}
+	static __device__ __forceinline__ float max_value(const Max & acc) { return fmaxf(__low2float(acc.m), __high2float(acc.m)); }
+	struct Shift { __nv_bfloat162 m; };
+	static __device__ __forceinline__ Shift shift_of(float row_max) { Shift s; s.m = __float2bfloat162_rn(row_max); return s; }   // exact: the max is a bf16 value
+	static __device__ __forceinline__ void shifted(const Shift & sh, const uint32_t (&raw)[FW], float (&d)[E]) {
+		#pragma unroll
+		for (int i = 0; i < FW; i++) {
+			const __nv_bfloat162 v = __hsub2(*reinterpret_cast<const __nv_bfloat162 *>(&raw[i]), sh.m);
+			Word<bf16_t>::unpack(*reinterpret_cast<const uint32_t *>(&v), &d[2 * i]);
+		}
+	}
+};
+
+template <> struct RowMath<f16_t, f16_t> {
+	static constexpr int FW = 4;
+	struct Max { __half2 m; };
+	static __device__ __forceinline__ Max max_init() { Max a; a.m = __float2half2_rn(-CUDART_INF_F); return a; }
+	static __device__ __forceinline__ void max_chunk(Max & acc, const uint32_t (&raw)[FW]) {
+		#pragma unroll
+		for (int i = 0; i < FW; i++) acc.m = __hmax2(acc.m, *reinterpret_cast<const __half2 *>(&raw[i]));
+	}
+	static __device__ __forceinline__ float max_value(const Max & acc) { return fmaxf(__low2float(acc.m), __high2float(acc.m)); }
+	struct Shift { __half2 m; };
+	static __device__ __forceinline__ Shift shift_of(float row_max) { Shift s; s.m = __float2half2_rn(row_max); return s; }
+	static __device__ __forceinline__ void shifted(const Shift & sh, const uint32_t (&raw)[FW], float (&d)[E]) {
+		#pragma unroll
+		for (int i = 0; i < FW; i++) {
+			const __half2 v = __hsub2(*reinterpret_cast<const __half2 *>(&raw[i]), sh.m);
+			Word<f16_t>::unpack(*reinterpret_cast<const uint32_t *>(&v), &d[2 * i]);
+		}
+	}
+};
 
 template <typename F, typename B, int CPT, bool FUSE_CE>
 __global__ void __launch_bounds__(SOFTMAX_MAX_THREADS)
@@ -56,7 +129,9 @@ softmax_rows_kernel(int n_rows, int n_cols, int slice_chunks, const void * __res
 	const int c_end = min(n_chunks, c_begin + slice_chunks);
 	const uint64_t row_elem = (uint64_t) row * (uint64_t) n_cols;
 
-	// ---- load: every packet of the slice is requested before anything is consumed
+	// ---- load: every packet of the slice is requested before anything is consumed (and the row's label with them)
+	uint32_t label = 0xffffffffu;
+	if constexpr (FUSE_CE) label = __ldg(labels + row);
 	uint32_t raw[CPT][FW];
 	#pragma unroll
 	for (int k = 0; k < CPT; k++) {
@@ -65,19 +140,14 @@ softmax_rows_kernel(int n_rows, int n_cols, int slice_chunks, const void * __res
 	}
 
 	// ---- phase 1: row maximum
-	float m = -CUDART_INF_F;
+	using Math = RowMath<F, B>;
+	typename Math::Max macc = Math::max_init();
 	#pragma unroll
 	for (int k = 0; k < CPT; k++) {
 		const int c = c_begin + tid + k * nthr;
-		if (c < c_end) {
-			float x[E];
-			#pragma unroll
-			for (int i = 0; i < FW; i++) Word<F>::unpack(raw[k][i], &x[i * Word<F>::EPW]);
-			#pragma unroll
-			for (int i = 0; i < E; i++) m = fmaxf(m, x[i]);
-		}
+		if (c < c_end) Math::max_chunk(macc, raw[k]);
 	}
-	m = warp_max(m);
+	float m = warp_max(Math::max_value(macc));
 	if (lane == 0) s_warp_max[warp] = m;
 	__syncthreads();
 	if (warp == 0) {
@@ -97,6 +167,7 @@ softmax_rows_kernel(int n_rows, int n_cols, int slice_chunks, const void * __res
 	}
 	__syncthreads();
 	const float row_max = s_row[0];
+	const typename Math::Shift shift = Math::shift_of(row_max);
 
 	// ---- phase 2: 32 interleaved partial sums of exp(W(x - max))
 	float part = 0.0f;
@@ -104,11 +175,10 @@ softmax_rows_kernel(int n_rows, int n_cols, int slice_chunks, const void * __res
 	for (int k = 0; k < CPT; k++) {
 		const int c = c_begin + tid + k * nthr;
 		if (c < c_end) {
-			float x[E];
+			float d[E];
+			Math::shifted(shift, raw[k], d);
 			#pragma unroll
-			for (int i = 0; i < FW; i++) Word<F>::unpack(raw[k][i], &x[i * Word<F>::EPW]);
-			#pragma unroll
-			for (int i = 0; i < E; i++) part += __expf(round_to<B>(x[i] - row_max));
+			for (int i = 0; i < E; i++) part += fast_exp(d[i]);
 		}
 	}
 	// chunk c covers elements 8c..8c+7, so its partial index is (c / 4) % 32; c = tid + k*nthr with
@@ -143,35 +213,47 @@ softmax_rows_kernel(int n_rows, int n_cols, int slice_chunks, const void * __res
 	__syncthreads();
 	const float total = s_row[1];
 
-	// ---- phase 3: normalise, optional cross-entropy step, store
-	uint32_t label = 0xffffffffu;
-	if constexpr (FUSE_CE) label = __ldg(labels + row);
+	// ---- phase 3: normalise and store. exp(d) / total is the approximate division of the reference build, i.e. a
+	// multiplication by rcp.approx(total); the reciprocal is taken once per thread.
+	const float inv_total = fast_rcp(total);
+	bool owns_label = false;
 	#pragma unroll
 	for (int k = 0; k < CPT; k++) {
 		const int c = c_begin + tid + k * nthr;
 		if (c < c_end) {
-			float x[E], o[E];
+			float d[E], o[E];
+			Math::shifted(shift, raw[k], d);
 			#pragma unroll
-			for (int i = 0; i < FW; i++) Word<F>::unpack(raw[k][i], &x[i * Word<F>::EPW]);
-			#pragma unroll
-			for (int i = 0; i < E; i++) o[i] = __fdividef(__expf(round_to<B>(x[i] - row_max)), total);
-			if constexpr (FUSE_CE) {
-				const uint32_t first = (uint32_t) c * E;
-				if (label >= first && label < first + E) {
-					#pragma unroll
-					for (int i = 0; i < E; i++) {
-						if (first + i == label) {
-							// the separate kernel reads the stored W probability and subtracts one in W
-							o[i] = round_to<B>(o[i]) - 1.0f;
-							if (row_loss) row_loss[row] = logf(total) - round_to<B>(x[i] - row_max);
-						}
-					}
-				}
-			}
+			for (int i = 0; i < E; i++) o[i] = fast_exp(d[i]) * inv_total;
 			store_elems<B, E>(out, row_elem + (uint64_t) c * E, o);
+			if constexpr (FUSE_CE) owns_label |= (label / E == (uint32_t) c);
 		}
 	}
+	// ---- cross-entropy step, by the one thread of the row whose packet holds the label, outside the hot loop: it
+	// re-reads the probability it has just stored (its own store, so program order guarantees it sees it), subtracts
+	// one in the working type as the separate kernel does, and forms the row's loss from the label's logit.
 	if constexpr (FUSE_CE) {
+		if (owns_label) {
+			const uint64_t idx = row_elem + label;
+			float p[1], x[1];
+			if constexpr (Word<B>::EPW == 1) {
+				float * q = reinterpret_cast<float *>(out) + idx;
+				*q = *q - 1.0f;
+			} else {
+				uint16_t * q = reinterpret_cast<uint16_t *>(out) + idx;
+				float pair[2];
+				Word<B>::unpack((uint32_t) *q, pair);
+				pair[0] -= 1.0f; pair[1] = 0.0f;
+				*q = (uint16_t) (Word<B>::pack(pair) & 0xffffu);
+			}
+			if (row_loss) {
+				if constexpr (Word<F>::EPW == 1) x[0] = reinterpret_cast<const float *>(X)[idx];
+				else if constexpr (Word<F>::EPW == 2) { float pr[2]; Word<F>::unpack((uint32_t) reinterpret_cast<const uint16_t *>(X)[idx], pr); x[0] = pr[0]; }
+				else { float qd[4]; Word<F>::unpack((uint32_t) reinterpret_cast<const uint8_t *>(X)[idx], qd); x[0] = qd[0]; }
+				row_loss[row] = logf(total) - round_to<B>(x[0] - row_max);
+			}
+			(void) p;
+		}
 		if (row_loss && label >= (uint32_t) n_cols && crank == 0 && tid == 0) row_loss[row] = 0.0f;
 	}
 	if (csize > 1) cluster.barrier_wait();  // no CTA leaves while a peer may still read its shared memory

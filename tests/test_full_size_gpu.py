@@ -1,0 +1,144 @@
+"""Full-size checks at the BASELINE.json configurations (C1 RMSNorm 4096x4096, C2 the 8192-token Llama-3-8B chain,
+C3 fused softmax + cross entropy 16384 x 128256), where the CPU oracle would take too long: size-independent
+properties of the ops, plus PyTorch fp32 re-computations on the GPU that model the reference's rounding points.
+Inputs: seeded torch normals of the configs' shapes and distributions (synthetic stand-ins for activations)."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from dataflow_lib_b200 import ops as _ops
+    return _ops
+
+
+def _randn(shape, seed, std=1.0, mean=0.0, dtype=torch.bfloat16):
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    return (mean + std * torch.randn(shape, device="cuda", generator=g)).to(dtype)
+
+
+def _close(got, ref, rel=1e-2, scale=None):
+    got, ref = got.float(), ref.float()
+    s = ref.pow(2).mean().sqrt() if scale is None else scale
+    tol = rel * torch.maximum(ref.abs(), torch.as_tensor(s, device=ref.device))
+    bad = (got - ref).abs() > tol
+    assert not bad.any(), f"{int(bad.sum())}/{bad.numel()} outside {rel} rel"
+
+
+def test_c1_rms_norm_fwd_bwd(ops):
+    R, C, eps = 4096, 4096, 1e-5
+    X, w, dY = _randn((R, C), 0), _randn((C,), 1, 0.02, 1.0), _randn((R, C), 2)
+    Y, ws, rms = torch.empty_like(X), torch.empty(R, device="cuda"), torch.empty(R, device="cuda")
+    ops.rms_norm(R, C, eps, w, X, Y, ws, rms)
+    xf, wf, gf = X.float(), w.float(), dY.float()
+    r = torch.rsqrt(xf.pow(2).mean(1) + eps)
+    assert torch.allclose(rms, r, rtol=1e-5, atol=0)
+    assert torch.allclose(ws, (xf * wf).sum(1), rtol=1e-5, atol=1e-3)
+    same = (Y == ((xf * r[:, None]) * wf).bfloat16()).float().mean().item()
+    assert same > 0.999, same                              # one rounding of an fp32 product: bit-identical up to 1-ulp rsqrt effects
+    # backward-x: dX accumulates; reference formula dX += dY * bf16(w r - x r^3 / n * ws), fused multiply-add in bf16
+    for dX0 in (torch.zeros_like(X), _randn((R, C), 3)):
+        dX = dX0.clone()
+        ops.rms_norm_bwd_x(R, C, eps, ws, rms, w, X, dY, dX)
+        deriv = (wf * rms[:, None] - (xf * (rms ** 3)[:, None] / C) * ws[:, None]).bfloat16().float()
+        want = (dX0.double() + gf.double() * deriv.double()).float().bfloat16()       # exact then one rounding
+        assert (dX == want).float().mean().item() > 0.999
+        _close(dX, want, rel=2e-2)        # where this fp32 model and the kernel round bf16(deriv) differently, the product moves by ulp(deriv)*|dY|
+    # backward-w: exact column sums (fp64) within bf16 rounding; linear in dY (x2 is exact in bf16); accumulates into dW
+    dW = torch.zeros(C, dtype=torch.bfloat16, device="cuda")
+    ops.rms_norm_bwd_w(R, C, eps, rms, X, dY, dW)
+    exact = (gf * xf * rms[:, None]).double().sum(0)
+    assert ((dW.double() - exact).abs() <= 2.0 ** -8 * exact.abs() + 1e-6).all()
+    dW2 = torch.zeros_like(dW)
+    ops.rms_norm_bwd_w(R, C, eps, rms, X, (dY.float() * 2).bfloat16(), dW2)
+    assert torch.equal(dW2.float(), dW.float() * 2)
+    dW3 = dW.clone()
+    ops.rms_norm_bwd_w(R, C, eps, rms, X, dY, dW3)
+    assert ((dW3.double() - 2 * exact).abs() <= 2.0 ** -7 * exact.abs() * 2 + 1e-6).all()
+
+
+def test_c2_rope_roundtrip_and_swiglu(ops):
+    T, NH, NKV, HD, F, theta = 8192, 32, 8, 128, 14336, 500000
+    pos = torch.arange(T, device="cuda", dtype=torch.int32)
+    Q, K = _randn((T, NH * HD), 4), _randn((T, NKV * HD), 5)
+    q, k = Q.clone(), K.clone()
+    ops.rope(T * NH * HD, NH * HD, HD, NKV, theta, pos, q, k)
+    # textbook check in fp32: interleaved pairs times exp(i pos theta^(-2j/hd))
+    ang = pos.double()[:, None] * (float(theta) ** (-torch.arange(0, HD, 2, device="cuda").double() / HD))[None, :]
+    cs, sn = ang.cos().float(), ang.sin().float()
+    def rot(x, n_heads):
+        x = x.float().view(T, n_heads, HD // 2, 2)
+        e, o = x[..., 0], x[..., 1]
+        return torch.stack((cs[:, None] * e - sn[:, None] * o, cs[:, None] * o + sn[:, None] * e), -1).view(T, n_heads * HD)
+    _close(q, rot(Q, NH).bfloat16())
+    _close(k, rot(K, NKV).bfloat16())
+    # rotations preserve the norm of every pair (up to two bf16 roundings)
+    n0 = Q.float().view(T, -1, 2).pow(2).sum(-1).sqrt()
+    n1 = q.float().view(T, -1, 2).pow(2).sum(-1).sqrt()
+    assert ((n1 - n0).abs() <= 1.5e-2 * n0 + 1e-2).all()
+    # backward is the inverse rotation: fwd then bwd gives the input back within two bf16 roundings
+    ops.rope_bwd_x(T * NH * HD, NH * HD, HD, NKV, theta, pos, q, k)
+    _close(q, Q, rel=1.6e-2)
+    _close(k, K, rel=1.6e-2)
+    # swiglu forward/backward against the formulas in fp32
+    x1, x3, dY = _randn((T, F), 6), _randn((T, F), 7), _randn((T, F), 8)
+    out, d1, d3 = torch.empty_like(x1), torch.empty_like(x1), torch.empty_like(x1)
+    ops.swiglu(T, F, x1, x3, out)
+    ops.swiglu_bwd_x(T, F, x1, x3, dY, d1, d3)
+    a, b, g = x1.float(), x3.float(), dY.float()
+    e = torch.exp(-a)
+    silu = a / (1 + e)
+    assert (out == (silu * b).bfloat16()).float().mean().item() > 0.9999
+    _close(out, (silu * b).bfloat16())
+    _close(d3, (g * silu).bfloat16())
+    _close(d1, (g * (b * (1 + e + a * e)) / ((1 + e) * (1 + e))).bfloat16())
+
+
+def test_c3_fused_softmax_cross_entropy(ops):
+    T, V = 16384, 128256
+    g = torch.Generator(device="cuda").manual_seed(9)
+    logits = torch.empty(T, V, dtype=torch.bfloat16, device="cuda")
+    for i in range(0, T, 2048):                                     # N(0, 2) in slabs to bound temporary memory
+        logits[i:i + 2048] = (2.0 * torch.randn(2048, V, device="cuda", generator=g)).bfloat16()
+    labels = torch.randint(0, V, (T,), device="cuda", generator=g, dtype=torch.int32)
+    dl = torch.empty_like(logits)
+    row_loss, loss = torch.empty(T, device="cuda"), torch.zeros(2, device="cuda")
+    ops.softmax_cross_entropy(T, V, logits, labels, dl, row_loss, loss)
+    torch.cuda.synchronize()
+    assert loss[1].item() == T
+    lab = labels.long()
+    worst_sum, neg_count = 0.0, 0
+    model_loss = torch.empty(T, device="cuda", dtype=torch.float64)
+    for i in range(0, T, 1024):                                     # model of the reference's rounding points, in slabs
+        x = logits[i:i + 1024].float()
+        d = (x - x.max(1, keepdim=True).values).bfloat16().float()  # x - max rounded to bf16
+        e = torch.exp(d)
+        pad = (-V) % 1024
+        ep = torch.nn.functional.pad(e, (0, pad)).view(1024, -1, 32, 32)            # [row, k, partial index, lane]
+        partial = ep.sum(dim=(1, 3)).bfloat16().float()                               # 32 interleaved sums, each rounded to bf16
+        total = partial.sum(1).bfloat16().float()                                      # rounded again
+        p = (e / total[:, None]).bfloat16()
+        want = p.clone()
+        rows = torch.arange(1024, device="cuda")
+        want[rows, lab[i:i + 1024]] = (p[rows, lab[i:i + 1024]].float() - 1.0).bfloat16()
+        got = dl[i:i + 1024]
+        frac = (got == want).float().mean().item()
+        assert frac > 0.995, (i, frac)
+        _close(got, want, rel=1e-2, scale=1.0 / V)
+        gf = got.float()
+        neg = gf < 0
+        neg_count += int(neg.sum())
+        assert torch.equal(neg.nonzero()[:, 1], lab[i:i + 1024])                       # label indexing, bit-exact
+        worst_sum = max(worst_sum, gf.sum(1).abs().max().item())                       # softmax - onehot sums to ~0 per row
+        model_loss[i:i + 1024] = (torch.log(total) - d[rows, lab[i:i + 1024]]).double()
+    assert neg_count == T and worst_sum < 2e-2
+    assert torch.allclose(row_loss.double(), model_loss, rtol=0, atol=5e-3)
+    mean_model = model_loss.sum().item() / T
+    mean_got = loss[0].item() / T
+    assert abs(mean_got - mean_model) <= 1e-5 * abs(mean_model), (mean_got, mean_model)
+    assert abs(loss[0].item() - row_loss.double().sum().item()) <= 1e-6 * abs(loss[0].item())   # fp64 fixed-order sum of the fp32 row losses
+    # and against the textbook loss the quirks stay small: a few 1e-3 relative on the mean
+    ce = torch.stack([torch.nn.functional.cross_entropy(logits[i:i + 2048].float(), lab[i:i + 2048], reduction="sum") for i in range(0, T, 2048)]).sum().item() / T
+    assert abs(mean_got - ce) / ce < 5e-3, (mean_got, ce)
