@@ -18,6 +18,12 @@
 // Within a partial sum the fp32 addition order differs from the reference's (it cannot be
 // reproduced by a different thread layout); that changes a partial by a few fp32 ulps before
 // its rounding to W.
+//
+// A persistent variant that staged row slices through shared memory with bulk asynchronous copies
+// (3-deep ring, one 1024-thread CTA per SM) was measured at 16384 x 128256 bf16 and was SLOWER
+// (3.4 ms against 1.9 ms): per row the chain max -> cluster barrier -> sums -> cluster barrier ->
+// normalise costs about 7 us of latency however the data arrives, so what matters is how many
+// independent rows an SM has in flight, and registers hold more of them than one big CTA does.
 #include "common.cuh"
 
 #include <cooperative_groups.h>
@@ -170,7 +176,7 @@ softmax_rows_kernel(int n_rows, int n_cols, int slice_chunks, const void * __res
 	const typename Math::Shift shift = Math::shift_of(row_max);
 
 	// ---- phase 2: 32 interleaved partial sums of exp(W(x - max))
-	float part = 0.0f;
+	float part4[4] = {0.0f, 0.0f, 0.0f, 0.0f};            // four independent chains: the adds are not the critical path
 	#pragma unroll
 	for (int k = 0; k < CPT; k++) {
 		const int c = c_begin + tid + k * nthr;
@@ -178,9 +184,10 @@ softmax_rows_kernel(int n_rows, int n_cols, int slice_chunks, const void * __res
 			float d[E];
 			Math::shifted(shift, raw[k], d);
 			#pragma unroll
-			for (int i = 0; i < E; i++) part += fast_exp(d[i]);
+			for (int i = 0; i < E; i++) part4[i & 3] += fast_exp(d[i]);
 		}
 	}
+	float part = (part4[0] + part4[1]) + (part4[2] + part4[3]);
 	// chunk c covers elements 8c..8c+7, so its partial index is (c / 4) % 32; c = tid + k*nthr with
 	// nthr % 128 == 0 and c_begin % 128 == 0 makes that (tid / 4) % 32 for every k.
 	part += __shfl_xor_sync(0xffffffffu, part, 1);

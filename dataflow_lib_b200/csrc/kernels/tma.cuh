@@ -16,7 +16,7 @@ namespace dfb200 {
 enum KernelStatusSlot { STATUS_ROPE = 0, STATUS_RMS = 1, STATUS_SOFTMAX = 2, STATUS_FFN = 3, STATUS_SLOTS = 8 };
 unsigned int * kernel_status_word(int slot);     // host: device address of a status word on the current device (NULL on error)
 
-constexpr uint32_t WAIT_LIMIT = 1u << 22;      // try_wait attempts (each blocks for a hardware time slice) before giving up
+constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;     // a wait gives up after two seconds of wall time
 
 __device__ __forceinline__ uint32_t smem_u32(const void * p) { return (uint32_t) __cvta_generic_to_shared(p); }
 
@@ -40,11 +40,22 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t * bar, uint32_t parity) {
 	return done != 0;
 }
 
+__device__ __forceinline__ unsigned long long global_timer_ns() {
+	unsigned long long t;
+	asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+	return t;
+}
+
 // Waits for the phase with the given parity to complete. Returns false (and records `where`
-// in *status) when the limit is reached.
+// in *status) when the time limit is reached; the clock is only consulted every 1024 attempts.
 __device__ __forceinline__ bool mbar_wait_bounded(uint64_t * bar, uint32_t parity, unsigned int * status, unsigned int where) {
-	for (uint32_t i = 0; i < WAIT_LIMIT; i++)
-		if (mbar_try_wait(bar, parity)) return true;
+	if (mbar_try_wait(bar, parity)) return true;
+	const unsigned long long t0 = global_timer_ns();
+	for (;;) {
+		for (int i = 0; i < 1024; i++)
+			if (mbar_try_wait(bar, parity)) return true;
+		if (global_timer_ns() - t0 > WAIT_LIMIT_NS) break;
+	}
 	atomicMax(status, where);
 	return false;
 }
