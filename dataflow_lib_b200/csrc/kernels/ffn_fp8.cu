@@ -1,0 +1,395 @@
+// FP8-weight SwiGLU FFN forward on the 5th-generation tensor cores (tcgen05 + tensor memory).
+//
+//   H   = silu(A Wg^T * sa sg) * (A Wu^T * sa su)        [T, f]  bf16
+//   Out = (H Wd^T) * sh sd                                [T, d]  bf16
+//
+// Weights are e4m3 with one fp32 scale per OUTPUT channel and are stored [out_features, in_features] (reduction
+// dimension contiguous). tcgen05.mma kind::f8f6f4 needs both operands in 8 bits, so activations are quantised to e4m3
+// with one fp32 scale per ROW (token) by quantize_rows_e4m3_kernel; both scales leave the contraction and are applied
+// to the fp32 accumulator in the epilogue. The reference has no such op (its only GEMM is a cuBLASLt call without
+// scale pointers, src/ops/nvidia/external/matmul_helper/src/matmul_helper.c:379-416); the arithmetic contract is the
+// one restated by the CPU oracle (oracle_ffn_fp8_*).
+//
+// GEMM kernel, one 128 x 256 accumulator tile per CTA, warp-specialised:
+//   warp 0      one thread issues TMA tile loads (cp.async.bulk.tensor, 128-byte swizzle, CTA-local destination)
+//               into a 4-stage shared-memory ring (A 128x128 B + B 256x128 B per stage), completion on mbarriers;
+//   warp 1      allocates 256 columns of tensor memory; one thread issues tcgen05.mma (M128 N128/256 K32, fp32
+//               accumulation in TMEM) and tcgen05.commit, which releases ring stages and finally signals the epilogue;
+//   warps 2-5   read the accumulator with tcgen05.ld (each warp its 32-lane quarter), apply the scales (and SwiGLU
+//               for the gate/up pair, whose two 128-column halves are the gate and the up projection of the same 128
+//               output channels), convert to bf16 and store.
+// Every mbarrier wait is bounded and reports through the kernel status word.
+#include "common.cuh"
+#include "tma.cuh"
+
+#include <cuda.h>
+
+namespace dfb200 {
+
+constexpr int GEMM_BM = 128, GEMM_BK = 128;            // BK in elements = bytes (e4m3)
+constexpr int GEMM_BN_HALF = 128;                        // columns per accumulator half
+constexpr int GEMM_STAGES = 4;
+constexpr int GEMM_THREADS = 192;
+constexpr uint32_t TMEM_COLS = 256;
+constexpr uint32_t A_STAGE_BYTES = GEMM_BM * GEMM_BK;                   // 16 KB
+constexpr uint32_t B_STAGE_BYTES = 2 * GEMM_BN_HALF * GEMM_BK;          // 32 KB
+constexpr uint32_t STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
+
+// ---------------------------------------------------------------------------------------------------------------
+// PTX wrappers (tensor-map TMA, tcgen05)
+// ---------------------------------------------------------------------------------------------------------------
+__device__ __forceinline__ void tma_load_2d(void * smem_dst, const CUtensorMap * map, int x, int y, uint64_t * bar) {
+	asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+	             :: "r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void prefetch_tensormap(const CUtensorMap * map) {
+	asm volatile("prefetch.tensormap [%0];" :: "l"(reinterpret_cast<uint64_t>(map)) : "memory");
+}
+__device__ __forceinline__ void tmem_alloc(uint32_t * smem_slot, uint32_t cols) {
+	asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" :: "r"(smem_u32(smem_slot)), "r"(cols) : "memory");
+	asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
+	asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" :: "r"(taddr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before_sync() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after_sync() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+// All tcgen05.mma issued so far by this thread arrive on `bar` when they have completed (and no longer read shared memory).
+__device__ __forceinline__ void tc_commit(uint64_t * bar) {
+	asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" :: "r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tc_mma_f8(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+	asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+	             "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}"
+	             :: "r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(0u) : "memory");
+}
+// 32 consecutive fp32 columns of this warp's 32 lanes (thread i gets lane base+i).
+__device__ __forceinline__ void tmem_ld_32cols(uint32_t taddr, float (&v)[32]) {
+	uint32_t r[32];
+	asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+	             : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]),
+	               "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]),
+	               "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+	             : "r"(taddr) : "memory");
+	asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+	#pragma unroll
+	for (int i = 0; i < 32; i++) v[i] = __uint_as_float(r[i]);
+}
+
+// Shared-memory matrix descriptor of a K-major operand tile stored with the 128-byte swizzle: rows of 128 bytes,
+// groups of 8 rows (1024 bytes) stacked along M/N. Fields: start address >> 4 [0,14), leading byte offset >> 4 [16,30)
+// (not used by swizzled K-major layouts; 1), stride byte offset >> 4 [32,46) = 1024 B between 8-row groups,
+// descriptor version 1 [46,48), layout type SWIZZLE_128B = 2 [61,64).
+__device__ __forceinline__ uint64_t umma_desc_k_sw128(const void * smem_tile) {
+	uint64_t d = (uint64_t) ((smem_u32(smem_tile) & 0x3ffffu) >> 4);
+	d |= (uint64_t) 1 << 16;
+	d |= (uint64_t) (1024 >> 4) << 32;
+	d |= (uint64_t) 1 << 46;
+	d |= (uint64_t) 2 << 61;
+	return d;
+}
+// Instruction descriptor of kind::f8f6f4: D fp32 [4,6) = 1, A and B e4m3 (0), both K-major (0), N >> 3 at [17,23), M >> 4 at [24,29).
+__host__ __device__ constexpr uint32_t umma_idesc_e4m3(int m, int n) { return (1u << 4) | ((uint32_t) (n >> 3) << 17) | ((uint32_t) (m >> 4) << 24); }
+
+// ---------------------------------------------------------------------------------------------------------------
+// row quantisation: q[r, :] = e4m3( x[r, :] * (448 / amax_r) ),  scale[r] = amax_r / 448  (1 when the row is all zero)
+// ---------------------------------------------------------------------------------------------------------------
+template <int VPT>
+__global__ void __launch_bounds__(256)
+quantize_rows_e4m3_kernel(int n_rows, int n_cols, const void * __restrict__ X, void * __restrict__ Q, float * __restrict__ scales) {
+	__shared__ float red[8];
+	const int n_chunks = n_cols / 8, tid = threadIdx.x, nthr = blockDim.x;
+	for (int row = blockIdx.x; row < n_rows; row += gridDim.x) {
+		float x[VPT][8];
+		float amax = 0.0f;
+		#pragma unroll
+		for (int v = 0; v < VPT; v++) {
+			const int c = tid + v * nthr;
+			if (c < n_chunks) {
+				load_elems<bf16_t, 8>(X, (uint64_t) row * n_cols + (uint64_t) c * 8, x[v]);
+				#pragma unroll
+				for (int i = 0; i < 8; i++) amax = fmaxf(amax, fabsf(x[v][i]));
+			}
+		}
+		amax = warp_max(amax);
+		__syncthreads();                               // red[] of the previous row has been read
+		if ((tid & 31) == 0) red[tid >> 5] = amax;
+		__syncthreads();
+		amax = red[0];
+		for (int w = 1; w < (nthr >> 5); w++) amax = fmaxf(amax, red[w]);
+		const float inv = amax > 0.0f ? __fdiv_rn(448.0f, amax) : 1.0f;
+		if (tid == 0) scales[row] = amax > 0.0f ? __fdiv_rn(amax, 448.0f) : 1.0f;
+		#pragma unroll
+		for (int v = 0; v < VPT; v++) {
+			const int c = tid + v * nthr;
+			if (c < n_chunks) {
+				float q[8];
+				#pragma unroll
+				for (int i = 0; i < 8; i++) q[i] = __fmul_rn(x[v][i], inv);
+				store_elems<e4m3_t, 8>(Q, (uint64_t) row * n_cols + (uint64_t) c * 8, q);
+			}
+		}
+	}
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// GEMM: D[m, n] = sum_k A[m, k] * B[n, k]  (e4m3 x e4m3 -> fp32 in TMEM), two 128-column halves per CTA.
+//   SWIGLU = true : half 0 = gate rows n0.., half 1 = up rows n0.. (tensor maps map_b0 / map_b1), 128 outputs:
+//                   out[m, n0 + j] = bf16( silu(g) * u ),  g = acc0 * sa[m] * sb0[n], u = acc1 * sa[m] * sb1[n]
+//   SWIGLU = false: halves are columns n0.. and n0 + 128.. of one weight matrix (map_b0 twice), 256 outputs:
+//                   out[m, n] = bf16( acc * sa[m] * sb0[n] )
+// ---------------------------------------------------------------------------------------------------------------
+template <bool SWIGLU>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+gemm_e4m3_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b0, const __grid_constant__ CUtensorMap map_b1,
+                 int M, int N, int K, int tiles_m, int tiles_n, const float * __restrict__ sa, const float * __restrict__ sb0,
+                 const float * __restrict__ sb1, void * __restrict__ out, int ld_out, unsigned int * status) {
+	extern __shared__ uint8_t smem_raw[];
+	uint8_t * smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t) 1023);   // swizzled tiles need 1024-byte alignment
+	uint8_t * ring = smem;
+	uint64_t * full = reinterpret_cast<uint64_t *>(smem + GEMM_STAGES * STAGE_BYTES);
+	uint64_t * empty = full + GEMM_STAGES;
+	uint64_t * accum_full = empty + GEMM_STAGES;
+	uint32_t * tmem_slot = reinterpret_cast<uint32_t *>(accum_full + 1);
+	float * s_scale = reinterpret_cast<float *>(tmem_slot + 2);        // [2][128] column scales of this tile
+
+	const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+	constexpr int N_PER_TILE = SWIGLU ? GEMM_BN_HALF : 2 * GEMM_BN_HALF;
+
+	// tile raster: groups of 16 row tiles sweep the column tiles, so that concurrently running CTAs share A and B tiles in L2
+	const int group = 16;
+	const int tiles_per_group = group * tiles_n;
+	const int g = blockIdx.x / tiles_per_group, r = blockIdx.x % tiles_per_group;
+	const int rows_in_group = min(group, tiles_m - g * group);
+	const int tile_m = g * group + r % rows_in_group, tile_n = r / rows_in_group;
+	const int m0 = tile_m * GEMM_BM, n0 = tile_n * N_PER_TILE;
+	const int num_kb = (K + GEMM_BK - 1) / GEMM_BK;
+
+	if (threadIdx.x == 0) {
+		for (int s = 0; s < GEMM_STAGES; s++) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+		mbar_init(accum_full, 1);
+		mbar_fence_init();
+		prefetch_tensormap(&map_a); prefetch_tensormap(&map_b0); prefetch_tensormap(&map_b1);
+	}
+	if (warp == 1) tmem_alloc(tmem_slot, TMEM_COLS);
+	if (warp >= 2) {                                   // column scales of this tile
+		for (int j = threadIdx.x - 64; j < 2 * GEMM_BN_HALF; j += 128) {
+			const int half = j / GEMM_BN_HALF, col = SWIGLU ? n0 + (j % GEMM_BN_HALF) : n0 + j;
+			const float * sb = (SWIGLU && half == 1) ? sb1 : sb0;
+			s_scale[j] = col < N ? __ldg(sb + col) : 0.0f;
+		}
+	}
+	tc_fence_before_sync();
+	__syncthreads();
+	tc_fence_after_sync();
+	const uint32_t tmem_base = *tmem_slot;
+
+	if (warp == 0) {
+		// ---------------- TMA producer
+		if (lane == 0) {
+			for (int kb = 0; kb < num_kb; kb++) {
+				const int s = kb % GEMM_STAGES;
+				const uint32_t parity = ((kb / GEMM_STAGES) & 1) ^ 1;
+				if (!mbar_wait_bounded(&empty[s], parity, status, 0x300u + s)) break;
+				uint8_t * a_dst = ring + (size_t) s * STAGE_BYTES;
+				uint8_t * b_dst = a_dst + A_STAGE_BYTES;
+				mbar_arrive_expect_tx(&full[s], STAGE_BYTES);
+				tma_load_2d(a_dst, &map_a, kb * GEMM_BK, m0, &full[s]);
+				if (SWIGLU) {
+					tma_load_2d(b_dst, &map_b0, kb * GEMM_BK, n0, &full[s]);
+					tma_load_2d(b_dst + GEMM_BN_HALF * GEMM_BK, &map_b1, kb * GEMM_BK, n0, &full[s]);
+				} else {
+					tma_load_2d(b_dst, &map_b0, kb * GEMM_BK, n0, &full[s]);
+					tma_load_2d(b_dst + GEMM_BN_HALF * GEMM_BK, &map_b0, kb * GEMM_BK, n0 + GEMM_BN_HALF, &full[s]);
+				}
+			}
+		}
+	} else if (warp == 1) {
+		// ---------------- MMA issuer
+		if (lane == 0) {
+			constexpr uint32_t idesc = umma_idesc_e4m3(GEMM_BM, GEMM_BN_HALF);
+			bool ok = true;
+			for (int kb = 0; kb < num_kb && ok; kb++) {
+				const int s = kb % GEMM_STAGES;
+				ok = mbar_wait_bounded(&full[s], (kb / GEMM_STAGES) & 1, status, 0x310u + s);
+				if (!ok) break;
+				tc_fence_after_sync();
+				const uint8_t * a_tile = ring + (size_t) s * STAGE_BYTES;
+				const uint64_t da = umma_desc_k_sw128(a_tile);
+				const uint64_t db0 = umma_desc_k_sw128(a_tile + A_STAGE_BYTES);
+				const uint64_t db1 = umma_desc_k_sw128(a_tile + A_STAGE_BYTES + GEMM_BN_HALF * GEMM_BK);
+				#pragma unroll
+				for (int j = 0; j < GEMM_BK / 32; j++) {          // K = 32 per instruction: advance 32 bytes inside the swizzle atom
+					const uint32_t acc = (kb > 0 || j > 0) ? 1u : 0u;
+					tc_mma_f8(tmem_base, da + 2 * j, db0 + 2 * j, idesc, acc);
+					tc_mma_f8(tmem_base + GEMM_BN_HALF, da + 2 * j, db1 + 2 * j, idesc, acc);
+				}
+				tc_commit(&empty[s]);                               // stage reusable once these MMAs have read it
+			}
+			tc_commit(accum_full);                                   // accumulator complete (or abandoned) -> epilogue
+		}
+	} else {
+		// ---------------- epilogue: warp w reads TMEM lanes 32 * (w % 4) .. + 32
+		const int quarter = warp & 3;
+		const int row = m0 + quarter * 32 + lane;
+		const bool ok = __all_sync(0xffffffffu, mbar_wait_bounded(accum_full, 0, status, 0x320u));     // warp-uniform: tcgen05.ld is warp-wide
+		tc_fence_after_sync();
+		if (ok) {
+			const float a_scale = row < M ? __ldg(sa + row) : 0.0f;
+			const uint32_t taddr = tmem_base + ((uint32_t) (quarter * 32) << 16);
+			__nv_bfloat16 * out_row = reinterpret_cast<__nv_bfloat16 *>(out) + (size_t) row * ld_out;
+			#pragma unroll 1
+			for (int c = 0; c < N_PER_TILE / 32; c++) {
+				float v0[32], o[32];
+				if (SWIGLU) {
+					float v1[32];
+					tmem_ld_32cols(taddr + c * 32, v0);
+					tmem_ld_32cols(taddr + GEMM_BN_HALF + c * 32, v1);
+					#pragma unroll
+					for (int i = 0; i < 32; i++) {
+						const float gte = (v0[i] * a_scale) * s_scale[c * 32 + i];
+						const float up = (v1[i] * a_scale) * s_scale[GEMM_BN_HALF + c * 32 + i];
+						o[i] = (gte * fast_rcp(1.0f + fast_exp(-gte))) * up;
+					}
+				} else {
+					tmem_ld_32cols(taddr + c * 32, v0);
+					#pragma unroll
+					for (int i = 0; i < 32; i++) o[i] = (v0[i] * a_scale) * s_scale[c * 32 + i];
+				}
+				const int col0 = n0 + c * 32;
+				if (row < M) {
+					if (col0 + 32 <= N) {
+						#pragma unroll
+						for (int i = 0; i < 32; i += 8) {
+							uint32_t w[4];
+							#pragma unroll
+							for (int k = 0; k < 4; k++) w[k] = Word<bf16_t>::pack(&o[i + 2 * k]);
+							*reinterpret_cast<uint4 *>(out_row + col0 + i) = make_uint4(w[0], w[1], w[2], w[3]);
+						}
+					} else {
+						for (int i = 0; i < 32 && col0 + i < N; i++) out_row[col0 + i] = __float2bfloat16_rn(o[i]);
+					}
+				}
+			}
+		}
+	}
+	tc_fence_before_sync();
+	__syncthreads();
+	if (warp == 1) { tc_fence_after_sync(); tmem_dealloc(tmem_base, TMEM_COLS); }
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// host side
+// ---------------------------------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *, const cuuint32_t *,
+                                  const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_tiled_fn() {
+	static EncodeTiledFn fn = nullptr;
+	if (!fn) {
+		void * p = nullptr;
+		cudaDriverEntryPointQueryResult q;
+		if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess || q != cudaDriverEntryPointSuccess) { cudaGetLastError(); return nullptr; }
+		fn = reinterpret_cast<EncodeTiledFn>(p);
+	}
+	return fn;
+}
+
+// Tensor map of a row-major [rows, k] e4m3 matrix, boxes of 128 rows x 128 bytes, 128-byte swizzle, zero fill outside.
+static int make_map(CUtensorMap * map, const void * base, uint64_t rows, uint64_t k) {
+	EncodeTiledFn fn = encode_tiled_fn();
+	if (!fn) return set_error(DFB200_ERR_CUDA, "ffn_fp8: cuTensorMapEncodeTiled is not available");
+	cuuint64_t dims[2] = {k, rows};
+	cuuint64_t strides[1] = {k};
+	cuuint32_t box[2] = {(cuuint32_t) GEMM_BK, (cuuint32_t) GEMM_BM};
+	cuuint32_t estr[2] = {1, 1};
+	CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+	                CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+	if (r != CUDA_SUCCESS) return set_error(DFB200_ERR_CUDA, "ffn_fp8: cuTensorMapEncodeTiled failed (%d)", (int) r);
+	return DFB200_OK;
+}
+
+template <bool SWIGLU>
+static int launch_gemm(int M, int N, int K, const void * A, const float * sa, const void * B0, const float * sb0, const void * B1, const float * sb1,
+                       void * out, int ld_out, cudaStream_t stream) {
+	if (K % 16 || !aligned16(A) || !aligned16(B0) || (SWIGLU && !aligned16(B1)) || !aligned16(out) || ld_out % 8)
+		return set_error(DFB200_ERR_ARG, "ffn_fp8: K must be a multiple of 16, tensors 16-byte aligned, output pitch a multiple of 8");
+	CUtensorMap ma, mb0, mb1;
+	int rc = make_map(&ma, A, (uint64_t) M, (uint64_t) K);
+	if (!rc) rc = make_map(&mb0, B0, (uint64_t) N, (uint64_t) K);
+	if (!rc) rc = make_map(&mb1, SWIGLU ? B1 : B0, (uint64_t) N, (uint64_t) K);
+	if (rc) return rc;
+	unsigned int * status = kernel_status_word(STATUS_FFN);
+	if (!status) return set_error(DFB200_ERR_CUDA, "ffn_fp8: no status word");
+	constexpr int n_per_tile = SWIGLU ? GEMM_BN_HALF : 2 * GEMM_BN_HALF;
+	const int tiles_m = (M + GEMM_BM - 1) / GEMM_BM, tiles_n = (N + n_per_tile - 1) / n_per_tile;
+	const size_t smem = 1024 + GEMM_STAGES * STAGE_BYTES + (2 * GEMM_STAGES + 1) * sizeof(uint64_t) + 2 * sizeof(uint32_t) + 2 * GEMM_BN_HALF * sizeof(float);
+	auto kernel = gemm_e4m3_kernel<SWIGLU>;
+	allow_dyn_smem(reinterpret_cast<const void *>(kernel), smem);
+	kernel<<<tiles_m * tiles_n, GEMM_THREADS, smem, stream>>>(ma, mb0, mb1, M, N, K, tiles_m, tiles_n, sa, sb0, SWIGLU ? sb1 : sb0, out, ld_out, status);
+	return check_launch("ffn_fp8 gemm");
+}
+
+}  // namespace dfb200
+
+using namespace dfb200;
+
+extern "C" int dfb200_quantize_rows_e4m3(int n_rows, int n_cols, const void * X_bf16, void * Q_e4m3, float * row_scales, void * stream) {
+	if (n_rows < 0 || n_cols <= 0 || n_cols % 8) return set_error(DFB200_ERR_ARG, "quantize_rows_e4m3: bad shape %d x %d (columns must be a multiple of 8)", n_rows, n_cols);
+	if (n_rows == 0) return DFB200_OK;
+	if (!X_bf16 || !Q_e4m3 || !row_scales || !aligned16(X_bf16) || !aligned16(Q_e4m3)) return set_error(DFB200_ERR_ARG, "quantize_rows_e4m3: NULL or misaligned tensor");
+	const int n_chunks = n_cols / 8;
+	if (n_chunks > 256 * 8) return set_error(DFB200_ERR_ARG, "quantize_rows_e4m3: n_cols = %d exceeds the supported maximum of %d", n_cols, 256 * 8 * 8);
+	int vpt = 1;
+	while (vpt < 8 && (n_chunks + vpt - 1) / vpt > 256) vpt *= 2;
+	int threads = ((n_chunks + vpt - 1) / vpt + 31) / 32 * 32;
+	const int grid = n_rows < sm_count() * 8 ? n_rows : sm_count() * 8;
+	cudaStream_t s = (cudaStream_t) stream;
+	switch (vpt) {
+		case 1: quantize_rows_e4m3_kernel<1><<<grid, threads, 0, s>>>(n_rows, n_cols, X_bf16, Q_e4m3, row_scales); break;
+		case 2: quantize_rows_e4m3_kernel<2><<<grid, threads, 0, s>>>(n_rows, n_cols, X_bf16, Q_e4m3, row_scales); break;
+		case 4: quantize_rows_e4m3_kernel<4><<<grid, threads, 0, s>>>(n_rows, n_cols, X_bf16, Q_e4m3, row_scales); break;
+		default: quantize_rows_e4m3_kernel<8><<<grid, threads, 0, s>>>(n_rows, n_cols, X_bf16, Q_e4m3, row_scales); break;
+	}
+	return check_launch("quantize_rows_e4m3");
+}
+
+extern "C" int dfb200_gemm_e4m3_swiglu(int M, int N, int K, const void * A_e4m3, const float * a_row_scales, const void * Wgate_e4m3, const float * gate_scales,
+                                       const void * Wup_e4m3, const float * up_scales, void * H_bf16, void * stream) {
+	if (M <= 0 || N <= 0 || K <= 0) return set_error(DFB200_ERR_ARG, "gemm_e4m3_swiglu: bad shape");
+	return launch_gemm<true>(M, N, K, A_e4m3, a_row_scales, Wgate_e4m3, gate_scales, Wup_e4m3, up_scales, H_bf16, N, (cudaStream_t) stream);
+}
+
+extern "C" int dfb200_gemm_e4m3(int M, int N, int K, const void * A_e4m3, const float * a_row_scales, const void * W_e4m3, const float * w_scales,
+                                void * out_bf16, void * stream) {
+	if (M <= 0 || N <= 0 || K <= 0) return set_error(DFB200_ERR_ARG, "gemm_e4m3: bad shape");
+	return launch_gemm<false>(M, N, K, A_e4m3, a_row_scales, W_e4m3, w_scales, nullptr, nullptr, out_bf16, N, (cudaStream_t) stream);
+}
+
+extern "C" uint64_t dfb200_swiglu_ffn_fp8_workspace_bytes(int T, int d, int f) {
+	// quantised input [T, d] + its scales, hidden [T, f] bf16, quantised hidden [T, f] + its scales
+	const uint64_t a = ((uint64_t) T * d + 255) & ~255ull, h = ((uint64_t) T * f * 2 + 255) & ~255ull, hq = ((uint64_t) T * f + 255) & ~255ull;
+	const uint64_t sc = ((uint64_t) T * 4 + 255) & ~255ull;
+	return a + sc + h + hq + sc;
+}
+
+extern "C" int dfb200_swiglu_ffn_fp8(int T, int d, int f, const void * A_bf16, const void * Wgate, const float * gate_scales, const void * Wup,
+                                     const float * up_scales, const void * Wdown, const float * down_scales, void * out_bf16, void * workspace,
+                                     uint64_t workspace_bytes, void * stream) {
+	if (T <= 0 || d <= 0 || f <= 0 || d % 16 || f % 16) return set_error(DFB200_ERR_ARG, "swiglu_ffn_fp8: bad shape (T %d, d %d, f %d; d and f multiples of 16)", T, d, f);
+	const uint64_t need = dfb200_swiglu_ffn_fp8_workspace_bytes(T, d, f);
+	if (!workspace || workspace_bytes < need || !aligned16(workspace))
+		return set_error(DFB200_ERR_WORKSPACE, "swiglu_ffn_fp8: needs %llu bytes of 16-byte aligned workspace, got %llu", (unsigned long long) need, (unsigned long long) workspace_bytes);
+	uint8_t * p = static_cast<uint8_t *>(workspace);
+	auto take = [&](uint64_t bytes) { uint8_t * q = p; p += (bytes + 255) & ~255ull; return q; };
+	void * Aq = take((uint64_t) T * d);
+	float * sa = reinterpret_cast<float *>(take((uint64_t) T * 4));
+	void * H = take((uint64_t) T * f * 2);
+	void * Hq = take((uint64_t) T * f);
+	float * sh = reinterpret_cast<float *>(take((uint64_t) T * 4));
+	int rc = dfb200_quantize_rows_e4m3(T, d, A_bf16, Aq, sa, stream);
+	if (!rc) rc = dfb200_gemm_e4m3_swiglu(T, f, d, Aq, sa, Wgate, gate_scales, Wup, up_scales, H, stream);
+	if (!rc) rc = dfb200_quantize_rows_e4m3(T, f, H, Hq, sh, stream);
+	if (!rc) rc = dfb200_gemm_e4m3(T, d, f, Hq, sh, Wdown, down_scales, out_bf16, stream);
+	return rc;
+}

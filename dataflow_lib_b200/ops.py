@@ -108,3 +108,23 @@ def softmax_cross_entropy(n_rows, n_cols, logits, labels, dlogits, row_loss=None
     _check(_lib_.dfb200_softmax_cross_entropy(dt_of(logits), dt_of(dlogits), n_rows, n_cols, _ptr(logits), _ptr(labels), _ptr(dlogits),
                                               _ptr(row_loss), _ptr(loss_sum), _ptr(ws), ws.numel() * ws.element_size(),
                                               _stream(stream)), "softmax_cross_entropy")
+
+
+def quantize_rows_e4m3(n_rows, n_cols, X, Q, row_scales, stream=None):
+    _check(_lib_.dfb200_quantize_rows_e4m3(n_rows, n_cols, _ptr(X), _ptr(Q), _ptr(row_scales), _stream(stream)), "quantize_rows_e4m3")
+
+
+def gemm_e4m3(M, N, K, A, a_row_scales, W, w_scales, out, stream=None):
+    _check(_lib_.dfb200_gemm_e4m3(M, N, K, _ptr(A), _ptr(a_row_scales), _ptr(W), _ptr(w_scales), _ptr(out), _stream(stream)), "gemm_e4m3")
+
+
+def gemm_e4m3_swiglu(M, N, K, A, a_row_scales, Wgate, gate_scales, Wup, up_scales, H, stream=None):
+    _check(_lib_.dfb200_gemm_e4m3_swiglu(M, N, K, _ptr(A), _ptr(a_row_scales), _ptr(Wgate), _ptr(gate_scales), _ptr(Wup), _ptr(up_scales),
+                                         _ptr(H), _stream(stream)), "gemm_e4m3_swiglu")
+
+
+def swiglu_ffn_fp8(T, d, f, A, Wgate, gate_scales, Wup, up_scales, Wdown, down_scales, out, stream=None, workspace=None):
+    need = _lib_.dfb200_swiglu_ffn_fp8_workspace_bytes(T, d, f)
+    ws = workspace if workspace is not None else _workspace(A.device, need)
+    _check(_lib_.dfb200_swiglu_ffn_fp8(T, d, f, _ptr(A), _ptr(Wgate), _ptr(gate_scales), _ptr(Wup), _ptr(up_scales), _ptr(Wdown),
+                                       _ptr(down_scales), _ptr(out), _ptr(ws), ws.numel() * ws.element_size(), _stream(stream)), "swiglu_ffn_fp8")

@@ -130,6 +130,26 @@ int dfb200_softmax_cross_entropy(int fwd_dt, int bwd_dt, int n_rows, int n_cols,
                                  float * row_loss, float * loss_sum,
                                  void * workspace, uint64_t workspace_bytes, void * stream);
 
+/* ---- FP8-weight SwiGLU FFN (forward) -------------------------------------------------------
+ * No counterpart in the reference (its only GEMM is the external cuBLASLt call, without scales:
+ * src/ops/nvidia/external/matmul_helper/src/matmul_helper.c:577-657). tcgen05 tensor-core GEMMs with fp32
+ * accumulation in tensor memory. Weights: e4m3, stored [out_features, in_features] row-major, one fp32 scale per
+ * output channel (w = code * scale). Activations: bf16, quantised inside to e4m3 with one scale per row.
+ *   dfb200_quantize_rows_e4m3   Q[r,:] = e4m3(X[r,:] * 448 / amax_r), row_scales[r] = amax_r / 448
+ *   dfb200_gemm_e4m3            out[m,n] = bf16( (sum_k A[m,k] W[n,k]) * a_row_scales[m] * w_scales[n] )
+ *   dfb200_gemm_e4m3_swiglu     H[m,n]   = bf16( silu(g) * u ), g/u = the same with the gate / up weights
+ *   dfb200_swiglu_ffn_fp8       the four steps above for out = down(swiglu(gate(A), up(A))); workspace from the caller
+ * Shapes: K (the reduction length) a multiple of 16, N a multiple of 8, 16-byte aligned tensors. */
+int dfb200_quantize_rows_e4m3(int n_rows, int n_cols, const void * X_bf16, void * Q_e4m3, float * row_scales, void * stream);
+int dfb200_gemm_e4m3(int M, int N, int K, const void * A_e4m3, const float * a_row_scales, const void * W_e4m3, const float * w_scales,
+                     void * out_bf16, void * stream);
+int dfb200_gemm_e4m3_swiglu(int M, int N, int K, const void * A_e4m3, const float * a_row_scales, const void * Wgate_e4m3,
+                            const float * gate_scales, const void * Wup_e4m3, const float * up_scales, void * H_bf16, void * stream);
+uint64_t dfb200_swiglu_ffn_fp8_workspace_bytes(int T, int d, int f);
+int dfb200_swiglu_ffn_fp8(int T, int d, int f, const void * A_bf16, const void * Wgate, const float * gate_scales, const void * Wup,
+                          const float * up_scales, const void * Wdown, const float * down_scales, void * out_bf16, void * workspace,
+                          uint64_t workspace_bytes, void * stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -484,3 +484,72 @@ void oracle_fill_normal(int dt, void * out, long n_rows, long per_row, uint64_t 
 void oracle_fill_labels(uint32_t * out, long n, uint64_t seed, uint32_t n_classes) {
 	for (long i = 0; i < n; i++) out[i] = (uint32_t) (splitmix64(seed * 0x100000001b3ull + (uint64_t) i) % n_classes);
 }
+
+/* ------------------------------------------------------------------------------------------
+ * FP8-weight SwiGLU FFN (no counterpart in the reference: parity unpinned; this restatement IS the contract)
+ *   row quantisation   q[r,k] = e4m3( x[r,k] * (448 / amax_r) ),  scale[r] = amax_r / 448   (1 for an all-zero row)
+ *   projections        acc[m,n] = sum_k f32(A[m,k]) * f32(W[n,k])       weights stored [out, in]; sum in fp64 here
+ *   gate/up epilogue   g = (acc_g * sa[m]) * sg[n];  u = (acc_u * sa[m]) * su[n];  h = bf16( (g / (1 + exp(-g))) * u )
+ *   plain epilogue     out = bf16( (acc * sa[m]) * sw[n] )
+ * ---------------------------------------------------------------------------------------- */
+
+typedef struct { int n_cols; const uint16_t * X; uint8_t * Q; float * scales; } Quant;
+
+static void quant_rows(long r0, long r1, void * p) {
+	Quant * a = (Quant *) p;
+	for (long r = r0; r < r1; r++) {
+		const uint16_t * x = a->X + (size_t) r * a->n_cols;
+		float amax = 0.0f;
+		for (int k = 0; k < a->n_cols; k++) { const float v = fabsf(oracle_bf16_to_f32(x[k])); if (v > amax) amax = v; }
+		const float inv = amax > 0.0f ? 448.0f / amax : 1.0f;
+		a->scales[r] = amax > 0.0f ? amax / 448.0f : 1.0f;
+		for (int k = 0; k < a->n_cols; k++) a->Q[(size_t) r * a->n_cols + k] = oracle_f32_to_e4m3(oracle_bf16_to_f32(x[k]) * inv);
+	}
+}
+
+void oracle_quantize_rows_e4m3(int n_rows, int n_cols, const void * X_bf16, void * Q, float * scales, int n_threads) {
+	Quant a = {n_cols, (const uint16_t *) X_bf16, (uint8_t *) Q, scales};
+	for_rows(n_rows, n_threads, quant_rows, &a);
+}
+
+typedef struct { int N, K, swiglu; const uint8_t * A, * W0, * W1; const float * sa, * s0, * s1; uint16_t * out; const float * lut; } Gemm8;
+
+static void gemm8_rows(long r0, long r1, void * p) {
+	Gemm8 * a = (Gemm8 *) p;
+	float * arow = (float *) malloc(sizeof(float) * (size_t) a->K);
+	for (long m = r0; m < r1; m++) {
+		for (int k = 0; k < a->K; k++) arow[k] = a->lut[a->A[(size_t) m * a->K + k]];
+		for (int n = 0; n < a->N; n++) {
+			const uint8_t * w0 = a->W0 + (size_t) n * a->K;
+			double acc0 = 0.0, acc1 = 0.0;
+			for (int k = 0; k < a->K; k++) acc0 += (double) (arow[k] * a->lut[w0[k]]);       /* products of two e4m3 values are exact in fp32 */
+			if (a->swiglu) {
+				const uint8_t * w1 = a->W1 + (size_t) n * a->K;
+				for (int k = 0; k < a->K; k++) acc1 += (double) (arow[k] * a->lut[w1[k]]);
+				const float g = ((float) acc0 * a->sa[m]) * a->s0[n], u = ((float) acc1 * a->sa[m]) * a->s1[n];
+				a->out[(size_t) m * a->N + n] = oracle_f32_to_bf16((g / (1.0f + expf(-g))) * u);
+			} else {
+				a->out[(size_t) m * a->N + n] = oracle_f32_to_bf16(((float) acc0 * a->sa[m]) * a->s0[n]);
+			}
+		}
+	}
+	free(arow);
+}
+
+static void gemm8(int M, int N, int K, int swiglu, const void * A, const float * sa, const void * W0, const float * s0, const void * W1,
+                  const float * s1, void * out, int n_threads) {
+	float lut[256];
+	for (int i = 0; i < 256; i++) lut[i] = oracle_e4m3_to_f32((uint8_t) i);
+	lut[0x7f] = 0.0f; lut[0xff] = 0.0f;          /* NaN codes never occur in quantised data */
+	Gemm8 a = {N, K, swiglu, (const uint8_t *) A, (const uint8_t *) W0, (const uint8_t *) W1, sa, s0, s1, (uint16_t *) out, lut};
+	for_rows(M, n_threads, gemm8_rows, &a);
+}
+
+void oracle_gemm_e4m3(int M, int N, int K, const void * A, const float * sa, const void * W, const float * sw, void * out_bf16, int n_threads) {
+	gemm8(M, N, K, 0, A, sa, W, sw, NULL, NULL, out_bf16, n_threads);
+}
+
+void oracle_gemm_e4m3_swiglu(int M, int N, int K, const void * A, const float * sa, const void * Wg, const float * sg, const void * Wu,
+                             const float * su, void * H_bf16, int n_threads) {
+	gemm8(M, N, K, 1, A, sa, Wg, sg, Wu, su, H_bf16, n_threads);
+}

@@ -37,6 +37,9 @@ _sig = {
     "oracle_softmax": (None, [_i, _i, _i, _i, _vp, _vp, _i]),
     "oracle_cross_entropy_loss": (None, [_i, _i, _i, _vp, _vp]),
     "oracle_softmax_cross_entropy": (None, [_i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _i]),
+    "oracle_quantize_rows_e4m3": (None, [_i, _i, _vp, _vp, _vp, _i]),
+    "oracle_gemm_e4m3": (None, [_i, _i, _i, _vp, _vp, _vp, _vp, _vp, _i]),
+    "oracle_gemm_e4m3_swiglu": (None, [_i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i]),
     "oracle_fill_normal": (None, [_i, _vp, _l, _l, _u64, _f, _f, _i]),
     "oracle_fill_labels": (None, [_vp, _l, _u64, C.c_uint32]),
 }
@@ -149,3 +152,38 @@ def softmax_cross_entropy(fwd_dt, bwd_dt, logits, labels, threads=None):
     _lib.oracle_softmax_cross_entropy(fwd_dt, bwd_dt, n_rows, n_cols, _p(logits), _p(np.ascontiguousarray(labels, np.uint32)), _p(dl),
                                       _p(row_loss), _p(loss_sum), threads or N_THREADS)
     return dl, row_loss, loss_sum
+
+
+def quantize_rows_e4m3(X_bf16, threads=None):
+    """Per-row e4m3 quantisation: returns (codes uint8 [rows, cols], scales fp32 [rows])."""
+    Q = np.empty(X_bf16.shape, np.uint8)
+    sc = np.empty(X_bf16.shape[0], np.float32)
+    _lib.oracle_quantize_rows_e4m3(X_bf16.shape[0], X_bf16.shape[1], _p(X_bf16), _p(Q), _p(sc), threads or N_THREADS)
+    return Q, sc
+
+
+def quantize_weight_e4m3(W_f32):
+    """Per-output-channel quantisation of a weight matrix [out, in] (fp32): scale = amax / 448 per row."""
+    amax = np.abs(W_f32).max(1)
+    scale = np.where(amax > 0, amax / 448.0, 1.0).astype(np.float32)
+    return from_f32((W_f32 / scale[:, None]).astype(np.float32), E4M3), scale
+
+
+def gemm_e4m3(A, sa, W, sw, threads=None):
+    out = np.empty((A.shape[0], W.shape[0]), np.uint16)
+    _lib.oracle_gemm_e4m3(A.shape[0], W.shape[0], A.shape[1], _p(A), _p(sa), _p(W), _p(sw), _p(out), threads or N_THREADS)
+    return out
+
+
+def gemm_e4m3_swiglu(A, sa, Wg, sg, Wu, su, threads=None):
+    out = np.empty((A.shape[0], Wg.shape[0]), np.uint16)
+    _lib.oracle_gemm_e4m3_swiglu(A.shape[0], Wg.shape[0], A.shape[1], _p(A), _p(sa), _p(Wg), _p(sg), _p(Wu), _p(su), _p(out), threads or N_THREADS)
+    return out
+
+
+def swiglu_ffn_fp8(A_bf16, Wg, sg, Wu, su, Wd, sd, threads=None):
+    """The whole forward: quantise rows, gate/up + SwiGLU, quantise the hidden rows, down projection. Returns (out, hidden)."""
+    Aq, sa = quantize_rows_e4m3(A_bf16, threads)
+    H = gemm_e4m3_swiglu(Aq, sa, Wg, sg, Wu, su, threads)
+    Hq, sh = quantize_rows_e4m3(H, threads)
+    return gemm_e4m3(Hq, sh, Wd, sd, threads), H
