@@ -10,7 +10,8 @@
 // scale pointers, src/ops/nvidia/external/matmul_helper/src/matmul_helper.c:379-416); the arithmetic contract is the
 // one restated by the CPU oracle (oracle_ffn_fp8_*).
 //
-// GEMM kernel, one 128 x 256 accumulator tile per CTA, warp-specialised:
+// GEMM kernel: persistent CTAs (one per SM) walk 128 x 256 accumulator tiles; two accumulator stages in tensor memory
+// (2 x 256 of the 512 columns) let the epilogue of one tile overlap the MMAs of the next. Warp-specialised:
 //   warp 0      one thread issues TMA tile loads (cp.async.bulk.tensor, 128-byte swizzle, CTA-local destination)
 //               into a 4-stage shared-memory ring (A 128x128 B + B 256x128 B per stage), completion on mbarriers;
 //   warp 1      allocates 256 columns of tensor memory; one thread issues tcgen05.mma (M128 N128/256 K32, fp32
@@ -30,7 +31,7 @@ constexpr int GEMM_BM = 128, GEMM_BK = 128;            // BK in elements = bytes
 constexpr int GEMM_BN_HALF = 128;                        // columns per accumulator half
 constexpr int GEMM_STAGES = 4;
 constexpr int GEMM_THREADS = 192;
-constexpr uint32_t TMEM_COLS = 256;
+constexpr uint32_t TMEM_COLS = 512;                      // two 256-column accumulator stages
 constexpr uint32_t A_STAGE_BYTES = GEMM_BM * GEMM_BK;                   // 16 KB
 constexpr uint32_t B_STAGE_BYTES = 2 * GEMM_BN_HALF * GEMM_BK;          // 32 KB
 constexpr uint32_t STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
@@ -149,94 +150,124 @@ gemm_e4m3_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
 	uint8_t * ring = smem;
 	uint64_t * full = reinterpret_cast<uint64_t *>(smem + GEMM_STAGES * STAGE_BYTES);
 	uint64_t * empty = full + GEMM_STAGES;
-	uint64_t * accum_full = empty + GEMM_STAGES;
-	uint32_t * tmem_slot = reinterpret_cast<uint32_t *>(accum_full + 1);
-	float * s_scale = reinterpret_cast<float *>(tmem_slot + 2);        // [2][128] column scales of this tile
+	uint64_t * accum_full = empty + GEMM_STAGES;            // [2]
+	uint64_t * accum_empty = accum_full + 2;                // [2]
+	uint32_t * tmem_slot = reinterpret_cast<uint32_t *>(accum_empty + 2);
+	float * s_scale = reinterpret_cast<float *>(tmem_slot + 2);        // [2 accumulator stages][256] column scales of the tile
 
 	const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 	constexpr int N_PER_TILE = SWIGLU ? GEMM_BN_HALF : 2 * GEMM_BN_HALF;
-
-	// tile raster: groups of 16 row tiles sweep the column tiles, so that concurrently running CTAs share A and B tiles in L2
-	const int group = 16;
-	const int tiles_per_group = group * tiles_n;
-	const int g = blockIdx.x / tiles_per_group, r = blockIdx.x % tiles_per_group;
-	const int rows_in_group = min(group, tiles_m - g * group);
-	const int tile_m = g * group + r % rows_in_group, tile_n = r / rows_in_group;
-	const int m0 = tile_m * GEMM_BM, n0 = tile_n * N_PER_TILE;
 	const int num_kb = (K + GEMM_BK - 1) / GEMM_BK;
+	const int num_tiles = tiles_m * tiles_n;
+
+	// Persistent CTAs walk tiles blockIdx.x, + gridDim.x, ... Tile raster: groups of 16 row tiles sweep the column tiles,
+	// so that the CTAs running at the same time share A and B tiles in L2.
+	auto tile_origin = [&](int tile, int & m0, int & n0) {
+		const int group = 16, tiles_per_group = group * tiles_n;
+		const int g = tile / tiles_per_group, r = tile % tiles_per_group;
+		const int rows_in_group = min(group, tiles_m - g * group);
+		m0 = (g * group + r % rows_in_group) * GEMM_BM;
+		n0 = (r / rows_in_group) * N_PER_TILE;
+	};
 
 	if (threadIdx.x == 0) {
 		for (int s = 0; s < GEMM_STAGES; s++) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
-		mbar_init(accum_full, 1);
+		for (int a = 0; a < 2; a++) { mbar_init(&accum_full[a], 1); mbar_init(&accum_empty[a], 4); }      // 4 epilogue warps release an accumulator
 		mbar_fence_init();
 		prefetch_tensormap(&map_a); prefetch_tensormap(&map_b0); prefetch_tensormap(&map_b1);
 	}
 	if (warp == 1) tmem_alloc(tmem_slot, TMEM_COLS);
-	if (warp >= 2) {                                   // column scales of this tile
-		for (int j = threadIdx.x - 64; j < 2 * GEMM_BN_HALF; j += 128) {
-			const int half = j / GEMM_BN_HALF, col = SWIGLU ? n0 + (j % GEMM_BN_HALF) : n0 + j;
-			const float * sb = (SWIGLU && half == 1) ? sb1 : sb0;
-			s_scale[j] = col < N ? __ldg(sb + col) : 0.0f;
-		}
-	}
 	tc_fence_before_sync();
 	__syncthreads();
 	tc_fence_after_sync();
 	const uint32_t tmem_base = *tmem_slot;
 
 	if (warp == 0) {
-		// ---------------- TMA producer
+		// ---------------- TMA producer: one stream of k-blocks across all of this CTA's tiles
 		if (lane == 0) {
-			for (int kb = 0; kb < num_kb; kb++) {
-				const int s = kb % GEMM_STAGES;
-				const uint32_t parity = ((kb / GEMM_STAGES) & 1) ^ 1;
-				if (!mbar_wait_bounded(&empty[s], parity, status, 0x300u + s)) break;
-				uint8_t * a_dst = ring + (size_t) s * STAGE_BYTES;
-				uint8_t * b_dst = a_dst + A_STAGE_BYTES;
-				mbar_arrive_expect_tx(&full[s], STAGE_BYTES);
-				tma_load_2d(a_dst, &map_a, kb * GEMM_BK, m0, &full[s]);
-				if (SWIGLU) {
-					tma_load_2d(b_dst, &map_b0, kb * GEMM_BK, n0, &full[s]);
-					tma_load_2d(b_dst + GEMM_BN_HALF * GEMM_BK, &map_b1, kb * GEMM_BK, n0, &full[s]);
-				} else {
-					tma_load_2d(b_dst, &map_b0, kb * GEMM_BK, n0, &full[s]);
-					tma_load_2d(b_dst + GEMM_BN_HALF * GEMM_BK, &map_b0, kb * GEMM_BK, n0 + GEMM_BN_HALF, &full[s]);
+			uint32_t it = 0;
+			bool ok = true;
+			for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+				int m0, n0;
+				tile_origin(tile, m0, n0);
+				for (int kb = 0; kb < num_kb; kb++, it++) {
+					const int s = it % GEMM_STAGES;
+					ok = mbar_wait_bounded(&empty[s], ((it / GEMM_STAGES) & 1) ^ 1, status, 0x300u + s);
+					if (!ok) break;
+					uint8_t * a_dst = ring + (size_t) s * STAGE_BYTES;
+					uint8_t * b_dst = a_dst + A_STAGE_BYTES;
+					mbar_arrive_expect_tx(&full[s], STAGE_BYTES);
+					tma_load_2d(a_dst, &map_a, kb * GEMM_BK, m0, &full[s]);
+					if (SWIGLU) {
+						tma_load_2d(b_dst, &map_b0, kb * GEMM_BK, n0, &full[s]);
+						tma_load_2d(b_dst + GEMM_BN_HALF * GEMM_BK, &map_b1, kb * GEMM_BK, n0, &full[s]);
+					} else {
+						tma_load_2d(b_dst, &map_b0, kb * GEMM_BK, n0, &full[s]);
+						tma_load_2d(b_dst + GEMM_BN_HALF * GEMM_BK, &map_b0, kb * GEMM_BK, n0 + GEMM_BN_HALF, &full[s]);
+					}
 				}
 			}
 		}
 	} else if (warp == 1) {
-		// ---------------- MMA issuer
+		// ---------------- MMA issuer: accumulator stage (tile index % 2) lets the epilogue of one tile overlap the next tile's MMAs
 		if (lane == 0) {
 			constexpr uint32_t idesc = umma_idesc_e4m3(GEMM_BM, GEMM_BN_HALF);
+			uint32_t it = 0, local = 0;
 			bool ok = true;
-			for (int kb = 0; kb < num_kb && ok; kb++) {
-				const int s = kb % GEMM_STAGES;
-				ok = mbar_wait_bounded(&full[s], (kb / GEMM_STAGES) & 1, status, 0x310u + s);
+			for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, local++) {
+				const uint32_t acc_stage = local & 1;
+				ok = mbar_wait_bounded(&accum_empty[acc_stage], ((local >> 1) & 1) ^ 1, status, 0x330u + acc_stage);
 				if (!ok) break;
 				tc_fence_after_sync();
-				const uint8_t * a_tile = ring + (size_t) s * STAGE_BYTES;
-				const uint64_t da = umma_desc_k_sw128(a_tile);
-				const uint64_t db0 = umma_desc_k_sw128(a_tile + A_STAGE_BYTES);
-				const uint64_t db1 = umma_desc_k_sw128(a_tile + A_STAGE_BYTES + GEMM_BN_HALF * GEMM_BK);
-				#pragma unroll
-				for (int j = 0; j < GEMM_BK / 32; j++) {          // K = 32 per instruction: advance 32 bytes inside the swizzle atom
-					const uint32_t acc = (kb > 0 || j > 0) ? 1u : 0u;
-					tc_mma_f8(tmem_base, da + 2 * j, db0 + 2 * j, idesc, acc);
-					tc_mma_f8(tmem_base + GEMM_BN_HALF, da + 2 * j, db1 + 2 * j, idesc, acc);
+				const uint32_t d_tmem = tmem_base + acc_stage * (2 * GEMM_BN_HALF);
+				for (int kb = 0; kb < num_kb; kb++, it++) {
+					const int s = it % GEMM_STAGES;
+					ok = mbar_wait_bounded(&full[s], (it / GEMM_STAGES) & 1, status, 0x310u + s);
+					if (!ok) break;
+					tc_fence_after_sync();
+					const uint8_t * a_tile = ring + (size_t) s * STAGE_BYTES;
+					const uint64_t da = umma_desc_k_sw128(a_tile);
+					const uint64_t db0 = umma_desc_k_sw128(a_tile + A_STAGE_BYTES);
+					const uint64_t db1 = umma_desc_k_sw128(a_tile + A_STAGE_BYTES + GEMM_BN_HALF * GEMM_BK);
+					#pragma unroll
+					for (int j = 0; j < GEMM_BK / 32; j++) {          // K = 32 per instruction: advance 32 bytes inside the swizzle atom
+						const uint32_t acc = (kb > 0 || j > 0) ? 1u : 0u;
+						tc_mma_f8(d_tmem, da + 2 * j, db0 + 2 * j, idesc, acc);
+						tc_mma_f8(d_tmem + GEMM_BN_HALF, da + 2 * j, db1 + 2 * j, idesc, acc);
+					}
+					tc_commit(&empty[s]);                               // stage reusable once these MMAs have read it
 				}
-				tc_commit(&empty[s]);                               // stage reusable once these MMAs have read it
+				tc_commit(&accum_full[acc_stage]);                       // accumulator complete (or abandoned) -> epilogue
 			}
-			tc_commit(accum_full);                                   // accumulator complete (or abandoned) -> epilogue
 		}
 	} else {
 		// ---------------- epilogue: warp w reads TMEM lanes 32 * (w % 4) .. + 32
 		const int quarter = warp & 3;
-		const int row = m0 + quarter * 32 + lane;
-		const bool ok = __all_sync(0xffffffffu, mbar_wait_bounded(accum_full, 0, status, 0x320u));     // warp-uniform: tcgen05.ld is warp-wide
-		tc_fence_after_sync();
-		if (ok) {
+		const int etid = threadIdx.x - 64;                   // 0..127 among the epilogue threads
+		uint32_t local = 0;
+		bool ok = true;
+		for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, local++) {
+			const uint32_t acc_stage = local & 1;
+			int m0, n0;
+			tile_origin(tile, m0, n0);
+			float * scale = s_scale + acc_stage * (2 * GEMM_BN_HALF);
+			for (int j = etid; j < 2 * GEMM_BN_HALF; j += 128) {         // column scales of this tile (buffer last read two tiles ago)
+				const int half = j / GEMM_BN_HALF, col = SWIGLU ? n0 + (j % GEMM_BN_HALF) : n0 + j;
+				const float * sb = (SWIGLU && half == 1) ? sb1 : sb0;
+				scale[j] = col < N ? __ldg(sb + col) : 0.0f;
+			}
+			const int row = m0 + quarter * 32 + lane;
 			const float a_scale = row < M ? __ldg(sa + row) : 0.0f;
-			const uint32_t taddr = tmem_base + ((uint32_t) (quarter * 32) << 16);
+			const bool mine = mbar_wait_bounded(&accum_full[acc_stage], (local >> 1) & 1, status, 0x320u + acc_stage);
+			// One named barrier over the 128 epilogue threads does two jobs: it publishes the scales, and it ANDs the
+			// outcome of the wait so that all four warps take the same branch (tcgen05.ld and the barrier are collective).
+			uint32_t all_ok;
+			asm volatile("{\n\t.reg .pred p, q;\n\tsetp.ne.b32 p, %1, 0;\n\tbar.red.and.pred q, 1, 128, p;\n\tselp.u32 %0, 1, 0, q;\n\t}"
+			             : "=r"(all_ok) : "r"((uint32_t) mine) : "memory");
+			ok = all_ok != 0;
+			tc_fence_after_sync();
+			if (!ok) break;
+			const uint32_t taddr = tmem_base + acc_stage * (2 * GEMM_BN_HALF) + ((uint32_t) (quarter * 32) << 16);
 			__nv_bfloat16 * out_row = reinterpret_cast<__nv_bfloat16 *>(out) + (size_t) row * ld_out;
 			#pragma unroll 1
 			for (int c = 0; c < N_PER_TILE / 32; c++) {
@@ -247,14 +278,19 @@ gemm_e4m3_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
 					tmem_ld_32cols(taddr + GEMM_BN_HALF + c * 32, v1);
 					#pragma unroll
 					for (int i = 0; i < 32; i++) {
-						const float gte = (v0[i] * a_scale) * s_scale[c * 32 + i];
-						const float up = (v1[i] * a_scale) * s_scale[GEMM_BN_HALF + c * 32 + i];
+						const float gte = (v0[i] * a_scale) * scale[c * 32 + i];
+						const float up = (v1[i] * a_scale) * scale[GEMM_BN_HALF + c * 32 + i];
 						o[i] = (gte * fast_rcp(1.0f + fast_exp(-gte))) * up;
 					}
 				} else {
 					tmem_ld_32cols(taddr + c * 32, v0);
 					#pragma unroll
-					for (int i = 0; i < 32; i++) o[i] = (v0[i] * a_scale) * s_scale[c * 32 + i];
+					for (int i = 0; i < 32; i++) o[i] = (v0[i] * a_scale) * scale[c * 32 + i];
+				}
+				if (c == N_PER_TILE / 32 - 1) {                  // last read of this accumulator: hand it back to the MMA warp
+					tc_fence_before_sync();
+					__syncwarp();
+					if (lane == 0) mbar_arrive(&accum_empty[acc_stage]);
 				}
 				const int col0 = n0 + c * 32;
 				if (row < M) {
@@ -323,10 +359,11 @@ static int launch_gemm(int M, int N, int K, const void * A, const float * sa, co
 	if (!status) return set_error(DFB200_ERR_CUDA, "ffn_fp8: no status word");
 	constexpr int n_per_tile = SWIGLU ? GEMM_BN_HALF : 2 * GEMM_BN_HALF;
 	const int tiles_m = (M + GEMM_BM - 1) / GEMM_BM, tiles_n = (N + n_per_tile - 1) / n_per_tile;
-	const size_t smem = 1024 + GEMM_STAGES * STAGE_BYTES + (2 * GEMM_STAGES + 1) * sizeof(uint64_t) + 2 * sizeof(uint32_t) + 2 * GEMM_BN_HALF * sizeof(float);
+	const size_t smem = 1024 + GEMM_STAGES * STAGE_BYTES + (2 * GEMM_STAGES + 4) * sizeof(uint64_t) + 2 * sizeof(uint32_t) + 4 * GEMM_BN_HALF * sizeof(float);
 	auto kernel = gemm_e4m3_kernel<SWIGLU>;
 	allow_dyn_smem(reinterpret_cast<const void *>(kernel), smem);
-	kernel<<<tiles_m * tiles_n, GEMM_THREADS, smem, stream>>>(ma, mb0, mb1, M, N, K, tiles_m, tiles_n, sa, sb0, SWIGLU ? sb1 : sb0, out, ld_out, status);
+	const int grid = tiles_m * tiles_n < sm_count() ? tiles_m * tiles_n : sm_count();      // persistent: one CTA per SM
+	kernel<<<grid, GEMM_THREADS, smem, stream>>>(ma, mb0, mb1, M, N, K, tiles_m, tiles_n, sa, sb0, SWIGLU ? sb1 : sb0, out, ld_out, status);
 	return check_launch("ffn_fp8 gemm");
 }
 
