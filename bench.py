@@ -180,6 +180,8 @@ def run_gpu_arm(args):
 
     h = DataflowHandle(device_id=local, num_streams=2)
     stream = torch.cuda.ExternalStream(h.stream_ptr(0), device=torch.device("cuda", local))
+    stream1 = torch.cuda.ExternalStream(h.stream_ptr(1), device=torch.device("cuda", local))
+    exchange_state = [None]
     BF, S0 = int(DT.BF16), 0
     T = TOKENS
 
@@ -235,6 +237,9 @@ def run_gpu_arm(args):
         """One step. `events[i] = (start, end)` are recorded around op i (all ops, or just op `only`)."""
         for i, call in enumerate(calls):
             timed = events is not None and (only is None or only == i)
+            if world > 1 and i == len(calls) - 1 and exchange_state[0] is not None:
+                # rms_norm_bwd_w rewrites dW: it has to wait for the previous step's exchange, which ran on stream 1
+                assert h.submit_dependency(S0, exchange_state[0]) == 0
             if timed:
                 events[i][0].record(stream)
             rc = call()
@@ -243,8 +248,16 @@ def run_gpu_arm(args):
             if rc != 0:
                 raise RuntimeError(f"submit of {op_names[i]} failed")
         if world > 1:
-            with torch.cuda.stream(stream):
-                allreduce_step(step_loss, [dW])          # the data-parallel exchange: one packed fp32 all-reduce (16 KB)
+            # the data-parallel exchange (one packed fp32 all-reduce, 16 KB) runs on the handle's second stream behind a
+            # dependency on the compute stream, so that it overlaps the next step's kernels
+            assert h.submit_dependency(1, h.get_stream_state(S0)) == 0
+            with torch.cuda.stream(stream1):
+                allreduce_step(step_loss, [dW])
+            exchange_state[0] = h.get_stream_state(1)
+
+    def join_exchange():
+        if world > 1 and exchange_state[0] is not None:
+            assert h.submit_dependency(S0, exchange_state[0]) == 0
 
     def barrier():
         if world > 1:
@@ -269,6 +282,7 @@ def run_gpu_arm(args):
     t_begin.record(stream)
     for s in range(args.steps):
         chain(ev[s], only=DOM)
+    join_exchange()
     t_end.record(stream)
     host_enqueue_ms = 1e3 * (time.perf_counter() - host_t0) / args.steps      # host time to submit one step (no sync)
     barrier()
@@ -291,6 +305,7 @@ def run_gpu_arm(args):
     def e2e_step():
         upload()
         chain()
+        join_exchange()
         assert h.submit_outbound_transfer(S0, out_host["dW"].ctypes.data, dW, out_host["dW"].nbytes) == 0
         assert h.submit_outbound_transfer(S0, out_host["rms"].ctypes.data, rms, out_host["rms"].nbytes) == 0
         assert h.submit_outbound_transfer(S0, out_host["ws"].ctypes.data, ws, out_host["ws"].nbytes) == 0

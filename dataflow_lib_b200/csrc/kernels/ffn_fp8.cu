@@ -96,10 +96,18 @@ __host__ __device__ constexpr uint32_t umma_idesc_e4m3(int m, int n) { return (1
 // row quantisation: q[r, :] = e4m3( x[r, :] * (448 / amax_r) ),  scale[r] = amax_r / 448  (1 when the row is all zero)
 // ---------------------------------------------------------------------------------------------------------------
 template <int VPT>
-__global__ void __launch_bounds__(256)
-quantize_rows_e4m3_kernel(int n_rows, int n_cols, const void * __restrict__ X, void * __restrict__ Q, float * __restrict__ scales) {
-	__shared__ float red[8];
+__global__ void __launch_bounds__(512)
+quantize_rows_e4m3_kernel(int n_rows, int n_cols, const void * __restrict__ X, const float * __restrict__ col_mult, void * __restrict__ Q,
+                          float * __restrict__ scales) {
+	__shared__ float red[16];
 	const int n_chunks = n_cols / 8, tid = threadIdx.x, nthr = blockDim.x;
+	float mult[VPT][8];                               // optional per-column factor applied before quantisation (1 when absent)
+	#pragma unroll
+	for (int v = 0; v < VPT; v++) {
+		const int c = tid + v * nthr;
+		#pragma unroll
+		for (int i = 0; i < 8; i++) mult[v][i] = (col_mult && c < n_chunks) ? __ldg(col_mult + c * 8 + i) : 1.0f;
+	}
 	for (int row = blockIdx.x; row < n_rows; row += gridDim.x) {
 		float x[VPT][8];
 		float amax = 0.0f;
@@ -109,7 +117,7 @@ quantize_rows_e4m3_kernel(int n_rows, int n_cols, const void * __restrict__ X, v
 			if (c < n_chunks) {
 				load_elems<bf16_t, 8>(X, (uint64_t) row * n_cols + (uint64_t) c * 8, x[v]);
 				#pragma unroll
-				for (int i = 0; i < 8; i++) amax = fmaxf(amax, fabsf(x[v][i]));
+				for (int i = 0; i < 8; i++) { x[v][i] = __fmul_rn(x[v][i], mult[v][i]); amax = fmaxf(amax, fabsf(x[v][i])); }
 			}
 		}
 		amax = warp_max(amax);
@@ -133,18 +141,37 @@ quantize_rows_e4m3_kernel(int n_rows, int n_cols, const void * __restrict__ X, v
 	}
 }
 
+// out[c, r] = in[r, c] for byte matrices (weight codes): 32 x 32 tiles through shared memory.
+__global__ void __launch_bounds__(256)
+transpose_bytes_kernel(int rows, int cols, const uint8_t * __restrict__ in, int ld_in, uint8_t * __restrict__ out, int ld_out) {
+	__shared__ uint8_t tile[32][33];
+	const int r0 = blockIdx.y * 32, c0 = blockIdx.x * 32;
+	const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+	for (int i = ty; i < 32; i += 8)
+		if (r0 + i < rows && c0 + tx < cols) tile[i][tx] = in[(size_t) (r0 + i) * ld_in + c0 + tx];
+	__syncthreads();
+	for (int i = ty; i < 32; i += 8)
+		if (c0 + i < cols && r0 + tx < rows) out[(size_t) (c0 + i) * ld_out + r0 + tx] = tile[tx][i];
+}
+
 // ---------------------------------------------------------------------------------------------------------------
 // GEMM: D[m, n] = sum_k A[m, k] * B[n, k]  (e4m3 x e4m3 -> fp32 in TMEM), two 128-column halves per CTA.
-//   SWIGLU = true : half 0 = gate rows n0.., half 1 = up rows n0.. (tensor maps map_b0 / map_b1), 128 outputs:
-//                   out[m, n0 + j] = bf16( silu(g) * u ),  g = acc0 * sa[m] * sb0[n], u = acc1 * sa[m] * sb1[n]
-//   SWIGLU = false: halves are columns n0.. and n0 + 128.. of one weight matrix (map_b0 twice), 256 outputs:
-//                   out[m, n] = bf16( acc * sa[m] * sb0[n] )
+//   MODE_SWIGLU    : half 0 = gate rows n0.., half 1 = up rows n0.. (tensor maps map_b0 / map_b1), 128 outputs:
+//                    out[m, n0 + j] = bf16( silu(g) * u ),  g = acc0 * sa[m] * sb0[n], u = acc1 * sa[m] * sb1[n];
+//                    g and u are also stored (bf16) to aux0 / aux1 when those are given (saved for the backward pass)
+//   MODE_PLAIN     : halves are columns n0.. and n0 + 128.. of one weight matrix (map_b0 twice), 256 outputs:
+//                    out[m, n] = bf16( acc * sa[m] * sb0[n] )            (sb0 == NULL: no column scale)
+//   MODE_SWIGLU_BWD: as MODE_PLAIN for dh = acc * sa[m] (gradient w.r.t. the hidden activation), then with the saved
+//                    g = aux0[m, n], u = aux1[m, n]:  out[m, n] = bf16( dh * u * dsilu(g) ),  out[m, N + n] = bf16( dh * silu(g) )
+//                    (gate and up gradients side by side in one [M, 2N] buffer, ld_out = 2N)
+enum GemmMode { MODE_PLAIN = 0, MODE_SWIGLU = 1, MODE_SWIGLU_BWD = 2 };
 // ---------------------------------------------------------------------------------------------------------------
-template <bool SWIGLU>
+template <int MODE>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_e4m3_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b0, const __grid_constant__ CUtensorMap map_b1,
                  int M, int N, int K, int tiles_m, int tiles_n, const float * __restrict__ sa, const float * __restrict__ sb0,
-                 const float * __restrict__ sb1, void * __restrict__ out, int ld_out, unsigned int * status) {
+                 const float * __restrict__ sb1, void * __restrict__ out, int ld_out, void * aux0, void * aux1, unsigned int * status) {
+	constexpr bool SWIGLU = MODE == MODE_SWIGLU;
 	extern __shared__ uint8_t smem_raw[];
 	uint8_t * smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t) 1023);   // swizzled tiles need 1024-byte alignment
 	uint8_t * ring = smem;
@@ -254,7 +281,7 @@ gemm_e4m3_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
 			for (int j = etid; j < 2 * GEMM_BN_HALF; j += 128) {         // column scales of this tile (buffer last read two tiles ago)
 				const int half = j / GEMM_BN_HALF, col = SWIGLU ? n0 + (j % GEMM_BN_HALF) : n0 + j;
 				const float * sb = (SWIGLU && half == 1) ? sb1 : sb0;
-				scale[j] = col < N ? __ldg(sb + col) : 0.0f;
+				scale[j] = col < N ? (sb ? __ldg(sb + col) : 1.0f) : 0.0f;
 			}
 			const int row = m0 + quarter * 32 + lane;
 			const float a_scale = row < M ? __ldg(sa + row) : 0.0f;
@@ -269,18 +296,48 @@ gemm_e4m3_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
 			if (!ok) break;
 			const uint32_t taddr = tmem_base + acc_stage * (2 * GEMM_BN_HALF) + ((uint32_t) (quarter * 32) << 16);
 			__nv_bfloat16 * out_row = reinterpret_cast<__nv_bfloat16 *>(out) + (size_t) row * ld_out;
+			auto store32 = [&](__nv_bfloat16 * dst_row, int col0, const float (&val)[32], int n_limit) {
+				if (col0 + 32 <= n_limit) {
+					#pragma unroll
+					for (int i = 0; i < 32; i += 8) {
+						uint32_t w[4];
+						#pragma unroll
+						for (int k = 0; k < 4; k++) w[k] = Word<bf16_t>::pack(&val[i + 2 * k]);
+						*reinterpret_cast<uint4 *>(dst_row + col0 + i) = make_uint4(w[0], w[1], w[2], w[3]);
+					}
+				} else {
+					for (int i = 0; i < 32 && col0 + i < n_limit; i++) dst_row[col0 + i] = __float2bfloat16_rn(val[i]);
+				}
+			};
+			auto load32 = [&](const __nv_bfloat16 * src_row, int col0, float (&val)[32], int n_limit) {
+				if (col0 + 32 <= n_limit) {
+					#pragma unroll
+					for (int i = 0; i < 32; i += 8) {
+						const uint4 w = *reinterpret_cast<const uint4 *>(src_row + col0 + i);
+						Word<bf16_t>::unpack(w.x, &val[i]); Word<bf16_t>::unpack(w.y, &val[i + 2]);
+						Word<bf16_t>::unpack(w.z, &val[i + 4]); Word<bf16_t>::unpack(w.w, &val[i + 6]);
+					}
+				} else {
+					for (int i = 0; i < 32; i++) val[i] = col0 + i < n_limit ? __bfloat162float(src_row[col0 + i]) : 0.0f;
+				}
+			};
 			#pragma unroll 1
 			for (int c = 0; c < N_PER_TILE / 32; c++) {
 				float v0[32], o[32];
-				if (SWIGLU) {
+				const int col0 = n0 + c * 32;
+				if constexpr (MODE == MODE_SWIGLU) {
 					float v1[32];
 					tmem_ld_32cols(taddr + c * 32, v0);
 					tmem_ld_32cols(taddr + GEMM_BN_HALF + c * 32, v1);
 					#pragma unroll
 					for (int i = 0; i < 32; i++) {
-						const float gte = (v0[i] * a_scale) * scale[c * 32 + i];
-						const float up = (v1[i] * a_scale) * scale[GEMM_BN_HALF + c * 32 + i];
-						o[i] = (gte * fast_rcp(1.0f + fast_exp(-gte))) * up;
+						v0[i] = (v0[i] * a_scale) * scale[c * 32 + i];                       // gate pre-activation
+						v1[i] = (v1[i] * a_scale) * scale[GEMM_BN_HALF + c * 32 + i];        // up pre-activation
+						o[i] = (v0[i] * fast_rcp(1.0f + fast_exp(-v0[i]))) * v1[i];
+					}
+					if (row < M && aux0) {
+						store32(reinterpret_cast<__nv_bfloat16 *>(aux0) + (size_t) row * N, col0, v0, N);
+						store32(reinterpret_cast<__nv_bfloat16 *>(aux1) + (size_t) row * N, col0, v1, N);
 					}
 				} else {
 					tmem_ld_32cols(taddr + c * 32, v0);
@@ -292,18 +349,22 @@ gemm_e4m3_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
 					__syncwarp();
 					if (lane == 0) mbar_arrive(&accum_empty[acc_stage]);
 				}
-				const int col0 = n0 + c * 32;
 				if (row < M) {
-					if (col0 + 32 <= N) {
+					if constexpr (MODE == MODE_SWIGLU_BWD) {
+						// o = dL/dh; saved pre-activations give the gate and up gradients (same expressions as swiglu_bwd_x)
+						float gte[32], up[32], dgate[32], dup[32];
+						load32(reinterpret_cast<const __nv_bfloat16 *>(aux0) + (size_t) row * N, col0, gte, N);
+						load32(reinterpret_cast<const __nv_bfloat16 *>(aux1) + (size_t) row * N, col0, up, N);
 						#pragma unroll
-						for (int i = 0; i < 32; i += 8) {
-							uint32_t w[4];
-							#pragma unroll
-							for (int k = 0; k < 4; k++) w[k] = Word<bf16_t>::pack(&o[i + 2 * k]);
-							*reinterpret_cast<uint4 *>(out_row + col0 + i) = make_uint4(w[0], w[1], w[2], w[3]);
+						for (int i = 0; i < 32; i++) {
+							const float e = fast_exp(-gte[i]), ope = 1.0f + e, r = fast_rcp(ope);
+							dup[i] = o[i] * (gte[i] * r);
+							dgate[i] = o[i] * ((up[i] * (ope + gte[i] * e)) * (r * r));
 						}
+						store32(out_row, col0, dgate, N);
+						store32(out_row + N, col0, dup, N);
 					} else {
-						for (int i = 0; i < 32 && col0 + i < N; i++) out_row[col0 + i] = __float2bfloat16_rn(o[i]);
+						store32(out_row, col0, o, N);
 					}
 				}
 			}
@@ -345,11 +406,14 @@ static int make_map(CUtensorMap * map, const void * base, uint64_t rows, uint64_
 	return DFB200_OK;
 }
 
-template <bool SWIGLU>
+template <int MODE>
 static int launch_gemm(int M, int N, int K, const void * A, const float * sa, const void * B0, const float * sb0, const void * B1, const float * sb1,
-                       void * out, int ld_out, cudaStream_t stream) {
-	if (K % 16 || !aligned16(A) || !aligned16(B0) || (SWIGLU && !aligned16(B1)) || !aligned16(out) || ld_out % 8)
-		return set_error(DFB200_ERR_ARG, "ffn_fp8: K must be a multiple of 16, tensors 16-byte aligned, output pitch a multiple of 8");
+                       void * out, int ld_out, void * aux0, void * aux1, cudaStream_t stream) {
+	constexpr bool SWIGLU = MODE == MODE_SWIGLU;
+	if (K % 16 || N % 8 || !aligned16(A) || !aligned16(B0) || (SWIGLU && !aligned16(B1)) || !aligned16(out) || ld_out % 8 || !aligned16(aux0) || !aligned16(aux1))
+		return set_error(DFB200_ERR_ARG, "ffn_fp8: K must be a multiple of 16, N of 8, tensors 16-byte aligned, output pitch a multiple of 8");
+	if (!A || !sa || !B0 || !out || (SWIGLU && (!B1 || !sb0 || !sb1)) || (MODE == MODE_SWIGLU_BWD && (!aux0 || !aux1)) || (SWIGLU && !aux0 != !aux1))
+		return set_error(DFB200_ERR_ARG, "ffn_fp8: NULL tensor argument");
 	CUtensorMap ma, mb0, mb1;
 	int rc = make_map(&ma, A, (uint64_t) M, (uint64_t) K);
 	if (!rc) rc = make_map(&mb0, B0, (uint64_t) N, (uint64_t) K);
@@ -360,73 +424,133 @@ static int launch_gemm(int M, int N, int K, const void * A, const float * sa, co
 	constexpr int n_per_tile = SWIGLU ? GEMM_BN_HALF : 2 * GEMM_BN_HALF;
 	const int tiles_m = (M + GEMM_BM - 1) / GEMM_BM, tiles_n = (N + n_per_tile - 1) / n_per_tile;
 	const size_t smem = 1024 + GEMM_STAGES * STAGE_BYTES + (2 * GEMM_STAGES + 4) * sizeof(uint64_t) + 2 * sizeof(uint32_t) + 4 * GEMM_BN_HALF * sizeof(float);
-	auto kernel = gemm_e4m3_kernel<SWIGLU>;
+	auto kernel = gemm_e4m3_kernel<MODE>;
 	allow_dyn_smem(reinterpret_cast<const void *>(kernel), smem);
 	const int grid = tiles_m * tiles_n < sm_count() ? tiles_m * tiles_n : sm_count();      // persistent: one CTA per SM
-	kernel<<<grid, GEMM_THREADS, smem, stream>>>(ma, mb0, mb1, M, N, K, tiles_m, tiles_n, sa, sb0, SWIGLU ? sb1 : sb0, out, ld_out, status);
+	kernel<<<grid, GEMM_THREADS, smem, stream>>>(ma, mb0, mb1, M, N, K, tiles_m, tiles_n, sa, sb0, SWIGLU ? sb1 : sb0, out, ld_out, aux0, aux1, status);
 	return check_launch("ffn_fp8 gemm");
 }
+
+static uint64_t align256(uint64_t x) { return (x + 255) & ~255ull; }
 
 }  // namespace dfb200
 
 using namespace dfb200;
 
-extern "C" int dfb200_quantize_rows_e4m3(int n_rows, int n_cols, const void * X_bf16, void * Q_e4m3, float * row_scales, void * stream) {
+extern "C" int dfb200_quantize_rows_e4m3(int n_rows, int n_cols, const void * X_bf16, const float * col_factors, void * Q_e4m3, float * row_scales,
+                                         void * stream) {
 	if (n_rows < 0 || n_cols <= 0 || n_cols % 8) return set_error(DFB200_ERR_ARG, "quantize_rows_e4m3: bad shape %d x %d (columns must be a multiple of 8)", n_rows, n_cols);
 	if (n_rows == 0) return DFB200_OK;
 	if (!X_bf16 || !Q_e4m3 || !row_scales || !aligned16(X_bf16) || !aligned16(Q_e4m3)) return set_error(DFB200_ERR_ARG, "quantize_rows_e4m3: NULL or misaligned tensor");
 	const int n_chunks = n_cols / 8;
-	if (n_chunks > 256 * 8) return set_error(DFB200_ERR_ARG, "quantize_rows_e4m3: n_cols = %d exceeds the supported maximum of %d", n_cols, 256 * 8 * 8);
+	if (n_chunks > 512 * 8) return set_error(DFB200_ERR_ARG, "quantize_rows_e4m3: n_cols = %d exceeds the supported maximum of %d", n_cols, 512 * 8 * 8);
 	int vpt = 1;
 	while (vpt < 8 && (n_chunks + vpt - 1) / vpt > 256) vpt *= 2;
-	int threads = ((n_chunks + vpt - 1) / vpt + 31) / 32 * 32;
-	const int grid = n_rows < sm_count() * 8 ? n_rows : sm_count() * 8;
+	int threads = ((n_chunks + vpt - 1) / vpt + 31) / 32 * 32;       // <= 256 unless the row needs 8 packets per thread at 512 threads
+	const int grid = n_rows < sm_count() * 4 ? n_rows : sm_count() * 4;
 	cudaStream_t s = (cudaStream_t) stream;
 	switch (vpt) {
-		case 1: quantize_rows_e4m3_kernel<1><<<grid, threads, 0, s>>>(n_rows, n_cols, X_bf16, Q_e4m3, row_scales); break;
-		case 2: quantize_rows_e4m3_kernel<2><<<grid, threads, 0, s>>>(n_rows, n_cols, X_bf16, Q_e4m3, row_scales); break;
-		case 4: quantize_rows_e4m3_kernel<4><<<grid, threads, 0, s>>>(n_rows, n_cols, X_bf16, Q_e4m3, row_scales); break;
-		default: quantize_rows_e4m3_kernel<8><<<grid, threads, 0, s>>>(n_rows, n_cols, X_bf16, Q_e4m3, row_scales); break;
+		case 1: quantize_rows_e4m3_kernel<1><<<grid, threads, 0, s>>>(n_rows, n_cols, X_bf16, col_factors, Q_e4m3, row_scales); break;
+		case 2: quantize_rows_e4m3_kernel<2><<<grid, threads, 0, s>>>(n_rows, n_cols, X_bf16, col_factors, Q_e4m3, row_scales); break;
+		case 4: quantize_rows_e4m3_kernel<4><<<grid, threads, 0, s>>>(n_rows, n_cols, X_bf16, col_factors, Q_e4m3, row_scales); break;
+		default: quantize_rows_e4m3_kernel<8><<<grid, threads, 0, s>>>(n_rows, n_cols, X_bf16, col_factors, Q_e4m3, row_scales); break;
 	}
 	return check_launch("quantize_rows_e4m3");
 }
 
+extern "C" int dfb200_transpose_bytes(int rows, int cols, const void * in, int ld_in, void * out, int ld_out, void * stream) {
+	if (rows <= 0 || cols <= 0 || !in || !out || ld_in < cols || ld_out < rows) return set_error(DFB200_ERR_ARG, "transpose_bytes: bad arguments");
+	dim3 grid((cols + 31) / 32, (rows + 31) / 32);
+	transpose_bytes_kernel<<<grid, 256, 0, (cudaStream_t) stream>>>(rows, cols, static_cast<const uint8_t *>(in), ld_in, static_cast<uint8_t *>(out), ld_out);
+	return check_launch("transpose_bytes");
+}
+
 extern "C" int dfb200_gemm_e4m3_swiglu(int M, int N, int K, const void * A_e4m3, const float * a_row_scales, const void * Wgate_e4m3, const float * gate_scales,
-                                       const void * Wup_e4m3, const float * up_scales, void * H_bf16, void * stream) {
+                                       const void * Wup_e4m3, const float * up_scales, void * H_bf16, void * gate_save_bf16, void * up_save_bf16, void * stream) {
 	if (M <= 0 || N <= 0 || K <= 0) return set_error(DFB200_ERR_ARG, "gemm_e4m3_swiglu: bad shape");
-	return launch_gemm<true>(M, N, K, A_e4m3, a_row_scales, Wgate_e4m3, gate_scales, Wup_e4m3, up_scales, H_bf16, N, (cudaStream_t) stream);
+	return launch_gemm<MODE_SWIGLU>(M, N, K, A_e4m3, a_row_scales, Wgate_e4m3, gate_scales, Wup_e4m3, up_scales, H_bf16, N, gate_save_bf16, up_save_bf16,
+	                                (cudaStream_t) stream);
 }
 
 extern "C" int dfb200_gemm_e4m3(int M, int N, int K, const void * A_e4m3, const float * a_row_scales, const void * W_e4m3, const float * w_scales,
                                 void * out_bf16, void * stream) {
 	if (M <= 0 || N <= 0 || K <= 0) return set_error(DFB200_ERR_ARG, "gemm_e4m3: bad shape");
-	return launch_gemm<false>(M, N, K, A_e4m3, a_row_scales, W_e4m3, w_scales, nullptr, nullptr, out_bf16, N, (cudaStream_t) stream);
+	return launch_gemm<MODE_PLAIN>(M, N, K, A_e4m3, a_row_scales, W_e4m3, w_scales, nullptr, nullptr, out_bf16, N, nullptr, nullptr, (cudaStream_t) stream);
+}
+
+extern "C" int dfb200_gemm_e4m3_swiglu_bwd(int M, int N, int K, const void * dOut_e4m3, const float * dout_row_scales, const void * WdownT_e4m3,
+                                           const void * gate_saved_bf16, const void * up_saved_bf16, void * dgate_dup_bf16, void * stream) {
+	if (M <= 0 || N <= 0 || K <= 0) return set_error(DFB200_ERR_ARG, "gemm_e4m3_swiglu_bwd: bad shape");
+	return launch_gemm<MODE_SWIGLU_BWD>(M, N, K, dOut_e4m3, dout_row_scales, WdownT_e4m3, nullptr, nullptr, nullptr, dgate_dup_bf16, 2 * N,
+	                                    const_cast<void *>(gate_saved_bf16), const_cast<void *>(up_saved_bf16), (cudaStream_t) stream);
 }
 
 extern "C" uint64_t dfb200_swiglu_ffn_fp8_workspace_bytes(int T, int d, int f) {
-	// quantised input [T, d] + its scales, hidden [T, f] bf16, quantised hidden [T, f] + its scales
-	const uint64_t a = ((uint64_t) T * d + 255) & ~255ull, h = ((uint64_t) T * f * 2 + 255) & ~255ull, hq = ((uint64_t) T * f + 255) & ~255ull;
-	const uint64_t sc = ((uint64_t) T * 4 + 255) & ~255ull;
-	return a + sc + h + hq + sc;
+	// forward: quantised input [T, d] + scales, hidden [T, f] bf16, quantised hidden [T, f] + scales
+	// backward: quantised dOut [T, d] + scales, gate|up gradients [T, 2f] bf16, their quantised form [T, 2f] + scales (larger: it is the bound)
+	const uint64_t fwd = align256((uint64_t) T * d) + align256((uint64_t) T * 4) + align256((uint64_t) T * f * 2) + align256((uint64_t) T * f) + align256((uint64_t) T * 4);
+	const uint64_t bwd = align256((uint64_t) T * d) + align256((uint64_t) T * 4) + align256((uint64_t) T * f * 4) + align256((uint64_t) T * f * 2) + align256((uint64_t) T * 4);
+	return fwd > bwd ? fwd : bwd;
 }
 
 extern "C" int dfb200_swiglu_ffn_fp8(int T, int d, int f, const void * A_bf16, const void * Wgate, const float * gate_scales, const void * Wup,
-                                     const float * up_scales, const void * Wdown, const float * down_scales, void * out_bf16, void * workspace,
-                                     uint64_t workspace_bytes, void * stream) {
+                                     const float * up_scales, const void * Wdown, const float * down_scales, void * out_bf16, void * gate_save_bf16,
+                                     void * up_save_bf16, void * workspace, uint64_t workspace_bytes, void * stream) {
 	if (T <= 0 || d <= 0 || f <= 0 || d % 16 || f % 16) return set_error(DFB200_ERR_ARG, "swiglu_ffn_fp8: bad shape (T %d, d %d, f %d; d and f multiples of 16)", T, d, f);
 	const uint64_t need = dfb200_swiglu_ffn_fp8_workspace_bytes(T, d, f);
 	if (!workspace || workspace_bytes < need || !aligned16(workspace))
 		return set_error(DFB200_ERR_WORKSPACE, "swiglu_ffn_fp8: needs %llu bytes of 16-byte aligned workspace, got %llu", (unsigned long long) need, (unsigned long long) workspace_bytes);
 	uint8_t * p = static_cast<uint8_t *>(workspace);
-	auto take = [&](uint64_t bytes) { uint8_t * q = p; p += (bytes + 255) & ~255ull; return q; };
+	auto take = [&](uint64_t bytes) { uint8_t * q = p; p += align256(bytes); return q; };
 	void * Aq = take((uint64_t) T * d);
 	float * sa = reinterpret_cast<float *>(take((uint64_t) T * 4));
 	void * H = take((uint64_t) T * f * 2);
 	void * Hq = take((uint64_t) T * f);
 	float * sh = reinterpret_cast<float *>(take((uint64_t) T * 4));
-	int rc = dfb200_quantize_rows_e4m3(T, d, A_bf16, Aq, sa, stream);
-	if (!rc) rc = dfb200_gemm_e4m3_swiglu(T, f, d, Aq, sa, Wgate, gate_scales, Wup, up_scales, H, stream);
-	if (!rc) rc = dfb200_quantize_rows_e4m3(T, f, H, Hq, sh, stream);
+	int rc = dfb200_quantize_rows_e4m3(T, d, A_bf16, nullptr, Aq, sa, stream);
+	if (!rc) rc = dfb200_gemm_e4m3_swiglu(T, f, d, Aq, sa, Wgate, gate_scales, Wup, up_scales, H, gate_save_bf16, up_save_bf16, stream);
+	if (!rc) rc = dfb200_quantize_rows_e4m3(T, f, H, nullptr, Hq, sh, stream);
 	if (!rc) rc = dfb200_gemm_e4m3(T, d, f, Hq, sh, Wdown, down_scales, out_bf16, stream);
+	return rc;
+}
+
+// Backward weights: the gradient GEMMs contract over the OUTPUT channels of the forward weights, so they need the codes
+// transposed: WdownT [f, d] = Wdown^T, and WgateupT [d, 2f] = [Wgate^T | Wup^T] side by side (one GEMM with K = 2f gives
+// dA = dG Wg + dU Wu). The per-output-channel scales then sit on the contraction index; they are folded into the
+// activation gradients before those are quantised (column factors of dfb200_quantize_rows_e4m3).
+extern "C" int dfb200_ffn_fp8_prepare_bwd_weights(int d, int f, const void * Wgate, const void * Wup, const void * Wdown, void * WgateupT, void * WdownT,
+                                                  void * stream) {
+	if (d <= 0 || f <= 0 || d % 16 || f % 16) return set_error(DFB200_ERR_ARG, "ffn_fp8_prepare_bwd_weights: bad shape");
+	int rc = dfb200_transpose_bytes(f, d, Wgate, d, WgateupT, 2 * f, stream);                                   // [f, d] -> [d, f] into columns [0, f)
+	if (!rc) rc = dfb200_transpose_bytes(f, d, Wup, d, static_cast<uint8_t *>(WgateupT) + f, 2 * f, stream);     // columns [f, 2f)
+	if (!rc) rc = dfb200_transpose_bytes(d, f, Wdown, f, WdownT, d, stream);                                     // [d, f] -> [f, d]
+	return rc;
+}
+
+// dA = d(loss)/d(input) of the FFN, given dOut and the pre-activations saved by the forward pass:
+//   dOq, s1     = quantise_rows(dOut * down_scales[col])                         (scale of the contraction index folded in)
+//   dH          = (dOq WdownT^T) * s1                                            [T, f]   never stored
+//   dG | dU     = swiglu backward of dH with the saved gate / up pre-activations  [T, 2f] bf16
+//   dGUq, s2    = quantise_rows([dG | dU] * [gate_scales | up_scales])
+//   dA          = bf16( (dGUq WgateupT^T) * s2 )                                 [T, d]
+// gateup_scales is the concatenation [gate_scales | up_scales] (2f floats). Weight gradients are not computed here.
+extern "C" int dfb200_swiglu_ffn_fp8_bwd(int T, int d, int f, const void * dOut_bf16, const void * gate_saved_bf16, const void * up_saved_bf16,
+                                         const void * WdownT, const float * down_scales, const void * WgateupT, const float * gateup_scales,
+                                         void * dA_bf16, void * workspace, uint64_t workspace_bytes, void * stream) {
+	if (T <= 0 || d <= 0 || f <= 0 || d % 16 || f % 16) return set_error(DFB200_ERR_ARG, "swiglu_ffn_fp8_bwd: bad shape (T %d, d %d, f %d; d and f multiples of 16)", T, d, f);
+	const uint64_t need = dfb200_swiglu_ffn_fp8_workspace_bytes(T, d, f);
+	if (!workspace || workspace_bytes < need || !aligned16(workspace))
+		return set_error(DFB200_ERR_WORKSPACE, "swiglu_ffn_fp8_bwd: needs %llu bytes of 16-byte aligned workspace, got %llu", (unsigned long long) need, (unsigned long long) workspace_bytes);
+	uint8_t * p = static_cast<uint8_t *>(workspace);
+	auto take = [&](uint64_t bytes) { uint8_t * q = p; p += align256(bytes); return q; };
+	void * dOq = take((uint64_t) T * d);
+	float * s1 = reinterpret_cast<float *>(take((uint64_t) T * 4));
+	void * dGU = take((uint64_t) T * f * 4);
+	void * dGUq = take((uint64_t) T * f * 2);
+	float * s2 = reinterpret_cast<float *>(take((uint64_t) T * 4));
+	int rc = dfb200_quantize_rows_e4m3(T, d, dOut_bf16, down_scales, dOq, s1, stream);
+	if (!rc) rc = dfb200_gemm_e4m3_swiglu_bwd(T, f, d, dOq, s1, WdownT, gate_saved_bf16, up_saved_bf16, dGU, stream);
+	if (!rc) rc = dfb200_quantize_rows_e4m3(T, 2 * f, dGU, gateup_scales, dGUq, s2, stream);
+	if (!rc) rc = dfb200_gemm_e4m3(T, d, 2 * f, dGUq, s2, WgateupT, nullptr, dA_bf16, stream);
 	return rc;
 }

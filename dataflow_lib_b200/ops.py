@@ -110,21 +110,34 @@ def softmax_cross_entropy(n_rows, n_cols, logits, labels, dlogits, row_loss=None
                                               _stream(stream)), "softmax_cross_entropy")
 
 
-def quantize_rows_e4m3(n_rows, n_cols, X, Q, row_scales, stream=None):
-    _check(_lib_.dfb200_quantize_rows_e4m3(n_rows, n_cols, _ptr(X), _ptr(Q), _ptr(row_scales), _stream(stream)), "quantize_rows_e4m3")
+def quantize_rows_e4m3(n_rows, n_cols, X, Q, row_scales, col_factors=None, stream=None):
+    _check(_lib_.dfb200_quantize_rows_e4m3(n_rows, n_cols, _ptr(X), _ptr(col_factors), _ptr(Q), _ptr(row_scales), _stream(stream)), "quantize_rows_e4m3")
 
 
 def gemm_e4m3(M, N, K, A, a_row_scales, W, w_scales, out, stream=None):
     _check(_lib_.dfb200_gemm_e4m3(M, N, K, _ptr(A), _ptr(a_row_scales), _ptr(W), _ptr(w_scales), _ptr(out), _stream(stream)), "gemm_e4m3")
 
 
-def gemm_e4m3_swiglu(M, N, K, A, a_row_scales, Wgate, gate_scales, Wup, up_scales, H, stream=None):
+def gemm_e4m3_swiglu(M, N, K, A, a_row_scales, Wgate, gate_scales, Wup, up_scales, H, gate_save=None, up_save=None, stream=None):
     _check(_lib_.dfb200_gemm_e4m3_swiglu(M, N, K, _ptr(A), _ptr(a_row_scales), _ptr(Wgate), _ptr(gate_scales), _ptr(Wup), _ptr(up_scales),
-                                         _ptr(H), _stream(stream)), "gemm_e4m3_swiglu")
+                                         _ptr(H), _ptr(gate_save), _ptr(up_save), _stream(stream)), "gemm_e4m3_swiglu")
 
 
-def swiglu_ffn_fp8(T, d, f, A, Wgate, gate_scales, Wup, up_scales, Wdown, down_scales, out, stream=None, workspace=None):
+def swiglu_ffn_fp8(T, d, f, A, Wgate, gate_scales, Wup, up_scales, Wdown, down_scales, out, gate_save=None, up_save=None, stream=None, workspace=None):
     need = _lib_.dfb200_swiglu_ffn_fp8_workspace_bytes(T, d, f)
     ws = workspace if workspace is not None else _workspace(A.device, need)
     _check(_lib_.dfb200_swiglu_ffn_fp8(T, d, f, _ptr(A), _ptr(Wgate), _ptr(gate_scales), _ptr(Wup), _ptr(up_scales), _ptr(Wdown),
-                                       _ptr(down_scales), _ptr(out), _ptr(ws), ws.numel() * ws.element_size(), _stream(stream)), "swiglu_ffn_fp8")
+                                       _ptr(down_scales), _ptr(out), _ptr(gate_save), _ptr(up_save), _ptr(ws), ws.numel() * ws.element_size(),
+                                       _stream(stream)), "swiglu_ffn_fp8")
+
+
+def ffn_fp8_prepare_bwd_weights(d, f, Wgate, Wup, Wdown, WgateupT, WdownT, stream=None):
+    _check(_lib_.dfb200_ffn_fp8_prepare_bwd_weights(d, f, _ptr(Wgate), _ptr(Wup), _ptr(Wdown), _ptr(WgateupT), _ptr(WdownT), _stream(stream)),
+           "ffn_fp8_prepare_bwd_weights")
+
+
+def swiglu_ffn_fp8_bwd(T, d, f, dOut, gate_saved, up_saved, WdownT, down_scales, WgateupT, gateup_scales, dA, stream=None, workspace=None):
+    need = _lib_.dfb200_swiglu_ffn_fp8_workspace_bytes(T, d, f)
+    ws = workspace if workspace is not None else _workspace(dOut.device, need)
+    _check(_lib_.dfb200_swiglu_ffn_fp8_bwd(T, d, f, _ptr(dOut), _ptr(gate_saved), _ptr(up_saved), _ptr(WdownT), _ptr(down_scales), _ptr(WgateupT),
+                                           _ptr(gateup_scales), _ptr(dA), _ptr(ws), ws.numel() * ws.element_size(), _stream(stream)), "swiglu_ffn_fp8_bwd")

@@ -493,26 +493,29 @@ void oracle_fill_labels(uint32_t * out, long n, uint64_t seed, uint32_t n_classe
  *   plain epilogue     out = bf16( (acc * sa[m]) * sw[n] )
  * ---------------------------------------------------------------------------------------- */
 
-typedef struct { int n_cols; const uint16_t * X; uint8_t * Q; float * scales; } Quant;
+typedef struct { int n_cols; const uint16_t * X; const float * col; uint8_t * Q; float * scales; } Quant;
 
 static void quant_rows(long r0, long r1, void * p) {
 	Quant * a = (Quant *) p;
 	for (long r = r0; r < r1; r++) {
 		const uint16_t * x = a->X + (size_t) r * a->n_cols;
 		float amax = 0.0f;
-		for (int k = 0; k < a->n_cols; k++) { const float v = fabsf(oracle_bf16_to_f32(x[k])); if (v > amax) amax = v; }
+		for (int k = 0; k < a->n_cols; k++) { const float v = fabsf(oracle_bf16_to_f32(x[k]) * (a->col ? a->col[k] : 1.0f)); if (v > amax) amax = v; }
 		const float inv = amax > 0.0f ? 448.0f / amax : 1.0f;
 		a->scales[r] = amax > 0.0f ? amax / 448.0f : 1.0f;
-		for (int k = 0; k < a->n_cols; k++) a->Q[(size_t) r * a->n_cols + k] = oracle_f32_to_e4m3(oracle_bf16_to_f32(x[k]) * inv);
+		for (int k = 0; k < a->n_cols; k++)
+			a->Q[(size_t) r * a->n_cols + k] = oracle_f32_to_e4m3((oracle_bf16_to_f32(x[k]) * (a->col ? a->col[k] : 1.0f)) * inv);
 	}
 }
 
-void oracle_quantize_rows_e4m3(int n_rows, int n_cols, const void * X_bf16, void * Q, float * scales, int n_threads) {
-	Quant a = {n_cols, (const uint16_t *) X_bf16, (uint8_t *) Q, scales};
+/* col_factors (optional, n_cols floats): v = f32(x) * factor is what gets quantised (scales that sit on a contraction index) */
+void oracle_quantize_rows_e4m3(int n_rows, int n_cols, const void * X_bf16, const float * col_factors, void * Q, float * scales, int n_threads) {
+	Quant a = {n_cols, (const uint16_t *) X_bf16, col_factors, (uint8_t *) Q, scales};
 	for_rows(n_rows, n_threads, quant_rows, &a);
 }
 
-typedef struct { int N, K, swiglu; const uint8_t * A, * W0, * W1; const float * sa, * s0, * s1; uint16_t * out; const float * lut; } Gemm8;
+/* mode 0 plain, 1 gate/up + SwiGLU (optionally saving g and u), 2 SwiGLU backward from saved g and u */
+typedef struct { int N, K, mode; const uint8_t * A, * W0, * W1; const float * sa, * s0, * s1; uint16_t * out, * g_save, * u_save; const float * lut; } Gemm8;
 
 static void gemm8_rows(long r0, long r1, void * p) {
 	Gemm8 * a = (Gemm8 *) p;
@@ -523,33 +526,47 @@ static void gemm8_rows(long r0, long r1, void * p) {
 			const uint8_t * w0 = a->W0 + (size_t) n * a->K;
 			double acc0 = 0.0, acc1 = 0.0;
 			for (int k = 0; k < a->K; k++) acc0 += (double) (arow[k] * a->lut[w0[k]]);       /* products of two e4m3 values are exact in fp32 */
-			if (a->swiglu) {
+			if (a->mode == 1) {
 				const uint8_t * w1 = a->W1 + (size_t) n * a->K;
 				for (int k = 0; k < a->K; k++) acc1 += (double) (arow[k] * a->lut[w1[k]]);
 				const float g = ((float) acc0 * a->sa[m]) * a->s0[n], u = ((float) acc1 * a->sa[m]) * a->s1[n];
 				a->out[(size_t) m * a->N + n] = oracle_f32_to_bf16((g / (1.0f + expf(-g))) * u);
+				if (a->g_save) { a->g_save[(size_t) m * a->N + n] = oracle_f32_to_bf16(g); a->u_save[(size_t) m * a->N + n] = oracle_f32_to_bf16(u); }
+			} else if (a->mode == 2) {
+				/* dh from the accumulator; gate and up gradients with the expressions of swiglu_bwd_x.cu:68-77 on the saved bf16 g, u */
+				const float dh = (float) acc0 * a->sa[m];
+				const float g = oracle_bf16_to_f32(a->g_save[(size_t) m * a->N + n]), u = oracle_bf16_to_f32(a->u_save[(size_t) m * a->N + n]);
+				const float e = expf(-g);
+				a->out[(size_t) m * 2 * a->N + n] = oracle_f32_to_bf16(dh * ((u * (1 + e + g * e)) / ((1 + e) * (1 + e))));
+				a->out[(size_t) m * 2 * a->N + a->N + n] = oracle_f32_to_bf16(dh * (g / (1 + e)));
 			} else {
-				a->out[(size_t) m * a->N + n] = oracle_f32_to_bf16(((float) acc0 * a->sa[m]) * a->s0[n]);
+				a->out[(size_t) m * a->N + n] = oracle_f32_to_bf16(((float) acc0 * a->sa[m]) * (a->s0 ? a->s0[n] : 1.0f));
 			}
 		}
 	}
 	free(arow);
 }
 
-static void gemm8(int M, int N, int K, int swiglu, const void * A, const float * sa, const void * W0, const float * s0, const void * W1,
-                  const float * s1, void * out, int n_threads) {
+static void gemm8(int M, int N, int K, int mode, const void * A, const float * sa, const void * W0, const float * s0, const void * W1,
+                  const float * s1, void * out, void * g_save, void * u_save, int n_threads) {
 	float lut[256];
 	for (int i = 0; i < 256; i++) lut[i] = oracle_e4m3_to_f32((uint8_t) i);
 	lut[0x7f] = 0.0f; lut[0xff] = 0.0f;          /* NaN codes never occur in quantised data */
-	Gemm8 a = {N, K, swiglu, (const uint8_t *) A, (const uint8_t *) W0, (const uint8_t *) W1, sa, s0, s1, (uint16_t *) out, lut};
+	Gemm8 a = {N, K, mode, (const uint8_t *) A, (const uint8_t *) W0, (const uint8_t *) W1, sa, s0, s1, (uint16_t *) out, (uint16_t *) g_save, (uint16_t *) u_save, lut};
 	for_rows(M, n_threads, gemm8_rows, &a);
 }
 
 void oracle_gemm_e4m3(int M, int N, int K, const void * A, const float * sa, const void * W, const float * sw, void * out_bf16, int n_threads) {
-	gemm8(M, N, K, 0, A, sa, W, sw, NULL, NULL, out_bf16, n_threads);
+	gemm8(M, N, K, 0, A, sa, W, sw, NULL, NULL, out_bf16, NULL, NULL, n_threads);
 }
 
 void oracle_gemm_e4m3_swiglu(int M, int N, int K, const void * A, const float * sa, const void * Wg, const float * sg, const void * Wu,
-                             const float * su, void * H_bf16, int n_threads) {
-	gemm8(M, N, K, 1, A, sa, Wg, sg, Wu, su, H_bf16, n_threads);
+                             const float * su, void * H_bf16, void * g_save_bf16, void * u_save_bf16, int n_threads) {
+	gemm8(M, N, K, 1, A, sa, Wg, sg, Wu, su, H_bf16, g_save_bf16, u_save_bf16, n_threads);
+}
+
+/* dGU [M, 2N]: gate gradients in columns [0, N), up gradients in [N, 2N) */
+void oracle_gemm_e4m3_swiglu_bwd(int M, int N, int K, const void * dOq, const float * s_rows, const void * WdownT, const void * g_saved_bf16,
+                                 const void * u_saved_bf16, void * dGU_bf16, int n_threads) {
+	gemm8(M, N, K, 2, dOq, s_rows, WdownT, NULL, NULL, NULL, dGU_bf16, (void *) g_saved_bf16, (void *) u_saved_bf16, n_threads);
 }

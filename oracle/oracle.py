@@ -37,9 +37,10 @@ _sig = {
     "oracle_softmax": (None, [_i, _i, _i, _i, _vp, _vp, _i]),
     "oracle_cross_entropy_loss": (None, [_i, _i, _i, _vp, _vp]),
     "oracle_softmax_cross_entropy": (None, [_i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _i]),
-    "oracle_quantize_rows_e4m3": (None, [_i, _i, _vp, _vp, _vp, _i]),
+    "oracle_quantize_rows_e4m3": (None, [_i, _i, _vp, _vp, _vp, _vp, _i]),
     "oracle_gemm_e4m3": (None, [_i, _i, _i, _vp, _vp, _vp, _vp, _vp, _i]),
-    "oracle_gemm_e4m3_swiglu": (None, [_i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i]),
+    "oracle_gemm_e4m3_swiglu": (None, [_i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i]),
+    "oracle_gemm_e4m3_swiglu_bwd": (None, [_i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i]),
     "oracle_fill_normal": (None, [_i, _vp, _l, _l, _u64, _f, _f, _i]),
     "oracle_fill_labels": (None, [_vp, _l, _u64, C.c_uint32]),
 }
@@ -154,11 +155,12 @@ def softmax_cross_entropy(fwd_dt, bwd_dt, logits, labels, threads=None):
     return dl, row_loss, loss_sum
 
 
-def quantize_rows_e4m3(X_bf16, threads=None):
-    """Per-row e4m3 quantisation: returns (codes uint8 [rows, cols], scales fp32 [rows])."""
+def quantize_rows_e4m3(X_bf16, col_factors=None, threads=None):
+    """Per-row e4m3 quantisation of X * col_factors: returns (codes uint8 [rows, cols], scales fp32 [rows])."""
     Q = np.empty(X_bf16.shape, np.uint8)
     sc = np.empty(X_bf16.shape[0], np.float32)
-    _lib.oracle_quantize_rows_e4m3(X_bf16.shape[0], X_bf16.shape[1], _p(X_bf16), _p(Q), _p(sc), threads or N_THREADS)
+    cf = None if col_factors is None else np.ascontiguousarray(col_factors, np.float32)
+    _lib.oracle_quantize_rows_e4m3(X_bf16.shape[0], X_bf16.shape[1], _p(X_bf16), _p(cf), _p(Q), _p(sc), threads or N_THREADS)
     return Q, sc
 
 
@@ -175,15 +177,37 @@ def gemm_e4m3(A, sa, W, sw, threads=None):
     return out
 
 
-def gemm_e4m3_swiglu(A, sa, Wg, sg, Wu, su, threads=None):
+def gemm_e4m3_swiglu(A, sa, Wg, sg, Wu, su, save=False, threads=None):
+    """H = silu(g) * u; with save=True also returns the bf16 pre-activations (H, g, u)."""
     out = np.empty((A.shape[0], Wg.shape[0]), np.uint16)
-    _lib.oracle_gemm_e4m3_swiglu(A.shape[0], Wg.shape[0], A.shape[1], _p(A), _p(sa), _p(Wg), _p(sg), _p(Wu), _p(su), _p(out), threads or N_THREADS)
+    g = np.empty_like(out) if save else None
+    u = np.empty_like(out) if save else None
+    _lib.oracle_gemm_e4m3_swiglu(A.shape[0], Wg.shape[0], A.shape[1], _p(A), _p(sa), _p(Wg), _p(sg), _p(Wu), _p(su), _p(out), _p(g), _p(u),
+                                 threads or N_THREADS)
+    return (out, g, u) if save else out
+
+
+def gemm_e4m3_swiglu_bwd(dOq, s_rows, WdownT, g_saved, u_saved, threads=None):
+    """[dG | dU] (bf16 [M, 2f]) from the quantised output gradient, the transposed down weights and the saved pre-activations."""
+    M, f = g_saved.shape
+    out = np.empty((M, 2 * f), np.uint16)
+    _lib.oracle_gemm_e4m3_swiglu_bwd(M, f, dOq.shape[1], _p(dOq), _p(s_rows), _p(WdownT), _p(g_saved), _p(u_saved), _p(out), threads or N_THREADS)
     return out
 
 
 def swiglu_ffn_fp8(A_bf16, Wg, sg, Wu, su, Wd, sd, threads=None):
-    """The whole forward: quantise rows, gate/up + SwiGLU, quantise the hidden rows, down projection. Returns (out, hidden)."""
-    Aq, sa = quantize_rows_e4m3(A_bf16, threads)
-    H = gemm_e4m3_swiglu(Aq, sa, Wg, sg, Wu, su, threads)
-    Hq, sh = quantize_rows_e4m3(H, threads)
-    return gemm_e4m3(Hq, sh, Wd, sd, threads), H
+    """The whole forward: quantise rows, gate/up + SwiGLU, quantise the hidden rows, down projection. Returns (out, g, u)."""
+    Aq, sa = quantize_rows_e4m3(A_bf16, None, threads)
+    H, g, u = gemm_e4m3_swiglu(Aq, sa, Wg, sg, Wu, su, True, threads)
+    Hq, sh = quantize_rows_e4m3(H, None, threads)
+    return gemm_e4m3(Hq, sh, Wd, sd, threads), g, u
+
+
+def swiglu_ffn_fp8_bwd(dOut_bf16, g, u, Wg, sg, Wu, su, Wd, sd, threads=None):
+    """Input gradient of the FFN (see dfb200_swiglu_ffn_fp8_bwd): returns dA bf16 [T, d]."""
+    WdT = np.ascontiguousarray(Wd.T)                                           # [f, d]
+    WguT = np.ascontiguousarray(np.concatenate([Wg.T, Wu.T], axis=1))          # [d, 2f]
+    dOq, s1 = quantize_rows_e4m3(dOut_bf16, sd, threads)
+    dGU = gemm_e4m3_swiglu_bwd(dOq, s1, WdT, g, u, threads)
+    dGUq, s2 = quantize_rows_e4m3(dGU, np.concatenate([sg, su]), threads)
+    return gemm_e4m3(dGUq, s2, WguT, None, threads)

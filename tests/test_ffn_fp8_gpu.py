@@ -72,11 +72,14 @@ def test_swiglu_ffn_fp8_forward(ops):
     Wg, sg = _weights(f, d, 12)
     Wu, su = _weights(f, d, 13)
     Wd, sd = _weights(d, f, 14)
-    ref, _ = O.swiglu_ffn_fp8(A, Wg, sg, Wu, su, Wd, sd)
+    ref, ref_g, ref_u = O.swiglu_ffn_fp8(A, Wg, sg, Wu, su, Wd, sd)
     out = torch.empty((T, d), dtype=torch.bfloat16, device="cuda")
+    G, U = torch.empty((T, f), dtype=torch.bfloat16, device="cuda"), torch.empty((T, f), dtype=torch.bfloat16, device="cuda")
     t = lambda a: torch.from_numpy(a).cuda()
-    ops.swiglu_ffn_fp8(T, d, f, to_dev(A, O.BF16), t(Wg), t(sg), t(Wu), t(su), t(Wd), t(sd), out)
+    ops.swiglu_ffn_fp8(T, d, f, to_dev(A, O.BF16), t(Wg), t(sg), t(Wu), t(su), t(Wd), t(sd), out, G, U)
     torch.cuda.synchronize()
+    assert check_lowp(to_host(G, O.BF16), ref_g, O.BF16, "saved gate pre-activation") > 0.99
+    assert check_lowp(to_host(U, O.BF16), ref_u, O.BF16, "saved up pre-activation") > 0.99
     # the hidden rows are re-quantised from bf16 values that may differ by one ulp from the oracle's: allow 2e-2 here
     check_lowp(to_host(out, O.BF16), ref, O.BF16, "swiglu_ffn_fp8 out", rel=2e-2)
     # and against the unquantised-activation FFN the fp8 activations cost a few per cent of the output scale
@@ -86,6 +89,64 @@ def test_swiglu_ffn_fp8_forward(ops):
     full = ((g / (1 + np.exp(-g))) * u) @ wd.T.astype(np.float64)
     err = np.sqrt(((f32(to_host(out, O.BF16), O.BF16) - full) ** 2).mean()) / np.sqrt((full ** 2).mean())
     assert err < 0.08, err
+
+
+@pytest.mark.parametrize("shape", [(192, 512, 1024), (100, 256, 384), (256, 4096, 1792)], ids=str)
+def test_swiglu_ffn_fp8_backward(ops, shape):
+    T, d, f = shape
+    A = O.fill_normal(O.BF16, (T, d), 21)
+    Wg, sg = _weights(f, d, 22)
+    Wu, su = _weights(f, d, 23)
+    Wd, sd = _weights(d, f, 24)
+    dOut = O.fill_normal(O.BF16, (T, d), 25)
+    _, g, u = O.swiglu_ffn_fp8(A, Wg, sg, Wu, su, Wd, sd)
+    ref = O.swiglu_ffn_fp8_bwd(dOut, g, u, Wg, sg, Wu, su, Wd, sd)
+    t = lambda a: torch.from_numpy(a).cuda()
+    WguT = torch.empty((d, 2 * f), dtype=torch.uint8, device="cuda")
+    WdT = torch.empty((f, d), dtype=torch.uint8, device="cuda")
+    ops.ffn_fp8_prepare_bwd_weights(d, f, t(Wg), t(Wu), t(Wd), WguT, WdT)
+    torch.cuda.synchronize()
+    assert np.array_equal(WdT.cpu().numpy(), Wd.T) and np.array_equal(WguT.cpu().numpy(), np.concatenate([Wg.T, Wu.T], axis=1))
+    dA = torch.empty((T, d), dtype=torch.bfloat16, device="cuda")
+    # backward from the ORACLE's saved pre-activations, so that the comparison isolates the backward kernels
+    ops.swiglu_ffn_fp8_bwd(T, d, f, to_dev(dOut, O.BF16), to_dev(g, O.BF16), to_dev(u, O.BF16), WdT, t(sd), WguT, t(np.concatenate([sg, su])), dA)
+    torch.cuda.synchronize()
+    # gate/up gradients are re-quantised from bf16 values that can differ from the oracle's by one ulp: 2e-2
+    check_lowp(to_host(dA, O.BF16), ref, O.BF16, f"swiglu_ffn_fp8_bwd dA {shape}", rel=2e-2)
+    # against autograd of the dequantised-weight FFN in fp64 the fp8 gradients cost a few per cent of the gradient's scale
+    a64 = torch.tensor(f32(A, O.BF16), dtype=torch.float64, requires_grad=True)
+    wg, wu, wd = (torch.tensor(f32(W, O.E4M3) * s[:, None], dtype=torch.float64) for W, s in ((Wg, sg), (Wu, su), (Wd, sd)))
+    ((torch.nn.functional.silu(a64 @ wg.T) * (a64 @ wu.T)) @ wd.T).backward(torch.tensor(f32(dOut, O.BF16), dtype=torch.float64))
+    full = a64.grad.numpy()
+    err = np.sqrt(((f32(to_host(dA, O.BF16), O.BF16) - full) ** 2).mean()) / np.sqrt((full ** 2).mean())
+    assert err < 0.1, err
+
+
+def test_gemm_swiglu_bwd_epilogue(ops):
+    M, f, d = 200, 264, 400
+    dOq, s1 = O.quantize_rows_e4m3(O.fill_normal(O.BF16, (M, d), 31))
+    WdT, _ = _weights(f, d, 32)
+    g, u = O.fill_normal(O.BF16, (M, f), 33), O.fill_normal(O.BF16, (M, f), 34)
+    ref = O.gemm_e4m3_swiglu_bwd(dOq, s1, WdT, g, u)
+    out = torch.full((M, 2 * f), float("nan"), dtype=torch.bfloat16, device="cuda")
+    from dataflow_lib_b200 import _lib
+    t = lambda a: torch.from_numpy(a).cuda()
+    a_, s_, w_, g_, u_ = t(dOq), t(s1), t(WdT), to_dev(g, O.BF16), to_dev(u, O.BF16)
+    rc = _lib.lib.dfb200_gemm_e4m3_swiglu_bwd(M, f, d, a_.data_ptr(), s_.data_ptr(), w_.data_ptr(), g_.data_ptr(), u_.data_ptr(), out.data_ptr(),
+                                              torch.cuda.current_stream().cuda_stream)
+    assert rc == 0, _lib.last_error()
+    torch.cuda.synchronize()
+    assert check_lowp(to_host(out, O.BF16), ref, O.BF16, "gemm_e4m3_swiglu_bwd") > 0.98
+
+
+def test_quantize_rows_with_column_factors(ops):
+    shape = (64, 28672)
+    X, cf = O.fill_normal(O.BF16, shape, 41), np.abs(O.fill_normal(O.FP32, (shape[1],), 42)) + 0.1
+    q_ref, s_ref = O.quantize_rows_e4m3(X, cf)
+    Q, sc = torch.empty(shape, dtype=torch.uint8, device="cuda"), torch.empty(shape[0], device="cuda")
+    ops.quantize_rows_e4m3(shape[0], shape[1], to_dev(X, O.BF16), Q, sc, torch.from_numpy(cf).cuda())
+    torch.cuda.synchronize()
+    assert np.array_equal(Q.cpu().numpy(), q_ref) and np.array_equal(sc.cpu().numpy(), s_ref)
 
 
 def test_ffn_waits_completed(ops):
