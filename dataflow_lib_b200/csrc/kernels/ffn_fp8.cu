@@ -14,7 +14,7 @@
 // (2 x 256 of the 512 columns) let the epilogue of one tile overlap the MMAs of the next. Warp-specialised:
 //   warp 0      one thread issues TMA tile loads (cp.async.bulk.tensor, 128-byte swizzle, CTA-local destination)
 //               into a 4-stage shared-memory ring (A 128x128 B + B 256x128 B per stage), completion on mbarriers;
-//   warp 1      allocates 256 columns of tensor memory; one thread issues tcgen05.mma (M128 N128/256 K32, fp32
+//   warp 1      allocates the tensor memory; one thread issues tcgen05.mma (M128 N256 K32, fp32
 //               accumulation in TMEM) and tcgen05.commit, which releases ring stages and finally signals the epilogue;
 //   warps 2-5   read the accumulator with tcgen05.ld (each warp its 32-lane quarter), apply the scales (and SwiGLU
 //               for the gate/up pair, whose two 128-column halves are the gate and the up projection of the same 128
@@ -238,7 +238,7 @@ gemm_e4m3_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
 	} else if (warp == 1) {
 		// ---------------- MMA issuer: accumulator stage (tile index % 2) lets the epilogue of one tile overlap the next tile's MMAs
 		if (lane == 0) {
-			constexpr uint32_t idesc = umma_idesc_e4m3(GEMM_BM, GEMM_BN_HALF);
+			constexpr uint32_t idesc = umma_idesc_e4m3(GEMM_BM, 2 * GEMM_BN_HALF);
 			uint32_t it = 0, local = 0;
 			bool ok = true;
 			for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, local++) {
@@ -253,15 +253,13 @@ gemm_e4m3_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
 					if (!ok) break;
 					tc_fence_after_sync();
 					const uint8_t * a_tile = ring + (size_t) s * STAGE_BYTES;
+					// The two 128-row B halves are adjacent in shared memory and form one 256-row K-major tile, so a single
+					// M128 x N256 x K32 instruction (the largest 1-CTA shape) fills both accumulator halves.
 					const uint64_t da = umma_desc_k_sw128(a_tile);
-					const uint64_t db0 = umma_desc_k_sw128(a_tile + A_STAGE_BYTES);
-					const uint64_t db1 = umma_desc_k_sw128(a_tile + A_STAGE_BYTES + GEMM_BN_HALF * GEMM_BK);
+					const uint64_t db = umma_desc_k_sw128(a_tile + A_STAGE_BYTES);
 					#pragma unroll
-					for (int j = 0; j < GEMM_BK / 32; j++) {          // K = 32 per instruction: advance 32 bytes inside the swizzle atom
-						const uint32_t acc = (kb > 0 || j > 0) ? 1u : 0u;
-						tc_mma_f8(d_tmem, da + 2 * j, db0 + 2 * j, idesc, acc);
-						tc_mma_f8(d_tmem + GEMM_BN_HALF, da + 2 * j, db1 + 2 * j, idesc, acc);
-					}
+					for (int j = 0; j < GEMM_BK / 32; j++)            // K = 32 per instruction: advance 32 bytes inside the swizzle atom
+						tc_mma_f8(d_tmem, da + 2 * j, db + 2 * j, idesc, (kb > 0 || j > 0) ? 1u : 0u);
 					tc_commit(&empty[s]);                               // stage reusable once these MMAs have read it
 				}
 				tc_commit(&accum_full[acc_stage]);                       // accumulator complete (or abandoned) -> epilogue

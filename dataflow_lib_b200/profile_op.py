@@ -17,7 +17,7 @@ D, NH, NKV, HD, F, V = 4096, 32, 8, 128, 14336, 128256
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("op", choices=["rms_norm", "rms_norm_bwd_x", "rms_norm_bwd_w", "rope", "rope_bwd_x", "swiglu", "swiglu_bwd_x",
-                                   "softmax", "softmax_cross_entropy", "swiglu_ffn_fp8", "gemm_e4m3_swiglu", "gemm_e4m3", "fp8_peak"])
+                                   "softmax", "softmax_cross_entropy", "swiglu_ffn_fp8", "swiglu_ffn_fp8_bwd", "gemm_e4m3_swiglu", "gemm_e4m3", "fp8_peak"])
     ap.add_argument("--tokens", type=int, default=2048)
     ap.add_argument("--iters", type=int, default=3)
     ap.add_argument("--dtype", default="bf16", choices=["bf16", "fp16", "fp32"])
@@ -28,22 +28,36 @@ def main():
     rn = lambda *s: torch.randn(*s, device="cuda", generator=g).to(dt)
     es = torch.empty(0, dtype=dt).element_size()
     if a.op == "fp8_peak":
-        # the tensor-core ceiling for the FFN numbers: a library e4m3 GEMM (torch._scaled_mm -> cuBLASLt), 8192^3, best of 10
-        n = 8192
-        A8 = torch.randn(n, n, device="cuda", generator=g).to(torch.float8_e4m3fn)
-        B8 = torch.randn(n, n, device="cuda", generator=g).to(torch.float8_e4m3fn).t()
+        # the tensor-core ceiling for the FFN numbers: a library e4m3 GEMM (torch._scaled_mm -> cuBLASLt). Burst = best single launch
+        # of 8192^3; sustained = the FFN's own shapes, 5 launches back to back (what profile_op reports for this library's kernels)
         one = torch.ones((), device="cuda")
+
+        def lib_gemm(m, n, k):
+            A8 = torch.randn(m, k, device="cuda", generator=g).to(torch.float8_e4m3fn)
+            B8 = torch.randn(n, k, device="cuda", generator=g).to(torch.float8_e4m3fn).t()
+            return lambda: torch._scaled_mm(A8, B8, scale_a=one, scale_b=one, out_dtype=torch.bfloat16)
+
+        f8 = lib_gemm(8192, 8192, 8192)
         best = 1e9
         for _ in range(10):
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            e0.record()
-            torch._scaled_mm(A8, B8, scale_a=one, scale_b=one, out_dtype=torch.bfloat16)
-            e1.record()
+            e0.record(); f8(); e1.record()
             torch.cuda.synchronize()
             best = min(best, e0.elapsed_time(e1))
-        print(f"fp8_peak: library e4m3 GEMM 8192^3 best of 10: {best * 1e3:.1f} us, {2 * n ** 3 / (best * 1e-3) / 1e12:.0f} TFLOP/s")
+        print(f"fp8_peak burst: library e4m3 GEMM 8192^3 best of 10: {best * 1e3:.1f} us, {2 * 8192 ** 3 / (best * 1e-3) / 1e12:.0f} TFLOP/s")
+        for name, (m, n, k) in {"gate or up projection": (T, F, D), "down projection": (T, D, F)}.items():
+            fn = lib_gemm(m, n, k)
+            fn(); torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(a.iters):
+                fn()
+            e1.record()
+            torch.cuda.synchronize()
+            ms = e0.elapsed_time(e1) / a.iters
+            print(f"fp8_peak sustained: library e4m3 GEMM {m}x{n}x{k} ({name}), {a.iters} back to back: {ms * 1e3:.1f} us, {2 * m * n * k / (ms * 1e-3) / 1e12:.0f} TFLOP/s")
         return
-    if a.op in ("swiglu_ffn_fp8", "gemm_e4m3_swiglu", "gemm_e4m3"):
+    if a.op in ("swiglu_ffn_fp8", "swiglu_ffn_fp8_bwd", "gemm_e4m3_swiglu", "gemm_e4m3"):
         def qw(n_out, n_in):
             W = 0.02 * torch.randn(n_out, n_in, device="cuda", generator=g)
             sc = W.abs().amax(1) / 448.0
@@ -58,10 +72,16 @@ def main():
         ops.quantize_rows_e4m3(T, D, A, Aq, sa)
         ops.gemm_e4m3_swiglu(T, F, D, Aq, sa, Wg, sg, Wu, su, H)
         ops.quantize_rows_e4m3(T, F, H, Hq, sh)
-        fn = {"swiglu_ffn_fp8": lambda: ops.swiglu_ffn_fp8(T, D, F, A, Wg, sg, Wu, su, Wd, sd, out),
+        G, U = torch.empty_like(H), torch.empty_like(H)
+        WguT, WdT = torch.empty(D, 2 * F, device="cuda", dtype=torch.uint8), torch.empty(F, D, device="cuda", dtype=torch.uint8)
+        ops.ffn_fp8_prepare_bwd_weights(D, F, Wg, Wu, Wd, WguT, WdT)
+        ops.swiglu_ffn_fp8(T, D, F, A, Wg, sg, Wu, su, Wd, sd, out, G, U)
+        dOut, dA, sgu = rn(T, D), torch.empty(T, D, device="cuda", dtype=torch.bfloat16), torch.cat([sg, su])
+        fn = {"swiglu_ffn_fp8": lambda: ops.swiglu_ffn_fp8(T, D, F, A, Wg, sg, Wu, su, Wd, sd, out, G, U),
+              "swiglu_ffn_fp8_bwd": lambda: ops.swiglu_ffn_fp8_bwd(T, D, F, dOut, G, U, WdT, sd, WguT, sgu, dA),
               "gemm_e4m3_swiglu": lambda: ops.gemm_e4m3_swiglu(T, F, D, Aq, sa, Wg, sg, Wu, su, H),
               "gemm_e4m3": lambda: ops.gemm_e4m3(T, D, F, Hq, sh, Wd, sd, out)}[a.op]
-        flops = {"swiglu_ffn_fp8": 6.0, "gemm_e4m3_swiglu": 4.0, "gemm_e4m3": 2.0}[a.op] * T * D * F
+        flops = {"swiglu_ffn_fp8": 6.0, "swiglu_ffn_fp8_bwd": 6.0, "gemm_e4m3_swiglu": 4.0, "gemm_e4m3": 2.0}[a.op] * T * D * F
         fn()
         torch.cuda.synchronize()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
