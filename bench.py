@@ -18,6 +18,9 @@ Synthetic seeded inputs (N(0,1); weight N(1, 0.02)). The working set of a step (
           handle->submit_inbound_transfer, runs the ops, and reads the weight gradient and the per-row statistics
           back through submit_outbound_transfer.
 `roofline` the dominant kernel (swiglu_bwd_x: 5 tensors x 14336 x 2 B per token), timed with events around each launch.
+
+    python bench.py --workload stack [--gpus N]              a second, non-default workload: the 4-layer token-sharded training
+                                                             step (FP8 FFN, vocabulary projection, fused softmax + cross entropy)
 """
 import argparse
 import json
@@ -86,8 +89,12 @@ def cpu_baseline(target_seconds=12.0):
     sample = int(min(TOKENS, max(64, rate * target_seconds)))
     sample -= sample % 64
     rate, secs = cpu_chain_tokens_per_s(sample, threads)
-    return {"value": rate, "unit": UNIT, "cores": threads, "kind": "port",
-            "sample": f"{sample} of {TOKENS} tokens of the same chain, oracle/oracle.c on {threads} threads, {secs:.1f} s"}
+    passes, total = 1, secs
+    while total < target_seconds and passes < 64:                       # the whole batch is short on a many-core host: repeat it
+        _, secs = cpu_chain_tokens_per_s(sample, threads)
+        passes, total = passes + 1, total + secs
+    return {"value": sample * passes / total, "unit": UNIT, "cores": threads, "kind": "port",
+            "sample": f"{passes} passes over {sample} of {TOKENS} tokens of the same chain, oracle/oracle.c on {threads} threads, {total:.1f} s"}
 
 
 def run_reference_arm(args):
@@ -362,15 +369,142 @@ def run_gpu_arm(args):
         dist.destroy_process_group()
 
 
+def run_stack_arm(args):
+    """--workload stack: the token-sharded 4-layer training step of dataflow_lib_b200/op_stack.py (16384 tokens per GPU,
+    d 4096, ffn 14336, 32/8 heads x 128, vocabulary 128256; bf16 activations, FP8 FFN weights, seed-0 random weights identical
+    on every rank, data seeded per rank; loss sum and RMSNorm weight gradients all-reduced over NCCL). Not the default
+    workload: `value` is tokens/s of the whole step, the library vocabulary GEMMs included and reported separately."""
+    import torch
+    import torch.distributed as dist
+
+    from dataflow_lib_b200 import ops
+    from dataflow_lib_b200.op_stack import OpStackStep
+
+    rank, world, local = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1")), int(os.environ.get("LOCAL_RANK", "0"))
+    assert world == args.gpus, f"--gpus {args.gpus} but WORLD_SIZE={world} (launch N > 1 with torchrun)"
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    T, V, LAYERS = args.tokens or 16384, 128256, 4
+    st = OpStackStep(T, D_MODEL, FFN, N_HEADS, N_KV, HEAD_DIM, V, LAYERS, EPS, float(THETA))
+    st.random_weights(seed=0)
+    g = torch.Generator(device="cuda").manual_seed(1 + rank)
+    host_x = torch.randn(T, D_MODEL, generator=g, device="cuda").bfloat16().cpu().pin_memory()
+    host_labels = torch.randint(0, V, (T,), generator=g, device="cuda", dtype=torch.int32).cpu().pin_memory()
+    host_loss = torch.zeros(2).pin_memory()
+    st.x[0].copy_(host_x); st.labels.copy_(host_labels)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    warm = max(args.warmup, 3)
+    for _ in range(warm):
+        st.step()
+    barrier()
+    sampler = ClockSampler("GPU-" + str(torch.cuda.get_device_properties(local).uuid)) if rank == 0 else None
+    ev = lambda: torch.cuda.Event(enable_timing=True)
+    t0, t1 = ev(), ev()
+    barrier()
+    t0.record()
+    for _ in range(args.steps):
+        st.step()
+    t1.record()
+    barrier()
+    ms_total = t0.elapsed_time(t1)
+
+    # end to end: the step's tokens and labels come from pinned host memory, the loss goes back, every step
+    e_steps = max(3, min(args.steps, 10))
+    def e2e_step():
+        st.x[0].copy_(host_x, non_blocking=True); st.labels.copy_(host_labels, non_blocking=True)
+        st.step()
+        host_loss.copy_(st.loss_sum, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+    e2e_step()
+    e0, e1 = ev(), ev()
+    barrier()
+    e0.record()
+    for _ in range(e_steps):
+        e2e_step()
+    e1.record()
+    barrier()
+    ms_e2e = e0.elapsed_time(e1)
+
+    # untimed accounting: three more steps with an event at every segment boundary, and this library's dominant kernel by itself
+    st.marks = []
+    for _ in range(3):
+        st.step()
+    torch.cuda.synchronize()
+    breakdown = {k: v / 3 for k, v in st.segment_ms().items()}
+    st.marks = None
+
+    def timed(fn, n=5):
+        fn(); a, b = ev(), ev()
+        a.record()
+        for _ in range(n):
+            fn()
+        b.record(); torch.cuda.synchronize()
+        return a.elapsed_time(b) / n
+    Aq = torch.empty(T, D_MODEL, dtype=torch.uint8, device="cuda"); sa = torch.empty(T, device="cuda")
+    ops.quantize_rows_e4m3(T, D_MODEL, st.h, Aq, sa)
+    H = torch.empty(T, FFN, dtype=torch.bfloat16, device="cuda")
+    ms_gemm = timed(lambda: ops.gemm_e4m3_swiglu(T, FFN, D_MODEL, Aq, sa, st.Wg[0], st.sg[0], st.Wu[0], st.su[0], H, st.G[0], st.U[0]))
+    clocks = sampler.stop() if sampler else None
+    status = ops.read_kernel_status()
+    assert not any(status), f"a device-side wait gave up: {status}"
+
+    times = torch.tensor([ms_total, ms_e2e], device="cuda", dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(times, op=dist.ReduceOp.MAX)
+    ms_total, ms_e2e = times.tolist()
+    if rank == 0:
+        try:
+            with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+                bf16_sustained, src = float(json.load(f)["bf16_tflops_sustained"]), "2 x bf16_tflops_sustained of MEASURED_PEAKS.json (it holds no fp8 figure)"
+        except (OSError, KeyError, ValueError):
+            bf16_sustained, src = 1400.0, "2 x the fallback's sustained bf16 figure"
+        flops = 4.0 * T * D_MODEL * FFN
+        achieved = flops / (ms_gemm * 1e-3) / 1e12
+        step_ms = ms_total / args.steps
+        line = {
+            "metric": "tokens_per_s_op_stack_step", "value": world * T * args.steps / (ms_total * 1e-3), "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": warm, "ms_per_step": step_ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "bf16 activations, e4m3 FFN operands with fp32 accumulation", "data": "synthetic",
+            "config": {"workload": f"4-layer op stack step fwd+bwd (RMSNorm -> RoPE -> FP8 SwiGLU FFN + residual) x4 + head (RMSNorm -> vocabulary GEMM -> "
+                                   f"fused softmax+CE), {T} tokens/GPU, d 4096, ffn 14336, vocab 128256",
+                       "tokens_per_gpu": T, "l2": "inputs larger than L2 (tens of GB touched per step)",
+                       "parallelism": f"token-sharded x{world}" + (", NCCL all-reduce of loss and RMSNorm weight gradients" if world > 1 else "")},
+            "roofline": {"bound": "tensor", "kernel": "gemm_e4m3_kernel<SWIGLU> (gate+up projections with the SwiGLU epilogue)", "achieved": achieved,
+                         "peak": 2 * bf16_sustained, "unit": "TFLOP/s", "frac": achieved / (2 * bf16_sustained), "traffic": None, "peak_source": src},
+            "step_breakdown_ms": breakdown,
+            "e2e": {"value": world * T * e_steps / (ms_e2e * 1e-3), "unit": UNIT, "h2d_bytes_per_step": host_x.numel() * 2 + host_labels.numel() * 4,
+                    "d2h_bytes_per_step": 8, "steps": e_steps, "ms_per_step": ms_e2e / e_steps},
+            "gpu_launches": st.library_launches_per_step() * args.steps,
+            "loss": float(st.loss_sum[0]) / max(float(st.loss_sum[1]), 1.0),
+            "clocks": clocks,
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--workload", default="chain", choices=["chain", "stack"],
+                    help="chain (default): the elementwise op chain the headline metric is quoted on; stack: the 4-layer token-sharded training step")
+    ap.add_argument("--tokens", type=int, default=0, help="stack workload only: tokens per GPU (default 16384)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference_arm(args)
+    elif args.workload == "stack":
+        if args.steps == 200:
+            args.steps = 10
+        run_stack_arm(args)
     else:
         run_gpu_arm(args)
 

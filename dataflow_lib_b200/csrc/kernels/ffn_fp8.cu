@@ -160,7 +160,7 @@ transpose_bytes_kernel(int rows, int cols, const uint8_t * __restrict__ in, int 
 //                    out[m, n0 + j] = bf16( silu(g) * u ),  g = acc0 * sa[m] * sb0[n], u = acc1 * sa[m] * sb1[n];
 //                    g and u are also stored (bf16) to aux0 / aux1 when those are given (saved for the backward pass)
 //   MODE_PLAIN     : halves are columns n0.. and n0 + 128.. of one weight matrix (map_b0 twice), 256 outputs:
-//                    out[m, n] = bf16( acc * sa[m] * sb0[n] )            (sb0 == NULL: no column scale)
+//                    out[m, n] = bf16( acc * sa[m] * sb0[n] + residual[m, n] )   (sb0 == NULL: no column scale; residual = aux0, optional)
 //   MODE_SWIGLU_BWD: as MODE_PLAIN for dh = acc * sa[m] (gradient w.r.t. the hidden activation), then with the saved
 //                    g = aux0[m, n], u = aux1[m, n]:  out[m, n] = bf16( dh * u * dsilu(g) ),  out[m, N + n] = bf16( dh * silu(g) )
 //                    (gate and up gradients side by side in one [M, 2N] buffer, ld_out = 2N)
@@ -170,7 +170,7 @@ template <int MODE>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_e4m3_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b0, const __grid_constant__ CUtensorMap map_b1,
                  int M, int N, int K, int tiles_m, int tiles_n, const float * __restrict__ sa, const float * __restrict__ sb0,
-                 const float * __restrict__ sb1, void * __restrict__ out, int ld_out, void * aux0, void * aux1, unsigned int * status) {
+                 const float * __restrict__ sb1, void * out, int ld_out, void * aux0, void * aux1, unsigned int * status) {
 	constexpr bool SWIGLU = MODE == MODE_SWIGLU;
 	extern __shared__ uint8_t smem_raw[];
 	uint8_t * smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t) 1023);   // swizzled tiles need 1024-byte alignment
@@ -341,6 +341,12 @@ gemm_e4m3_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
 					tmem_ld_32cols(taddr + c * 32, v0);
 					#pragma unroll
 					for (int i = 0; i < 32; i++) o[i] = (v0[i] * a_scale) * scale[c * 32 + i];
+					if (MODE == MODE_PLAIN && aux0 && row < M) {          // residual: out = bf16( acc * scales + residual )
+						float res[32];
+						load32(reinterpret_cast<const __nv_bfloat16 *>(aux0) + (size_t) row * N, col0, res, N);
+						#pragma unroll
+						for (int i = 0; i < 32; i++) o[i] += res[i];
+					}
 				}
 				if (c == N_PER_TILE / 32 - 1) {                  // last read of this accumulator: hand it back to the MMA warp
 					tc_fence_before_sync();
@@ -410,7 +416,7 @@ static int launch_gemm(int M, int N, int K, const void * A, const float * sa, co
 	constexpr bool SWIGLU = MODE == MODE_SWIGLU;
 	if (K % 16 || N % 8 || !aligned16(A) || !aligned16(B0) || (SWIGLU && !aligned16(B1)) || !aligned16(out) || ld_out % 8 || !aligned16(aux0) || !aligned16(aux1))
 		return set_error(DFB200_ERR_ARG, "ffn_fp8: K must be a multiple of 16, N of 8, tensors 16-byte aligned, output pitch a multiple of 8");
-	if (!A || !sa || !B0 || !out || (SWIGLU && (!B1 || !sb0 || !sb1)) || (MODE == MODE_SWIGLU_BWD && (!aux0 || !aux1)) || (SWIGLU && !aux0 != !aux1))
+	if (!A || !sa || !B0 || !out || (SWIGLU && (!B1 || !sb0 || !sb1)) || (MODE == MODE_SWIGLU_BWD && (!aux0 || !aux1)) || (SWIGLU && !aux0 != !aux1))   // plain: aux0 = optional residual
 		return set_error(DFB200_ERR_ARG, "ffn_fp8: NULL tensor argument");
 	CUtensorMap ma, mb0, mb1;
 	int rc = make_map(&ma, A, (uint64_t) M, (uint64_t) K);
@@ -471,9 +477,10 @@ extern "C" int dfb200_gemm_e4m3_swiglu(int M, int N, int K, const void * A_e4m3,
 }
 
 extern "C" int dfb200_gemm_e4m3(int M, int N, int K, const void * A_e4m3, const float * a_row_scales, const void * W_e4m3, const float * w_scales,
-                                void * out_bf16, void * stream) {
+                                const void * residual_bf16, void * out_bf16, void * stream) {
 	if (M <= 0 || N <= 0 || K <= 0) return set_error(DFB200_ERR_ARG, "gemm_e4m3: bad shape");
-	return launch_gemm<MODE_PLAIN>(M, N, K, A_e4m3, a_row_scales, W_e4m3, w_scales, nullptr, nullptr, out_bf16, N, nullptr, nullptr, (cudaStream_t) stream);
+	return launch_gemm<MODE_PLAIN>(M, N, K, A_e4m3, a_row_scales, W_e4m3, w_scales, nullptr, nullptr, out_bf16, N, const_cast<void *>(residual_bf16), nullptr,
+	                               (cudaStream_t) stream);
 }
 
 extern "C" int dfb200_gemm_e4m3_swiglu_bwd(int M, int N, int K, const void * dOut_e4m3, const float * dout_row_scales, const void * WdownT_e4m3,
@@ -492,8 +499,8 @@ extern "C" uint64_t dfb200_swiglu_ffn_fp8_workspace_bytes(int T, int d, int f) {
 }
 
 extern "C" int dfb200_swiglu_ffn_fp8(int T, int d, int f, const void * A_bf16, const void * Wgate, const float * gate_scales, const void * Wup,
-                                     const float * up_scales, const void * Wdown, const float * down_scales, void * out_bf16, void * gate_save_bf16,
-                                     void * up_save_bf16, void * workspace, uint64_t workspace_bytes, void * stream) {
+                                     const float * up_scales, const void * Wdown, const float * down_scales, const void * residual_bf16, void * out_bf16,
+                                     void * gate_save_bf16, void * up_save_bf16, void * workspace, uint64_t workspace_bytes, void * stream) {
 	if (T <= 0 || d <= 0 || f <= 0 || d % 16 || f % 16) return set_error(DFB200_ERR_ARG, "swiglu_ffn_fp8: bad shape (T %d, d %d, f %d; d and f multiples of 16)", T, d, f);
 	const uint64_t need = dfb200_swiglu_ffn_fp8_workspace_bytes(T, d, f);
 	if (!workspace || workspace_bytes < need || !aligned16(workspace))
@@ -508,7 +515,7 @@ extern "C" int dfb200_swiglu_ffn_fp8(int T, int d, int f, const void * A_bf16, c
 	int rc = dfb200_quantize_rows_e4m3(T, d, A_bf16, nullptr, Aq, sa, stream);
 	if (!rc) rc = dfb200_gemm_e4m3_swiglu(T, f, d, Aq, sa, Wgate, gate_scales, Wup, up_scales, H, gate_save_bf16, up_save_bf16, stream);
 	if (!rc) rc = dfb200_quantize_rows_e4m3(T, f, H, nullptr, Hq, sh, stream);
-	if (!rc) rc = dfb200_gemm_e4m3(T, d, f, Hq, sh, Wdown, down_scales, out_bf16, stream);
+	if (!rc) rc = dfb200_gemm_e4m3(T, d, f, Hq, sh, Wdown, down_scales, residual_bf16, out_bf16, stream);
 	return rc;
 }
 
@@ -549,6 +556,6 @@ extern "C" int dfb200_swiglu_ffn_fp8_bwd(int T, int d, int f, const void * dOut_
 	int rc = dfb200_quantize_rows_e4m3(T, d, dOut_bf16, down_scales, dOq, s1, stream);
 	if (!rc) rc = dfb200_gemm_e4m3_swiglu_bwd(T, f, d, dOq, s1, WdownT, gate_saved_bf16, up_saved_bf16, dGU, stream);
 	if (!rc) rc = dfb200_quantize_rows_e4m3(T, 2 * f, dGU, gateup_scales, dGUq, s2, stream);
-	if (!rc) rc = dfb200_gemm_e4m3(T, d, 2 * f, dGUq, s2, WgateupT, nullptr, dA_bf16, stream);
+	if (!rc) rc = dfb200_gemm_e4m3(T, d, 2 * f, dGUq, s2, WgateupT, nullptr, nullptr, dA_bf16, stream);
 	return rc;
 }

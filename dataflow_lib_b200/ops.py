@@ -43,6 +43,17 @@ def _check(rc, what):
         raise RuntimeError(f"{what} failed ({rc}): {_lib.last_error()}")
 
 
+def read_kernel_status(stream=None):
+    """The device-side status words (one per kernel family that waits on asynchronous copies): all zero unless a bounded
+    wait gave up. Synchronises `stream`."""
+    import ctypes
+    words = (ctypes.c_uint32 * 8)()
+    rc = _lib_.dfb200_read_kernel_status(_stream(stream), words, 8)
+    if rc < 0:
+        _check(rc, "read_kernel_status")
+    return list(words)
+
+
 _workspaces = {}
 
 
@@ -114,8 +125,8 @@ def quantize_rows_e4m3(n_rows, n_cols, X, Q, row_scales, col_factors=None, strea
     _check(_lib_.dfb200_quantize_rows_e4m3(n_rows, n_cols, _ptr(X), _ptr(col_factors), _ptr(Q), _ptr(row_scales), _stream(stream)), "quantize_rows_e4m3")
 
 
-def gemm_e4m3(M, N, K, A, a_row_scales, W, w_scales, out, stream=None):
-    _check(_lib_.dfb200_gemm_e4m3(M, N, K, _ptr(A), _ptr(a_row_scales), _ptr(W), _ptr(w_scales), _ptr(out), _stream(stream)), "gemm_e4m3")
+def gemm_e4m3(M, N, K, A, a_row_scales, W, w_scales, out, residual=None, stream=None):
+    _check(_lib_.dfb200_gemm_e4m3(M, N, K, _ptr(A), _ptr(a_row_scales), _ptr(W), _ptr(w_scales), _ptr(residual), _ptr(out), _stream(stream)), "gemm_e4m3")
 
 
 def gemm_e4m3_swiglu(M, N, K, A, a_row_scales, Wgate, gate_scales, Wup, up_scales, H, gate_save=None, up_save=None, stream=None):
@@ -123,11 +134,12 @@ def gemm_e4m3_swiglu(M, N, K, A, a_row_scales, Wgate, gate_scales, Wup, up_scale
                                          _ptr(H), _ptr(gate_save), _ptr(up_save), _stream(stream)), "gemm_e4m3_swiglu")
 
 
-def swiglu_ffn_fp8(T, d, f, A, Wgate, gate_scales, Wup, up_scales, Wdown, down_scales, out, gate_save=None, up_save=None, stream=None, workspace=None):
+def swiglu_ffn_fp8(T, d, f, A, Wgate, gate_scales, Wup, up_scales, Wdown, down_scales, out, gate_save=None, up_save=None, residual=None, stream=None,
+                   workspace=None):
     need = _lib_.dfb200_swiglu_ffn_fp8_workspace_bytes(T, d, f)
     ws = workspace if workspace is not None else _workspace(A.device, need)
     _check(_lib_.dfb200_swiglu_ffn_fp8(T, d, f, _ptr(A), _ptr(Wgate), _ptr(gate_scales), _ptr(Wup), _ptr(up_scales), _ptr(Wdown),
-                                       _ptr(down_scales), _ptr(out), _ptr(gate_save), _ptr(up_save), _ptr(ws), ws.numel() * ws.element_size(),
+                                       _ptr(down_scales), _ptr(residual), _ptr(out), _ptr(gate_save), _ptr(up_save), _ptr(ws), ws.numel() * ws.element_size(),
                                        _stream(stream)), "swiglu_ffn_fp8")
 
 

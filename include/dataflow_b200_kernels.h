@@ -136,18 +136,19 @@ int dfb200_softmax_cross_entropy(int fwd_dt, int bwd_dt, int n_rows, int n_cols,
  * accumulation in tensor memory. Weights: e4m3, stored [out_features, in_features] row-major, one fp32 scale per
  * output channel (w = code * scale). Activations: bf16, quantised inside to e4m3 with one scale per row.
  *   dfb200_quantize_rows_e4m3    v = X[r,c] * col_factors[c] (factors optional); Q = e4m3(v * 448 / amax_r); row_scales[r] = amax_r / 448
- *   dfb200_gemm_e4m3             out[m,n] = bf16( (sum_k A[m,k] W[n,k]) * a_row_scales[m] * w_scales[n] )      (w_scales may be NULL)
+ *   dfb200_gemm_e4m3             out[m,n] = bf16( (sum_k A[m,k] W[n,k]) * a_row_scales[m] * w_scales[n] + residual[m,n] )
+ *                                (w_scales and residual may be NULL; residual bf16 [M,N], may alias out)
  *   dfb200_gemm_e4m3_swiglu      H[m,n] = bf16( silu(g) * u ), g / u = the same with the gate / up weights; g and u are also stored
  *                                (bf16 [M,N]) when gate_save / up_save are given
  *   dfb200_gemm_e4m3_swiglu_bwd  dh = (sum_k dOut[m,k] WdownT[n,k]) * row_scale[m]; [dG | dU][m, n and N+n] from dh and the saved g, u
- *   dfb200_swiglu_ffn_fp8        out = down(swiglu(gate(A), up(A)));  dfb200_swiglu_ffn_fp8_bwd: dA from dOut and the saved g, u
+ *   dfb200_swiglu_ffn_fp8        out = down(swiglu(gate(A), up(A))) + residual (optional);  dfb200_swiglu_ffn_fp8_bwd: dA from dOut and the saved g, u
  *   dfb200_ffn_fp8_prepare_bwd_weights  WgateupT [d, 2f] = [Wgate^T | Wup^T], WdownT [f, d] = Wdown^T (codes only)
  * Both FFN calls take dfb200_swiglu_ffn_fp8_workspace_bytes() bytes of scratch from the caller. Weight gradients are not computed.
  * Shapes: reduction lengths multiples of 16, N a multiple of 8, 16-byte aligned tensors, row length of a quantised matrix <= 32768. */
 int dfb200_quantize_rows_e4m3(int n_rows, int n_cols, const void * X_bf16, const float * col_factors, void * Q_e4m3, float * row_scales, void * stream);
 int dfb200_transpose_bytes(int rows, int cols, const void * in, int ld_in, void * out, int ld_out, void * stream);
 int dfb200_gemm_e4m3(int M, int N, int K, const void * A_e4m3, const float * a_row_scales, const void * W_e4m3, const float * w_scales,
-                     void * out_bf16, void * stream);
+                     const void * residual_bf16, void * out_bf16, void * stream);
 int dfb200_gemm_e4m3_swiglu(int M, int N, int K, const void * A_e4m3, const float * a_row_scales, const void * Wgate_e4m3,
                             const float * gate_scales, const void * Wup_e4m3, const float * up_scales, void * H_bf16,
                             void * gate_save_bf16, void * up_save_bf16, void * stream);
@@ -155,7 +156,7 @@ int dfb200_gemm_e4m3_swiglu_bwd(int M, int N, int K, const void * dOut_e4m3, con
                                 const void * gate_saved_bf16, const void * up_saved_bf16, void * dgate_dup_bf16, void * stream);
 uint64_t dfb200_swiglu_ffn_fp8_workspace_bytes(int T, int d, int f);
 int dfb200_swiglu_ffn_fp8(int T, int d, int f, const void * A_bf16, const void * Wgate, const float * gate_scales, const void * Wup,
-                          const float * up_scales, const void * Wdown, const float * down_scales, void * out_bf16,
+                          const float * up_scales, const void * Wdown, const float * down_scales, const void * residual_bf16, void * out_bf16,
                           void * gate_save_bf16, void * up_save_bf16, void * workspace, uint64_t workspace_bytes, void * stream);
 int dfb200_ffn_fp8_prepare_bwd_weights(int d, int f, const void * Wgate, const void * Wup, const void * Wdown, void * WgateupT, void * WdownT,
                                        void * stream);

@@ -49,6 +49,14 @@ def test_gemm_e4m3(ops, mnk):
     torch.cuda.synchronize()
     frac = check_lowp(to_host(out, O.BF16), ref, O.BF16, f"gemm_e4m3 {mnk}")
     assert frac > 0.98, frac
+    # residual fused into the epilogue (in place on the residual buffer): bf16( fp32 result + residual )
+    res = O.fill_normal(O.BF16, (M, N), 15)
+    buf = to_dev(res, O.BF16)
+    ops.gemm_e4m3(M, N, K, torch.from_numpy(Aq).cuda(), torch.from_numpy(sa).cuda(), torch.from_numpy(Wq).cuda(), torch.from_numpy(sw).cuda(), buf, residual=buf)
+    torch.cuda.synchronize()
+    acc = (f32(Aq, O.E4M3).astype(np.float64) @ f32(Wq, O.E4M3).astype(np.float64).T).astype(np.float32)
+    want = O.from_f32((acc * sa[:, None]) * sw[None, :] + f32(res, O.BF16), O.BF16)
+    assert check_lowp(to_host(buf, O.BF16), want, O.BF16, f"gemm_e4m3 + residual {mnk}") > 0.98
 
 
 @pytest.mark.parametrize("mnk", [(128, 128, 128), (256, 512, 512), (200, 264, 400), (64, 14336 // 8, 4096)], ids=str)
