@@ -43,6 +43,9 @@ KERNEL_ABI = {
     "dfb200_swiglu_ffn_fp8": (_i, [_i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _u64, _vp]),
     "dfb200_ffn_fp8_prepare_bwd_weights": (_i, [_i, _i, _vp, _vp, _vp, _vp, _vp, _vp]),
     "dfb200_swiglu_ffn_fp8_bwd": (_i, [_i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _u64, _vp]),
+    "dfb200_embedding": (_i, [_i, _i, _i, _vp, _vp, _vp, _vp]),
+    "dfb200_copy_to_seq_context": (_i, [_i, _u64, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp]),
+    "dfb200_select_experts": (_i, [_i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
     "dfb200_softmax_cross_entropy_workspace_bytes": (_u64, [_i, _i]),
     "dfb200_softmax_cross_entropy": (_i, [_i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _u64, _vp]),
 }
@@ -89,6 +92,10 @@ HOST_ABI = {
     "set_native_softmax_skeleton": (None, [_SK, _i, _i]),
     "set_native_cross_entropy_loss_skeleton": (None, [_SK, _i]),
     "set_native_softmax_cross_entropy_skeleton": (None, [_SK, _i, _i]),
+    "set_native_select_experts_skeleton": (None, [_SK, _i]),
+    "submit_embedding": (_i, [_H, _i, _i, _i, _i, _vp, _vp, _vp]),
+    "submit_copy_to_seq_context": (_i, [_H, _i, _i, _u64, _i, _i, _vp, _vp, _vp, _vp, _vp]),
+    "submit_select_experts": (_i, [_H, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp]),
     "submit_rms_norm": (_i, [_H, _i, _i, _i, _i, _f, _vp, _vp, _vp, _vp, _vp]),
     "submit_rms_norm_bwd_x": (_i, [_H, _i, _i, _i, _i, _i, _f, _vp, _vp, _vp, _vp, _vp, _vp]),
     "submit_rms_norm_bwd_w": (_i, [_H, _i, _i, _i, _i, _i, _f, _vp, _vp, _vp, _vp]),
@@ -111,6 +118,9 @@ HOST_ABI = {
     "dataflow_b200_softmax": (_i, [_H, _i, _vp, _vp]),
     "dataflow_b200_cross_entropy_loss": (_i, [_H, _i, _vp, _vp]),
     "dataflow_b200_softmax_cross_entropy": (_i, [_H, _i, _vp, _vp]),
+    "dataflow_b200_embedding": (_i, [_H, _i, _vp, _vp]),
+    "dataflow_b200_copy_to_seq_context": (_i, [_H, _i, _vp, _vp]),
+    "dataflow_b200_select_experts": (_i, [_H, _i, _vp, _vp]),
 }
 
 for _table in (KERNEL_ABI, HOST_ABI):

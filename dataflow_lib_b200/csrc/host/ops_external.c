@@ -120,3 +120,22 @@ int dataflow_b200_softmax_cross_entropy(Dataflow_Handle * h, int stream_id, Op *
 	                                           ARG(op, 4, void *), row_loss, loss_sum, scratch, scratch_bytes, stream_of(h, stream_id)),
 	              "softmax_cross_entropy");
 }
+
+int dataflow_b200_embedding(Dataflow_Handle * h, int stream_id, Op * op, void * op_extra) {
+	(void) op_extra;
+	return finish(dfb200_embedding(DT(op, 3), ARG(op, 0, int), ARG(op, 1, int), ARG(op, 2, uint32_t *), ARG(op, 3, void *), ARG(op, 4, void *),
+	                               stream_of(h, stream_id)), "embedding");
+}
+
+int dataflow_b200_copy_to_seq_context(Dataflow_Handle * h, int stream_id, Op * op, void * op_extra) {
+	(void) op_extra;
+	return finish(dfb200_copy_to_seq_context(DT(op, 3), ARG(op, 0, uint64_t), ARG(op, 1, int), ARG(op, 2, int), ARG(op, 3, void *), ARG(op, 4, void *),
+	                                         ARG(op, 5, int *), ARG(op, 6, uint64_t *), ARG(op, 7, int *), stream_of(h, stream_id)), "copy_to_seq_context");
+}
+
+int dataflow_b200_select_experts(Dataflow_Handle * h, int stream_id, Op * op, void * op_extra) {
+	(void) op_extra;
+	return finish(dfb200_select_experts(DT(op, 3), ARG(op, 0, int), ARG(op, 1, int), ARG(op, 2, int), ARG(op, 3, void *), ARG(op, 4, void *),
+	                                    ARG(op, 5, uint16_t *), ARG(op, 6, int *), ARG(op, 7, int *), ARG(op, 8, int *), stream_of(h, stream_id)),
+	              "select_experts");
+}

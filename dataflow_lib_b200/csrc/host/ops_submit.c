@@ -97,3 +97,31 @@ int submit_softmax_cross_entropy(Dataflow_Handle * handle, int stream_id, Datafl
 	ARGS(op, &n_rows, &n_cols, &logits, &labels, &dlogits, &row_loss, &loss_sum);
 	return submit(handle, &op, stream_id, "softmax cross entropy");
 }
+
+/* src/dataflow_ops/src/preprocess_ops.c:3-34 */
+int submit_embedding(Dataflow_Handle * handle, int stream_id, DataflowDatatype fwd_dt, int num_tokens, int embed_dim,
+                     uint32_t * token_ids, void * embedding_table, void * output) {
+	Op op;
+	set_native_embedding_skeleton(&op.op_skeleton, fwd_dt);
+	ARGS(op, &num_tokens, &embed_dim, &token_ids, &embedding_table, &output);
+	return submit(handle, &op, stream_id, "embedding");
+}
+
+/* src/dataflow_ops/src/attn_misc_ops.c:69-101 */
+int submit_copy_to_seq_context(Dataflow_Handle * handle, int stream_id, DataflowDatatype fwd_dt, uint64_t N, int total_tokens, int kv_dim,
+                               void * X_k, void * X_v, int * seq_positions, uint64_t * seq_context_ptrs, int * seq_context_sizes) {
+	Op op;
+	set_native_copy_to_seq_context_skeleton(&op.op_skeleton, fwd_dt);
+	ARGS(op, &N, &total_tokens, &kv_dim, &X_k, &X_v, &seq_positions, &seq_context_ptrs, &seq_context_sizes);
+	return submit(handle, &op, stream_id, "copy to seq context");
+}
+
+int submit_select_experts(Dataflow_Handle * handle, int stream_id, DataflowDatatype fwd_dt, int total_tokens, int n_experts, int top_k_experts,
+                          void * X_routed, void * token_expert_weights, uint16_t * chosen_experts, int * expert_counts,
+                          int * expert_counts_cumsum, int * num_routed_by_expert) {
+	Op op;
+	set_native_select_experts_skeleton(&op.op_skeleton, fwd_dt);
+	ARGS(op, &total_tokens, &n_experts, &top_k_experts, &X_routed, &token_expert_weights, &chosen_experts, &expert_counts, &expert_counts_cumsum,
+	     &num_routed_by_expert);
+	return submit(handle, &op, stream_id, "select experts");
+}

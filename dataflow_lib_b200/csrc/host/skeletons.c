@@ -95,6 +95,10 @@ void set_native_cross_entropy_loss_skeleton(Op_Skeleton * skeleton, DataflowData
 	char nick[MAX_OP_NICKNAME_SIZE];   /* n_rows, n_cols, pred_logits, labels */
 	build_skeleton(skeleton, nick1(nick, "cross_entropy_loss", bwd), I_S, I_S, bwd, DATAFLOW_UINT32, END);
 }
+void set_native_select_experts_skeleton(Op_Skeleton * skeleton, DataflowDatatype fwd) {
+	char nick[MAX_OP_NICKNAME_SIZE];   /* total_tokens, n_experts, top_k, X_routed, weights, chosen_experts, counts, cumsum, num_routed */
+	build_skeleton(skeleton, nick1(nick, "select_experts", fwd), I_S, I_S, I_S, fwd, fwd, DATAFLOW_UINT16, DATAFLOW_INT, DATAFLOW_INT, DATAFLOW_INT, END);
+}
 void set_native_softmax_cross_entropy_skeleton(Op_Skeleton * skeleton, DataflowDatatype fwd, DataflowDatatype bwd) {
 	char nick[MAX_OP_NICKNAME_SIZE];   /* n_rows, n_cols, logits, labels, dlogits, row_loss, loss_sum */
 	build_skeleton(skeleton, nick2(nick, "softmax_cross_entropy", fwd, bwd), I_S, I_S, fwd, DATAFLOW_UINT32, bwd, DATAFLOW_FP32, DATAFLOW_FP32, END);
@@ -113,6 +117,7 @@ int set_native_op_skeleton(Op_Skeleton * skeleton, char * op_name, DataflowDatat
 	else if (!strcmp(op_name, "softmax")) set_native_softmax_skeleton(skeleton, fwd_dt, bwd_dt);
 	else if (!strcmp(op_name, "cross_entropy_loss")) set_native_cross_entropy_loss_skeleton(skeleton, bwd_dt);
 	else if (!strcmp(op_name, "softmax_cross_entropy")) set_native_softmax_cross_entropy_skeleton(skeleton, fwd_dt, bwd_dt);
+	else if (!strcmp(op_name, "select_experts")) set_native_select_experts_skeleton(skeleton, fwd_dt);
 	else {
 		printf("Cannot set skeleton, unknown op: %s, with fwd_dt: %s, bwd_dt: %s\n", op_name,
 		       dataflow_datatype_as_string(fwd_dt), dataflow_datatype_as_string(bwd_dt));
@@ -131,10 +136,12 @@ typedef struct {
 	bool needs_workspace;     /* give the op an init function that allocates per-handle scratch */
 } Op_Family;
 
-/* The reference registers 54 identities (set_native_op_skeletons.c:13-39). `embedding` (5) is
- * outside the transformer op path this library implements and is not exported, which leaves
- * 49 reference identities, plus the 7 datatype pairs of the fused softmax+cross-entropy op. */
+/* The reference registers 54 identities (set_native_op_skeletons.c:13-39): all of them are here. Added: the 5
+ * copy_to_seq_context identities (the reference has the skeleton, the wrapper and the kernels but leaves them out of
+ * its registration list), 5 select_experts identities (kernels only in the reference) and the 7 datatype pairs of
+ * the fused softmax+cross-entropy op: 71 in total. */
 static const Op_Family FAMILIES[] = {
+	{"embedding", KEY_FWD, false},      {"copy_to_seq_context", KEY_FWD, false}, {"select_experts", KEY_FWD, false},
 	{"rms_norm", KEY_FWD, false},       {"rms_norm_bwd_x", KEY_PAIR, false}, {"rms_norm_bwd_w", KEY_PAIR, true},
 	{"rope", KEY_FWD, false},           {"rope_bwd_x", KEY_BWD, false},
 	{"swiglu", KEY_FWD, false},         {"swiglu_bwd_x", KEY_PAIR, false},

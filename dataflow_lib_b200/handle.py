@@ -99,6 +99,19 @@ class DataflowHandle:
         return _L.submit_softmax_cross_entropy(C.byref(self.h), stream_id, int(fwd_dt), int(bwd_dt), n_rows, n_cols, _p(logits), _p(labels),
                                                _p(dlogits), _p(row_loss), _p(loss_sum))
 
+    def submit_embedding(self, stream_id, fwd_dt, num_tokens, embed_dim, token_ids, embedding_table, output):
+        return _L.submit_embedding(C.byref(self.h), stream_id, int(fwd_dt), num_tokens, embed_dim, _p(token_ids), _p(embedding_table), _p(output))
+
+    def submit_copy_to_seq_context(self, stream_id, fwd_dt, N, total_tokens, kv_dim, X_k, X_v, seq_positions, seq_context_ptrs, seq_context_sizes):
+        return _L.submit_copy_to_seq_context(C.byref(self.h), stream_id, int(fwd_dt), N, total_tokens, kv_dim, _p(X_k), _p(X_v), _p(seq_positions),
+                                             _p(seq_context_ptrs), _p(seq_context_sizes))
+
+    def submit_select_experts(self, stream_id, fwd_dt, total_tokens, n_experts, top_k_experts, X_routed, token_expert_weights, chosen_experts,
+                              expert_counts, expert_counts_cumsum, num_routed_by_expert):
+        return _L.submit_select_experts(C.byref(self.h), stream_id, int(fwd_dt), total_tokens, n_experts, top_k_experts, _p(X_routed),
+                                        _p(token_expert_weights), _p(chosen_experts), _p(expert_counts), _p(expert_counts_cumsum),
+                                        _p(num_routed_by_expert))
+
     def close(self):
         if self.h.streams:
             _L.destroy_cuda_dataflow_handle(C.byref(self.h))

@@ -121,6 +121,23 @@ def softmax_cross_entropy(n_rows, n_cols, logits, labels, dlogits, row_loss=None
                                               _stream(stream)), "softmax_cross_entropy")
 
 
+def embedding(num_tokens, embed_dim, token_ids, embedding_table, output, stream=None):
+    _check(_lib_.dfb200_embedding(dt_of(embedding_table), num_tokens, embed_dim, _ptr(token_ids), _ptr(embedding_table), _ptr(output), _stream(stream)),
+           "embedding")
+
+
+def copy_to_seq_context(N, total_tokens, kv_dim, X_k, X_v, seq_positions, seq_context_ptrs, seq_context_sizes, stream=None):
+    _check(_lib_.dfb200_copy_to_seq_context(dt_of(X_k), N, total_tokens, kv_dim, _ptr(X_k), _ptr(X_v), _ptr(seq_positions), _ptr(seq_context_ptrs),
+                                            _ptr(seq_context_sizes), _stream(stream)), "copy_to_seq_context")
+
+
+def select_experts(total_tokens, n_experts, top_k_experts, X_routed, token_expert_weights, chosen_experts, expert_counts, expert_counts_cumsum,
+                   num_routed_by_expert, stream=None):
+    _check(_lib_.dfb200_select_experts(dt_of(X_routed), total_tokens, n_experts, top_k_experts, _ptr(X_routed), _ptr(token_expert_weights),
+                                       _ptr(chosen_experts), _ptr(expert_counts), _ptr(expert_counts_cumsum), _ptr(num_routed_by_expert),
+                                       _stream(stream)), "select_experts")
+
+
 def quantize_rows_e4m3(n_rows, n_cols, X, Q, row_scales, col_factors=None, stream=None):
     _check(_lib_.dfb200_quantize_rows_e4m3(n_rows, n_cols, _ptr(X), _ptr(col_factors), _ptr(Q), _ptr(row_scales), _stream(stream)), "quantize_rows_e4m3")
 

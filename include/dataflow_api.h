@@ -67,8 +67,8 @@ int init_cuda_dataflow_handle(Dataflow_Handle * dataflow_handle, ComputeType com
 void destroy_cuda_dataflow_handle(Dataflow_Handle * dataflow_handle);
 
 /* ---- op skeletons and registration ---------------------------------------------------- */
-/* Registers the 54 (op x datatype) identities of the reference's native op set, plus this
- * library's fused ops, on the handle. `native_function_code_filename` names the shared object
+/* Registers the 54 (op x datatype) identities of the reference's native op set, plus copy_to_seq_context,
+ * select_experts and this library's fused ops, on the handle. `native_function_code_filename` names the shared object
  * that exports the ops (this library; NULL = the library containing this function);
  * `native_function_config_filename` is accepted for source compatibility and ignored.
  * Returns the number of ops registered. */
@@ -85,10 +85,22 @@ void set_native_swiglu_skeleton(Op_Skeleton * skeleton, DataflowDatatype fwd_dat
 void set_native_swiglu_bwd_x_skeleton(Op_Skeleton * skeleton, DataflowDatatype fwd_datatype, DataflowDatatype bwd_datatype);
 void set_native_softmax_skeleton(Op_Skeleton * skeleton, DataflowDatatype fwd_datatype, DataflowDatatype bwd_datatype);
 void set_native_cross_entropy_loss_skeleton(Op_Skeleton * skeleton, DataflowDatatype bwd_datatype);
+/* The reference declares the select_experts kernels (src/ops/nvidia/include/nvidia_ops.h:110-114) but gives them no skeleton;
+ * this one is "select_experts_<DT>": total_tokens, n_experts, top_k, X_routed, weights, chosen (uint16), counts, cumsum, num_routed. */
+void set_native_select_experts_skeleton(Op_Skeleton * skeleton, DataflowDatatype fwd_datatype);
 /* Not in the reference: the fused softmax + cross-entropy op ("softmax_cross_entropy_<F>_<B>"). */
 void set_native_softmax_cross_entropy_skeleton(Op_Skeleton * skeleton, DataflowDatatype fwd_datatype, DataflowDatatype bwd_datatype);
 
 /* ---- op submission -------------------------------------------------------------------- */
+int submit_embedding(Dataflow_Handle * handle, int stream_id, DataflowDatatype fwd_dt,
+                     int num_tokens, int embed_dim, uint32_t * token_ids, void * embedding_table, void * output);
+int submit_copy_to_seq_context(Dataflow_Handle * handle, int stream_id, DataflowDatatype fwd_dt,
+                               uint64_t N, int total_tokens, int kv_dim,
+                               void * X_k, void * X_v, int * seq_positions, uint64_t * seq_context_ptrs, int * seq_context_sizes);
+/* No reference wrapper exists for the router; argument order is the kernel's (src/ops/nvidia/include/nvidia_ops.h:110). */
+int submit_select_experts(Dataflow_Handle * handle, int stream_id, DataflowDatatype fwd_dt,
+                          int total_tokens, int n_experts, int top_k_experts, void * X_routed, void * token_expert_weights,
+                          uint16_t * chosen_experts, int * expert_counts, int * expert_counts_cumsum, int * num_routed_by_expert);
 int submit_rms_norm(Dataflow_Handle * handle, int stream_id, DataflowDatatype fwd_dt,
                     int n_rows, int n_cols, float eps,
                     void * rms_weight, void * X, void * out, float * weighted_sums, float * rms_vals);

@@ -164,6 +164,26 @@ int dfb200_swiglu_ffn_fp8_bwd(int T, int d, int f, const void * dOut_bf16, const
                               const void * WdownT, const float * down_scales, const void * WgateupT, const float * gateup_scales,
                               void * dA_bf16, void * workspace, uint64_t workspace_bytes, void * stream);
 
+/* ---- row gather / scatter ---------------------------------------------------------------
+ * dfb200_embedding            output[t, :] = embedding_table[token_ids[t], :]
+ *   replaces embedding_<dt>_kernel (src/ops/nvidia/preprocess/embedding.cu:3-24; the intended row copy -- the
+ *   reference's offsets are scaled by the element size twice, :14-20). Any datatype of 1, 2 or 4 bytes.
+ * dfb200_copy_to_seq_context  context[t][pos[t], :] = keys[t, :]; context[t][size[t] + pos[t], :] = values[t, :]
+ *   replaces copy_to_seq_context_<dt>_kernel (src/ops/nvidia/attention/copy_to_seq_context.cu:3-20).
+ *   seq_context_ptrs holds one device address per token; N must equal total_tokens * kv_dim. */
+int dfb200_embedding(int dt, int num_tokens, int embed_dim, const uint32_t * token_ids, const void * embedding_table, void * output, void * stream);
+int dfb200_copy_to_seq_context(int dt, uint64_t N, int total_tokens, int kv_dim, const void * keys, const void * values,
+                               const int * seq_positions, const uint64_t * seq_context_ptrs, const int * seq_context_sizes, void * stream);
+
+/* ---- mixture-of-experts router --------------------------------------------------------------
+ * replaces select_experts_<dt>_kernel (src/ops/nvidia/moe/select_experts.cu:3-239): sigmoid scores, top-k by an
+ * index-order scan with strict comparisons (slot order as the reference's), weights = score / sum of the chosen
+ * scores in the tensor's datatype, uint16 expert ids, expert_counts[e] += tokens routed to e (caller zeroes;
+ * n_experts + 1 entries, the last is the kernel's block counter and is left 0), inclusive prefix sum,
+ * num_routed_by_expert zeroed. 1 <= top_k <= min(32, n_experts), n_experts <= 8192. Nothing spins. */
+int dfb200_select_experts(int dt, int total_tokens, int n_experts, int top_k_experts, const void * X_routed, void * token_expert_weights,
+                          uint16_t * chosen_experts, int * expert_counts, int * expert_counts_cumsum, int * num_routed_by_expert, void * stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -570,3 +570,107 @@ void oracle_gemm_e4m3_swiglu_bwd(int M, int N, int K, const void * dOq, const fl
                                  const void * u_saved_bf16, void * dGU_bf16, int n_threads) {
 	gemm8(M, N, K, 2, dOq, s_rows, WdownT, NULL, NULL, NULL, dGU_bf16, (void *) g_saved_bf16, (void *) u_saved_bf16, n_threads);
 }
+
+/* ------------------------------------------------------------------------------------------
+ * embedding and copy_to_seq_context: row copies
+ * ---------------------------------------------------------------------------------------- */
+
+/* src/ops/nvidia/preprocess/embedding.cu:3-24, intended semantics: output[t, :] = table[token_ids[t], :]
+ * (the reference scales its element offsets by sizeof(element) while indexing typed pointers, :14-20). */
+void oracle_embedding(int dt, int num_tokens, int embed_dim, const uint32_t * token_ids, const void * table, void * out) {
+	const size_t row = (size_t) embed_dim * (size_t) oracle_sizeof(dt);
+	for (int t = 0; t < num_tokens; t++)
+		memcpy((uint8_t *) out + (size_t) t * row, (const uint8_t *) table + (size_t) token_ids[t] * row, row);
+}
+
+/* src/ops/nvidia/attention/copy_to_seq_context.cu:3-20: token t's key row goes to row seq_positions[t] of its context,
+ * its value row to row seq_context_sizes[t] + seq_positions[t] (keys of the whole context first, then values). */
+void oracle_copy_to_seq_context(int dt, int total_tokens, int kv_dim, const void * keys, const void * values, const int * seq_positions,
+                                const uint64_t * seq_context_ptrs, const int * seq_context_sizes) {
+	const size_t row = (size_t) kv_dim * (size_t) oracle_sizeof(dt);
+	for (int t = 0; t < total_tokens; t++) {
+		uint8_t * ctx = (uint8_t *) (uintptr_t) seq_context_ptrs[t];
+		memcpy(ctx + (size_t) seq_positions[t] * row, (const uint8_t *) keys + (size_t) t * row, row);
+		memcpy(ctx + ((size_t) seq_context_sizes[t] + (size_t) seq_positions[t]) * row, (const uint8_t *) values + (size_t) t * row, row);
+	}
+}
+
+/* ------------------------------------------------------------------------------------------
+ * select_experts (src/ops/nvidia/moe/select_experts.cu:3-239)
+ * ---------------------------------------------------------------------------------------- */
+
+/* exp(x) as a fixed sequence of IEEE fp32 operations (Cody-Waite reduction, Cephes polynomial): the CUDA kernel runs
+ * the same sequence with explicit round-to-nearest intrinsics, so scores agree bit for bit. The reference's fast-math
+ * build uses the hardware approximation instead (a few ulps away). */
+static inline float det_expf(float x) {
+	x = fminf(fmaxf(x, -87.0f), 88.0f);
+	const float n = rintf(x * 1.44269504088896341f);
+	float r = fmaf(n, -0.693359375f, x);
+	r = fmaf(n, 2.12194440e-4f, r);
+	float p = 1.9875691500e-4f;
+	p = fmaf(p, r, 1.3981999507e-3f);
+	p = fmaf(p, r, 8.3334519073e-3f);
+	p = fmaf(p, r, 4.1665795894e-2f);
+	p = fmaf(p, r, 1.6666665459e-1f);
+	p = fmaf(p, r, 5.0000001201e-1f);
+	const float r2 = r * r;
+	const float e = fmaf(p, r2, r) + 1.0f;
+	return e * u2f((uint32_t) ((int) n + 127) << 23);
+}
+
+/* `1.0 / (1 + expf(-x))` (:112): fp32 add, double division, rounded to fp32 */
+static inline float sigmoid_score(float x) {
+	if (x != x) return x;
+	const float denom = 1.0f + det_expf(-x);
+	return (float) (1.0 / (double) denom);
+}
+
+float oracle_sigmoid_score(float x) { return sigmoid_score(x); }
+
+typedef struct { int dt, n_experts, top_k; const void * X; void * w; uint16_t * ids; int * counts; pthread_mutex_t * mu; } Select_Ctx;
+
+static void select_rows(long r0, long r1, void * p) {
+	Select_Ctx * c = (Select_Ctx *) p;
+	const int k = c->top_k, ne = c->n_experts;
+	float vals[64];
+	int ids[64];
+	int * local = (int *) calloc((size_t) ne, sizeof(int));
+	for (long t = r0; t < r1; t++) {
+		for (int j = 0; j < k; j++) { vals[j] = -INFINITY; ids[j] = 0xFFFF; }     /* :96-101 */
+		float min_val = -INFINITY, sum = 0.0f;
+		int min_slot = 0;
+		for (int e = 0; e < ne; e++) {
+			const float score = sigmoid_score(ld(c->dt, c->X, (size_t) t * ne + e));
+			if (score > min_val) {                                               /* :128, strict */
+				if (vals[min_slot] != -INFINITY) sum -= vals[min_slot];          /* :130-132 */
+				vals[min_slot] = score; ids[min_slot] = e;
+				sum += score;                                                    /* :137 */
+				min_val = INFINITY;                                              /* :141-147: first slot holding the minimum */
+				for (int j = 0; j < k; j++)
+					if (vals[j] < min_val) { min_val = vals[j]; min_slot = j; }
+			}
+		}
+		for (int j = 0; j < k; j++) {                                            /* :158-172 */
+			st(c->dt, c->w, (size_t) t * k + j, vals[j] / sum);
+			c->ids[(size_t) t * k + j] = (uint16_t) ids[j];
+			if (ids[j] < ne) local[ids[j]]++;
+		}
+	}
+	pthread_mutex_lock(c->mu);
+	for (int e = 0; e < ne; e++) c->counts[e] += local[e];
+	pthread_mutex_unlock(c->mu);
+	free(local);
+}
+
+/* expert_counts has n_experts + 1 entries and is ACCUMULATED into (the reference adds with atomicAdd, :185); entry
+ * n_experts (the kernel's block counter) is left at 0. cumsum = inclusive prefix sum; num_routed_by_expert zeroed (:226-236). */
+void oracle_select_experts(int dt, int total_tokens, int n_experts, int top_k, const void * X_routed, void * token_expert_weights,
+                           uint16_t * chosen_experts, int * expert_counts, int * expert_counts_cumsum, int * num_routed_by_expert, int n_threads) {
+	if (top_k > 64) return;
+	pthread_mutex_t mu = PTHREAD_MUTEX_INITIALIZER;
+	Select_Ctx c = {dt, n_experts, top_k, X_routed, token_expert_weights, chosen_experts, expert_counts, &mu};
+	for_rows(total_tokens, n_threads, select_rows, &c);
+	int run = 0;
+	for (int e = 0; e < n_experts; e++) { run += expert_counts[e]; expert_counts_cumsum[e] = run; num_routed_by_expert[e] = 0; }
+	expert_counts[n_experts] = 0;
+}

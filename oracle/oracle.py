@@ -41,6 +41,10 @@ _sig = {
     "oracle_gemm_e4m3": (None, [_i, _i, _i, _vp, _vp, _vp, _vp, _vp, _i]),
     "oracle_gemm_e4m3_swiglu": (None, [_i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i]),
     "oracle_gemm_e4m3_swiglu_bwd": (None, [_i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i]),
+    "oracle_embedding": (None, [_i, _i, _i, _vp, _vp, _vp]),
+    "oracle_copy_to_seq_context": (None, [_i, _i, _i, _vp, _vp, _vp, _vp, _vp]),
+    "oracle_select_experts": (None, [_i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i]),
+    "oracle_sigmoid_score": (_f, [_f]),
     "oracle_fill_normal": (None, [_i, _vp, _l, _l, _u64, _f, _f, _i]),
     "oracle_fill_labels": (None, [_vp, _l, _u64, C.c_uint32]),
 }
@@ -211,3 +215,34 @@ def swiglu_ffn_fp8_bwd(dOut_bf16, g, u, Wg, sg, Wu, su, Wd, sd, threads=None):
     dGU = gemm_e4m3_swiglu_bwd(dOq, s1, WdT, g, u, threads)
     dGUq, s2 = quantize_rows_e4m3(dGU, np.concatenate([sg, su]), threads)
     return gemm_e4m3(dGUq, s2, WguT, None, threads)
+
+
+def embedding(dt, token_ids, table):
+    out = np.empty((len(token_ids), table.shape[1]), table.dtype)
+    _lib.oracle_embedding(dt, len(token_ids), table.shape[1], _p(np.ascontiguousarray(token_ids, np.uint32)), _p(table), _p(out))
+    return out
+
+
+def copy_to_seq_context(dt, keys, values, seq_positions, contexts, token_context, context_sizes):
+    """contexts: list of writable arrays [2 * size, kv_dim] (keys then values); token_context[t] = index of token t's context.
+    Updates the arrays in place."""
+    ptrs = np.array([contexts[c].ctypes.data for c in token_context], np.uint64)
+    sizes = np.array([context_sizes[c] for c in token_context], np.int32)
+    _lib.oracle_copy_to_seq_context(dt, keys.shape[0], keys.shape[1], _p(keys), _p(values), _p(np.ascontiguousarray(seq_positions, np.int32)),
+                                    _p(ptrs), _p(sizes))
+
+
+def select_experts(dt, X_routed, top_k, counts_in=None, threads=None):
+    """Returns (weights [T, k] in dt, chosen uint16 [T, k], counts int32 [n_experts + 1], cumsum int32 [n_experts], num_routed int32 [n_experts])."""
+    T, ne = X_routed.shape
+    w = np.empty((T, top_k), NP_OF[dt])
+    ids = np.empty((T, top_k), np.uint16)
+    counts = np.zeros(ne + 1, np.int32) if counts_in is None else np.ascontiguousarray(counts_in, np.int32).copy()
+    cumsum = np.empty(ne, np.int32)
+    routed = np.full(ne, -1, np.int32)
+    _lib.oracle_select_experts(dt, T, ne, top_k, _p(X_routed), _p(w), _p(ids), _p(counts), _p(cumsum), _p(routed), threads or N_THREADS)
+    return w, ids, counts, cumsum, routed
+
+
+def sigmoid_score(x):
+    return float(_lib.oracle_sigmoid_score(float(x)))

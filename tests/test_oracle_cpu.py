@@ -149,3 +149,52 @@ def test_oracle_edge_cases():
     # fill is a pure function of (seed, index): a slice equals the slice of the whole
     whole = O.fill_normal(O.BF16, (8, 16), 5)
     assert np.array_equal(O.fill_normal(O.BF16, (4, 16), 5), whole[:4])
+
+
+# ---- router, embedding, sequence context ------------------------------------------------------------------------
+
+def test_sigmoid_score_is_accurate():
+    for x in [-100.0, -88.5, -20.0, -1.0, -1e-3, 0.0, 1e-3, 0.5, 3.0, 17.0, 87.5, 100.0]:
+        want = 1.0 / (1.0 + np.exp(-np.float64(x)))
+        got = O.sigmoid_score(x)
+        assert abs(got - want) <= 4e-7 * max(want, 1e-30) + 1e-38, (x, got, want)
+    assert np.isnan(O.sigmoid_score(float("nan")))
+
+
+def test_select_experts_slot_order_and_ties():
+    """Hand-traced cases of the reference's scan (src/ops/nvidia/moe/select_experts.cu:124-153)."""
+    X = np.array([[1, 3, 2, 0], [1, 1, 1, 1], [0, 1, 2, 3], [3, 2, 1, 0]], np.float32)
+    w, ids, counts, cumsum, routed = O.select_experts(O.FP32, X, 2, threads=1)
+    # row 0: e0 -> slot 0, e1 -> slot 1, e2 (2 > 1) evicts slot 0, e3 loses
+    # row 1: ties never replace (strict >): the first two experts stay
+    # row 2: e2 evicts e0 from slot 0, then e3 evicts e1 from slot 1;  row 3: nothing after the first two wins
+    assert ids.tolist() == [[2, 1], [0, 1], [2, 3], [0, 1]]
+    s = lambda v: 1.0 / (1.0 + np.exp(-np.float64(v)))
+    assert np.allclose(w[0], [s(2) / (s(2) + s(3)), s(3) / (s(2) + s(3))], rtol=1e-6)
+    assert np.allclose(w.sum(1), 1.0, rtol=1e-6)
+    assert counts.tolist() == [2, 3, 2, 1, 0] and cumsum.tolist() == [2, 5, 7, 8] and not routed.any()
+
+
+def test_select_experts_matches_a_sort_when_there_are_no_ties():
+    T, ne, k = 200, 64, 8
+    X = O.fill_normal(O.FP32, (T, ne), 3)
+    w, ids, counts, cumsum, _ = O.select_experts(O.FP32, X, k)
+    want = np.argsort(-X, axis=1, kind="stable")[:, :k]
+    assert np.array_equal(np.sort(ids.astype(np.int64), axis=1), np.sort(want, axis=1))
+    sc = 1.0 / (1.0 + np.exp(-X.astype(np.float64)))
+    picked = np.take_along_axis(sc, ids.astype(np.int64), axis=1)
+    assert np.allclose(w, picked / picked.sum(1, keepdims=True), rtol=2e-6)
+    assert np.array_equal(counts[:ne], np.bincount(ids.ravel(), minlength=ne)) and np.array_equal(cumsum, np.cumsum(counts[:ne]))
+
+
+def test_embedding_and_seq_context_oracle():
+    table = O.fill_normal(O.BF16, (50, 24), 1)
+    ids = np.array([3, 49, 0, 3], np.uint32)
+    assert np.array_equal(O.embedding(O.BF16, ids, table), table[ids])
+    keys, values = O.fill_normal(O.BF16, (3, 8), 2), O.fill_normal(O.BF16, (3, 8), 3)
+    ctx = [np.zeros((2 * 4, 8), np.uint16), np.zeros((2 * 2, 8), np.uint16)]
+    O.copy_to_seq_context(O.BF16, keys, values, [1, 0, 3], ctx, [0, 1, 0], [4, 2])
+    assert np.array_equal(ctx[0][1], keys[0]) and np.array_equal(ctx[0][4 + 1], values[0])
+    assert np.array_equal(ctx[1][0], keys[1]) and np.array_equal(ctx[1][2 + 0], values[1])
+    assert np.array_equal(ctx[0][3], keys[2]) and np.array_equal(ctx[0][4 + 3], values[2])
+    assert not ctx[0][[0, 2, 4, 6]].any()
