@@ -43,6 +43,7 @@ KERNEL_ABI = {
     "dfb200_swiglu_ffn_fp8": (_i, [_i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _u64, _vp]),
     "dfb200_ffn_fp8_prepare_bwd_weights": (_i, [_i, _i, _vp, _vp, _vp, _vp, _vp, _vp]),
     "dfb200_swiglu_ffn_fp8_bwd": (_i, [_i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _u64, _vp]),
+    "dfb200_softmax_fp32_out": (_i, [_i, _i, _i, _vp, _vp, _vp, _vp]),
     "dfb200_embedding": (_i, [_i, _i, _i, _vp, _vp, _vp, _vp]),
     "dfb200_copy_to_seq_context": (_i, [_i, _u64, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp]),
     "dfb200_select_experts": (_i, [_i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
@@ -93,6 +94,8 @@ HOST_ABI = {
     "set_native_cross_entropy_loss_skeleton": (None, [_SK, _i]),
     "set_native_softmax_cross_entropy_skeleton": (None, [_SK, _i, _i]),
     "set_native_select_experts_skeleton": (None, [_SK, _i]),
+    "set_native_softmax_argmax_skeleton": (None, [_SK, _i]),
+    "submit_softmax_argmax": (_i, [_H, _i, _i, _i, _i, _vp, _vp, _vp]),
     "submit_embedding": (_i, [_H, _i, _i, _i, _i, _vp, _vp, _vp]),
     "submit_copy_to_seq_context": (_i, [_H, _i, _i, _u64, _i, _i, _vp, _vp, _vp, _vp, _vp]),
     "submit_select_experts": (_i, [_H, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp]),
@@ -121,6 +124,7 @@ HOST_ABI = {
     "dataflow_b200_embedding": (_i, [_H, _i, _vp, _vp]),
     "dataflow_b200_copy_to_seq_context": (_i, [_H, _i, _vp, _vp]),
     "dataflow_b200_select_experts": (_i, [_H, _i, _vp, _vp]),
+    "dataflow_b200_softmax_argmax": (_i, [_H, _i, _vp, _vp]),
 }
 
 for _table in (KERNEL_ABI, HOST_ABI):

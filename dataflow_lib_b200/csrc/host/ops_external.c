@@ -139,3 +139,9 @@ int dataflow_b200_select_experts(Dataflow_Handle * h, int stream_id, Op * op, vo
 	                                    ARG(op, 5, uint16_t *), ARG(op, 6, int *), ARG(op, 7, int *), ARG(op, 8, int *), stream_of(h, stream_id)),
 	              "select_experts");
 }
+
+int dataflow_b200_softmax_argmax(Dataflow_Handle * h, int stream_id, Op * op, void * op_extra) {
+	(void) op_extra;
+	return finish(dfb200_softmax_fp32_out(DT(op, 2), ARG(op, 0, int), ARG(op, 1, int), ARG(op, 2, void *), ARG(op, 3, float *), ARG(op, 4, uint32_t *),
+	                                      stream_of(h, stream_id)), "softmax_argmax");
+}

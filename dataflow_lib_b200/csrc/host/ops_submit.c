@@ -125,3 +125,11 @@ int submit_select_experts(Dataflow_Handle * handle, int stream_id, DataflowDatat
 	     &num_routed_by_expert);
 	return submit(handle, &op, stream_id, "select experts");
 }
+
+int submit_softmax_argmax(Dataflow_Handle * handle, int stream_id, DataflowDatatype fwd_dt, int n_rows, int n_cols, void * X, float * out,
+                          uint32_t * arg_maxs) {
+	Op op;
+	set_native_softmax_argmax_skeleton(&op.op_skeleton, fwd_dt);
+	ARGS(op, &n_rows, &n_cols, &X, &out, &arg_maxs);
+	return submit(handle, &op, stream_id, "softmax argmax");
+}

@@ -95,6 +95,10 @@ void set_native_cross_entropy_loss_skeleton(Op_Skeleton * skeleton, DataflowData
 	char nick[MAX_OP_NICKNAME_SIZE];   /* n_rows, n_cols, pred_logits, labels */
 	build_skeleton(skeleton, nick1(nick, "cross_entropy_loss", bwd), I_S, I_S, bwd, DATAFLOW_UINT32, END);
 }
+void set_native_softmax_argmax_skeleton(Op_Skeleton * skeleton, DataflowDatatype fwd) {
+	char nick[MAX_OP_NICKNAME_SIZE];   /* n_rows, n_cols, X, out, arg_maxs */
+	build_skeleton(skeleton, nick2(nick, "softmax_argmax", fwd, DATAFLOW_FP32), I_S, I_S, fwd, DATAFLOW_FP32, DATAFLOW_UINT32, END);
+}
 void set_native_select_experts_skeleton(Op_Skeleton * skeleton, DataflowDatatype fwd) {
 	char nick[MAX_OP_NICKNAME_SIZE];   /* total_tokens, n_experts, top_k, X_routed, weights, chosen_experts, counts, cumsum, num_routed */
 	build_skeleton(skeleton, nick1(nick, "select_experts", fwd), I_S, I_S, I_S, fwd, fwd, DATAFLOW_UINT16, DATAFLOW_INT, DATAFLOW_INT, DATAFLOW_INT, END);
@@ -118,6 +122,7 @@ int set_native_op_skeleton(Op_Skeleton * skeleton, char * op_name, DataflowDatat
 	else if (!strcmp(op_name, "cross_entropy_loss")) set_native_cross_entropy_loss_skeleton(skeleton, bwd_dt);
 	else if (!strcmp(op_name, "softmax_cross_entropy")) set_native_softmax_cross_entropy_skeleton(skeleton, fwd_dt, bwd_dt);
 	else if (!strcmp(op_name, "select_experts")) set_native_select_experts_skeleton(skeleton, fwd_dt);
+	else if (!strcmp(op_name, "softmax_argmax")) set_native_softmax_argmax_skeleton(skeleton, fwd_dt);
 	else {
 		printf("Cannot set skeleton, unknown op: %s, with fwd_dt: %s, bwd_dt: %s\n", op_name,
 		       dataflow_datatype_as_string(fwd_dt), dataflow_datatype_as_string(bwd_dt));
@@ -128,7 +133,7 @@ int set_native_op_skeleton(Op_Skeleton * skeleton, char * op_name, DataflowDatat
 
 /* ---- registration ---------------------------------------------------------------------- */
 
-typedef enum { KEY_FWD, KEY_BWD, KEY_PAIR } Key_Kind;
+typedef enum { KEY_FWD, KEY_BWD, KEY_PAIR, KEY_HALF } Key_Kind;   /* KEY_HALF: fp16 and bf16 inputs only */
 
 typedef struct {
 	const char * op;          /* skeleton family == exported symbol "dataflow_b200_<op>" */
@@ -139,7 +144,7 @@ typedef struct {
 /* The reference registers 54 identities (set_native_op_skeletons.c:13-39): all of them are here. Added: the 5
  * copy_to_seq_context identities (the reference has the skeleton, the wrapper and the kernels but leaves them out of
  * its registration list), 5 select_experts identities (kernels only in the reference) and the 7 datatype pairs of
- * the fused softmax+cross-entropy op: 71 in total. */
+ * the fused softmax+cross-entropy op, and 2 softmax_argmax identities (fp16 / bf16 -> fp32): 73 in total. */
 static const Op_Family FAMILIES[] = {
 	{"embedding", KEY_FWD, false},      {"copy_to_seq_context", KEY_FWD, false}, {"select_experts", KEY_FWD, false},
 	{"rms_norm", KEY_FWD, false},       {"rms_norm_bwd_x", KEY_PAIR, false}, {"rms_norm_bwd_w", KEY_PAIR, true},
@@ -147,6 +152,7 @@ static const Op_Family FAMILIES[] = {
 	{"swiglu", KEY_FWD, false},         {"swiglu_bwd_x", KEY_PAIR, false},
 	{"softmax", KEY_PAIR, false},       {"cross_entropy_loss", KEY_BWD, false},
 	{"softmax_cross_entropy", KEY_PAIR, true},
+	{"softmax_argmax", KEY_HALF, false},
 };
 
 static const DataflowDatatype FWD_DTS[5] = {DATAFLOW_FP32, DATAFLOW_FP16, DATAFLOW_BF16, DATAFLOW_FP8E4M3, DATAFLOW_FP8E5M2};
@@ -182,9 +188,9 @@ int register_native_ops(Dataflow_Handle * dataflow_handle, char * native_functio
 	int n = 0;
 	for (size_t f = 0; f < sizeof(FAMILIES) / sizeof(FAMILIES[0]); f++) {
 		const Op_Family * fam = &FAMILIES[f];
-		const int variants = fam->kind == KEY_FWD ? 5 : fam->kind == KEY_BWD ? 3 : 7;
+		const int variants = fam->kind == KEY_FWD ? 5 : fam->kind == KEY_BWD ? 3 : fam->kind == KEY_HALF ? 2 : 7;
 		for (int v = 0; v < variants && n < MAX_REGISTERED; v++, n++) {
-			const DataflowDatatype fwd = fam->kind == KEY_FWD ? FWD_DTS[v] : fam->kind == KEY_PAIR ? PAIR_FWD[v] : DATAFLOW_NONE;
+			const DataflowDatatype fwd = fam->kind == KEY_FWD ? FWD_DTS[v] : fam->kind == KEY_PAIR ? PAIR_FWD[v] : fam->kind == KEY_HALF ? FWD_DTS[1 + v] : DATAFLOW_NONE;
 			const DataflowDatatype bwd = fam->kind == KEY_BWD ? BWD_DTS[v] : fam->kind == KEY_PAIR ? PAIR_BWD[v] : DATAFLOW_NONE;
 			set_native_op_skeleton(&skeletons[n], (char *) fam->op, fwd, bwd);
 			symbols[n] = (char *) malloc(FUNC_SYMBOL_MAX_LEN);

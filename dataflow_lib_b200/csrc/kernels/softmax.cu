@@ -112,10 +112,15 @@ template <> struct RowMath<f16_t, f16_t> {
 	}
 };
 
-template <typename F, typename B, int CPT, bool FUSE_CE>
+// OUT = the type the probabilities are stored in: B for the registered ops; f32_t (with B = F) for the reference's
+// softmax_<f16|bf16>_fp32 kernels (src/ops/nvidia/loss/softmax.cu:965-1249), which keep their scratch in the input type and
+// store exp(..) / total unrounded. ARGMAX additionally writes the smallest index holding the row maximum to arg_maxs[row]
+// (the reference lets whichever thread sees the maximum last win, :1057-1059).
+template <typename F, typename B, int CPT, bool FUSE_CE, typename OUT = B, bool ARGMAX = false>
 __global__ void __launch_bounds__(SOFTMAX_MAX_THREADS)
 softmax_rows_kernel(int n_rows, int n_cols, int slice_chunks, const void * __restrict__ X, void * __restrict__ out,
-                    const uint32_t * __restrict__ labels, float * __restrict__ row_loss) {
+                    const uint32_t * __restrict__ labels, float * __restrict__ row_loss, uint32_t * __restrict__ arg_maxs = nullptr) {
+	static_assert(!FUSE_CE || sizeof(OUT) == sizeof(B), "the fused cross-entropy step works in the output type");
 	constexpr int FW = E / Word<F>::EPW;
 	__shared__ float s_warp_max[32];
 	__shared__ float s_warp_part[16][8];
@@ -155,6 +160,9 @@ softmax_rows_kernel(int n_rows, int n_cols, int slice_chunks, const void * __res
 	}
 	float m = warp_max(Math::max_value(macc));
 	if (lane == 0) s_warp_max[warp] = m;
+	if constexpr (ARGMAX) {
+		if (crank == 0 && tid == 0) arg_maxs[row] = 0xffffffffu;   // ordered before the atomicMin below by the barriers of this phase
+	}
 	__syncthreads();
 	if (warp == 0) {
 		float v = lane < n_warps ? s_warp_max[lane] : -CUDART_INF_F;
@@ -174,6 +182,21 @@ softmax_rows_kernel(int n_rows, int n_cols, int slice_chunks, const void * __res
 	__syncthreads();
 	const float row_max = s_row[0];
 	const typename Math::Shift shift = Math::shift_of(row_max);
+	if constexpr (ARGMAX) {
+		uint32_t first = 0xffffffffu;
+		#pragma unroll
+		for (int k = CPT - 1; k >= 0; k--) {
+			const int c = c_begin + tid + k * nthr;
+			if (c < c_end) {
+				float x[E];
+				#pragma unroll
+				for (int i = 0; i < FW; i++) Word<F>::unpack(raw[k][i], &x[i * Word<F>::EPW]);
+				#pragma unroll
+				for (int i = E - 1; i >= 0; i--) if (x[i] == row_max) first = (uint32_t) (c * E + i);
+			}
+		}
+		if (first != 0xffffffffu) atomicMin(arg_maxs + row, first);
+	}
 
 	// ---- phase 2: 32 interleaved partial sums of exp(W(x - max))
 	float part4[4] = {0.0f, 0.0f, 0.0f, 0.0f};            // four independent chains: the adds are not the critical path
@@ -232,7 +255,7 @@ softmax_rows_kernel(int n_rows, int n_cols, int slice_chunks, const void * __res
 			Math::shifted(shift, raw[k], d);
 			#pragma unroll
 			for (int i = 0; i < E; i++) o[i] = fast_exp(d[i]) * inv_total;
-			store_elems<B, E>(out, row_elem + (uint64_t) c * E, o);
+			store_elems<OUT, E>(out, row_elem + (uint64_t) c * E, o);
 			if constexpr (FUSE_CE) owns_label |= (label / E == (uint32_t) c);
 		}
 	}
@@ -340,14 +363,43 @@ static int launch_softmax_rows(const SoftmaxGeometry & g, int n_rows, int n_cols
 	attr[0].id = cudaLaunchAttributeClusterDimension;
 	attr[0].val.clusterDim.x = g.cluster; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
 	cfg.attrs = attr; cfg.numAttrs = 1;
+	uint32_t * no_argmax = nullptr;
 	cudaError_t e;
 	switch (g.cpt) {
-		case 1:  e = cudaLaunchKernelEx(&cfg, softmax_rows_kernel<F, B, 1, FUSE_CE>, n_rows, n_cols, g.slice_chunks, X, out, labels, row_loss); break;
-		case 2:  e = cudaLaunchKernelEx(&cfg, softmax_rows_kernel<F, B, 2, FUSE_CE>, n_rows, n_cols, g.slice_chunks, X, out, labels, row_loss); break;
-		case 4:  e = cudaLaunchKernelEx(&cfg, softmax_rows_kernel<F, B, 4, FUSE_CE>, n_rows, n_cols, g.slice_chunks, X, out, labels, row_loss); break;
-		default: e = cudaLaunchKernelEx(&cfg, softmax_rows_kernel<F, B, 8, FUSE_CE>, n_rows, n_cols, g.slice_chunks, X, out, labels, row_loss); break;
+		case 1:  e = cudaLaunchKernelEx(&cfg, softmax_rows_kernel<F, B, 1, FUSE_CE>, n_rows, n_cols, g.slice_chunks, X, out, labels, row_loss, no_argmax); break;
+		case 2:  e = cudaLaunchKernelEx(&cfg, softmax_rows_kernel<F, B, 2, FUSE_CE>, n_rows, n_cols, g.slice_chunks, X, out, labels, row_loss, no_argmax); break;
+		case 4:  e = cudaLaunchKernelEx(&cfg, softmax_rows_kernel<F, B, 4, FUSE_CE>, n_rows, n_cols, g.slice_chunks, X, out, labels, row_loss, no_argmax); break;
+		default: e = cudaLaunchKernelEx(&cfg, softmax_rows_kernel<F, B, 8, FUSE_CE>, n_rows, n_cols, g.slice_chunks, X, out, labels, row_loss, no_argmax); break;
 	}
 	if (e != cudaSuccess) { cudaGetLastError(); return set_error(DFB200_ERR_CUDA, "softmax launch: %s", cudaGetErrorString(e)); }
+	return DFB200_OK;
+}
+
+template <typename F>
+static int launch_softmax_fp32_out(const SoftmaxGeometry & g, int n_rows, int n_cols, const void * X, float * out, uint32_t * arg_maxs, cudaStream_t stream) {
+	cudaLaunchConfig_t cfg = {};
+	cfg.gridDim = dim3((unsigned) n_rows * g.cluster, 1, 1);
+	cfg.blockDim = dim3(g.threads, 1, 1);
+	cfg.stream = stream;
+	cudaLaunchAttribute attr[1];
+	attr[0].id = cudaLaunchAttributeClusterDimension;
+	attr[0].val.clusterDim.x = g.cluster; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+	cfg.attrs = attr; cfg.numAttrs = 1;
+	const uint32_t * no_labels = nullptr;
+	float * no_loss = nullptr;
+	void * o = out;
+	cudaError_t e;
+#define DFB200_SOFTMAX_F32_CASE(CPT_) \
+	(arg_maxs ? cudaLaunchKernelEx(&cfg, softmax_rows_kernel<F, F, CPT_, false, f32_t, true>, n_rows, n_cols, g.slice_chunks, X, o, no_labels, no_loss, arg_maxs) \
+	          : cudaLaunchKernelEx(&cfg, softmax_rows_kernel<F, F, CPT_, false, f32_t, false>, n_rows, n_cols, g.slice_chunks, X, o, no_labels, no_loss, arg_maxs))
+	switch (g.cpt) {
+		case 1:  e = DFB200_SOFTMAX_F32_CASE(1); break;
+		case 2:  e = DFB200_SOFTMAX_F32_CASE(2); break;
+		case 4:  e = DFB200_SOFTMAX_F32_CASE(4); break;
+		default: e = DFB200_SOFTMAX_F32_CASE(8); break;
+	}
+#undef DFB200_SOFTMAX_F32_CASE
+	if (e != cudaSuccess) { cudaGetLastError(); return set_error(DFB200_ERR_CUDA, "softmax (fp32 out) launch: %s", cudaGetErrorString(e)); }
 	return DFB200_OK;
 }
 
@@ -376,6 +428,17 @@ extern "C" int dfb200_softmax(int fwd_dt, int bwd_dt, int n_rows, int n_cols, co
 	DFB200_DISPATCH_PAIR(fwd_dt, bwd_dt, F, B,
 		rc = (launch_softmax_rows<F, B, false>(g, n_rows, n_cols, X, out, nullptr, nullptr, (cudaStream_t) stream)));
 	return rc;
+}
+
+extern "C" int dfb200_softmax_fp32_out(int fwd_dt, int n_rows, int n_cols, const void * X, float * out, uint32_t * arg_maxs, void * stream) {
+	if (fwd_dt != DATAFLOW_FP16 && fwd_dt != DATAFLOW_BF16)
+		return set_error(DFB200_ERR_DTYPE, "softmax_fp32_out: input must be fp16 or bf16 (got %d)", fwd_dt);
+	SoftmaxGeometry g;
+	int rc = check_softmax("softmax_fp32_out", fwd_dt, fwd_dt, n_rows, n_cols, X, out, &g);
+	if (rc || n_rows == 0) return rc;
+	if (arg_maxs && (reinterpret_cast<uintptr_t>(arg_maxs) & 3u)) return set_error(DFB200_ERR_ARG, "softmax_fp32_out: arg_maxs must be 4-byte aligned");
+	return fwd_dt == DATAFLOW_FP16 ? launch_softmax_fp32_out<f16_t>(g, n_rows, n_cols, X, out, arg_maxs, (cudaStream_t) stream)
+	                               : launch_softmax_fp32_out<bf16_t>(g, n_rows, n_cols, X, out, arg_maxs, (cudaStream_t) stream);
 }
 
 extern "C" int dfb200_cross_entropy_loss(int bwd_dt, int n_rows, int n_cols, void * pred_logits, const uint32_t * labels, void * stream) {

@@ -112,6 +112,9 @@ class DataflowHandle:
                                         _p(token_expert_weights), _p(chosen_experts), _p(expert_counts), _p(expert_counts_cumsum),
                                         _p(num_routed_by_expert))
 
+    def submit_softmax_argmax(self, stream_id, fwd_dt, n_rows, n_cols, X, out, arg_maxs=None):
+        return _L.submit_softmax_argmax(C.byref(self.h), stream_id, int(fwd_dt), n_rows, n_cols, _p(X), _p(out), _p(arg_maxs))
+
     def close(self):
         if self.h.streams:
             _L.destroy_cuda_dataflow_handle(C.byref(self.h))

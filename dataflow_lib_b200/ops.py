@@ -108,6 +108,10 @@ def softmax(n_rows, n_cols, X, out, stream=None):
     _check(_lib_.dfb200_softmax(dt_of(X), dt_of(out), n_rows, n_cols, _ptr(X), _ptr(out), _stream(stream)), "softmax")
 
 
+def softmax_fp32_out(n_rows, n_cols, X, out, arg_maxs=None, stream=None):
+    _check(_lib_.dfb200_softmax_fp32_out(dt_of(X), n_rows, n_cols, _ptr(X), _ptr(out), _ptr(arg_maxs), _stream(stream)), "softmax_fp32_out")
+
+
 def cross_entropy_loss(n_rows, n_cols, pred_logits, labels, stream=None):
     _check(_lib_.dfb200_cross_entropy_loss(dt_of(pred_logits), n_rows, n_cols, _ptr(pred_logits), _ptr(labels), _stream(stream)),
            "cross_entropy_loss")

@@ -88,6 +88,9 @@ void set_native_cross_entropy_loss_skeleton(Op_Skeleton * skeleton, DataflowData
 /* The reference declares the select_experts kernels (src/ops/nvidia/include/nvidia_ops.h:110-114) but gives them no skeleton;
  * this one is "select_experts_<DT>": total_tokens, n_experts, top_k, X_routed, weights, chosen (uint16), counts, cumsum, num_routed. */
 void set_native_select_experts_skeleton(Op_Skeleton * skeleton, DataflowDatatype fwd_datatype);
+/* The reference's softmax_fp16_fp32 / softmax_bf16_fp32 kernels (fp32 probabilities + arg-max; src/ops/nvidia/loss/softmax.cu:965-1249)
+ * have no skeleton either; this one is "softmax_argmax_<F>_FP32": n_rows, n_cols, X, out (fp32), arg_maxs (uint32). */
+void set_native_softmax_argmax_skeleton(Op_Skeleton * skeleton, DataflowDatatype fwd_datatype);
 /* Not in the reference: the fused softmax + cross-entropy op ("softmax_cross_entropy_<F>_<B>"). */
 void set_native_softmax_cross_entropy_skeleton(Op_Skeleton * skeleton, DataflowDatatype fwd_datatype, DataflowDatatype bwd_datatype);
 
@@ -126,6 +129,8 @@ int submit_softmax(Dataflow_Handle * handle, int stream_id, DataflowDatatype fwd
                    int n_rows, int n_cols, void * X, void * out);
 int submit_cross_entropy_loss(Dataflow_Handle * handle, int stream_id, DataflowDatatype bwd_dt,
                               int n_rows, int n_cols, void * pred_logits, uint32_t * labels);
+int submit_softmax_argmax(Dataflow_Handle * handle, int stream_id, DataflowDatatype fwd_dt,
+                          int n_rows, int n_cols, void * X, float * out, uint32_t * arg_maxs);
 /* Not in the reference: one pass producing dlogits = softmax - onehot, per-row losses and
  * {loss sum, valid-row count} (row_loss and loss_sum are optional device pointers). */
 int submit_softmax_cross_entropy(Dataflow_Handle * handle, int stream_id, DataflowDatatype fwd_dt, DataflowDatatype bwd_dt,

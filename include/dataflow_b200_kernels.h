@@ -164,6 +164,11 @@ int dfb200_swiglu_ffn_fp8_bwd(int T, int d, int f, const void * dOut_bf16, const
                               const void * WdownT, const float * down_scales, const void * WgateupT, const float * gateup_scales,
                               void * dA_bf16, void * workspace, uint64_t workspace_bytes, void * stream);
 
+/* Softmax of fp16 / bf16 rows into fp32 probabilities plus the index of each row's maximum: replaces softmax_fp16_fp32_kernel and
+ * softmax_bf16_fp32_kernel (src/ops/nvidia/loss/softmax.cu:965-1249). Scratch roundings are in the input type as in the reference,
+ * the probabilities are stored unrounded; arg_maxs (optional, uint32 [n_rows]) gets the SMALLEST index holding the maximum. */
+int dfb200_softmax_fp32_out(int fwd_dt, int n_rows, int n_cols, const void * X, float * out, uint32_t * arg_maxs, void * stream);
+
 /* ---- row gather / scatter ---------------------------------------------------------------
  * dfb200_embedding            output[t, :] = embedding_table[token_ids[t], :]
  *   replaces embedding_<dt>_kernel (src/ops/nvidia/preprocess/embedding.cu:3-24; the intended row copy -- the

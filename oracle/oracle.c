@@ -387,7 +387,7 @@ void oracle_swiglu_bwd_x(int fwd_dt, int bwd_dt, int n_rows, int n_cols, const v
  *   row_loss[r] = logf(total) - f32(W(x_label - max))   (no reference implementation exists)
  * ---------------------------------------------------------------------------------------- */
 
-typedef struct { int fdt, bdt, n_cols; const void * X; void * out; const uint32_t * labels; float * row_loss; } Softmax;
+typedef struct { int fdt, bdt, n_cols; const void * X; void * out; const uint32_t * labels; float * row_loss; int odt; uint32_t * arg_maxs; } Softmax;
 
 static void softmax_rows(long r0, long r1, void * p) {
 	Softmax * a = (Softmax *) p;
@@ -412,7 +412,12 @@ static void softmax_rows(long r0, long r1, void * p) {
 		}
 		const float total = rnd(W, tree32(warp_sums));
 		for (int i = 0; i < n; i++)
-			st(W, a->out, base + i, expf(rnd_d(W, (double) ld(a->fdt, a->X, base + i) - (double) mx)) / total);
+			st(a->odt, a->out, base + i, expf(rnd_d(W, (double) ld(a->fdt, a->X, base + i) - (double) mx)) / total);
+		if (a->arg_maxs) {                 /* the smallest index holding the maximum (the reference lets any such index win, :1057-1059) */
+			uint32_t arg = 0xffffffffu;
+			for (int i = n - 1; i >= 0; i--) if (ld(a->fdt, a->X, base + i) == mx) arg = (uint32_t) i;
+			a->arg_maxs[r] = arg;
+		}
 		if (a->labels) {
 			const uint32_t lab = a->labels[r];
 			if (lab < (uint32_t) n) {
@@ -424,7 +429,15 @@ static void softmax_rows(long r0, long r1, void * p) {
 }
 
 void oracle_softmax(int fwd_dt, int bwd_dt, int n_rows, int n_cols, const void * X, void * out, int n_threads) {
-	Softmax a = {fwd_dt, bwd_dt, n_cols, X, out, NULL, NULL};
+	Softmax a = {fwd_dt, bwd_dt, n_cols, X, out, NULL, NULL, bwd_dt, NULL};
+	for_rows(n_rows, n_threads, softmax_rows, &a);
+}
+
+/* softmax_fp16_fp32_kernel / softmax_bf16_fp32_kernel (loss/softmax.cu:965-1249): the same three passes with the scratch
+ * (x - max, warp sums, total) held in the INPUT type, the probabilities stored unrounded in fp32, and the index of the
+ * row maximum written to arg_maxs (optional). */
+void oracle_softmax_fp32_out(int fwd_dt, int n_rows, int n_cols, const void * X, float * out, uint32_t * arg_maxs, int n_threads) {
+	Softmax a = {fwd_dt, fwd_dt, n_cols, X, out, NULL, NULL, DT_FP32, arg_maxs};
 	for_rows(n_rows, n_threads, softmax_rows, &a);
 }
 
@@ -441,7 +454,7 @@ void oracle_cross_entropy_loss(int bwd_dt, int n_rows, int n_cols, void * pred, 
 void oracle_softmax_cross_entropy(int fwd_dt, int bwd_dt, int n_rows, int n_cols, const void * logits, const uint32_t * labels,
                                   void * dlogits, float * row_loss, float * loss_sum, int n_threads) {
 	float * losses = row_loss ? row_loss : (float *) malloc(sizeof(float) * (size_t) (n_rows > 0 ? n_rows : 1));
-	Softmax a = {fwd_dt, bwd_dt, n_cols, logits, dlogits, labels, losses};
+	Softmax a = {fwd_dt, bwd_dt, n_cols, logits, dlogits, labels, losses, bwd_dt, NULL};
 	for_rows(n_rows, n_threads, softmax_rows, &a);
 	if (loss_sum) {
 		double s = 0.0; long cnt = 0;

@@ -41,6 +41,7 @@ _sig = {
     "oracle_gemm_e4m3": (None, [_i, _i, _i, _vp, _vp, _vp, _vp, _vp, _i]),
     "oracle_gemm_e4m3_swiglu": (None, [_i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i]),
     "oracle_gemm_e4m3_swiglu_bwd": (None, [_i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i]),
+    "oracle_softmax_fp32_out": (None, [_i, _i, _i, _vp, _vp, _vp, _i]),
     "oracle_embedding": (None, [_i, _i, _i, _vp, _vp, _vp]),
     "oracle_copy_to_seq_context": (None, [_i, _i, _i, _vp, _vp, _vp, _vp, _vp]),
     "oracle_select_experts": (None, [_i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i]),
@@ -246,3 +247,11 @@ def select_experts(dt, X_routed, top_k, counts_in=None, threads=None):
 
 def sigmoid_score(x):
     return float(_lib.oracle_sigmoid_score(float(x)))
+
+
+def softmax_fp32_out(fwd_dt, X, threads=None):
+    """Returns (probabilities fp32, arg_maxs uint32): the reference's softmax_<f16|bf16>_fp32 kernels."""
+    out = np.empty(X.shape, np.float32)
+    arg = np.empty(X.shape[0], np.uint32)
+    _lib.oracle_softmax_fp32_out(fwd_dt, X.shape[0], X.shape[1], _p(X), _p(out), _p(arg), threads or N_THREADS)
+    return out, arg
