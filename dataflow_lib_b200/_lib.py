@@ -38,6 +38,8 @@ KERNEL_ABI = {
     "dfb200_transpose_bytes": (_i, [_i, _i, _vp, _i, _vp, _i, _vp]),
     "dfb200_gemm_e4m3": (_i, [_i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
     "dfb200_gemm_e4m3_swiglu": (_i, [_i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
+    "dfb200_swiglu_quantize_rows_e4m3": (_i, [_i, _i, _vp, _vp, _vp, _vp, _vp]),
+    "dfb200_swiglu_bwd_quantize_rows_e4m3": (_i, [_i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
     "dfb200_gemm_e4m3_swiglu_bwd": (_i, [_i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
     "dfb200_swiglu_ffn_fp8_workspace_bytes": (_u64, [_i, _i, _i]),
     "dfb200_swiglu_ffn_fp8": (_i, [_i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _u64, _vp]),

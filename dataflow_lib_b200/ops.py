@@ -146,6 +146,15 @@ def quantize_rows_e4m3(n_rows, n_cols, X, Q, row_scales, col_factors=None, strea
     _check(_lib_.dfb200_quantize_rows_e4m3(n_rows, n_cols, _ptr(X), _ptr(col_factors), _ptr(Q), _ptr(row_scales), _stream(stream)), "quantize_rows_e4m3")
 
 
+def swiglu_quantize_rows_e4m3(n_rows, f, gate, up, Q, row_scales, stream=None):
+    _check(_lib_.dfb200_swiglu_quantize_rows_e4m3(n_rows, f, _ptr(gate), _ptr(up), _ptr(Q), _ptr(row_scales), _stream(stream)), "swiglu_quantize_rows_e4m3")
+
+
+def swiglu_bwd_quantize_rows_e4m3(n_rows, f, gate, up, dH, Q, row_scales, col_factors=None, stream=None):
+    _check(_lib_.dfb200_swiglu_bwd_quantize_rows_e4m3(n_rows, f, _ptr(gate), _ptr(up), _ptr(dH), _ptr(col_factors), _ptr(Q), _ptr(row_scales),
+                                                      _stream(stream)), "swiglu_bwd_quantize_rows_e4m3")
+
+
 def gemm_e4m3(M, N, K, A, a_row_scales, W, w_scales, out, residual=None, stream=None):
     _check(_lib_.dfb200_gemm_e4m3(M, N, K, _ptr(A), _ptr(a_row_scales), _ptr(W), _ptr(w_scales), _ptr(residual), _ptr(out), _stream(stream)), "gemm_e4m3")
 
@@ -153,6 +162,11 @@ def gemm_e4m3(M, N, K, A, a_row_scales, W, w_scales, out, residual=None, stream=
 def gemm_e4m3_swiglu(M, N, K, A, a_row_scales, Wgate, gate_scales, Wup, up_scales, H, gate_save=None, up_save=None, stream=None):
     _check(_lib_.dfb200_gemm_e4m3_swiglu(M, N, K, _ptr(A), _ptr(a_row_scales), _ptr(Wgate), _ptr(gate_scales), _ptr(Wup), _ptr(up_scales),
                                          _ptr(H), _ptr(gate_save), _ptr(up_save), _stream(stream)), "gemm_e4m3_swiglu")
+
+
+def gemm_e4m3_swiglu_bwd(M, N, K, dOq, row_scales, WdownT, gate_saved, up_saved, dGU, stream=None):
+    _check(_lib_.dfb200_gemm_e4m3_swiglu_bwd(M, N, K, _ptr(dOq), _ptr(row_scales), _ptr(WdownT), _ptr(gate_saved), _ptr(up_saved), _ptr(dGU),
+                                             _stream(stream)), "gemm_e4m3_swiglu_bwd")
 
 
 def swiglu_ffn_fp8(T, d, f, A, Wgate, gate_scales, Wup, up_scales, Wdown, down_scales, out, gate_save=None, up_save=None, residual=None, stream=None,

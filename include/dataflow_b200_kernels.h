@@ -152,6 +152,13 @@ int dfb200_gemm_e4m3(int M, int N, int K, const void * A_e4m3, const float * a_r
 int dfb200_gemm_e4m3_swiglu(int M, int N, int K, const void * A_e4m3, const float * a_row_scales, const void * Wgate_e4m3,
                             const float * gate_scales, const void * Wup_e4m3, const float * up_scales, void * H_bf16,
                             void * gate_save_bf16, void * up_save_bf16, void * stream);
+/* Row quantisation fused with the elementwise op that makes the row (the bf16 intermediate is never stored):
+ *   dfb200_swiglu_quantize_rows_e4m3      codes [n_rows, f]  of h = bf16(silu(gate) * up)                      (arithmetic of dfb200_swiglu)
+ *   dfb200_swiglu_bwd_quantize_rows_e4m3  codes [n_rows, 2f] of [dgate | dup] = swiglu_bwd_x(gate, up, dH) in bf16, times col_factors[2f]
+ *                                         (arithmetic of dfb200_swiglu_bwd_x; col_factors may be NULL, else 16-byte aligned) */
+int dfb200_swiglu_quantize_rows_e4m3(int n_rows, int f, const void * gate_bf16, const void * up_bf16, void * Q_e4m3, float * row_scales, void * stream);
+int dfb200_swiglu_bwd_quantize_rows_e4m3(int n_rows, int f, const void * gate_bf16, const void * up_bf16, const void * dH_bf16,
+                                         const float * col_factors, void * Q_e4m3, float * row_scales, void * stream);
 int dfb200_gemm_e4m3_swiglu_bwd(int M, int N, int K, const void * dOut_e4m3, const float * dout_row_scales, const void * WdownT_e4m3,
                                 const void * gate_saved_bf16, const void * up_saved_bf16, void * dgate_dup_bf16, void * stream);
 uint64_t dfb200_swiglu_ffn_fp8_workspace_bytes(int T, int d, int f);

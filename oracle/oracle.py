@@ -201,20 +201,22 @@ def gemm_e4m3_swiglu_bwd(dOq, s_rows, WdownT, g_saved, u_saved, threads=None):
 
 
 def swiglu_ffn_fp8(A_bf16, Wg, sg, Wu, su, Wd, sd, threads=None):
-    """The whole forward: quantise rows, gate/up + SwiGLU, quantise the hidden rows, down projection. Returns (out, g, u)."""
+    """The whole forward (dfb200_swiglu_ffn_fp8): quantise rows, gate and up projections (bf16), SwiGLU in bf16, quantise the hidden
+    rows, down projection. Returns (out, g, u)."""
     Aq, sa = quantize_rows_e4m3(A_bf16, None, threads)
-    H, g, u = gemm_e4m3_swiglu(Aq, sa, Wg, sg, Wu, su, True, threads)
-    Hq, sh = quantize_rows_e4m3(H, None, threads)
+    g, u = gemm_e4m3(Aq, sa, Wg, sg, threads), gemm_e4m3(Aq, sa, Wu, su, threads)
+    Hq, sh = quantize_rows_e4m3(swiglu(BF16, g, u, threads), None, threads)
     return gemm_e4m3(Hq, sh, Wd, sd, threads), g, u
 
 
 def swiglu_ffn_fp8_bwd(dOut_bf16, g, u, Wg, sg, Wu, su, Wd, sd, threads=None):
-    """Input gradient of the FFN (see dfb200_swiglu_ffn_fp8_bwd): returns dA bf16 [T, d]."""
+    """Input gradient of the FFN (dfb200_swiglu_ffn_fp8_bwd): returns dA bf16 [T, d]."""
     WdT = np.ascontiguousarray(Wd.T)                                           # [f, d]
     WguT = np.ascontiguousarray(np.concatenate([Wg.T, Wu.T], axis=1))          # [d, 2f]
     dOq, s1 = quantize_rows_e4m3(dOut_bf16, sd, threads)
-    dGU = gemm_e4m3_swiglu_bwd(dOq, s1, WdT, g, u, threads)
-    dGUq, s2 = quantize_rows_e4m3(dGU, np.concatenate([sg, su]), threads)
+    dH = gemm_e4m3(dOq, s1, WdT, None, threads)
+    dg, du = swiglu_bwd_x(BF16, BF16, g, u, dH, threads)
+    dGUq, s2 = quantize_rows_e4m3(np.ascontiguousarray(np.concatenate([dg, du], axis=1)), np.concatenate([sg, su]), threads)
     return gemm_e4m3(dGUq, s2, WguT, None, threads)
 
 
