@@ -191,15 +191,27 @@ quantize_rows_e4m3_kernel(int n_rows, int n_cols, const void * __restrict__ X, c
 		}
 	};
 	float amax = 0.0f;
-	#pragma unroll
-	for (int v = 0; v < VPT; v++) {
-		const int c = tid + v * nthr;
-		if (c < n_chunks) {
-			float x[8];
-			scaled(v, c, x);
-			#pragma unroll
-			for (int i = 0; i < 8; i++) amax = fmaxf(amax, fabsf(x[i]));
+	if constexpr (HAS_MULT) {
+		#pragma unroll
+		for (int v = 0; v < VPT; v++) {
+			const int c = tid + v * nthr;
+			if (c < n_chunks) {
+				float x[8];
+				scaled(v, c, x);
+				#pragma unroll
+				for (int i = 0; i < 8; i++) amax = fmaxf(amax, fabsf(x[i]));
+			}
 		}
+	} else {                                               // the maximum of the bf16 values themselves, on packed pairs
+		__nv_bfloat162 m2 = __float2bfloat162_rn(0.0f);
+		#pragma unroll
+		for (int v = 0; v < VPT; v++) {
+			if (tid + v * nthr < n_chunks) {
+				#pragma unroll
+				for (int i = 0; i < 4; i++) m2 = __hmax2(m2, __habs2(*reinterpret_cast<const __nv_bfloat162 *>(&raw[v][i])));
+			}
+		}
+		amax = fmaxf(__low2float(m2), __high2float(m2));
 	}
 	amax = warp_max(amax);
 	if ((tid & 31) == 0) red[tid >> 5] = amax;
@@ -227,8 +239,8 @@ quantize_rows_e4m3_kernel(int n_rows, int n_cols, const void * __restrict__ X, c
 // Arithmetic of the elementwise part is that of swiglu_fwd_kernel / swiglu_bwd_x_kernel (reference:
 // src/ops/nvidia/activations/swiglu.cu:58-65, swiglu_bwd_x.cu:68-77), rounded to bf16 exactly where those kernels round; the
 // quantisation is quantize_rows_e4m3_kernel's. One CTA per row, the bf16 results stay packed in registers between the passes.
-template <int VPT, bool BWD>
-__global__ void __launch_bounds__(1024)
+template <int VPT, bool BWD, bool HAS_MULT>
+__global__ void __launch_bounds__(1024, VPT <= 2 ? 2 : 1)
 swiglu_quantize_rows_kernel(int n_rows, int f, const void * __restrict__ G, const void * __restrict__ U, const void * __restrict__ dH,
                             const float * __restrict__ col_mult, void * __restrict__ Q, float * __restrict__ scales) {
 	__shared__ float red[32];
@@ -248,10 +260,10 @@ swiglu_quantize_rows_kernel(int n_rows, int f, const void * __restrict__ G, cons
 				float dh[8], d1[8], d3[8];
 				load_elems<bf16_t, 8, Hint::STREAM>(dH, in_elem + (uint64_t) c * 8, dh);
 				#pragma unroll
-				for (int i = 0; i < 8; i++) {
-					const float e = __expf(-g[i]), ope = 1.0f + e;
-					d3[i] = dh[i] * __fdividef(g[i], ope);
-					d1[i] = dh[i] * __fdividef(u[i] * (ope + g[i] * e), ope * ope);
+				for (int i = 0; i < 8; i++) {                       // one reciprocal serves silu(g) and its derivative
+					const float e = __expf(-g[i]), ope = 1.0f + e, r = fast_rcp(ope);
+					d3[i] = dh[i] * (g[i] * r);
+					d1[i] = dh[i] * ((u[i] * (ope + g[i] * e)) * (r * r));
 				}
 				#pragma unroll
 				for (int i = 0; i < 4; i++) { res[v][0][i] = Word<bf16_t>::pack(&d1[2 * i]); res[v][1][i] = Word<bf16_t>::pack(&d3[2 * i]); }
@@ -267,7 +279,7 @@ swiglu_quantize_rows_kernel(int n_rows, int f, const void * __restrict__ G, cons
 	auto scaled = [&](int v, int part, int c, float (&x)[8]) {          // bf16 result * column factor (one fp32 rounding)
 		#pragma unroll
 		for (int i = 0; i < 4; i++) Word<bf16_t>::unpack(res[v][part][i], &x[2 * i]);
-		if (col_mult) {
+		if constexpr (HAS_MULT) {
 			const float * m = col_mult + (size_t) part * f + (size_t) c * 8;
 			const float4 m0 = __ldg(reinterpret_cast<const float4 *>(m)), m1 = __ldg(reinterpret_cast<const float4 *>(m + 4));
 			x[0] = __fmul_rn(x[0], m0.x); x[1] = __fmul_rn(x[1], m0.y); x[2] = __fmul_rn(x[2], m0.z); x[3] = __fmul_rn(x[3], m0.w);
@@ -275,18 +287,33 @@ swiglu_quantize_rows_kernel(int n_rows, int f, const void * __restrict__ G, cons
 		}
 	};
 	float amax = 0.0f;
-	#pragma unroll
-	for (int v = 0; v < VPT; v++) {
-		const int c = tid + v * nthr;
-		if (c < n_chunks) {
-			#pragma unroll
-			for (int part = 0; part < PARTS; part++) {
-				float x[8];
-				scaled(v, part, c, x);
+	if constexpr (HAS_MULT) {
+		#pragma unroll
+		for (int v = 0; v < VPT; v++) {
+			const int c = tid + v * nthr;
+			if (c < n_chunks) {
 				#pragma unroll
-				for (int i = 0; i < 8; i++) amax = fmaxf(amax, fabsf(x[i]));
+				for (int part = 0; part < PARTS; part++) {
+					float x[8];
+					scaled(v, part, c, x);
+					#pragma unroll
+					for (int i = 0; i < 8; i++) amax = fmaxf(amax, fabsf(x[i]));
+				}
 			}
 		}
+	} else {                                               // no factors: the maximum of the bf16 values themselves, on packed pairs
+		__nv_bfloat162 m2 = __float2bfloat162_rn(0.0f);
+		#pragma unroll
+		for (int v = 0; v < VPT; v++) {
+			const int c = tid + v * nthr;
+			if (c < n_chunks) {
+				#pragma unroll
+				for (int part = 0; part < PARTS; part++)
+					#pragma unroll
+					for (int i = 0; i < 4; i++) m2 = __hmax2(m2, __habs2(*reinterpret_cast<const __nv_bfloat162 *>(&res[v][part][i])));
+			}
+		}
+		amax = fmaxf(__low2float(m2), __high2float(m2));
 	}
 	amax = warp_max(amax);
 	if ((tid & 31) == 0) red[tid >> 5] = amax;
@@ -791,8 +818,9 @@ static int launch_swiglu_quantize(bool bwd, int n_rows, int f, const void * G, c
 	const int threads = ((n_chunks + vpt - 1) / vpt + 31) / 32 * 32;
 	cudaStream_t s = (cudaStream_t) stream;
 #define DFB200_SQ_CASE(V) \
-	if (bwd) swiglu_quantize_rows_kernel<V, true><<<n_rows, threads, 0, s>>>(n_rows, f, G, U, dH, col_factors, Q, row_scales); \
-	else swiglu_quantize_rows_kernel<V, false><<<n_rows, threads, 0, s>>>(n_rows, f, G, U, dH, col_factors, Q, row_scales)
+	if (bwd && col_factors) swiglu_quantize_rows_kernel<V, true, true><<<n_rows, threads, 0, s>>>(n_rows, f, G, U, dH, col_factors, Q, row_scales); \
+	else if (bwd) swiglu_quantize_rows_kernel<V, true, false><<<n_rows, threads, 0, s>>>(n_rows, f, G, U, dH, col_factors, Q, row_scales); \
+	else swiglu_quantize_rows_kernel<V, false, false><<<n_rows, threads, 0, s>>>(n_rows, f, G, U, dH, col_factors, Q, row_scales)
 	switch (vpt) {
 		case 1: DFB200_SQ_CASE(1); break;
 		case 2: DFB200_SQ_CASE(2); break;
