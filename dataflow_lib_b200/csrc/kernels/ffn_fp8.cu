@@ -1,24 +1,27 @@
-// FP8-weight SwiGLU FFN forward on the 5th-generation tensor cores (tcgen05 + tensor memory).
+// FP8-weight SwiGLU FFN, forward and input gradient, on the 5th-generation tensor cores (tcgen05 + tensor memory).
 //
-//   H   = silu(A Wg^T * sa sg) * (A Wu^T * sa su)        [T, f]  bf16
-//   Out = (H Wd^T) * sh sd                                [T, d]  bf16
+//   forward   Aq, sa = quantise_rows(A);  g = (Aq Wg^T) sa sg;  u = (Aq Wu^T) sa su            [T, f] bf16 each
+//             Hq, sh = quantise_rows( bf16(silu(g) u) );  Out = (Hq Wd^T) sh sd (+ residual)    [T, d] bf16
+//   backward  dOq, s1 = quantise_rows(dOut * sd);  dH = (dOq Wd) s1;  dGUq, s2 = quantise_rows( swiglu_bwd_x(g, u, dH) * [sg | su] );
+//             dA = (dGUq [Wg | Wu]) s2
 //
 // Weights are e4m3 with one fp32 scale per OUTPUT channel and are stored [out_features, in_features] (reduction
 // dimension contiguous). tcgen05.mma kind::f8f6f4 needs both operands in 8 bits, so activations are quantised to e4m3
-// with one fp32 scale per ROW (token) by quantize_rows_e4m3_kernel; both scales leave the contraction and are applied
-// to the fp32 accumulator in the epilogue. The reference has no such op (its only GEMM is a cuBLASLt call without
-// scale pointers, src/ops/nvidia/external/matmul_helper/src/matmul_helper.c:379-416); the arithmetic contract is the
-// one restated by the CPU oracle (oracle_ffn_fp8_*).
+// with one fp32 scale per ROW (token); both scales leave the contraction and are applied to the fp32 accumulator in the
+// epilogue. Scales that sit on a contraction index (backward) are folded into the activations before quantisation.
+// The reference has no such op (its only GEMM is a cuBLASLt call without scale pointers,
+// src/ops/nvidia/external/matmul_helper/src/matmul_helper.c:379-416); the arithmetic contract is the one restated by the
+// CPU oracle (oracle_quantize_rows_e4m3, oracle_gemm_e4m3*, and the reference's own swiglu / swiglu_bwd_x arithmetic).
 //
-// GEMM kernel: persistent CTAs (one per SM) walk 128 x 256 accumulator tiles; two accumulator stages in tensor memory
-// (2 x 256 of the 512 columns) let the epilogue of one tile overlap the MMAs of the next. Warp-specialised:
-//   warp 0      one thread issues TMA tile loads (cp.async.bulk.tensor, 128-byte swizzle, CTA-local destination)
-//               into a 4-stage shared-memory ring (A 128x128 B + B 256x128 B per stage), completion on mbarriers;
-//   warp 1      allocates the tensor memory; one thread issues tcgen05.mma (M128 N256 K32, fp32
-//               accumulation in TMEM) and tcgen05.commit, which releases ring stages and finally signals the epilogue;
-//   warps 2-9   read the accumulator with tcgen05.ld (two warps per 32-lane quarter, half of the columns each), apply the scales (and SwiGLU
-//               for the gate/up pair, whose two 128-column halves are the gate and the up projection of the same 128
-//               output channels), convert to bf16 and store.
+// GEMM kernel: persistent, warp-specialised, two accumulator stages in tensor memory (2 x 256 of the 512 columns) so that the
+// epilogue of one tile overlaps the MMAs of the next:
+//   warp 0      one thread issues TMA tile loads (cp.async.bulk.tensor, 128-byte swizzle) into a shared-memory ring,
+//               completion on mbarriers;
+//   warp 1      allocates the tensor memory; one thread issues tcgen05.mma (fp32 accumulation in TMEM) and tcgen05.commit,
+//               which releases ring stages and finally signals the epilogue;
+//   warps 2-9   read the accumulator with tcgen05.ld (two warps per 32-lane quarter, half of the columns each), apply the
+//               scales (and, in the fused modes, SwiGLU or its backward), convert to bf16 and store.
+// Two forms: CTA PAIRS on 256 x 256 tiles (tcgen05 cta_group::2; see gemm_e4m3_kernel) and one CTA per 128 x 256 tile.
 // Every mbarrier wait is bounded and reports through the kernel status word.
 #include "common.cuh"
 #include "tma.cuh"
