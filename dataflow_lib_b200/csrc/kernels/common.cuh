@@ -28,6 +28,27 @@ int ctas_per_sm(const void * kernel, int threads, size_t dyn_smem);
 // Opts `kernel` in to `dyn_smem` bytes of dynamic shared memory (needed above 48 KB); remembered per kernel and device.
 void allow_dyn_smem(const void * kernel, size_t dyn_smem);
 
+// Launch with programmatic stream serialisation: the kernel's CTAs may become resident while the previous kernel of the stream
+// is still draining (that kernel calls pdl_prologue(), which lets its successor be scheduled early). A kernel launched this way
+// must call pdl_prologue() before its first access to global memory: it returns once the predecessor has completed and its
+// writes are visible, so stream order is kept exactly; what is saved is the launch latency and the ramp between short kernels.
+template <typename... KArgs, typename... Args>
+static inline void launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args &&... args) {
+	cudaLaunchConfig_t cfg = {};
+	cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = stream;
+	cudaLaunchAttribute attr[1];
+	attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+	attr[0].val.programmaticStreamSerializationAllowed = 1;
+	cfg.attrs = attr; cfg.numAttrs = 1;
+	(void) cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);      // a failure stays readable through cudaGetLastError (check_launch)
+}
+#ifdef __CUDACC__
+__device__ __forceinline__ void pdl_prologue() {
+	cudaTriggerProgrammaticLaunchCompletion();       // the next kernel of the stream may be scheduled; it still waits for this one to finish
+	cudaGridDependencySynchronize();                 // the previous kernel of the stream has finished and its writes are visible
+}
+#endif
+
 static inline bool aligned16(const void * p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 static inline int dtype_size(int dt) {

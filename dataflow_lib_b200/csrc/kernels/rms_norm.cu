@@ -60,6 +60,7 @@ __global__ void __launch_bounds__(fwd_max_threads(VPT))
 rms_norm_fwd_kernel(int n_rows, int n_cols, float eps, const void * __restrict__ weight, const void * __restrict__ X,
                     void * __restrict__ out, float * __restrict__ weighted_sums, float * __restrict__ rms_vals) {
 	__shared__ float red[2][2][32];
+	pdl_prologue();
 	const int n_chunks = n_cols / E;
 	const int tid = threadIdx.x, nthr = blockDim.x;
 
@@ -154,6 +155,7 @@ __global__ void __launch_bounds__(bwd_x_max_threads(VPT))
 rms_norm_bwd_x_kernel(int n_rows, int n_cols, const float * __restrict__ fwd_weighted_sums, const float * __restrict__ fwd_rms_vals,
                       const void * __restrict__ weight, const void * __restrict__ X, const void * __restrict__ dY, void * dX) {
 	constexpr int BEPW = Word<B>::EPW, BW = E / BEPW;
+	pdl_prologue();
 	const int n_chunks = n_cols / E;
 	const int tid = threadIdx.x, nthr = blockDim.x;
 	const float n_cols_f = (float) n_cols;
@@ -210,6 +212,7 @@ __global__ void __launch_bounds__(bwd_w_max_threads(VPT))
 rms_norm_bwd_w_partial_kernel(int n_rows, int n_cols, int group_threads, const float * __restrict__ fwd_rms_vals,
                               const void * __restrict__ X, const void * __restrict__ dY, float * __restrict__ partials) {
 	extern __shared__ float group_sums[];      // [groups - 1][n_cols]
+	pdl_prologue();                            // also lets stage 2 be scheduled: it waits for this grid in its own prologue
 	const int n_chunks = n_cols / E;
 	const int groups = blockDim.x / group_threads;
 	const int g = threadIdx.x / group_threads;
@@ -263,7 +266,6 @@ rms_norm_bwd_w_partial_kernel(int n_rows, int n_cols, int group_threads, const f
 		#pragma unroll
 		for (int v = 0; v < VPT; v++) { xr[v] = xn[v]; gr[v] = gn[v]; }
 	}
-	cudaTriggerProgrammaticLaunchCompletion();       // the dependent (stage 2) may start being scheduled
 
 	if (g > 0) {
 		#pragma unroll
@@ -307,7 +309,7 @@ rms_norm_bwd_w_final_kernel(int n_cols, int n_partials, const float * __restrict
 	__shared__ float slice_sum[32][33];
 	const int lane = threadIdx.x & 31, slice = threadIdx.x >> 5;
 	const int col = blockIdx.x * 32 + lane;
-	cudaGridDependencySynchronize();
+	pdl_prologue();
 	float s = 0.0f;
 	if (col < n_cols) {
 		#pragma unroll 4
@@ -393,7 +395,7 @@ extern "C" int dfb200_rms_norm(int fwd_dt, int n_rows, int n_cols, float eps, co
 	DFB200_DISPATCH_DTYPE(fwd_dt, T, DFB200_DISPATCH_VPT(geo.vpt, VPT, {
 		auto kernel = rms_norm_fwd_kernel<T, VPT>;
 		const int grid = persistent_grid(kernel, n_rows, geo.threads);
-		kernel<<<grid, geo.threads, 0, (cudaStream_t) stream>>>(n_rows, n_cols, eps, rms_weight, X, out, weighted_sums, rms_vals);
+		launch_pdl(kernel, dim3(grid), dim3(geo.threads), 0, (cudaStream_t) stream, n_rows, n_cols, eps, rms_weight, X, out, weighted_sums, rms_vals);
 	}));
 	return check_launch("rms_norm");
 }
@@ -414,7 +416,7 @@ extern "C" int dfb200_rms_norm_bwd_x(int fwd_dt, int bwd_dt, int n_rows, int n_c
 	DFB200_DISPATCH_PAIR(fwd_dt, bwd_dt, F, B, DFB200_DISPATCH_VPT(geo.vpt, VPT, {
 		auto kernel = rms_norm_bwd_x_kernel<F, B, VPT>;
 		const int grid = persistent_grid(kernel, n_rows, geo.threads);
-		kernel<<<grid, geo.threads, 0, (cudaStream_t) stream>>>(n_rows, n_cols, fwd_weighted_sums, fwd_rms_vals, rms_weight, X_inp, upstream_dX, dX);
+		launch_pdl(kernel, dim3(grid), dim3(geo.threads), 0, (cudaStream_t) stream, n_rows, n_cols, fwd_weighted_sums, fwd_rms_vals, rms_weight, X_inp, upstream_dX, dX);
 	}));
 	return check_launch("rms_norm_bwd_x");
 }
@@ -466,7 +468,7 @@ extern "C" int dfb200_rms_norm_bwd_w(int fwd_dt, int bwd_dt, int n_rows, int n_c
 	DFB200_DISPATCH_PAIR(fwd_dt, bwd_dt, F, B, DFB200_DISPATCH_VPT(geo.vpt, VPT, {
 		auto kernel = rms_norm_bwd_w_partial_kernel<F, B, VPT>;
 		allow_dyn_smem(reinterpret_cast<const void *>(kernel), smem);
-		kernel<<<grid, groups * geo.threads, smem, s>>>(n_rows, n_cols, geo.threads, fwd_rms_vals, X_inp, upstream_dX, partials);
+		launch_pdl(kernel, dim3(grid), dim3(groups * geo.threads), smem, s, n_rows, n_cols, geo.threads, fwd_rms_vals, X_inp, upstream_dX, partials);
 	}));
 	rc = check_launch("rms_norm_bwd_w (partial sums)");
 	if (rc) return rc;

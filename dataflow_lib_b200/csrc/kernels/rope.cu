@@ -44,6 +44,7 @@ rope_kernel(int tokens, int model_dim, int kv_dim, int head_dim, int tok_per_ite
 	float2 * table = reinterpret_cast<float2 *>(smem_f + ((half + 3) & ~3)); // [2][tok_per_iter * half]
 	const int table_len = tok_per_iter * half;
 	const int tid = threadIdx.x;
+	cudaTriggerProgrammaticLaunchCompletion();       // see pdl_prologue(): the frequencies below need no global memory,
 
 	// angle_j = theta^(-(2j)/head_dim). The exponent is formed in fp32 as the reference does;
 	// the power is taken in fp64 and rounded once, which gives the correctly rounded fp32 powf.
@@ -52,6 +53,7 @@ rope_kernel(int tokens, int model_dim, int kv_dim, int head_dim, int tok_per_ite
 		inv_freq[j] = (float) pow((double) theta, (double) expo);
 	}
 	__syncthreads();
+	cudaGridDependencySynchronize();                 // so the wait for the previous kernel of the stream comes after them
 
 	const int q_chunks = model_dim / E, k_chunks = kv_dim / E;
 	const int row_chunks = q_chunks + k_chunks;
@@ -142,6 +144,7 @@ rope_staged_kernel(int tokens, int model_dim, int kv_dim, int head_dim, int tok_
 	uint64_t * full = reinterpret_cast<uint64_t *>(inv_freq + ((half + 3) & ~3));       // [STAGES]
 	const int tid = threadIdx.x;
 
+	cudaTriggerProgrammaticLaunchCompletion();       // see pdl_prologue(): barrier setup and the frequencies need no global memory,
 	if (tid == 0) {
 		for (int s = 0; s < ROPE_STAGES; s++) mbar_init(&full[s], 1);
 		mbar_fence_init();
@@ -151,6 +154,7 @@ rope_staged_kernel(int tokens, int model_dim, int kv_dim, int head_dim, int tok_
 		inv_freq[j] = (float) pow((double) theta, (double) expo);
 	}
 	__syncthreads();
+	cudaGridDependencySynchronize();                 // so the wait for the previous kernel of the stream comes after them
 
 	// this CTA's iterations: token blocks blockIdx.x, + gridDim.x, ...
 	const int n_blocks = (tokens + tok_per_stage - 1) / tok_per_stage;
@@ -284,8 +288,8 @@ static int launch_rope(const char * op, int dt, uint64_t N, int model_dim, int h
 				long long g = (long long) sm_count() * per_sm;
 				const long long blocks = ((long long) tokens + tok - 1) / tok;
 				if (g > blocks) g = blocks;
-				kernel<<<(int) (g < 1 ? 1 : g), ROPE_STAGED_THREADS, smem, (cudaStream_t) stream>>>(tokens, model_dim, kv_dim, head_dim, tok, (float) theta,
-				                                                                                  seq_positions, X_q, X_k, status);
+				launch_pdl(kernel, dim3((unsigned) (g < 1 ? 1 : g)), dim3(ROPE_STAGED_THREADS), smem, (cudaStream_t) stream, tokens, model_dim, kv_dim, head_dim, tok,
+				           (float) theta, seq_positions, X_q, X_k, status);
 				rc = check_launch(op);
 			});
 			return rc;
@@ -304,7 +308,8 @@ static int launch_rope(const char * op, int dt, uint64_t N, int model_dim, int h
 		const long long iters = ((long long) tokens + tok_per_iter - 1) / tok_per_iter;
 		if (g > iters) g = iters;
 		grid = g < 1 ? 1 : (int) g;
-		kernel<<<grid, ROPE_THREADS, smem, (cudaStream_t) stream>>>(tokens, model_dim, kv_dim, head_dim, tok_per_iter, (float) theta, seq_positions, X_q, X_k);
+		launch_pdl(kernel, dim3(grid), dim3(ROPE_THREADS), smem, (cudaStream_t) stream, tokens, model_dim, kv_dim, head_dim, tok_per_iter, (float) theta,
+		           seq_positions, X_q, X_k);
 	});
 	return check_launch(op);
 }

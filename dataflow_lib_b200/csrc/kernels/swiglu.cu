@@ -24,6 +24,7 @@ __device__ __forceinline__ float silu_and_e(float x, float & e) {
 template <typename F, int THREADS, int UNROLL>
 __global__ void __launch_bounds__(THREADS)
 swiglu_fwd_kernel(uint64_t n_chunks, const void * __restrict__ x_w1, const void * __restrict__ x_w3, void * __restrict__ out) {
+	pdl_prologue();
 	const uint64_t first = (uint64_t) blockIdx.x * (THREADS * UNROLL) + threadIdx.x;
 	float a[UNROLL][E], b[UNROLL][E];
 	#pragma unroll
@@ -52,6 +53,7 @@ template <typename F, typename B, int THREADS, int UNROLL>
 __global__ void __launch_bounds__(THREADS)
 swiglu_bwd_x_kernel(uint64_t n_chunks, const void * __restrict__ x_w1, const void * __restrict__ x_w3,
                     const void * __restrict__ upstream_dX, void * __restrict__ dX_w1, void * __restrict__ dX_w3) {
+	pdl_prologue();
 	const uint64_t first = (uint64_t) blockIdx.x * (THREADS * UNROLL) + threadIdx.x;
 	float a[UNROLL][E], b[UNROLL][E], g[UNROLL][E];
 	#pragma unroll
@@ -109,7 +111,7 @@ extern "C" int dfb200_swiglu(int fwd_dt, int num_rows, int num_cols, const void 
 	const uint64_t blocks = (n_chunks + THREADS * UNROLL - 1) / (THREADS * UNROLL);
 	if (blocks > 0x7fffffffull) return set_error(DFB200_ERR_ARG, "swiglu: tensor too large");
 	DFB200_DISPATCH_DTYPE(fwd_dt, F,
-		(swiglu_fwd_kernel<F, THREADS, UNROLL><<<(unsigned) blocks, THREADS, 0, (cudaStream_t) stream>>>(n_chunks, x_w1, x_w3, out)));
+		(launch_pdl(swiglu_fwd_kernel<F, THREADS, UNROLL>, dim3((unsigned) blocks), dim3(THREADS), 0, (cudaStream_t) stream, n_chunks, x_w1, x_w3, out)));
 	return check_launch("swiglu");
 }
 
@@ -124,6 +126,6 @@ extern "C" int dfb200_swiglu_bwd_x(int fwd_dt, int bwd_dt, int num_rows, int num
 	const uint64_t blocks = (n_chunks + THREADS * UNROLL - 1) / (THREADS * UNROLL);
 	if (blocks > 0x7fffffffull) return set_error(DFB200_ERR_ARG, "swiglu_bwd_x: tensor too large");
 	DFB200_DISPATCH_PAIR(fwd_dt, bwd_dt, F, B,
-		(swiglu_bwd_x_kernel<F, B, THREADS, UNROLL><<<(unsigned) blocks, THREADS, 0, (cudaStream_t) stream>>>(n_chunks, x_w1, x_w3, upstream_dX, dX_w1, dX_w3)));
+		(launch_pdl(swiglu_bwd_x_kernel<F, B, THREADS, UNROLL>, dim3((unsigned) blocks), dim3(THREADS), 0, (cudaStream_t) stream, n_chunks, x_w1, x_w3, upstream_dX, dX_w1, dX_w3)));
 	return check_launch("swiglu_bwd_x");
 }
