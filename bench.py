@@ -128,6 +128,68 @@ def run_reference_arm(args):
 
 # ----------------------------------------------------------------------------------------------- GPU arm
 
+def other_configs(hbm_peak):
+    """Untimed extras for the JSON line (N = 1 only, after the timed regions): the other configurations of the hot path, each op
+    launched 5 times back to back between two CUDA events after a warm-up launch, through the C-ABI launchers on torch tensors.
+    HBM-bound ops report algorithmic GB/s and its fraction of the measured copy ceiling; the FP8 FFN reports TFLOP/s."""
+    import torch
+    from dataflow_lib_b200 import ops
+
+    def timed(fn, n=5):
+        fn(); torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(n):
+            fn()
+        b.record(); torch.cuda.synchronize()
+        return a.elapsed_time(b) / n
+
+    g = torch.Generator(device="cuda").manual_seed(0)
+    rn = lambda *s: torch.randn(*s, device="cuda", generator=g).bfloat16()
+    hbm = lambda nbytes, ms: {"ms": ms, "GB/s": nbytes / ms / 1e6, "frac_of_peak": nbytes / ms / 1e6 / hbm_peak}
+    out = {}
+    # C1: RMSNorm 4096 x 4096 (32 MiB tensors: partly L2-resident when repeated, as the configuration is defined)
+    R, C = 4096, 4096
+    X, dY, w = rn(R, C), rn(R, C), (1 + 0.02 * torch.randn(C, device="cuda", generator=g)).bfloat16()
+    Y, dX, dW = torch.empty_like(X), torch.zeros_like(X), torch.zeros(C, device="cuda", dtype=torch.bfloat16)
+    ws, rms = torch.empty(R, device="cuda"), torch.empty(R, device="cuda")
+    out["c1_rms_norm_4096x4096"] = {
+        "fwd": hbm(2 * R * C * 2, timed(lambda: ops.rms_norm(R, C, EPS, w, X, Y, ws, rms))),
+        "bwd_x": hbm(4 * R * C * 2, timed(lambda: ops.rms_norm_bwd_x(R, C, EPS, ws, rms, w, X, dY, dX))),
+        "bwd_w": hbm(2 * R * C * 2, timed(lambda: ops.rms_norm_bwd_w(R, C, EPS, rms, X, dY, dW))),
+        "note": "64-128 MiB per launch against a 126 MB L2: repeated launches partly hit L2"}
+    del X, dY, Y, dX
+    # C3: fused softmax + cross entropy 16384 x 128256
+    T3, V = 16384, 128256
+    logits = (2 * torch.randn(T3, V, device="cuda", generator=g)).bfloat16()
+    dlogits = torch.empty_like(logits)
+    labels = torch.randint(0, V, (T3,), device="cuda", generator=g, dtype=torch.int32)
+    loss = torch.zeros(2, device="cuda")
+    out["c3_softmax_cross_entropy_16384x128256"] = hbm(2 * T3 * V * 2, timed(lambda: ops.softmax_cross_entropy(T3, V, logits, labels, dlogits, None, loss), 3))
+    out["c3_softmax_cross_entropy_16384x128256"]["mean_loss"] = float(loss[0] / loss[1])
+    del logits, dlogits
+    # C4: FP8-weight SwiGLU FFN 16384 x 4096 x 14336, forward and input gradient
+    T4 = 16384
+    u8 = lambda *s: torch.empty(*s, dtype=torch.uint8, device="cuda")
+    def qw(n_out, n_in):
+        W = rn(n_out, n_in) * 0.02
+        Q, sc = u8(n_out, n_in), torch.empty(n_out, device="cuda")
+        ops.quantize_rows_e4m3(n_out, n_in, W.contiguous(), Q, sc)
+        return Q, sc
+    (Wg, sg), (Wu, su), (Wd, sd) = qw(FFN, D_MODEL), qw(FFN, D_MODEL), qw(D_MODEL, FFN)
+    WguT, WdT = u8(D_MODEL, 2 * FFN), u8(FFN, D_MODEL)
+    ops.ffn_fp8_prepare_bwd_weights(D_MODEL, FFN, Wg, Wu, Wd, WguT, WdT)
+    A, dO = rn(T4, D_MODEL), rn(T4, D_MODEL)
+    G, U = torch.empty(T4, FFN, device="cuda", dtype=torch.bfloat16), torch.empty(T4, FFN, device="cuda", dtype=torch.bfloat16)
+    o, dA, sgu = torch.empty_like(A), torch.empty_like(A), torch.cat([sg, su])
+    flops = 6.0 * T4 * D_MODEL * FFN
+    ms_f = timed(lambda: ops.swiglu_ffn_fp8(T4, D_MODEL, FFN, A, Wg, sg, Wu, su, Wd, sd, o, G, U))
+    ms_b = timed(lambda: ops.swiglu_ffn_fp8_bwd(T4, D_MODEL, FFN, dO, G, U, WdT, sd, WguT, sgu, dA))
+    out["c4_swiglu_ffn_fp8_16384x4096x14336"] = {"fwd": {"ms": ms_f, "TFLOP/s": flops / ms_f / 1e9}, "bwd_input_grad": {"ms": ms_b, "TFLOP/s": flops / ms_b / 1e9},
+                                                 "tokens_per_s_fwd_bwd": T4 / ((ms_f + ms_b) * 1e-3)}
+    return out
+
+
 class ClockSampler:
     """nvidia-smi sampling of SM clock and throttle reasons while the timed regions run."""
     FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
@@ -342,6 +404,7 @@ def run_gpu_arm(args):
         ops_report = {name: {"ms": per_op_ms[name], "GB/s": BYTES_PER_TOKEN[name] * T / (per_op_ms[name] * 1e-3) / 1e9,
                              "frac_of_peak": BYTES_PER_TOKEN[name] * T / (per_op_ms[name] * 1e-3) / 1e9 / peak} for name in op_names}
         cpu = cpu_baseline() if world == 1 else None
+        others = other_configs(peak) if world == 1 else None
         line = {
             "metric": METRIC, "value": world * T * args.steps / (ms_total * 1e-3), "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": ms_total / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
@@ -360,6 +423,8 @@ def run_gpu_arm(args):
         }
         if cpu is not None:
             line["cpu_baseline"] = cpu
+        if others is not None:
+            line["other_configs"] = others
         print(json.dumps(line), flush=True)
 
     for a in list(host.values()) + list(out_host.values()):

@@ -201,3 +201,28 @@ def test_handle_api_fails_cleanly_without_a_device(L, capfd):
     assert L.dfb200_swiglu(5, 1, 7, None, None, None, None) == -1
     assert b"multiple of 8" in L.dfb200_last_error()
     assert L.dfb200_rms_norm(1, 1, 8, 1e-5, None, None, None, None, None, None) == -2
+
+
+def test_own_op_identities_are_stable(L):
+    """Identities this library adds (ops whose kernels the reference has but never gave a skeleton, and the fused op): the
+    nickname, argument list and fingerprint are part of the registry contract, so they are pinned here; each fingerprint is
+    also the plain SHA-256 of the 388-byte header (checked with hashlib)."""
+    import hashlib
+    from dataflow_lib_b200 import abi
+    want = {
+        ("set_native_select_experts_skeleton", (5,)): ("select_experts_BF16", [26, 26, 26, 5, 5, 10, 13, 13, 13],
+                                                        "4683b3047ffaec6f53315b8cfabe6a675b9a72e499f59203dbc4dbd5a95c73ab"),
+        ("set_native_softmax_argmax_skeleton", (5,)): ("softmax_argmax_BF16_FP32", [26, 26, 5, 3, 9],
+                                                        "13b5caeb8d64aaa103411c0bb1c5399a625a0e6318a6d041425527b2f1df6580"),
+        ("set_native_softmax_argmax_skeleton", (4,)): ("softmax_argmax_FP16_FP32", [26, 26, 4, 3, 9],
+                                                        "00bf0355dfb6b3de7356d47462035a81c77a2c8541b5f4721b14bd6834c9e97c"),
+        ("set_native_softmax_cross_entropy_skeleton", (5, 5)): ("softmax_cross_entropy_BF16_BF16", [26, 26, 5, 9, 5, 3, 3],
+                                                                "e769fbd45e29682394e79ad43293bd5d087f6af5cacea9039631b052b9377975"),
+    }
+    for (fn, args), (nick, dts, digest) in want.items():
+        sk = abi.OpSkeleton()
+        C.memset(C.byref(sk), 0xAB, C.sizeof(sk))
+        getattr(L, fn)(C.byref(sk), *args)
+        assert sk.header.op_nickname.decode() == nick
+        assert list(sk.header.arg_dtypes)[:sk.header.num_args] == dts and all(d == 0 for d in list(sk.header.arg_dtypes)[sk.header.num_args:])
+        assert bytes(sk.identifier.fingerprint).hex() == digest == hashlib.sha256(bytes(sk.header)).hexdigest()
