@@ -93,8 +93,46 @@ def cpu_baseline(target_seconds=12.0):
     while total < target_seconds and passes < 64:                       # the whole batch is short on a many-core host: repeat it
         _, secs = cpu_chain_tokens_per_s(sample, threads)
         passes, total = passes + 1, total + secs
-    return {"value": sample * passes / total, "unit": UNIT, "cores": threads, "kind": "port",
-            "sample": f"{passes} passes over {sample} of {TOKENS} tokens of the same chain, oracle/oracle.c on {threads} threads, {total:.1f} s"}
+    out = {"value": sample * passes / total, "unit": UNIT, "cores": threads, "kind": "port",
+           "sample": f"{passes} passes over {sample} of {TOKENS} tokens of the same chain, oracle/oracle.c on {threads} threads, {total:.1f} s"}
+    ref = reference_convert_rate(threads)
+    if ref is not None:
+        out["reference_convert_datatype"] = ref
+    return out
+
+
+def reference_convert_rate(threads):
+    """The one piece of the path the reference implements on the CPU: dataflow_convert_datatype (src/datatype/src/dataflow_datatype.c:81-90),
+    used to make bf16 inputs from fp32. Times the reference's own build of it (oracle/_ref/libref_host.so, when present) and this
+    library's host implementation on the chain's activation shape [8192, 4096], fp32 -> bf16, same thread count."""
+    import ctypes as C
+    import numpy as np
+    so = os.path.join(ROOT, "oracle", "_ref", "libref_host.so")
+    if not os.path.exists(so):
+        return None
+    try:
+        ref = C.CDLL(so)
+        from dataflow_lib_b200 import _lib
+    except OSError:
+        return None
+    sig = [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_long, C.c_int]
+    ref.dataflow_convert_datatype.argtypes = sig
+    n = TOKENS * D_MODEL
+    src = np.random.default_rng(0).standard_normal(n, dtype=np.float32)
+    dst_ref, dst_own = np.empty(n, np.uint16), np.empty(n, np.uint16)
+    FP32, BF16 = 3, 5
+
+    def rate(fn, dst):
+        fn(dst.ctypes.data, src.ctypes.data, BF16, FP32, n, threads)
+        t0 = time.perf_counter()
+        reps = 0
+        while time.perf_counter() - t0 < 1.0:
+            fn(dst.ctypes.data, src.ctypes.data, BF16, FP32, n, threads)
+            reps += 1
+        return n * reps / (time.perf_counter() - t0)
+    r_ref, r_own = rate(ref.dataflow_convert_datatype, dst_ref), rate(_lib.lib.dataflow_convert_datatype, dst_own)
+    return {"kind": "reference", "what": f"fp32 -> bf16 of [{TOKENS}, {D_MODEL}] on {threads} threads", "reference_elements_per_s": r_ref,
+            "this_library_elements_per_s": r_own, "identical_output": bool(np.array_equal(dst_ref, dst_own))}
 
 
 def run_reference_arm(args):

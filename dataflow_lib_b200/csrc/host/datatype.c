@@ -108,8 +108,76 @@ static float load_as_fp32(const void * p, DataflowDatatype dt, long i) {
 	}
 }
 
+/* Vector paths for the two conversions that make 16-bit inputs from fp32 and back (8 lanes of integer arithmetic, AVX2; chosen at
+ * run time). They produce the scalar functions' bits: NaN lanes are patched by the scalar code. */
+#if defined(__x86_64__)
+#include <immintrin.h>
+__attribute__((target("avx2")))
+static long fp32_to_bf16_avx2(uint16_t * to, const float * from, long begin, long end) {
+	long i = begin;
+	const __m256i bias = _mm256_set1_epi32(0x7fff), one = _mm256_set1_epi32(1), absmask = _mm256_set1_epi32(0x7fffffff), inf = _mm256_set1_epi32(0x7f800000);
+	for (; i + 8 <= end; i += 8) {
+		const __m256i u = _mm256_loadu_si256((const __m256i *) (from + i));
+		const __m256i nan = _mm256_cmpgt_epi32(_mm256_and_si256(u, absmask), inf);
+		const __m256i r = _mm256_srli_epi32(_mm256_add_epi32(u, _mm256_add_epi32(bias, _mm256_and_si256(_mm256_srli_epi32(u, 16), one))), 16);
+		const __m128i packed = _mm_packus_epi32(_mm256_castsi256_si128(r), _mm256_extracti128_si256(r, 1));
+		_mm_storeu_si128((__m128i *) (to + i), packed);
+		if (_mm256_movemask_epi8(nan)) for (int k = 0; k < 8; k++) to[i + k] = solo_fp32_to_bf16(from[i + k]);
+	}
+	return i;
+}
+__attribute__((target("avx2")))
+static long bf16_to_fp32_avx2(float * to, const uint16_t * from, long begin, long end) {
+	long i = begin;
+	for (; i + 8 <= end; i += 8) {
+		const __m256i w = _mm256_cvtepu16_epi32(_mm_loadu_si128((const __m128i *) (from + i)));
+		_mm256_storeu_si256((__m256i *) (to + i), _mm256_slli_epi32(w, 16));
+	}
+	return i;
+}
+/* fp16 through the F16C converters (round to nearest even, subnormals handled in hardware) */
+__attribute__((target("avx2,f16c")))
+static long fp32_to_fp16_f16c(uint16_t * to, const float * from, long begin, long end) {
+	long i = begin;
+	const __m256i absmask = _mm256_set1_epi32(0x7fffffff), inf = _mm256_set1_epi32(0x7f800000);
+	for (; i + 8 <= end; i += 8) {
+		const __m256 v = _mm256_loadu_ps(from + i);
+		const __m256i nan = _mm256_cmpgt_epi32(_mm256_and_si256(_mm256_castps_si256(v), absmask), inf);
+		_mm_storeu_si128((__m128i *) (to + i), _mm256_cvtps_ph(v, _MM_FROUND_TO_NEAREST_INT | _MM_FROUND_NO_EXC));
+		if (_mm256_movemask_epi8(nan)) for (int k = 0; k < 8; k++) to[i + k] = solo_fp32_to_fp16(from[i + k]);
+	}
+	return i;
+}
+__attribute__((target("avx2,f16c")))
+static long fp16_to_fp32_f16c(float * to, const uint16_t * from, long begin, long end) {
+	long i = begin;
+	for (; i + 8 <= end; i += 8) {
+		const __m128i h = _mm_loadu_si128((const __m128i *) (from + i));
+		const __m128i expo = _mm_and_si128(h, _mm_set1_epi16(0x7c00)), mant = _mm_and_si128(h, _mm_set1_epi16(0x03ff));
+		const int nan = _mm_movemask_epi8(_mm_andnot_si128(_mm_cmpeq_epi16(mant, _mm_setzero_si128()), _mm_cmpeq_epi16(expo, _mm_set1_epi16(0x7c00))));
+		_mm256_storeu_ps(to + i, _mm256_cvtph_ps(h));
+		if (nan) for (int k = 0; k < 8; k++) to[i + k] = solo_fp16_to_fp32(from[i + k]);
+	}
+	return i;
+}
+static int have_avx2(void) { static int v = -1; if (v < 0) v = __builtin_cpu_supports("avx2") ? 1 : 0; return v; }
+static int have_f16c(void) { static int v = -1; if (v < 0) v = (__builtin_cpu_supports("avx2") && __builtin_cpu_supports("f16c")) ? 1 : 0; return v; }
+#else
+static int have_avx2(void) { return 0; }
+#endif
+
 static void * convert_worker(void * arg) {
 	Convert_Job * job = (Convert_Job *) arg;
+#if defined(__x86_64__)
+	if (have_avx2()) {
+		if (job->from_dt == DATAFLOW_FP32 && job->to_dt == DATAFLOW_BF16) job->begin = fp32_to_bf16_avx2((uint16_t *) job->to, (const float *) job->from, job->begin, job->end);
+		else if (job->from_dt == DATAFLOW_BF16 && job->to_dt == DATAFLOW_FP32) job->begin = bf16_to_fp32_avx2((float *) job->to, (const uint16_t *) job->from, job->begin, job->end);
+	}
+	if (have_f16c()) {
+		if (job->from_dt == DATAFLOW_FP32 && job->to_dt == DATAFLOW_FP16) job->begin = fp32_to_fp16_f16c((uint16_t *) job->to, (const float *) job->from, job->begin, job->end);
+		else if (job->from_dt == DATAFLOW_FP16 && job->to_dt == DATAFLOW_FP32) job->begin = fp16_to_fp32_f16c((float *) job->to, (const uint16_t *) job->from, job->begin, job->end);
+	}
+#endif
 	for (long i = job->begin; i < job->end; i++) {
 		const float v = load_as_fp32(job->from, job->from_dt, i);
 		switch (job->to_dt) {
