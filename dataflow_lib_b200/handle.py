@@ -45,6 +45,13 @@ class DataflowHandle:
         return self.h.register_native_code(C.byref(self.h), cubin_path.encode(), config_lib_path.encode(), n, sk,
                                            to_arr(symbols), to_arr(launch_symbols), to_arr(init_symbols))
 
+    def register_external_code(self, lib_path, skeletons, symbols, init_symbols):
+        """handle->register_external_code: plug-in functions (External_Lib_Func) from a shared object, e.g. the reference's cuBLASLt matmul."""
+        n = len(skeletons)
+        sk = (abi.OpSkeleton * n)(*skeletons)
+        to_arr = lambda xs: (C.c_char_p * n)(*[x.encode() if x else None for x in xs])
+        return self.h.register_external_code(C.byref(self.h), lib_path.encode(), n, sk, to_arr(symbols), to_arr(init_symbols))
+
     @property
     def device_info(self):
         return C.cast(self.h.device_info, C.POINTER(abi.CudaDeviceInfo)).contents

@@ -226,3 +226,19 @@ def test_own_op_identities_are_stable(L):
         assert sk.header.op_nickname.decode() == nick
         assert list(sk.header.arg_dtypes)[:sk.header.num_args] == dts and all(d == 0 for d in list(sk.header.arg_dtypes)[sk.header.num_args:])
         assert bytes(sk.identifier.fingerprint).hex() == digest == hashlib.sha256(bytes(sk.header)).hexdigest()
+
+
+def test_reference_external_wrappers_link_against_this_library():
+    """The reference's external-op wrappers and skeletons (matmul, attention), compiled unchanged, resolve what they need
+    (do_fingerprinting) from this library: the matmul identity they produce is the reference's."""
+    so = os.path.join(ROOT, "oracle", "_ref", "libref_external_ops.so")
+    if not os.path.exists(so):
+        pytest.skip("reference wrappers not built (make -C oracle ref)")
+    from dataflow_lib_b200 import abi
+    ext = C.CDLL(so)
+    sk = abi.OpSkeleton()
+    ext.set_external_matmul_skeleton(C.byref(sk))
+    assert sk.header.op_nickname == b"matmul" and sk.header.num_args == 19
+    assert bytes(sk.identifier.fingerprint).hex() == "2a113b16e997d04b8408f9aa299dd5a80bb77d29c95c8cc78270410ef84f3590"
+    for name in ("submit_matmul", "submit_attention", "submit_attention_bwd"):
+        assert hasattr(ext, name)
