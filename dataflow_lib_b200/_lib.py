@@ -97,6 +97,10 @@ HOST_ABI = {
     "set_native_softmax_cross_entropy_skeleton": (None, [_SK, _i, _i]),
     "set_native_select_experts_skeleton": (None, [_SK, _i]),
     "set_native_softmax_argmax_skeleton": (None, [_SK, _i]),
+    "set_native_swiglu_ffn_fp8_skeleton": (None, [_SK]),
+    "set_native_swiglu_ffn_fp8_bwd_skeleton": (None, [_SK]),
+    "submit_swiglu_ffn_fp8": (_i, [_H, _i, _i, _i, _i] + [_vp] * 11),
+    "submit_swiglu_ffn_fp8_bwd": (_i, [_H, _i, _i, _i, _i] + [_vp] * 8),
     "submit_softmax_argmax": (_i, [_H, _i, _i, _i, _i, _vp, _vp, _vp]),
     "submit_embedding": (_i, [_H, _i, _i, _i, _i, _vp, _vp, _vp]),
     "submit_copy_to_seq_context": (_i, [_H, _i, _i, _u64, _i, _i, _vp, _vp, _vp, _vp, _vp]),
@@ -127,6 +131,8 @@ HOST_ABI = {
     "dataflow_b200_copy_to_seq_context": (_i, [_H, _i, _vp, _vp]),
     "dataflow_b200_select_experts": (_i, [_H, _i, _vp, _vp]),
     "dataflow_b200_softmax_argmax": (_i, [_H, _i, _vp, _vp]),
+    "dataflow_b200_swiglu_ffn_fp8": (_i, [_H, _i, _vp, _vp]),
+    "dataflow_b200_swiglu_ffn_fp8_bwd": (_i, [_H, _i, _vp, _vp]),
 }
 
 for _table in (KERNEL_ABI, HOST_ABI):

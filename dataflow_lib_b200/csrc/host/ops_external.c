@@ -145,3 +145,21 @@ int dataflow_b200_softmax_argmax(Dataflow_Handle * h, int stream_id, Op * op, vo
 	return finish(dfb200_softmax_fp32_out(DT(op, 2), ARG(op, 0, int), ARG(op, 1, int), ARG(op, 2, void *), ARG(op, 3, float *), ARG(op, 4, uint32_t *),
 	                                      stream_of(h, stream_id)), "softmax_argmax");
 }
+
+int dataflow_b200_swiglu_ffn_fp8(Dataflow_Handle * h, int stream_id, Op * op, void * op_extra) {
+	Op_Workspace * ws = (Op_Workspace *) op_extra;
+	const int T = ARG(op, 0, int), d = ARG(op, 1, int), f = ARG(op, 2, int);
+	if (ensure_workspace(ws, dfb200_swiglu_ffn_fp8_workspace_bytes(T, d, f))) return -1;
+	return finish(dfb200_swiglu_ffn_fp8(T, d, f, ARG(op, 3, void *), ARG(op, 4, void *), ARG(op, 5, float *), ARG(op, 6, void *), ARG(op, 7, float *),
+	                                    ARG(op, 8, void *), ARG(op, 9, float *), ARG(op, 10, void *), ARG(op, 11, void *), ARG(op, 12, void *),
+	                                    ARG(op, 13, void *), ws->ptr, ws->bytes, stream_of(h, stream_id)), "swiglu_ffn_fp8");
+}
+
+int dataflow_b200_swiglu_ffn_fp8_bwd(Dataflow_Handle * h, int stream_id, Op * op, void * op_extra) {
+	Op_Workspace * ws = (Op_Workspace *) op_extra;
+	const int T = ARG(op, 0, int), d = ARG(op, 1, int), f = ARG(op, 2, int);
+	if (ensure_workspace(ws, dfb200_swiglu_ffn_fp8_workspace_bytes(T, d, f))) return -1;
+	return finish(dfb200_swiglu_ffn_fp8_bwd(T, d, f, ARG(op, 3, void *), ARG(op, 4, void *), ARG(op, 5, void *), ARG(op, 6, void *), ARG(op, 7, float *),
+	                                        ARG(op, 8, void *), ARG(op, 9, float *), ARG(op, 10, void *), ws->ptr, ws->bytes, stream_of(h, stream_id)),
+	              "swiglu_ffn_fp8_bwd");
+}

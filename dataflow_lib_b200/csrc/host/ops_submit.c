@@ -133,3 +133,20 @@ int submit_softmax_argmax(Dataflow_Handle * handle, int stream_id, DataflowDatat
 	ARGS(op, &n_rows, &n_cols, &X, &out, &arg_maxs);
 	return submit(handle, &op, stream_id, "softmax argmax");
 }
+
+int submit_swiglu_ffn_fp8(Dataflow_Handle * handle, int stream_id, int num_tokens, int model_dim, int ffn_dim, void * A, void * Wgate,
+                          float * gate_scales, void * Wup, float * up_scales, void * Wdown, float * down_scales, void * residual, void * out,
+                          void * gate_save, void * up_save) {
+	Op op;
+	set_native_swiglu_ffn_fp8_skeleton(&op.op_skeleton);
+	ARGS(op, &num_tokens, &model_dim, &ffn_dim, &A, &Wgate, &gate_scales, &Wup, &up_scales, &Wdown, &down_scales, &residual, &out, &gate_save, &up_save);
+	return submit(handle, &op, stream_id, "swiglu ffn fp8");
+}
+
+int submit_swiglu_ffn_fp8_bwd(Dataflow_Handle * handle, int stream_id, int num_tokens, int model_dim, int ffn_dim, void * dOut, void * gate_saved,
+                              void * up_saved, void * WdownT, float * down_scales, void * WgateupT, float * gateup_scales, void * dA) {
+	Op op;
+	set_native_swiglu_ffn_fp8_bwd_skeleton(&op.op_skeleton);
+	ARGS(op, &num_tokens, &model_dim, &ffn_dim, &dOut, &gate_saved, &up_saved, &WdownT, &down_scales, &WgateupT, &gateup_scales, &dA);
+	return submit(handle, &op, stream_id, "swiglu ffn fp8 bwd");
+}

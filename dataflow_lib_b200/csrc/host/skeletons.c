@@ -95,6 +95,16 @@ void set_native_cross_entropy_loss_skeleton(Op_Skeleton * skeleton, DataflowData
 	char nick[MAX_OP_NICKNAME_SIZE];   /* n_rows, n_cols, pred_logits, labels */
 	build_skeleton(skeleton, nick1(nick, "cross_entropy_loss", bwd), I_S, I_S, bwd, DATAFLOW_UINT32, END);
 }
+void set_native_swiglu_ffn_fp8_skeleton(Op_Skeleton * skeleton) {
+	/* T, d, f, A, Wgate, gate_scales, Wup, up_scales, Wdown, down_scales, residual, out, gate_save, up_save */
+	const DataflowDatatype a = DATAFLOW_BF16, w = DATAFLOW_FP8E4M3, sc = DATAFLOW_FP32;
+	build_skeleton(skeleton, "swiglu_ffn_fp8_BF16", I_S, I_S, I_S, a, w, sc, w, sc, w, sc, a, a, a, a, END);
+}
+void set_native_swiglu_ffn_fp8_bwd_skeleton(Op_Skeleton * skeleton) {
+	/* T, d, f, dOut, gate_saved, up_saved, WdownT, down_scales, WgateupT, gateup_scales, dA */
+	const DataflowDatatype a = DATAFLOW_BF16, w = DATAFLOW_FP8E4M3, sc = DATAFLOW_FP32;
+	build_skeleton(skeleton, "swiglu_ffn_fp8_bwd_BF16", I_S, I_S, I_S, a, a, a, w, sc, w, sc, a, END);
+}
 void set_native_softmax_argmax_skeleton(Op_Skeleton * skeleton, DataflowDatatype fwd) {
 	char nick[MAX_OP_NICKNAME_SIZE];   /* n_rows, n_cols, X, out, arg_maxs */
 	build_skeleton(skeleton, nick2(nick, "softmax_argmax", fwd, DATAFLOW_FP32), I_S, I_S, fwd, DATAFLOW_FP32, DATAFLOW_UINT32, END);
@@ -123,6 +133,8 @@ int set_native_op_skeleton(Op_Skeleton * skeleton, char * op_name, DataflowDatat
 	else if (!strcmp(op_name, "softmax_cross_entropy")) set_native_softmax_cross_entropy_skeleton(skeleton, fwd_dt, bwd_dt);
 	else if (!strcmp(op_name, "select_experts")) set_native_select_experts_skeleton(skeleton, fwd_dt);
 	else if (!strcmp(op_name, "softmax_argmax")) set_native_softmax_argmax_skeleton(skeleton, fwd_dt);
+	else if (!strcmp(op_name, "swiglu_ffn_fp8")) set_native_swiglu_ffn_fp8_skeleton(skeleton);
+	else if (!strcmp(op_name, "swiglu_ffn_fp8_bwd")) set_native_swiglu_ffn_fp8_bwd_skeleton(skeleton);
 	else {
 		printf("Cannot set skeleton, unknown op: %s, with fwd_dt: %s, bwd_dt: %s\n", op_name,
 		       dataflow_datatype_as_string(fwd_dt), dataflow_datatype_as_string(bwd_dt));
@@ -133,7 +145,7 @@ int set_native_op_skeleton(Op_Skeleton * skeleton, char * op_name, DataflowDatat
 
 /* ---- registration ---------------------------------------------------------------------- */
 
-typedef enum { KEY_FWD, KEY_BWD, KEY_PAIR, KEY_HALF } Key_Kind;   /* KEY_HALF: fp16 and bf16 inputs only */
+typedef enum { KEY_FWD, KEY_BWD, KEY_PAIR, KEY_HALF, KEY_ONE } Key_Kind;   /* KEY_HALF: fp16 and bf16 inputs only; KEY_ONE: a single identity */
 
 typedef struct {
 	const char * op;          /* skeleton family == exported symbol "dataflow_b200_<op>" */
@@ -144,7 +156,7 @@ typedef struct {
 /* The reference registers 54 identities (set_native_op_skeletons.c:13-39): all of them are here. Added: the 5
  * copy_to_seq_context identities (the reference has the skeleton, the wrapper and the kernels but leaves them out of
  * its registration list), 5 select_experts identities (kernels only in the reference) and the 7 datatype pairs of
- * the fused softmax+cross-entropy op, and 2 softmax_argmax identities (fp16 / bf16 -> fp32): 73 in total. */
+ * the fused softmax+cross-entropy op, 2 softmax_argmax identities (fp16 / bf16 -> fp32) and the FP8 FFN forward and backward: 75 in total. */
 static const Op_Family FAMILIES[] = {
 	{"embedding", KEY_FWD, false},      {"copy_to_seq_context", KEY_FWD, false}, {"select_experts", KEY_FWD, false},
 	{"rms_norm", KEY_FWD, false},       {"rms_norm_bwd_x", KEY_PAIR, false}, {"rms_norm_bwd_w", KEY_PAIR, true},
@@ -153,6 +165,7 @@ static const Op_Family FAMILIES[] = {
 	{"softmax", KEY_PAIR, false},       {"cross_entropy_loss", KEY_BWD, false},
 	{"softmax_cross_entropy", KEY_PAIR, true},
 	{"softmax_argmax", KEY_HALF, false},
+	{"swiglu_ffn_fp8", KEY_ONE, true},  {"swiglu_ffn_fp8_bwd", KEY_ONE, true},
 };
 
 static const DataflowDatatype FWD_DTS[5] = {DATAFLOW_FP32, DATAFLOW_FP16, DATAFLOW_BF16, DATAFLOW_FP8E4M3, DATAFLOW_FP8E5M2};
@@ -188,7 +201,7 @@ int register_native_ops(Dataflow_Handle * dataflow_handle, char * native_functio
 	int n = 0;
 	for (size_t f = 0; f < sizeof(FAMILIES) / sizeof(FAMILIES[0]); f++) {
 		const Op_Family * fam = &FAMILIES[f];
-		const int variants = fam->kind == KEY_FWD ? 5 : fam->kind == KEY_BWD ? 3 : fam->kind == KEY_HALF ? 2 : 7;
+		const int variants = fam->kind == KEY_FWD ? 5 : fam->kind == KEY_BWD ? 3 : fam->kind == KEY_HALF ? 2 : fam->kind == KEY_ONE ? 1 : 7;
 		for (int v = 0; v < variants && n < MAX_REGISTERED; v++, n++) {
 			const DataflowDatatype fwd = fam->kind == KEY_FWD ? FWD_DTS[v] : fam->kind == KEY_PAIR ? PAIR_FWD[v] : fam->kind == KEY_HALF ? FWD_DTS[1 + v] : DATAFLOW_NONE;
 			const DataflowDatatype bwd = fam->kind == KEY_BWD ? BWD_DTS[v] : fam->kind == KEY_PAIR ? PAIR_BWD[v] : DATAFLOW_NONE;

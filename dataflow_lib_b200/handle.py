@@ -122,6 +122,15 @@ class DataflowHandle:
     def submit_softmax_argmax(self, stream_id, fwd_dt, n_rows, n_cols, X, out, arg_maxs=None):
         return _L.submit_softmax_argmax(C.byref(self.h), stream_id, int(fwd_dt), n_rows, n_cols, _p(X), _p(out), _p(arg_maxs))
 
+    def submit_swiglu_ffn_fp8(self, stream_id, T, d, f, A, Wgate, gate_scales, Wup, up_scales, Wdown, down_scales, out, residual=None, gate_save=None,
+                              up_save=None):
+        return _L.submit_swiglu_ffn_fp8(C.byref(self.h), stream_id, T, d, f, _p(A), _p(Wgate), _p(gate_scales), _p(Wup), _p(up_scales), _p(Wdown),
+                                        _p(down_scales), _p(residual), _p(out), _p(gate_save), _p(up_save))
+
+    def submit_swiglu_ffn_fp8_bwd(self, stream_id, T, d, f, dOut, gate_saved, up_saved, WdownT, down_scales, WgateupT, gateup_scales, dA):
+        return _L.submit_swiglu_ffn_fp8_bwd(C.byref(self.h), stream_id, T, d, f, _p(dOut), _p(gate_saved), _p(up_saved), _p(WdownT), _p(down_scales),
+                                            _p(WgateupT), _p(gateup_scales), _p(dA))
+
     def close(self):
         if self.h.streams:
             _L.destroy_cuda_dataflow_handle(C.byref(self.h))

@@ -91,6 +91,10 @@ void set_native_select_experts_skeleton(Op_Skeleton * skeleton, DataflowDatatype
 /* The reference's softmax_fp16_fp32 / softmax_bf16_fp32 kernels (fp32 probabilities + arg-max; src/ops/nvidia/loss/softmax.cu:965-1249)
  * have no skeleton either; this one is "softmax_argmax_<F>_FP32": n_rows, n_cols, X, out (fp32), arg_maxs (uint32). */
 void set_native_softmax_argmax_skeleton(Op_Skeleton * skeleton, DataflowDatatype fwd_datatype);
+/* Not in the reference: the FP8-weight SwiGLU FFN, forward ("swiglu_ffn_fp8_BF16") and input gradient ("swiglu_ffn_fp8_bwd_BF16").
+ * Activations bf16, weights e4m3 codes (DATAFLOW_FP8E4M3) with fp32 per-output-channel scales; argument lists as submit_swiglu_ffn_fp8*. */
+void set_native_swiglu_ffn_fp8_skeleton(Op_Skeleton * skeleton);
+void set_native_swiglu_ffn_fp8_bwd_skeleton(Op_Skeleton * skeleton);
 /* Not in the reference: the fused softmax + cross-entropy op ("softmax_cross_entropy_<F>_<B>"). */
 void set_native_softmax_cross_entropy_skeleton(Op_Skeleton * skeleton, DataflowDatatype fwd_datatype, DataflowDatatype bwd_datatype);
 
@@ -136,6 +140,16 @@ int submit_softmax_argmax(Dataflow_Handle * handle, int stream_id, DataflowDatat
 int submit_softmax_cross_entropy(Dataflow_Handle * handle, int stream_id, DataflowDatatype fwd_dt, DataflowDatatype bwd_dt,
                                  int n_rows, int n_cols, void * logits, uint32_t * labels, void * dlogits,
                                  float * row_loss, float * loss_sum);
+
+/* Not in the reference: out = down(silu(gate(A)) * up(A)) + residual with e4m3 weights (include/dataflow_b200_kernels.h,
+ * dfb200_swiglu_ffn_fp8). residual, gate_save and up_save may be NULL (gate_save and up_save together); the op keeps its own
+ * device workspace. The backward op needs the transposed codes made by dfb200_ffn_fp8_prepare_bwd_weights. */
+int submit_swiglu_ffn_fp8(Dataflow_Handle * handle, int stream_id, int num_tokens, int model_dim, int ffn_dim,
+                          void * A, void * Wgate, float * gate_scales, void * Wup, float * up_scales, void * Wdown, float * down_scales,
+                          void * residual, void * out, void * gate_save, void * up_save);
+int submit_swiglu_ffn_fp8_bwd(Dataflow_Handle * handle, int stream_id, int num_tokens, int model_dim, int ffn_dim,
+                              void * dOut, void * gate_saved, void * up_saved, void * WdownT, float * down_scales,
+                              void * WgateupT, float * gateup_scales, void * dA);
 
 #ifdef __cplusplus
 }

@@ -201,3 +201,34 @@ def test_swiglu_bwd_quantize_rows(ops, shape, with_factors):
                                       col_factors=None if cf is None else torch.from_numpy(cf).cuda())
     torch.cuda.synchronize()
     _check_codes(Q, sc, q_ref, s_ref, f"swiglu_bwd_quantize_rows {shape}")
+
+
+def test_ffn_through_the_handle(ops):
+    """submit_swiglu_ffn_fp8 / submit_swiglu_ffn_fp8_bwd through the registry (the op keeps its own workspace) give the launcher's bits."""
+    from dataflow_lib_b200 import DataflowHandle
+    T, d, f = 300, 512, 1024
+    A, dOut, res = O.fill_normal(O.BF16, (T, d), 61), O.fill_normal(O.BF16, (T, d), 62), O.fill_normal(O.BF16, (T, d), 63)
+    Wg, sg = _weights(f, d, 64)
+    Wu, su = _weights(f, d, 65)
+    Wd, sd = _weights(d, f, 66)
+    t = lambda a: torch.from_numpy(a).cuda()
+    a_, do_, r_ = to_dev(A, O.BF16), to_dev(dOut, O.BF16), to_dev(res, O.BF16)
+    wg, sg_, wu, su_, wd, sd_ = t(Wg), t(sg), t(Wu), t(su), t(Wd), t(sd)
+    sgu = torch.cat([sg_, su_])
+    WguT, WdT = torch.empty((d, 2 * f), dtype=torch.uint8, device="cuda"), torch.empty((f, d), dtype=torch.uint8, device="cuda")
+    ops.ffn_fp8_prepare_bwd_weights(d, f, wg, wu, wd, WguT, WdT)
+    bf = lambda *s: torch.empty(s, dtype=torch.bfloat16, device="cuda")
+    out0, G0, U0, dA0 = bf(T, d), bf(T, f), bf(T, f), bf(T, d)
+    ops.swiglu_ffn_fp8(T, d, f, a_, wg, sg_, wu, su_, wd, sd_, out0, G0, U0, residual=r_)
+    ops.swiglu_ffn_fp8_bwd(T, d, f, do_, G0, U0, WdT, sd_, WguT, sgu, dA0)
+    h = DataflowHandle(device_id=0, num_streams=1)
+    out1, G1, U1, dA1, out2 = bf(T, d), bf(T, f), bf(T, f), bf(T, d), bf(T, d)
+    assert h.submit_swiglu_ffn_fp8(0, T, d, f, a_, wg, sg_, wu, su_, wd, sd_, out1, residual=r_, gate_save=G1, up_save=U1) == 0
+    assert h.submit_swiglu_ffn_fp8_bwd(0, T, d, f, do_, G1, U1, WdT, sd_, WguT, sgu, dA1) == 0
+    assert h.submit_swiglu_ffn_fp8(0, T, d, f, a_, wg, sg_, wu, su_, wd, sd_, out2) == 0          # no residual, nothing saved
+    assert h.sync_stream(0) == 0
+    torch.cuda.synchronize()
+    assert torch.equal(out0, out1) and torch.equal(G0, G1) and torch.equal(U0, U1) and torch.equal(dA0, dA1)
+    ref, _, _ = O.swiglu_ffn_fp8(A, Wg, sg, Wu, su, Wd, sd)
+    check_lowp(to_host(out2, O.BF16), ref, O.BF16, "swiglu_ffn_fp8 through the handle", rel=2e-2)
+    h.close()
