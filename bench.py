@@ -223,8 +223,13 @@ def other_configs(hbm_peak):
     flops = 6.0 * T4 * D_MODEL * FFN
     ms_f = timed(lambda: ops.swiglu_ffn_fp8(T4, D_MODEL, FFN, A, Wg, sg, Wu, su, Wd, sd, o, G, U))
     ms_b = timed(lambda: ops.swiglu_ffn_fp8_bwd(T4, D_MODEL, FFN, dO, G, U, WdT, sd, WguT, sgu, dA))
+    dGU = torch.empty(T4, 2 * FFN, device="cuda", dtype=torch.bfloat16)
+    ops.swiglu_ffn_fp8_bwd(T4, D_MODEL, FFN, dO, G, U, WdT, sd, WguT, sgu, dA, dgate_dup=dGU)
+    dWg, dWu, dWd = (torch.empty(s_, device="cuda", dtype=torch.bfloat16) for s_ in ((FFN, D_MODEL), (FFN, D_MODEL), (D_MODEL, FFN)))
+    ms_w = timed(lambda: ops.swiglu_ffn_fp8_wgrad(T4, D_MODEL, FFN, A, dO, G, U, dGU, dWg, dWu, dWd))
     out["c4_swiglu_ffn_fp8_16384x4096x14336"] = {"fwd": {"ms": ms_f, "TFLOP/s": flops / ms_f / 1e9}, "bwd_input_grad": {"ms": ms_b, "TFLOP/s": flops / ms_b / 1e9},
-                                                 "tokens_per_s_fwd_bwd": T4 / ((ms_f + ms_b) * 1e-3)}
+                                                 "bwd_weight_grads": {"ms": ms_w, "TFLOP/s": flops / ms_w / 1e9},
+                                                 "tokens_per_s_fwd_bwd": T4 / ((ms_f + ms_b + ms_w) * 1e-3)}
     return out
 
 

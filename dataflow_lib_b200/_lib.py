@@ -39,12 +39,16 @@ KERNEL_ABI = {
     "dfb200_gemm_e4m3": (_i, [_i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
     "dfb200_gemm_e4m3_swiglu": (_i, [_i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
     "dfb200_swiglu_quantize_rows_e4m3": (_i, [_i, _i, _vp, _vp, _vp, _vp, _vp]),
-    "dfb200_swiglu_bwd_quantize_rows_e4m3": (_i, [_i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
+    "dfb200_swiglu_bwd_quantize_rows_e4m3": (_i, [_i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
+    "dfb200_col_amax_bf16": (_i, [_i, _i, _vp, _vp, _vp]),
+    "dfb200_transpose_quantize_e4m3": (_i, [_i, _i, _vp, _vp, _vp, _vp, _vp]),
+    "dfb200_swiglu_ffn_fp8_wgrad_workspace_bytes": (_u64, [_i, _i, _i]),
+    "dfb200_swiglu_ffn_fp8_wgrad": (_i, [_i, _i, _i] + [_vp] * 9 + [_u64, _vp]),
     "dfb200_gemm_e4m3_swiglu_bwd": (_i, [_i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
     "dfb200_swiglu_ffn_fp8_workspace_bytes": (_u64, [_i, _i, _i]),
     "dfb200_swiglu_ffn_fp8": (_i, [_i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _u64, _vp]),
     "dfb200_ffn_fp8_prepare_bwd_weights": (_i, [_i, _i, _vp, _vp, _vp, _vp, _vp, _vp]),
-    "dfb200_swiglu_ffn_fp8_bwd": (_i, [_i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _u64, _vp]),
+    "dfb200_swiglu_ffn_fp8_bwd": (_i, [_i, _i, _i] + [_vp] * 10 + [_u64, _vp]),
     "dfb200_softmax_fp32_out": (_i, [_i, _i, _i, _vp, _vp, _vp, _vp]),
     "dfb200_embedding": (_i, [_i, _i, _i, _vp, _vp, _vp, _vp]),
     "dfb200_copy_to_seq_context": (_i, [_i, _u64, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp]),

@@ -160,6 +160,6 @@ int dataflow_b200_swiglu_ffn_fp8_bwd(Dataflow_Handle * h, int stream_id, Op * op
 	const int T = ARG(op, 0, int), d = ARG(op, 1, int), f = ARG(op, 2, int);
 	if (ensure_workspace(ws, dfb200_swiglu_ffn_fp8_workspace_bytes(T, d, f))) return -1;
 	return finish(dfb200_swiglu_ffn_fp8_bwd(T, d, f, ARG(op, 3, void *), ARG(op, 4, void *), ARG(op, 5, void *), ARG(op, 6, void *), ARG(op, 7, float *),
-	                                        ARG(op, 8, void *), ARG(op, 9, float *), ARG(op, 10, void *), ws->ptr, ws->bytes, stream_of(h, stream_id)),
+	                                        ARG(op, 8, void *), ARG(op, 9, float *), ARG(op, 10, void *), NULL, ws->ptr, ws->bytes, stream_of(h, stream_id)),
 	              "swiglu_ffn_fp8_bwd");
 }

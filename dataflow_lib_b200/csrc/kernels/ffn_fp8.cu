@@ -245,7 +245,7 @@ quantize_rows_e4m3_kernel(int n_rows, int n_cols, const void * __restrict__ X, c
 template <int VPT, bool BWD, bool HAS_MULT>
 __global__ void __launch_bounds__(1024, VPT <= 2 ? 2 : 1)
 swiglu_quantize_rows_kernel(int n_rows, int f, const void * __restrict__ G, const void * __restrict__ U, const void * __restrict__ dH,
-                            const float * __restrict__ col_mult, void * __restrict__ Q, float * __restrict__ scales) {
+                            const float * __restrict__ col_mult, void * __restrict__ Q, float * __restrict__ scales, void * __restrict__ bf16_out) {
 	__shared__ float red[32];
 	const int n_chunks = f / 8, tid = threadIdx.x, nthr = blockDim.x;
 	const int row = blockIdx.x;
@@ -337,7 +337,95 @@ swiglu_quantize_rows_kernel(int n_rows, int f, const void * __restrict__ G, cons
 				#pragma unroll
 				for (int i = 0; i < 8; i++) q[i] = __fmul_rn(x[i], inv);
 				store_elems<e4m3_t, 8>(Q, out_elem + (uint64_t) part * f + (uint64_t) c * 8, q);
+				// the bf16 values themselves (before the column factors), for the weight-gradient pass
+				if (bf16_out) st_words<4>(reinterpret_cast<char *>(bf16_out) + (out_elem + (uint64_t) part * f + (uint64_t) c * 8) * 2, res[v][part]);
 			}
+		}
+	}
+}
+
+// Weight gradients contract over the TOKENS, so their operands are the transposes of activation matrices, quantised with one scale
+// per row of the transpose (= per column of the activation matrix; no scale sits on the contraction index):
+//   col_amax_kernel          amax[c] = max_r |X[r, c]|           (persistent CTAs keep packed running maxima per column chunk in registers
+//                                                                 and merge them with one integer atomicMax per column: order-independent)
+//   transpose_quantize_kernel Qt[c, r] = e4m3( X[r, c] * (448 / amax[c]) ), scale[c] = amax[c] / 448 (1 for an all-zero column);
+//                            128-token x 64-column tiles through shared memory, 128-byte rows of the transpose per store group
+template <int VPT>
+__global__ void __launch_bounds__(1024)
+col_amax_kernel(int n_rows, int n_cols, const void * __restrict__ X, float * amax) {
+	const int n_chunks = n_cols / 8, tid = threadIdx.x, nthr = blockDim.x;
+	__nv_bfloat162 m[VPT][4];
+	#pragma unroll
+	for (int v = 0; v < VPT; v++)
+		#pragma unroll
+		for (int i = 0; i < 4; i++) m[v][i] = __float2bfloat162_rn(0.0f);
+	for (int row = blockIdx.x; row < n_rows; row += gridDim.x) {
+		uint32_t raw[VPT][4];
+		#pragma unroll
+		for (int v = 0; v < VPT; v++) {
+			const int c = tid + v * nthr;
+			if (c < n_chunks) ld_words<4, Hint::STREAM>(reinterpret_cast<const char *>(X) + ((uint64_t) row * n_cols + (uint64_t) c * 8) * 2, raw[v]);
+		}
+		#pragma unroll
+		for (int v = 0; v < VPT; v++) {
+			if (tid + v * nthr < n_chunks) {
+				#pragma unroll
+				for (int i = 0; i < 4; i++) m[v][i] = __hmax2(m[v][i], __habs2(*reinterpret_cast<const __nv_bfloat162 *>(&raw[v][i])));
+			}
+		}
+	}
+	#pragma unroll
+	for (int v = 0; v < VPT; v++) {
+		const int c = tid + v * nthr;
+		if (c < n_chunks) {
+			#pragma unroll
+			for (int i = 0; i < 4; i++) {      // non-negative floats order like their bit patterns
+				atomicMax(reinterpret_cast<unsigned int *>(amax) + c * 8 + 2 * i, __float_as_uint(__low2float(m[v][i])));
+				atomicMax(reinterpret_cast<unsigned int *>(amax) + c * 8 + 2 * i + 1, __float_as_uint(__high2float(m[v][i])));
+			}
+		}
+	}
+}
+
+constexpr int TQ_TOKENS = 128, TQ_COLS = 64, TQ_PITCH = TQ_TOKENS + 4;
+__global__ void __launch_bounds__(256)
+transpose_quantize_kernel(int n_rows, int n_cols, const void * __restrict__ X, const float * __restrict__ amax, uint8_t * __restrict__ Qt,
+                          float * __restrict__ col_scales) {
+	__shared__ __align__(16) uint8_t tile[TQ_COLS][TQ_PITCH];          // [column][token] codes
+	__shared__ float inv[TQ_COLS];
+	const int r0 = blockIdx.y * TQ_TOKENS, c0 = blockIdx.x * TQ_COLS, tid = threadIdx.x;
+	if (tid < TQ_COLS) {
+		const int c = c0 + tid;
+		const float a = c < n_cols ? amax[c] : 0.0f;
+		inv[tid] = a > 0.0f ? __fdiv_rn(448.0f, a) : 1.0f;
+		if (blockIdx.y == 0 && c < n_cols) col_scales[c] = a > 0.0f ? __fdiv_rn(a, 448.0f) : 1.0f;
+	}
+	__syncthreads();
+	// phase 1: 128 tokens x 8 column chunks; 8 consecutive lanes read one 128-byte row segment
+	#pragma unroll
+	for (int k = 0; k < (TQ_TOKENS * TQ_COLS / 8) / 256; k++) {
+		const int item = tid + k * 256, t = item >> 3, ch = item & 7;
+		const int r = r0 + t, c = c0 + ch * 8;
+		float x[8];
+		if (r < n_rows && c < n_cols) load_elems<bf16_t, 8, Hint::STREAM>(X, (uint64_t) r * n_cols + c, x);
+		else { for (int i = 0; i < 8; i++) x[i] = 0.0f; }
+		#pragma unroll
+		for (int i = 0; i < 8; i += 2) {
+			const float q0 = __fmul_rn(x[i], inv[ch * 8 + i]), q1 = __fmul_rn(x[i + 1], inv[ch * 8 + i + 1]);
+			const __nv_fp8x2_storage_t pr = __nv_cvt_float2_to_fp8x2(make_float2(q0, q1), __NV_SATFINITE, __NV_E4M3);
+			tile[ch * 8 + i][t] = (uint8_t) (pr & 0xff);
+			tile[ch * 8 + i + 1][t] = (uint8_t) (pr >> 8);
+		}
+	}
+	__syncthreads();
+	// phase 2: 64 columns x 8 segments of 16 tokens; 8 consecutive lanes write one 128-byte row of the transpose
+	#pragma unroll
+	for (int k = 0; k < (TQ_COLS * TQ_TOKENS / 16) / 256; k++) {
+		const int item = tid + k * 256, cl = item >> 3, seg = item & 7;
+		const int c = c0 + cl, r = r0 + seg * 16;
+		if (c < n_cols && r < n_rows) {                 // n_rows is a multiple of 16
+			const uint32_t * src = reinterpret_cast<const uint32_t *>(&tile[cl][seg * 16]);
+			*reinterpret_cast<uint4 *>(Qt + (uint64_t) c * n_rows + r) = make_uint4(src[0], src[1], src[2], src[3]);
 		}
 	}
 }
@@ -807,13 +895,14 @@ extern "C" int dfb200_quantize_rows_e4m3(int n_rows, int n_cols, const void * X_
 }
 
 static int launch_swiglu_quantize(bool bwd, int n_rows, int f, const void * G, const void * U, const void * dH, const float * col_factors, void * Q,
-                                  float * row_scales, void * stream) {
+                                  float * row_scales, void * bf16_out, void * stream) {
 	const char * op = bwd ? "swiglu_bwd_quantize_rows_e4m3" : "swiglu_quantize_rows_e4m3";
 	if (n_rows < 0 || f <= 0 || f % 8) return set_error(DFB200_ERR_ARG, "%s: bad shape %d x %d (columns must be a multiple of 8)", op, n_rows, f);
 	if (n_rows == 0) return DFB200_OK;
 	if (!G || !U || (bwd && !dH) || !Q || !row_scales || !aligned16(G) || !aligned16(U) || !aligned16(dH) || !aligned16(Q) || (f % 16 && bwd))
 		return set_error(DFB200_ERR_ARG, "%s: NULL or misaligned tensor", op);
 	if (col_factors && (reinterpret_cast<uintptr_t>(col_factors) & 15u)) return set_error(DFB200_ERR_ARG, "%s: col_factors must be 16-byte aligned", op);
+	if (!aligned16(bf16_out)) return set_error(DFB200_ERR_ARG, "%s: the bf16 output must be 16-byte aligned", op);
 	const int n_chunks = f / 8;
 	if (n_chunks > 1024 * 4) return set_error(DFB200_ERR_ARG, "%s: f = %d exceeds the supported maximum of %d", op, f, 1024 * 4 * 8);
 	int vpt = n_chunks >= 512 ? 2 : 1;
@@ -821,9 +910,9 @@ static int launch_swiglu_quantize(bool bwd, int n_rows, int f, const void * G, c
 	const int threads = ((n_chunks + vpt - 1) / vpt + 31) / 32 * 32;
 	cudaStream_t s = (cudaStream_t) stream;
 #define DFB200_SQ_CASE(V) \
-	if (bwd && col_factors) swiglu_quantize_rows_kernel<V, true, true><<<n_rows, threads, 0, s>>>(n_rows, f, G, U, dH, col_factors, Q, row_scales); \
-	else if (bwd) swiglu_quantize_rows_kernel<V, true, false><<<n_rows, threads, 0, s>>>(n_rows, f, G, U, dH, col_factors, Q, row_scales); \
-	else swiglu_quantize_rows_kernel<V, false, false><<<n_rows, threads, 0, s>>>(n_rows, f, G, U, dH, col_factors, Q, row_scales)
+	if (bwd && col_factors) swiglu_quantize_rows_kernel<V, true, true><<<n_rows, threads, 0, s>>>(n_rows, f, G, U, dH, col_factors, Q, row_scales, bf16_out); \
+	else if (bwd) swiglu_quantize_rows_kernel<V, true, false><<<n_rows, threads, 0, s>>>(n_rows, f, G, U, dH, col_factors, Q, row_scales, bf16_out); \
+	else swiglu_quantize_rows_kernel<V, false, false><<<n_rows, threads, 0, s>>>(n_rows, f, G, U, dH, col_factors, Q, row_scales, bf16_out)
 	switch (vpt) {
 		case 1: DFB200_SQ_CASE(1); break;
 		case 2: DFB200_SQ_CASE(2); break;
@@ -835,12 +924,46 @@ static int launch_swiglu_quantize(bool bwd, int n_rows, int f, const void * G, c
 
 extern "C" int dfb200_swiglu_quantize_rows_e4m3(int n_rows, int f, const void * gate_bf16, const void * up_bf16, void * Q_e4m3, float * row_scales,
                                                 void * stream) {
-	return launch_swiglu_quantize(false, n_rows, f, gate_bf16, up_bf16, nullptr, nullptr, Q_e4m3, row_scales, stream);
+	return launch_swiglu_quantize(false, n_rows, f, gate_bf16, up_bf16, nullptr, nullptr, Q_e4m3, row_scales, nullptr, stream);
 }
 
 extern "C" int dfb200_swiglu_bwd_quantize_rows_e4m3(int n_rows, int f, const void * gate_bf16, const void * up_bf16, const void * dH_bf16,
-                                                    const float * col_factors, void * Q_e4m3, float * row_scales, void * stream) {
-	return launch_swiglu_quantize(true, n_rows, f, gate_bf16, up_bf16, dH_bf16, col_factors, Q_e4m3, row_scales, stream);
+                                                    const float * col_factors, void * Q_e4m3, float * row_scales, void * dgate_dup_bf16, void * stream) {
+	return launch_swiglu_quantize(true, n_rows, f, gate_bf16, up_bf16, dH_bf16, col_factors, Q_e4m3, row_scales, dgate_dup_bf16, stream);
+}
+
+extern "C" int dfb200_col_amax_bf16(int n_rows, int n_cols, const void * X_bf16, float * col_amax, void * stream) {
+	if (n_rows <= 0 || n_cols <= 0 || n_cols % 8) return set_error(DFB200_ERR_ARG, "col_amax_bf16: bad shape %d x %d (columns must be a multiple of 8)", n_rows, n_cols);
+	if (!X_bf16 || !col_amax || !aligned16(X_bf16) || (reinterpret_cast<uintptr_t>(col_amax) & 3u)) return set_error(DFB200_ERR_ARG, "col_amax_bf16: NULL or misaligned tensor");
+	const int n_chunks = n_cols / 8;
+	if (n_chunks > 1024 * 4) return set_error(DFB200_ERR_ARG, "col_amax_bf16: n_cols = %d exceeds the supported maximum of %d", n_cols, 1024 * 4 * 8);
+	cudaStream_t s = (cudaStream_t) stream;
+	cudaError_t e = cudaMemsetAsync(col_amax, 0, (size_t) n_cols * sizeof(float), s);
+	if (e != cudaSuccess) { cudaGetLastError(); return set_error(DFB200_ERR_CUDA, "col_amax_bf16: %s", cudaGetErrorString(e)); }
+	int vpt = 1;
+	while (vpt < 4 && (n_chunks + vpt - 1) / vpt > 1024) vpt *= 2;
+	const int threads = ((n_chunks + vpt - 1) / vpt + 31) / 32 * 32;
+	const int per_sm = 2048 / threads < 1 ? 1 : 2048 / threads;
+	long long grid = (long long) sm_count() * per_sm;
+	if (grid > n_rows) grid = n_rows;
+	switch (vpt) {
+		case 1: col_amax_kernel<1><<<(int) grid, threads, 0, s>>>(n_rows, n_cols, X_bf16, col_amax); break;
+		case 2: col_amax_kernel<2><<<(int) grid, threads, 0, s>>>(n_rows, n_cols, X_bf16, col_amax); break;
+		default: col_amax_kernel<4><<<(int) grid, threads, 0, s>>>(n_rows, n_cols, X_bf16, col_amax); break;
+	}
+	return check_launch("col_amax_bf16");
+}
+
+extern "C" int dfb200_transpose_quantize_e4m3(int n_rows, int n_cols, const void * X_bf16, const float * col_amax, void * Qt_e4m3, float * col_scales,
+                                              void * stream) {
+	if (n_rows <= 0 || n_cols <= 0 || n_cols % 8 || n_rows % 16)
+		return set_error(DFB200_ERR_ARG, "transpose_quantize_e4m3: bad shape %d x %d (rows a multiple of 16, columns of 8)", n_rows, n_cols);
+	if (!X_bf16 || !col_amax || !Qt_e4m3 || !col_scales || !aligned16(X_bf16) || !aligned16(Qt_e4m3))
+		return set_error(DFB200_ERR_ARG, "transpose_quantize_e4m3: NULL or misaligned tensor");
+	dim3 grid((n_cols + TQ_COLS - 1) / TQ_COLS, (n_rows + TQ_TOKENS - 1) / TQ_TOKENS);
+	if (grid.y > 65535) return set_error(DFB200_ERR_ARG, "transpose_quantize_e4m3: too many rows");
+	transpose_quantize_kernel<<<grid, 256, 0, (cudaStream_t) stream>>>(n_rows, n_cols, X_bf16, col_amax, static_cast<uint8_t *>(Qt_e4m3), col_scales);
+	return check_launch("transpose_quantize_e4m3");
 }
 
 extern "C" int dfb200_transpose_bytes(int rows, int cols, const void * in, int ld_in, void * out, int ld_out, void * stream) {
@@ -928,7 +1051,7 @@ extern "C" int dfb200_ffn_fp8_prepare_bwd_weights(int d, int f, const void * Wga
 // gateup_scales is the concatenation [gate_scales | up_scales] (2f floats, 16-byte aligned). Weight gradients are not computed here.
 extern "C" int dfb200_swiglu_ffn_fp8_bwd(int T, int d, int f, const void * dOut_bf16, const void * gate_saved_bf16, const void * up_saved_bf16,
                                          const void * WdownT, const float * down_scales, const void * WgateupT, const float * gateup_scales,
-                                         void * dA_bf16, void * workspace, uint64_t workspace_bytes, void * stream) {
+                                         void * dA_bf16, void * dgate_dup_bf16, void * workspace, uint64_t workspace_bytes, void * stream) {
 	if (T <= 0 || d <= 0 || f <= 0 || d % 16 || f % 16) return set_error(DFB200_ERR_ARG, "swiglu_ffn_fp8_bwd: bad shape (T %d, d %d, f %d; d and f multiples of 16)", T, d, f);
 	const uint64_t need = dfb200_swiglu_ffn_fp8_workspace_bytes(T, d, f);
 	if (!workspace || workspace_bytes < need || !aligned16(workspace))
@@ -942,7 +1065,51 @@ extern "C" int dfb200_swiglu_ffn_fp8_bwd(int T, int d, int f, const void * dOut_
 	float * s2 = reinterpret_cast<float *>(take((uint64_t) T * 4));
 	int rc = dfb200_quantize_rows_e4m3(T, d, dOut_bf16, down_scales, dOq, s1, stream);
 	if (!rc) rc = dfb200_gemm_e4m3(T, f, d, dOq, s1, WdownT, nullptr, nullptr, dH, stream);
-	if (!rc) rc = dfb200_swiglu_bwd_quantize_rows_e4m3(T, f, gate_saved_bf16, up_saved_bf16, dH, gateup_scales, dGUq, s2, stream);
+	if (!rc) rc = dfb200_swiglu_bwd_quantize_rows_e4m3(T, f, gate_saved_bf16, up_saved_bf16, dH, gateup_scales, dGUq, s2, dgate_dup_bf16, stream);
 	if (!rc) rc = dfb200_gemm_e4m3(T, d, 2 * f, dGUq, s2, WgateupT, nullptr, nullptr, dA_bf16, stream);
+	return rc;
+}
+
+// Weight gradients of the FFN (bf16), from the forward input A, the output gradient, the saved pre-activations and the gate|up
+// gradients [T, 2f] that dfb200_swiglu_ffn_fp8_bwd stores on request:
+//   dWdown[d, f] = dOut^T H,  H = bf16(silu(g) u);   dWgate[f, d] = dG^T A;   dWup[f, d] = dU^T A
+// Each operand is transposed and quantised to e4m3 with one scale per row of the transpose (col_amax + transpose_quantize), so the
+// three GEMMs (reduction over the T tokens) are the plain kernel with both scales on output indices.
+extern "C" uint64_t dfb200_swiglu_ffn_fp8_wgrad_workspace_bytes(int T, int d, int f) {
+	return align256((uint64_t) T * f * 2)                                              // H bf16
+	     + 2 * align256((uint64_t) T * d) + align256((uint64_t) T * f) + align256((uint64_t) T * f * 2)   // dOut^T, A^T, H^T, [dG | dU]^T codes
+	     + 2 * (2 * align256((uint64_t) d * 4) + align256((uint64_t) f * 4) + align256((uint64_t) f * 8));   // column maxima and scales of the four
+}
+
+extern "C" int dfb200_swiglu_ffn_fp8_wgrad(int T, int d, int f, const void * A_bf16, const void * dOut_bf16, const void * gate_saved_bf16,
+                                           const void * up_saved_bf16, const void * dgate_dup_bf16, void * dWgate_bf16, void * dWup_bf16,
+                                           void * dWdown_bf16, void * workspace, uint64_t workspace_bytes, void * stream) {
+	if (T <= 0 || d <= 0 || f <= 0 || d % 16 || f % 16 || T % 16)
+		return set_error(DFB200_ERR_ARG, "swiglu_ffn_fp8_wgrad: bad shape (T %d, d %d, f %d; all multiples of 16)", T, d, f);
+	if (!A_bf16 || !dOut_bf16 || !gate_saved_bf16 || !up_saved_bf16 || !dgate_dup_bf16 || !dWgate_bf16 || !dWup_bf16 || !dWdown_bf16)
+		return set_error(DFB200_ERR_ARG, "swiglu_ffn_fp8_wgrad: NULL tensor argument");
+	const uint64_t need = dfb200_swiglu_ffn_fp8_wgrad_workspace_bytes(T, d, f);
+	if (!workspace || workspace_bytes < need || !aligned16(workspace))
+		return set_error(DFB200_ERR_WORKSPACE, "swiglu_ffn_fp8_wgrad: needs %llu bytes of 16-byte aligned workspace, got %llu", (unsigned long long) need, (unsigned long long) workspace_bytes);
+	uint8_t * p = static_cast<uint8_t *>(workspace);
+	auto take = [&](uint64_t bytes) { uint8_t * q = p; p += align256(bytes); return q; };
+	void * H = take((uint64_t) T * f * 2);
+	void * dOt = take((uint64_t) T * d);  void * At = take((uint64_t) T * d);  void * Ht = take((uint64_t) T * f);  uint8_t * dGUt = take((uint64_t) T * f * 2);
+	float * m_do = reinterpret_cast<float *>(take((uint64_t) d * 4)), * s_do = reinterpret_cast<float *>(take((uint64_t) d * 4));
+	float * m_a = reinterpret_cast<float *>(take((uint64_t) d * 4)),  * s_a = reinterpret_cast<float *>(take((uint64_t) d * 4));
+	float * m_h = reinterpret_cast<float *>(take((uint64_t) f * 4)),  * s_h = reinterpret_cast<float *>(take((uint64_t) f * 4));
+	float * m_gu = reinterpret_cast<float *>(take((uint64_t) f * 8)), * s_gu = reinterpret_cast<float *>(take((uint64_t) f * 8));
+	int rc = dfb200_swiglu(DATAFLOW_BF16, T, f, gate_saved_bf16, up_saved_bf16, H, stream);
+	auto transposed = [&](int cols, const void * X, float * m, void * Qt, float * sc) {
+		if (!rc) rc = dfb200_col_amax_bf16(T, cols, X, m, stream);
+		if (!rc) rc = dfb200_transpose_quantize_e4m3(T, cols, X, m, Qt, sc, stream);
+	};
+	transposed(d, dOut_bf16, m_do, dOt, s_do);
+	transposed(d, A_bf16, m_a, At, s_a);
+	transposed(f, H, m_h, Ht, s_h);
+	transposed(2 * f, dgate_dup_bf16, m_gu, dGUt, s_gu);
+	if (!rc) rc = dfb200_gemm_e4m3(d, f, T, dOt, s_do, Ht, s_h, nullptr, dWdown_bf16, stream);
+	if (!rc) rc = dfb200_gemm_e4m3(f, d, T, dGUt, s_gu, At, s_a, nullptr, dWgate_bf16, stream);
+	if (!rc) rc = dfb200_gemm_e4m3(f, d, T, dGUt + (uint64_t) f * T, s_gu + f, At, s_a, nullptr, dWup_bf16, stream);
 	return rc;
 }

@@ -150,9 +150,18 @@ def swiglu_quantize_rows_e4m3(n_rows, f, gate, up, Q, row_scales, stream=None):
     _check(_lib_.dfb200_swiglu_quantize_rows_e4m3(n_rows, f, _ptr(gate), _ptr(up), _ptr(Q), _ptr(row_scales), _stream(stream)), "swiglu_quantize_rows_e4m3")
 
 
-def swiglu_bwd_quantize_rows_e4m3(n_rows, f, gate, up, dH, Q, row_scales, col_factors=None, stream=None):
+def swiglu_bwd_quantize_rows_e4m3(n_rows, f, gate, up, dH, Q, row_scales, col_factors=None, dgate_dup=None, stream=None):
     _check(_lib_.dfb200_swiglu_bwd_quantize_rows_e4m3(n_rows, f, _ptr(gate), _ptr(up), _ptr(dH), _ptr(col_factors), _ptr(Q), _ptr(row_scales),
-                                                      _stream(stream)), "swiglu_bwd_quantize_rows_e4m3")
+                                                      _ptr(dgate_dup), _stream(stream)), "swiglu_bwd_quantize_rows_e4m3")
+
+
+def col_amax_bf16(n_rows, n_cols, X, col_amax, stream=None):
+    _check(_lib_.dfb200_col_amax_bf16(n_rows, n_cols, _ptr(X), _ptr(col_amax), _stream(stream)), "col_amax_bf16")
+
+
+def transpose_quantize_e4m3(n_rows, n_cols, X, col_amax, Qt, col_scales, stream=None):
+    _check(_lib_.dfb200_transpose_quantize_e4m3(n_rows, n_cols, _ptr(X), _ptr(col_amax), _ptr(Qt), _ptr(col_scales), _stream(stream)),
+           "transpose_quantize_e4m3")
 
 
 def gemm_e4m3(M, N, K, A, a_row_scales, W, w_scales, out, residual=None, stream=None):
@@ -183,8 +192,17 @@ def ffn_fp8_prepare_bwd_weights(d, f, Wgate, Wup, Wdown, WgateupT, WdownT, strea
            "ffn_fp8_prepare_bwd_weights")
 
 
-def swiglu_ffn_fp8_bwd(T, d, f, dOut, gate_saved, up_saved, WdownT, down_scales, WgateupT, gateup_scales, dA, stream=None, workspace=None):
+def swiglu_ffn_fp8_bwd(T, d, f, dOut, gate_saved, up_saved, WdownT, down_scales, WgateupT, gateup_scales, dA, dgate_dup=None, stream=None,
+                       workspace=None):
     need = _lib_.dfb200_swiglu_ffn_fp8_workspace_bytes(T, d, f)
     ws = workspace if workspace is not None else _workspace(dOut.device, need)
     _check(_lib_.dfb200_swiglu_ffn_fp8_bwd(T, d, f, _ptr(dOut), _ptr(gate_saved), _ptr(up_saved), _ptr(WdownT), _ptr(down_scales), _ptr(WgateupT),
-                                           _ptr(gateup_scales), _ptr(dA), _ptr(ws), ws.numel() * ws.element_size(), _stream(stream)), "swiglu_ffn_fp8_bwd")
+                                           _ptr(gateup_scales), _ptr(dA), _ptr(dgate_dup), _ptr(ws), ws.numel() * ws.element_size(), _stream(stream)),
+           "swiglu_ffn_fp8_bwd")
+
+
+def swiglu_ffn_fp8_wgrad(T, d, f, A, dOut, gate_saved, up_saved, dgate_dup, dWgate, dWup, dWdown, stream=None, workspace=None):
+    need = _lib_.dfb200_swiglu_ffn_fp8_wgrad_workspace_bytes(T, d, f)
+    ws = workspace if workspace is not None else _workspace(A.device, need)
+    _check(_lib_.dfb200_swiglu_ffn_fp8_wgrad(T, d, f, _ptr(A), _ptr(dOut), _ptr(gate_saved), _ptr(up_saved), _ptr(dgate_dup), _ptr(dWgate), _ptr(dWup),
+                                             _ptr(dWdown), _ptr(ws), ws.numel() * ws.element_size(), _stream(stream)), "swiglu_ffn_fp8_wgrad")

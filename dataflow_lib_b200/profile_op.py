@@ -17,7 +17,8 @@ D, NH, NKV, HD, F, V = 4096, 32, 8, 128, 14336, 128256
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("op", choices=["rms_norm", "rms_norm_bwd_x", "rms_norm_bwd_w", "rope", "rope_bwd_x", "swiglu", "swiglu_bwd_x",
-                                   "softmax", "softmax_cross_entropy", "swiglu_ffn_fp8", "swiglu_ffn_fp8_bwd", "gemm_e4m3_swiglu", "gemm_e4m3", "fp8_peak"])
+                                   "softmax", "softmax_cross_entropy", "swiglu_ffn_fp8", "swiglu_ffn_fp8_bwd", "swiglu_ffn_fp8_wgrad", "gemm_e4m3_swiglu", "gemm_e4m3",
+                                   "fp8_peak"])
     ap.add_argument("--tokens", type=int, default=2048)
     ap.add_argument("--iters", type=int, default=3)
     ap.add_argument("--dtype", default="bf16", choices=["bf16", "fp16", "fp32"])
@@ -57,7 +58,7 @@ def main():
             ms = e0.elapsed_time(e1) / a.iters
             print(f"fp8_peak sustained: library e4m3 GEMM {m}x{n}x{k} ({name}), {a.iters} back to back: {ms * 1e3:.1f} us, {2 * m * n * k / (ms * 1e-3) / 1e12:.0f} TFLOP/s")
         return
-    if a.op in ("swiglu_ffn_fp8", "swiglu_ffn_fp8_bwd", "gemm_e4m3_swiglu", "gemm_e4m3"):
+    if a.op in ("swiglu_ffn_fp8", "swiglu_ffn_fp8_bwd", "swiglu_ffn_fp8_wgrad", "gemm_e4m3_swiglu", "gemm_e4m3"):
         def qw(n_out, n_in):
             W = 0.02 * torch.randn(n_out, n_in, device="cuda", generator=g)
             sc = W.abs().amax(1) / 448.0
@@ -77,11 +78,15 @@ def main():
         ops.ffn_fp8_prepare_bwd_weights(D, F, Wg, Wu, Wd, WguT, WdT)
         ops.swiglu_ffn_fp8(T, D, F, A, Wg, sg, Wu, su, Wd, sd, out, G, U)
         dOut, dA, sgu = rn(T, D), torch.empty(T, D, device="cuda", dtype=torch.bfloat16), torch.cat([sg, su])
+        dGU = torch.empty(T, 2 * F, device="cuda", dtype=torch.bfloat16)
+        ops.swiglu_ffn_fp8_bwd(T, D, F, dOut, G, U, WdT, sd, WguT, sgu, dA, dgate_dup=dGU)
+        dWg, dWu, dWd = (torch.empty(s_, device="cuda", dtype=torch.bfloat16) for s_ in ((F, D), (F, D), (D, F)))
         fn = {"swiglu_ffn_fp8": lambda: ops.swiglu_ffn_fp8(T, D, F, A, Wg, sg, Wu, su, Wd, sd, out, G, U),
               "swiglu_ffn_fp8_bwd": lambda: ops.swiglu_ffn_fp8_bwd(T, D, F, dOut, G, U, WdT, sd, WguT, sgu, dA),
+              "swiglu_ffn_fp8_wgrad": lambda: ops.swiglu_ffn_fp8_wgrad(T, D, F, A, dOut, G, U, dGU, dWg, dWu, dWd),
               "gemm_e4m3_swiglu": lambda: ops.gemm_e4m3_swiglu(T, F, D, Aq, sa, Wg, sg, Wu, su, H),
               "gemm_e4m3": lambda: ops.gemm_e4m3(T, D, F, Hq, sh, Wd, sd, out)}[a.op]
-        flops = {"swiglu_ffn_fp8": 6.0, "swiglu_ffn_fp8_bwd": 6.0, "gemm_e4m3_swiglu": 4.0, "gemm_e4m3": 2.0}[a.op] * T * D * F
+        flops = {"swiglu_ffn_fp8": 6.0, "swiglu_ffn_fp8_bwd": 6.0, "swiglu_ffn_fp8_wgrad": 6.0, "gemm_e4m3_swiglu": 4.0, "gemm_e4m3": 2.0}[a.op] * T * D * F
         fn()
         torch.cuda.synchronize()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)

@@ -143,7 +143,7 @@ int dfb200_softmax_cross_entropy(int fwd_dt, int bwd_dt, int n_rows, int n_cols,
  *   dfb200_gemm_e4m3_swiglu_bwd  dh = (sum_k dOut[m,k] WdownT[n,k]) * row_scale[m]; [dG | dU][m, n and N+n] from dh and the saved g, u
  *   dfb200_swiglu_ffn_fp8        out = down(swiglu(gate(A), up(A))) + residual (optional);  dfb200_swiglu_ffn_fp8_bwd: dA from dOut and the saved g, u
  *   dfb200_ffn_fp8_prepare_bwd_weights  WgateupT [d, 2f] = [Wgate^T | Wup^T], WdownT [f, d] = Wdown^T (codes only)
- * Both FFN calls take dfb200_swiglu_ffn_fp8_workspace_bytes() bytes of scratch from the caller. Weight gradients are not computed.
+ * Both FFN calls take dfb200_swiglu_ffn_fp8_workspace_bytes() bytes of scratch from the caller; weight gradients: dfb200_swiglu_ffn_fp8_wgrad.
  * Shapes: reduction lengths multiples of 16, N a multiple of 8, 16-byte aligned tensors, row length of a quantised matrix <= 32768. */
 int dfb200_quantize_rows_e4m3(int n_rows, int n_cols, const void * X_bf16, const float * col_factors, void * Q_e4m3, float * row_scales, void * stream);
 int dfb200_transpose_bytes(int rows, int cols, const void * in, int ld_in, void * out, int ld_out, void * stream);
@@ -158,7 +158,14 @@ int dfb200_gemm_e4m3_swiglu(int M, int N, int K, const void * A_e4m3, const floa
  *                                         (arithmetic of dfb200_swiglu_bwd_x; col_factors may be NULL, else 16-byte aligned) */
 int dfb200_swiglu_quantize_rows_e4m3(int n_rows, int f, const void * gate_bf16, const void * up_bf16, void * Q_e4m3, float * row_scales, void * stream);
 int dfb200_swiglu_bwd_quantize_rows_e4m3(int n_rows, int f, const void * gate_bf16, const void * up_bf16, const void * dH_bf16,
-                                         const float * col_factors, void * Q_e4m3, float * row_scales, void * stream);
+                                         const float * col_factors, void * Q_e4m3, float * row_scales, void * dgate_dup_bf16 /* [n_rows, 2f] or NULL */,
+                                         void * stream);
+/* Operands of the weight-gradient GEMMs (reduction over the rows): the transpose, quantised with one scale per row of the transpose.
+ *   dfb200_col_amax_bf16            col_amax[c] = max_r |X[r, c]|
+ *   dfb200_transpose_quantize_e4m3  Qt[c, r] = e4m3( X[r, c] * 448 / col_amax[c] ), col_scales[c] = col_amax[c] / 448 (1 for an all-zero column);
+ *                                   n_rows a multiple of 16, n_cols of 8 */
+int dfb200_col_amax_bf16(int n_rows, int n_cols, const void * X_bf16, float * col_amax, void * stream);
+int dfb200_transpose_quantize_e4m3(int n_rows, int n_cols, const void * X_bf16, const float * col_amax, void * Qt_e4m3, float * col_scales, void * stream);
 int dfb200_gemm_e4m3_swiglu_bwd(int M, int N, int K, const void * dOut_e4m3, const float * dout_row_scales, const void * WdownT_e4m3,
                                 const void * gate_saved_bf16, const void * up_saved_bf16, void * dgate_dup_bf16, void * stream);
 uint64_t dfb200_swiglu_ffn_fp8_workspace_bytes(int T, int d, int f);
@@ -169,7 +176,14 @@ int dfb200_ffn_fp8_prepare_bwd_weights(int d, int f, const void * Wgate, const v
                                        void * stream);
 int dfb200_swiglu_ffn_fp8_bwd(int T, int d, int f, const void * dOut_bf16, const void * gate_saved_bf16, const void * up_saved_bf16,
                               const void * WdownT, const float * down_scales, const void * WgateupT, const float * gateup_scales,
-                              void * dA_bf16, void * workspace, uint64_t workspace_bytes, void * stream);
+                              void * dA_bf16, void * dgate_dup_bf16 /* [T, 2f] kept for the weight gradients, or NULL */,
+                              void * workspace, uint64_t workspace_bytes, void * stream);
+/* Weight gradients (bf16): dWdown[d, f] = dOut^T H, dWgate[f, d] = dG^T A, dWup[f, d] = dU^T A, with H = bf16(silu(g) u) recomputed and
+ * [dG | dU] = the dgate_dup_bf16 output of dfb200_swiglu_ffn_fp8_bwd. T, d, f multiples of 16. */
+uint64_t dfb200_swiglu_ffn_fp8_wgrad_workspace_bytes(int T, int d, int f);
+int dfb200_swiglu_ffn_fp8_wgrad(int T, int d, int f, const void * A_bf16, const void * dOut_bf16, const void * gate_saved_bf16,
+                                const void * up_saved_bf16, const void * dgate_dup_bf16, void * dWgate_bf16, void * dWup_bf16, void * dWdown_bf16,
+                                void * workspace, uint64_t workspace_bytes, void * stream);
 
 /* Softmax of fp16 / bf16 rows into fp32 probabilities plus the index of each row's maximum: replaces softmax_fp16_fp32_kernel and
  * softmax_bf16_fp32_kernel (src/ops/nvidia/loss/softmax.cu:965-1249). Scratch roundings are in the input type as in the reference,

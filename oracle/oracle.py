@@ -220,6 +220,28 @@ def swiglu_ffn_fp8_bwd(dOut_bf16, g, u, Wg, sg, Wu, su, Wd, sd, threads=None):
     return gemm_e4m3(dGUq, s2, WguT, None, threads)
 
 
+def transpose_quantize_e4m3(X_bf16):
+    """Column-wise quantisation of X [rows, cols] and its transpose: returns (codes uint8 [cols, rows], scales fp32 [cols], amax fp32 [cols])
+    with codes = e4m3(x * (448 / amax_col)) and scale = amax_col / 448 (1 for an all-zero column), all in fp32 arithmetic."""
+    Xf = to_f32(np.ascontiguousarray(X_bf16), BF16)
+    amax = np.abs(Xf).max(0).astype(np.float32)
+    pos = amax > 0
+    inv = np.where(pos, np.float32(448.0) / np.where(pos, amax, np.float32(1)), np.float32(1)).astype(np.float32)
+    q = from_f32(np.ascontiguousarray((Xf * inv[None, :]).astype(np.float32)), E4M3)
+    return np.ascontiguousarray(q.T), np.where(pos, amax / np.float32(448.0), np.float32(1)).astype(np.float32), amax
+
+
+def swiglu_ffn_fp8_wgrad(A_bf16, dOut_bf16, g, u, dGU_bf16, threads=None):
+    """Weight gradients of the FFN (dfb200_swiglu_ffn_fp8_wgrad): returns (dWgate [f, d], dWup [f, d], dWdown [d, f]) in bf16."""
+    f = g.shape[1]
+    H = swiglu(BF16, g, u, threads)
+    (dOt, s_do, _), (At, s_a, _), (Ht, s_h, _), (dGUt, s_gu, _) = (transpose_quantize_e4m3(X) for X in (dOut_bf16, A_bf16, H, dGU_bf16))
+    dWd = gemm_e4m3(dOt, s_do, Ht, s_h, threads)
+    dWg = gemm_e4m3(np.ascontiguousarray(dGUt[:f]), s_gu[:f].copy(), At, s_a, threads)
+    dWu = gemm_e4m3(np.ascontiguousarray(dGUt[f:]), s_gu[f:].copy(), At, s_a, threads)
+    return dWg, dWu, dWd
+
+
 def embedding(dt, token_ids, table):
     out = np.empty((len(token_ids), table.shape[1]), table.dtype)
     _lib.oracle_embedding(dt, len(token_ids), table.shape[1], _p(np.ascontiguousarray(token_ids, np.uint32)), _p(table), _p(out))

@@ -232,3 +232,71 @@ def test_ffn_through_the_handle(ops):
     ref, _, _ = O.swiglu_ffn_fp8(A, Wg, sg, Wu, su, Wd, sd)
     check_lowp(to_host(out2, O.BF16), ref, O.BF16, "swiglu_ffn_fp8 through the handle", rel=2e-2)
     h.close()
+
+
+@pytest.mark.parametrize("shape", [(256, 512), (144, 1000), (16, 8), (1024, 14336), (2064, 72)], ids=str)
+def test_col_amax_and_transpose_quantize(ops, shape):
+    T, C_ = shape
+    X = O.fill_normal(O.BF16, shape, 71)
+    X[:, 0] = 0                                            # an all-zero column keeps scale 1
+    qt_ref, s_ref, amax_ref = O.transpose_quantize_e4m3(X)
+    x_d = to_dev(X, O.BF16)
+    amax = torch.full((C_,), -1.0, device="cuda")
+    ops.col_amax_bf16(T, C_, x_d, amax)
+    Qt, sc = torch.full((C_, T), 0xAA, dtype=torch.uint8, device="cuda"), torch.empty(C_, device="cuda")
+    ops.transpose_quantize_e4m3(T, C_, x_d, amax, Qt, sc)
+    torch.cuda.synchronize()
+    assert np.array_equal(amax.cpu().numpy(), amax_ref)
+    assert np.array_equal(sc.cpu().numpy(), s_ref)
+    assert np.array_equal(Qt.cpu().numpy(), qt_ref)
+
+
+def test_swiglu_ffn_fp8_wgrad(ops):
+    T, d, f = 512, 256, 768
+    A, dOut = O.fill_normal(O.BF16, (T, d), 81), O.fill_normal(O.BF16, (T, d), 82)
+    Wg, sg = _weights(f, d, 83)
+    Wu, su = _weights(f, d, 84)
+    Wd, sd = _weights(d, f, 85)
+    _, g, u = O.swiglu_ffn_fp8(A, Wg, sg, Wu, su, Wd, sd)
+    # the gate|up gradients the backward pass hands to the weight-gradient pass, from the oracle's pieces
+    dOq, s1 = O.quantize_rows_e4m3(dOut, sd)
+    dH = O.gemm_e4m3(dOq, s1, np.ascontiguousarray(Wd.T), None)
+    dg, du = O.swiglu_bwd_x(O.BF16, O.BF16, g, u, dH)
+    dGU = np.ascontiguousarray(np.concatenate([dg, du], axis=1))
+    ref_g, ref_u, ref_d = O.swiglu_ffn_fp8_wgrad(A, dOut, g, u, dGU)
+    bf = lambda *s: torch.full(s, float("nan"), dtype=torch.bfloat16, device="cuda")
+    dWg, dWu, dWd = bf(f, d), bf(f, d), bf(d, f)
+    ops.swiglu_ffn_fp8_wgrad(T, d, f, to_dev(A, O.BF16), to_dev(dOut, O.BF16), to_dev(g, O.BF16), to_dev(u, O.BF16), to_dev(dGU, O.BF16), dWg, dWu, dWd)
+    torch.cuda.synchronize()
+    # H is recomputed on the device with the approximate exponential: a one-ulp bf16 difference can move a code, hence 2e-2
+    check_lowp(to_host(dWd, O.BF16), ref_d, O.BF16, "dWdown", rel=2e-2)
+    check_lowp(to_host(dWg, O.BF16), ref_g, O.BF16, "dWgate", rel=2e-2)
+    check_lowp(to_host(dWu, O.BF16), ref_u, O.BF16, "dWup", rel=2e-2)
+    # against fp64 autograd of the dequantised-weight FFN the fp8 operands cost a few per cent of the gradient's scale
+    a64 = torch.tensor(f32(A, O.BF16), dtype=torch.float64)
+    wg, wu, wd = (torch.tensor(f32(W, O.E4M3) * s[:, None], dtype=torch.float64, requires_grad=True) for W, s in ((Wg, sg), (Wu, su), (Wd, sd)))
+    ((torch.nn.functional.silu(a64 @ wg.T) * (a64 @ wu.T)) @ wd.T).backward(torch.tensor(f32(dOut, O.BF16), dtype=torch.float64))
+    for name, got, full in (("dWgate", dWg, wg.grad), ("dWup", dWu, wu.grad), ("dWdown", dWd, wd.grad)):
+        full = full.numpy()
+        err = np.sqrt(((f32(to_host(got, O.BF16), O.BF16) - full) ** 2).mean()) / np.sqrt((full ** 2).mean())
+        assert err < 0.1, (name, err)
+
+
+def test_ffn_bwd_stores_gate_up_gradients(ops):
+    T, d, f = 128, 256, 512
+    dOut = O.fill_normal(O.BF16, (T, d), 91)
+    g, u = O.fill_normal(O.BF16, (T, f), 92), O.fill_normal(O.BF16, (T, f), 93)
+    Wg, sg = _weights(f, d, 94)
+    Wu, su = _weights(f, d, 95)
+    Wd, sd = _weights(d, f, 96)
+    t = lambda a: torch.from_numpy(a).cuda()
+    WguT, WdT = torch.empty((d, 2 * f), dtype=torch.uint8, device="cuda"), torch.empty((f, d), dtype=torch.uint8, device="cuda")
+    ops.ffn_fp8_prepare_bwd_weights(d, f, t(Wg), t(Wu), t(Wd), WguT, WdT)
+    dA = torch.empty((T, d), dtype=torch.bfloat16, device="cuda")
+    dGU = torch.full((T, 2 * f), float("nan"), dtype=torch.bfloat16, device="cuda")
+    ops.swiglu_ffn_fp8_bwd(T, d, f, to_dev(dOut, O.BF16), to_dev(g, O.BF16), to_dev(u, O.BF16), WdT, t(sd), WguT, t(np.concatenate([sg, su])), dA, dgate_dup=dGU)
+    torch.cuda.synchronize()
+    dOq, s1 = O.quantize_rows_e4m3(dOut, sd)
+    dH = O.gemm_e4m3(dOq, s1, np.ascontiguousarray(Wd.T), None)
+    dg, du = O.swiglu_bwd_x(O.BF16, O.BF16, g, u, dH)
+    check_lowp(to_host(dGU, O.BF16), np.concatenate([dg, du], axis=1), O.BF16, "gate|up gradients kept by the backward pass", rel=2e-2)
