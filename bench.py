@@ -51,6 +51,13 @@ DOMINANT = "swiglu_bwd_x"
 DOMINANT_DRAM_TRAFFIC_BYTES = 1_132_800_000
 
 
+def quiet_nccl_banner():
+    """NCCL prints its version banner on STDOUT at the VERSION debug level, which would put a second line beside the JSON line; the banner
+    is dropped (WARN) unless the caller asked for a more verbose level explicitly."""
+    if os.environ.get("NCCL_DEBUG", "VERSION").upper() == "VERSION":
+        os.environ["NCCL_DEBUG"] = "WARN"
+
+
 def measured_peak_hbm():
     try:
         with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
@@ -288,6 +295,7 @@ def run_gpu_arm(args):
     assert world == args.gpus, f"--gpus {args.gpus} but WORLD_SIZE={world} (launch N > 1 with torchrun)"
     torch.cuda.set_device(local)
     if world > 1:
+        quiet_nccl_banner()
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
 
     h = DataflowHandle(device_id=local, num_streams=2)
@@ -492,6 +500,7 @@ def run_stack_arm(args):
     assert world == args.gpus, f"--gpus {args.gpus} but WORLD_SIZE={world} (launch N > 1 with torchrun)"
     torch.cuda.set_device(local)
     if world > 1:
+        quiet_nccl_banner()
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     T, V, LAYERS = args.tokens or 16384, 128256, 4
     st = OpStackStep(T, D_MODEL, FFN, N_HEADS, N_KV, HEAD_DIM, V, LAYERS, EPS, float(THETA))
