@@ -52,10 +52,9 @@ DOMINANT_DRAM_TRAFFIC_BYTES = 1_132_800_000
 
 
 def quiet_nccl_banner():
-    """NCCL prints its version banner on STDOUT at the VERSION debug level, which would put a second line beside the JSON line; the banner
-    is dropped (WARN) unless the caller asked for a more verbose level explicitly."""
-    if os.environ.get("NCCL_DEBUG", "VERSION").upper() == "VERSION":
-        os.environ["NCCL_DEBUG"] = "WARN"
+    """NCCL writes its debug output -- at the VERSION and WARN levels that includes a version banner -- to STDOUT, which would put a second
+    line beside the JSON line; it is sent to stderr instead unless the caller already chose a file."""
+    os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
 
 
 def measured_peak_hbm():
