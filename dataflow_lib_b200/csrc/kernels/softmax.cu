@@ -24,6 +24,11 @@
 // (3.4 ms against 1.9 ms): per row the chain max -> cluster barrier -> sums -> cluster barrier ->
 // normalise costs about 7 us of latency however the data arrives, so what matters is how many
 // independent rows an SM has in flight, and registers hold more of them than one big CTA does.
+//
+// Keeping the exponentials of phase 2 in registers for phase 3 (possible at <= 4 packets per thread, which for long rows
+// means a cluster twice as large) was measured too and was slower everywhere: 32768 columns 5.8 -> 3.6 TB/s, 65536 columns
+// 4.6 -> 3.3 TB/s, 128256 columns 4.3 -> 3.0 TB/s. Evaluating exp twice is cheaper than the larger clusters and the store
+// bursts of a compute-free phase 3.
 #include "common.cuh"
 
 #include <cooperative_groups.h>
