@@ -28,7 +28,7 @@
 // Keeping the exponentials of phase 2 in registers for phase 3 (possible at <= 4 packets per thread, which for long rows
 // means a cluster twice as large) was measured too and was slower everywhere: 32768 columns 5.8 -> 3.6 TB/s, 65536 columns
 // 4.6 -> 3.3 TB/s, 128256 columns 4.3 -> 3.0 TB/s. Evaluating exp twice is cheaper than the larger clusters and the store
-// bursts of a compute-free phase 3.
+// bursts of a compute-free phase 3. CTAs of 1024 threads (a cluster half as large) were slower as well (128256 columns: 3.5 TB/s).
 #include "common.cuh"
 
 #include <cooperative_groups.h>
@@ -41,7 +41,10 @@ namespace dfb200 {
 constexpr int E = 8;                       // elements per chunk
 constexpr int SLICE_ALIGN_CHUNKS = 128;    // slices start on a multiple of 1024 elements so that a thread's partial index is fixed
 constexpr int SOFTMAX_MAX_CLUSTER = 8;
-constexpr int SOFTMAX_MAX_THREADS = 512;
+#ifndef DFB200_SOFTMAX_MAX_THREADS
+#define DFB200_SOFTMAX_MAX_THREADS 512
+#endif
+constexpr int SOFTMAX_MAX_THREADS = DFB200_SOFTMAX_MAX_THREADS;
 #ifndef DFB200_SOFTMAX_MAX_CPT
 #define DFB200_SOFTMAX_MAX_CPT 8
 #endif
@@ -128,7 +131,7 @@ softmax_rows_kernel(int n_rows, int n_cols, int slice_chunks, const void * __res
 	static_assert(!FUSE_CE || sizeof(OUT) == sizeof(B), "the fused cross-entropy step works in the output type");
 	constexpr int FW = E / Word<F>::EPW;
 	__shared__ float s_warp_max[32];
-	__shared__ float s_warp_part[16][8];
+	__shared__ float s_warp_part[SOFTMAX_MAX_THREADS / 32][8];
 	__shared__ float s_cta_max;
 	__shared__ float s_cta_part[32];
 	__shared__ float s_row[2];              // row max, row total
