@@ -352,39 +352,59 @@ swiglu_quantize_rows_kernel(int n_rows, int f, const void * __restrict__ G, cons
 //                            128-token x 64-column tiles through shared memory, 128-byte rows of the transpose per store group
 template <int VPT>
 __global__ void __launch_bounds__(1024)
-col_amax_kernel(int n_rows, int n_cols, const void * __restrict__ X, float * amax) {
-	const int n_chunks = n_cols / 8, tid = threadIdx.x, nthr = blockDim.x;
+col_amax_kernel(int n_rows, int n_cols, int group_threads, const void * __restrict__ X, float * amax) {
+	extern __shared__ unsigned int s_max[];                // [n_cols] maxima of this CTA (bit patterns of non-negative floats order like the floats)
+	const int n_chunks = n_cols / 8;
+	const int groups = blockDim.x / group_threads, g = threadIdx.x / group_threads, tid = threadIdx.x - g * group_threads;
+	for (int c = threadIdx.x; c < n_cols; c += blockDim.x) s_max[c] = 0u;
 	__nv_bfloat162 m[VPT][4];
 	#pragma unroll
 	for (int v = 0; v < VPT; v++)
 		#pragma unroll
 		for (int i = 0; i < 4; i++) m[v][i] = __float2bfloat162_rn(0.0f);
-	for (int row = blockIdx.x; row < n_rows; row += gridDim.x) {
-		uint32_t raw[VPT][4];
+	// one CTA per SM; its row groups take interleaved rows, ROWS of them per iteration so that a thread has several loads in flight
+	constexpr int ROWS = VPT == 1 ? 4 : 2;
+	const int stride = gridDim.x * groups;
+	for (int row0 = blockIdx.x * groups + g; row0 < n_rows && g < groups; row0 += ROWS * stride) {
+		uint32_t raw[ROWS][VPT][4];
 		#pragma unroll
-		for (int v = 0; v < VPT; v++) {
-			const int c = tid + v * nthr;
-			if (c < n_chunks) ld_words<4, Hint::STREAM>(reinterpret_cast<const char *>(X) + ((uint64_t) row * n_cols + (uint64_t) c * 8) * 2, raw[v]);
-		}
-		#pragma unroll
-		for (int v = 0; v < VPT; v++) {
-			if (tid + v * nthr < n_chunks) {
-				#pragma unroll
-				for (int i = 0; i < 4; i++) m[v][i] = __hmax2(m[v][i], __habs2(*reinterpret_cast<const __nv_bfloat162 *>(&raw[v][i])));
-			}
-		}
-	}
-	#pragma unroll
-	for (int v = 0; v < VPT; v++) {
-		const int c = tid + v * nthr;
-		if (c < n_chunks) {
+		for (int r = 0; r < ROWS; r++) {
+			const int row = row0 + r * stride;
 			#pragma unroll
-			for (int i = 0; i < 4; i++) {      // non-negative floats order like their bit patterns
-				atomicMax(reinterpret_cast<unsigned int *>(amax) + c * 8 + 2 * i, __float_as_uint(__low2float(m[v][i])));
-				atomicMax(reinterpret_cast<unsigned int *>(amax) + c * 8 + 2 * i + 1, __float_as_uint(__high2float(m[v][i])));
+			for (int v = 0; v < VPT; v++) {
+				const int c = tid + v * group_threads;
+				if (row < n_rows && c < n_chunks) ld_words<4, Hint::STREAM>(reinterpret_cast<const char *>(X) + ((uint64_t) row * n_cols + (uint64_t) c * 8) * 2, raw[r][v]);
+			}
+		}
+		#pragma unroll
+		for (int r = 0; r < ROWS; r++) {
+			if (row0 + r * stride >= n_rows) continue;
+			#pragma unroll
+			for (int v = 0; v < VPT; v++) {
+				if (tid + v * group_threads < n_chunks) {
+					#pragma unroll
+					for (int i = 0; i < 4; i++) m[v][i] = __hmax2(m[v][i], __habs2(*reinterpret_cast<const __nv_bfloat162 *>(&raw[r][v][i])));
+				}
 			}
 		}
 	}
+	__syncthreads();                                       // s_max cleared
+	if (g < groups) {
+		#pragma unroll
+		for (int v = 0; v < VPT; v++) {
+			const int c = tid + v * group_threads;
+			if (c < n_chunks) {
+				#pragma unroll
+				for (int i = 0; i < 4; i++) {
+					atomicMax(&s_max[c * 8 + 2 * i], __float_as_uint(__low2float(m[v][i])));
+					atomicMax(&s_max[c * 8 + 2 * i + 1], __float_as_uint(__high2float(m[v][i])));
+				}
+			}
+		}
+	}
+	__syncthreads();
+	for (int c = threadIdx.x; c < n_cols; c += blockDim.x)
+		if (s_max[c]) atomicMax(reinterpret_cast<unsigned int *>(amax) + c, s_max[c]);
 }
 
 constexpr int TQ_TOKENS = 128, TQ_COLS = 64, TQ_PITCH = TQ_TOKENS + 4;
@@ -942,14 +962,19 @@ extern "C" int dfb200_col_amax_bf16(int n_rows, int n_cols, const void * X_bf16,
 	if (e != cudaSuccess) { cudaGetLastError(); return set_error(DFB200_ERR_CUDA, "col_amax_bf16: %s", cudaGetErrorString(e)); }
 	int vpt = 1;
 	while (vpt < 4 && (n_chunks + vpt - 1) / vpt > 1024) vpt *= 2;
-	const int threads = ((n_chunks + vpt - 1) / vpt + 31) / 32 * 32;
-	const int per_sm = 2048 / threads < 1 ? 1 : 2048 / threads;
-	long long grid = (long long) sm_count() * per_sm;
-	if (grid > n_rows) grid = n_rows;
+	const int group_threads = ((n_chunks + vpt - 1) / vpt + 31) / 32 * 32;
+	int groups = 1024 / group_threads;
+	if (groups < 1) groups = 1;
+	int grid = sm_count();
+	if ((long long) grid * groups > n_rows) grid = (n_rows + groups - 1) / groups;
+	const size_t smem = (size_t) n_cols * sizeof(unsigned int);
 	switch (vpt) {
-		case 1: col_amax_kernel<1><<<(int) grid, threads, 0, s>>>(n_rows, n_cols, X_bf16, col_amax); break;
-		case 2: col_amax_kernel<2><<<(int) grid, threads, 0, s>>>(n_rows, n_cols, X_bf16, col_amax); break;
-		default: col_amax_kernel<4><<<(int) grid, threads, 0, s>>>(n_rows, n_cols, X_bf16, col_amax); break;
+		case 1: allow_dyn_smem(reinterpret_cast<const void *>(col_amax_kernel<1>), smem);
+		        col_amax_kernel<1><<<grid, groups * group_threads, smem, s>>>(n_rows, n_cols, group_threads, X_bf16, col_amax); break;
+		case 2: allow_dyn_smem(reinterpret_cast<const void *>(col_amax_kernel<2>), smem);
+		        col_amax_kernel<2><<<grid, groups * group_threads, smem, s>>>(n_rows, n_cols, group_threads, X_bf16, col_amax); break;
+		default: allow_dyn_smem(reinterpret_cast<const void *>(col_amax_kernel<4>), smem);
+		        col_amax_kernel<4><<<grid, groups * group_threads, smem, s>>>(n_rows, n_cols, group_threads, X_bf16, col_amax); break;
 	}
 	return check_launch("col_amax_bf16");
 }
