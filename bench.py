@@ -52,8 +52,10 @@ DOMINANT_DRAM_TRAFFIC_BYTES = 1_132_800_000
 
 
 def quiet_nccl_banner():
-    """NCCL writes its debug output -- at the VERSION and WARN levels that includes a version banner -- to STDOUT, which would put a second
-    line beside the JSON line; it is sent to stderr instead unless the caller already chose a file."""
+    """NCCL writes its debug output to STDOUT; at the VERSION level (which ignores NCCL_DEBUG_FILE) that is a version banner beside the
+    JSON line. VERSION is raised to WARN and the output sent to stderr, unless the caller chose a more verbose level or a file."""
+    if os.environ.get("NCCL_DEBUG", "").upper() in ("", "VERSION"):
+        os.environ["NCCL_DEBUG"] = "WARN"
     os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
 
 
