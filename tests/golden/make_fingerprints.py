@@ -1,6 +1,6 @@
 """Generates tests/golden/fingerprints.json from the REFERENCE's own host code.
 
-Runs only where /root/reference is mounted: it loads oracle/_ref/libref_host.so, which oracle/Makefile
+Runs only where the reference tree is mounted (the REF path below, the default of oracle/Makefile): it loads oracle/_ref/libref_host.so, which oracle/Makefile
 (`make -C oracle ref`) compiles from the reference's unmodified src/set_ops, src/fingerprint and
 src/datatype sources, calls the reference's set_native_*_skeleton builders for every (op, datatype)
 identity its register_native_ops enumerates, and records nickname, argument datatypes and SHA-256

@@ -1,4 +1,4 @@
-"""Full-size checks at the BASELINE.json configurations (C1 RMSNorm 4096x4096, C2 the 8192-token Llama-3-8B chain,
+"""Full-size checks at the benchmark configurations (C1 RMSNorm 4096x4096, C2 the 8192-token Llama-3-8B chain,
 C3 fused softmax + cross entropy 16384 x 128256), where the CPU oracle would take too long: size-independent
 properties of the ops, plus PyTorch fp32 re-computations on the GPU that model the reference's rounding points.
 Inputs: seeded torch normals of the configs' shapes and distributions (synthetic stand-ins for activations)."""
