@@ -29,6 +29,11 @@ template <typename T>
 __device__ __forceinline__ void ld_raw(const void * base, uint64_t elem_idx, RawChunk<T> & c) {
 	ld_words<E / Word<T>::EPW, Hint::STREAM>(reinterpret_cast<const char *>(base) + elem_idx * (4 / Word<T>::EPW), c.w);
 }
+// the same load without the evict-first hint, for tensors that the next op of a backward pass reads again
+template <typename T>
+__device__ __forceinline__ void ld_raw_keep(const void * base, uint64_t elem_idx, RawChunk<T> & c) {
+	ld_words<E / Word<T>::EPW, Hint::KEEP>(reinterpret_cast<const char *>(base) + elem_idx * (4 / Word<T>::EPW), c.w);
+}
 template <typename T>
 __device__ __forceinline__ void to_f32(const RawChunk<T> & c, float (&f)[E]) {
 	#pragma unroll
@@ -175,8 +180,8 @@ rms_norm_bwd_x_kernel(int n_rows, int n_cols, const float * __restrict__ fwd_wei
 			const int c = tid + v * nthr;
 			if (c < n_chunks) {
 				const uint64_t off = (uint64_t) row * n_cols + (uint64_t) c * E;
-				ld_raw<F>(X, off, xr[v]);
-				ld_raw<B>(dY, off, gr[v]);
+				ld_raw_keep<F>(X, off, xr[v]);           // X and dY are read again by rms_norm_bwd_w, which walks the rows backwards
+				ld_raw_keep<B>(dY, off, gr[v]);
 				ld_raw<B>(dX, off, dr[v]);
 			}
 		}
@@ -224,6 +229,8 @@ rms_norm_bwd_w_partial_kernel(int n_rows, int n_cols, int group_threads, const f
 		#pragma unroll
 		for (int i = 0; i < E; i++) acc[v][i] = 0.0f;
 
+	// Rows are visited from the LAST one backwards: this op usually follows rms_norm_bwd_x on the same X and dY, whose last rows are
+	// the ones still in L2 (the two tensors exceed it), so the walk starts where the cache is warm. The sum does not depend on the order.
 	const int row_stride = gridDim.x * groups;
 	RawChunk<F> xr[VPT], xn[VPT];
 	RawChunk<B> gr[VPT], gn[VPT];
@@ -233,7 +240,7 @@ rms_norm_bwd_w_partial_kernel(int n_rows, int n_cols, int group_threads, const f
 		for (int v = 0; v < VPT; v++) {
 			const int c = tid + v * group_threads;
 			if (c < n_chunks) {
-				const uint64_t off = (uint64_t) row * n_cols + (uint64_t) c * E;
+				const uint64_t off = (uint64_t) (n_rows - 1 - row) * n_cols + (uint64_t) c * E;
 				ld_raw<F>(X, off, xr[v]);
 				ld_raw<B>(dY, off, gr[v]);
 			}
@@ -246,13 +253,13 @@ rms_norm_bwd_w_partial_kernel(int n_rows, int n_cols, int group_threads, const f
 			for (int v = 0; v < VPT; v++) {
 				const int c = tid + v * group_threads;
 				if (c < n_chunks) {
-					const uint64_t off = (uint64_t) next_row * n_cols + (uint64_t) c * E;
+					const uint64_t off = (uint64_t) (n_rows - 1 - next_row) * n_cols + (uint64_t) c * E;
 					ld_raw<F>(X, off, xn[v]);
 					ld_raw<B>(dY, off, gn[v]);
 				}
 			}
 		}
-		const float r = __ldg(fwd_rms_vals + row);
+		const float r = __ldg(fwd_rms_vals + (n_rows - 1 - row));
 		#pragma unroll
 		for (int v = 0; v < VPT; v++) {
 			const int c = tid + v * group_threads;
