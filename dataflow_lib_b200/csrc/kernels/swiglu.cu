@@ -31,8 +31,8 @@ swiglu_fwd_kernel(uint64_t n_chunks, const void * __restrict__ x_w1, const void 
 	for (int u = 0; u < UNROLL; u++) {
 		const uint64_t c = first + (uint64_t) u * THREADS;
 		if (c < n_chunks) {
-			load_elems<F, E>(x_w1, c * E, a[u]);
-			load_elems<F, E>(x_w3, c * E, b[u]);
+			load_elems<F, E, Hint::KEEP>(x_w1, c * E, a[u]);     // no evict-first hint: the backward op reads these again (from their end)
+			load_elems<F, E, Hint::KEEP>(x_w3, c * E, b[u]);
 		}
 	}
 	#pragma unroll
@@ -54,11 +54,13 @@ __global__ void __launch_bounds__(THREADS)
 swiglu_bwd_x_kernel(uint64_t n_chunks, const void * __restrict__ x_w1, const void * __restrict__ x_w3,
                     const void * __restrict__ upstream_dX, void * __restrict__ dX_w1, void * __restrict__ dX_w3) {
 	pdl_prologue();
-	const uint64_t first = (uint64_t) blockIdx.x * (THREADS * UNROLL) + threadIdx.x;
+	// The tensors are walked from their END: in a layer's forward-then-backward sequence the tail of x_w1 and x_w3 is what the forward
+	// kernel left in L2.
+	const uint64_t first = (uint64_t) blockIdx.x * (THREADS * UNROLL) + threadIdx.x, last = n_chunks - 1;
 	float a[UNROLL][E], b[UNROLL][E], g[UNROLL][E];
 	#pragma unroll
 	for (int u = 0; u < UNROLL; u++) {
-		const uint64_t c = first + (uint64_t) u * THREADS;
+		const uint64_t c = last - (first + (uint64_t) u * THREADS);        // c < n_chunks also rejects the wrapped values
 		if (c < n_chunks) {
 			load_elems<F, E>(x_w1, c * E, a[u]);
 			load_elems<F, E>(x_w3, c * E, b[u]);
@@ -67,7 +69,7 @@ swiglu_bwd_x_kernel(uint64_t n_chunks, const void * __restrict__ x_w1, const voi
 	}
 	#pragma unroll
 	for (int u = 0; u < UNROLL; u++) {
-		const uint64_t c = first + (uint64_t) u * THREADS;
+		const uint64_t c = last - (first + (uint64_t) u * THREADS);        // c < n_chunks also rejects the wrapped values
 		if (c < n_chunks) {
 			float d1[E], d3[E];
 			#pragma unroll
