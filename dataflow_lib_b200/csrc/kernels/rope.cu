@@ -121,7 +121,13 @@ rope_kernel(int tokens, int model_dim, int kv_dim, int head_dim, int tok_per_ite
 // ----------------------------------------------------------------------------------------
 // staged kernel
 // ----------------------------------------------------------------------------------------
-constexpr int ROPE_STAGES = 4;
+#ifndef DFB200_ROPE_STAGES
+#define DFB200_ROPE_STAGES 4
+#endif
+#ifndef DFB200_ROPE_STAGE_BUDGET
+#define DFB200_ROPE_STAGE_BUDGET 24576
+#endif
+constexpr int ROPE_STAGES = DFB200_ROPE_STAGES;
 constexpr int ROPE_STAGED_THREADS = 512;
 
 template <typename T, bool BWD>
@@ -272,7 +278,7 @@ static int launch_rope(const char * op, int dt, uint64_t N, int model_dim, int h
 		const size_t esize = (size_t) dtype_size(dt);
 		const size_t row_bytes = ((size_t) model_dim + kv_dim) * esize;
 		const bool copyable = (model_dim * esize) % 16 == 0 && (kv_dim * esize) % 16 == 0;
-		int tok = (int) (24576 / row_bytes);
+		int tok = (int) (DFB200_ROPE_STAGE_BUDGET / row_bytes);
 		if (tok > 8) tok = 8;
 		if (tok > tokens) tok = tokens;
 		unsigned int * status = kernel_status_word(STATUS_ROPE);
