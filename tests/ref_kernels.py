@@ -90,3 +90,9 @@ class RefKernels:
     def softmax(self, name_dts, rows, cols, X, out):
         self.launch(f"softmax_{name_dts}_kernel", rows, 1024, 0, [rows, cols, X.data_ptr(), out.data_ptr()],
                     [C.c_int, C.c_int] + [C.c_void_p] * 2)
+
+    def softmax_fp32_out(self, name_dt, rows, cols, X, out, arg_maxs):
+        """softmax_<fp16|bf16>_fp32_kernel (src/ops/nvidia/loss/softmax.cu:965-1249): fp32 probabilities + the index of each row's maximum."""
+        self.launch(f"softmax_{name_dt}_fp32_kernel", rows, 1024, 0, [rows, cols, X.data_ptr(), out.data_ptr(), arg_maxs.data_ptr()],
+                    [C.c_int, C.c_int] + [C.c_void_p] * 3)
+

@@ -164,6 +164,30 @@ def test_softmax_bf16(ref, ops, shape):
     assert worst > 1e-2, worst
 
 
+@pytest.mark.parametrize("dt,name", [(O.BF16, "bf16"), (O.FP16, "fp16")])
+def test_softmax_fp32_out_and_argmax(ref, ops, dt, name):
+    """The reference's fp32-output softmax (probabilities unrounded, scratch in the input type) and its arg-max, on rows without ties for
+    the maximum (with ties the reference lets an arbitrary matching index win)."""
+    R, Cn = 12, 32000
+    X = fill(dt, (R, Cn), 13, 0.0, 2.0)
+    Xf = O.to_f32(X, dt)
+    for r in range(R):                                   # make every row's maximum unique
+        X[r, (7919 * (r + 1)) % Cn] = O.from_f32(np.array([Xf[r].max() + 1.0], np.float32), dt)[0]
+    Xd = to_dev(X, dt)
+    r_out, m_out = torch.empty((R, Cn), device="cuda"), torch.empty((R, Cn), device="cuda")
+    r_arg, m_arg = torch.zeros(R, dtype=torch.int32, device="cuda"), torch.zeros(R, dtype=torch.int32, device="cuda")
+    ref.softmax_fp32_out(name, R, Cn, Xd, r_out, r_arg)
+    ops.softmax_fp32_out(R, Cn, Xd, m_out, m_arg)
+    torch.cuda.synchronize()
+    assert torch.equal(r_arg, m_arg) and np.array_equal(m_arg.cpu().numpy(), O.to_f32(X, dt).argmax(1))
+    r, m = r_out.cpu().numpy(), m_out.cpu().numpy()
+    same = float((r == m).mean())
+    print(f"softmax_{name}_fp32: bit-identical to the reference kernel: {same:.5f}")
+    np.testing.assert_allclose(m, r, rtol=2e-6, atol=1e-12)
+    o, _ = O.softmax_fp32_out(dt, X)
+    np.testing.assert_allclose(r, o, rtol=1e-5, atol=1e-12)
+
+
 @pytest.mark.parametrize("name", sorted(CASES))
 def test_golden_cases_live(ref, name):
     """The committed golden file must be what the reference kernels produce here (guards against a stale fixture)."""
