@@ -96,3 +96,10 @@ class RefKernels:
         self.launch(f"softmax_{name_dt}_fp32_kernel", rows, 1024, 0, [rows, cols, X.data_ptr(), out.data_ptr(), arg_maxs.data_ptr()],
                     [C.c_int, C.c_int] + [C.c_void_p] * 3)
 
+    def copy_to_seq_context(self, name_dt, total_tokens, kv_dim, keys, values, seq_positions, seq_context_ptrs, seq_context_sizes):
+        """copy_to_seq_context_<dt>_kernel (src/ops/nvidia/attention/copy_to_seq_context.cu), launch geometry of attn_misc_config.c:56-79."""
+        N = total_tokens * kv_dim
+        self.launch(f"copy_to_seq_context_{name_dt}_kernel", -(-N // 1024), 1024, 0,
+                    [N, total_tokens, kv_dim, keys.data_ptr(), values.data_ptr(), seq_positions.data_ptr(), seq_context_ptrs.data_ptr(),
+                     seq_context_sizes.data_ptr()], [C.c_uint64, C.c_int, C.c_int] + [C.c_void_p] * 5)
+

@@ -188,6 +188,29 @@ def test_softmax_fp32_out_and_argmax(ref, ops, dt, name):
     np.testing.assert_allclose(r, o, rtol=1e-5, atol=1e-12)
 
 
+def test_copy_to_seq_context(ref, ops):
+    """Same scatter as the reference's kernel: two sequences' contexts in one buffer, every (context, position) written once."""
+    kv_dim, sizes, per_ctx = 1024, [96, 40], [70, 40]
+    T = sum(per_ctx)
+    rng = np.random.default_rng(3)
+    tok_ctx = rng.permutation(np.repeat(np.arange(2), per_ctx))
+    pos = np.empty(T, np.int32)
+    for c in range(2):
+        pos[tok_ctx == c] = rng.permutation(sizes[c])[:per_ctx[c]]
+    keys, values = to_dev(fill(BF, (T, kv_dim), 21), BF), to_dev(fill(BF, (T, kv_dim), 22), BF)
+    offs = [0, 2 * sizes[0] * kv_dim]
+    total = offs[1] + 2 * sizes[1] * kv_dim
+    bufs = [torch.zeros(total, dtype=torch.bfloat16, device="cuda") for _ in range(2)]
+    pos_d = torch.from_numpy(pos).cuda()
+    csz = torch.from_numpy(np.array([sizes[c] for c in tok_ctx], np.int32)).cuda()
+    for buf, run in zip(bufs, (lambda p: ref.copy_to_seq_context("bf16", T, kv_dim, keys, values, pos_d, p, csz),
+                               lambda p: ops.copy_to_seq_context(T * kv_dim, T, kv_dim, keys, values, pos_d, p, csz))):
+        ptrs = torch.from_numpy(np.array([buf.data_ptr() + 2 * offs[c] for c in tok_ctx], np.uint64).view(np.int64)).cuda()
+        run(ptrs)
+    torch.cuda.synchronize()
+    assert torch.equal(bufs[0], bufs[1]) and bufs[0].abs().sum() > 0
+
+
 @pytest.mark.parametrize("name", sorted(CASES))
 def test_golden_cases_live(ref, name):
     """The committed golden file must be what the reference kernels produce here (guards against a stale fixture)."""
