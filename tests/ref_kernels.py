@@ -103,3 +103,15 @@ class RefKernels:
                     [N, total_tokens, kv_dim, keys.data_ptr(), values.data_ptr(), seq_positions.data_ptr(), seq_context_ptrs.data_ptr(),
                      seq_context_sizes.data_ptr()], [C.c_uint64, C.c_int, C.c_int] + [C.c_void_p] * 5)
 
+    def select_experts(self, name_dt, total_tokens, n_experts, top_k, X, weights, chosen, counts, cumsum, routed, blocks=64, threads=128):
+        """select_experts_<dt>_kernel (src/ops/nvidia/moe/select_experts.cu). The reference has no launch configuration for it; this one keeps
+        the conditions its code needs: blocks <= total_tokens (a block without rows returns before it reports completion, and block 0 waits for
+        every block, :18-20,198-202), n_experts a multiple of 32 (full-mask shuffles in the prefix sum, :217-231), and dynamic shared memory for
+        its four arrays (:44-56)."""
+        assert blocks <= total_tokens and n_experts % 32 == 0 and threads % 32 == 0 and (threads // 32 * top_k) % 2 == 0
+        warps = threads // 32
+        smem = 4 * warps * 32 + 4 * warps * top_k + 2 * warps * top_k + 4 * n_experts
+        self.launch(f"select_experts_{name_dt}_kernel", blocks, threads, smem,
+                    [total_tokens, n_experts, top_k, X.data_ptr(), weights.data_ptr(), chosen.data_ptr(), counts.data_ptr(), cumsum.data_ptr(),
+                     routed.data_ptr()], [C.c_int, C.c_int, C.c_int] + [C.c_void_p] * 6)
+

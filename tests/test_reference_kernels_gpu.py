@@ -188,6 +188,36 @@ def test_softmax_fp32_out_and_argmax(ref, ops, dt, name):
     np.testing.assert_allclose(r, o, rtol=1e-5, atol=1e-12)
 
 
+@pytest.mark.parametrize("dt,name", [(O.FP32, "fp32"), (O.BF16, "bf16")])
+def test_select_experts(ref, ops, dt, name):
+    """The router against the reference's own kernel. Its scores come from the fast-math exponential, this library's from a fixed IEEE
+    sequence, so two experts whose scores differ in the last bits can swap: at least 99.5 % of the tokens must get identical expert ids in
+    identical slot order, the weights of those tokens agree to the datatype's rounding, and the per-expert counts differ by no more than
+    the number of tokens that differ."""
+    T, ne, k = 4096, 64, 8
+    X = fill(dt, (T, ne), 17, 0.0, 1.5)
+    Xd = to_dev(X, dt)
+    tdt = torch.float32 if dt == O.FP32 else torch.bfloat16
+    outs = []
+    for run in (lambda *a: ref.select_experts(name, T, ne, k, Xd, *a), lambda *a: ops.select_experts(T, ne, k, Xd, *a)):
+        w = torch.zeros((T, k), dtype=tdt, device="cuda")
+        ids = torch.zeros((T, k), dtype=torch.int16, device="cuda")
+        counts = torch.zeros(ne + 1, dtype=torch.int32, device="cuda")
+        cum, routed = torch.zeros(ne, dtype=torch.int32, device="cuda"), torch.ones(ne, dtype=torch.int32, device="cuda")
+        run(w, ids, counts, cum, routed)
+        torch.cuda.synchronize()
+        outs.append((w.float().cpu().numpy(), ids.cpu().numpy().view(np.uint16), counts.cpu().numpy(), cum.cpu().numpy(), routed.cpu().numpy()))
+    (rw, rid, rc, rcum, rr), (mw, mid, mc, mcum, mr) = outs
+    same_rows = (rid == mid).all(1)
+    print(f"select_experts {name}: tokens with identical expert ids and slot order: {same_rows.mean():.5f}")
+    assert same_rows.mean() >= 0.995
+    tol = 1e-5 if dt == O.FP32 else 1e-2
+    assert np.allclose(rw[same_rows], mw[same_rows], rtol=tol, atol=tol * 1e-2)
+    assert rc[ne] == 0 and mc[ne] == 0 and not rr.any() and not mr.any()
+    assert np.abs(rc[:ne] - mc[:ne]).sum() <= 2 * k * int((~same_rows).sum())
+    assert mcum[-1] == T * k and np.array_equal(mcum, np.cumsum(mc[:ne]))
+
+
 def test_copy_to_seq_context(ref, ops):
     """Same scatter as the reference's kernel: two sequences' contexts in one buffer, every (context, position) written once."""
     kv_dim, sizes, per_ctx = 1024, [96, 40], [70, 40]
