@@ -65,6 +65,21 @@ def main():
             out = torch.empty((R, Cn), dtype=to_dev(np.zeros(1, O.NP_OF[bdt]), bdt).dtype, device="cuda")
             ref.softmax(f"{nf}_{nb}", R, Cn, d["X"], out)
             blobs[name + "/out"] = to_host(out, bdt)
+        elif op == "softmax_fp32_out":
+            R, Cn = inp["X"].shape
+            out, arg = torch.empty((R, Cn), device="cuda"), torch.zeros(R, dtype=torch.int32, device="cuda")
+            ref.softmax_fp32_out(nf, R, Cn, d["X"], out, arg)
+            blobs[name + "/out"], blobs[name + "/argmax"] = out.cpu().numpy(), arg.cpu().numpy().view(np.uint32)
+        elif op == "select_experts":
+            T, ne, k = case["tokens"], case["n_experts"], case["top_k"]
+            w = torch.zeros((T, k), dtype=d["X"].dtype, device="cuda")
+            ids = torch.zeros((T, k), dtype=torch.int16, device="cuda")
+            counts = torch.zeros(ne + 1, dtype=torch.int32, device="cuda")
+            cum, routed = torch.zeros(ne, dtype=torch.int32, device="cuda"), torch.ones(ne, dtype=torch.int32, device="cuda")
+            ref.select_experts(nf, T, ne, k, d["X"], w, ids, counts, cum, routed)
+            torch.cuda.synchronize()
+            blobs[name + "/weights"], blobs[name + "/ids"] = to_host(w, fdt), ids.cpu().numpy().view(np.uint16)
+            blobs[name + "/counts"] = counts.cpu().numpy()
         torch.cuda.synchronize()
     np.savez_compressed(out_path, **blobs)
     print(f"wrote {len(blobs)} arrays for {len(CASES)} cases to {out_path} ({os.path.getsize(out_path) / 1024:.0f} KiB)")

@@ -28,6 +28,10 @@ CASES["rope_bf16_long"] = {"op": "rope", "fdt": BF, "tokens": 16, "model_dim": 5
 CASES["softmax_bf16_vocab"] = {"op": "softmax", "fdt": BF, "bdt": BF, "shape": (2, 128256), "dts": {"X": BF}}
 CASES["softmax_fp8e4m3_bf16"] = {"op": "softmax", "fdt": E4, "bdt": BF, "shape": (4, 4096), "dts": {"X": E4}}
 CASES["swiglu_fp8e4m3"] = {"op": "swiglu", "fdt": E4, "shape": (6, 1024), "dts": {"x1": E4, "x3": E4}}
+for _dt, _n in ((F32, "fp32"), (BF, "bf16")):
+    CASES[f"select_experts_{_n}"] = {"op": "select_experts", "fdt": _dt, "tokens": 192, "n_experts": 64, "top_k": 8, "dts": {"X": _dt}}
+for _dt, _n in ((BF, "bf16"), (FH, "fp16")):
+    CASES[f"softmax_{_n}_fp32_argmax"] = {"op": "softmax_fp32_out", "fdt": _dt, "bdt": F32, "shape": (4, 4096), "dts": {"X": _dt}}
 CASES["swiglu_bwd_x_fp8e5m2_fp16"] = {"op": "swiglu_bwd_x", "fdt": E5, "bdt": FH, "shape": (6, 1024), "dts": {"x1": E5, "x3": E5, "dY": FH}}
 
 
@@ -57,4 +61,12 @@ def inputs_for(case):
         return {"x1": O.fill_normal(fdt, case["shape"], 107), "x3": O.fill_normal(fdt, case["shape"], 108), "dY": O.fill_normal(bdt, case["shape"], 109)}
     if op == "softmax":
         return {"X": O.fill_normal(fdt, case["shape"], 110, 0.0, 2.0)}
+    if op == "softmax_fp32_out":
+        X = O.fill_normal(fdt, case["shape"], 110, 0.0, 2.0)
+        Xf = O.to_f32(X, fdt)
+        for r in range(X.shape[0]):                       # a unique maximum per row (with ties the reference's arg-max is arbitrary)
+            X[r, (997 * (r + 1)) % X.shape[1]] = O.from_f32(np.array([Xf[r].max() + 1.0], np.float32), fdt)[0]
+        return {"X": X}
+    if op == "select_experts":
+        return {"X": O.fill_normal(fdt, (case["tokens"], case["n_experts"]), 111, 0.0, 1.5)}
     raise KeyError(op)

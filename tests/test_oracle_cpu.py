@@ -67,6 +67,15 @@ def test_oracle_matches_reference_kernel_outputs(name):
     elif op == "softmax":
         out = O.softmax(fdt, bdt, inp["X"])
         assert check_lowp(out, g("out"), bdt, name, rel=_rel(bdt) if bdt != O.FP32 else 1e-4, scale=1.0 / case["shape"][1]) >= min_same
+    elif op == "softmax_fp32_out":
+        out, arg = O.softmax_fp32_out(fdt, inp["X"])
+        np.testing.assert_allclose(out, g("out"), rtol=1e-5, atol=1e-12)
+        assert np.array_equal(arg, g("argmax"))
+    elif op == "select_experts":
+        w, ids, counts, _, _ = O.select_experts(fdt, inp["X"], case["top_k"])
+        assert np.array_equal(ids, g("ids"))                       # expert ids and slot order as the reference kernel chose them
+        assert np.array_equal(counts, g("counts"))
+        check_lowp(w, g("weights"), fdt, name + " weights", rel=_rel(fdt) if fdt != O.FP32 else 1e-5)
     else:
         raise AssertionError(op)
 
