@@ -35,7 +35,8 @@ def test_quantize_rows(ops, shape):
     assert np.array_equal(sc.cpu().numpy(), s_ref)
 
 
-@pytest.mark.parametrize("mnk", [(128, 256, 128), (256, 512, 512), (200, 264, 400), (1, 8, 16), (130, 1024, 4096), (512, 384, 14336)], ids=str)
+@pytest.mark.parametrize("mnk", [(128, 256, 128), (256, 512, 512), (200, 264, 400), (1, 8, 16), (130, 1024, 4096), (512, 384, 14336), (256, 8, 16), (300, 40, 48),
+                                 (1000, 136, 144)], ids=str)
 def test_gemm_e4m3(ops, mnk):
     M, N, K = mnk
     Aq, sa = O.quantize_rows_e4m3(O.fill_normal(O.BF16, (M, K), 5))
