@@ -23,6 +23,7 @@ KERNEL_ABI = {
     "dfb200_target_arch": (C.c_char_p, []),
     "dfb200_sm_count": (_i, []),
     "dfb200_read_kernel_status": (_i, [_vp, _vp, _i]),
+    "dfb200_selftest_bounded_wait": (_i, [_i, _vp]),
     "dfb200_rms_norm": (_i, [_i, _i, _i, _f, _vp, _vp, _vp, _vp, _vp, _vp]),
     "dfb200_rms_norm_bwd_x": (_i, [_i, _i, _i, _i, _f, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
     "dfb200_rms_norm_bwd_w_workspace_bytes": (_u64, [_i, _i]),

@@ -38,6 +38,10 @@ const char * dfb200_last_error(void);
  * CUDA error. The status words are cleared when non-zero. */
 int dfb200_read_kernel_status(void * stream, unsigned int * status_words, int n_words);
 
+/* Self-test of the bounded waits: a kernel waits (about two seconds, the limit) on a barrier nothing completes, gives up, records code
+ * 0x7e57 in status word `slot` and ends normally. Returns 1 when the wait gave up as designed. Allocates a 4-byte flag for the call. */
+int dfb200_selftest_bounded_wait(int slot, void * stream);
+
 /* Library build info: "sm_100a", and the SM count of the current device (0 if no device). */
 const char * dfb200_target_arch(void);
 int dfb200_sm_count(void);

@@ -268,3 +268,24 @@ def test_no_bounded_wait_gave_up(ops):
     words = (ctypes.c_uint * 8)()
     rc = _lib.lib.dfb200_read_kernel_status(None, words, 8)
     assert rc == 0, (rc, list(words), _lib.last_error())
+
+
+def test_bounded_wait_gives_up_and_reports():
+    """A device-side wait that can never complete returns at its limit, the kernel ends, the status word names the wait, and the context
+    keeps working afterwards (no trap, no hang: the failure is made by leaving a barrier without its arrival)."""
+    import ctypes
+    import time
+    from dataflow_lib_b200 import _lib, ops as _ops
+    L = _lib.lib
+    words = (ctypes.c_uint * 8)()
+    assert L.dfb200_read_kernel_status(None, words, 8) == 0                  # clean before
+    t0 = time.time()
+    assert L.dfb200_selftest_bounded_wait(7, None) == 1, _lib.last_error()
+    assert 1.0 < time.time() - t0 < 20.0                                      # the limit is two seconds
+    assert L.dfb200_read_kernel_status(None, words, 8) == 0x7e57 and words[7] == 0x7e57 and not any(words[i] for i in range(7))
+    assert L.dfb200_read_kernel_status(None, words, 8) == 0                  # cleared by the read
+    x = torch.randn(64, 256, device="cuda").bfloat16()
+    out = torch.empty_like(x)
+    _ops.swiglu(64, 256, x, x, out)                                           # the context is still usable
+    torch.cuda.synchronize()
+    assert torch.isfinite(out.float()).all()
