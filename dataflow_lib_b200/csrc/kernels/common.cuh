@@ -188,6 +188,18 @@ __device__ __forceinline__ void store_elems(void * base, uint64_t idx, const flo
 	for (int i = 0; i < WORDS; i++) w[i] = Word<T>::pack(&f[i * EPW]);
 	st_words<WORDS>(reinterpret_cast<char *>(base) + idx * (4 / EPW), w);
 }
+// one element, rounded to T like store_elems rounds (the element occupies the low bits of a packed word)
+template <typename T>
+__device__ __forceinline__ void store_one(void * base, uint64_t idx, float f) {
+	constexpr int EPW = Word<T>::EPW;
+	float v[EPW];
+	#pragma unroll
+	for (int i = 0; i < EPW; i++) v[i] = i == 0 ? f : 0.0f;
+	const uint32_t w = Word<T>::pack(v);
+	if constexpr (EPW == 1) reinterpret_cast<uint32_t *>(base)[idx] = w;
+	else if constexpr (EPW == 2) reinterpret_cast<uint16_t *>(base)[idx] = (uint16_t) w;
+	else reinterpret_cast<uint8_t *>(base)[idx] = (uint8_t) w;
+}
 
 // ---------------------------------------------------------------------------------------
 // fast math: the approximate, flush-to-zero hardware forms that the reference build selects with

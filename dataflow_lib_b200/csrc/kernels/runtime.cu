@@ -57,7 +57,7 @@ int ctas_per_sm(const void * kernel, int threads, size_t dyn_smem) {
 }
 
 void allow_dyn_smem(const void * kernel, size_t dyn_smem) {
-	if (dyn_smem <= 48 * 1024) return;
+	if (dyn_smem <= 32 * 1024) return;             // static + dynamic may use 48 KB without opting in; kernels here have up to a few KB static
 	int dev = 0;
 	cudaGetDevice(&dev);
 	pthread_mutex_lock(&g_memo_lock);

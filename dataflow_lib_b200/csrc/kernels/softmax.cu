@@ -1,9 +1,10 @@
 // Row softmax, the cross-entropy gradient step, and the two fused into one pass.
 //
-// A row lives in REGISTERS: a thread-block cluster of 1, 2, 4 or 8 CTAs owns one row, every
-// thread requests its (up to CPT) 128-bit packets up front, and the three phases of the
+// A row lives ON CHIP: a thread-block cluster of 1, 2, 4 or 8 CTAs owns one row, every
+// thread requests its packets up front (up to 8 of 128 bits into registers; for long rows of
+// 16-bit elements 8 more into shared-memory slots of its own), and the three phases of the
 // reference kernel (max, sum of exponentials, normalise; src/ops/nvidia/loss/softmax.cu:311-405)
-// run on the register copy. The row is read from HBM once and written once; the reference
+// run on that copy. The row is read from HBM once and written once; the reference
 // reads it three times. Cross-CTA exchange of the maxima and partial sums goes through
 // distributed shared memory with the hardware cluster barrier (no spinning on memory).
 //
@@ -124,17 +125,27 @@ template <> struct RowMath<f16_t, f16_t> {
 // softmax_<f16|bf16>_fp32 kernels (src/ops/nvidia/loss/softmax.cu:965-1249), which keep their scratch in the input type and
 // store exp(..) / total unrounded. ARGMAX additionally writes the smallest index holding the row maximum to arg_maxs[row]
 // (the reference lets whichever thread sees the maximum last win, :1057-1059).
-template <typename F, typename B, int CPT, bool FUSE_CE, typename OUT = B, bool ARGMAX = false>
-__global__ void __launch_bounds__(SOFTMAX_MAX_THREADS)
+// SPT > 0 (16-bit inputs only): a thread owns SPT more packets of the row in SHARED memory (slots [k][tid], fetched with
+// per-thread asynchronous 16-byte copies and read back only by the thread that requested them, so no barrier guards them).
+// A 512-thread CTA then covers (CPT + SPT) x 512 = 8192 packets with 64 KB of shared memory and 64 registers per thread, so two
+// CTAs stay resident per SM and one computes exponentials while the other waits for memory. Rows of up to 65536 elements take one
+// such CTA, rows of up to 131072 elements a cluster of two. Measured at 16384 x 128256 bf16: cluster of 4 register-only CTAs
+// 1.93 ms; one 1024-thread CTA with 128 KB of shared memory (no cluster, but one CTA per SM) 1.76 ms; the cluster of two 1.64 ms.
+template <typename F, typename B, int CPT, bool FUSE_CE, typename OUT = B, bool ARGMAX = false, int SPT = 0>
+__global__ void __launch_bounds__(SOFTMAX_MAX_THREADS, SPT > 0 ? 2 : 0)
 softmax_rows_kernel(int n_rows, int n_cols, int slice_chunks, const void * __restrict__ X, void * __restrict__ out,
                     const uint32_t * __restrict__ labels, float * __restrict__ row_loss, uint32_t * __restrict__ arg_maxs = nullptr) {
 	static_assert(!FUSE_CE || sizeof(OUT) == sizeof(B), "the fused cross-entropy step works in the output type");
 	constexpr int FW = E / Word<F>::EPW;
+	static_assert(SPT == 0 || FW == 4, "shared-memory packets are 16 bytes");
+	constexpr int NPK = CPT + SPT;                         // packets per thread: the first CPT in registers, the rest in shared memory
+	extern __shared__ uint4 s_pack[];                      // [SPT][blockDim.x]
 	__shared__ float s_warp_max[32];
 	__shared__ float s_warp_part[SOFTMAX_MAX_THREADS / 32][8];
 	__shared__ float s_cta_max;
 	__shared__ float s_cta_part[32];
 	__shared__ float s_row[2];              // row max, row total
+	__shared__ uint32_t s_label;
 
 	cg::cluster_group cluster = cg::this_cluster();
 	const unsigned csize = cluster.num_blocks();
@@ -148,15 +159,37 @@ softmax_rows_kernel(int n_rows, int n_cols, int slice_chunks, const void * __res
 	const int c_end = min(n_chunks, c_begin + slice_chunks);
 	const uint64_t row_elem = (uint64_t) row * (uint64_t) n_cols;
 
-	// ---- load: every packet of the slice is requested before anything is consumed (and the row's label with them)
-	uint32_t label = 0xffffffffu;
-	if constexpr (FUSE_CE) label = __ldg(labels + row);
+	// ---- load: every packet of the slice is requested before anything is consumed
 	uint32_t raw[CPT][FW];
 	#pragma unroll
 	for (int k = 0; k < CPT; k++) {
 		const int c = c_begin + tid + k * nthr;
 		if (c < c_end) ld_words<FW, Hint::STREAM>(reinterpret_cast<const char *>(X) + (row_elem + (uint64_t) c * E) * (4 / Word<F>::EPW), raw[k]);
 	}
+	if constexpr (SPT > 0) {
+		#pragma unroll
+		for (int k = 0; k < SPT; k++) {
+			const int c = c_begin + tid + (CPT + k) * nthr;
+			if (c < c_end) {
+				const uint32_t dst = (uint32_t) __cvta_generic_to_shared(&s_pack[k * nthr + tid]);
+				asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" :: "r"(dst), "l"(reinterpret_cast<const char *>(X) + (row_elem + (uint64_t) c * E) * 2) : "memory");
+			}
+		}
+		asm volatile("cp.async.commit_group;" ::: "memory");
+	}
+	if constexpr (FUSE_CE) {
+		if (tid == 0) s_label = __ldg(labels + row);      // requested after the packets; read again only after phase 3
+	}
+	// packet k of this thread: registers for k < CPT, its own shared-memory slot otherwise (k is a compile-time constant after unrolling)
+	auto packet = [&](int k, uint32_t (&w)[FW]) {
+		if (k < CPT) {
+			#pragma unroll
+			for (int i = 0; i < FW; i++) w[i] = raw[k < CPT ? k : 0][i];
+		} else if constexpr (SPT > 0) {
+			const uint4 v = s_pack[(k - CPT) * nthr + tid];
+			w[0] = v.x; w[1] = v.y; w[2] = v.z; w[3] = v.w;
+		}
+	};
 
 	// ---- phase 1: row maximum
 	using Math = RowMath<F, B>;
@@ -165,6 +198,14 @@ softmax_rows_kernel(int n_rows, int n_cols, int slice_chunks, const void * __res
 	for (int k = 0; k < CPT; k++) {
 		const int c = c_begin + tid + k * nthr;
 		if (c < c_end) Math::max_chunk(macc, raw[k]);
+	}
+	if constexpr (SPT > 0) {
+		asm volatile("cp.async.wait_group 0;" ::: "memory");       // this thread's own copies have landed
+		#pragma unroll
+		for (int k = CPT; k < NPK; k++) {
+			const int c = c_begin + tid + k * nthr;
+			if (c < c_end) { uint32_t w[FW]; packet(k, w); Math::max_chunk(macc, w); }
+		}
 	}
 	float m = warp_max(Math::max_value(macc));
 	if (lane == 0) s_warp_max[warp] = m;
@@ -193,12 +234,14 @@ softmax_rows_kernel(int n_rows, int n_cols, int slice_chunks, const void * __res
 	if constexpr (ARGMAX) {
 		uint32_t first = 0xffffffffu;
 		#pragma unroll
-		for (int k = CPT - 1; k >= 0; k--) {
+		for (int k = NPK - 1; k >= 0; k--) {
 			const int c = c_begin + tid + k * nthr;
 			if (c < c_end) {
 				float x[E];
+				uint32_t w[FW];
+				packet(k, w);
 				#pragma unroll
-				for (int i = 0; i < FW; i++) Word<F>::unpack(raw[k][i], &x[i * Word<F>::EPW]);
+				for (int i = 0; i < FW; i++) Word<F>::unpack(w[i], &x[i * Word<F>::EPW]);
 				#pragma unroll
 				for (int i = E - 1; i >= 0; i--) if (x[i] == row_max) first = (uint32_t) (c * E + i);
 			}
@@ -209,11 +252,13 @@ softmax_rows_kernel(int n_rows, int n_cols, int slice_chunks, const void * __res
 	// ---- phase 2: 32 interleaved partial sums of exp(W(x - max))
 	float part4[4] = {0.0f, 0.0f, 0.0f, 0.0f};            // four independent chains: the adds are not the critical path
 	#pragma unroll
-	for (int k = 0; k < CPT; k++) {
+	for (int k = 0; k < NPK; k++) {
 		const int c = c_begin + tid + k * nthr;
 		if (c < c_end) {
 			float d[E];
-			Math::shifted(shift, raw[k], d);
+			uint32_t w[FW];
+			packet(k, w);
+			Math::shifted(shift, w, d);
 			#pragma unroll
 			for (int i = 0; i < E; i++) part4[i & 3] += fast_exp(d[i]);
 		}
@@ -254,45 +299,52 @@ softmax_rows_kernel(int n_rows, int n_cols, int slice_chunks, const void * __res
 	// ---- phase 3: normalise and store. exp(d) / total is the approximate division of the reference build, i.e. a
 	// multiplication by rcp.approx(total); the reciprocal is taken once per thread.
 	const float inv_total = fast_rcp(total);
-	bool owns_label = false;
 	#pragma unroll
-	for (int k = 0; k < CPT; k++) {
+	for (int k = 0; k < NPK; k++) {
 		const int c = c_begin + tid + k * nthr;
 		if (c < c_end) {
 			float d[E], o[E];
-			Math::shifted(shift, raw[k], d);
+			uint32_t w[FW];
+			packet(k, w);
+			Math::shifted(shift, w, d);
 			#pragma unroll
 			for (int i = 0; i < E; i++) o[i] = fast_exp(d[i]) * inv_total;
 			store_elems<OUT, E>(out, row_elem + (uint64_t) c * E, o);
-			if constexpr (FUSE_CE) owns_label |= (label / E == (uint32_t) c);
 		}
 	}
-	// ---- cross-entropy step, by the one thread of the row whose packet holds the label, outside the hot loop: it
-	// re-reads the probability it has just stored (its own store, so program order guarantees it sees it), subtracts
-	// one in the working type as the separate kernel does, and forms the row's loss from the label's logit.
+	// ---- cross-entropy step, outside the hot loop and by the one thread of the row whose packet holds the label. The label waits
+	// in shared memory until here so that it costs the loops no register. The thread recomputes the label's probability from its own
+	// packet (nothing is read back from memory), rounds it to the working type, subtracts one and rounds again -- what the separate
+	// kernel does to the stored value -- and stores over it; the row's loss comes from the label's shifted logit.
 	if constexpr (FUSE_CE) {
-		if (owns_label) {
-			const uint64_t idx = row_elem + label;
-			float p[1], x[1];
-			if constexpr (Word<B>::EPW == 1) {
-				float * q = reinterpret_cast<float *>(out) + idx;
-				*q = *q - 1.0f;
-			} else {
-				uint16_t * q = reinterpret_cast<uint16_t *>(out) + idx;
-				float pair[2];
-				Word<B>::unpack((uint32_t) *q, pair);
-				pair[0] -= 1.0f; pair[1] = 0.0f;
-				*q = (uint16_t) (Word<B>::pack(pair) & 0xffffu);
+		const uint32_t label = s_label;                   // written by thread 0 before the barriers of phase 1
+		if (label < (uint32_t) n_cols) {
+			const int rel = (int) (label / E) - c_begin - tid;
+			if (rel >= 0 && rel % nthr == 0 && rel / nthr < NPK && (int) (label / E) < c_end) {
+				const int kl = rel / nthr, j = (int) (label % E);
+				uint32_t w[FW];
+				if (kl >= CPT) {
+					if constexpr (SPT > 0) { const uint4 v = s_pack[(kl - CPT) * nthr + tid]; w[0] = v.x; w[1] = v.y; w[2] = v.z; w[3] = v.w; }
+				} else {
+					#pragma unroll
+					for (int k = 0; k < CPT; k++) {
+						if (k == kl) {
+							#pragma unroll
+							for (int i = 0; i < FW; i++) w[i] = raw[k][i];
+						}
+					}
+				}
+				float d[E], dj = 0.0f;
+				Math::shifted(shift, w, d);
+				#pragma unroll
+				for (int i = 0; i < E; i++) if (i == j) dj = d[i];
+				const float grad = round_to<B>(fast_exp(dj) * inv_total) - 1.0f;
+				store_one<OUT>(out, row_elem + label, grad);
+				if (row_loss) row_loss[row] = logf(total) - dj;
 			}
-			if (row_loss) {
-				if constexpr (Word<F>::EPW == 1) x[0] = reinterpret_cast<const float *>(X)[idx];
-				else if constexpr (Word<F>::EPW == 2) { float pr[2]; Word<F>::unpack((uint32_t) reinterpret_cast<const uint16_t *>(X)[idx], pr); x[0] = pr[0]; }
-				else { float qd[4]; Word<F>::unpack((uint32_t) reinterpret_cast<const uint8_t *>(X)[idx], qd); x[0] = qd[0]; }
-				row_loss[row] = logf(total) - round_to<B>(x[0] - row_max);
-			}
-			(void) p;
+		} else if (row_loss && crank == 0 && tid == 0) {
+			row_loss[row] = 0.0f;
 		}
-		if (row_loss && label >= (uint32_t) n_cols && crank == 0 && tid == 0) row_loss[row] = 0.0f;
 	}
 	if (csize > 1) cluster.barrier_wait();  // no CTA leaves while a peer may still read its shared memory
 }
@@ -337,9 +389,24 @@ loss_sum_kernel(int n_rows, int n_cols, const float * __restrict__ row_loss, con
 	if (threadIdx.x == 0) { loss_sum[0] = (float) s_sum[0]; loss_sum[1] = (float) s_cnt[0]; }
 }
 
-struct SoftmaxGeometry { int cluster, threads, cpt, slice_chunks; };
+struct SoftmaxGeometry { int cluster, threads, cpt, slice_chunks, spt; };      // spt > 0: packets per thread kept in shared memory
 
-static bool softmax_geometry(int n_chunks, SoftmaxGeometry * g) {
+constexpr int SOFTMAX_SPT = 8;                            // shared-memory packets per thread of the one-CTA-per-row form for long rows
+
+static bool softmax_geometry(int n_chunks, bool packets_16_bytes, SoftmaxGeometry * g) {
+	g->spt = 0;
+	// Long rows of 16-bit elements: CTAs of up to 512 threads with 8 packets per thread in registers and 8 in shared memory (64 KB, two
+	// CTAs per SM); one CTA for rows of up to 65536 elements, a cluster of two up to 131072.
+	if (packets_16_bytes && n_chunks > SOFTMAX_MAX_THREADS * SOFTMAX_MAX_CPT && n_chunks <= 2 * SOFTMAX_MAX_THREADS * (SOFTMAX_MAX_CPT + SOFTMAX_SPT) && SOFTMAX_MAX_CPT == 8 && SOFTMAX_MAX_THREADS == 512) {
+		const int cluster = n_chunks > SOFTMAX_MAX_THREADS * (SOFTMAX_MAX_CPT + SOFTMAX_SPT) ? 2 : 1;
+		int slice = (n_chunks + cluster - 1) / cluster;
+		slice = (slice + SLICE_ALIGN_CHUNKS - 1) / SLICE_ALIGN_CHUNKS * SLICE_ALIGN_CHUNKS;
+		int threads = (slice + SOFTMAX_MAX_CPT + SOFTMAX_SPT - 1) / (SOFTMAX_MAX_CPT + SOFTMAX_SPT);
+		threads = (threads + 127) / 128 * 128;
+		g->cluster = cluster; g->threads = threads; g->cpt = SOFTMAX_MAX_CPT; g->slice_chunks = slice;
+		g->spt = SOFTMAX_SPT;
+		return true;
+	}
 	// smallest cluster whose CTAs (<= 512 threads, <= 8 packets per thread) cover the row
 	int cluster = 1;
 	while (cluster < SOFTMAX_MAX_CLUSTER && (long long) cluster * SOFTMAX_MAX_THREADS * SOFTMAX_MAX_CPT < n_chunks) cluster *= 2;
@@ -359,9 +426,35 @@ static bool softmax_geometry(int n_chunks, SoftmaxGeometry * g) {
 	return true;
 }
 
+// The form with shared-memory packets (16-bit inputs, long rows).
+template <typename F, typename B, bool FUSE_CE, typename OUT, bool ARGMAX>
+static int launch_softmax_long_rows(const SoftmaxGeometry & g, int n_rows, int n_cols, const void * X, void * out, const uint32_t * labels, float * row_loss,
+                                    uint32_t * arg_maxs, cudaStream_t stream) {
+	if constexpr (Word<F>::EPW != 2) {
+		return set_error(DFB200_ERR_DTYPE, "softmax: internal geometry error");
+	} else {
+		const size_t smem = (size_t) g.spt * g.threads * sizeof(uint4);
+		cudaLaunchConfig_t cfg = {};
+		cfg.gridDim = dim3((unsigned) n_rows * g.cluster, 1, 1);
+		cfg.blockDim = dim3(g.threads, 1, 1);
+		cfg.dynamicSmemBytes = smem;
+		cfg.stream = stream;
+		cudaLaunchAttribute attr[1];
+		attr[0].id = cudaLaunchAttributeClusterDimension;
+		attr[0].val.clusterDim.x = g.cluster; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+		cfg.attrs = attr; cfg.numAttrs = 1;
+		auto kernel = softmax_rows_kernel<F, B, 8, FUSE_CE, OUT, ARGMAX, SOFTMAX_SPT>;
+		allow_dyn_smem(reinterpret_cast<const void *>(kernel), smem);
+		const cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, n_rows, n_cols, g.slice_chunks, X, out, labels, row_loss, arg_maxs);
+		if (e != cudaSuccess) { cudaGetLastError(); return set_error(DFB200_ERR_CUDA, "softmax launch: %s", cudaGetErrorString(e)); }
+		return DFB200_OK;
+	}
+}
+
 template <typename F, typename B, bool FUSE_CE>
 static int launch_softmax_rows(const SoftmaxGeometry & g, int n_rows, int n_cols, const void * X, void * out, const uint32_t * labels,
                                float * row_loss, cudaStream_t stream) {
+	if (g.spt) return launch_softmax_long_rows<F, B, FUSE_CE, B, false>(g, n_rows, n_cols, X, out, labels, row_loss, nullptr, stream);
 	cudaLaunchConfig_t cfg = {};
 	cfg.gridDim = dim3((unsigned) n_rows * g.cluster, 1, 1);
 	cfg.blockDim = dim3(g.threads, 1, 1);
@@ -385,6 +478,10 @@ static int launch_softmax_rows(const SoftmaxGeometry & g, int n_rows, int n_cols
 
 template <typename F>
 static int launch_softmax_fp32_out(const SoftmaxGeometry & g, int n_rows, int n_cols, const void * X, float * out, uint32_t * arg_maxs, cudaStream_t stream) {
+	if (g.spt) {
+		return arg_maxs ? launch_softmax_long_rows<F, F, false, f32_t, true>(g, n_rows, n_cols, X, out, nullptr, nullptr, arg_maxs, stream)
+		                : launch_softmax_long_rows<F, F, false, f32_t, false>(g, n_rows, n_cols, X, out, nullptr, nullptr, nullptr, stream);
+	}
 	cudaLaunchConfig_t cfg = {};
 	cfg.gridDim = dim3((unsigned) n_rows * g.cluster, 1, 1);
 	cfg.blockDim = dim3(g.threads, 1, 1);
@@ -416,7 +513,7 @@ static int check_softmax(const char * op, int fwd_dt, int bwd_dt, int n_rows, in
 	if (n_rows < 0 || n_cols <= 0) return set_error(DFB200_ERR_ARG, "%s: bad shape %d x %d", op, n_rows, n_cols);
 	if (n_cols % E) return set_error(DFB200_ERR_ARG, "%s: n_cols = %d is not a multiple of %d", op, n_cols, E);
 	if ((long long) n_rows * SOFTMAX_MAX_CLUSTER > 0x7fffffffLL) return set_error(DFB200_ERR_ARG, "%s: too many rows", op);
-	if (!softmax_geometry(n_cols / E, g))
+	if (!softmax_geometry(n_cols / E, fwd_dt == DATAFLOW_FP16 || fwd_dt == DATAFLOW_BF16, g))
 		return set_error(DFB200_ERR_ARG, "%s: n_cols = %d exceeds the supported maximum of %d", op, n_cols,
 		                 SOFTMAX_MAX_CLUSTER * SOFTMAX_MAX_THREADS * SOFTMAX_MAX_CPT * E);
 	if (n_rows && (!X || !out)) return set_error(DFB200_ERR_ARG, "%s: NULL tensor argument", op);
