@@ -5,8 +5,9 @@
 // 16-bit elements 8 more into shared-memory slots of its own), and the three phases of the
 // reference kernel (max, sum of exponentials, normalise; src/ops/nvidia/loss/softmax.cu:311-405)
 // run on that copy. The row is read from HBM once and written once; the reference
-// reads it three times. Cross-CTA exchange of the maxima and partial sums goes through
-// distributed shared memory with the hardware cluster barrier (no spinning on memory).
+// reads it three times. The CTAs of a cluster exchange their maxima and partial sums by
+// pushing them into each other's shared memory (asynchronous stores counted on a barrier in
+// the receiver's shared memory; every wait is bounded).
 //
 // Rounding points kept from the reference (W = the output/"backward" datatype, which is also
 // the type the reference holds its shared-memory scratch in):
@@ -31,6 +32,7 @@
 // 4.6 -> 3.3 TB/s, 128256 columns 4.3 -> 3.0 TB/s. Evaluating exp twice is cheaper than the larger clusters and the store
 // bursts of a compute-free phase 3. CTAs of 1024 threads (a cluster half as large) were slower as well (128256 columns: 3.5 TB/s).
 #include "common.cuh"
+#include "tma.cuh"
 
 #include <cooperative_groups.h>
 #include <math_constants.h>
@@ -50,6 +52,44 @@ constexpr int SOFTMAX_MAX_THREADS = DFB200_SOFTMAX_MAX_THREADS;
 #define DFB200_SOFTMAX_MAX_CPT 8
 #endif
 constexpr int SOFTMAX_MAX_CPT = DFB200_SOFTMAX_MAX_CPT;
+
+// ---- exchange between the CTAs of a cluster: every CTA PUSHES its value into the shared memory of each peer with an asynchronous
+// store that counts its bytes on a barrier in the peer's shared memory, and waits (bounded) on its own barrier. Against
+// barrier.cluster + remote loads this takes the memory fence of the cluster barrier's release and one round trip out of each of the
+// two exchanges of a row.
+__device__ __forceinline__ void cluster_arrive_release() { asm volatile("barrier.cluster.arrive.release;" ::: "memory"); }
+__device__ __forceinline__ void cluster_arrive_relaxed() { asm volatile("barrier.cluster.arrive.relaxed;" ::: "memory"); }
+__device__ __forceinline__ void cluster_wait_acquire() { asm volatile("barrier.cluster.wait.acquire;" ::: "memory"); }
+__device__ __forceinline__ uint32_t peer_smem_addr(const void * p, unsigned cta_rank) {
+	uint32_t r;
+	asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_u32(p)), "r"(cta_rank));
+	return r;
+}
+__device__ __forceinline__ void push_f32(uint32_t peer_dst, float v, uint32_t peer_bar) {
+	asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.b32 [%0], %1, [%2];"
+	             :: "r"(peer_dst), "r"(__float_as_uint(v)), "r"(peer_bar) : "memory");
+}
+// Waits for phase 0 of `bar` (its expected bytes have arrived from the peers). Gives up after WAIT_LIMIT_NS and records `where`;
+// once any wait of the launch has given up, the others give up at their next look at the status word, so a broken exchange costs
+// the launch one time limit and not one per row.
+__device__ __forceinline__ bool wait_pushed(uint64_t * bar, unsigned int * status, unsigned int where) {
+	auto done = [&]() {
+		uint32_t ok;
+		asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], 0;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+		             : "=r"(ok) : "r"(smem_u32(bar)) : "memory");
+		return ok != 0;
+	};
+	if (done()) return true;
+	const unsigned long long t0 = global_timer_ns();
+	for (;;) {
+		for (int i = 0; i < 1024; i++)
+			if (done()) return true;
+		if (global_timer_ns() - t0 > WAIT_LIMIT_NS) break;
+		if (status && *reinterpret_cast<volatile unsigned int *>(status) != 0) break;
+	}
+	if (status) atomicMax(status, where);
+	return false;
+}
 
 // Per-chunk arithmetic. The softmax is instruction-bound before it is memory-bound (two exponentials per element
 // plus the rounding of x - max to the working type): at 6.5 TB/s an SM has about 22 issue slots per element, and
@@ -129,12 +169,18 @@ template <> struct RowMath<f16_t, f16_t> {
 // per-thread asynchronous 16-byte copies and read back only by the thread that requested them, so no barrier guards them).
 // A 512-thread CTA then covers (CPT + SPT) x 512 = 8192 packets with 64 KB of shared memory and 64 registers per thread, so two
 // CTAs stay resident per SM and one computes exponentials while the other waits for memory. Rows of up to 65536 elements take one
-// such CTA, rows of up to 131072 elements a cluster of two. Measured at 16384 x 128256 bf16: cluster of 4 register-only CTAs
-// 1.93 ms; one 1024-thread CTA with 128 KB of shared memory (no cluster, but one CTA per SM) 1.76 ms; the cluster of two 1.64 ms.
-template <typename F, typename B, int CPT, bool FUSE_CE, typename OUT = B, bool ARGMAX = false, int SPT = 0>
-__global__ void __launch_bounds__(SOFTMAX_MAX_THREADS, SPT > 0 ? 2 : 0)
+// such CTA, rows of up to 131072 elements a cluster of two, up to 262144 a cluster of four. Measured at 16384 x 128256 bf16: cluster of 4 register-only CTAs
+// 1.93 ms; one 1024-thread CTA with 128 KB of shared memory (no cluster, but one CTA per SM) 1.76 ms; the cluster of two 1.64 ms with
+// cluster barriers and remote reads, 1.50 ms with the pushed exchange above.
+// Resident CTAs per SM the compiler is asked to make room for, by the registers the row copy takes (32-bit words per thread): up to
+// 16 words leave room for four 512-thread CTAs (32 registers per thread), up to 32 words for two (64 registers); beyond that
+// (fp32 rows at 8 packets per thread) the compiler is left alone.
+constexpr int softmax_min_ctas(int row_words_per_thread, int spt) { return spt > 0 ? 2 : row_words_per_thread <= 16 ? 4 : row_words_per_thread <= 32 ? 2 : 0; }
+
+template <typename F, typename B, int CPT, bool FUSE_CE, typename OUT = B, bool ARGMAX = false, int SPT = 0, bool MULTI = false>
+__global__ void __launch_bounds__(SOFTMAX_MAX_THREADS, softmax_min_ctas(CPT * (E / Word<F>::EPW), SPT))
 softmax_rows_kernel(int n_rows, int n_cols, int slice_chunks, const void * __restrict__ X, void * __restrict__ out,
-                    const uint32_t * __restrict__ labels, float * __restrict__ row_loss, uint32_t * __restrict__ arg_maxs = nullptr) {
+                    const uint32_t * __restrict__ labels, float * __restrict__ row_loss, uint32_t * __restrict__ arg_maxs, unsigned int * status) {
 	static_assert(!FUSE_CE || sizeof(OUT) == sizeof(B), "the fused cross-entropy step works in the output type");
 	constexpr int FW = E / Word<F>::EPW;
 	static_assert(SPT == 0 || FW == 4, "shared-memory packets are 16 bytes");
@@ -142,14 +188,16 @@ softmax_rows_kernel(int n_rows, int n_cols, int slice_chunks, const void * __res
 	extern __shared__ uint4 s_pack[];                      // [SPT][blockDim.x]
 	__shared__ float s_warp_max[32];
 	__shared__ float s_warp_part[SOFTMAX_MAX_THREADS / 32][8];
-	__shared__ float s_cta_max;
-	__shared__ float s_cta_part[32];
+	__shared__ float s_peer_max[SOFTMAX_MAX_CLUSTER];      // [r] pushed here by CTA r of the cluster
+	__shared__ float s_peer_part[SOFTMAX_MAX_CLUSTER][32];
+	__shared__ uint64_t s_pushed[2];                       // byte-counting barriers of the two exchanges
 	__shared__ float s_row[2];              // row max, row total
-	__shared__ uint32_t s_label;
+	__shared__ uint32_t s_label[3];         // label, owning thread, packet index (fused cross entropy)
 
-	cg::cluster_group cluster = cg::this_cluster();
-	const unsigned csize = cluster.num_blocks();
-	const unsigned crank = cluster.block_rank();
+	// MULTI = the row is shared by a cluster of more than one CTA (only rows that need 8 packets per thread are); without it the
+	// cluster code compiles away.
+	unsigned csize = 1, crank = 0;
+	if constexpr (MULTI) { csize = cg::this_cluster().num_blocks(); crank = cg::this_cluster().block_rank(); }
 	const int row = blockIdx.x / csize;
 	const int tid = threadIdx.x, nthr = blockDim.x;
 	const int warp = tid >> 5, lane = tid & 31, n_warps = nthr >> 5;
@@ -158,6 +206,25 @@ softmax_rows_kernel(int n_rows, int n_cols, int slice_chunks, const void * __res
 	const int c_begin = crank * slice_chunks;
 	const int c_end = min(n_chunks, c_begin + slice_chunks);
 	const uint64_t row_elem = (uint64_t) row * (uint64_t) n_cols;
+
+	if constexpr (ARGMAX) {
+		// ordered before every atomicMin below: by the release / acquire of the cluster barrier for the peers, by __syncthreads here
+		if (crank == 0 && tid == 0) arg_maxs[row] = 0xffffffffu;
+	}
+	// ---- cluster set-up, before any load is in flight so that the release of the arrive has nothing to wait for: the two barriers
+	// expect the peers' bytes (4 per peer for the maximum, 128 per peer for the partial sums); peers push only after their wait.
+	if constexpr (MULTI) {
+		if (tid == 0) {
+			mbar_init(&s_pushed[0], 1);
+			mbar_init(&s_pushed[1], 1);
+			mbar_fence_init();
+			mbar_arrive_expect_tx(&s_pushed[0], (csize - 1) * 4u);
+			mbar_arrive_expect_tx(&s_pushed[1], (csize - 1) * 128u);
+		}
+		__syncwarp();
+		// fence.mbarrier_init has published the barriers; only the arg-max form has a store (above) that the arrive must release
+		if constexpr (ARGMAX) cluster_arrive_release(); else cluster_arrive_relaxed();
+	}
 
 	// ---- load: every packet of the slice is requested before anything is consumed
 	uint32_t raw[CPT][FW];
@@ -178,7 +245,16 @@ softmax_rows_kernel(int n_rows, int n_cols, int slice_chunks, const void * __res
 		asm volatile("cp.async.commit_group;" ::: "memory");
 	}
 	if constexpr (FUSE_CE) {
-		if (tid == 0) s_label = __ldg(labels + row);      // requested after the packets; read again only after phase 3
+		// Requested after the packets. Thread 0 also works out which thread of the cluster holds the label's packet and as which of
+		// its packets, so that the other threads pay one shared-memory read and a compare for the cross-entropy step.
+		if (tid == 0) {
+			const uint32_t label = __ldg(labels + row);
+			const int rel = (int) (label / E) - c_begin;
+			const bool mine = label < (uint32_t) n_cols && rel >= 0 && (int) (label / E) < c_end;
+			s_label[0] = label;
+			s_label[1] = mine ? (uint32_t) (rel % nthr) : 0xffffffffu;   // owning thread of this CTA, if any
+			s_label[2] = mine ? (uint32_t) (rel / nthr) : 0u;            // index of the packet in that thread
+		}
 	}
 	// packet k of this thread: registers for k < CPT, its own shared-memory slot otherwise (k is a compile-time constant after unrolling)
 	auto packet = [&](int k, uint32_t (&w)[FW]) {
@@ -209,28 +285,50 @@ softmax_rows_kernel(int n_rows, int n_cols, int slice_chunks, const void * __res
 	}
 	float m = warp_max(Math::max_value(macc));
 	if (lane == 0) s_warp_max[warp] = m;
-	if constexpr (ARGMAX) {
-		if (crank == 0 && tid == 0) arg_maxs[row] = 0xffffffffu;   // ordered before the atomicMin below by the barriers of this phase
-	}
+	if constexpr (MULTI) cluster_wait_acquire();  // every CTA of the cluster runs and has its barriers set up (long since: the loads came between)
 	__syncthreads();
 	if (warp == 0) {
 		float v = lane < n_warps ? s_warp_max[lane] : -CUDART_INF_F;
 		v = warp_max(v);
-		if (lane == 0) s_cta_max = v;
-	}
-	if (csize > 1) {
-		cluster.sync();                     // also orders the s_cta_max write before the remote reads
-		if (warp == 0) {
-			float v = lane < csize ? *cluster.map_shared_rank(&s_cta_max, lane) : -CUDART_INF_F;
+		if constexpr (MULTI) {
+			if ((unsigned) lane == crank) s_peer_max[crank] = v;
+			else if ((unsigned) lane < csize) push_f32(peer_smem_addr(&s_peer_max[crank], lane), v, peer_smem_addr(&s_pushed[0], lane));
+			wait_pushed(&s_pushed[0], status, 0x50000001u);
+			__syncwarp();
+			v = (unsigned) lane < csize ? s_peer_max[lane] : -CUDART_INF_F;
 			v = warp_max(v);
-			if (lane == 0) s_row[0] = v;
 		}
-	} else {
-		if (tid == 0) s_row[0] = s_cta_max; // same thread wrote it
+		if (lane == 0) s_row[0] = v;
 	}
 	__syncthreads();
 	const float row_max = s_row[0];
 	const typename Math::Shift shift = Math::shift_of(row_max);
+	// ---- the fused cross-entropy step needs W(x[label] - max) after the last phase: the one thread of the row whose packet holds the
+	// label takes it aside now (one register through the hot loops; the label itself waits in shared memory), so that the row copy can
+	// be given up packet by packet in phase 3.
+	constexpr float NO_LABEL = 1.0f;                       // shifted logits are <= 0 (or NaN)
+	float label_logit = NO_LABEL;
+	if constexpr (FUSE_CE) {
+		if ((uint32_t) tid == s_label[1]) {               // written by thread 0 before the barriers of phase 1
+			const int kl = (int) s_label[2], j = (int) (s_label[0] % E);
+			uint32_t w[FW];
+			if (kl >= CPT) {
+				if constexpr (SPT > 0) { const uint4 v = s_pack[(kl - CPT) * nthr + tid]; w[0] = v.x; w[1] = v.y; w[2] = v.z; w[3] = v.w; }
+			} else {
+				#pragma unroll
+				for (int k = 0; k < CPT; k++) {
+					if (k == kl) {
+						#pragma unroll
+						for (int i = 0; i < FW; i++) w[i] = raw[k][i];
+					}
+				}
+			}
+			float d[E];
+			Math::shifted(shift, w, d);
+			#pragma unroll
+			for (int i = 0; i < E; i++) if (i == j) label_logit = d[i];
+		}
+	}
 	if constexpr (ARGMAX) {
 		uint32_t first = 0xffffffffu;
 		#pragma unroll
@@ -274,25 +372,21 @@ softmax_rows_kernel(int n_rows, int n_cols, int slice_chunks, const void * __res
 		// partial `lane` was produced by warps w with w % 4 == lane / 8 (8 partials per warp)
 		float v = 0.0f;
 		for (int w = lane >> 3; w < n_warps; w += 4) v += s_warp_part[w][lane & 7];
-		s_cta_part[lane] = v;
-	}
-	if (csize > 1) {
-		cluster.sync();
-		if (warp == 0) {
-			float v = 0.0f;
-			for (unsigned r = 0; r < csize; r++) v += cluster.map_shared_rank(s_cta_part, r)[lane];
-			v = round_to<B>(v);
-			v = warp_sum(v);
-			if (lane == 0) s_row[1] = round_to<B>(v);
+		if constexpr (MULTI) {
+			s_peer_part[crank][lane] = v;
+			for (unsigned r = 0; r < csize; r++)
+				if (r != crank) push_f32(peer_smem_addr(&s_peer_part[crank][lane], r), v, peer_smem_addr(&s_pushed[1], r));
+			wait_pushed(&s_pushed[1], status, 0x50000002u);
+			v = 0.0f;
+			for (unsigned r = 0; r < csize; r++) v += s_peer_part[r][lane];   // the same order in every CTA of the cluster
 		}
-		cluster.barrier_arrive();           // remote reads done; matched by barrier_wait before exit
-	} else {
-		if (warp == 0) {
-			float v = round_to<B>(s_cta_part[lane]);   // written by this same lane
-			v = warp_sum(v);
-			if (lane == 0) s_row[1] = round_to<B>(v);
-		}
+		v = round_to<B>(v);
+		v = warp_sum(v);
+		if (lane == 0) s_row[1] = round_to<B>(v);
 	}
+	// A CTA has received everything its peers will ever write into its shared memory once both waits have returned, so it may leave
+	// without a closing barrier; the arrive / wait pair below only covers a wait that gave up (the status word then says so).
+	if constexpr (MULTI) cluster_arrive_relaxed();
 	__syncthreads();
 	const float total = s_row[1];
 
@@ -312,41 +406,18 @@ softmax_rows_kernel(int n_rows, int n_cols, int slice_chunks, const void * __res
 			store_elems<OUT, E>(out, row_elem + (uint64_t) c * E, o);
 		}
 	}
-	// ---- cross-entropy step, outside the hot loop and by the one thread of the row whose packet holds the label. The label waits
-	// in shared memory until here so that it costs the loops no register. The thread recomputes the label's probability from its own
-	// packet (nothing is read back from memory), rounds it to the working type, subtracts one and rounds again -- what the separate
-	// kernel does to the stored value -- and stores over it; the row's loss comes from the label's shifted logit.
+	// ---- cross-entropy step, by the one thread of the row that holds the label: the probability is recomputed from the logit taken
+	// aside above (nothing is read back from memory), rounded to the working type, one is subtracted and the difference rounded again
+	// -- what the separate kernel does to the stored value -- and stored over it; the row's loss comes from the same shifted logit.
 	if constexpr (FUSE_CE) {
-		const uint32_t label = s_label;                   // written by thread 0 before the barriers of phase 1
-		if (label < (uint32_t) n_cols) {
-			const int rel = (int) (label / E) - c_begin - tid;
-			if (rel >= 0 && rel % nthr == 0 && rel / nthr < NPK && (int) (label / E) < c_end) {
-				const int kl = rel / nthr, j = (int) (label % E);
-				uint32_t w[FW];
-				if (kl >= CPT) {
-					if constexpr (SPT > 0) { const uint4 v = s_pack[(kl - CPT) * nthr + tid]; w[0] = v.x; w[1] = v.y; w[2] = v.z; w[3] = v.w; }
-				} else {
-					#pragma unroll
-					for (int k = 0; k < CPT; k++) {
-						if (k == kl) {
-							#pragma unroll
-							for (int i = 0; i < FW; i++) w[i] = raw[k][i];
-						}
-					}
-				}
-				float d[E], dj = 0.0f;
-				Math::shifted(shift, w, d);
-				#pragma unroll
-				for (int i = 0; i < E; i++) if (i == j) dj = d[i];
-				const float grad = round_to<B>(fast_exp(dj) * inv_total) - 1.0f;
-				store_one<OUT>(out, row_elem + label, grad);
-				if (row_loss) row_loss[row] = logf(total) - dj;
-			}
-		} else if (row_loss && crank == 0 && tid == 0) {
+		if (label_logit != NO_LABEL) {
+			store_one<OUT>(out, row_elem + s_label[0], round_to<B>(fast_exp(label_logit) * inv_total) - 1.0f);
+			if (row_loss) row_loss[row] = logf(total) - label_logit;
+		} else if (row_loss && crank == 0 && tid == 0 && s_label[0] >= (uint32_t) n_cols) {
 			row_loss[row] = 0.0f;
 		}
 	}
-	if (csize > 1) cluster.barrier_wait();  // no CTA leaves while a peer may still read its shared memory
+	if constexpr (MULTI) cluster_wait_acquire();
 }
 
 // pred[r, labels[r]] -= 1 in the tensor's own type (intended semantics of
@@ -377,7 +448,18 @@ loss_sum_kernel(int n_rows, int n_cols, const float * __restrict__ row_loss, con
 	__shared__ unsigned s_cnt[1024];
 	double acc = 0.0;
 	unsigned cnt = 0;
-	for (int r = threadIdx.x; r < n_rows; r += 1024) {
+	// eight rows per thread in flight; the additions keep the order r, r + 1024, r + 2048, ...
+	int r = threadIdx.x;
+	for (; r + 7 * 1024 < n_rows; r += 8 * 1024) {
+		uint32_t l[8];
+		float v[8];
+		#pragma unroll
+		for (int i = 0; i < 8; i++) { l[i] = __ldg(labels + r + i * 1024); v[i] = row_loss[r + i * 1024]; }
+		#pragma unroll
+		for (int i = 0; i < 8; i++)
+			if (l[i] < (uint32_t) n_cols) { acc += (double) v[i]; cnt++; }
+	}
+	for (; r < n_rows; r += 1024) {
 		if (labels[r] < (uint32_t) n_cols) { acc += (double) row_loss[r]; cnt++; }
 	}
 	s_sum[threadIdx.x] = acc; s_cnt[threadIdx.x] = cnt;
@@ -396,9 +478,10 @@ constexpr int SOFTMAX_SPT = 8;                            // shared-memory packe
 static bool softmax_geometry(int n_chunks, bool packets_16_bytes, SoftmaxGeometry * g) {
 	g->spt = 0;
 	// Long rows of 16-bit elements: CTAs of up to 512 threads with 8 packets per thread in registers and 8 in shared memory (64 KB, two
-	// CTAs per SM); one CTA for rows of up to 65536 elements, a cluster of two up to 131072.
-	if (packets_16_bytes && n_chunks > SOFTMAX_MAX_THREADS * SOFTMAX_MAX_CPT && n_chunks <= 2 * SOFTMAX_MAX_THREADS * (SOFTMAX_MAX_CPT + SOFTMAX_SPT) && SOFTMAX_MAX_CPT == 8 && SOFTMAX_MAX_THREADS == 512) {
-		const int cluster = n_chunks > SOFTMAX_MAX_THREADS * (SOFTMAX_MAX_CPT + SOFTMAX_SPT) ? 2 : 1;
+	// CTAs per SM); one CTA for rows of up to 65536 elements, a cluster of two up to 131072, of four up to 262144.
+	if (packets_16_bytes && n_chunks > SOFTMAX_MAX_THREADS * SOFTMAX_MAX_CPT && n_chunks <= 4 * SOFTMAX_MAX_THREADS * (SOFTMAX_MAX_CPT + SOFTMAX_SPT) && SOFTMAX_MAX_CPT == 8 && SOFTMAX_MAX_THREADS == 512) {
+		const int per_cta = SOFTMAX_MAX_THREADS * (SOFTMAX_MAX_CPT + SOFTMAX_SPT);
+		const int cluster = n_chunks > 2 * per_cta ? 4 : n_chunks > per_cta ? 2 : 1;
 		int slice = (n_chunks + cluster - 1) / cluster;
 		slice = (slice + SLICE_ALIGN_CHUNKS - 1) / SLICE_ALIGN_CHUNKS * SLICE_ALIGN_CHUNKS;
 		int threads = (slice + SOFTMAX_MAX_CPT + SOFTMAX_SPT - 1) / (SOFTMAX_MAX_CPT + SOFTMAX_SPT);
@@ -422,6 +505,7 @@ static bool softmax_geometry(int n_chunks, bool packets_16_bytes, SoftmaxGeometr
 	int threads = (slice + cpt - 1) / cpt;
 	threads = (threads + 127) / 128 * 128;
 	if (threads > SOFTMAX_MAX_THREADS) return false;
+	if (cluster > 1 && cpt != 8) return false;     // the cluster forms of the kernel exist for 8 packets per thread only (never taken: see above)
 	g->cluster = cluster; g->threads = threads; g->cpt = cpt; g->slice_chunks = slice;
 	return true;
 }
@@ -434,6 +518,7 @@ static int launch_softmax_long_rows(const SoftmaxGeometry & g, int n_rows, int n
 		return set_error(DFB200_ERR_DTYPE, "softmax: internal geometry error");
 	} else {
 		const size_t smem = (size_t) g.spt * g.threads * sizeof(uint4);
+		unsigned int * status = kernel_status_word(STATUS_SOFTMAX);
 		cudaLaunchConfig_t cfg = {};
 		cfg.gridDim = dim3((unsigned) n_rows * g.cluster, 1, 1);
 		cfg.blockDim = dim3(g.threads, 1, 1);
@@ -443,9 +528,10 @@ static int launch_softmax_long_rows(const SoftmaxGeometry & g, int n_rows, int n
 		attr[0].id = cudaLaunchAttributeClusterDimension;
 		attr[0].val.clusterDim.x = g.cluster; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
 		cfg.attrs = attr; cfg.numAttrs = 1;
-		auto kernel = softmax_rows_kernel<F, B, 8, FUSE_CE, OUT, ARGMAX, SOFTMAX_SPT>;
+		auto kernel = g.cluster > 1 ? softmax_rows_kernel<F, B, 8, FUSE_CE, OUT, ARGMAX, SOFTMAX_SPT, true>
+		                            : softmax_rows_kernel<F, B, 8, FUSE_CE, OUT, ARGMAX, SOFTMAX_SPT, false>;
 		allow_dyn_smem(reinterpret_cast<const void *>(kernel), smem);
-		const cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, n_rows, n_cols, g.slice_chunks, X, out, labels, row_loss, arg_maxs);
+		const cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, n_rows, n_cols, g.slice_chunks, X, out, labels, row_loss, arg_maxs, status);
 		if (e != cudaSuccess) { cudaGetLastError(); return set_error(DFB200_ERR_CUDA, "softmax launch: %s", cudaGetErrorString(e)); }
 		return DFB200_OK;
 	}
@@ -465,12 +551,15 @@ static int launch_softmax_rows(const SoftmaxGeometry & g, int n_rows, int n_cols
 	attr[0].val.clusterDim.x = g.cluster; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
 	cfg.attrs = attr; cfg.numAttrs = 1;
 	uint32_t * no_argmax = nullptr;
+	unsigned int * status = kernel_status_word(STATUS_SOFTMAX);
 	cudaError_t e;
 	switch (g.cpt) {
-		case 1:  e = cudaLaunchKernelEx(&cfg, softmax_rows_kernel<F, B, 1, FUSE_CE>, n_rows, n_cols, g.slice_chunks, X, out, labels, row_loss, no_argmax); break;
-		case 2:  e = cudaLaunchKernelEx(&cfg, softmax_rows_kernel<F, B, 2, FUSE_CE>, n_rows, n_cols, g.slice_chunks, X, out, labels, row_loss, no_argmax); break;
-		case 4:  e = cudaLaunchKernelEx(&cfg, softmax_rows_kernel<F, B, 4, FUSE_CE>, n_rows, n_cols, g.slice_chunks, X, out, labels, row_loss, no_argmax); break;
-		default: e = cudaLaunchKernelEx(&cfg, softmax_rows_kernel<F, B, 8, FUSE_CE>, n_rows, n_cols, g.slice_chunks, X, out, labels, row_loss, no_argmax); break;
+		case 1:  e = cudaLaunchKernelEx(&cfg, softmax_rows_kernel<F, B, 1, FUSE_CE>, n_rows, n_cols, g.slice_chunks, X, out, labels, row_loss, no_argmax, status); break;
+		case 2:  e = cudaLaunchKernelEx(&cfg, softmax_rows_kernel<F, B, 2, FUSE_CE>, n_rows, n_cols, g.slice_chunks, X, out, labels, row_loss, no_argmax, status); break;
+		case 4:  e = cudaLaunchKernelEx(&cfg, softmax_rows_kernel<F, B, 4, FUSE_CE>, n_rows, n_cols, g.slice_chunks, X, out, labels, row_loss, no_argmax, status); break;
+		default: e = g.cluster > 1 ? cudaLaunchKernelEx(&cfg, softmax_rows_kernel<F, B, 8, FUSE_CE, B, false, 0, true>, n_rows, n_cols, g.slice_chunks, X, out, labels, row_loss, no_argmax, status)
+		                           : cudaLaunchKernelEx(&cfg, softmax_rows_kernel<F, B, 8, FUSE_CE>, n_rows, n_cols, g.slice_chunks, X, out, labels, row_loss, no_argmax, status);
+		         break;
 	}
 	if (e != cudaSuccess) { cudaGetLastError(); return set_error(DFB200_ERR_CUDA, "softmax launch: %s", cudaGetErrorString(e)); }
 	return DFB200_OK;
@@ -491,17 +580,18 @@ static int launch_softmax_fp32_out(const SoftmaxGeometry & g, int n_rows, int n_
 	attr[0].val.clusterDim.x = g.cluster; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
 	cfg.attrs = attr; cfg.numAttrs = 1;
 	const uint32_t * no_labels = nullptr;
+	unsigned int * status = kernel_status_word(STATUS_SOFTMAX);
 	float * no_loss = nullptr;
 	void * o = out;
 	cudaError_t e;
-#define DFB200_SOFTMAX_F32_CASE(CPT_) \
-	(arg_maxs ? cudaLaunchKernelEx(&cfg, softmax_rows_kernel<F, F, CPT_, false, f32_t, true>, n_rows, n_cols, g.slice_chunks, X, o, no_labels, no_loss, arg_maxs) \
-	          : cudaLaunchKernelEx(&cfg, softmax_rows_kernel<F, F, CPT_, false, f32_t, false>, n_rows, n_cols, g.slice_chunks, X, o, no_labels, no_loss, arg_maxs))
+#define DFB200_SOFTMAX_F32_CASE(CPT_, MULTI_) \
+	(arg_maxs ? cudaLaunchKernelEx(&cfg, softmax_rows_kernel<F, F, CPT_, false, f32_t, true, 0, MULTI_>, n_rows, n_cols, g.slice_chunks, X, o, no_labels, no_loss, arg_maxs, status) \
+	          : cudaLaunchKernelEx(&cfg, softmax_rows_kernel<F, F, CPT_, false, f32_t, false, 0, MULTI_>, n_rows, n_cols, g.slice_chunks, X, o, no_labels, no_loss, arg_maxs, status))
 	switch (g.cpt) {
-		case 1:  e = DFB200_SOFTMAX_F32_CASE(1); break;
-		case 2:  e = DFB200_SOFTMAX_F32_CASE(2); break;
-		case 4:  e = DFB200_SOFTMAX_F32_CASE(4); break;
-		default: e = DFB200_SOFTMAX_F32_CASE(8); break;
+		case 1:  e = DFB200_SOFTMAX_F32_CASE(1, false); break;
+		case 2:  e = DFB200_SOFTMAX_F32_CASE(2, false); break;
+		case 4:  e = DFB200_SOFTMAX_F32_CASE(4, false); break;
+		default: e = g.cluster > 1 ? DFB200_SOFTMAX_F32_CASE(8, true) : DFB200_SOFTMAX_F32_CASE(8, false); break;
 	}
 #undef DFB200_SOFTMAX_F32_CASE
 	if (e != cudaSuccess) { cudaGetLastError(); return set_error(DFB200_ERR_CUDA, "softmax (fp32 out) launch: %s", cudaGetErrorString(e)); }
