@@ -120,6 +120,12 @@ HOST_ABI = {
     "submit_softmax": (_i, [_H, _i, _i, _i, _i, _i, _vp, _vp]),
     "submit_cross_entropy_loss": (_i, [_H, _i, _i, _i, _i, _vp, _vp]),
     "submit_softmax_cross_entropy": (_i, [_H, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp]),
+    "set_external_matmul_skeleton": (None, [_SK]),
+    "set_external_flash3_attention_fwd_skeleton": (None, [_SK]),
+    "set_external_flash3_attention_bwd_skeleton": (None, [_SK]),
+    "submit_matmul": (_i, [_H, _i, _i, _i, _i, _i, _i, _i, _i, _i, _i, _i, _f, _f, _vp, _vp, _vp, _vp, _u64, _vp]),
+    "submit_attention": (_i, [_H, _i, _i, _i, _i, _i, _vp, _vp, _i, _vp, _vp, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _u64, _vp]),
+    "submit_attention_bwd": (_i, [_H, _i, _i, _i, _i, _i, _vp, _vp, _i, _vp, _vp, _i, _i, _i, _i] + [_vp] * 9 + [_u64, _vp]),
     # external-op plug-in symbols (ops_external.c)
     "dataflow_b200_workspace_init": (_i, [_H, _vp]),
     "dataflow_b200_rms_norm": (_i, [_H, _i, _vp, _vp]),

@@ -150,3 +150,40 @@ int submit_swiglu_ffn_fp8_bwd(Dataflow_Handle * handle, int stream_id, int num_t
 	ARGS(op, &num_tokens, &model_dim, &ffn_dim, &dOut, &gate_saved, &up_saved, &WdownT, &down_scales, &WgateupT, &gateup_scales, &dA);
 	return submit(handle, &op, stream_id, "swiglu ffn fp8 bwd");
 }
+
+/* ---- external ops (als244/dataflow_lib src/dataflow_ops/src/matmul_op.c:10-66, attention_op.c:36-82, 88-138): the op must have been
+ * registered on the handle by the user (register_external_code with the plug-in's shared object); this library only builds the Op.
+ * A, C, D row-major and B column-major give D = alpha * A B + beta * C. num_sms = 0 means "all". */
+int submit_matmul(Dataflow_Handle * handle, int stream_id, DataflowDatatype a_dt, DataflowDatatype b_dt, DataflowDatatype c_dt,
+                  DataflowDatatype d_dt, DataflowDatatype compute_dt, int to_trans_a, int to_trans_b, int M, int K, int N,
+                  float alpha, float beta, void * A, void * B, void * C, void * D, uint64_t workspaceBytes, void * workspace) {
+	Op op;
+	set_external_matmul_skeleton(&op.op_skeleton);
+	int num_sms = 0;
+	ARGS(op, &num_sms, &a_dt, &b_dt, &c_dt, &d_dt, &compute_dt, &to_trans_a, &to_trans_b, &M, &K, &N, &alpha, &beta, &A, &B, &C, &D,
+	     &workspaceBytes, &workspace);
+	return submit(handle, &op, stream_id, "matmul");
+}
+
+int submit_attention(Dataflow_Handle * handle, int stream_id, DataflowDatatype fwd_dt, int num_seqs, int total_q, int total_k,
+                     int * q_seq_offsets, int * q_seq_lens, int max_seqlen_q, int * k_seq_offsets, int * k_seq_lens, int max_seqlen_k,
+                     int num_q_heads, int num_kv_heads, int head_dim, void * x_q, void * x_k, void * x_v, void * x_attn_out,
+                     void * softmax_lse, uint64_t workspaceBytes, void * workspace) {
+	Op op;
+	set_external_flash3_attention_fwd_skeleton(&op.op_skeleton);
+	ARGS(op, &fwd_dt, &num_seqs, &total_q, &total_k, &q_seq_offsets, &q_seq_lens, &max_seqlen_q, &k_seq_offsets, &k_seq_lens, &max_seqlen_k,
+	     &num_q_heads, &num_kv_heads, &head_dim, &x_q, &x_k, &x_v, &x_attn_out, &softmax_lse, &workspaceBytes, &workspace);
+	return submit(handle, &op, stream_id, "attention");
+}
+
+int submit_attention_bwd(Dataflow_Handle * handle, int stream_id, DataflowDatatype bwd_dt, int num_seqs, int total_q, int total_k,
+                         int * q_seq_offsets, int * q_seq_lens, int max_seqlen_q, int * k_seq_offsets, int * k_seq_lens, int max_seqlen_k,
+                         int num_q_heads, int num_kv_heads, int head_dim, void * x_q, void * x_k, void * x_v, void * x_attn_out,
+                         void * softmax_lse, void * dx_out, void * dx_q, void * dx_k, void * dx_v, uint64_t workspaceBytes, void * workspace) {
+	Op op;
+	set_external_flash3_attention_bwd_skeleton(&op.op_skeleton);
+	ARGS(op, &bwd_dt, &num_seqs, &total_q, &total_k, &q_seq_offsets, &q_seq_lens, &max_seqlen_q, &k_seq_offsets, &k_seq_lens, &max_seqlen_k,
+	     &num_q_heads, &num_kv_heads, &head_dim, &x_q, &x_k, &x_v, &x_attn_out, &softmax_lse, &dx_out, &dx_q, &dx_k, &dx_v,
+	     &workspaceBytes, &workspace);
+	return submit(handle, &op, stream_id, "attention bwd");
+}

@@ -118,6 +118,27 @@ void set_native_softmax_cross_entropy_skeleton(Op_Skeleton * skeleton, DataflowD
 	build_skeleton(skeleton, nick2(nick, "softmax_cross_entropy", fwd, bwd), I_S, I_S, fwd, DATAFLOW_UINT32, bwd, DATAFLOW_FP32, DATAFLOW_FP32, END);
 }
 
+/* ---- external ops: the identities under which a user registers the cuBLASLt matmul and FlashAttention-3 plug-ins
+ * (als244/dataflow_lib src/set_ops/src/set_external_op_skeletons.c:4-73, 75-155, 157-243). This library ships no such plug-in;
+ * the skeletons exist so that code written against the reference finds the same fingerprints here. Datatypes travel as
+ * integer scalars, tensors as untyped pointers. */
+#define V_P DATAFLOW_VOID
+void set_external_matmul_skeleton(Op_Skeleton * skeleton) {
+	/* num_sms, a_dt, b_dt, c_dt, d_dt, compute_dt, to_trans_a, to_trans_b, M, K, N, alpha, beta, A, B, C, D, workspaceBytes, workspace */
+	build_skeleton(skeleton, "matmul", I_S, I_S, I_S, I_S, I_S, I_S, I_S, I_S, I_S, I_S, I_S, F_S, F_S, V_P, V_P, V_P, V_P,
+	               DATAFLOW_UINT64, V_P, END);
+}
+/* dtype, num_seqs, total_q, total_k, q_seq_offsets, q_seq_lens, max_seqlen_q, k_seq_offsets, k_seq_lens, max_seqlen_k,
+ * num_q_heads, num_kv_heads, head_dim, x_q, x_k, x_v, x_attn_out, softmax_lse, [dx_out, dx_q, dx_k, dx_v,] workspaceBytes, workspace */
+void set_external_flash3_attention_fwd_skeleton(Op_Skeleton * skeleton) {
+	build_skeleton(skeleton, "flash3_attention_fwd", I_S, I_S, I_S, I_S, DATAFLOW_INT, DATAFLOW_INT, I_S, DATAFLOW_INT, DATAFLOW_INT, I_S,
+	               I_S, I_S, I_S, V_P, V_P, V_P, V_P, V_P, U64_S, V_P, END);
+}
+void set_external_flash3_attention_bwd_skeleton(Op_Skeleton * skeleton) {
+	build_skeleton(skeleton, "flash3_attention_bwd", I_S, I_S, I_S, I_S, DATAFLOW_INT, DATAFLOW_INT, I_S, DATAFLOW_INT, DATAFLOW_INT, I_S,
+	               I_S, I_S, I_S, V_P, V_P, V_P, V_P, V_P, V_P, V_P, V_P, V_P, U64_S, V_P, END);
+}
+
 int set_native_op_skeleton(Op_Skeleton * skeleton, char * op_name, DataflowDatatype fwd_dt, DataflowDatatype bwd_dt) {
 	if (!strcmp(op_name, "embedding")) set_native_embedding_skeleton(skeleton, fwd_dt);
 	else if (!strcmp(op_name, "rms_norm")) set_native_rms_norm_skeleton(skeleton, fwd_dt);

@@ -95,6 +95,10 @@ void set_native_softmax_argmax_skeleton(Op_Skeleton * skeleton, DataflowDatatype
  * Activations bf16, weights e4m3 codes (DATAFLOW_FP8E4M3) with fp32 per-output-channel scales; argument lists as submit_swiglu_ffn_fp8*. */
 void set_native_swiglu_ffn_fp8_skeleton(Op_Skeleton * skeleton);
 void set_native_swiglu_ffn_fp8_bwd_skeleton(Op_Skeleton * skeleton);
+/* External ops (src/set_ops/include/set_external_op_skeletons.h:10-16): identities of the cuBLASLt matmul and FlashAttention-3 plug-ins. */
+void set_external_matmul_skeleton(Op_Skeleton * skeleton);
+void set_external_flash3_attention_fwd_skeleton(Op_Skeleton * skeleton);
+void set_external_flash3_attention_bwd_skeleton(Op_Skeleton * skeleton);
 /* Not in the reference: the fused softmax + cross-entropy op ("softmax_cross_entropy_<F>_<B>"). */
 void set_native_softmax_cross_entropy_skeleton(Op_Skeleton * skeleton, DataflowDatatype fwd_datatype, DataflowDatatype bwd_datatype);
 
@@ -150,6 +154,22 @@ int submit_swiglu_ffn_fp8(Dataflow_Handle * handle, int stream_id, int num_token
 int submit_swiglu_ffn_fp8_bwd(Dataflow_Handle * handle, int stream_id, int num_tokens, int model_dim, int ffn_dim,
                               void * dOut, void * gate_saved, void * up_saved, void * WdownT, float * down_scales,
                               void * WgateupT, float * gateup_scales, void * dA);
+
+/* External ops (src/dataflow_ops/include/dataflow_ops.h:69-76, 112-120, 130-140). The op itself comes from a plug-in that the user
+ * registers on the handle (register_external_code); these wrappers only build the Op and submit it. submit_matmul: with A, C, D
+ * row-major and B column-major, D = alpha * A B + beta * C. Return 0 on success, -1 if the op is not registered or fails. */
+int submit_matmul(Dataflow_Handle * handle, int stream_id, DataflowDatatype a_dt, DataflowDatatype b_dt, DataflowDatatype c_dt,
+                  DataflowDatatype d_dt, DataflowDatatype compute_dt, int to_trans_a, int to_trans_b, int M, int K, int N,
+                  float alpha, float beta, void * A, void * B, void * C, void * D, uint64_t workspaceBytes, void * workspace);
+int submit_attention(Dataflow_Handle * handle, int stream_id, DataflowDatatype fwd_dt, int num_seqs, int total_q, int total_k,
+                     int * q_seq_offsets, int * q_seq_lens, int max_seqlen_q, int * k_seq_offsets, int * k_seq_lens, int max_seqlen_k,
+                     int num_q_heads, int num_kv_heads, int head_dim, void * x_q, void * x_k, void * x_v, void * x_attn_out,
+                     void * softmax_lse, uint64_t workspaceBytes, void * workspace);
+int submit_attention_bwd(Dataflow_Handle * handle, int stream_id, DataflowDatatype bwd_dt, int num_seqs, int total_q, int total_k,
+                         int * q_seq_offsets, int * q_seq_lens, int max_seqlen_q, int * k_seq_offsets, int * k_seq_lens, int max_seqlen_k,
+                         int num_q_heads, int num_kv_heads, int head_dim, void * x_q, void * x_k, void * x_v, void * x_attn_out,
+                         void * softmax_lse, void * dx_out, void * dx_q, void * dx_k, void * dx_v, uint64_t workspaceBytes,
+                         void * workspace);
 
 #ifdef __cplusplus
 }

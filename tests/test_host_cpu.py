@@ -242,3 +242,76 @@ def test_reference_external_wrappers_link_against_this_library():
     assert bytes(sk.identifier.fingerprint).hex() == "2a113b16e997d04b8408f9aa299dd5a80bb77d29c95c8cc78270410ef84f3590"
     for name in ("submit_matmul", "submit_attention", "submit_attention_bwd"):
         assert hasattr(ext, name)
+
+
+def test_external_op_skeletons_match_the_reference(L):
+    """set_external_{matmul,flash3_attention_fwd,flash3_attention_bwd}_skeleton of this library: nickname, argument list and
+    fingerprint pinned (the matmul digest is the one the reference's own wrapper produces, see the test above), each digest the
+    plain SHA-256 of the header; when the reference's wrappers were compiled here, all three skeletons are compared with theirs
+    byte for byte (als244/dataflow_lib src/set_ops/src/set_external_op_skeletons.c:4-243)."""
+    import hashlib
+    from dataflow_lib_b200 import abi
+    D = abi.DataflowDatatype
+    IS, FS, VP, INT, U64, U64S = int(D.INT_SCALAR), int(D.FP32_SCALAR), int(D.VOID), int(D.INT), int(D.UINT64), int(D.UINT64_SCALAR)
+    want = {
+        "set_external_matmul_skeleton": ("matmul", [IS] * 11 + [FS, FS] + [VP] * 4 + [U64, VP]),
+        "set_external_flash3_attention_fwd_skeleton": ("flash3_attention_fwd", [IS] * 4 + [INT, INT, IS, INT, INT, IS, IS, IS, IS] + [VP] * 5 + [U64S, VP]),
+        "set_external_flash3_attention_bwd_skeleton": ("flash3_attention_bwd", [IS] * 4 + [INT, INT, IS, INT, INT, IS, IS, IS, IS] + [VP] * 9 + [U64S, VP]),
+    }
+    so = os.path.join(ROOT, "oracle", "_ref", "libref_external_ops.so")
+    ext = C.CDLL(so) if os.path.exists(so) else None
+    for fn, (nick, dts) in want.items():
+        sk = abi.OpSkeleton()
+        C.memset(C.byref(sk), 0xAB, C.sizeof(sk))
+        getattr(L, fn)(C.byref(sk))
+        assert sk.header.op_nickname.decode() == nick and sk.header.num_args == len(dts)
+        names = [abi.DataflowDatatype(d).name for d in list(sk.header.arg_dtypes)[:sk.header.num_args]]
+        assert list(sk.header.arg_dtypes)[:sk.header.num_args] == dts, names
+        assert bytes(sk.identifier.fingerprint).hex() == hashlib.sha256(bytes(sk.header)).hexdigest()
+        if ext is not None:
+            theirs = abi.OpSkeleton()
+            C.memset(C.byref(theirs), 0, C.sizeof(theirs))
+            getattr(ext, fn)(C.byref(theirs))
+            assert bytes(theirs) == bytes(sk), fn
+    sk = abi.OpSkeleton()
+    L.set_external_matmul_skeleton(C.byref(sk))
+    assert bytes(sk.identifier.fingerprint).hex() == "2a113b16e997d04b8408f9aa299dd5a80bb77d29c95c8cc78270410ef84f3590"
+
+
+def test_external_op_wrappers_build_the_reference_argument_lists(L):
+    """submit_matmul / submit_attention / submit_attention_bwd hand the handle an Op whose op_args point at the values in the
+    reference's order (src/dataflow_ops/src/matmul_op.c:33-51, attention_op.c:55-74, 107-130); checked with a handle whose submit_op
+    is a Python callback. An unregistered op (callback returns non-zero) makes the wrapper return -1."""
+    from dataflow_lib_b200 import abi
+    seen = {}
+
+    def capture(handle, op_ptr, stream_id):
+        op = op_ptr.contents
+        n = op.op_skeleton.header.num_args
+        seen["nick"], seen["stream"] = op.op_skeleton.header.op_nickname.decode(), stream_id
+        seen["args"] = [op.op_args[i] for i in range(n)]
+        dts = list(op.op_skeleton.header.arg_dtypes)[:n]
+        vals = []
+        for a, dt in zip(seen["args"], dts):
+            name = abi.DataflowDatatype(dt).name
+            ctype = {"INT_SCALAR": C.c_int, "FP32_SCALAR": C.c_float, "UINT64": C.c_uint64, "UINT64_SCALAR": C.c_uint64}.get(name, C.c_void_p)
+            vals.append(C.cast(a, C.POINTER(ctype)).contents.value)
+        seen["vals"] = vals
+        return seen.get("rc", 0)
+
+    h = abi.DataflowHandleStruct()
+    cb = type(h.submit_op)(capture)
+    h.submit_op = cb
+    BF16, FP32, NONE = int(abi.DataflowDatatype.BF16), int(abi.DataflowDatatype.FP32), int(abi.DataflowDatatype.NONE)
+    assert L.submit_matmul(C.byref(h), 3, BF16, BF16, NONE, BF16, FP32, 1, 0, 64, 32, 16, 1.5, 0.25, 0x1000, 0x2000, None, 0x4000, 4096, 0x5000) == 0
+    assert seen["nick"] == "matmul" and seen["stream"] == 3
+    assert seen["vals"] == [0, BF16, BF16, NONE, BF16, FP32, 1, 0, 64, 32, 16, 1.5, 0.25, 0x1000, 0x2000, None, 0x4000, 4096, 0x5000]
+    assert L.submit_attention(C.byref(h), 1, BF16, 2, 100, 120, 0x10, 0x20, 60, 0x30, 0x40, 70, 32, 8, 128, 0x50, 0x60, 0x70, 0x80, 0x90, 77, 0xA0) == 0
+    assert seen["nick"] == "flash3_attention_fwd"
+    assert seen["vals"] == [BF16, 2, 100, 120, 0x10, 0x20, 60, 0x30, 0x40, 70, 32, 8, 128, 0x50, 0x60, 0x70, 0x80, 0x90, 77, 0xA0]
+    assert L.submit_attention_bwd(C.byref(h), 1, BF16, 2, 100, 120, 0x10, 0x20, 60, 0x30, 0x40, 70, 32, 8, 128, 0x50, 0x60, 0x70, 0x80, 0x90,
+                                  0xB0, 0xC0, 0xD0, 0xE0, 88, 0xF0) == 0
+    assert seen["nick"] == "flash3_attention_bwd"
+    assert seen["vals"] == [BF16, 2, 100, 120, 0x10, 0x20, 60, 0x30, 0x40, 70, 32, 8, 128, 0x50, 0x60, 0x70, 0x80, 0x90, 0xB0, 0xC0, 0xD0, 0xE0, 88, 0xF0]
+    seen["rc"] = -1
+    assert L.submit_matmul(C.byref(h), 0, BF16, BF16, NONE, BF16, FP32, 0, 0, 8, 8, 8, 1.0, 0.0, None, None, None, None, 0, None) == -1

@@ -23,10 +23,18 @@ EXT_OPS, MATMUL = os.path.join(REF_DIR, "libref_external_ops.so"), os.path.join(
 
 
 @pytest.mark.skipif(not (os.path.exists(EXT_OPS) and os.path.exists(MATMUL)), reason="reference plug-ins not built (make -C oracle ref)")
-def test_reference_matmul_plugin_on_this_handle():
+@pytest.mark.parametrize("wrappers", ["reference", "own"])
+def test_reference_matmul_plugin_on_this_handle(wrappers):
+    """wrappers = "reference": submit_matmul and the matmul skeleton come from the reference's own compiled code; "own": from this
+    library (same identity, same argument list), so the plug-in is found and fed the same way."""
     from dataflow_lib_b200 import DataflowHandle, abi
     from dataflow_lib_b200.abi import DataflowDatatype as DT
-    ext = C.CDLL(EXT_OPS)
+    if wrappers == "reference":
+        ext = C.CDLL(EXT_OPS)
+    else:
+        from dataflow_lib_b200 import _lib
+        ext = C.CDLL(_lib.LIB_PATH)
+        ext.set_external_matmul_skeleton.restype = None
     h = DataflowHandle(device_id=0, num_streams=1)
     sk = abi.OpSkeleton()
     ext.set_external_matmul_skeleton(C.byref(sk))
