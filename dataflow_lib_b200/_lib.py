@@ -126,6 +126,10 @@ HOST_ABI = {
     "submit_matmul": (_i, [_H, _i, _i, _i, _i, _i, _i, _i, _i, _i, _i, _i, _f, _f, _vp, _vp, _vp, _vp, _u64, _vp]),
     "submit_attention": (_i, [_H, _i, _i, _i, _i, _i, _vp, _vp, _i, _vp, _vp, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _u64, _vp]),
     "submit_attention_bwd": (_i, [_H, _i, _i, _i, _i, _i, _vp, _vp, _i, _vp, _vp, _i, _i, _i, _i] + [_vp] * 9 + [_u64, _vp]),
+    "submit_transformer_head": (_i, [_H, _i, _i, C.POINTER(abi.TransformerBlockTransition), C.POINTER(abi.TransformerHead),
+                                    C.POINTER(abi.TransformerHeadActivations), C.POINTER(abi.TransformerModelOutput),
+                                    C.POINTER(abi.TransformerHead), C.POINTER(abi.TransformerHeadActivations),
+                                    C.POINTER(abi.TransformerBlockTransition), C.POINTER(abi.TransformerBlockTransition)]),
     # external-op plug-in symbols (ops_external.c)
     "dataflow_b200_workspace_init": (_i, [_H, _vp]),
     "dataflow_b200_rms_norm": (_i, [_H, _i, _vp, _vp]),

@@ -113,3 +113,28 @@ DataflowHandleStruct._fields_ = [
 ]
 
 assert C.sizeof(OpSkeletonHeader) == 388 and C.sizeof(OpSkeleton) == 420 and C.sizeof(Op) == 680
+
+
+# ---- include/dataflow_transformer.h -------------------------------------------------------------------------------------
+class EmbeddingConfig(C.Structure):
+    _fields_ = [("vocab_size", C.c_int), ("embedding_size", C.c_int)]
+
+
+class TransformerHead(C.Structure):
+    _fields_ = [("fwd_dt", C.c_int), ("bwd_dt", C.c_int), ("compute_dt", C.c_int), ("eps", C.c_float),
+                ("embedding_config", EmbeddingConfig), ("buffer", C.c_void_p), ("w_head_norm", C.c_void_p), ("w_head", C.c_void_p)]
+
+
+class TransformerHeadActivations(C.Structure):
+    _fields_ = [("num_tokens", C.c_int), ("buffer", C.c_void_p), ("head_norm_out", C.c_void_p), ("head_norm_weighted_sums", C.c_void_p),
+                ("head_norm_rms_vals", C.c_void_p), ("head_out", C.c_void_p), ("kernel_workspace", C.c_void_p),
+                ("kernel_workspaceBytes", C.c_uint64)]
+
+
+class TransformerBlockTransition(C.Structure):
+    _fields_ = [("batch_config", C.c_void_p), ("X", C.c_void_p)]
+
+
+class TransformerModelOutput(C.Structure):
+    _fields_ = [("batch_config", C.c_void_p), ("token_ids", C.c_void_p), ("labels", C.c_void_p), ("logits", C.c_void_p),
+                ("loss", C.c_void_p), ("loss_avg", C.c_float)]

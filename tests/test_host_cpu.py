@@ -315,3 +315,76 @@ def test_external_op_wrappers_build_the_reference_argument_lists(L):
     assert seen["vals"] == [BF16, 2, 100, 120, 0x10, 0x20, 60, 0x30, 0x40, 70, 32, 8, 128, 0x50, 0x60, 0x70, 0x80, 0x90, 0xB0, 0xC0, 0xD0, 0xE0, 88, 0xF0]
     seen["rc"] = -1
     assert L.submit_matmul(C.byref(h), 0, BF16, BF16, NONE, BF16, FP32, 0, 0, 8, 8, 8, 1.0, 0.0, None, None, None, None, 0, None) == -1
+
+
+def _head_containers(abi, T=8, d=16, V=64):
+    BF16, FP32 = int(abi.DataflowDatatype.BF16), int(abi.DataflowDatatype.FP32)
+    head = abi.TransformerHead(BF16, BF16, FP32, 1e-5, abi.EmbeddingConfig(V, d), None, 0x1000, 0x2000)
+    act = abi.TransformerHeadActivations(T, None, 0x3000, 0x3100, 0x3200, 0x3300, 0x3400, 4096)
+    xin = abi.TransformerBlockTransition(None, 0x4000)
+    out = abi.TransformerModelOutput(None, None, 0x5000, 0x5100, 0x5200, 0.0)
+    ghead = abi.TransformerHead(BF16, BF16, FP32, 1e-5, abi.EmbeddingConfig(V, d), None, 0x6000, 0x6100)
+    gact = abi.TransformerHeadActivations(T, None, 0x7000, None, None, 0x7300, 0x7400, 8192)
+    gs, gs2 = abi.TransformerBlockTransition(None, 0x8000), abi.TransformerBlockTransition(None, 0x9000)
+    return head, act, xin, out, ghead, gact, gs, gs2
+
+
+def test_transformer_head_submits_the_reference_chain(L):
+    """submit_transformer_head on a handle made of Python callbacks: the ops arrive in the reference's order
+    (src/dataflow_models/dataflow_transformer/src/dataflow_transformer.c:316-492) with the buffers wired as documented, the copy of
+    the head gradient is ordered after the compute stream, and a failing step stops the chain with that step's code."""
+    from dataflow_lib_b200 import abi
+    log = []
+
+    def on_op(handle, op_ptr, stream_id):
+        op = op_ptr.contents
+        n = op.op_skeleton.header.num_args
+        ptrs = []
+        for i, dt in enumerate(list(op.op_skeleton.header.arg_dtypes)[:n]):
+            name = abi.DataflowDatatype(dt).name
+            if not name.endswith("_SCALAR") and name != "UINT64":
+                ptrs.append(C.cast(op.op_args[i], C.POINTER(C.c_void_p)).contents.value)
+        nick = op.op_skeleton.header.op_nickname.decode()
+        log.append((nick, stream_id, ptrs))
+        return -7 if nick == fail_on[0] else 0
+
+    fail_on = [None]
+    h = abi.DataflowHandleStruct()
+    state = C.c_int(0)
+    cbs = {
+        "submit_op": type(h.submit_op)(on_op),
+        "get_stream_state": type(h.get_stream_state)(lambda hh, s: (log.append(("state", s, [])), C.addressof(state))[1]),
+        "submit_dependency": type(h.submit_dependency)(lambda hh, s, st: (log.append(("dep", s, [st])), 0)[1]),
+        "submit_peer_transfer": type(h.submit_peer_transfer)(lambda hh, s, dst, src, n: (log.append(("copy", s, [dst, src, n])), 0)[1]),
+    }
+    for k, v in cbs.items():
+        setattr(h, k, v)
+    head, act, xin, out, ghead, gact, gs, gs2 = _head_containers(abi)
+    T, d, V = 8, 16, 64
+    r = C.byref
+    # forward only
+    assert L.submit_transformer_head(r(h), 2, 3, r(xin), r(head), r(act), r(out), None, None, None, None) == 0
+    assert [e[0] for e in log] == ["rms_norm_BF16", "matmul", "softmax_BF16_BF16"] and all(e[1] == 2 for e in log)
+    assert log[0][2] == [0x1000, 0x4000, 0x3000, 0x3100, 0x3200]          # weight, X, out, weighted sums, rms values
+    assert log[1][2] == [0x2000, 0x3000, None, 0x3300, 0x3400]            # A = w_head, B = head_norm_out, C, D = logits, workspace
+    assert log[2][2] == [0x3300, 0x5100]
+    # forward + backward with the copy to the next location
+    log.clear()
+    assert L.submit_transformer_head(r(h), 2, 3, r(xin), r(head), r(act), r(out), r(ghead), r(gact), r(gs), r(gs2)) == 0
+    assert [e[0] for e in log] == ["rms_norm_BF16", "matmul", "softmax_cross_entropy_BF16_BF16", "matmul", "matmul", "rms_norm_bwd_x_BF16_BF16",
+                                   "rms_norm_bwd_w_BF16_BF16", "state", "dep", "copy"]
+    assert log[2][2] == [0x3300, 0x5000, 0x5100, 0x5200, None]            # logits, labels, dlogits, row losses, no loss sum
+    assert log[3][2] == [0x2000, 0x5100, None, 0x7000, 0x7400]            # d(head_norm_out) = w_head . dlogits
+    assert log[4][2] == [0x3000, 0x5100, 0x6100, 0x6100, 0x7400]          # dW_head += head_norm_out . dlogits^T
+    assert log[5][2] == [0x3100, 0x3200, 0x1000, 0x4000, 0x7000, 0x8000]  # sums, rms, weight, X, upstream, dX
+    assert log[6][2] == [0x3200, 0x4000, 0x7000, 0x6000]                  # rms, X, upstream, dW_norm
+    assert log[7][1] == 2 and log[8][1] == 3 and log[8][2] == [C.addressof(state)]
+    assert log[9][1] == 3 and log[9][2] == [0x9000, 0x8000, T * d * 2]
+    # a failing step ends the chain with its code
+    log.clear()
+    fail_on[0] = "softmax_cross_entropy_BF16_BF16"
+    assert L.submit_transformer_head(r(h), 0, 1, r(xin), r(head), r(act), r(out), r(ghead), r(gact), r(gs), None) == -1
+    assert [e[0] for e in log] == ["rms_norm_BF16", "matmul", "softmax_cross_entropy_BF16_BF16"]
+    # a backward pass without its containers is refused before anything is submitted
+    log.clear()
+    assert L.submit_transformer_head(r(h), 0, 1, r(xin), r(head), r(act), r(out), r(ghead), None, None, None) == -1 and not log
