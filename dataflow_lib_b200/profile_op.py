@@ -21,13 +21,16 @@ def main():
                                    "fp8_peak"])
     ap.add_argument("--tokens", type=int, default=2048)
     ap.add_argument("--iters", type=int, default=3)
-    ap.add_argument("--dtype", default="bf16", choices=["bf16", "fp16", "fp32"])
+    ap.add_argument("--dtype", default="bf16", choices=["bf16", "fp16", "fp32", "fp8e4m3", "fp8e5m2"],
+                    help="datatype of the forward tensors; with an fp8 type the gradients are bf16 (the registered fp8 x bf16 pairs)")
     a = ap.parse_args()
-    dt = {"bf16": torch.bfloat16, "fp16": torch.float16, "fp32": torch.float32}[a.dtype]
+    dt = {"bf16": torch.bfloat16, "fp16": torch.float16, "fp32": torch.float32, "fp8e4m3": torch.float8_e4m3fn, "fp8e5m2": torch.float8_e5m2}[a.dtype]
+    bdt = torch.bfloat16 if a.dtype.startswith("fp8") else dt        # datatype of gradients
     T = a.tokens
     g = torch.Generator(device="cuda").manual_seed(0)
     rn = lambda *s: torch.randn(*s, device="cuda", generator=g).to(dt)
-    es = torch.empty(0, dtype=dt).element_size()
+    rnb = lambda *s: torch.randn(*s, device="cuda", generator=g).to(bdt)
+    es, bes = torch.empty(0, dtype=dt).element_size(), torch.empty(0, dtype=bdt).element_size()
     if a.op == "fp8_peak":
         # the tensor-core ceiling for the FFN numbers: a library e4m3 GEMM (torch._scaled_mm -> cuBLASLt). Burst = best single launch
         # of 8192^3; sustained = the FFN's own shapes, 5 launches back to back (what profile_op reports for this library's kernels)
@@ -99,31 +102,33 @@ def main():
         print(f"{a.op} tokens={T} d={D} f={F}: {ms * 1e3:.1f} us/launch, {flops / (ms * 1e-3) / 1e12:.0f} TFLOP/s ({flops / 1e12:.2f} TFLOP)")
         return
     if a.op.startswith("rms_norm"):
-        X, w, dY, dX = rn(T, D), (1 + 0.02 * torch.randn(D, device="cuda", generator=g)).to(dt), rn(T, D), torch.zeros(T, D, device="cuda", dtype=dt)
-        Y, dW = torch.empty_like(X), torch.zeros(D, device="cuda", dtype=dt)
+        X, w, dY, dX = rn(T, D), (1 + 0.02 * torch.randn(D, device="cuda", generator=g)).to(dt), rnb(T, D), torch.zeros(T, D, device="cuda", dtype=bdt)
+        Y, dW = torch.empty_like(X), torch.zeros(D, device="cuda", dtype=bdt)
         ws, rms = torch.empty(T, device="cuda"), torch.empty(T, device="cuda")
         ops.rms_norm(T, D, 1e-5, w, X, Y, ws, rms)
         fn = {"rms_norm": lambda: ops.rms_norm(T, D, 1e-5, w, X, Y, ws, rms),
               "rms_norm_bwd_x": lambda: ops.rms_norm_bwd_x(T, D, 1e-5, ws, rms, w, X, dY, dX),
               "rms_norm_bwd_w": lambda: ops.rms_norm_bwd_w(T, D, 1e-5, rms, X, dY, dW)}[a.op]
-        nbytes = T * D * es * {"rms_norm": 2, "rms_norm_bwd_x": 4, "rms_norm_bwd_w": 2}[a.op]
+        nbytes = T * D * {"rms_norm": 2 * es, "rms_norm_bwd_x": es + 3 * bes, "rms_norm_bwd_w": es + bes}[a.op]
     elif a.op.startswith("rope"):
-        Q, K, pos = rn(T, NH * HD), rn(T, NKV * HD), torch.arange(T, device="cuda", dtype=torch.int32)
+        rdt = dt if a.op == "rope" else bdt                      # the backward op works on gradients
+        Q, K = (torch.randn(T, n * HD, device="cuda", generator=g).to(rdt) for n in (NH, NKV))
+        pos = torch.arange(T, device="cuda", dtype=torch.int32)
         f = ops.rope if a.op == "rope" else ops.rope_bwd_x
         fn = lambda: f(T * NH * HD, NH * HD, HD, NKV, 500000, pos, Q, K)
-        nbytes = 2 * T * (NH + NKV) * HD * es
+        nbytes = 2 * T * (NH + NKV) * HD * Q.element_size()
     elif a.op.startswith("swiglu"):
-        x1, x3, dY = rn(T, F), rn(T, F), rn(T, F)
-        out, d1, d3 = torch.empty_like(x1), torch.empty_like(x1), torch.empty_like(x1)
+        x1, x3, dY = rn(T, F), rn(T, F), rnb(T, F)
+        out, d1, d3 = torch.empty_like(x1), torch.empty_like(dY), torch.empty_like(dY)
         fn = (lambda: ops.swiglu(T, F, x1, x3, out)) if a.op == "swiglu" else (lambda: ops.swiglu_bwd_x(T, F, x1, x3, dY, d1, d3))
-        nbytes = T * F * es * (3 if a.op == "swiglu" else 5)
+        nbytes = T * F * (3 * es if a.op == "swiglu" else 2 * es + 3 * bes)
     else:
         L = (2 * torch.randn(T, V, device="cuda", generator=g)).to(dt)
-        out = torch.empty_like(L)
+        out = torch.empty(T, V, device="cuda", dtype=bdt)
         labels = torch.randint(0, V, (T,), device="cuda", generator=g, dtype=torch.int32)
         loss = torch.zeros(2, device="cuda")
         fn = (lambda: ops.softmax(T, V, L, out)) if a.op == "softmax" else (lambda: ops.softmax_cross_entropy(T, V, L, labels, out, None, loss))
-        nbytes = 2 * T * V * es
+        nbytes = T * V * (es + bes)
     fn()
     torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
