@@ -165,9 +165,9 @@ template <> struct RowMath<f16_t, f16_t> {
 // softmax_<f16|bf16>_fp32 kernels (src/ops/nvidia/loss/softmax.cu:965-1249), which keep their scratch in the input type and
 // store exp(..) / total unrounded. ARGMAX additionally writes the smallest index holding the row maximum to arg_maxs[row]
 // (the reference lets whichever thread sees the maximum last win, :1057-1059).
-// SPT > 0 (16-bit inputs only): a thread owns SPT more packets of the row in SHARED memory (slots [k][tid], fetched with
+// SPT > 0 (16- and 32-bit inputs): a thread owns SPT more packets of the row in SHARED memory (slots [k][quarter][tid], fetched with
 // per-thread asynchronous 16-byte copies and read back only by the thread that requested them, so no barrier guards them).
-// A 512-thread CTA then covers (CPT + SPT) x 512 = 8192 packets with 64 KB of shared memory and 64 registers per thread, so two
+// A 512-thread CTA then covers (CPT + SPT) x 512 packets (8 + 8 of 16 bytes, or 4 + 4 of 32 bytes for fp32) with 64 KB of shared memory and 64 registers per thread, so two
 // CTAs stay resident per SM and one computes exponentials while the other waits for memory. Rows of up to 65536 elements take one
 // such CTA, rows of up to 131072 elements a cluster of two, up to 262144 a cluster of four. Measured at 16384 x 128256 bf16: cluster of 4 register-only CTAs
 // 1.93 ms; one 1024-thread CTA with 128 KB of shared memory (no cluster, but one CTA per SM) 1.76 ms; the cluster of two 1.64 ms with
@@ -183,9 +183,10 @@ softmax_rows_kernel(int n_rows, int n_cols, int slice_chunks, const void * __res
                     const uint32_t * __restrict__ labels, float * __restrict__ row_loss, uint32_t * __restrict__ arg_maxs, unsigned int * status) {
 	static_assert(!FUSE_CE || sizeof(OUT) == sizeof(B), "the fused cross-entropy step works in the output type");
 	constexpr int FW = E / Word<F>::EPW;
-	static_assert(SPT == 0 || FW == 4, "shared-memory packets are 16 bytes");
+	static_assert(SPT == 0 || FW % 4 == 0, "shared-memory packets are made of 16-byte quarters");
+	constexpr int QW = FW / 4;                             // 16-byte quarters per packet: 1 for 16-bit elements, 2 for fp32
 	constexpr int NPK = CPT + SPT;                         // packets per thread: the first CPT in registers, the rest in shared memory
-	extern __shared__ uint4 s_pack[];                      // [SPT][blockDim.x]
+	extern __shared__ uint4 s_pack[];                      // [SPT][QW][blockDim.x]
 	__shared__ float s_warp_max[32];
 	__shared__ float s_warp_part[SOFTMAX_MAX_THREADS / 32][8];
 	__shared__ float s_peer_max[SOFTMAX_MAX_CLUSTER];      // [r] pushed here by CTA r of the cluster
@@ -238,8 +239,12 @@ softmax_rows_kernel(int n_rows, int n_cols, int slice_chunks, const void * __res
 		for (int k = 0; k < SPT; k++) {
 			const int c = c_begin + tid + (CPT + k) * nthr;
 			if (c < c_end) {
-				const uint32_t dst = (uint32_t) __cvta_generic_to_shared(&s_pack[k * nthr + tid]);
-				asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" :: "r"(dst), "l"(reinterpret_cast<const char *>(X) + (row_elem + (uint64_t) c * E) * 2) : "memory");
+				const char * src = reinterpret_cast<const char *>(X) + (row_elem + (uint64_t) c * E) * (4 / Word<F>::EPW);
+				#pragma unroll
+				for (int q = 0; q < QW; q++) {
+					const uint32_t dst = (uint32_t) __cvta_generic_to_shared(&s_pack[(k * QW + q) * nthr + tid]);
+					asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" :: "r"(dst), "l"(src + 16 * q) : "memory");
+				}
 			}
 		}
 		asm volatile("cp.async.commit_group;" ::: "memory");
@@ -256,14 +261,22 @@ softmax_rows_kernel(int n_rows, int n_cols, int slice_chunks, const void * __res
 			s_label[2] = mine ? (uint32_t) (rel / nthr) : 0u;            // index of the packet in that thread
 		}
 	}
+	auto shared_packet = [&](int ks, uint32_t (&w)[FW]) {   // shared-memory packet ks of this thread
+		if constexpr (SPT > 0) {
+			#pragma unroll
+			for (int q = 0; q < QW; q++) {
+				const uint4 v = s_pack[(ks * QW + q) * nthr + tid];
+				w[4 * q] = v.x; w[4 * q + 1] = v.y; w[4 * q + 2] = v.z; w[4 * q + 3] = v.w;
+			}
+		}
+	};
 	// packet k of this thread: registers for k < CPT, its own shared-memory slot otherwise (k is a compile-time constant after unrolling)
 	auto packet = [&](int k, uint32_t (&w)[FW]) {
 		if (k < CPT) {
 			#pragma unroll
 			for (int i = 0; i < FW; i++) w[i] = raw[k < CPT ? k : 0][i];
 		} else if constexpr (SPT > 0) {
-			const uint4 v = s_pack[(k - CPT) * nthr + tid];
-			w[0] = v.x; w[1] = v.y; w[2] = v.z; w[3] = v.w;
+			shared_packet(k - CPT, w);
 		}
 	};
 
@@ -313,7 +326,7 @@ softmax_rows_kernel(int n_rows, int n_cols, int slice_chunks, const void * __res
 			const int kl = (int) s_label[2], j = (int) (s_label[0] % E);
 			uint32_t w[FW];
 			if (kl >= CPT) {
-				if constexpr (SPT > 0) { const uint4 v = s_pack[(kl - CPT) * nthr + tid]; w[0] = v.x; w[1] = v.y; w[2] = v.z; w[3] = v.w; }
+				shared_packet(kl - CPT, w);
 			} else {
 				#pragma unroll
 				for (int k = 0; k < CPT; k++) {
@@ -473,22 +486,31 @@ loss_sum_kernel(int n_rows, int n_cols, const float * __restrict__ row_loss, con
 
 struct SoftmaxGeometry { int cluster, threads, cpt, slice_chunks, spt; };      // spt > 0: packets per thread kept in shared memory
 
-constexpr int SOFTMAX_SPT = 8;                            // shared-memory packets per thread of the one-CTA-per-row form for long rows
+// The form with shared-memory packets: per thread 8 + 8 packets of 16 bytes (16-bit elements) or 4 + 4 packets of 32 bytes (fp32), i.e.
+// 32 words of the row in registers and 64 KB of shared memory per 512-thread CTA in both cases.
+constexpr int SOFTMAX_SPT_16BIT = 8, SOFTMAX_SPT_FP32 = 4;
 
-static bool softmax_geometry(int n_chunks, bool packets_16_bytes, SoftmaxGeometry * g) {
+// packet_bytes = bytes of one 8-element chunk in the input type (8 for fp8, 16 for fp16 / bf16, 32 for fp32)
+static bool softmax_geometry(int n_chunks, int packet_bytes, SoftmaxGeometry * g) {
 	g->spt = 0;
-	// Long rows of 16-bit elements: CTAs of up to 512 threads with 8 packets per thread in registers and 8 in shared memory (64 KB, two
-	// CTAs per SM); one CTA for rows of up to 65536 elements, a cluster of two up to 131072, of four up to 262144.
-	if (packets_16_bytes && n_chunks > SOFTMAX_MAX_THREADS * SOFTMAX_MAX_CPT && n_chunks <= 4 * SOFTMAX_MAX_THREADS * (SOFTMAX_MAX_CPT + SOFTMAX_SPT) && SOFTMAX_MAX_CPT == 8 && SOFTMAX_MAX_THREADS == 512) {
-		const int per_cta = SOFTMAX_MAX_THREADS * (SOFTMAX_MAX_CPT + SOFTMAX_SPT);
-		const int cluster = n_chunks > 2 * per_cta ? 4 : n_chunks > per_cta ? 2 : 1;
+	// Long rows of 16- and 32-bit elements: CTAs of up to 512 threads with half of their packets in registers and half in shared memory
+	// (two CTAs per SM). 16-bit: one CTA for rows of up to 65536 elements, a cluster of two up to 131072, of four up to 262144; fp32: one
+	// CTA up to 32768 elements, clusters of two, four and eight up to 262144. Shorter rows (<= 32 words per thread) stay in registers.
+	const int half = packet_bytes == 16 ? SOFTMAX_SPT_16BIT : packet_bytes == 32 ? SOFTMAX_SPT_FP32 : 0;
+	if (half && n_chunks > SOFTMAX_MAX_THREADS * half && n_chunks <= SOFTMAX_MAX_CLUSTER * SOFTMAX_MAX_THREADS * 2 * half &&
+	    SOFTMAX_MAX_CPT == 8 && SOFTMAX_MAX_THREADS == 512) {
+		const int per_cta = SOFTMAX_MAX_THREADS * 2 * half;
+		int cluster = 1;
+		while (cluster * per_cta < n_chunks) cluster *= 2;
 		int slice = (n_chunks + cluster - 1) / cluster;
 		slice = (slice + SLICE_ALIGN_CHUNKS - 1) / SLICE_ALIGN_CHUNKS * SLICE_ALIGN_CHUNKS;
-		int threads = (slice + SOFTMAX_MAX_CPT + SOFTMAX_SPT - 1) / (SOFTMAX_MAX_CPT + SOFTMAX_SPT);
+		int threads = (slice + 2 * half - 1) / (2 * half);
 		threads = (threads + 127) / 128 * 128;
-		g->cluster = cluster; g->threads = threads; g->cpt = SOFTMAX_MAX_CPT; g->slice_chunks = slice;
-		g->spt = SOFTMAX_SPT;
-		return true;
+		if (cluster <= SOFTMAX_MAX_CLUSTER && threads <= SOFTMAX_MAX_THREADS) {
+			g->cluster = cluster; g->threads = threads; g->cpt = half; g->slice_chunks = slice;
+			g->spt = half;
+			return true;
+		}
 	}
 	// smallest cluster whose CTAs (<= 512 threads, <= 8 packets per thread) cover the row
 	int cluster = 1;
@@ -514,10 +536,13 @@ static bool softmax_geometry(int n_chunks, bool packets_16_bytes, SoftmaxGeometr
 template <typename F, typename B, bool FUSE_CE, typename OUT, bool ARGMAX>
 static int launch_softmax_long_rows(const SoftmaxGeometry & g, int n_rows, int n_cols, const void * X, void * out, const uint32_t * labels, float * row_loss,
                                     uint32_t * arg_maxs, cudaStream_t stream) {
-	if constexpr (Word<F>::EPW != 2) {
+	if constexpr (Word<F>::EPW > 2) {
 		return set_error(DFB200_ERR_DTYPE, "softmax: internal geometry error");
 	} else {
-		const size_t smem = (size_t) g.spt * g.threads * sizeof(uint4);
+		constexpr int HALF = Word<F>::EPW == 2 ? SOFTMAX_SPT_16BIT : SOFTMAX_SPT_FP32;       // packets per thread in registers = in shared memory
+		constexpr int QW = (E / Word<F>::EPW) / 4;
+		if (g.spt != HALF || g.cpt != HALF) return set_error(DFB200_ERR_DTYPE, "softmax: internal geometry error");
+		const size_t smem = (size_t) HALF * QW * g.threads * sizeof(uint4);
 		unsigned int * status = kernel_status_word(STATUS_SOFTMAX);
 		cudaLaunchConfig_t cfg = {};
 		cfg.gridDim = dim3((unsigned) n_rows * g.cluster, 1, 1);
@@ -528,8 +553,8 @@ static int launch_softmax_long_rows(const SoftmaxGeometry & g, int n_rows, int n
 		attr[0].id = cudaLaunchAttributeClusterDimension;
 		attr[0].val.clusterDim.x = g.cluster; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
 		cfg.attrs = attr; cfg.numAttrs = 1;
-		auto kernel = g.cluster > 1 ? softmax_rows_kernel<F, B, 8, FUSE_CE, OUT, ARGMAX, SOFTMAX_SPT, true>
-		                            : softmax_rows_kernel<F, B, 8, FUSE_CE, OUT, ARGMAX, SOFTMAX_SPT, false>;
+		auto kernel = g.cluster > 1 ? softmax_rows_kernel<F, B, HALF, FUSE_CE, OUT, ARGMAX, HALF, true>
+		                            : softmax_rows_kernel<F, B, HALF, FUSE_CE, OUT, ARGMAX, HALF, false>;
 		allow_dyn_smem(reinterpret_cast<const void *>(kernel), smem);
 		const cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, n_rows, n_cols, g.slice_chunks, X, out, labels, row_loss, arg_maxs, status);
 		if (e != cudaSuccess) { cudaGetLastError(); return set_error(DFB200_ERR_CUDA, "softmax launch: %s", cudaGetErrorString(e)); }
@@ -603,7 +628,8 @@ static int check_softmax(const char * op, int fwd_dt, int bwd_dt, int n_rows, in
 	if (n_rows < 0 || n_cols <= 0) return set_error(DFB200_ERR_ARG, "%s: bad shape %d x %d", op, n_rows, n_cols);
 	if (n_cols % E) return set_error(DFB200_ERR_ARG, "%s: n_cols = %d is not a multiple of %d", op, n_cols, E);
 	if ((long long) n_rows * SOFTMAX_MAX_CLUSTER > 0x7fffffffLL) return set_error(DFB200_ERR_ARG, "%s: too many rows", op);
-	if (!softmax_geometry(n_cols / E, fwd_dt == DATAFLOW_FP16 || fwd_dt == DATAFLOW_BF16, g))
+	const int packet_bytes = fwd_dt == DATAFLOW_FP32 ? 32 : (fwd_dt == DATAFLOW_FP16 || fwd_dt == DATAFLOW_BF16) ? 16 : 8;
+	if (!softmax_geometry(n_cols / E, packet_bytes, g))
 		return set_error(DFB200_ERR_ARG, "%s: n_cols = %d exceeds the supported maximum of %d", op, n_cols,
 		                 SOFTMAX_MAX_CLUSTER * SOFTMAX_MAX_THREADS * SOFTMAX_MAX_CPT * E);
 	if (n_rows && (!X || !out)) return set_error(DFB200_ERR_ARG, "%s: NULL tensor argument", op);
