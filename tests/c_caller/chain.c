@@ -7,6 +7,7 @@
  * links and the library loads (no device needed).
  */
 #include "dataflow_api.h"
+#include "dataflow_transformer.h"
 
 #include <math.h>
 #include <stdio.h>
@@ -36,7 +37,15 @@ int main(int argc, char ** argv) {
 		Op_Skeleton sk;
 		set_native_rms_norm_skeleton(&sk, DATAFLOW_BF16);
 		printf("linked; %s has %d arguments\n", sk.header.op_nickname, sk.header.num_args);
-		return sk.header.num_args == 8 ? 0 : 1;
+		if (sk.header.num_args != 8) return 1;
+		/* the external-op identities and the head caller are reachable from C as well; a call without its containers is refused */
+		Op_Skeleton mm;
+		set_external_matmul_skeleton(&mm);
+		Transformer_Head head = { DATAFLOW_BF16, DATAFLOW_BF16, DATAFLOW_FP32, 1e-5f, { 128, 64 }, NULL, NULL, NULL };
+		printf("%s has %d arguments; head of %d x %d\n", mm.header.op_nickname, mm.header.num_args, head.embedding_config.vocab_size,
+		       head.embedding_config.embedding_size);
+		const int refused = submit_transformer_head(NULL, 0, 1, NULL, &head, NULL, NULL, NULL, NULL, NULL, NULL);
+		return (mm.header.num_args == 19 && refused == -1) ? 0 : 1;
 	}
 	const int rows = 512, cols = 1024, ffn = 2048;
 	const float eps = 1e-5f;

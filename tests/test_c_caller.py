@@ -22,7 +22,7 @@ def chain_binary(tmp_path_factory):
 
 def test_c_caller_links(chain_binary):
     res = subprocess.run([chain_binary, "link"], capture_output=True, text=True, timeout=60)
-    assert res.returncode == 0 and "rms_norm_BF16 has 8 arguments" in res.stdout, res.stdout + res.stderr
+    assert res.returncode == 0 and "rms_norm_BF16 has 8 arguments" in res.stdout and "matmul has 19 arguments" in res.stdout, res.stdout + res.stderr
 
 
 @pytest.mark.gpu
