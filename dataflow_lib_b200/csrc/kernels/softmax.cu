@@ -629,7 +629,7 @@ static int check_softmax(const char * op, int fwd_dt, int bwd_dt, int n_rows, in
 	if (n_cols % E) return set_error(DFB200_ERR_ARG, "%s: n_cols = %d is not a multiple of %d", op, n_cols, E);
 	if ((long long) n_rows * SOFTMAX_MAX_CLUSTER > 0x7fffffffLL) return set_error(DFB200_ERR_ARG, "%s: too many rows", op);
 	const int packet_bytes = fwd_dt == DATAFLOW_FP32 ? 32 : (fwd_dt == DATAFLOW_FP16 || fwd_dt == DATAFLOW_BF16) ? 16 : 8;
-	if (!softmax_geometry(n_cols / E, packet_bytes, g))
+	if (n_cols > SOFTMAX_MAX_CLUSTER * SOFTMAX_MAX_THREADS * SOFTMAX_MAX_CPT * E || !softmax_geometry(n_cols / E, packet_bytes, g))
 		return set_error(DFB200_ERR_ARG, "%s: n_cols = %d exceeds the supported maximum of %d", op, n_cols,
 		                 SOFTMAX_MAX_CLUSTER * SOFTMAX_MAX_THREADS * SOFTMAX_MAX_CPT * E);
 	if (n_rows && (!X || !out)) return set_error(DFB200_ERR_ARG, "%s: NULL tensor argument", op);

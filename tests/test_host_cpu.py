@@ -201,6 +201,10 @@ def test_handle_api_fails_cleanly_without_a_device(L, capfd):
     assert L.dfb200_swiglu(5, 1, 7, None, None, None, None) == -1
     assert b"multiple of 8" in L.dfb200_last_error()
     assert L.dfb200_rms_norm(1, 1, 8, 1e-5, None, None, None, None, None, None) == -2
+    # the softmax row limit holds in every datatype (the long-row geometries must not widen it silently)
+    for dt in (3, 4, 5, 6):
+        assert L.dfb200_softmax(dt, 5 if dt == 6 else dt, 1, 8 * 40000, 0x1000, 0x2000, None) != 0
+        assert b"exceeds the supported maximum of 262144" in L.dfb200_last_error()
 
 
 def test_own_op_identities_are_stable(L):
