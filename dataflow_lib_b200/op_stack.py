@@ -20,9 +20,10 @@ for it); callers that account time per kernel exclude it.
 Every op goes through the C-ABI launchers (ops.py); there is no CPU path.
 """
 import torch
+import torch.distributed as dist
 
 from . import ops
-from .sharding import allreduce_step
+from .sharding import allreduce_step, pack_reduction
 
 
 class OpStackStep:
@@ -55,6 +56,7 @@ class OpStackStep:
         self.WguT, self.WdT = [u8(d, 2 * f) for _ in range(L)], [u8(f, d) for _ in range(L)]
         self.W_vocab = e(V, d)
         self.marks = None                                        # a list while a step is being profiled: (segment name, CUDA event) pairs
+        self._xstream, self._xdone, self.reduced = None, None, None   # side stream, completion event and result of exchange_overlapped
         self.ffn_ws = torch.empty(int(ops._lib_.dfb200_swiglu_ffn_fp8_workspace_bytes(T, d, f)), dtype=torch.uint8, device=dev)   # forward and backward
 
     # ------------------------------------------------------------------ weights
@@ -144,10 +146,44 @@ class OpStackStep:
         allreduce_step(self.loss_sum, self.dW, group=group)
         self._mark("exchange")
 
-    def step(self, group=None):
+    def exchange_overlapped(self, group=None):
+        """The same all-reduce, taken off the compute stream: the packed buffer is filled on the compute stream, reduced on a side
+        stream and left in `self.reduced` ([loss sum, valid rows | dW_0 .. dW_L], fp32), so the next step's kernels run while this
+        rank waits for the slowest one. `loss_sum` and `dW` keep the rank's own values. The next exchange (or wait_exchange) waits
+        for this one before the packed buffer is reused."""
+        if not dist.is_initialized() or dist.get_world_size(group) == 1:
+            self.reduced = pack_reduction(self.loss_sum, self.dW)
+            self._mark("exchange")
+            return
+        cur = torch.cuda.current_stream()
+        if self._xstream is None:
+            self._xstream = torch.cuda.Stream()
+        self.wait_exchange()
+        buf = pack_reduction(self.loss_sum, self.dW)
+        buf.record_stream(self._xstream)
+        packed = torch.cuda.Event()
+        packed.record(cur)
+        with torch.cuda.stream(self._xstream):
+            self._xstream.wait_event(packed)
+            dist.all_reduce(buf, op=dist.ReduceOp.SUM, group=group)
+            self._xdone = torch.cuda.Event()
+            self._xdone.record(self._xstream)
+        self.reduced = buf
+        self._mark("exchange")
+
+    def wait_exchange(self):
+        """Orders the current stream after the last overlapped exchange (no host synchronisation)."""
+        if self._xdone is not None:
+            torch.cuda.current_stream().wait_event(self._xdone)
+            self._xdone = None
+
+    def step(self, group=None, overlap=False):
         self.forward()
         self.backward()
-        self.exchange(group)
+        if overlap:
+            self.exchange_overlapped(group)
+        else:
+            self.exchange(group)
 
     # launches of this library's kernels in one step (for accounting): per layer fwd rms 1 + rope 1 + ffn 4 (2 quantise, 2 GEMM),
     # bwd ffn 4 + rope 1 + bwd_w 2 + bwd_x 1; head rms 1 + softmax/CE 2 (rows + loss sum) + bwd_w 2 + bwd_x 1
