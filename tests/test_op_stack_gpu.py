@@ -87,3 +87,25 @@ def test_stack_matches_oracle_composition():
     for l in range(L + 1):
         assert _rel_l2(f32(to_host(st.dW[l], O.BF16), O.BF16), f32(dW[l], O.BF16)) < 6e-2, l
     assert st.library_launches_per_step() == L * 14 + 6
+
+
+def test_overlapped_exchange_on_one_rank_keeps_the_step():
+    """step(overlap=True) without a process group: the step's results are unchanged and `reduced` is the packed buffer
+    [loss sum, valid rows | dW_0 .. dW_L] that a multi-rank run would have all-reduced (bench.py checks the multi-rank case against
+    the in-stream exchange on the GPUs it runs on)."""
+    from dataflow_lib_b200.op_stack import OpStackStep
+    from dataflow_lib_b200.sharding import pack_reduction
+
+    st = OpStackStep(T, D, F, HEADS, KV, HD, V, L, EPS, THETA)
+    st.random_weights(seed=3)
+    g = torch.Generator(device="cuda").manual_seed(5)
+    st.x[0].copy_(torch.randn(T, D, device="cuda", generator=g).bfloat16())
+    st.labels.copy_(torch.randint(0, V, (T,), device="cuda", generator=g, dtype=torch.int32))
+    st.step()
+    loss, dW = st.loss_sum.clone(), st.dW_all.clone()
+    st.step(overlap=True)
+    st.wait_exchange()
+    torch.cuda.synchronize()
+    assert torch.equal(st.loss_sum, loss) and torch.equal(st.dW_all, dW)
+    assert torch.equal(st.reduced, pack_reduction(loss, list(dW.unbind(0))))
+    assert st.reduced.numel() == 2 + (L + 1) * D and st.reduced[1].item() == T
