@@ -1,8 +1,8 @@
 // Row softmax, the cross-entropy gradient step, and the two fused into one pass.
 //
 // A row lives ON CHIP: a thread-block cluster of 1, 2, 4 or 8 CTAs owns one row, every
-// thread requests its packets up front (up to 8 of 128 bits into registers; for long rows of
-// 16-bit elements 8 more into shared-memory slots of its own), and the three phases of the
+// thread requests its packets up front (up to 8 into registers; for long rows of 16- and 32-bit
+// elements half of them into shared-memory slots of its own), and the three phases of the
 // reference kernel (max, sum of exponentials, normalise; src/ops/nvidia/loss/softmax.cu:311-405)
 // run on that copy. The row is read from HBM once and written once; the reference
 // reads it three times. The CTAs of a cluster exchange their maxima and partial sums by
@@ -21,11 +21,11 @@
 // reproduced by a different thread layout); that changes a partial by a few fp32 ulps before
 // its rounding to W.
 //
-// A persistent variant that staged row slices through shared memory with bulk asynchronous copies
-// (3-deep ring, one 1024-thread CTA per SM) was measured at 16384 x 128256 bf16 and was SLOWER
-// (3.4 ms against 1.9 ms): per row the chain max -> cluster barrier -> sums -> cluster barrier ->
-// normalise costs about 7 us of latency however the data arrives, so what matters is how many
-// independent rows an SM has in flight, and registers hold more of them than one big CTA does.
+// Measured history at 16384 x 128256 bf16. A persistent variant that staged row slices through shared memory with bulk
+// asynchronous copies (3-deep ring, one 1024-thread CTA per SM): 3.4 ms. Register-only CTAs in clusters of four with cluster
+// barriers: 1.9 ms -- per row the chain max -> exchange -> sums -> exchange -> normalise is latency however the data arrives, so
+// what matters is how many independent rows an SM has in flight and how cheap the exchange is. The current form (two resident
+// CTAs per SM, half of each thread's packets in shared memory, pushed exchange): 1.5 ms.
 //
 // Keeping the exponentials of phase 2 in registers for phase 3 (possible at <= 4 packets per thread, which for long rows
 // means a cluster twice as large) was measured too and was slower everywhere: 32768 columns 5.8 -> 3.6 TB/s, 65536 columns
