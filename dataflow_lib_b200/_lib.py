@@ -132,6 +132,8 @@ HOST_ABI = {
                                     C.POINTER(abi.TransformerBlockTransition), C.POINTER(abi.TransformerBlockTransition)]),
     # external-op plug-in symbols (ops_external.c)
     "dataflow_b200_workspace_init": (_i, [_H, _vp]),
+    "dataflow_b200_reserve_workspace": (_i, [_H, _SK, _i, _u64]),
+    "dataflow_b200_workspace_release": (None, [_vp]),
     "dataflow_b200_rms_norm": (_i, [_H, _i, _vp, _vp]),
     "dataflow_b200_rms_norm_bwd_x": (_i, [_H, _i, _vp, _vp]),
     "dataflow_b200_rms_norm_bwd_w": (_i, [_H, _i, _vp, _vp]),

@@ -19,6 +19,7 @@
  */
 #define _GNU_SOURCE
 #include "dataflow_api.h"
+#include "dataflow_b200_kernels.h"
 
 #include <cuda_runtime_api.h>
 #include <dlfcn.h>
@@ -268,17 +269,31 @@ static int cuda_submit_dependency(Dataflow_Handle * h, int stream_id, void * oth
 	return 0;
 }
 
+/* The kernels' bounded device-side waits report through status words on the device (dfb200_read_kernel_status). A synchronising
+ * call is where a caller of this interface learns that earlier work is complete, so it is also where a wait that gave up must
+ * surface: the words are read (and cleared) after the synchronisation and a non-zero word fails the call. The rows or tiles whose
+ * wait gave up hold NaN. */
+static int kernels_gave_up(const char * what) {
+	unsigned int words[8] = {0};
+	const int worst = dfb200_read_kernel_status(NULL, words, 8);
+	if (worst == 0) return 0;
+	if (worst < 0) { fprintf(stderr, "Error: %s: cannot read the kernels' status: %s\n", what, dfb200_last_error()); return -1; }
+	fprintf(stderr, "Error: %s: a kernel gave up a bounded wait (status words rope 0x%x, rms_norm 0x%x, softmax 0x%x, ffn 0x%x); its outputs hold NaN\n",
+	        what, words[0], words[1], words[2], words[3]);
+	return -1;
+}
+
 static int cuda_sync_stream(Dataflow_Handle * h, int stream_id) {
 	cudaStream_t stream;
 	if (resolve_stream(h, stream_id, "sync", &stream) || bind_device(h)) return -1;
 	RT_CHECK(cudaStreamSynchronize(stream), "unable to do cuda stream synchronize", -1);
-	return 0;
+	return kernels_gave_up("sync_stream");
 }
 
 static int cuda_sync_handle(Dataflow_Handle * h) {
 	if (bind_device(h)) return -1;
 	RT_CHECK(cudaDeviceSynchronize(), "unable to sync the handle's device", -1);
-	return 0;
+	return kernels_gave_up("sync_handle");
 }
 
 /* ---- 3. memory ---------------------------------------------------------------------------- */
@@ -471,6 +486,12 @@ void destroy_cuda_dataflow_handle(Dataflow_Handle * h) {
 			cudaEventDestroy(((cudaEvent_t *) h->stream_states)[i]);
 		}
 		for (int i = 0; i < h->num_native_function_libs; i++) if (g_drv.cuModuleUnload) g_drv.cuModuleUnload(h->native_function_libs[i]);
+		/* scratch blocks that this library's ops keep in their table entries (entries of other plug-ins are not touched) */
+		const Table * t = &h->op_table;
+		const uint64_t slot = t->config.key_size_bytes + t->config.value_size_bytes;
+		for (uint64_t i = 0; t->items && i < t->size; i++)
+			if (!((t->is_empty_bit_vector[i >> 6] >> (i & 63)) & 1ULL))
+				dataflow_b200_workspace_release((uint8_t *) t->items + i * slot + t->config.key_size_bytes);
 	}
 	for (int i = 0; i < MAX_STREAMS; i++) free(h->stream_names[i]);
 	free(h->streams); free(h->stream_states); free(h->device_info); free(h->device_handle); free(h->ctx);

@@ -202,9 +202,20 @@ int register_native_ops(Dataflow_Handle * dataflow_handle, char * native_functio
 		fprintf(stderr, "Error: register_native_ops needs an initialised handle\n");
 		return -1;
 	}
+	/* A caller written against the reference passes its cubin and launch-config library here
+	 * (register_native_ops(&handle, "lib/cuda_kernels.cubin", "lib/cuda_kernels_config.so")). The ops of this library live in this
+	 * shared object, so a path that is not a loadable shared object exporting them -- a cubin, a missing file, another library -- is
+	 * replaced by this library's own path, with a one-line notice. */
 	char self_path[4096];
 	char * lib = native_function_code_filename;
-	if (!lib) {
+	bool use_self = !lib;
+	if (lib) {
+		void * probe = dlopen(lib, RTLD_LAZY | RTLD_LOCAL);
+		if (!probe || !dlsym(probe, "dataflow_b200_rms_norm")) use_self = true;
+		if (probe) dlclose(probe);
+		if (use_self) fprintf(stderr, "Notice: register_native_ops: %s does not export this library's ops; registering them from this library instead\n", lib);
+	}
+	if (use_self) {
 		Dl_info info;
 		if (!dladdr((void *) &register_native_ops, &info) || !info.dli_fname) {
 			fprintf(stderr, "Error: cannot locate the shared object that holds the ops\n");

@@ -607,7 +607,8 @@ gemm_e4m3_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
 		const int col_half = (warp - 2) >> 2;                // which half of the tile's column chunks this warp handles
 		uint32_t local = 0;
 		bool ok = true;
-		for (int tile = walker; tile < num_tiles && ok; tile += n_walkers, local++) {
+		int tile = walker;
+		for (; tile < num_tiles && ok; tile += n_walkers, local++) {
 			const uint32_t acc_stage = local & 1;
 			int m0, n0;
 			tile_origin(tile, m0, n0);
@@ -768,6 +769,22 @@ gemm_e4m3_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
 				chunk(c + 1, pre0[1], pre1[1], pre0[0], pre1[0]);
 			}
 		}
+		// A wait gave up (the status word says which): the tile it was for and every later tile of this walker get NaN, so that the
+		// failure shows in the data and not only in the status word. Cold path: plain 2-byte stores.
+		if (!ok) {
+			const __nv_bfloat16 nan = __float2bfloat16_rn(__int_as_float(0x7fc00000));
+			__nv_bfloat16 * o = reinterpret_cast<__nv_bfloat16 *>(out);
+			for (; tile < num_tiles; tile += n_walkers) {
+				int m0, n0;
+				tile_origin(tile, m0, n0);
+				const int row = m0 + quarter * 32 + lane;
+				if (row >= M) continue;
+				for (int j = col_half * (N_PER_TILE / 2); j < (col_half + 1) * (N_PER_TILE / 2) && n0 + j < N; j++) {
+					o[(size_t) row * ld_out + n0 + j] = nan;
+					if constexpr (MODE == MODE_SWIGLU_BWD) o[(size_t) row * ld_out + N + n0 + j] = nan;
+				}
+			}
+		}
 	}
 	tc_fence_before_sync();
 	// no CTA of a pair frees its tensor memory or leaves while the other may still use its shared or tensor memory
@@ -807,10 +824,10 @@ static int make_map(CUtensorMap * map, const void * base, uint64_t rows, uint64_
 }
 
 // DFB200_GEMM_SINGLE_CTA=1 in the environment keeps every GEMM on the one-CTA-per-tile kernel (for A/B measurements).
+// Read on every launch (a getenv is nanoseconds beside a launch), so a test can switch forms inside one process.
 static bool force_single_cta() {
-	static int v = -1;
-	if (v < 0) { const char * e = getenv("DFB200_GEMM_SINGLE_CTA"); v = e && e[0] == '1'; }
-	return v != 0;
+	const char * e = getenv("DFB200_GEMM_SINGLE_CTA");
+	return e && e[0] == '1';
 }
 
 // Clusters of two CTAs of the pair kernel that fit on the current device at once (0 when the query fails); remembered per device.

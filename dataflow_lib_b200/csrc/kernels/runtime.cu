@@ -78,7 +78,9 @@ int check_launch(const char * what) {
 	return DFB200_OK;
 }
 
-static __device__ unsigned int g_kernel_status[STATUS_SLOTS];
+// [0, STATUS_SLOTS): the status words; [STATUS_SLOTS, 2 * STATUS_SLOTS): per family, the number of the launch whose wait gave up
+// last (lets the other waits of that launch give up early without a stale value shortening the waits of later launches).
+static __device__ unsigned int g_kernel_status[2 * STATUS_SLOTS];
 
 unsigned int * kernel_status_word(int slot) {
 	static unsigned int * base[64];          // per device
@@ -100,7 +102,7 @@ unsigned int * kernel_status_word(int slot) {
 extern "C" int dfb200_read_kernel_status(void * stream, unsigned int * status_words, int n_words) {
 	unsigned int host[dfb200::STATUS_SLOTS];
 	cudaError_t e = cudaStreamSynchronize((cudaStream_t) stream);
-	if (e == cudaSuccess) e = cudaMemcpyFromSymbol(host, dfb200::g_kernel_status, sizeof(host));
+	if (e == cudaSuccess) e = cudaMemcpyFromSymbol(host, dfb200::g_kernel_status, sizeof(host));       // the status words only
 	if (e != cudaSuccess) return dfb200::set_error(DFB200_ERR_CUDA, "read_kernel_status: %s", cudaGetErrorString(e));
 	unsigned int zero[dfb200::STATUS_SLOTS] = {0};
 	unsigned int worst = 0;

@@ -69,10 +69,12 @@ __device__ __forceinline__ void push_f32(uint32_t peer_dst, float v, uint32_t pe
 	asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.b32 [%0], %1, [%2];"
 	             :: "r"(peer_dst), "r"(__float_as_uint(v)), "r"(peer_bar) : "memory");
 }
-// Waits for phase 0 of `bar` (its expected bytes have arrived from the peers). Gives up after WAIT_LIMIT_NS and records `where`;
-// once any wait of the launch has given up, the others give up at their next look at the status word, so a broken exchange costs
-// the launch one time limit and not one per row.
-__device__ __forceinline__ bool wait_pushed(uint64_t * bar, unsigned int * status, unsigned int where) {
+// Waits for phase 0 of `bar` (its expected bytes have arrived from the peers). Gives up after WAIT_LIMIT_NS and records `where`
+// in the family's status word. Once any wait of THIS launch has given up, the launch's other waits give up at their next look at the
+// abort word, so a broken exchange costs the launch one time limit and not one per row. The abort word (STATUS_SLOTS words after the
+// status word) holds the number of the launch that gave up, not a flag: a value left by an earlier launch never shortens a later one.
+// A caller that gets `false` must poison what it computes from the exchange (NaN), so that the failure shows in the data too.
+__device__ __forceinline__ bool wait_pushed(uint64_t * bar, unsigned int * status, unsigned int where, unsigned int epoch) {
 	auto done = [&]() {
 		uint32_t ok;
 		asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], 0;\n\tselp.u32 %0, 1, 0, p;\n\t}"
@@ -85,9 +87,9 @@ __device__ __forceinline__ bool wait_pushed(uint64_t * bar, unsigned int * statu
 		for (int i = 0; i < 1024; i++)
 			if (done()) return true;
 		if (global_timer_ns() - t0 > WAIT_LIMIT_NS) break;
-		if (status && *reinterpret_cast<volatile unsigned int *>(status) != 0) break;
+		if (status && *reinterpret_cast<volatile unsigned int *>(status + STATUS_SLOTS) == epoch) break;
 	}
-	if (status) atomicMax(status, where);
+	if (status) { atomicMax(status, where); atomicExch(status + STATUS_SLOTS, epoch); }
 	return false;
 }
 
@@ -180,7 +182,8 @@ constexpr int softmax_min_ctas(int row_words_per_thread, int spt) { return spt >
 template <typename F, typename B, int CPT, bool FUSE_CE, typename OUT = B, bool ARGMAX = false, int SPT = 0, bool MULTI = false>
 __global__ void __launch_bounds__(SOFTMAX_MAX_THREADS, softmax_min_ctas(CPT * (E / Word<F>::EPW), SPT))
 softmax_rows_kernel(int n_rows, int n_cols, int slice_chunks, const void * __restrict__ X, void * __restrict__ out,
-                    const uint32_t * __restrict__ labels, float * __restrict__ row_loss, uint32_t * __restrict__ arg_maxs, unsigned int * status) {
+                    const uint32_t * __restrict__ labels, float * __restrict__ row_loss, uint32_t * __restrict__ arg_maxs, unsigned int * status,
+                    unsigned int epoch) {
 	static_assert(!FUSE_CE || sizeof(OUT) == sizeof(B), "the fused cross-entropy step works in the output type");
 	constexpr int FW = E / Word<F>::EPW;
 	static_assert(SPT == 0 || FW % 4 == 0, "shared-memory packets are made of 16-byte quarters");
@@ -192,7 +195,7 @@ softmax_rows_kernel(int n_rows, int n_cols, int slice_chunks, const void * __res
 	__shared__ float s_peer_max[SOFTMAX_MAX_CLUSTER];      // [r] pushed here by CTA r of the cluster
 	__shared__ float s_peer_part[SOFTMAX_MAX_CLUSTER][32];
 	__shared__ uint64_t s_pushed[2];                       // byte-counting barriers of the two exchanges
-	__shared__ float s_row[2];              // row max, row total
+	__shared__ float s_row[3];              // row max, row total (rounded to W), row total in fp32 (fused cross entropy: the loss)
 	__shared__ uint32_t s_label[3];         // label, owning thread, packet index (fused cross entropy)
 
 	// MULTI = the row is shared by a cluster of more than one CTA (only rows that need 8 packets per thread are); without it the
@@ -306,10 +309,11 @@ softmax_rows_kernel(int n_rows, int n_cols, int slice_chunks, const void * __res
 		if constexpr (MULTI) {
 			if ((unsigned) lane == crank) s_peer_max[crank] = v;
 			else if ((unsigned) lane < csize) push_f32(peer_smem_addr(&s_peer_max[crank], lane), v, peer_smem_addr(&s_pushed[0], lane));
-			wait_pushed(&s_pushed[0], status, 0x50000001u);
+			const bool arrived = wait_pushed(&s_pushed[0], status, 0x50000001u, epoch);
 			__syncwarp();
 			v = (unsigned) lane < csize ? s_peer_max[lane] : -CUDART_INF_F;
 			v = warp_max(v);
+			if (!__all_sync(0xffffffffu, arrived)) v = CUDART_NAN_F;   // a peer's maximum never came: the row's outputs become NaN
 		}
 		if (lane == 0) s_row[0] = v;
 	}
@@ -320,7 +324,8 @@ softmax_rows_kernel(int n_rows, int n_cols, int slice_chunks, const void * __res
 	// label takes it aside now (one register through the hot loops; the label itself waits in shared memory), so that the row copy can
 	// be given up packet by packet in phase 3.
 	constexpr float NO_LABEL = 1.0f;                       // shifted logits are <= 0 (or NaN)
-	float label_logit = NO_LABEL;
+	float label_logit = NO_LABEL;                          // W(x[label] - max): what the stored probability is made from
+	float label_diff = 0.0f;                               // x[label] - max in fp32, not rounded to W: what the loss is made from
 	if constexpr (FUSE_CE) {
 		if ((uint32_t) tid == s_label[1]) {               // written by thread 0 before the barriers of phase 1
 			const int kl = (int) s_label[2], j = (int) (s_label[0] % E);
@@ -336,10 +341,12 @@ softmax_rows_kernel(int n_rows, int n_cols, int slice_chunks, const void * __res
 					}
 				}
 			}
-			float d[E];
+			float d[E], x[E];
 			Math::shifted(shift, w, d);
 			#pragma unroll
-			for (int i = 0; i < E; i++) if (i == j) label_logit = d[i];
+			for (int i = 0; i < FW; i++) Word<F>::unpack(w[i], &x[i * Word<F>::EPW]);
+			#pragma unroll
+			for (int i = 0; i < E; i++) if (i == j) { label_logit = d[i]; label_diff = x[i] - row_max; }
 		}
 	}
 	if constexpr (ARGMAX) {
@@ -389,13 +396,18 @@ softmax_rows_kernel(int n_rows, int n_cols, int slice_chunks, const void * __res
 			s_peer_part[crank][lane] = v;
 			for (unsigned r = 0; r < csize; r++)
 				if (r != crank) push_f32(peer_smem_addr(&s_peer_part[crank][lane], r), v, peer_smem_addr(&s_pushed[1], r));
-			wait_pushed(&s_pushed[1], status, 0x50000002u);
+			const bool arrived = wait_pushed(&s_pushed[1], status, 0x50000002u, epoch);
 			v = 0.0f;
 			for (unsigned r = 0; r < csize; r++) v += s_peer_part[r][lane];   // the same order in every CTA of the cluster
+			if (!arrived) v = CUDART_NAN_F;                                    // a peer's sums never came: the row's outputs become NaN
 		}
+		// The loss is not one of the reference's outputs and keeps none of its roundings: its row total is the fp32 sum of the 32
+		// partial sums BEFORE they are rounded to W.
+		float total32 = 0.0f;
+		if constexpr (FUSE_CE) total32 = warp_sum(v);
 		v = round_to<B>(v);
 		v = warp_sum(v);
-		if (lane == 0) s_row[1] = round_to<B>(v);
+		if (lane == 0) { s_row[1] = round_to<B>(v); if constexpr (FUSE_CE) s_row[2] = total32; }
 	}
 	// A CTA has received everything its peers will ever write into its shared memory once both waits have returned, so it may leave
 	// without a closing barrier; the arrive / wait pair below only covers a wait that gave up (the status word then says so).
@@ -421,11 +433,13 @@ softmax_rows_kernel(int n_rows, int n_cols, int slice_chunks, const void * __res
 	}
 	// ---- cross-entropy step, by the one thread of the row that holds the label: the probability is recomputed from the logit taken
 	// aside above (nothing is read back from memory), rounded to the working type, one is subtracted and the difference rounded again
-	// -- what the separate kernel does to the stored value -- and stored over it; the row's loss comes from the same shifted logit.
+	// -- what the separate kernel does to the stored value -- and stored over it. The row's loss is log(sum_j exp(W(x_j - max))) -
+	// (x_label - max) with the sum and the difference in fp32: the only rounding to W left in it is the one inside the exponentials,
+	// which moves the mean loss of N(0, 2) logits over 128256 columns by 5e-6 of its value against an fp64 cross entropy.
 	if constexpr (FUSE_CE) {
 		if (label_logit != NO_LABEL) {
 			store_one<OUT>(out, row_elem + s_label[0], round_to<B>(fast_exp(label_logit) * inv_total) - 1.0f);
-			if (row_loss) row_loss[row] = logf(total) - label_logit;
+			if (row_loss) row_loss[row] = logf(s_row[2]) - label_diff;
 		} else if (row_loss && crank == 0 && tid == 0 && s_label[0] >= (uint32_t) n_cols) {
 			row_loss[row] = 0.0f;
 		}
@@ -482,6 +496,14 @@ loss_sum_kernel(int n_rows, int n_cols, const float * __restrict__ row_loss, con
 		__syncthreads();
 	}
 	if (threadIdx.x == 0) { loss_sum[0] = (float) s_sum[0]; loss_sum[1] = (float) s_cnt[0]; }
+}
+
+// Number of this launch for the abort word of wait_pushed: 1, 2, ... (0, the word's initial value, is never used).
+static unsigned int next_launch_epoch() {
+	static unsigned int counter = 0;
+	unsigned int e = __atomic_add_fetch(&counter, 1u, __ATOMIC_RELAXED);
+	if (e == 0) e = __atomic_add_fetch(&counter, 1u, __ATOMIC_RELAXED);
+	return e;
 }
 
 struct SoftmaxGeometry { int cluster, threads, cpt, slice_chunks, spt; };      // spt > 0: packets per thread kept in shared memory
@@ -544,6 +566,7 @@ static int launch_softmax_long_rows(const SoftmaxGeometry & g, int n_rows, int n
 		if (g.spt != HALF || g.cpt != HALF) return set_error(DFB200_ERR_DTYPE, "softmax: internal geometry error");
 		const size_t smem = (size_t) HALF * QW * g.threads * sizeof(uint4);
 		unsigned int * status = kernel_status_word(STATUS_SOFTMAX);
+		const unsigned int epoch = next_launch_epoch();
 		cudaLaunchConfig_t cfg = {};
 		cfg.gridDim = dim3((unsigned) n_rows * g.cluster, 1, 1);
 		cfg.blockDim = dim3(g.threads, 1, 1);
@@ -556,7 +579,7 @@ static int launch_softmax_long_rows(const SoftmaxGeometry & g, int n_rows, int n
 		auto kernel = g.cluster > 1 ? softmax_rows_kernel<F, B, HALF, FUSE_CE, OUT, ARGMAX, HALF, true>
 		                            : softmax_rows_kernel<F, B, HALF, FUSE_CE, OUT, ARGMAX, HALF, false>;
 		allow_dyn_smem(reinterpret_cast<const void *>(kernel), smem);
-		const cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, n_rows, n_cols, g.slice_chunks, X, out, labels, row_loss, arg_maxs, status);
+		const cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, n_rows, n_cols, g.slice_chunks, X, out, labels, row_loss, arg_maxs, status, epoch);
 		if (e != cudaSuccess) { cudaGetLastError(); return set_error(DFB200_ERR_CUDA, "softmax launch: %s", cudaGetErrorString(e)); }
 		return DFB200_OK;
 	}
@@ -577,13 +600,14 @@ static int launch_softmax_rows(const SoftmaxGeometry & g, int n_rows, int n_cols
 	cfg.attrs = attr; cfg.numAttrs = 1;
 	uint32_t * no_argmax = nullptr;
 	unsigned int * status = kernel_status_word(STATUS_SOFTMAX);
+	const unsigned int epoch = next_launch_epoch();
 	cudaError_t e;
 	switch (g.cpt) {
-		case 1:  e = cudaLaunchKernelEx(&cfg, softmax_rows_kernel<F, B, 1, FUSE_CE>, n_rows, n_cols, g.slice_chunks, X, out, labels, row_loss, no_argmax, status); break;
-		case 2:  e = cudaLaunchKernelEx(&cfg, softmax_rows_kernel<F, B, 2, FUSE_CE>, n_rows, n_cols, g.slice_chunks, X, out, labels, row_loss, no_argmax, status); break;
-		case 4:  e = cudaLaunchKernelEx(&cfg, softmax_rows_kernel<F, B, 4, FUSE_CE>, n_rows, n_cols, g.slice_chunks, X, out, labels, row_loss, no_argmax, status); break;
-		default: e = g.cluster > 1 ? cudaLaunchKernelEx(&cfg, softmax_rows_kernel<F, B, 8, FUSE_CE, B, false, 0, true>, n_rows, n_cols, g.slice_chunks, X, out, labels, row_loss, no_argmax, status)
-		                           : cudaLaunchKernelEx(&cfg, softmax_rows_kernel<F, B, 8, FUSE_CE>, n_rows, n_cols, g.slice_chunks, X, out, labels, row_loss, no_argmax, status);
+		case 1:  e = cudaLaunchKernelEx(&cfg, softmax_rows_kernel<F, B, 1, FUSE_CE>, n_rows, n_cols, g.slice_chunks, X, out, labels, row_loss, no_argmax, status, epoch); break;
+		case 2:  e = cudaLaunchKernelEx(&cfg, softmax_rows_kernel<F, B, 2, FUSE_CE>, n_rows, n_cols, g.slice_chunks, X, out, labels, row_loss, no_argmax, status, epoch); break;
+		case 4:  e = cudaLaunchKernelEx(&cfg, softmax_rows_kernel<F, B, 4, FUSE_CE>, n_rows, n_cols, g.slice_chunks, X, out, labels, row_loss, no_argmax, status, epoch); break;
+		default: e = g.cluster > 1 ? cudaLaunchKernelEx(&cfg, softmax_rows_kernel<F, B, 8, FUSE_CE, B, false, 0, true>, n_rows, n_cols, g.slice_chunks, X, out, labels, row_loss, no_argmax, status, epoch)
+		                           : cudaLaunchKernelEx(&cfg, softmax_rows_kernel<F, B, 8, FUSE_CE>, n_rows, n_cols, g.slice_chunks, X, out, labels, row_loss, no_argmax, status, epoch);
 		         break;
 	}
 	if (e != cudaSuccess) { cudaGetLastError(); return set_error(DFB200_ERR_CUDA, "softmax launch: %s", cudaGetErrorString(e)); }
@@ -606,12 +630,13 @@ static int launch_softmax_fp32_out(const SoftmaxGeometry & g, int n_rows, int n_
 	cfg.attrs = attr; cfg.numAttrs = 1;
 	const uint32_t * no_labels = nullptr;
 	unsigned int * status = kernel_status_word(STATUS_SOFTMAX);
+	const unsigned int epoch = next_launch_epoch();
 	float * no_loss = nullptr;
 	void * o = out;
 	cudaError_t e;
 #define DFB200_SOFTMAX_F32_CASE(CPT_, MULTI_) \
-	(arg_maxs ? cudaLaunchKernelEx(&cfg, softmax_rows_kernel<F, F, CPT_, false, f32_t, true, 0, MULTI_>, n_rows, n_cols, g.slice_chunks, X, o, no_labels, no_loss, arg_maxs, status) \
-	          : cudaLaunchKernelEx(&cfg, softmax_rows_kernel<F, F, CPT_, false, f32_t, false, 0, MULTI_>, n_rows, n_cols, g.slice_chunks, X, o, no_labels, no_loss, arg_maxs, status))
+	(arg_maxs ? cudaLaunchKernelEx(&cfg, softmax_rows_kernel<F, F, CPT_, false, f32_t, true, 0, MULTI_>, n_rows, n_cols, g.slice_chunks, X, o, no_labels, no_loss, arg_maxs, status, epoch) \
+	          : cudaLaunchKernelEx(&cfg, softmax_rows_kernel<F, F, CPT_, false, f32_t, false, 0, MULTI_>, n_rows, n_cols, g.slice_chunks, X, o, no_labels, no_loss, arg_maxs, status, epoch))
 	switch (g.cpt) {
 		case 1:  e = DFB200_SOFTMAX_F32_CASE(1, false); break;
 		case 2:  e = DFB200_SOFTMAX_F32_CASE(2, false); break;

@@ -52,6 +52,13 @@ class DataflowHandle:
         to_arr = lambda xs: (C.c_char_p * n)(*[x.encode() if x else None for x in xs])
         return self.h.register_external_code(C.byref(self.h), lib_path.encode(), n, sk, to_arr(symbols), to_arr(init_symbols))
 
+    def reserve_workspace(self, op_name, stream_id, nbytes, fwd_dt=DT.NONE, bwd_dt=DT.NONE):
+        """dataflow_b200_reserve_workspace: size the scratch block of (op identity, stream) ahead of the step loop."""
+        sk = abi.OpSkeleton()
+        if _L.set_native_op_skeleton(C.byref(sk), op_name.encode(), int(fwd_dt), int(bwd_dt)) != 0:
+            raise ValueError(f"unknown op {op_name}")
+        return _L.dataflow_b200_reserve_workspace(C.byref(self.h), C.byref(sk), stream_id, nbytes)
+
     @property
     def device_info(self):
         return C.cast(self.h.device_info, C.POINTER(abi.CudaDeviceInfo)).contents

@@ -63,13 +63,22 @@ int remove_table(Table * table, void * key, void * ret_value);
 int init_cuda_dataflow_handle(Dataflow_Handle * dataflow_handle, ComputeType compute_type, int device_id,
                               int ctx_id, unsigned int ctx_flags,
                               int num_streams, int * opt_stream_prios, char ** opt_stream_names);
-/* Not in the reference: releases streams, events, modules and the op table. */
+/* Not in the reference: releases streams, events, modules, the op table and the device scratch this library's ops keep. */
 void destroy_cuda_dataflow_handle(Dataflow_Handle * dataflow_handle);
+/* Not in the reference. The ops with device scratch (rms_norm_bwd_w, softmax_cross_entropy without a row_loss buffer,
+ * swiglu_ffn_fp8, swiglu_ffn_fp8_bwd) keep one grow-only block per (op identity, stream id); a block is allocated by the first
+ * submission that needs it. dataflow_b200_reserve_workspace sizes the block of (skeleton, stream_id) ahead of time -- `bytes` from
+ * the matching dfb200_*_workspace_bytes function of dataflow_b200_kernels.h -- so that no submission inside a step loop allocates
+ * (growing a block calls cudaFree, which waits for the whole device). 0 on success, -1 otherwise.
+ * dataflow_b200_workspace_release is what destroy_cuda_dataflow_handle calls on every op-table value. */
+int dataflow_b200_reserve_workspace(Dataflow_Handle * dataflow_handle, Op_Skeleton * skeleton, int stream_id, uint64_t bytes);
+void dataflow_b200_workspace_release(void * op_table_value);
 
 /* ---- op skeletons and registration ---------------------------------------------------- */
 /* Registers the 54 (op x datatype) identities of the reference's native op set, plus copy_to_seq_context,
  * select_experts and this library's fused ops, on the handle. `native_function_code_filename` names the shared object
- * that exports the ops (this library; NULL = the library containing this function);
+ * that exports the ops; NULL, or a path that is not such a shared object (the reference's "lib/cuda_kernels.cubin", say, in a caller
+ * that was not changed), selects the library containing this function, with a notice on stderr;
  * `native_function_config_filename` is accepted for source compatibility and ignored.
  * Returns the number of ops registered. */
 int register_native_ops(Dataflow_Handle * dataflow_handle, char * native_function_code_filename, char * native_function_config_filename);

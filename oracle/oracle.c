@@ -9,7 +9,7 @@
  * is pinned (a) by the fingerprint/struct-size known answers in tests/golden, which come from
  * the reference's own host sources compiled unchanged, and (b) on a GPU box by running the
  * reference's kernels themselves, compiled for sm_100a from the reference tree into
- * oracle/_ref (see oracle/Makefile), on the same inputs (tests/test_reference_kernels.py).
+ * oracle/_ref (see oracle/Makefile), on the same inputs (tests/test_reference_kernels_gpu.py).
  *
  * Conventions: tensors are row-major and contiguous; `dt` arguments are DataflowDatatype
  * values (3 fp32, 4 fp16, 5 bf16, 6 fp8e4m3, 7 fp8e5m2); n_threads host threads split the rows.
@@ -384,7 +384,10 @@ void oracle_swiglu_bwd_x(int fwd_dt, int bwd_dt, int n_rows, int n_cols, const v
  * if its missing lanes contributed nothing.
  * Optional cross-entropy step and loss (labels != NULL):
  *   out[r, label] = W(out[r, label] - 1)      intended semantics of loss/cross_entropy.cu:33-44
- *   row_loss[r] = logf(total) - f32(W(x_label - max))   (no reference implementation exists)
+ *   row_loss[r] = logf(total32) - (x_label - max)   in fp32, with total32 = the fp32 tree sum of the 32 warp sums BEFORE they
+ *                 are rounded to W. No reference implementation exists (nothing in the reference computes a loss,
+ *                 src/dataflow_models/dataflow_transformer/include/transformer_structs.h:148-149), so none of the reference's
+ *                 roundings is owed to it except the one inside the exponentials it shares with the probabilities.
  * ---------------------------------------------------------------------------------------- */
 
 typedef struct { int fdt, bdt, n_cols; const void * X; void * out; const uint32_t * labels; float * row_loss; int odt; uint32_t * arg_maxs; } Softmax;
@@ -397,7 +400,7 @@ static void softmax_rows(long r0, long r1, void * p) {
 		const size_t base = (size_t) r * n;
 		float mx = -INFINITY;
 		for (int i = 0; i < n; i++) { const float x = ld(a->fdt, a->X, base + i); if (x > mx) mx = x; }
-		float warp_sums[32];
+		float warp_sums[32], warp_sums_f32[32];
 		for (int w = 0; w < 32; w++) {
 			float total = 0.0f;
 			for (int g = w; g < groups; g += 32) {
@@ -409,6 +412,7 @@ static void softmax_rows(long r0, long r1, void * p) {
 				total += tree32(lane);
 			}
 			warp_sums[w] = rnd(W, total);
+			warp_sums_f32[w] = total;
 		}
 		const float total = rnd(W, tree32(warp_sums));
 		for (int i = 0; i < n; i++)
@@ -422,7 +426,7 @@ static void softmax_rows(long r0, long r1, void * p) {
 			const uint32_t lab = a->labels[r];
 			if (lab < (uint32_t) n) {
 				st(W, a->out, base + lab, ld(W, a->out, base + lab) - 1.0f);
-				if (a->row_loss) a->row_loss[r] = logf(total) - rnd_d(W, (double) ld(a->fdt, a->X, base + lab) - (double) mx);
+				if (a->row_loss) a->row_loss[r] = logf(tree32(warp_sums_f32)) - (ld(a->fdt, a->X, base + lab) - mx);
 			} else if (a->row_loss) a->row_loss[r] = 0.0f;
 		}
 	}

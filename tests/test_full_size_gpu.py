@@ -19,11 +19,19 @@ def _randn(shape, seed, std=1.0, mean=0.0, dtype=torch.bfloat16):
     return (mean + std * torch.randn(shape, device="cuda", generator=g)).to(dtype)
 
 
-def _close(got, ref, rel=1e-2, scale=None):
+def _close(got, ref, rel=1e-2, scale=None, flipped_frac=0.0):
+    """|got - ref| <= rel * max(|ref|, scale). `flipped_frac` > 0 names the share of elements allowed between rel and 2 rel: those
+    whose bf16 INPUT differs by one unit between the device and this fp32 model (two fp32 sums in different orders that straddle a
+    rounding boundary), which moves the output by that unit on top of its own rounding."""
     got, ref = got.float(), ref.float()
+    assert torch.isfinite(got).all(), "non-finite output"
     s = ref.pow(2).mean().sqrt() if scale is None else scale
     tol = rel * torch.maximum(ref.abs(), torch.as_tensor(s, device=ref.device))
-    bad = (got - ref).abs() > tol
+    err = (got - ref).abs()
+    bad = err > tol
+    if flipped_frac:
+        assert bad.float().mean().item() <= flipped_frac, f"{int(bad.sum())}/{bad.numel()} outside {rel} rel"
+        bad = err > 2 * tol
     assert not bad.any(), f"{int(bad.sum())}/{bad.numel()} outside {rel} rel"
 
 
@@ -132,13 +140,109 @@ def test_c3_fused_softmax_cross_entropy(ops):
         neg_count += int(neg.sum())
         assert torch.equal(neg.nonzero()[:, 1], lab[i:i + 1024])                       # label indexing, bit-exact
         worst_sum = max(worst_sum, gf.sum(1).abs().max().item())                       # softmax - onehot sums to ~0 per row
-        model_loss[i:i + 1024] = (torch.log(total) - d[rows, lab[i:i + 1024]]).double()
+        # the loss keeps none of those roundings but the one inside the exponentials: fp32 sum of the unrounded partials, fp32 x_label - max
+        total32 = ep.sum(dim=(1, 3)).sum(1)
+        model_loss[i:i + 1024] = (torch.log(total32) - (x - x.max(1, keepdim=True).values)[rows, lab[i:i + 1024]]).double()
     assert neg_count == T and worst_sum < 2e-2
-    assert torch.allclose(row_loss.double(), model_loss, rtol=0, atol=5e-3)
-    mean_model = model_loss.sum().item() / T
+    assert torch.allclose(row_loss.double(), model_loss, rtol=1e-5, atol=0)
     mean_got = loss[0].item() / T
-    assert abs(mean_got - mean_model) <= 1e-5 * abs(mean_model), (mean_got, mean_model)
     assert abs(loss[0].item() - row_loss.double().sum().item()) <= 1e-6 * abs(loss[0].item())   # fp64 fixed-order sum of the fp32 row losses
-    # and against the textbook loss the quirks stay small: a few 1e-3 relative on the mean
-    ce = torch.stack([torch.nn.functional.cross_entropy(logits[i:i + 2048].float(), lab[i:i + 2048], reduction="sum") for i in range(0, T, 2048)]).sum().item() / T
-    assert abs(mean_got - ce) / ce < 5e-3, (mean_got, ce)
+    # the configuration's bound: the mean loss within 1e-5 relative of the cross entropy of these bf16 logits computed in fp64
+    ce = 0.0
+    for i in range(0, T, 1024):
+        ce += torch.nn.functional.cross_entropy(logits[i:i + 1024].double(), lab[i:i + 1024], reduction="sum").item()
+    ce /= T
+    assert abs(mean_got - ce) <= 1e-5 * abs(ce), (mean_got, ce)
+
+
+def test_c4_swiglu_ffn_fp8(ops):
+    """FP8-weight SwiGLU FFN at 16384 x 4096 x 14336: forward, input gradient and weight gradients. The reference has no such op;
+    the checker is the same composition of the quantised arithmetic in fp32 on the GPU (torch matmul, TF32 off, in row slabs):
+    every GEMM of the three passes is re-computed from the codes and scales that went into it -- produced by the row / column
+    quantisers, which are checked bit for bit against the CPU oracle at small sizes -- and its bf16 output must be within 1e-2 of
+    max(|ref|, rms(ref)). At this size every walker of the persistent GEMM takes 24 to 48 tiles."""
+    import ctypes
+    from dataflow_lib_b200 import _lib
+    torch.backends.cuda.matmul.allow_tf32 = False
+    T, d, f = 16384, 4096, 14336
+    u8 = lambda *s: torch.empty(s, dtype=torch.uint8, device="cuda")
+    f32v = lambda n: torch.empty(n, device="cuda")
+    bf = lambda *s: torch.full(s, float("nan"), dtype=torch.bfloat16, device="cuda")
+    e4 = lambda q: q.view(torch.float8_e4m3fn).float()
+
+    def weight(n_out, n_in, seed):                              # N(0, 0.02) quantised with one fp32 scale per output channel
+        g = torch.Generator(device="cuda").manual_seed(seed)
+        W = 0.02 * torch.randn(n_out, n_in, device="cuda", generator=g)
+        s = W.abs().amax(1) / 448.0
+        return (W / s[:, None]).to(torch.float8_e4m3fn).view(torch.uint8), s
+
+    def check_gemm(got, Aq, sa, Wq, sw, what, add=None, post=None, slab=2048):
+        """got[m, :] against bf16( post( (Aq Wq^T)[m, :] * sa[m] * sw[:] ) + add[m, :] ), slab by slab."""
+        wf = e4(Wq)
+        for i in range(0, Aq.shape[0], slab):
+            ref = (e4(Aq[i:i + slab]) @ wf.T) * sa[i:i + slab, None]
+            if sw is not None:
+                ref = ref * sw[None, :]
+            if add is not None:
+                ref = ref + add[i:i + slab].float()
+            _close(got[i:i + slab], ref.bfloat16(), rel=1e-2)
+        del wf
+
+    A, dOut, res = _randn((T, d), 21), _randn((T, d), 22), _randn((T, d), 23)
+    Wg, sg = weight(f, d, 24)
+    Wu, su = weight(f, d, 25)
+    Wd, sd = weight(d, f, 26)
+    # ---- forward: saved pre-activations and the output with the residual added in the down projection's epilogue
+    out, G, U = bf(T, d), bf(T, f), bf(T, f)
+    ops.swiglu_ffn_fp8(T, d, f, A, Wg, sg, Wu, su, Wd, sd, out, G, U, residual=res)
+    Aq, sa = u8(T, d), f32v(T)
+    ops.quantize_rows_e4m3(T, d, A, Aq, sa)
+    check_gemm(G, Aq, sa, Wg, sg, "gate")
+    check_gemm(U, Aq, sa, Wu, su, "up")
+    Hq, sh = u8(T, f), f32v(T)
+    ops.swiglu_quantize_rows_e4m3(T, f, G, U, Hq, sh)
+    check_gemm(out, Hq, sh, Wd, sd, "down + residual", add=res)
+    del Aq, Hq
+    # ---- input gradient
+    WguT, WdT = u8(d, 2 * f), u8(f, d)
+    ops.ffn_fp8_prepare_bwd_weights(d, f, Wg, Wu, Wd, WguT, WdT)
+    dA, dGU = bf(T, d), bf(T, 2 * f)
+    sgu = torch.cat([sg, su])
+    ops.swiglu_ffn_fp8_bwd(T, d, f, dOut, G, U, WdT, sd, WguT, sgu, dA, dgate_dup=dGU)
+    dOq, s1 = u8(T, d), f32v(T)
+    ops.quantize_rows_e4m3(T, d, dOut, dOq, s1, col_factors=sd)
+    wdt = e4(WdT)
+    for i in range(0, T, 2048):                                 # dH = bf16(GEMM), then the SwiGLU backward formulas of swiglu_bwd_x
+        dh = ((e4(dOq[i:i + 2048]) @ wdt.T) * s1[i:i + 2048, None]).bfloat16().float()
+        gf, uf = G[i:i + 2048].float(), U[i:i + 2048].float()
+        e = torch.exp(-gf)
+        _close(dGU[i:i + 2048, :f], (dh * (uf * (1 + e + gf * e)) / ((1 + e) * (1 + e))).bfloat16(), rel=1e-2, flipped_frac=1e-4)
+        _close(dGU[i:i + 2048, f:], (dh * (gf / (1 + e))).bfloat16(), rel=1e-2, flipped_frac=1e-4)
+    del wdt, dOq
+    dGUq, s2 = u8(T, 2 * f), f32v(T)
+    ops.quantize_rows_e4m3(T, 2 * f, dGU, dGUq, s2, col_factors=sgu)
+    check_gemm(dA, dGUq, s2, WguT, None, "input gradient")
+    del dGUq, WguT, WdT
+    # ---- weight gradients: operands are the transposes, quantised with one scale per row of the transpose
+    dWg, dWu, dWd = bf(f, d), bf(f, d), bf(d, f)
+    ops.swiglu_ffn_fp8_wgrad(T, d, f, A, dOut, G, U, dGU, dWg, dWu, dWd)
+    H = bf(T, f)
+    ops.swiglu(T, f, G, U, H)
+
+    def transposed(X, cols):
+        amax, Qt, sc = f32v(cols), u8(cols, T), f32v(cols)
+        ops.col_amax_bf16(T, cols, X, amax)
+        ops.transpose_quantize_e4m3(T, cols, X, amax, Qt, sc)
+        return Qt, sc
+
+    dOt, s_do = transposed(dOut, d)
+    Ht, s_h = transposed(H, f)
+    check_gemm(dWd, dOt, s_do, Ht, s_h, "dWdown")
+    del dOt, Ht, H
+    At, s_a = transposed(A, d)
+    dGUt, s_gu = transposed(dGU, 2 * f)
+    check_gemm(dWg, dGUt[:f], s_gu[:f], At, s_a, "dWgate")
+    check_gemm(dWu, dGUt[f:], s_gu[f:], At, s_a, "dWup")
+    torch.cuda.synchronize()
+    words = (ctypes.c_uint * 8)()
+    assert _lib.lib.dfb200_read_kernel_status(None, words, 8) == 0, [hex(w) for w in words]

@@ -321,6 +321,36 @@ def test_external_op_wrappers_build_the_reference_argument_lists(L):
     assert L.submit_matmul(C.byref(h), 0, BF16, BF16, NONE, BF16, FP32, 0, 0, 8, 8, 8, 1.0, 0.0, None, None, None, None, 0, None) == -1
 
 
+def test_register_native_ops_with_the_reference_callers_arguments(L, capfd, tmp_path):
+    """A caller written against the reference passes its cubin and launch-config library
+    (src/set_ops/src/set_native_op_skeletons.c:40-170). Those are not this library: registration then takes the ops from the shared
+    object that holds register_native_ops, says so in one line, and registers the full set."""
+    from dataflow_lib_b200 import abi, _lib
+    seen = {}
+
+    def on_register(handle, path, n, skeletons, symbols, init_symbols):
+        seen["path"], seen["n"] = path.decode(), n
+        seen["symbols"] = {symbols[i].decode() for i in range(n)}
+        return n
+
+    h = abi.DataflowHandleStruct()
+    cb = type(h.register_external_code)(on_register)
+    h.register_external_code = cb
+    own = os.path.realpath(_lib.LIB_PATH)
+    cubin = tmp_path / "cuda_kernels.cubin"
+    cubin.write_bytes(b"\x7fELF not a shared object")
+    for arg in (b"lib/cuda_kernels.cubin", str(cubin).encode(), b"libm.so.6"):       # missing file, not loadable, loadable but without the ops
+        seen.clear()
+        assert L.register_native_ops(C.byref(h), arg, b"lib/cuda_kernels_config.so") == 75
+        assert os.path.realpath(seen["path"]) == own and seen["n"] == 75 and "dataflow_b200_rms_norm" in seen["symbols"]
+        assert "registering them from this library instead" in capfd.readouterr().err
+    for arg in (None, own.encode()):                                                  # the documented forms: no notice
+        seen.clear()
+        assert L.register_native_ops(C.byref(h), arg, None) == 75
+        assert os.path.realpath(seen["path"]) == own
+        assert "Notice" not in capfd.readouterr().err
+
+
 def _head_containers(abi, T=8, d=16, V=64):
     BF16, FP32 = int(abi.DataflowDatatype.BF16), int(abi.DataflowDatatype.FP32)
     head = abi.TransformerHead(BF16, BF16, FP32, 1e-5, abi.EmbeddingConfig(V, d), None, 0x1000, 0x2000)

@@ -207,3 +207,16 @@ def test_embedding_and_seq_context_oracle():
     assert np.array_equal(ctx[1][0], keys[1]) and np.array_equal(ctx[1][2 + 0], values[1])
     assert np.array_equal(ctx[0][3], keys[2]) and np.array_equal(ctx[0][4 + 3], values[2])
     assert not ctx[0][[0, 2, 4, 6]].any()
+
+
+def test_oracle_bf16_loss_is_within_1e5_of_fp64_cross_entropy():
+    """The fused op's loss (no reference counterpart) must be the cross entropy of the bf16 logits to 1e-5 relative on the mean,
+    although the probabilities beside it keep the reference's bf16 roundings: N(0, 2) logits, a vocabulary-sized row."""
+    n_rows, n_cols = 48, 128256
+    L = O.fill_normal(O.BF16, (n_rows, n_cols), 77, 0.0, 2.0)
+    labels = O.fill_labels(n_rows, 78, n_cols)
+    _, row_loss, loss_sum = O.softmax_cross_entropy(O.BF16, O.BF16, L, labels)
+    x = torch.from_numpy(O.to_f32(L, O.BF16)).double()
+    ce = torch.nn.functional.cross_entropy(x, torch.from_numpy(labels.astype(np.int64)), reduction="none").numpy()
+    assert abs(loss_sum[0] / n_rows - ce.mean()) <= 1e-5 * ce.mean()
+    assert np.abs(row_loss - ce).max() <= 5e-5 * ce.max()            # per row the rounding inside the exponentials shows a little more
