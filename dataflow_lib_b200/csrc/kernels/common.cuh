@@ -25,8 +25,13 @@ int check_launch(const char * what);                 // cudaGetLastError -> DFB2
 // Resident CTAs per SM of `kernel` at this launch shape on the current device (>= 1); the driver query is made
 // once per (kernel, threads, shared memory, device) and remembered.
 int ctas_per_sm(const void * kernel, int threads, size_t dyn_smem);
-// Opts `kernel` in to `dyn_smem` bytes of dynamic shared memory (needed above 48 KB); remembered per kernel and device.
+// Opts `kernel` in to `dyn_smem` bytes of dynamic shared memory (needed above 48 KB); remembered per kernel and CUDA context.
 void allow_dyn_smem(const void * kernel, size_t dyn_smem);
+// Unique id of the CUDA context current on the calling thread (binds the device's primary context when the thread has none).
+uint64_t context_key();
+// Device address of a __device__ variable in the current context (cudaGetSymbolAddress), remembered per (variable, context);
+// NULL on error. Host code must never pass the variable's name itself to a kernel: there it is a host-side stand-in.
+void * symbol_address(const void * symbol);
 
 // Launch with programmatic stream serialisation: the kernel's CTAs may become resident while the previous kernel of the stream
 // is still draining (that kernel calls pdl_prologue(), which lets its successor be scheduled early). A kernel launched this way

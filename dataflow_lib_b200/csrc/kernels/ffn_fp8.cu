@@ -877,6 +877,7 @@ static int launch_gemm(int M, int N, int K, const void * A, const float * sa, co
 	if (pairs > 0) {
 		const int tiles_m = (M + 2 * GEMM_BM - 1) / (2 * GEMM_BM);
 		auto kernel = gemm_e4m3_kernel<MODE, true>;
+		allow_dyn_smem(reinterpret_cast<const void *>(kernel), GemmShape<true>::SMEM);     // per context; max_resident_pairs remembers per device
 		cudaLaunchConfig_t cfg = {};
 		const int n_pairs = tiles_m * tiles_n < pairs ? tiles_m * tiles_n : pairs;
 		cfg.gridDim = dim3(2 * n_pairs, 1, 1);

@@ -510,8 +510,9 @@ static __device__ __align__(256) float g_bwd_w_static_scratch[STATIC_SCRATCH_FLO
 
 // Same arithmetic, kernels and results as dfb200_rms_norm_bwd_w, with the scratch taken from the array above instead
 // of a caller workspace. It calls no cudaMalloc, cudaFree or allocating library routine.
-//  * The first call on each device looks up the array's device address (cudaGetSymbolAddress, with that device
-//    current) and remembers it; make that first call outside any stream capture.
+//  * The first call on each device (more exactly: in each CUDA context, for programs that make contexts of their own) looks up
+//    the array's device address (cudaGetSymbolAddress, with that device current) and remembers it; make that first call
+//    outside any stream capture.
 //  * Limit: n_SM * n_cols <= 1,310,720 floats (n_cols <= 8192 on a 148-SM B200); larger shapes are rejected
 //    with DFB200_ERR_WORKSPACE and a message, never truncated.
 //  * All calls on a device share the one array and it keeps the previous call's contents. Nothing in it has to
@@ -519,22 +520,18 @@ static __device__ __align__(256) float g_bwd_w_static_scratch[STATIC_SCRATCH_FLO
 //    GPU (different streams, no dependency between them) race on it: order them.
 extern "C" int dfb200_rms_norm_bwd_w_static(int fwd_dt, int bwd_dt, int n_rows, int n_cols, float eps, const float * fwd_rms_vals,
                                             const void * X_inp, const void * upstream_dX, void * dW, void * stream) {
-	static float * scratch_of_device[64];          // device address of g_bwd_w_static_scratch, per device
 	int dev = -1;
 	cudaError_t e = cudaGetDevice(&dev);
-	if (e != cudaSuccess || dev < 0 || dev >= 64) { cudaGetLastError(); return set_error(DFB200_ERR_CUDA, "rms_norm_bwd_w_static: no current device (%s)", cudaGetErrorString(e)); }
-	if (!scratch_of_device[dev]) {
-		void * p = nullptr;
-		// in host code the array's name is only a handle for the runtime, not a device address: ask for the address
-		e = cudaGetSymbolAddress(&p, g_bwd_w_static_scratch);
-		if (e != cudaSuccess || !p) { cudaGetLastError(); return set_error(DFB200_ERR_CUDA, "rms_norm_bwd_w_static: cudaGetSymbolAddress failed: %s", cudaGetErrorString(e)); }
-		scratch_of_device[dev] = static_cast<float *>(p);
-	}
+	if (e != cudaSuccess || dev < 0) { cudaGetLastError(); return set_error(DFB200_ERR_CUDA, "rms_norm_bwd_w_static: no current device (%s)", cudaGetErrorString(e)); }
+	// in host code the array's name is only a handle for the runtime, not a device address: symbol_address asks the runtime
+	// (cudaGetSymbolAddress, return code checked) once per context and remembers the answer
+	float * scratch = static_cast<float *>(symbol_address(g_bwd_w_static_scratch));
+	if (!scratch) return set_error(DFB200_ERR_CUDA, "rms_norm_bwd_w_static: cudaGetSymbolAddress failed for the built-in scratch array");
 	const uint64_t capacity = (uint64_t) STATIC_SCRATCH_FLOATS * sizeof(float);
 	const uint64_t need = dfb200_rms_norm_bwd_w_workspace_bytes(n_rows, n_cols);
 	if (need > capacity)
 		return set_error(DFB200_ERR_WORKSPACE, "rms_norm_bwd_w_static: n_cols = %d needs %llu bytes of scratch on this device, the built-in array holds %llu "
 		                 "(n_SM * n_cols <= %d); use dfb200_rms_norm_bwd_w with a caller workspace", n_cols, (unsigned long long) need,
 		                 (unsigned long long) capacity, STATIC_SCRATCH_FLOATS);
-	return dfb200_rms_norm_bwd_w(fwd_dt, bwd_dt, n_rows, n_cols, eps, fwd_rms_vals, X_inp, upstream_dX, dW, scratch_of_device[dev], capacity, stream);
+	return dfb200_rms_norm_bwd_w(fwd_dt, bwd_dt, n_rows, n_cols, eps, fwd_rms_vals, X_inp, upstream_dX, dW, scratch, capacity, stream);
 }
