@@ -130,6 +130,14 @@ HOST_ABI = {
                                     C.POINTER(abi.TransformerHeadActivations), C.POINTER(abi.TransformerModelOutput),
                                     C.POINTER(abi.TransformerHead), C.POINTER(abi.TransformerHeadActivations),
                                     C.POINTER(abi.TransformerBlockTransition), C.POINTER(abi.TransformerBlockTransition)]),
+    "submit_transformer_block": (_i, [_H, _i, _i, C.POINTER(abi.TransformerBlockTransition), C.POINTER(abi.TransformerBlock),
+                                     C.POINTER(abi.TransformerBlockActivations), C.POINTER(abi.TransformerBlockTransition)]),
+    "submit_transformer_block_bwd_x": (_i, [_H, _i, _i, C.POINTER(abi.TransformerBlock), C.POINTER(abi.TransformerBlockTransition),
+                                           C.POINTER(abi.TransformerBlockActivations), C.POINTER(abi.TransformerBlockTransition),
+                                           C.POINTER(abi.TransformerBlockActivations), C.POINTER(abi.TransformerBlock),
+                                           C.POINTER(abi.TransformerBlockTransition)]),
+    "submit_transformer_block_bwd_w": (_i, [_H, _i, C.POINTER(abi.TransformerBlockTransition), C.POINTER(abi.TransformerBlockActivations),
+                                           C.POINTER(abi.TransformerBlockActivations), C.POINTER(abi.TransformerBlock)]),
     # external-op plug-in symbols (ops_external.c)
     "dataflow_b200_workspace_init": (_i, [_H, _vp]),
     "dataflow_b200_reserve_workspace": (_i, [_H, _SK, _i, _u64]),

@@ -138,3 +138,57 @@ class TransformerBlockTransition(C.Structure):
 class TransformerModelOutput(C.Structure):
     _fields_ = [("batch_config", C.c_void_p), ("token_ids", C.c_void_p), ("labels", C.c_void_p), ("logits", C.c_void_p),
                 ("loss", C.c_void_p), ("loss_avg", C.c_float)]
+
+
+class SeqBatchConfig(C.Structure):
+    _fields_ = [("num_seqs", C.c_int), ("total_q", C.c_int), ("total_k", C.c_int), ("seq_positions", C.c_void_p),
+                ("q_seq_offsets", C.c_void_p), ("q_seq_lens", C.c_void_p), ("max_seqlen_q", C.c_int),
+                ("k_seq_offsets", C.c_void_p), ("k_seq_lens", C.c_void_p), ("max_seqlen_k", C.c_int)]
+
+
+class SeqBatchSavedActivations(C.Structure):
+    _fields_ = [("config", C.POINTER(SeqBatchConfig)), ("buffer", C.c_void_p), ("activationBufferBytes", C.c_uint64),
+                ("attn_norm_weighted_sums", C.c_void_p), ("attn_norm_rms_vals", C.c_void_p), ("x_q", C.c_void_p),
+                ("x_k_local", C.c_void_p), ("x_v_local", C.c_void_p), ("softmax_lse", C.c_void_p), ("x_attn_out", C.c_void_p),
+                ("x_o", C.c_void_p), ("ffn_norm_weighted_sums", C.c_void_p), ("ffn_norm_rms_vals", C.c_void_p),
+                ("x_1", C.POINTER(C.c_void_p)), ("x_2", C.POINTER(C.c_void_p)), ("x_3", C.POINTER(C.c_void_p))]
+
+
+class SeqBatchContext(C.Structure):
+    _fields_ = [("config", C.POINTER(SeqBatchConfig)), ("buffer", C.c_void_p), ("contextBufferBytes", C.c_uint64),
+                ("x_k", C.c_void_p), ("x_v", C.c_void_p)]
+
+
+class SeqBatchActivationWorkspace(C.Structure):
+    _fields_ = [("config", C.POINTER(SeqBatchConfig)), ("buffer", C.c_void_p), ("activationWorkspaceBytes", C.c_uint64),
+                ("x_temp", C.c_void_p), ("x_temp_mlp", C.c_void_p), ("recomputed_attn_norm", C.c_void_p),
+                ("recomputed_ffn_norm", C.c_void_p), ("kernel_workspace", C.c_void_p), ("kernel_workspaceBytes", C.c_uint64)]
+
+
+class MoEConfig(C.Structure):
+    _fields_ = [("top_k_experts", C.c_int), ("num_global_experts", C.c_int), ("num_local_experts", C.c_int), ("local_expert_inds", C.c_void_p)]
+
+
+class TransformerBlockWeightOffsets(C.Structure):
+    _fields_ = [(n, C.c_uint64) for n in ("w_attn_norm", "w_q", "w_k", "w_v", "w_o", "w_ffn_norm", "w_router")] + \
+               [("w_1", C.c_void_p), ("w_2", C.c_void_p), ("w_3", C.c_void_p)]
+
+
+class TransformerBlockConfig(C.Structure):
+    _fields_ = [("block_dt", C.c_int), ("compute_dt", C.c_int), ("normalization_type", C.c_int), ("attention_type", C.c_int),
+                ("mlp_type", C.c_int), ("activation_type", C.c_int), ("eps", C.c_float), ("theta", C.c_int), ("num_q_heads", C.c_int),
+                ("num_kv_heads", C.c_int), ("head_dim", C.c_int), ("model_dim", C.c_int), ("kv_dim", C.c_int), ("ffn_dim", C.c_int),
+                ("moe_config", MoEConfig), ("pointer_alignment", C.c_int), ("weight_offsets", TransformerBlockWeightOffsets),
+                ("block_raw_size", C.c_uint64), ("block_aligned_size", C.c_uint64)]
+
+
+class TransformerBlock(C.Structure):
+    _fields_ = [("config", TransformerBlockConfig), ("buffer", C.c_void_p), ("w_attn_norm", C.c_void_p), ("w_q", C.c_void_p),
+                ("w_k", C.c_void_p), ("w_v", C.c_void_p), ("w_o", C.c_void_p), ("w_ffn_norm", C.c_void_p), ("w_router", C.c_void_p),
+                ("w_1", C.POINTER(C.c_void_p)), ("w_2", C.POINTER(C.c_void_p)), ("w_3", C.POINTER(C.c_void_p))]
+
+
+class TransformerBlockActivations(C.Structure):
+    _fields_ = [("block", C.POINTER(TransformerBlock)), ("batch_config", C.POINTER(SeqBatchConfig)),
+                ("saved_activations", C.POINTER(SeqBatchSavedActivations)), ("context", C.POINTER(SeqBatchContext)),
+                ("activation_workspace", C.POINTER(SeqBatchActivationWorkspace))]

@@ -422,3 +422,202 @@ def test_transformer_head_submits_the_reference_chain(L):
     # a backward pass without its containers is refused before anything is submitted
     log.clear()
     assert L.submit_transformer_head(r(h), 0, 1, r(xin), r(head), r(act), r(out), r(ghead), None, None, None) == -1 and not log
+
+
+# ---- the block callers on a handle made of callbacks ------------------------------------------------------------------------
+
+def _callback_handle(abi, log, fail_on):
+    """A Dataflow_Handle whose function table is Python: every op, memset, copy, stream state and dependency is appended to `log`
+    as (name, stream, values). Op values: every argument in order, scalars by value and pointers as integers."""
+    h = abi.DataflowHandleStruct()
+    state = C.c_int(0)
+
+    def on_op(handle, op_ptr, stream_id):
+        op = op_ptr.contents
+        n = op.op_skeleton.header.num_args
+        vals = []
+        for i, dt in enumerate(list(op.op_skeleton.header.arg_dtypes)[:n]):
+            name = abi.DataflowDatatype(dt).name
+            ctype = {"INT_SCALAR": C.c_int, "FP32_SCALAR": C.c_float, "UINT64": C.c_uint64, "UINT64_SCALAR": C.c_uint64}.get(name, C.c_void_p)
+            vals.append(C.cast(op.op_args[i], C.POINTER(ctype)).contents.value)
+        nick = op.op_skeleton.header.op_nickname.decode()
+        log.append((nick, stream_id, vals))
+        return -7 if nick == fail_on[0] else 0
+
+    cbs = {
+        "submit_op": type(h.submit_op)(on_op),
+        "get_stream_state": type(h.get_stream_state)(lambda hh, s: (log.append(("state", s, [])), C.addressof(state))[1]),
+        "submit_dependency": type(h.submit_dependency)(lambda hh, s, st: (log.append(("dep", s, [st])), 0)[1]),
+        "submit_peer_transfer": type(h.submit_peer_transfer)(lambda hh, s, dst, src, n: (log.append(("copy", s, [dst, src, n])), 0)[1]),
+        "set_mem": type(h.set_mem)(lambda hh, s, p, v, n: (log.append(("set_mem", s, [p, v, n])), 0)[1]),
+    }
+    for k, v in cbs.items():
+        setattr(h, k, v)
+    return h, cbs, C.addressof(state)
+
+
+def _block_containers(abi, base, T=8, nq=4, nkv=2, hd=8, f=48):
+    """A block (or gradient block) and its activation containers with recognisable fake addresses starting at `base`."""
+    BF16, FP32 = int(abi.DataflowDatatype.BF16), int(abi.DataflowDatatype.FP32)
+    keep = []
+    one = lambda addr: (keep.append((C.c_void_p * 1)(addr)), C.cast(keep[-1], C.POINTER(C.c_void_p)))[1]
+    blk = abi.TransformerBlock()
+    c = blk.config
+    c.block_dt, c.compute_dt, c.eps, c.theta = BF16, FP32, 1e-5, 10000
+    c.num_q_heads, c.num_kv_heads, c.head_dim, c.model_dim, c.kv_dim, c.ffn_dim = nq, nkv, hd, nq * hd, nkv * hd, f
+    blk.w_attn_norm, blk.w_q, blk.w_k, blk.w_v, blk.w_o, blk.w_ffn_norm = (base + 0x10 * i for i in range(1, 7))
+    blk.w_1, blk.w_2, blk.w_3 = one(base + 0x70), one(base + 0x80), one(base + 0x90)
+    bc = abi.SeqBatchConfig(2, T, T + 4, base + 0x100, base + 0x110, base + 0x120, 5, base + 0x130, base + 0x140, 7)
+    sv = abi.SeqBatchSavedActivations()
+    sv.attn_norm_weighted_sums, sv.attn_norm_rms_vals, sv.x_q, sv.x_k_local, sv.x_v_local = (base + 0x200 + 0x10 * i for i in range(5))
+    sv.softmax_lse, sv.x_attn_out, sv.x_o, sv.ffn_norm_weighted_sums, sv.ffn_norm_rms_vals = (base + 0x250 + 0x10 * i for i in range(5))
+    sv.x_1, sv.x_2, sv.x_3 = one(base + 0x2a0), one(base + 0x2b0), one(base + 0x2c0)
+    ctx = abi.SeqBatchContext(None, None, 0, base + 0x300, base + 0x310)
+    ws = abi.SeqBatchActivationWorkspace(None, None, 0, base + 0x400, base + 0x410, base + 0x420, base + 0x430, base + 0x440, 4096)
+    act = abi.TransformerBlockActivations(C.pointer(blk), C.pointer(bc), C.pointer(sv), C.pointer(ctx), C.pointer(ws))
+    keep += [blk, bc, sv, ctx, ws]
+    return blk, act, keep
+
+
+def test_transformer_struct_mirrors_match_the_header(tmp_path):
+    """The ctypes mirrors used by the tests have the sizes the C header gives the structs."""
+    from dataflow_lib_b200 import abi
+    names = {"Seq_Batch_Config": abi.SeqBatchConfig, "Seq_Batch_Saved_Activations": abi.SeqBatchSavedActivations,
+             "Seq_Batch_Context": abi.SeqBatchContext, "Seq_Batch_Activation_Workspace": abi.SeqBatchActivationWorkspace,
+             "MoE_Config": abi.MoEConfig, "Transformer_Block_Config": abi.TransformerBlockConfig, "Transformer_Block": abi.TransformerBlock,
+             "Transformer_Block_Activations": abi.TransformerBlockActivations, "Transformer_Head": abi.TransformerHead,
+             "Transformer_Head_Activations": abi.TransformerHeadActivations, "Transformer_Block_Transition": abi.TransformerBlockTransition,
+             "Transformer_Model_Output": abi.TransformerModelOutput}
+    src = tmp_path / "sizes.c"
+    src.write_text('#include "dataflow_transformer.h"\n#include <stdio.h>\nint main(void) {\n' +
+                   "".join(f'printf("{n} %zu\\n", sizeof({n}));\n' for n in names) +
+                   'printf("w_1 %zu x_o %zu\\n", offsetof(Transformer_Block, w_1), offsetof(Seq_Batch_Saved_Activations, x_o));\nreturn 0; }\n')
+    exe = str(tmp_path / "sizes")
+    subprocess.check_call(["gcc", f"-I{ROOT}/include", str(src), "-o", exe])
+    out = dict(line.split(" ", 1) for line in subprocess.check_output([exe], text=True).strip().splitlines())
+    for n, t in names.items():
+        assert int(out[n]) == C.sizeof(t), n
+    assert out["w_1"] == f"{abi.TransformerBlock.w_1.offset} x_o {abi.SeqBatchSavedActivations.x_o.offset}"
+
+
+def test_transformer_block_forward_submits_the_reference_chain(L):
+    """submit_transformer_block on a handle made of callbacks: op order of src/dataflow_models/dataflow_transformer/src/dataflow_transformer.c:72-283,
+    buffer wiring, RoPE in place on x_q / x_k_local, residual projections with beta = 1 and C = the residual, K / V projections with
+    kv_dim outputs, the workspace zeroed before the attention, the output copy ordered after the compute stream."""
+    from dataflow_lib_b200 import abi
+    log, fail_on = [], [None]
+    h, cbs, state = _callback_handle(abi, log, fail_on)
+    B = 0x10000
+    blk, act, keep = _block_containers(abi, B)
+    T, d, kv, f = 8, 32, 16, 48
+    BF16, FP32, NONE = int(abi.DataflowDatatype.BF16), int(abi.DataflowDatatype.FP32), int(abi.DataflowDatatype.NONE)
+    xin, xout = abi.TransformerBlockTransition(None, 0x5000), abi.TransformerBlockTransition(None, 0x6000)
+    r = C.byref
+    assert L.submit_transformer_block(r(h), 2, 3, r(xin), r(blk), r(act), r(xout)) == 0
+    names = [e[0] for e in log]
+    assert names == ["rms_norm_BF16", "matmul", "matmul", "matmul", "rope_BF16", "set_mem", "flash3_attention_fwd", "matmul", "rms_norm_BF16",
+                     "matmul", "matmul", "swiglu_BF16", "matmul", "state", "dep", "copy"]
+    assert all(e[1] == 2 for e in log[:14]) and log[14][1] == 3 and log[15][1] == 3
+
+    def mm(e):      # (to_trans_a, to_trans_b, M, K, N, alpha, beta, c_dt, A, B, C, D)
+        v = e[2]
+        return (v[6], v[7], v[8], v[9], v[10], v[11], v[12], v[3], v[13], v[14], v[15], v[16])
+
+    x_temp, x_mlp = B + 0x400, B + 0x410
+    sums_a, rms_a, x_q, x_k, x_v, lse, attn_out, x_o, sums_f, rms_f = (B + 0x200 + 0x10 * i for i in range(10))
+    x_1, x_2, x_3 = B + 0x2a0, B + 0x2b0, B + 0x2c0
+    assert log[0][2] == [T, d, pytest.approx(1e-5), B + 0x10, 0x5000, x_temp, sums_a, rms_a]
+    assert mm(log[1]) == (1, 0, d, d, T, 1.0, 0.0, NONE, B + 0x20, x_temp, None, x_q)
+    assert mm(log[2]) == (1, 0, kv, d, T, 1.0, 0.0, NONE, B + 0x30, x_temp, None, x_k)
+    assert mm(log[3]) == (1, 0, kv, d, T, 1.0, 0.0, NONE, B + 0x40, x_temp, None, x_v)
+    assert log[4][2] == [T * d, d, 8, 2, 10000, B + 0x100, x_q, x_k]                      # in place on the projections' outputs
+    assert log[5][2] == [B + 0x440, 0, 4096]
+    assert log[6][2] == [BF16, 2, T, T + 4, B + 0x110, B + 0x120, 5, B + 0x130, B + 0x140, 7, 4, 2, 8, x_q, B + 0x300, B + 0x310, attn_out, lse, 4096, B + 0x440]
+    assert mm(log[7]) == (1, 0, d, d, T, 1.0, 1.0, BF16, B + 0x50, attn_out, 0x5000, x_o)    # + the block input (residual)
+    assert log[8][2] == [T, d, pytest.approx(1e-5), B + 0x60, x_o, x_temp, sums_f, rms_f]
+    assert mm(log[9]) == (1, 0, f, d, T, 1.0, 0.0, NONE, B + 0x70, x_temp, None, x_1)
+    assert mm(log[10]) == (1, 0, f, d, T, 1.0, 0.0, NONE, B + 0x90, x_temp, None, x_3)
+    assert log[11][2] == [T, f, x_1, x_3, x_mlp]
+    assert mm(log[12]) == (1, 0, d, f, T, 1.0, 1.0, BF16, B + 0x80, x_mlp, x_o, x_2)          # + x_o (residual)
+    assert log[13][1] == 2 and log[14][2] == [state] and log[15][2] == [0x6000, x_2, T * d * 2]
+    # a failing step ends the chain with its code; no output transition = no copy
+    log.clear()
+    fail_on[0] = "flash3_attention_fwd"
+    assert L.submit_transformer_block(r(h), 0, 1, r(xin), r(blk), r(act), r(xout)) == -1
+    assert [e[0] for e in log][-1] == "flash3_attention_fwd" and len(log) == 7
+    log.clear()
+    fail_on[0] = None
+    assert L.submit_transformer_block(r(h), 0, 1, r(xin), r(blk), r(act), None) == 0 and "copy" not in [e[0] for e in log]
+    assert L.submit_transformer_block(r(h), 0, 1, r(xin), r(blk), None, None) == -1
+
+
+def test_transformer_block_backward_chains(L):
+    """submit_transformer_block_bwd_x and _bwd_w on a handle made of callbacks (dataflow_transformer.c:565-1003): step order, the two
+    RMSNorm input-gradient ops accumulating into the stream gradient, accumulated (C = D, beta = 1) W_3 / W_k / W_v products, d(x_o)
+    kept for the W_o weight gradient, the two recompute RMSNorm calls with NULL statistics, and the weight-gradient products."""
+    from dataflow_lib_b200 import abi
+    log, fail_on = [], [None]
+    h, cbs, state = _callback_handle(abi, log, fail_on)
+    W, G, GW = 0x10000, 0x20000, 0x30000                     # forward containers, gradient containers, gradient weights
+    blk, act, k1 = _block_containers(abi, W)
+    _, gact, k2 = _block_containers(abi, G)
+    gblk, _, k3 = _block_containers(abi, GW)
+    T, d, kv, f = 8, 32, 16, 48
+    BF16, NONE = int(abi.DataflowDatatype.BF16), int(abi.DataflowDatatype.NONE)
+    dstream, xin, dnext = abi.TransformerBlockTransition(None, 0x5000), abi.TransformerBlockTransition(None, 0x6000), abi.TransformerBlockTransition(None, 0x7000)
+    r = C.byref
+    assert L.submit_transformer_block_bwd_x(r(h), 2, 3, r(blk), r(dstream), r(act), r(xin), r(gact), r(gblk), r(dnext)) == 0
+    names = [e[0] for e in log]
+    assert names == ["matmul", "swiglu_bwd_x_BF16_BF16", "matmul", "matmul", "rms_norm_bwd_x_BF16_BF16", "rms_norm_bwd_w_BF16_BF16", "copy",
+                     "matmul", "set_mem", "flash3_attention_bwd", "rope_bwd_x_BF16", "matmul", "matmul", "matmul",
+                     "rms_norm_bwd_x_BF16_BF16", "rms_norm_bwd_w_BF16_BF16", "rms_norm_BF16", "rms_norm_BF16", "state", "dep", "copy"]
+
+    def mm(e):
+        v = e[2]
+        return (v[6], v[7], v[8], v[9], v[10], v[11], v[12], v[3], v[13], v[14], v[15], v[16])
+
+    sv = lambda base, i: base + 0x200 + 0x10 * i          # attn sums, attn rms, x_q, x_k_local, x_v_local, lse, attn_out, x_o, ffn sums, ffn rms
+    g_temp, g_mlp, re_attn, re_ffn, g_ws = G + 0x400, G + 0x410, G + 0x420, G + 0x430, G + 0x440
+    dX = 0x5000
+    assert mm(log[0]) == (0, 0, f, d, T, 1.0, 0.0, NONE, W + 0x80, dX, None, g_mlp)                     # d(swiglu out) = dOut W_2
+    assert log[1][2] == [T, f, W + 0x2a0, W + 0x2c0, g_mlp, G + 0x2a0, G + 0x2c0]
+    assert mm(log[2]) == (0, 0, d, f, T, 1.0, 0.0, NONE, W + 0x70, G + 0x2a0, None, g_temp)
+    assert mm(log[3]) == (0, 0, d, f, T, 1.0, 1.0, BF16, W + 0x90, G + 0x2c0, g_temp, g_temp)           # accumulated
+    assert log[4][2] == [T, d, pytest.approx(1e-5), sv(W, 8), sv(W, 9), W + 0x60, sv(W, 7), g_temp, dX]   # accumulates into the stream gradient
+    assert log[5][2] == [T, d, pytest.approx(1e-5), sv(W, 9), sv(W, 7), g_temp, GW + 0x60]
+    assert log[6][1] == 2 and log[6][2] == [sv(G, 7), dX, T * d * 2]                                      # d(x_o) kept
+    assert mm(log[7]) == (0, 0, d, d, T, 1.0, 0.0, NONE, W + 0x50, sv(G, 7), None, g_temp)
+    assert log[8][2] == [g_ws, 0, 4096]
+    assert log[9][2] == [BF16, 2, T, T + 4, G + 0x110, G + 0x120, 5, G + 0x130, G + 0x140, 7, 4, 2, 8, sv(W, 2), W + 0x300, W + 0x310, sv(W, 6), sv(W, 5),
+                         g_temp, sv(G, 2), G + 0x300, G + 0x310, 4096, g_ws]
+    assert log[10][2] == [T * d, d, 8, 2, 10000, G + 0x100, sv(G, 2), sv(G, 3)]
+    assert mm(log[11]) == (0, 0, d, d, T, 1.0, 0.0, NONE, W + 0x20, sv(G, 2), None, g_temp)
+    assert mm(log[12]) == (0, 0, d, kv, T, 1.0, 1.0, BF16, W + 0x30, sv(G, 3), g_temp, g_temp)
+    assert mm(log[13]) == (0, 0, d, kv, T, 1.0, 1.0, BF16, W + 0x40, sv(G, 4), g_temp, g_temp)
+    assert log[14][2] == [T, d, pytest.approx(1e-5), sv(W, 0), sv(W, 1), W + 0x10, 0x6000, g_temp, dX]
+    assert log[15][2] == [T, d, pytest.approx(1e-5), sv(W, 1), 0x6000, g_temp, GW + 0x10]
+    assert log[16][2] == [T, d, pytest.approx(1e-5), W + 0x10, 0x6000, re_attn, None, None]
+    assert log[17][2] == [T, d, pytest.approx(1e-5), W + 0x60, sv(W, 7), re_ffn, None, None]
+    assert log[19][1] == 3 and log[20][1] == 3 and log[20][2] == [0x7000, dX, T * d * 2]
+    assert all(e[1] == 2 for e in log[:19])
+
+    # weight gradients
+    log.clear()
+    dout = abi.TransformerBlockTransition(None, 0x8000)
+    assert L.submit_transformer_block_bwd_w(r(h), 4, r(dout), r(act), r(gact), r(gblk)) == 0
+    assert [e[0] for e in log] == ["swiglu_BF16"] + ["matmul"] * 7 and all(e[1] == 4 for e in log)
+    assert log[0][2] == [T, f, W + 0x2a0, W + 0x2c0, g_mlp]
+    wg = lambda e: mm(e)
+    assert wg(log[1]) == (0, 1, f, T, d, 1.0, 1.0, BF16, g_mlp, 0x8000, GW + 0x80, GW + 0x80)            # dW_2 [d, f] += dOut^T h
+    assert wg(log[2]) == (0, 1, d, T, f, 1.0, 1.0, BF16, re_ffn, G + 0x2a0, GW + 0x70, GW + 0x70)
+    assert wg(log[3]) == (0, 1, d, T, f, 1.0, 1.0, BF16, re_ffn, G + 0x2c0, GW + 0x90, GW + 0x90)
+    assert wg(log[4]) == (0, 1, d, T, d, 1.0, 1.0, BF16, sv(W, 6), sv(G, 7), GW + 0x50, GW + 0x50)
+    assert wg(log[5]) == (0, 1, d, T, kv, 1.0, 1.0, BF16, re_attn, sv(G, 4), GW + 0x40, GW + 0x40)
+    assert wg(log[6]) == (0, 1, d, T, kv, 1.0, 1.0, BF16, re_attn, sv(G, 3), GW + 0x30, GW + 0x30)
+    assert wg(log[7]) == (0, 1, d, T, d, 1.0, 1.0, BF16, re_attn, sv(G, 2), GW + 0x20, GW + 0x20)
+    # failures propagate
+    log.clear()
+    fail_on[0] = "flash3_attention_bwd"
+    assert L.submit_transformer_block_bwd_x(r(h), 2, 3, r(blk), r(dstream), r(act), r(xin), r(gact), r(gblk), None) == -1
+    assert [e[0] for e in log][-1] == "flash3_attention_bwd"
+    assert L.submit_transformer_block_bwd_w(r(h), 4, r(dout), r(act), None, r(gblk)) == -1
