@@ -139,7 +139,9 @@ def test_block_forward_and_backward_chains(standin):
     check_lowp(B(g["x_3"]), d3, O.BF16, "d(x_3)")
     t = _mm(B(g["x_3"]), host["W3"], _mm(B(g["x_1"]), host["W1"], transpose_b=False), transpose_b=False)     # d(FFN norm output)
     dxo_ref = O.rms_norm_bwd_x(O.BF16, O.BF16, a["sums_f"].cpu().numpy(), a["rms_f"].cpu().numpy(), host["w_fn"], B(a["x_o"]), t, host["dOut"])
-    check_lowp(B(g["x_o"]), dxo_ref, O.BF16, "d(x_o) = output gradient + FFN norm path")
+    # `t` is made here, not read from the device (x_temp is reused later in the chain): where the two GEMMs round an element of it to
+    # different bf16 neighbours the product dY * deriv moves by that unit on top of its own rounding, hence 2e-2 for this op's output
+    check_lowp(B(g["x_o"]), dxo_ref, O.BF16, "d(x_o) = output gradient + FFN norm path", rel=2e-2)
     check_lowp(B(gdev["w_fn"]), O.rms_norm_bwd_w(O.BF16, O.BF16, a["rms_f"].cpu().numpy(), B(a["x_o"]), t, g0["w_fn"]), O.BF16, "dW_ffn_norm", rel=2e-2)
     u = _mm(B(g["x_o"]), host["Wo"], transpose_b=False)                                   # d(x_attn_out); the stand-in hands it on as d(x_q)
     dq_ref, dk_ref = O.rope(O.BF16, d, hd, nkv, theta, pos, u, B(a["x_k"]), bwd=True)     # ... and x_k as d(x_k), both then rotated back
@@ -150,7 +152,7 @@ def test_block_forward_and_backward_chains(standin):
     t2 = _mm(B(g["x_k"]), host["Wk"], t2, transpose_b=False)
     t2 = _mm(B(g["x_v"]), host["Wv"], t2, transpose_b=False)                               # d(attention norm output)
     dx_ref = O.rms_norm_bwd_x(O.BF16, O.BF16, a["sums_a"].cpu().numpy(), a["rms_a"].cpu().numpy(), host["w_an"], host["X"], t2, B(g["x_o"]))
-    check_lowp(B(dX), dx_ref, O.BF16, "gradient with respect to the block input")
+    check_lowp(B(dX), dx_ref, O.BF16, "gradient with respect to the block input", rel=2e-2)        # t2 is made here too
     check_lowp(B(gdev["w_an"]), O.rms_norm_bwd_w(O.BF16, O.BF16, a["rms_a"].cpu().numpy(), host["X"], t2, g0["w_an"]), O.BF16, "dW_attn_norm", rel=2e-2)
     check_lowp(B(g["re_attn"]), hn, O.BF16, "recomputed attention norm")
     check_lowp(B(g["re_ffn"]), fn, O.BF16, "recomputed FFN norm")
