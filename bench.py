@@ -144,29 +144,33 @@ def reference_convert_rate(threads):
             "this_library_elements_per_s": r_own, "identical_output": bool(np.array_equal(dst_ref, dst_own))}
 
 
+def chain_config(world):
+    """The `config` object of the JSON line: the same for this library's arm and for the CPU arm, so that the two lines compare."""
+    return {"workload": WORKLOAD, "tokens_per_gpu": TOKENS, "l2": "inputs larger than L2 (1.7 GiB touched per step vs 126 MB)",
+            "parallelism": f"token-sharded x{world}" + (", NCCL all-reduce (from C) of the packed loss / RMSNorm weight gradient buffer" if world > 1 else "")}
+
+
 def run_reference_arm(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
     threads = os.cpu_count() or 1
-    rate, _ = cpu_chain_tokens_per_s(64, threads)
-    # a step is a bounded sample of the workload: about min(1 s, 150 s / K) of CPU work
-    sample = int(max(64, min(TOKENS, rate * min(1.0, 150.0 / max(args.steps, 1)))))
-    sample -= sample % 64
+    # a step is one pass of the chain over the whole batch of 8192 tokens, as in this library's arm (0.3 - 0.5 s on 16 - 32 host threads)
     for _ in range(args.warmup):
-        cpu_chain_tokens_per_s(sample, threads)
+        cpu_chain_tokens_per_s(TOKENS, threads)
     times = []
     for _ in range(args.steps):
-        _, secs = cpu_chain_tokens_per_s(sample, threads)
+        _, secs = cpu_chain_tokens_per_s(TOKENS, threads)
         times.append(secs)
     total = sum(times)
-    value = sample * args.steps / total
+    value = TOKENS * args.steps / total
     line = {
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": 1e3 * total / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
-        "data": "synthetic", "config": {"workload": WORKLOAD, "note": "the reference ships these ops only as CUDA kernels; this arm is the CPU port "
-                                        "of their arithmetic (oracle/oracle.c), each step a bounded sample of the workload (see cpu_baseline.sample)"},
-        "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": "port", "sample": f"{sample} tokens per step on {threads} threads"},
+        "data": "synthetic", "config": chain_config(args.gpus),
+        "note": "the reference ships these ops only as CUDA kernels; this arm is the CPU port of their arithmetic (oracle/oracle.c) on all host "
+                "threads of rank 0, one full batch per step; it does not grow with --gpus",
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": "port", "sample": f"{TOKENS} tokens per step on {threads} threads"},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
@@ -200,11 +204,18 @@ def other_configs(hbm_peak):
     X, dY, w = rn(R, C), rn(R, C), (1 + 0.02 * torch.randn(C, device="cuda", generator=g)).bfloat16()
     Y, dX, dW = torch.empty_like(X), torch.zeros_like(X), torch.zeros(C, device="cuda", dtype=torch.bfloat16)
     ws, rms = torch.empty(R, device="cuda"), torch.empty(R, device="cuda")
+    def c1_sequence():
+        ops.rms_norm(R, C, EPS, w, X, Y, ws, rms)
+        ops.rms_norm_bwd_x(R, C, EPS, ws, rms, w, X, dY, dX)
+        ops.rms_norm_bwd_w(R, C, EPS, rms, X, dY, dW)
     out["c1_rms_norm_4096x4096"] = {
         "fwd": hbm(2 * R * C * 2, timed(lambda: ops.rms_norm(R, C, EPS, w, X, Y, ws, rms))),
         "bwd_x": hbm(4 * R * C * 2, timed(lambda: ops.rms_norm_bwd_x(R, C, EPS, ws, rms, w, X, dY, dX))),
         "bwd_w": hbm(2 * R * C * 2, timed(lambda: ops.rms_norm_bwd_w(R, C, EPS, rms, X, dY, dW))),
-        "note": "64-128 MiB per launch against a 126 MB L2: repeated launches partly hit L2"}
+        "fwd_bwd_x_bwd_w_sequence": hbm(8 * R * C * 2, timed(c1_sequence, 20)),
+        "note": "the configuration as it is run: forward, input gradient and weight gradient back to back (4 launches, programmatic dependent "
+                "launches), 256 MiB algorithmic per sequence; the whole working set (4 x 32 MiB) is of the order of the 126 MB L2, so single ops "
+                "repeated in isolation partly hit L2 and can read above the DRAM ceiling"}
     del X, dY, Y, dX
     # C3: fused softmax + cross entropy 16384 x 128256
     T3, V = 16384, 128256
@@ -236,9 +247,32 @@ def other_configs(hbm_peak):
     ops.swiglu_ffn_fp8_bwd(T4, D_MODEL, FFN, dO, G, U, WdT, sd, WguT, sgu, dA, dgate_dup=dGU)
     dWg, dWu, dWd = (torch.empty(s_, device="cuda", dtype=torch.bfloat16) for s_ in ((FFN, D_MODEL), (FFN, D_MODEL), (D_MODEL, FFN)))
     ms_w = timed(lambda: ops.swiglu_ffn_fp8_wgrad(T4, D_MODEL, FFN, A, dO, G, U, dGU, dWg, dWu, dWd))
-    out["c4_swiglu_ffn_fp8_16384x4096x14336"] = {"fwd": {"ms": ms_f, "TFLOP/s": flops / ms_f / 1e9}, "bwd_input_grad": {"ms": ms_b, "TFLOP/s": flops / ms_b / 1e9},
-                                                 "bwd_weight_grads": {"ms": ms_w, "TFLOP/s": flops / ms_w / 1e9},
-                                                 "tokens_per_s_fwd_bwd": T4 / ((ms_f + ms_b + ms_w) * 1e-3)}
+    # the tensor ceiling, measured in this run: the library's e4m3 GEMM (torch._scaled_mm -> cuBLASLt) alone on the GEMM shapes of each
+    # pass, without the quantisation passes an FFN op also has to run (MEASURED_PEAKS.json holds no fp8 figure)
+    one = torch.ones((), device="cuda")
+    def lib_gemm_ms(m, n, k):
+        A8 = torch.randn(m, k, device="cuda", generator=g).to(torch.float8_e4m3fn)
+        B8 = torch.randn(n, k, device="cuda", generator=g).to(torch.float8_e4m3fn).t()
+        return timed(lambda: torch._scaled_mm(A8, B8, scale_a=one, scale_b=one, out_dtype=torch.bfloat16))
+    try:
+        g_up, g_down, g_dgrad = lib_gemm_ms(T4, FFN, D_MODEL), lib_gemm_ms(T4, D_MODEL, FFN), lib_gemm_ms(T4, D_MODEL, 2 * FFN)
+        g_wdown, g_wup = lib_gemm_ms(D_MODEL, FFN, T4), lib_gemm_ms(FFN, D_MODEL, T4)
+        lib = {"fwd": 2 * g_up + g_down, "bwd_input_grad": g_up + g_dgrad, "bwd_weight_grads": g_wdown + 2 * g_wup}
+    except Exception as e:                                       # the library lacks an fp8 GEMM here: report without the fraction
+        lib = {}
+        print(f"note: no library e4m3 GEMM for the in-run ceiling ({e})", file=sys.stderr)
+    def entry(name, ms):
+        d = {"ms": ms, "TFLOP/s": flops / ms / 1e9}
+        if name in lib:
+            d["library_gemms_alone_ms"] = lib[name]
+            d["library_gemms_alone_TFLOP/s"] = flops / lib[name] / 1e9
+            d["frac"] = lib[name] / ms
+        return d
+    out["c4_swiglu_ffn_fp8_16384x4096x14336"] = {
+        "fwd": entry("fwd", ms_f), "bwd_input_grad": entry("bwd_input_grad", ms_b), "bwd_weight_grads": entry("bwd_weight_grads", ms_w),
+        "tokens_per_s_fwd_bwd": T4 / ((ms_f + ms_b + ms_w) * 1e-3),
+        "frac_is": "time of the library's e4m3 GEMMs (cuBLASLt through torch._scaled_mm) alone on the pass's GEMM shapes / time of the pass, "
+                   "both measured in this run; the pass also quantises its activations, which the library figure leaves out"}
     return out
 
 
@@ -283,15 +317,38 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(sm)}
 
 
+def seeded_inputs(rank):
+    """Host inputs of the chain: seed 0 + rank for the data, identical weights on all ranks. numpy normals rounded to bf16 by torch on the
+    CPU; returned as raw 16-bit arrays (what the handle's transfers move)."""
+    import numpy as np
+    import torch
+
+    def normal_bf16(shape, seed, mean=0.0, std=1.0):
+        a = np.random.default_rng(seed).standard_normal(shape, dtype=np.float32)
+        if mean != 0.0 or std != 1.0:
+            a = mean + std * a
+        return torch.from_numpy(a).bfloat16().view(torch.int16).numpy().view(np.uint16)
+
+    T, seed = TOKENS, 1000 * rank
+    return {
+        "X": normal_bf16((T, D_MODEL), seed + 1), "w": normal_bf16((D_MODEL,), 2, 1.0, 0.02), "dY": normal_bf16((T, D_MODEL), seed + 3),
+        "Q": normal_bf16((T, N_HEADS * HEAD_DIM), seed + 4), "K": normal_bf16((T, N_KV * HEAD_DIM), seed + 5),
+        "gate": normal_bf16((T, FFN), seed + 6), "up": normal_bf16((T, FFN), seed + 7), "dS": normal_bf16((T, FFN), seed + 8),
+        "pos": np.arange(T, dtype=np.int32),
+    }
+
+
 def run_gpu_arm(args):
+    import ctypes as C
+
     import numpy as np
     import torch
     import torch.distributed as dist
 
-    import oracle as O   # input generation only (seeded fills); the timed path never touches it
     from dataflow_lib_b200 import DataflowHandle
+    from dataflow_lib_b200 import _lib as _dl
     from dataflow_lib_b200.abi import DataflowDatatype as DT
-    from dataflow_lib_b200.sharding import allreduce_step
+    from dataflow_lib_b200.sharding import Exchange, PackedReduction
 
     rank, world, local = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1")), int(os.environ.get("LOCAL_RANK", "0"))
     assert world == args.gpus, f"--gpus {args.gpus} but WORLD_SIZE={world} (launch N > 1 with torchrun)"
@@ -300,68 +357,72 @@ def run_gpu_arm(args):
         quiet_nccl_banner()
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
 
-    h = DataflowHandle(device_id=local, num_streams=2)
+    # stream 0 computes; stream 1 (higher priority) carries the exchange; stream 2, in the end-to-end region, the next step's uploads
+    h = DataflowHandle(device_id=local, num_streams=3, stream_prios=[0, -1, 0])
     stream = torch.cuda.ExternalStream(h.stream_ptr(0), device=torch.device("cuda", local))
     stream1 = torch.cuda.ExternalStream(h.stream_ptr(1), device=torch.device("cuda", local))
-    exchange_state = [None]
-    BF, S0 = int(DT.BF16), 0
+    BF, S0, S1, S2 = int(DT.BF16), 0, 1, 2
     T = TOKENS
+    L, hp = _dl.lib, C.byref(h.h)
 
-    # ---- host inputs (seed 0 + rank for data, identical weights on all ranks), pinned through the handle
-    seed = 1000 * rank
-    host = {
-        "X": O.fill_normal(O.BF16, (T, D_MODEL), seed + 1), "w": O.fill_normal(O.BF16, (D_MODEL,), 2, 1.0, 0.02),
-        "dY": O.fill_normal(O.BF16, (T, D_MODEL), seed + 3), "Q": O.fill_normal(O.BF16, (T, N_HEADS * HEAD_DIM), seed + 4),
-        "K": O.fill_normal(O.BF16, (T, N_KV * HEAD_DIM), seed + 5), "gate": O.fill_normal(O.BF16, (T, FFN), seed + 6),
-        "up": O.fill_normal(O.BF16, (T, FFN), seed + 7), "dS": O.fill_normal(O.BF16, (T, FFN), seed + 8),
-        "pos": np.arange(T, dtype=np.int32),
-    }
+    # ---- host inputs, pinned through the handle
+    host = seeded_inputs(rank)
     for a in host.values():
         assert h.enable_access_to_host_mem(a.ctypes.data, a.nbytes, 0) == 0
-    out_host = {"dW": np.zeros(D_MODEL, np.uint16), "rms": np.zeros(T, np.float32), "ws": np.zeros(T, np.float32)}
+    out_host = {"dW": np.zeros(D_MODEL, np.float32 if world > 1 else np.uint16), "rms": np.zeros(T, np.float32), "ws": np.zeros(T, np.float32)}
     for a in out_host.values():
         assert h.enable_access_to_host_mem(a.ctypes.data, a.nbytes, 0) == 0
 
-    dev = {k: torch.empty(v.shape, dtype=torch.int32 if k == "pos" else torch.bfloat16, device="cuda") for k, v in host.items()}
-    Y, dX = torch.empty_like(dev["X"]), torch.zeros_like(dev["X"])
-    S, d1, d3 = torch.empty_like(dev["gate"]), torch.empty_like(dev["gate"]), torch.empty_like(dev["gate"])
+    def device_set():
+        return {k: torch.empty(v.shape, dtype=torch.int32 if k == "pos" else torch.bfloat16, device="cuda") for k, v in host.items()}
+    sets = [device_set(), device_set()]           # two input sets: the end-to-end region uploads step s + 1 while step s computes
+    Y, dX = torch.empty_like(sets[0]["X"]), torch.zeros_like(sets[0]["X"])
+    S, d1, d3 = (torch.empty_like(sets[0]["gate"]) for _ in range(3))
     dW = torch.zeros(D_MODEL, dtype=torch.bfloat16, device="cuda")
     ws, rms = torch.empty(T, device="cuda"), torch.empty(T, device="cuda")
-    step_loss = torch.zeros(2, device="cuda")            # [loss sum, valid rows]: unused by this chain, part of the packed exchange
+    # The step's reductions over tokens: [loss sum, valid rows | dW]. At N > 1 the weight-gradient kernel writes its fp32 column sums
+    # straight into the dW slot and the packed buffer is all-reduced in place by the library's C exchange (NCCL called from C); the
+    # chain has no loss, so those two floats stay zero.
+    packed = PackedReduction([D_MODEL], device="cuda")
+    exchange = Exchange(h) if world > 1 else None
 
-    def upload():
+    def upload(dev, stream_id):
         for k, a in host.items():
-            assert h.submit_inbound_transfer(S0, dev[k], a.ctypes.data, a.nbytes) == 0
+            assert h.submit_inbound_transfer(stream_id, dev[k], a.ctypes.data, a.nbytes) == 0
 
     op_names = ["rms_norm", "rope", "swiglu", "swiglu_bwd_x", "rope_bwd_x", "rms_norm_bwd_x", "rms_norm_bwd_w"]
-
     DOM = op_names.index(DOMINANT)
-
-    # The submissions of one step, bound once: the C entry points (submit_* of include/dataflow_api.h) with plain
-    # integer pointers, so that the per-step host work is the C path (skeleton + SHA-256 + table lookup + launch)
-    # and not Python argument marshalling.
-    import ctypes as C
-    from dataflow_lib_b200 import _lib as _dl
-    L, hp = _dl.lib, C.byref(h.h)
-    P = {k: v.data_ptr() for k, v in dev.items()}
     N = T * N_HEADS * HEAD_DIM
-    calls = [
-        lambda: L.submit_rms_norm(hp, S0, BF, T, D_MODEL, EPS, P["w"], P["X"], Y.data_ptr(), ws.data_ptr(), rms.data_ptr()),
-        lambda: L.submit_rope(hp, S0, BF, N, N_HEADS * HEAD_DIM, HEAD_DIM, N_KV, THETA, P["pos"], P["Q"], P["K"]),
-        lambda: L.submit_swiglu(hp, S0, BF, T, FFN, P["gate"], P["up"], S.data_ptr()),
-        lambda: L.submit_swiglu_bwd_x(hp, S0, BF, BF, T, FFN, P["gate"], P["up"], P["dS"], d1.data_ptr(), d3.data_ptr()),
-        lambda: L.submit_rope_bwd_x(hp, S0, BF, N, N_HEADS * HEAD_DIM, HEAD_DIM, N_KV, THETA, P["pos"], P["Q"], P["K"]),
-        lambda: L.submit_rms_norm_bwd_x(hp, S0, BF, BF, T, D_MODEL, EPS, ws.data_ptr(), rms.data_ptr(), P["w"], P["X"], P["dY"], dX.data_ptr()),
-        lambda: L.submit_rms_norm_bwd_w(hp, S0, BF, BF, T, D_MODEL, EPS, rms.data_ptr(), P["X"], P["dY"], dW.data_ptr()),
-    ]
 
-    def chain(events=None, only=None):
-        """One step. `events[i] = (start, end)` are recorded around op i (all ops, or just op `only`)."""
+    def bind(dev):
+        """The submissions of one step on input set `dev`, bound once: the C entry points (submit_* of include/dataflow_api.h) with plain
+        integer pointers, so that the per-step host work is the C path (skeleton + SHA-256 + table lookup + launch)."""
+        P = {k: v.data_ptr() for k, v in dev.items()}
+        calls = [
+            lambda: L.submit_rms_norm(hp, S0, BF, T, D_MODEL, EPS, P["w"], P["X"], Y.data_ptr(), ws.data_ptr(), rms.data_ptr()),
+            lambda: L.submit_rope(hp, S0, BF, N, N_HEADS * HEAD_DIM, HEAD_DIM, N_KV, THETA, P["pos"], P["Q"], P["K"]),
+            lambda: L.submit_swiglu(hp, S0, BF, T, FFN, P["gate"], P["up"], S.data_ptr()),
+            lambda: L.submit_swiglu_bwd_x(hp, S0, BF, BF, T, FFN, P["gate"], P["up"], P["dS"], d1.data_ptr(), d3.data_ptr()),
+            lambda: L.submit_rope_bwd_x(hp, S0, BF, N, N_HEADS * HEAD_DIM, HEAD_DIM, N_KV, THETA, P["pos"], P["Q"], P["K"]),
+            lambda: L.submit_rms_norm_bwd_x(hp, S0, BF, BF, T, D_MODEL, EPS, ws.data_ptr(), rms.data_ptr(), P["w"], P["X"], P["dY"], dX.data_ptr()),
+        ]
+        if world > 1:       # the weight gradient as fp32 column sums in its slot of the packed buffer (overwritten every step)
+            calls.append(lambda: L.submit_rms_norm_bwd_w_sums(hp, S0, BF, BF, T, D_MODEL, EPS, rms.data_ptr(), P["X"], P["dY"], packed.dW[0].data_ptr()))
+        else:               # the reference's identity: accumulates into the bf16 dW
+            calls.append(lambda: L.submit_rms_norm_bwd_w(hp, S0, BF, BF, T, D_MODEL, EPS, rms.data_ptr(), P["X"], P["dY"], dW.data_ptr()))
+        return calls
+    bound = [bind(sets[0]), bind(sets[1])]
+    exchange_pending = [False]
+
+    def chain(events=None, only=None, which=0):
+        """One step on input set `which`. `events[i] = (start, end)` are recorded around op i (all ops, or just op `only`)."""
+        calls = bound[which]
         for i, call in enumerate(calls):
             timed = events is not None and (only is None or only == i)
-            if world > 1 and i == len(calls) - 1 and exchange_state[0] is not None:
-                # rms_norm_bwd_w rewrites dW: it has to wait for the previous step's exchange, which ran on stream 1
-                assert h.submit_dependency(S0, exchange_state[0]) == 0
+            if world > 1 and i == len(calls) - 1 and exchange_pending[0]:
+                # the weight-gradient kernel rewrites the packed buffer: it waits for the previous step's exchange on stream 1
+                assert h.submit_dependency(S0, h.get_stream_state(S1)) == 0
+                exchange_pending[0] = False
             if timed:
                 events[i][0].record(stream)
             rc = call()
@@ -370,144 +431,221 @@ def run_gpu_arm(args):
             if rc != 0:
                 raise RuntimeError(f"submit of {op_names[i]} failed")
         if world > 1:
-            # the data-parallel exchange (one packed fp32 all-reduce, 16 KB) runs on the handle's second stream behind a
-            # dependency on the compute stream, so that it overlaps the next step's kernels
-            assert h.submit_dependency(1, h.get_stream_state(S0)) == 0
-            with torch.cuda.stream(stream1):
-                allreduce_step(step_loss, [dW])
-            exchange_state[0] = h.get_stream_state(1)
+            # the data-parallel exchange (one in-place fp32 all-reduce of 16 KB, issued from C) runs on the handle's second stream behind
+            # a dependency on the compute stream, so that it overlaps the next step's kernels
+            assert h.submit_dependency(S1, h.get_stream_state(S0)) == 0
+            assert exchange.all_reduce(S1, packed) == 0
+            exchange_pending[0] = True
 
     def join_exchange():
-        if world > 1 and exchange_state[0] is not None:
-            assert h.submit_dependency(S0, exchange_state[0]) == 0
+        if world > 1 and exchange_pending[0]:
+            assert h.submit_dependency(S0, h.get_stream_state(S1)) == 0
+            exchange_pending[0] = False
 
     def barrier():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
 
-    upload()
-    h.sync_stream(S0)
+    upload(sets[0], S0)
+    upload(sets[1], S0)
+    assert h.sync_stream(S0) == 0
     for _ in range(max(args.warmup, 3)):
         chain()
+    join_exchange()
     barrier()
 
     sampler = ClockSampler("GPU-" + str(torch.cuda.get_device_properties(local).uuid)) if rank == 0 else None
 
-    # ---- timed region 1: inputs resident in HBM. Only the dominant kernel is bracketed by events here (an event
-    # pair costs a few microseconds of stream serialisation, which seven pairs per 0.4 ms step would distort).
+    # ---- timed regions 1: inputs resident in HBM; EXACTLY `steps` steps per region, `repeats` regions, each bracketed by a barrier and a
+    # synchronize; the median region is reported (with the spread). Only the dominant kernel is bracketed by events (an event pair costs
+    # a few microseconds of stream serialisation, which seven pairs per 0.4 ms step would distort).
     new_events = lambda: [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in op_names]
-    ev = [new_events() for _ in range(args.steps)]
-    t_begin, t_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    region_ms, dom_ms_all, enqueue_ms = [], [], []
+    for _ in range(max(args.repeats, 1)):
+        ev = [new_events() for _ in range(args.steps)]
+        t_begin, t_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        host_t0 = time.perf_counter()
+        t_begin.record(stream)
+        for s in range(args.steps):
+            chain(ev[s], only=DOM)
+        join_exchange()
+        t_end.record(stream)
+        enqueue_ms.append(1e3 * (time.perf_counter() - host_t0) / args.steps)      # host time to submit one step (no sync)
+        barrier()
+        region_ms.append(t_begin.elapsed_time(t_end))
+        dom_ms_all.append(statistics.mean(ev[s][DOM][0].elapsed_time(ev[s][DOM][1]) for s in range(args.steps)))
+    regions = torch.tensor(region_ms, device="cuda", dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(regions, op=dist.ReduceOp.MAX)           # per region: the slowest rank
+    region_ms = regions.tolist()
+    ms_total = statistics.median(region_ms)
+    dom_ms = statistics.median(dom_ms_all)
+    host_enqueue_ms = statistics.median(enqueue_ms)
+
+    # ---- untimed: the dominant kernel alone, back to back (every launch re-reads its 0.7 GB of inputs from DRAM: it walks the tensors
+    # from the end, so what the previous launch left in L2 is the part it reads last)
+    iso = [torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)]
+    bound[0][DOM](); barrier()
+    iso[0].record(stream)
+    for _ in range(20):
+        bound[0][DOM]()
+    iso[1].record(stream)
     barrier()
-    host_t0 = time.perf_counter()
-    t_begin.record(stream)
-    for s in range(args.steps):
-        chain(ev[s], only=DOM)
-    join_exchange()
-    t_end.record(stream)
-    host_enqueue_ms = 1e3 * (time.perf_counter() - host_t0) / args.steps      # host time to submit one step (no sync)
-    barrier()
-    ms_total = t_begin.elapsed_time(t_end)
-    dom_ms = statistics.mean(ev[s][DOM][0].elapsed_time(ev[s][DOM][1]) for s in range(args.steps))
+    dom_alone_ms = iso[0].elapsed_time(iso[1]) / 20
 
     # ---- untimed pass: every op bracketed, for the per-op table (event-to-event times include launch latency)
     prof_steps = min(args.steps, 50)
     evp = [new_events() for _ in range(prof_steps)]
     for s in range(prof_steps):
         chain(evp[s])
+    join_exchange()
     barrier()
     per_op_ms = {name: statistics.mean(evp[s][i][0].elapsed_time(evp[s][i][1]) for s in range(prof_steps)) for i, name in enumerate(op_names)}
 
-    # ---- timed region 2: end to end with host buffers through the handle's transfer calls
+    # ---- untimed check of the multi-rank path: the packed buffer after the C exchange against the same partial sums all-reduced by
+    # torch.distributed, and against world x this rank's own sums where every rank holds the same data
+    exchange_check = None
+    if world > 1:
+        local_sums = torch.empty(D_MODEL, device="cuda")
+        with torch.cuda.stream(stream):
+            assert L.submit_rms_norm_bwd_w_sums(hp, S0, BF, BF, T, D_MODEL, EPS, rms.data_ptr(), sets[0]["X"].data_ptr(), sets[0]["dY"].data_ptr(), local_sums.data_ptr()) == 0
+        chain(); join_exchange()
+        barrier()
+        want = local_sums.clone()
+        dist.all_reduce(want)
+        got = packed.dW[0]
+        err = ((got - want).abs().max() / want.abs().max().clamp_min(1e-30)).item()
+        exchange_check = {"max_rel_diff_vs_torch_all_reduce": err, "ok": bool(err <= 1e-6), "loss_slots": packed.loss.tolist()}
+        if not exchange_check["ok"]:
+            print(f"warning: the C exchange and torch.distributed disagree (max relative difference {err:g})", file=sys.stderr)
+
+    # ---- timed region 2: end to end with host buffers through the handle's transfer calls. Every step's inputs come from pinned host
+    # memory (submit_inbound_transfer) and its results go back (submit_outbound_transfer) and are waited for; the uploads of step s + 1
+    # run on stream 1 into the other input set while step s computes on stream 0.
     e2e_steps = max(3, min(args.steps, 10))
     h2d = sum(a.nbytes for a in host.values())
+    grad_src = packed.dW[0] if world > 1 else dW
     d2h = sum(a.nbytes for a in out_host.values())
 
-    def e2e_step():
-        upload()
-        chain()
-        join_exchange()
-        assert h.submit_outbound_transfer(S0, out_host["dW"].ctypes.data, dW, out_host["dW"].nbytes) == 0
-        assert h.submit_outbound_transfer(S0, out_host["rms"].ctypes.data, rms, out_host["rms"].nbytes) == 0
-        assert h.submit_outbound_transfer(S0, out_host["ws"].ctypes.data, ws, out_host["ws"].nbytes) == 0
-        h.sync_stream(S0)                                # the host consumes the result every step
+    def e2e_region(n_steps):
+        upload(sets[0], S2)
+        for s in range(n_steps):
+            b = s & 1
+            assert h.submit_dependency(S0, h.get_stream_state(S2)) == 0      # this step's inputs have arrived
+            if s + 1 < n_steps:
+                upload(sets[1 - b], S2)                                          # the next step's inputs, beside this step's kernels
+            chain(which=b)
+            join_exchange()
+            assert h.submit_outbound_transfer(S0, out_host["dW"].ctypes.data, grad_src, out_host["dW"].nbytes) == 0
+            assert h.submit_outbound_transfer(S0, out_host["rms"].ctypes.data, rms, out_host["rms"].nbytes) == 0
+            assert h.submit_outbound_transfer(S0, out_host["ws"].ctypes.data, ws, out_host["ws"].nbytes) == 0
+            assert h.sync_stream(S0) == 0                                        # the host consumes the result every step
 
-    e2e_step()
-    e_begin, e_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e2e_region(2)
+    e2e_ms = []
+    for _ in range(3):
+        e_begin, e_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        e_begin.record(stream)
+        e2e_region(e2e_steps)
+        e_end.record(stream)
+        barrier()
+        e2e_ms.append(e_begin.elapsed_time(e_end))
+    # the host-side ceiling of that region: the same uploads alone, all ranks at once
+    c0, c1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
-    e_begin.record(stream)
-    for _ in range(e2e_steps):
-        e2e_step()
-    e_end.record(stream)
+    c0.record(stream1)
+    for _ in range(3):
+        upload(sets[0], S1)
+    c1.record(stream1)
     barrier()
-    ms_e2e = e_begin.elapsed_time(e_end)
+    copy_ms = c0.elapsed_time(c1) / 3
 
     clocks = sampler.stop() if sampler else None
 
-    times = torch.tensor([ms_total, ms_e2e], device="cuda", dtype=torch.float64)
+    times = torch.tensor(e2e_ms + [copy_ms], device="cuda", dtype=torch.float64)
     if world > 1:
         dist.all_reduce(times, op=dist.ReduceOp.MAX)
-    ms_total, ms_e2e = times.tolist()
+    *e2e_ms, copy_ms = times.tolist()
+    ms_e2e = statistics.median(e2e_ms)
+
+    c5 = None
+    if not args.no_stack:
+        # configuration C5 on the same GPUs: the token-sharded 4-layer step, after the chain's timed regions
+        c5 = stack_step_report(rank, world, local, steps=5, warmup=3, tokens=16384)
 
     if rank == 0:
         peak, peak_src = measured_peak_hbm()
         dom_bytes = BYTES_PER_TOKEN[DOMINANT] * T
-        achieved = dom_bytes / (dom_ms * 1e-3) / 1e9
+        achieved, alone = dom_bytes / (dom_ms * 1e-3) / 1e9, dom_bytes / (dom_alone_ms * 1e-3) / 1e9
         ops_report = {name: {"ms": per_op_ms[name], "GB/s": BYTES_PER_TOKEN[name] * T / (per_op_ms[name] * 1e-3) / 1e9,
                              "frac_of_peak": BYTES_PER_TOKEN[name] * T / (per_op_ms[name] * 1e-3) / 1e9 / peak} for name in op_names}
+        step_bytes = sum(BYTES_PER_TOKEN.values()) * T
         cpu = cpu_baseline() if world == 1 else None
-        others = other_configs(peak) if world == 1 else None
+        others = other_configs(peak) if (world == 1 and not args.no_other_configs) else {}
+        if c5 is not None:
+            others = dict(others or {}, c5_stack_4layer=c5)
         line = {
             "metric": METRIC, "value": world * T * args.steps / (ms_total * 1e-3), "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": ms_total / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-            "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": WORKLOAD, "tokens_per_gpu": T, "l2": "inputs larger than L2 (1.7 GiB touched per step vs 126 MB)",
-                       "parallelism": f"token-sharded x{world}" + (", NCCL all-reduce of the RMSNorm weight gradient" if world > 1 else "")},
+            "dtype": "bf16", "data": "synthetic", "config": chain_config(world),
+            "timed_regions": {"repeats": len(region_ms), "steps_each": args.steps, "ms": region_ms, "reported": "median",
+                              "min_ms_per_step": min(region_ms) / args.steps, "max_ms_per_step": max(region_ms) / args.steps},
+            "step_hbm": {"algorithmic_bytes": step_bytes, "GB/s": step_bytes / (ms_total / args.steps * 1e-3) / 1e9,
+                         "frac_of_peak": step_bytes / (ms_total / args.steps * 1e-3) / 1e9 / peak},
             "roofline": {"bound": "hbm", "kernel": DOMINANT, "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "traffic": DOMINANT_DRAM_TRAFFIC_BYTES, "algorithmic_bytes": dom_bytes, "peak_source": peak_src,
                          "frac_of_nominal_8000": achieved / 8000.0,
-                         "note": "traffic is from an ncu capture of the kernel run alone; in the chain it follows swiglu on the same x_w1, x_w3 and "
-                                 "walks them from the end, so the ~126 MB that swiglu left in L2 are not re-read from DRAM and frac can pass 1"},
+                         "alone": {"achieved": alone, "frac": alone / peak, "ms": dom_alone_ms,
+                                   "what": "the same kernel launched 20 times back to back by itself in this run: every byte comes from DRAM"},
+                         "traffic_source": "profiles/swiglu_bwd_x_bf16_2048x14336.md: ncu capture of the kernel alone at 2048 rows, reads scaled by the rows "
+                                           "(x4), writes less the size-independent ~42 MB still dirty in L2 at kernel end",
+                         "note": "achieved / frac are measured inside the chain, where the kernel follows swiglu on the same x_w1, x_w3 and walks "
+                                 "them from the end: the ~126 MB that swiglu left in L2 are not re-read from DRAM, so frac can pass 1; `alone` is the "
+                                 "distance to the DRAM roofline"},
             "ops_event_bracketed": ops_report,
             "e2e": {"value": world * T * e2e_steps / (ms_e2e * 1e-3), "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                    "steps": e2e_steps, "ms_per_step": ms_e2e / e2e_steps},
-            "gpu_launches": KERNEL_LAUNCHES_PER_STEP * args.steps,
+                    "steps": e2e_steps, "ms_per_step": ms_e2e / e2e_steps, "regions_ms": e2e_ms, "reported": "median of 3 regions",
+                    "copy_ms": copy_ms, "compute_ms": ms_total / args.steps,
+                    "h2d_GBps_per_rank": h2d / (copy_ms * 1e-3) / 1e9, "h2d_GBps_all_ranks": world * h2d / (copy_ms * 1e-3) / 1e9,
+                    "note": "uploads of step s + 1 run on stream 1 beside the kernels of step s; copy_ms is the upload of one step alone with all "
+                            "ranks copying at once (slowest rank): the host-side ceiling of this region"},
+            "gpu_launches": KERNEL_LAUNCHES_PER_STEP * args.steps * len(region_ms),
             "host_enqueue_ms_per_step": host_enqueue_ms,
             "clocks": clocks,
         }
+        if exchange_check is not None:
+            line["exchange_check"] = exchange_check
         if cpu is not None:
             line["cpu_baseline"] = cpu
-        if others is not None:
+        if others:
             line["other_configs"] = others
         print(json.dumps(line), flush=True)
 
     for a in list(host.values()) + list(out_host.values()):
         h.disable_access_to_host_mem(a.ctypes.data)
+    if exchange is not None:
+        exchange.close()
     h.close()
     if world > 1:
         dist.destroy_process_group()
 
 
-def run_stack_arm(args):
-    """--workload stack: the token-sharded 4-layer training step of dataflow_lib_b200/op_stack.py (16384 tokens per GPU,
-    d 4096, ffn 14336, 32/8 heads x 128, vocabulary 128256; bf16 activations, FP8 FFN weights, seed-0 random weights identical
-    on every rank, data seeded per rank; loss sum and RMSNorm weight gradients all-reduced over NCCL). Not the default
-    workload: `value` is tokens/s of the whole step, the library vocabulary GEMMs included and reported separately."""
+def stack_step_report(rank, world, local, steps, warmup, tokens, with_clocks=False):
+    """The token-sharded 4-layer training step of dataflow_lib_b200/op_stack.py (configuration C5: 16384 tokens per GPU, d 4096, ffn
+    14336, 32/8 heads x 128, vocabulary 128256; bf16 activations, FP8 FFN weights, seed-0 random weights identical on every rank, data
+    seeded per rank; loss sum and RMSNorm weight gradients in one packed buffer all-reduced by the library's C exchange). Returns the
+    report on rank 0 (None elsewhere); torch.distributed must already be initialised when world > 1."""
     import torch
     import torch.distributed as dist
 
     from dataflow_lib_b200 import ops
     from dataflow_lib_b200.op_stack import OpStackStep
 
-    rank, world, local = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1")), int(os.environ.get("LOCAL_RANK", "0"))
-    assert world == args.gpus, f"--gpus {args.gpus} but WORLD_SIZE={world} (launch N > 1 with torchrun)"
-    torch.cuda.set_device(local)
-    if world > 1:
-        quiet_nccl_banner()
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
-    T, V, LAYERS = args.tokens or 16384, 128256, 4
-    st = OpStackStep(T, D_MODEL, FFN, N_HEADS, N_KV, HEAD_DIM, V, LAYERS, EPS, float(THETA))
+    T, V, LAYERS = tokens, 128256, 4
+    st = OpStackStep(T, D_MODEL, FFN, N_HEADS, N_KV, HEAD_DIM, V, LAYERS, EPS, float(THETA), device=f"cuda:{local}")
     st.random_weights(seed=0)
     g = torch.Generator(device="cuda").manual_seed(1 + rank)
     host_x = torch.randn(T, D_MODEL, generator=g, device="cuda").bfloat16().cpu().pin_memory()
@@ -520,49 +658,56 @@ def run_stack_arm(args):
             dist.barrier()
         torch.cuda.synchronize()
 
-    warm = max(args.warmup, 3)
+    warm = max(warmup, 3)
     for _ in range(warm):
         st.step()
     barrier()
-    sampler = ClockSampler("GPU-" + str(torch.cuda.get_device_properties(local).uuid)) if rank == 0 else None
+    sampler = ClockSampler("GPU-" + str(torch.cuda.get_device_properties(local).uuid)) if (rank == 0 and with_clocks) else None
     ev = lambda: torch.cuda.Event(enable_timing=True)
     t0, t1 = ev(), ev()
     barrier()
-    t0.record()
-    for _ in range(args.steps):
+    t0.record(st.stream)
+    for _ in range(steps):
         st.step(overlap=True)                     # the all-reduce runs beside the next step; the last one is waited for below
     st.wait_exchange()
-    t1.record()
+    t1.record(st.stream)
     barrier()
     ms_total = t0.elapsed_time(t1)
+    exchange_check = None
     if world > 1:
-        # untimed check of the overlapped exchange: the same step reduced on the compute stream gives the same buffer
-        from dataflow_lib_b200.sharding import pack_reduction
+        # untimed check of the C exchange: the step's packed partial sums all-reduced once more by torch.distributed
         st.step(overlap=True); st.wait_exchange()
-        overlapped = st.reduced.clone()
-        st.step()
-        in_stream = pack_reduction(st.loss_sum, st.dW)            # that path stores the reduced dW back in bf16
-        exchange_check = "identical" if (torch.equal(overlapped[:2], in_stream[:2]) and
-                                         torch.equal(overlapped[2:].bfloat16().float(), in_stream[2:])) else "differs"
-        if exchange_check != "identical":
-            print("warning: the overlapped exchange and the in-stream one gave different sums", file=sys.stderr)
-    else:
-        exchange_check = None
+        barrier()
+        got = st.reduced.clone()
+        partial = torch.empty_like(got)
+        saved_exchange, st._exchange = st._exchange, _NoExchange()
+        st.step()                                  # the same step without the collective: this rank's own sums
+        barrier()
+        partial.copy_(st.reduced)
+        st._exchange = saved_exchange
+        want = partial.clone()
+        dist.all_reduce(want)
+        err = ((got - want).abs().max() / want.abs().max().clamp_min(1e-30)).item()
+        exchange_check = {"max_rel_diff_vs_torch_all_reduce": err, "ok": bool(err <= 1e-6)}
+        if not exchange_check["ok"]:
+            print(f"warning: stack step: the C exchange and torch.distributed disagree (max relative difference {err:g})", file=sys.stderr)
 
     # end to end: the step's tokens and labels come from pinned host memory, the loss goes back, every step
-    e_steps = max(3, min(args.steps, 10))
+    e_steps = max(3, min(steps, 10))
     def e2e_step():
-        st.x[0].copy_(host_x, non_blocking=True); st.labels.copy_(host_labels, non_blocking=True)
+        with torch.cuda.stream(st.stream):
+            st.x[0].copy_(host_x, non_blocking=True); st.labels.copy_(host_labels, non_blocking=True)
         st.step()
-        host_loss.copy_(st.loss_sum, non_blocking=True)
-        torch.cuda.current_stream().synchronize()
+        with torch.cuda.stream(st.stream):
+            host_loss.copy_(st.loss_sum, non_blocking=True)
+        st.stream.synchronize()
     e2e_step()
     e0, e1 = ev(), ev()
     barrier()
-    e0.record()
+    e0.record(st.stream)
     for _ in range(e_steps):
         e2e_step()
-    e1.record()
+    e1.record(st.stream)
     barrier()
     ms_e2e = e0.elapsed_time(e1)
 
@@ -593,32 +738,60 @@ def run_stack_arm(args):
     if world > 1:
         dist.all_reduce(times, op=dist.ReduceOp.MAX)
     ms_total, ms_e2e = times.tolist()
+    loss = float(st.loss_sum[0]) / max(float(st.loss_sum[1]), 1.0)
+    launches = st.library_launches_per_step()
+    st.close()
+    if rank != 0:
+        return None
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            bf16_sustained, src = float(json.load(f)["bf16_tflops_sustained"]), "2 x bf16_tflops_sustained of MEASURED_PEAKS.json (it holds no fp8 figure)"
+    except (OSError, KeyError, ValueError):
+        bf16_sustained, src = 1400.0, "2 x the fallback's sustained bf16 figure"
+    flops = 2.0 * T * D_MODEL * FFN
+    achieved = flops / (ms_gemm * 1e-3) / 1e12
+    return {
+        "metric": "tokens_per_s_op_stack_step", "value": world * T * steps / (ms_total * 1e-3), "unit": UNIT, "n_gpus": world, "steps": steps,
+        "warmup": warm, "ms_per_step": ms_total / steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16 activations, e4m3 FFN operands with fp32 accumulation", "data": "synthetic",
+        "config": {"workload": f"4-layer op stack step fwd+bwd (RMSNorm -> RoPE -> FP8 SwiGLU FFN + residual) x4 + head (RMSNorm -> vocabulary GEMM -> "
+                               f"fused softmax+CE), {T} tokens/GPU, d 4096, ffn 14336, vocab 128256",
+                   "tokens_per_gpu": T, "l2": "inputs larger than L2 (tens of GB touched per step)",
+                   "parallelism": f"token-sharded x{world}" + (", packed loss / RMSNorm weight gradient buffer all-reduced over NCCL from C on a side stream, overlapped with the next step" if world > 1 else "")},
+        "roofline": {"bound": "tensor", "kernel": "gemm_e4m3_kernel<PLAIN, CTA pair> (the gate projection of the FFN forward, timed alone after the step)", "achieved": achieved,
+                     "peak": 2 * bf16_sustained, "unit": "TFLOP/s", "frac": achieved / (2 * bf16_sustained), "traffic": None, "peak_source": src},
+        "step_breakdown_ms": breakdown, "exchange_check": exchange_check,
+        "e2e": {"value": world * T * e_steps / (ms_e2e * 1e-3), "unit": UNIT, "h2d_bytes_per_step": host_x.numel() * 2 + host_labels.numel() * 4,
+                "d2h_bytes_per_step": 8, "steps": e_steps, "ms_per_step": ms_e2e / e_steps},
+        "gpu_launches": launches * steps,
+        "loss": loss,
+        "clocks": clocks,
+    }
+
+
+class _NoExchange:
+    """Stands in for the exchange during the untimed multi-rank check: the step without its collective."""
+    def all_reduce(self, stream_id, packed, count=None):
+        return 0
+
+    def close(self):
+        pass
+
+
+def run_stack_arm(args):
+    """--workload stack: configuration C5 by itself (the default workload reports it under other_configs.c5_stack_4layer). `value` is
+    tokens/s of the whole step, the library vocabulary GEMMs included and reported separately in the breakdown."""
+    import torch
+    import torch.distributed as dist
+
+    rank, world, local = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1")), int(os.environ.get("LOCAL_RANK", "0"))
+    assert world == args.gpus, f"--gpus {args.gpus} but WORLD_SIZE={world} (launch N > 1 with torchrun)"
+    torch.cuda.set_device(local)
+    if world > 1:
+        quiet_nccl_banner()
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    line = stack_step_report(rank, world, local, steps=args.steps, warmup=args.warmup, tokens=args.tokens or 16384, with_clocks=True)
     if rank == 0:
-        try:
-            with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
-                bf16_sustained, src = float(json.load(f)["bf16_tflops_sustained"]), "2 x bf16_tflops_sustained of MEASURED_PEAKS.json (it holds no fp8 figure)"
-        except (OSError, KeyError, ValueError):
-            bf16_sustained, src = 1400.0, "2 x the fallback's sustained bf16 figure"
-        flops = 2.0 * T * D_MODEL * FFN
-        achieved = flops / (ms_gemm * 1e-3) / 1e12
-        step_ms = ms_total / args.steps
-        line = {
-            "metric": "tokens_per_s_op_stack_step", "value": world * T * args.steps / (ms_total * 1e-3), "unit": UNIT, "n_gpus": world, "steps": args.steps,
-            "warmup": warm, "ms_per_step": step_ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-            "dtype": "bf16 activations, e4m3 FFN operands with fp32 accumulation", "data": "synthetic",
-            "config": {"workload": f"4-layer op stack step fwd+bwd (RMSNorm -> RoPE -> FP8 SwiGLU FFN + residual) x4 + head (RMSNorm -> vocabulary GEMM -> "
-                                   f"fused softmax+CE), {T} tokens/GPU, d 4096, ffn 14336, vocab 128256",
-                       "tokens_per_gpu": T, "l2": "inputs larger than L2 (tens of GB touched per step)",
-                       "parallelism": f"token-sharded x{world}" + (", NCCL all-reduce of loss and RMSNorm weight gradients on a side stream, overlapped with the next step" if world > 1 else "")},
-            "roofline": {"bound": "tensor", "kernel": "gemm_e4m3_kernel<PLAIN, CTA pair> (the gate projection of the FFN forward, timed alone after the step)", "achieved": achieved,
-                         "peak": 2 * bf16_sustained, "unit": "TFLOP/s", "frac": achieved / (2 * bf16_sustained), "traffic": None, "peak_source": src},
-            "step_breakdown_ms": breakdown, "exchange_check": exchange_check,
-            "e2e": {"value": world * T * e_steps / (ms_e2e * 1e-3), "unit": UNIT, "h2d_bytes_per_step": host_x.numel() * 2 + host_labels.numel() * 4,
-                    "d2h_bytes_per_step": 8, "steps": e_steps, "ms_per_step": ms_e2e / e_steps},
-            "gpu_launches": st.library_launches_per_step() * args.steps,
-            "loss": float(st.loss_sum[0]) / max(float(st.loss_sum[1]), 1.0),
-            "clocks": clocks,
-        }
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
@@ -633,6 +806,9 @@ def main():
     ap.add_argument("--workload", default="chain", choices=["chain", "stack"],
                     help="chain (default): the elementwise op chain the headline metric is quoted on; stack: the 4-layer token-sharded training step")
     ap.add_argument("--tokens", type=int, default=0, help="stack workload only: tokens per GPU (default 16384)")
+    ap.add_argument("--repeats", type=int, default=7, help="chain workload: timed regions of --steps steps each; the median region is reported")
+    ap.add_argument("--no-stack", action="store_true", help="chain workload: skip the 4-layer stack step (other_configs.c5_stack_4layer)")
+    ap.add_argument("--no-other-configs", action="store_true", help="chain workload, N = 1: skip configurations C1, C3 and C4")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference_arm(args)

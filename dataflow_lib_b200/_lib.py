@@ -28,6 +28,7 @@ KERNEL_ABI = {
     "dfb200_rms_norm_bwd_x": (_i, [_i, _i, _i, _i, _f, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
     "dfb200_rms_norm_bwd_w_workspace_bytes": (_u64, [_i, _i]),
     "dfb200_rms_norm_bwd_w": (_i, [_i, _i, _i, _i, _f, _vp, _vp, _vp, _vp, _vp, _u64, _vp]),
+    "dfb200_rms_norm_bwd_w_sums": (_i, [_i, _i, _i, _i, _f, _vp, _vp, _vp, _vp, _vp, _u64, _vp]),
     "dfb200_rms_norm_bwd_w_static": (_i, [_i, _i, _i, _i, _f, _vp, _vp, _vp, _vp, _vp]),
     "dfb200_rope": (_i, [_i, _u64, _i, _i, _i, _i, _vp, _vp, _vp, _vp]),
     "dfb200_rope_bwd_x": (_i, [_i, _u64, _i, _i, _i, _i, _vp, _vp, _vp, _vp]),
@@ -92,6 +93,7 @@ HOST_ABI = {
     "set_native_rms_norm_skeleton": (None, [_SK, _i]),
     "set_native_rms_norm_bwd_x_skeleton": (None, [_SK, _i, _i]),
     "set_native_rms_norm_bwd_w_skeleton": (None, [_SK, _i, _i]),
+    "set_native_rms_norm_bwd_w_sums_skeleton": (None, [_SK, _i, _i]),
     "set_native_rope_skeleton": (None, [_SK, _i]),
     "set_native_rope_bwd_x_skeleton": (None, [_SK, _i]),
     "set_native_copy_to_seq_context_skeleton": (None, [_SK, _i]),
@@ -113,6 +115,7 @@ HOST_ABI = {
     "submit_rms_norm": (_i, [_H, _i, _i, _i, _i, _f, _vp, _vp, _vp, _vp, _vp]),
     "submit_rms_norm_bwd_x": (_i, [_H, _i, _i, _i, _i, _i, _f, _vp, _vp, _vp, _vp, _vp, _vp]),
     "submit_rms_norm_bwd_w": (_i, [_H, _i, _i, _i, _i, _i, _f, _vp, _vp, _vp, _vp]),
+    "submit_rms_norm_bwd_w_sums": (_i, [_H, _i, _i, _i, _i, _i, _f, _vp, _vp, _vp, _vp]),
     "submit_rope": (_i, [_H, _i, _i, _u64, _i, _i, _i, _i, _vp, _vp, _vp]),
     "submit_rope_bwd_x": (_i, [_H, _i, _i, _u64, _i, _i, _i, _i, _vp, _vp, _vp]),
     "submit_swiglu": (_i, [_H, _i, _i, _i, _i, _vp, _vp, _vp]),
@@ -138,6 +141,11 @@ HOST_ABI = {
                                            C.POINTER(abi.TransformerBlockTransition)]),
     "submit_transformer_block_bwd_w": (_i, [_H, _i, C.POINTER(abi.TransformerBlockTransition), C.POINTER(abi.TransformerBlockActivations),
                                            C.POINTER(abi.TransformerBlockActivations), C.POINTER(abi.TransformerBlock)]),
+    # include/dataflow_b200_exchange.h
+    "dataflow_exchange_unique_id": (_i, [_vp]),
+    "dataflow_exchange_init": (_i, [C.POINTER(abi.DataflowExchange), _H, _i, _i, _vp]),
+    "dataflow_exchange_all_reduce_f32": (_i, [C.POINTER(abi.DataflowExchange), _i, _vp, _u64]),
+    "dataflow_exchange_destroy": (None, [C.POINTER(abi.DataflowExchange)]),
     # external-op plug-in symbols (ops_external.c)
     "dataflow_b200_workspace_init": (_i, [_H, _vp]),
     "dataflow_b200_reserve_workspace": (_i, [_H, _SK, _i, _u64]),
@@ -145,6 +153,7 @@ HOST_ABI = {
     "dataflow_b200_rms_norm": (_i, [_H, _i, _vp, _vp]),
     "dataflow_b200_rms_norm_bwd_x": (_i, [_H, _i, _vp, _vp]),
     "dataflow_b200_rms_norm_bwd_w": (_i, [_H, _i, _vp, _vp]),
+    "dataflow_b200_rms_norm_bwd_w_sums": (_i, [_H, _i, _vp, _vp]),
     "dataflow_b200_rope": (_i, [_H, _i, _vp, _vp]),
     "dataflow_b200_rope_bwd_x": (_i, [_H, _i, _vp, _vp]),
     "dataflow_b200_swiglu": (_i, [_H, _i, _vp, _vp]),

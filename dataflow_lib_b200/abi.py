@@ -192,3 +192,12 @@ class TransformerBlockActivations(C.Structure):
     _fields_ = [("block", C.POINTER(TransformerBlock)), ("batch_config", C.POINTER(SeqBatchConfig)),
                 ("saved_activations", C.POINTER(SeqBatchSavedActivations)), ("context", C.POINTER(SeqBatchContext)),
                 ("activation_workspace", C.POINTER(SeqBatchActivationWorkspace))]
+
+
+# ---- include/dataflow_b200_exchange.h -----------------------------------------------------------------------------------------
+EXCHANGE_ID_BYTES = 128
+
+
+class DataflowExchange(C.Structure):
+    _fields_ = [("handle", C.POINTER(DataflowHandleStruct)), ("world_size", C.c_int), ("rank", C.c_int), ("comm", C.c_void_p),
+                ("nccl_lib", C.c_void_p), ("fn", C.c_void_p * 6)]

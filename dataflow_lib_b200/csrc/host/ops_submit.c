@@ -41,6 +41,14 @@ int submit_rms_norm_bwd_w(Dataflow_Handle * handle, int stream_id, DataflowDatat
 	return submit(handle, &op, stream_id, "rms norm bwd w");
 }
 
+int submit_rms_norm_bwd_w_sums(Dataflow_Handle * handle, int stream_id, DataflowDatatype fwd_dt, DataflowDatatype bwd_dt,
+                               int n_rows, int n_cols, float eps, float * fwd_rms_vals, void * X_inp, void * upstream_dX, float * column_sums) {
+	Op op;
+	set_native_rms_norm_bwd_w_sums_skeleton(&op.op_skeleton, fwd_dt, bwd_dt);
+	ARGS(op, &n_rows, &n_cols, &eps, &fwd_rms_vals, &X_inp, &upstream_dX, &column_sums);
+	return submit(handle, &op, stream_id, "rms norm bwd w (fp32 column sums)");
+}
+
 int submit_rope(Dataflow_Handle * handle, int stream_id, DataflowDatatype fwd_dt, uint64_t N, int model_dim, int head_dim,
                 int num_kv_heads, int theta, int * seq_positions, void * X_q, void * X_k) {
 	Op op;

@@ -310,7 +310,9 @@ rms_norm_bwd_w_partial_kernel(int n_rows, int n_cols, int group_threads, const f
 // slices are combined in slice order. Launched as a programmatic dependent of stage 1: its CTAs
 // are scheduled while stage 1 drains and block in cudaGridDependencySynchronize() until stage 1
 // has completed and its partial sums are visible, which hides the launch latency.
-template <typename B>
+// SUMS = true: dW is a float array that RECEIVES the column sums (fp32, overwritten, nothing read): the form a data-parallel
+// caller wants, whose next step is an all-reduce of fp32 partial gradients (a slot of a packed exchange buffer).
+template <typename B, bool SUMS>
 __global__ void __launch_bounds__(1024)
 rms_norm_bwd_w_final_kernel(int n_cols, int n_partials, const float * __restrict__ partials, void * dW) {
 	__shared__ float slice_sum[32][33];
@@ -329,7 +331,9 @@ rms_norm_bwd_w_final_kernel(int n_cols, int n_partials, const float * __restrict
 		#pragma unroll
 		for (int k = 1; k < 32; k++) total += slice_sum[k][lane];
 		// element-wise read-modify-write of dW in its own type
-		if constexpr (Word<B>::EPW == 1) {
+		if constexpr (SUMS) {
+			reinterpret_cast<float *>(dW)[col] = total;
+		} else if constexpr (Word<B>::EPW == 1) {
 			float * p = reinterpret_cast<float *>(dW) + col;
 			*p = *p + total;
 		} else {
@@ -451,10 +455,8 @@ extern "C" uint64_t dfb200_rms_norm_bwd_w_workspace_bytes(int n_rows, int n_cols
 	return (uint64_t) sms * (uint64_t) n_cols * sizeof(float);
 }
 
-extern "C" int dfb200_rms_norm_bwd_w(int fwd_dt, int bwd_dt, int n_rows, int n_cols, float eps, const float * fwd_rms_vals,
-                                     const void * X_inp, const void * upstream_dX, void * dW, void * workspace, uint64_t workspace_bytes,
-                                     void * stream) {
-	(void) eps;
+static int launch_rms_norm_bwd_w(bool sums, int fwd_dt, int bwd_dt, int n_rows, int n_cols, const float * fwd_rms_vals, const void * X_inp,
+                                 const void * upstream_dX, void * dW, void * workspace, uint64_t workspace_bytes, void * stream) {
 	if (!valid_fwd_bwd_pair(fwd_dt, bwd_dt)) return set_error(DFB200_ERR_DTYPE, "rms_norm_bwd_w: unsupported datatype pair (%d, %d)", fwd_dt, bwd_dt);
 	RowGeometry geo;
 	int rc = check_rows("rms_norm_bwd_w", n_rows, n_cols, BWD_W_ROW_THREADS, &geo);
@@ -491,10 +493,31 @@ extern "C" int dfb200_rms_norm_bwd_w(int fwd_dt, int bwd_dt, int n_rows, int n_c
 		const float * cpartials = partials;
 		cudaError_t e = cudaErrorInvalidValue;
 		DFB200_DISPATCH_PAIR(fwd_dt, bwd_dt, F, B,
-			e = (cudaLaunchKernelEx(&cfg, rms_norm_bwd_w_final_kernel<B>, n_cols, grid, cpartials, dW)));
+			e = (sums ? cudaLaunchKernelEx(&cfg, rms_norm_bwd_w_final_kernel<B, true>, n_cols, grid, cpartials, dW)
+			          : cudaLaunchKernelEx(&cfg, rms_norm_bwd_w_final_kernel<B, false>, n_cols, grid, cpartials, dW)));
 		if (e != cudaSuccess) { cudaGetLastError(); return set_error(DFB200_ERR_CUDA, "rms_norm_bwd_w (final sum): %s", cudaGetErrorString(e)); }
 	}
 	return DFB200_OK;
+}
+
+extern "C" int dfb200_rms_norm_bwd_w(int fwd_dt, int bwd_dt, int n_rows, int n_cols, float eps, const float * fwd_rms_vals,
+                                     const void * X_inp, const void * upstream_dX, void * dW, void * workspace, uint64_t workspace_bytes,
+                                     void * stream) {
+	(void) eps;
+	return launch_rms_norm_bwd_w(false, fwd_dt, bwd_dt, n_rows, n_cols, fwd_rms_vals, X_inp, upstream_dX, dW, workspace, workspace_bytes, stream);
+}
+
+extern "C" int dfb200_rms_norm_bwd_w_sums(int fwd_dt, int bwd_dt, int n_rows, int n_cols, float eps, const float * fwd_rms_vals,
+                                          const void * X_inp, const void * upstream_dX, float * column_sums, void * workspace,
+                                          uint64_t workspace_bytes, void * stream) {
+	(void) eps;
+	if (reinterpret_cast<uintptr_t>(column_sums) & 3u) return set_error(DFB200_ERR_ARG, "rms_norm_bwd_w_sums: column_sums must be 4-byte aligned");
+	if (n_rows == 0 && n_cols > 0 && column_sums) {          // no rows: the sums are zero (the accumulating form leaves dW alone instead)
+		cudaError_t e = cudaMemsetAsync(column_sums, 0, (size_t) n_cols * sizeof(float), (cudaStream_t) stream);
+		if (e != cudaSuccess) { cudaGetLastError(); return set_error(DFB200_ERR_CUDA, "rms_norm_bwd_w_sums: %s", cudaGetErrorString(e)); }
+		return DFB200_OK;
+	}
+	return launch_rms_norm_bwd_w(true, fwd_dt, bwd_dt, n_rows, n_cols, fwd_rms_vals, X_inp, upstream_dX, column_sums, workspace, workspace_bytes, stream);
 }
 
 // ----------------------------------------------------------------------------------------

@@ -91,6 +91,10 @@ class DataflowHandle:
     def submit_rms_norm_bwd_w(self, stream_id, fwd_dt, bwd_dt, n_rows, n_cols, eps, fwd_rms_vals, X_inp, upstream_dX, dW):
         return _L.submit_rms_norm_bwd_w(C.byref(self.h), stream_id, int(fwd_dt), int(bwd_dt), n_rows, n_cols, eps, _p(fwd_rms_vals), _p(X_inp), _p(upstream_dX), _p(dW))
 
+    def submit_rms_norm_bwd_w_sums(self, stream_id, fwd_dt, bwd_dt, n_rows, n_cols, eps, fwd_rms_vals, X_inp, upstream_dX, column_sums):
+        return _L.submit_rms_norm_bwd_w_sums(C.byref(self.h), stream_id, int(fwd_dt), int(bwd_dt), n_rows, n_cols, eps, _p(fwd_rms_vals), _p(X_inp),
+                                             _p(upstream_dX), _p(column_sums))
+
     def submit_rope(self, stream_id, fwd_dt, N, model_dim, head_dim, num_kv_heads, theta, seq_positions, X_q, X_k):
         return _L.submit_rope(C.byref(self.h), stream_id, int(fwd_dt), N, model_dim, head_dim, num_kv_heads, theta, _p(seq_positions), _p(X_q), _p(X_k))
 

@@ -11,19 +11,22 @@ the ops this library provides:
     backward:  d h = dlogits @ W_vocab (library GEMM);  rms_norm_bwd_w / rms_norm_bwd_x (dx += ...) for the head, then per
                layer in reverse: FFN input gradient, rope_bwd_x, rms_norm_bwd_w, rms_norm_bwd_x accumulating into dx,
                which carries the residual branch.
-    exchange:  [loss sum, valid rows, dW_0 .. dW_L] in one packed fp32 all-reduce (sharding.allreduce_step).
+    exchange:  [loss sum, valid rows | dW_0 .. dW_L], one packed fp32 buffer that the loss kernel and the weight-gradient kernels
+               write directly (sharding.PackedReduction), summed over the ranks by the library's C exchange
+               (include/dataflow_b200_exchange.h: NCCL called from C) on a stream of the step's handle.
 
 Attention, the Q/K/V/O projections and the FFN weight gradients are not part of the step: the library has no kernels
 for them. The vocabulary projection is the one library GEMM (torch.matmul -> cuBLASLt, as the reference uses cuBLASLt
 for it); callers that account time per kernel exclude it.
 
-Every op goes through the C-ABI launchers (ops.py); there is no CPU path.
+Every op goes through the C-ABI launchers (ops.py) on stream 0 of the step's own Dataflow_Handle; there is no CPU path.
 """
 import torch
 import torch.distributed as dist
 
 from . import ops
-from .sharding import allreduce_step, pack_reduction
+from .handle import DataflowHandle
+from .sharding import Exchange, PackedReduction
 
 
 class OpStackStep:
@@ -42,9 +45,11 @@ class OpStackStep:
         self.ws, self.rms = [e(T, dtype=torch.float32) for _ in range(L + 1)], [e(T, dtype=torch.float32) for _ in range(L + 1)]
         self.logits, self.dlogits = e(T, V), e(T, V)
         self.dh, self.dA, self.dx = e(T, d), e(T, d), e(T, d)
-        self.dW_all = torch.zeros(L + 1, d, dtype=bf, device=dev)
-        self.dW = list(self.dW_all.unbind(0))                    # dW[l]: gradient of layer l's RMSNorm weight; dW[L]: the head's
-        self.loss_sum = torch.zeros(2, dtype=torch.float32, device=dev)
+        # The step's reductions over tokens live in a packed fp32 buffer that the kernels write directly: [loss sum, valid rows | dW_0 ..
+        # dW_L] (dW[l]: gradient of layer l's RMSNorm weight; dW[L]: the head's). Two buffers alternate between steps, so that an
+        # exchange running beside the next step is never overwritten by it.
+        self.packed = [PackedReduction([d] * (L + 1), device=dev) for _ in range(2)]
+        self._parity = 0
         self.pos = torch.arange(T, dtype=torch.int32, device=dev)
         self.labels = torch.zeros(T, dtype=torch.int32, device=dev)
         # weights (set_weights fills them)
@@ -56,7 +61,13 @@ class OpStackStep:
         self.WguT, self.WdT = [u8(d, 2 * f) for _ in range(L)], [u8(f, d) for _ in range(L)]
         self.W_vocab = e(V, d)
         self.marks = None                                        # a list while a step is being profiled: (segment name, CUDA event) pairs
-        self._xstream, self._xdone, self.reduced = None, None, None   # side stream, completion event and result of exchange_overlapped
+        # the step's own handle: ops run on its stream 0, an overlapped exchange on its stream 1
+        self.handle = DataflowHandle(device_id=dev.index if dev.index is not None else torch.cuda.current_device(), num_streams=2, register_ops=False)
+        self.stream = torch.cuda.ExternalStream(self.handle.stream_ptr(0), device=dev)
+        self._xstream = torch.cuda.ExternalStream(self.handle.stream_ptr(1), device=dev)
+        self._exchange = None                                    # made at the first exchange (needs the process group, if any)
+        self._xdone = [None, None]                               # per packed buffer: event after its overlapped exchange
+        self.reduced = None                                      # the packed buffer of the last exchanged step (global sums once its exchange is done)
         self.ffn_ws = torch.empty(int(ops._lib_.dfb200_swiglu_ffn_fp8_workspace_bytes(T, d, f)), dtype=torch.uint8, device=dev)   # forward and backward
 
     # ------------------------------------------------------------------ weights
@@ -88,11 +99,20 @@ class OpStackStep:
             ffn.append(tuple(row))
         self.set_weights(w_norm, ffn, rn(self.V, self.d, std=0.02).bfloat16())
 
+    # the current step's slots of the packed buffer
+    @property
+    def loss_sum(self):
+        return self.packed[self._parity].loss
+
+    @property
+    def dW(self):
+        return self.packed[self._parity].dW
+
     def _mark(self, name):
         """Segment boundary: when `marks` is a list, records an event that closes segment `name` on the current stream."""
         if self.marks is not None:
             ev = torch.cuda.Event(enable_timing=True)
-            ev.record()
+            ev.record(self.stream)
             self.marks.append((name, ev))
 
     def segment_ms(self):
@@ -120,6 +140,9 @@ class OpStackStep:
         self._mark("rms_norm + rope")
         torch.matmul(self.h, self.W_vocab.t(), out=self.logits)
         self._mark("vocabulary GEMMs (library)")
+        if self._xdone[self._parity] is not None:                 # this buffer's previous exchange (two steps ago) has long finished
+            self.stream.wait_event(self._xdone[self._parity])
+            self._xdone[self._parity] = None
         ops.softmax_cross_entropy(T, self.V, self.logits, self.labels, self.dlogits, None, self.loss_sum)
         self._mark("softmax_cross_entropy")
 
@@ -128,8 +151,7 @@ class OpStackStep:
         torch.matmul(self.dlogits, self.W_vocab, out=self.dh)
         self._mark("vocabulary GEMMs (library)")
         self.dx.zero_()
-        self.dW_all.zero_()
-        ops.rms_norm_bwd_w(T, d, self.eps, self.rms[L], self.x[L], self.dh, self.dW[L])
+        ops.rms_norm_bwd_w_sums(T, d, self.eps, self.rms[L], self.x[L], self.dh, self.dW[L])
         ops.rms_norm_bwd_x(T, d, self.eps, self.ws[L], self.rms[L], self.w_norm[L], self.x[L], self.dh, self.dx)
         self.dk.zero_()                                           # nothing consumes K in this stack: its upstream gradient is zero
         self._mark("rms_norm_bwd + rope_bwd")
@@ -138,54 +160,62 @@ class OpStackStep:
                                    workspace=self.ffn_ws)
             self._mark("swiglu_ffn_fp8_bwd")
             ops.rope_bwd_x(T * d, d, self.hd, self.n_kv, self.theta, self.pos, self.dA, self.dk)
-            ops.rms_norm_bwd_w(T, d, self.eps, self.rms[l], self.x[l], self.dA, self.dW[l])
+            ops.rms_norm_bwd_w_sums(T, d, self.eps, self.rms[l], self.x[l], self.dA, self.dW[l])
             ops.rms_norm_bwd_x(T, d, self.eps, self.ws[l], self.rms[l], self.w_norm[l], self.x[l], self.dA, self.dx)
             self._mark("rms_norm_bwd + rope_bwd")
 
+    def _the_exchange(self, group):
+        if self._exchange is None:
+            self._exchange = Exchange(self.handle, group=group)
+        return self._exchange
+
     def exchange(self, group=None):
-        allreduce_step(self.loss_sum, self.dW, group=group)
+        """The step's collective on the compute stream: afterwards `loss_sum` and `dW` hold the sums over all ranks."""
+        packed = self.packed[self._parity]
+        if self._the_exchange(group).all_reduce(0, packed) != 0:
+            raise RuntimeError("exchange failed (see stderr)")
+        self.reduced = packed.buffer
         self._mark("exchange")
 
     def exchange_overlapped(self, group=None):
-        """The same all-reduce, taken off the compute stream: the packed buffer is filled on the compute stream, reduced on a side
-        stream and left in `self.reduced` ([loss sum, valid rows | dW_0 .. dW_L], fp32), so the next step's kernels run while this
-        rank waits for the slowest one. `loss_sum` and `dW` keep the rank's own values. The next exchange (or wait_exchange) waits
-        for this one before the packed buffer is reused."""
-        if not dist.is_initialized() or dist.get_world_size(group) == 1:
-            self.reduced = pack_reduction(self.loss_sum, self.dW)
-            self._mark("exchange")
-            return
-        cur = torch.cuda.current_stream()
-        if self._xstream is None:
-            self._xstream = torch.cuda.Stream()
-        self.wait_exchange()
-        buf = pack_reduction(self.loss_sum, self.dW)
-        buf.record_stream(self._xstream)
-        packed = torch.cuda.Event()
-        packed.record(cur)
-        with torch.cuda.stream(self._xstream):
-            self._xstream.wait_event(packed)
-            dist.all_reduce(buf, op=dist.ReduceOp.SUM, group=group)
-            self._xdone = torch.cuda.Event()
-            self._xdone.record(self._xstream)
-        self.reduced = buf
+        """The same all-reduce on the handle's second stream, behind a dependency on the compute stream, so that the next step's
+        kernels run while this rank waits for the slowest one. `reduced` is this step's packed buffer; it holds the global sums once
+        wait_exchange (or the exchange after next, which reuses the buffer) has ordered the compute stream after it."""
+        packed = self.packed[self._parity]
+        h = self.handle
+        if h.submit_dependency(1, h.get_stream_state(0)) != 0 or self._the_exchange(group).all_reduce(1, packed) != 0:
+            raise RuntimeError("exchange failed (see stderr)")
+        done = torch.cuda.Event()
+        done.record(self._xstream)
+        self._xdone[self._parity] = done
+        self.reduced = packed.buffer
         self._mark("exchange")
 
     def wait_exchange(self):
-        """Orders the current stream after the last overlapped exchange (no host synchronisation)."""
-        if self._xdone is not None:
-            torch.cuda.current_stream().wait_event(self._xdone)
-            self._xdone = None
+        """Orders the compute stream after every overlapped exchange issued so far (no host synchronisation)."""
+        for i, ev in enumerate(self._xdone):
+            if ev is not None:
+                self.stream.wait_event(ev)
+                self._xdone[i] = None
 
     def step(self, group=None, overlap=False):
-        self.forward()
-        self.backward()
-        if overlap:
-            self.exchange_overlapped(group)
-        else:
-            self.exchange(group)
+        """One training step on the handle's compute stream (`self.stream`); the caller's current stream is not involved."""
+        self._parity ^= 1
+        self.stream.wait_stream(torch.cuda.current_stream())      # inputs the caller prepared on its own stream
+        with torch.cuda.stream(self.stream):
+            self.forward()
+            self.backward()
+            if overlap:
+                self.exchange_overlapped(group)
+            else:
+                self.exchange(group)
 
-    # launches of this library's kernels in one step (for accounting): per layer fwd rms 1 + rope 1 + ffn 4 (2 quantise, 2 GEMM),
+    def close(self):
+        if self._exchange is not None:
+            self._exchange.close()
+        self.handle.close()
+
+    # launches of this library's kernels in one step (for accounting): per layer fwd rms 1 + rope 1 + ffn 5 (2 row passes, 3 GEMMs),
     # bwd ffn 4 + rope 1 + bwd_w 2 + bwd_x 1; head rms 1 + softmax/CE 2 (rows + loss sum) + bwd_w 2 + bwd_x 1
     def library_launches_per_step(self):
-        return self.L * (1 + 1 + 4 + 4 + 1 + 2 + 1) + (1 + 2 + 2 + 1)
+        return self.L * (1 + 1 + 5 + 4 + 1 + 2 + 1) + (1 + 2 + 2 + 1)

@@ -85,6 +85,14 @@ def rms_norm_bwd_w(n_rows, n_cols, eps, fwd_rms_vals, X_inp, upstream_dX, dW, st
            "rms_norm_bwd_w")
 
 
+def rms_norm_bwd_w_sums(n_rows, n_cols, eps, fwd_rms_vals, X_inp, upstream_dX, column_sums, stream=None, workspace=None):
+    need = _lib_.dfb200_rms_norm_bwd_w_workspace_bytes(n_rows, n_cols)
+    ws = workspace if workspace is not None else _workspace(X_inp.device, need)
+    _check(_lib_.dfb200_rms_norm_bwd_w_sums(dt_of(X_inp), dt_of(upstream_dX), n_rows, n_cols, eps, _ptr(fwd_rms_vals), _ptr(X_inp),
+                                            _ptr(upstream_dX), _ptr(column_sums), _ptr(ws), ws.numel() * ws.element_size(), _stream(stream)),
+           "rms_norm_bwd_w_sums")
+
+
 def rope(N, model_dim, head_dim, num_kv_heads, theta, seq_positions, X_q, X_k, stream=None):
     _check(_lib_.dfb200_rope(dt_of(X_q), N, model_dim, head_dim, num_kv_heads, theta, _ptr(seq_positions), _ptr(X_q), _ptr(X_k),
                              _stream(stream)), "rope")

@@ -87,6 +87,8 @@ void set_native_embedding_skeleton(Op_Skeleton * skeleton, DataflowDatatype fwd_
 void set_native_rms_norm_skeleton(Op_Skeleton * skeleton, DataflowDatatype fwd_datatype);
 void set_native_rms_norm_bwd_x_skeleton(Op_Skeleton * skeleton, DataflowDatatype fwd_datatype, DataflowDatatype bwd_datatype);
 void set_native_rms_norm_bwd_w_skeleton(Op_Skeleton * skeleton, DataflowDatatype fwd_datatype, DataflowDatatype bwd_datatype);
+/* Not in the reference: "rms_norm_bwd_w_sums_<F>_<B>", the RMSNorm weight gradient written as fp32 column sums (dfb200_rms_norm_bwd_w_sums). */
+void set_native_rms_norm_bwd_w_sums_skeleton(Op_Skeleton * skeleton, DataflowDatatype fwd_datatype, DataflowDatatype bwd_datatype);
 void set_native_rope_skeleton(Op_Skeleton * skeleton, DataflowDatatype fwd_datatype);
 void set_native_rope_bwd_x_skeleton(Op_Skeleton * skeleton, DataflowDatatype bwd_datatype);
 void set_native_copy_to_seq_context_skeleton(Op_Skeleton * skeleton, DataflowDatatype fwd_datatype);
@@ -131,6 +133,10 @@ int submit_rms_norm_bwd_x(Dataflow_Handle * handle, int stream_id, DataflowDatat
 int submit_rms_norm_bwd_w(Dataflow_Handle * handle, int stream_id, DataflowDatatype fwd_dt, DataflowDatatype bwd_dt,
                           int n_rows, int n_cols, float eps,
                           float * fwd_rms_vals, void * X_inp, void * upstream_dX, void * dW);
+/* Not in the reference: column_sums[c] = sum over the rows of dY * X * rms, fp32, overwritten (a slot of a packed exchange buffer). */
+int submit_rms_norm_bwd_w_sums(Dataflow_Handle * handle, int stream_id, DataflowDatatype fwd_dt, DataflowDatatype bwd_dt,
+                               int n_rows, int n_cols, float eps,
+                               float * fwd_rms_vals, void * X_inp, void * upstream_dX, float * column_sums);
 int submit_rope(Dataflow_Handle * handle, int stream_id, DataflowDatatype fwd_dt,
                 uint64_t N, int model_dim, int head_dim, int num_kv_heads, int theta,
                 int * seq_positions, void * X_q, void * X_k);

@@ -76,6 +76,15 @@ int dfb200_rms_norm_bwd_w(int fwd_dt, int bwd_dt, int n_rows, int n_cols, float 
                           const void * upstream_dX, void * dW,
                           void * workspace, uint64_t workspace_bytes, void * stream);
 
+/* No counterpart in the reference (its kernel accumulates into dW with atomics in the gradient's own type): the same reduction with
+ * the column sums WRITTEN as fp32 -- column_sums[c] = sum_r f32(dY[r,c]) * f32(X[r,c]) * rms[r], overwritten, nothing read -- which is
+ * what a token-sharded caller all-reduces: column_sums can be a slot of the packed fp32 exchange buffer (dataflow_b200_exchange.h),
+ * so nothing has to be packed or unpacked around the collective. Same workspace as dfb200_rms_norm_bwd_w. */
+int dfb200_rms_norm_bwd_w_sums(int fwd_dt, int bwd_dt, int n_rows, int n_cols, float eps,
+                               const float * fwd_rms_vals, const void * X_inp,
+                               const void * upstream_dX, float * column_sums,
+                               void * workspace, uint64_t workspace_bytes, void * stream);
+
 /* No counterpart in the reference. rms_norm_bwd_w for callers that cannot allocate device memory or pass a
  * workspace: a program whose own arena already owns the whole device (one bulk alloc_mem at start-up), or a step
  * loop that must not hit cudaMalloc's device-wide synchronisation. Same results as dfb200_rms_norm_bwd_w; the

@@ -341,12 +341,12 @@ def test_register_native_ops_with_the_reference_callers_arguments(L, capfd, tmp_
     cubin.write_bytes(b"\x7fELF not a shared object")
     for arg in (b"lib/cuda_kernels.cubin", str(cubin).encode(), b"libm.so.6"):       # missing file, not loadable, loadable but without the ops
         seen.clear()
-        assert L.register_native_ops(C.byref(h), arg, b"lib/cuda_kernels_config.so") == 75
-        assert os.path.realpath(seen["path"]) == own and seen["n"] == 75 and "dataflow_b200_rms_norm" in seen["symbols"]
+        assert L.register_native_ops(C.byref(h), arg, b"lib/cuda_kernels_config.so") == 82
+        assert os.path.realpath(seen["path"]) == own and seen["n"] == 82 and "dataflow_b200_rms_norm" in seen["symbols"]
         assert "registering them from this library instead" in capfd.readouterr().err
     for arg in (None, own.encode()):                                                  # the documented forms: no notice
         seen.clear()
-        assert L.register_native_ops(C.byref(h), arg, None) == 75
+        assert L.register_native_ops(C.byref(h), arg, None) == 82
         assert os.path.realpath(seen["path"]) == own
         assert "Notice" not in capfd.readouterr().err
 

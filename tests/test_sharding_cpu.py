@@ -10,7 +10,7 @@ import torch.distributed as dist
 import torch.multiprocessing as mp
 
 import oracle as O
-from dataflow_lib_b200.sharding import allreduce_step, shard_rows
+from dataflow_lib_b200.sharding import PackedReduction, allreduce_packed, shard_rows
 
 ROWS, COLS, VOCAB = 37, 64, 256
 
@@ -37,10 +37,12 @@ def _worker(rank, world, port, out):
     sl = slice(start, start + count)
     dW = O.rms_norm_bwd_w(O.FP32, O.FP32, rms[sl].copy(), X[sl].copy(), dY[sl].copy(), np.zeros(COLS, np.float32), threads=1)
     _, _, ls = O.softmax_cross_entropy(O.FP32, O.FP32, logits[sl].copy(), labels[sl].copy(), threads=1)
-    loss_sum, dWt = torch.from_numpy(ls.copy()), torch.from_numpy(dW.copy())
-    allreduce_step(loss_sum, [dWt])
+    packed = PackedReduction([COLS])                           # the slots the kernels write on a GPU; the oracle's results stand in here
+    packed.loss.copy_(torch.from_numpy(ls.copy()))
+    packed.dW[0].copy_(torch.from_numpy(dW.copy()))
+    allreduce_packed(packed)
     if rank == 0:
-        out.put((loss_sum.numpy().copy(), dWt.numpy().copy()))
+        out.put((packed.loss.numpy().copy(), packed.dW[0].numpy().copy()))
     dist.barrier()
     dist.destroy_process_group()
 
@@ -71,3 +73,28 @@ def test_shard_rows_partitions_exactly():
             assert sum(c for _, c in blocks) == n
             assert blocks[0][0] == 0 and all(blocks[i][0] + blocks[i][1] == blocks[i + 1][0] for i in range(world - 1))
             assert max(c for _, c in blocks) - min(c for _, c in blocks) <= 1
+
+
+def test_packed_reduction_layout():
+    p = PackedReduction([4, 6])
+    assert len(p) == 12 and p.loss.data_ptr() == p.buffer.data_ptr()
+    assert p.dW[0].data_ptr() == p.buffer.data_ptr() + 8 and p.dW[1].data_ptr() == p.buffer.data_ptr() + 8 + 16
+    p.dW[1].fill_(3.0)
+    assert p.buffer.tolist() == [0.0] * 6 + [3.0] * 6
+
+
+def test_exchange_of_one_rank_needs_no_collective_library():
+    """A world of one: the C exchange (include/dataflow_b200_exchange.h) sets up without NCCL and without a device, and its all-reduce
+    is a no-op that succeeds; bad arguments are refused."""
+    import ctypes as C
+    from dataflow_lib_b200 import _lib, abi
+    L = _lib.lib
+    h, ex = abi.DataflowHandleStruct(), abi.DataflowExchange()
+    assert L.dataflow_exchange_init(C.byref(ex), C.byref(h), 1, 0, None) == 0
+    buf = torch.arange(5, dtype=torch.float32)
+    assert L.dataflow_exchange_all_reduce_f32(C.byref(ex), 0, buf.data_ptr(), 5) == 0
+    assert buf.tolist() == [0.0, 1.0, 2.0, 3.0, 4.0]
+    L.dataflow_exchange_destroy(C.byref(ex))
+    assert L.dataflow_exchange_init(C.byref(ex), C.byref(h), 2, 2, None) == -1        # rank outside the world
+    assert L.dataflow_exchange_init(C.byref(ex), C.byref(h), 2, 0, None) == -1        # several ranks need rank 0's id
+    assert L.dataflow_exchange_all_reduce_f32(None, 0, buf.data_ptr(), 5) == -1
