@@ -23,6 +23,7 @@ Synthetic seeded inputs (N(0,1); weight N(1, 0.02)). The working set of a step (
                                                              step (FP8 FFN, vocabulary projection, fused softmax + cross entropy)
 """
 import argparse
+import faulthandler
 import json
 import os
 import statistics
@@ -798,6 +799,7 @@ def run_stack_arm(args):
 
 
 def main():
+    faulthandler.enable()                      # a crash in native code leaves the Python stack on stderr
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=200)

@@ -147,6 +147,8 @@ class DataflowHandle:
             _L.destroy_cuda_dataflow_handle(C.byref(self.h))
 
     def __del__(self):
+        if getattr(self, "keep_until_exit", False):       # streams that other libraries may still reference: left to the process's end
+            return
         try:
             self.close()
         except Exception:

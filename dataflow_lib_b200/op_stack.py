@@ -29,9 +29,22 @@ from .handle import DataflowHandle
 from .sharding import Exchange, PackedReduction
 
 
+_SHARED_HANDLES = {}
+
+
+def _shared_handle(device_index):
+    """One Dataflow_Handle per device for the steps that are not given one, kept until the process exits: the framework's allocators
+    remember the stream a pinned buffer or a workspace was last used on and touch that stream again when the buffer is released, so
+    a handle whose streams carried framework work must outlive every such buffer."""
+    if device_index not in _SHARED_HANDLES:
+        _SHARED_HANDLES[device_index] = DataflowHandle(device_id=device_index, num_streams=2, stream_prios=[0, -1], register_ops=False)
+        _SHARED_HANDLES[device_index].keep_until_exit = True
+    return _SHARED_HANDLES[device_index]
+
+
 class OpStackStep:
     def __init__(self, tokens, d_model=4096, ffn_dim=14336, n_heads=32, n_kv_heads=8, head_dim=128, vocab=128256, n_layers=4,
-                 eps=1e-5, theta=500000.0, device="cuda"):
+                 eps=1e-5, theta=500000.0, device="cuda", handle=None):
         assert n_heads * head_dim == d_model
         self.T, self.d, self.f, self.V, self.L = tokens, d_model, ffn_dim, vocab, n_layers
         self.n_heads, self.n_kv, self.hd, self.eps, self.theta = n_heads, n_kv_heads, head_dim, eps, int(theta)
@@ -61,8 +74,8 @@ class OpStackStep:
         self.WguT, self.WdT = [u8(d, 2 * f) for _ in range(L)], [u8(f, d) for _ in range(L)]
         self.W_vocab = e(V, d)
         self.marks = None                                        # a list while a step is being profiled: (segment name, CUDA event) pairs
-        # the step's own handle: ops run on its stream 0, an overlapped exchange on its stream 1
-        self.handle = DataflowHandle(device_id=dev.index if dev.index is not None else torch.cuda.current_device(), num_streams=2, register_ops=False)
+        # ops run on stream 0 of the handle, an overlapped exchange on its stream 1 (the caller's handle, else one shared per device)
+        self.handle = handle if handle is not None else _shared_handle(dev.index if dev.index is not None else torch.cuda.current_device())
         self.stream = torch.cuda.ExternalStream(self.handle.stream_ptr(0), device=dev)
         self._xstream = torch.cuda.ExternalStream(self.handle.stream_ptr(1), device=dev)
         self._exchange = None                                    # made at the first exchange (needs the process group, if any)
@@ -211,9 +224,10 @@ class OpStackStep:
                 self.exchange(group)
 
     def close(self):
+        """Leaves the communicator of the exchange. The handle stays (see _shared_handle); a caller's own handle is the caller's to close."""
         if self._exchange is not None:
             self._exchange.close()
-        self.handle.close()
+            self._exchange = None
 
     # launches of this library's kernels in one step (for accounting): per layer fwd rms 1 + rope 1 + ffn 5 (2 row passes, 3 GEMMs),
     # bwd ffn 4 + rope 1 + bwd_w 2 + bwd_x 1; head rms 1 + softmax/CE 2 (rows + loss sum) + bwd_w 2 + bwd_x 1
