@@ -206,6 +206,16 @@ __device__ __forceinline__ void store_one(void * base, uint64_t idx, float f) {
 	else reinterpret_cast<uint8_t *>(base)[idx] = (uint8_t) w;
 }
 
+// one element as fp32 (the general-shape kernels: rows that are not multiples of 8 elements, tensors that are not 16-byte aligned)
+template <typename T>
+__device__ __forceinline__ float load_one(const void * base, uint64_t idx) {
+	constexpr int EPW = Word<T>::EPW;
+	float v[EPW];
+	if constexpr (EPW == 1) { Word<T>::unpack(reinterpret_cast<const uint32_t *>(base)[idx], v); return v[0]; }
+	else if constexpr (EPW == 2) { Word<T>::unpack((uint32_t) reinterpret_cast<const uint16_t *>(base)[idx], v); return v[0]; }
+	else { Word<T>::unpack((uint32_t) reinterpret_cast<const uint8_t *>(base)[idx], v); return v[0]; }
+}
+
 // ---------------------------------------------------------------------------------------
 // fast math: the approximate, flush-to-zero hardware forms that the reference build selects with
 // --use_fast_math (expf -> ex2.approx.ftz(x * log2 e), a / b -> a * rcp.approx.ftz(b)). Written as PTX because the

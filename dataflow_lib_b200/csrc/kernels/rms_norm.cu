@@ -13,7 +13,6 @@ namespace dfb200 {
 
 constexpr int E = 8;                 // elements per chunk
 constexpr int MAX_VPT = 8;
-constexpr int MAX_COLS = MAX_VPT * 512 * E;
 // Threads that share one row, chosen by measurement on B200 (8192 x 4096 bf16, persistent grids):
 // forward 128 x 4 chunks (6.5 TB/s; 256 x 2: 5.9, 512 x 1: 4.7), backward-x 256 x 2 chunks (6.5 TB/s),
 // backward-w row groups of 256 x 2 chunks, four groups per CTA (5.5 TB/s for the partial sums).
@@ -348,10 +347,88 @@ rms_norm_bwd_w_final_kernel(int n_cols, int n_partials, const float * __restrict
 }
 
 // ----------------------------------------------------------------------------------------
+// General shapes: any n_cols, tensors aligned to their element size only -- what the reference's thread-strided scalar loops
+// accept (src/ops/nvidia/norm/rms_norm.cu:339-406, rms_norm_bwd_x.cu:243-252, rms_norm_bwd_w.cu:270-299). One 256-thread CTA per
+// row at a time, one element per access; the arithmetic and the rounding points are those of the packet kernels above (the fp32
+// summation order within a row differs, as it does between any two thread layouts).
+// ----------------------------------------------------------------------------------------
+constexpr int GENERAL_THREADS = 256;
+
+template <typename T>
+__global__ void __launch_bounds__(GENERAL_THREADS)
+rms_norm_fwd_general_kernel(int n_rows, int n_cols, float eps, const void * __restrict__ weight, const void * __restrict__ X,
+                            void * __restrict__ out, float * __restrict__ weighted_sums, float * __restrict__ rms_vals) {
+	__shared__ float red[2][2][32];
+	pdl_prologue();
+	int slot = 0;
+	for (int row = blockIdx.x; row < n_rows; row += gridDim.x, slot ^= 1) {
+		const uint64_t base = (uint64_t) row * n_cols;
+		float ss = 0.0f, ws = 0.0f;
+		for (int i = threadIdx.x; i < n_cols; i += GENERAL_THREADS) {
+			const float x = load_one<T>(X, base + i), w = load_one<T>(weight, i);
+			ws = fmaf(w, x, ws); ss = fmaf(x, x, ss);
+		}
+		block_sum2(ss, ws, red, slot);
+		const float r = rsqrtf(ss / (float) n_cols + eps);
+		if (threadIdx.x == 0) {
+			if (weighted_sums) weighted_sums[row] = ws;
+			if (rms_vals) rms_vals[row] = r;
+		}
+		for (int i = threadIdx.x; i < n_cols; i += GENERAL_THREADS)
+			store_one<T>(out, base + i, (load_one<T>(X, base + i) * r) * load_one<T>(weight, i));
+	}
+}
+
+// dX + dY * B(deriv) as ONE fused multiply-add in B (see FusedUpdate), for a single element
+template <typename B> __device__ __forceinline__ float fused_update_one(float dx, float dy, float deriv);
+template <> __device__ __forceinline__ float fused_update_one<f32_t>(float dx, float dy, float deriv) { return fmaf(dy, deriv, dx); }
+template <> __device__ __forceinline__ float fused_update_one<bf16_t>(float dx, float dy, float deriv) {
+	return __bfloat162float(__hfma(__float2bfloat16_rn(dy), __float2bfloat16_rn(deriv), __float2bfloat16_rn(dx)));      // dy, dx are bf16 values: exact
+}
+template <> __device__ __forceinline__ float fused_update_one<f16_t>(float dx, float dy, float deriv) {
+	return __half2float(__hfma(__float2half_rn(dy), __float2half_rn(deriv), __float2half_rn(dx)));
+}
+
+template <typename F, typename B>
+__global__ void __launch_bounds__(GENERAL_THREADS)
+rms_norm_bwd_x_general_kernel(int n_rows, int n_cols, const float * __restrict__ fwd_weighted_sums, const float * __restrict__ fwd_rms_vals,
+                              const void * __restrict__ weight, const void * __restrict__ X, const void * __restrict__ dY, void * dX) {
+	pdl_prologue();
+	const float n_cols_f = (float) n_cols;
+	for (int row = blockIdx.x; row < n_rows; row += gridDim.x) {
+		const uint64_t base = (uint64_t) row * n_cols;
+		const float r = __ldg(fwd_rms_vals + row), ws = __ldg(fwd_weighted_sums + row);
+		const float r3 = r * r * r;
+		for (int i = threadIdx.x; i < n_cols; i += GENERAL_THREADS) {
+			const float deriv = (load_one<F>(weight, i) * r) - (__fdividef(load_one<F>(X, base + i) * r3, n_cols_f) * ws);
+			store_one<B>(dX, base + i, fused_update_one<B>(load_one<B>(dX, base + i), load_one<B>(dY, base + i), deriv));
+		}
+	}
+}
+
+// stage 1 of backward-w: CTA b sums its rows b, b + gridDim.x, ... for every column; thread t owns columns t, t + 256, ...
+template <typename F, typename B>
+__global__ void __launch_bounds__(GENERAL_THREADS)
+rms_norm_bwd_w_partial_general_kernel(int n_rows, int n_cols, const float * __restrict__ fwd_rms_vals, const void * __restrict__ X,
+                                      const void * __restrict__ dY, float * __restrict__ partials) {
+	pdl_prologue();
+	for (int c = threadIdx.x; c < n_cols; c += GENERAL_THREADS) {
+		float acc = 0.0f;
+		for (int row = blockIdx.x; row < n_rows; row += gridDim.x) {
+			const uint64_t i = (uint64_t) row * n_cols + c;
+			acc += load_one<B>(dY, i) * load_one<F>(X, i) * __ldg(fwd_rms_vals + row);
+		}
+		partials[(size_t) blockIdx.x * n_cols + c] = acc;
+	}
+}
+
+// ----------------------------------------------------------------------------------------
 // host side
 // ----------------------------------------------------------------------------------------
 
 struct RowGeometry { int vpt; int threads; };
+
+static bool elem_aligned(const void * p, int dt) { return reinterpret_cast<uintptr_t>(p) % (uintptr_t) dtype_size(dt) == 0; }
 
 // Pick the chunks-per-thread (1,2,4,8) and the CTA width (multiple of 32) for a row of
 // n_chunks chunks: about `row_threads` threads per row, wider (up to 512) only once VPT has
@@ -366,12 +443,17 @@ static bool row_geometry(int n_chunks, int row_threads, RowGeometry * geo) {
 	return true;
 }
 
-static int check_rows(const char * op, int n_rows, int n_cols, int row_threads, RowGeometry * geo) {
+// *packets = true: the row length is a multiple of 8 elements within the packet kernels' range (the caller still checks the 16-byte
+// alignment of its tensors); false: the general kernels take the call.
+static int check_rows(const char * op, int n_rows, int n_cols, int row_threads, RowGeometry * geo, bool * packets) {
 	if (n_rows < 0 || n_cols <= 0) return set_error(DFB200_ERR_ARG, "%s: bad shape %d x %d", op, n_rows, n_cols);
-	if (n_cols % E) return set_error(DFB200_ERR_ARG, "%s: n_cols = %d is not a multiple of %d", op, n_cols, E);
-	if (!row_geometry(n_cols / E, row_threads, geo))
-		return set_error(DFB200_ERR_ARG, "%s: n_cols = %d exceeds the supported maximum of %d", op, n_cols, MAX_COLS);
+	*packets = n_cols % E == 0 && row_geometry(n_cols / E, row_threads, geo);
 	return DFB200_OK;
+}
+
+static int general_row_grid(int n_rows) {
+	const long long cap = (long long) (sm_count() > 0 ? sm_count() : 1) * 8;
+	return (int) (n_rows < cap ? (n_rows > 0 ? n_rows : 1) : cap);
 }
 
 #define DFB200_DISPATCH_VPT(vpt, VPT, ...)                  \
@@ -398,11 +480,19 @@ extern "C" int dfb200_rms_norm(int fwd_dt, int n_rows, int n_cols, float eps, co
                                float * weighted_sums, float * rms_vals, void * stream) {
 	if (!dtype_size(fwd_dt)) return set_error(DFB200_ERR_DTYPE, "rms_norm: unsupported datatype %d", fwd_dt);
 	RowGeometry geo;
-	int rc = check_rows("rms_norm", n_rows, n_cols, FWD_ROW_THREADS, &geo);
+	bool packets;
+	int rc = check_rows("rms_norm", n_rows, n_cols, FWD_ROW_THREADS, &geo, &packets);
 	if (rc) return rc;
 	if (n_rows == 0) return DFB200_OK;
 	if (!rms_weight || !X || !out) return set_error(DFB200_ERR_ARG, "rms_norm: NULL tensor argument");
-	if (!aligned16(rms_weight) || !aligned16(X) || !aligned16(out)) return set_error(DFB200_ERR_ARG, "rms_norm: tensors must be 16-byte aligned");
+	if (!elem_aligned(rms_weight, fwd_dt) || !elem_aligned(X, fwd_dt) || !elem_aligned(out, fwd_dt))
+		return set_error(DFB200_ERR_ARG, "rms_norm: tensors must be aligned to their element size");
+	if (!packets || !aligned16(rms_weight) || !aligned16(X) || !aligned16(out)) {
+		DFB200_DISPATCH_DTYPE(fwd_dt, T,
+			(launch_pdl(rms_norm_fwd_general_kernel<T>, dim3(general_row_grid(n_rows)), dim3(GENERAL_THREADS), 0, (cudaStream_t) stream, n_rows, n_cols, eps,
+			            rms_weight, X, out, weighted_sums, rms_vals)));
+		return check_launch("rms_norm (general shape)");
+	}
 	DFB200_DISPATCH_DTYPE(fwd_dt, T, DFB200_DISPATCH_VPT(geo.vpt, VPT, {
 		auto kernel = rms_norm_fwd_kernel<T, VPT>;
 		const int grid = persistent_grid(kernel, n_rows, geo.threads);
@@ -417,13 +507,20 @@ extern "C" int dfb200_rms_norm_bwd_x(int fwd_dt, int bwd_dt, int n_rows, int n_c
 	(void) eps;
 	if (!valid_fwd_bwd_pair(fwd_dt, bwd_dt)) return set_error(DFB200_ERR_DTYPE, "rms_norm_bwd_x: unsupported datatype pair (%d, %d)", fwd_dt, bwd_dt);
 	RowGeometry geo;
-	int rc = check_rows("rms_norm_bwd_x", n_rows, n_cols, BWD_X_ROW_THREADS, &geo);
+	bool packets;
+	int rc = check_rows("rms_norm_bwd_x", n_rows, n_cols, BWD_X_ROW_THREADS, &geo, &packets);
 	if (rc) return rc;
 	if (n_rows == 0) return DFB200_OK;
 	if (!fwd_weighted_sums || !fwd_rms_vals || !rms_weight || !X_inp || !upstream_dX || !dX)
 		return set_error(DFB200_ERR_ARG, "rms_norm_bwd_x: NULL tensor argument");
-	if (!aligned16(rms_weight) || !aligned16(X_inp) || !aligned16(upstream_dX) || !aligned16(dX))
-		return set_error(DFB200_ERR_ARG, "rms_norm_bwd_x: tensors must be 16-byte aligned");
+	if (!elem_aligned(rms_weight, fwd_dt) || !elem_aligned(X_inp, fwd_dt) || !elem_aligned(upstream_dX, bwd_dt) || !elem_aligned(dX, bwd_dt))
+		return set_error(DFB200_ERR_ARG, "rms_norm_bwd_x: tensors must be aligned to their element size");
+	if (!packets || !aligned16(rms_weight) || !aligned16(X_inp) || !aligned16(upstream_dX) || !aligned16(dX)) {
+		DFB200_DISPATCH_PAIR(fwd_dt, bwd_dt, F, B,
+			(launch_pdl(rms_norm_bwd_x_general_kernel<F, B>, dim3(general_row_grid(n_rows)), dim3(GENERAL_THREADS), 0, (cudaStream_t) stream, n_rows, n_cols,
+			            fwd_weighted_sums, fwd_rms_vals, rms_weight, X_inp, upstream_dX, dX)));
+		return check_launch("rms_norm_bwd_x (general shape)");
+	}
 	DFB200_DISPATCH_PAIR(fwd_dt, bwd_dt, F, B, DFB200_DISPATCH_VPT(geo.vpt, VPT, {
 		auto kernel = rms_norm_bwd_x_kernel<F, B, VPT>;
 		const int grid = persistent_grid(kernel, n_rows, geo.threads);
@@ -459,13 +556,21 @@ static int launch_rms_norm_bwd_w(bool sums, int fwd_dt, int bwd_dt, int n_rows, 
                                  const void * upstream_dX, void * dW, void * workspace, uint64_t workspace_bytes, void * stream) {
 	if (!valid_fwd_bwd_pair(fwd_dt, bwd_dt)) return set_error(DFB200_ERR_DTYPE, "rms_norm_bwd_w: unsupported datatype pair (%d, %d)", fwd_dt, bwd_dt);
 	RowGeometry geo;
-	int rc = check_rows("rms_norm_bwd_w", n_rows, n_cols, BWD_W_ROW_THREADS, &geo);
+	bool packets;
+	int rc = check_rows("rms_norm_bwd_w", n_rows, n_cols, BWD_W_ROW_THREADS, &geo, &packets);
 	if (rc) return rc;
 	if (n_rows == 0) return DFB200_OK;
 	if (!fwd_rms_vals || !X_inp || !upstream_dX || !dW) return set_error(DFB200_ERR_ARG, "rms_norm_bwd_w: NULL tensor argument");
-	if (!aligned16(X_inp) || !aligned16(upstream_dX)) return set_error(DFB200_ERR_ARG, "rms_norm_bwd_w: tensors must be 16-byte aligned");
-	int groups, grid;
-	bwd_w_geometry(n_rows, geo, &groups, &grid);
+	if (!elem_aligned(X_inp, fwd_dt) || !elem_aligned(upstream_dX, bwd_dt) || !elem_aligned(dW, sums ? DATAFLOW_FP32 : bwd_dt))
+		return set_error(DFB200_ERR_ARG, "rms_norm_bwd_w: tensors must be aligned to their element size");
+	packets = packets && aligned16(X_inp) && aligned16(upstream_dX);
+	int groups = 1, grid;
+	if (packets) {
+		bwd_w_geometry(n_rows, geo, &groups, &grid);
+	} else {
+		grid = sm_count() > 0 ? sm_count() : 1;
+		if (grid > n_rows) grid = n_rows;
+	}
 	const uint64_t need = (uint64_t) grid * (uint64_t) n_cols * sizeof(float);
 	if (!workspace || workspace_bytes < need || !aligned16(workspace))
 		return set_error(DFB200_ERR_WORKSPACE, "rms_norm_bwd_w: needs %llu bytes of 16-byte aligned workspace, got %llu",
@@ -474,11 +579,16 @@ static int launch_rms_norm_bwd_w(bool sums, int fwd_dt, int bwd_dt, int n_rows, 
 	if (smem > 200 * 1024) return set_error(DFB200_ERR_ARG, "rms_norm_bwd_w: n_cols = %d too large", n_cols);
 	cudaStream_t s = (cudaStream_t) stream;
 	float * partials = reinterpret_cast<float *>(workspace);
-	DFB200_DISPATCH_PAIR(fwd_dt, bwd_dt, F, B, DFB200_DISPATCH_VPT(geo.vpt, VPT, {
-		auto kernel = rms_norm_bwd_w_partial_kernel<F, B, VPT>;
-		allow_dyn_smem(reinterpret_cast<const void *>(kernel), smem);
-		launch_pdl(kernel, dim3(grid), dim3(groups * geo.threads), smem, s, n_rows, n_cols, geo.threads, fwd_rms_vals, X_inp, upstream_dX, partials);
-	}));
+	if (packets) {
+		DFB200_DISPATCH_PAIR(fwd_dt, bwd_dt, F, B, DFB200_DISPATCH_VPT(geo.vpt, VPT, {
+			auto kernel = rms_norm_bwd_w_partial_kernel<F, B, VPT>;
+			allow_dyn_smem(reinterpret_cast<const void *>(kernel), smem);
+			launch_pdl(kernel, dim3(grid), dim3(groups * geo.threads), smem, s, n_rows, n_cols, geo.threads, fwd_rms_vals, X_inp, upstream_dX, partials);
+		}));
+	} else {
+		DFB200_DISPATCH_PAIR(fwd_dt, bwd_dt, F, B,
+			(launch_pdl(rms_norm_bwd_w_partial_general_kernel<F, B>, dim3(grid), dim3(GENERAL_THREADS), 0, s, n_rows, n_cols, fwd_rms_vals, X_inp, upstream_dX, partials)));
+	}
 	rc = check_launch("rms_norm_bwd_w (partial sums)");
 	if (rc) return rc;
 	{

@@ -253,6 +253,35 @@ rope_staged_kernel(int tokens, int model_dim, int kv_dim, int head_dim, int tok_
 	if (tid == 0) bulk_wait_all<0>();          // shared memory must outlive the write-backs
 }
 
+// General shapes: any even head_dim, tensors aligned to their element size only (the reference rotates one pair per thread with no
+// other demand, src/ops/nvidia/attention/rope.cu:137-171). One pair per thread; frequency, angle and rotation exactly as in the
+// kernels above (fp64 power rounded once, fp32 angle, sincosf, separately rounded products), recomputed per pair.
+constexpr int ROPE_GENERAL_THREADS = 256;
+
+template <typename T, bool BWD>
+__global__ void __launch_bounds__(ROPE_GENERAL_THREADS)
+rope_general_kernel(int tokens, int model_dim, int kv_dim, int head_dim, float theta, const int * __restrict__ seq_positions, void * X_q, void * X_k) {
+	pdl_prologue();
+	const uint64_t pairs_per_token = (uint64_t) (model_dim + kv_dim) / 2, n_pairs = (uint64_t) tokens * pairs_per_token;
+	for (uint64_t p = (uint64_t) blockIdx.x * ROPE_GENERAL_THREADS + threadIdx.x; p < n_pairs; p += (uint64_t) gridDim.x * ROPE_GENERAL_THREADS) {
+		const int t = (int) (p / pairs_per_token);
+		int e = 2 * (int) (p - (uint64_t) t * pairs_per_token);               // even element index within the token's Q | K row
+		const bool is_q = e < model_dim;
+		if (!is_q) e -= model_dim;
+		void * base = is_q ? X_q : X_k;
+		const uint64_t idx = (uint64_t) t * (is_q ? model_dim : kv_dim) + e;
+		const int j = (e % head_dim) >> 1;
+		const float expo = -1.0f * ((float) (2 * j) / (float) head_dim);
+		const float ang = (float) __ldg(seq_positions + t) * (float) pow((double) theta, (double) expo);
+		float sn, cs;
+		sincosf(ang, &sn, &cs);
+		if (BWD) sn = -sn;
+		const float x0 = load_one<T>(base, idx), x1 = load_one<T>(base, idx + 1);
+		store_one<T>(base, idx, __fsub_rn(__fmul_rn(cs, x0), __fmul_rn(sn, x1)));
+		store_one<T>(base, idx + 1, __fadd_rn(__fmul_rn(cs, x1), __fmul_rn(sn, x0)));
+	}
+}
+
 template <bool BWD>
 static int launch_rope(const char * op, int dt, uint64_t N, int model_dim, int head_dim, int num_kv_heads, int theta,
                        const int * seq_positions, void * X_q, void * X_k, void * stream) {
@@ -260,8 +289,8 @@ static int launch_rope(const char * op, int dt, uint64_t N, int model_dim, int h
 		return set_error(DFB200_ERR_DTYPE, "%s: unsupported datatype %d", op, dt);
 	if (model_dim <= 0 || head_dim <= 0 || num_kv_heads < 0 || theta <= 0)
 		return set_error(DFB200_ERR_ARG, "%s: bad dimensions (model_dim %d, head_dim %d, num_kv_heads %d, theta %d)", op, model_dim, head_dim, num_kv_heads, theta);
-	if (head_dim % E || model_dim % head_dim)
-		return set_error(DFB200_ERR_ARG, "%s: head_dim (%d) must be a multiple of %d and divide model_dim (%d)", op, head_dim, E, model_dim);
+	if (head_dim % 2 || model_dim % head_dim)
+		return set_error(DFB200_ERR_ARG, "%s: head_dim (%d) must be even and divide model_dim (%d)", op, head_dim, model_dim);
 	if (N % (uint64_t) model_dim) return set_error(DFB200_ERR_ARG, "%s: N is not a multiple of model_dim", op);
 	const uint64_t tokens64 = N / (uint64_t) model_dim;
 	if (tokens64 > 0x7fffffffull) return set_error(DFB200_ERR_ARG, "%s: too many tokens", op);
@@ -269,9 +298,18 @@ static int launch_rope(const char * op, int dt, uint64_t N, int model_dim, int h
 	if (tokens == 0) return DFB200_OK;
 	const int kv_dim = num_kv_heads * head_dim;
 	if (!seq_positions || !X_q || (kv_dim && !X_k)) return set_error(DFB200_ERR_ARG, "%s: NULL tensor argument", op);
-	if (!aligned16(X_q) || !aligned16(X_k)) return set_error(DFB200_ERR_ARG, "%s: tensors must be 16-byte aligned", op);
+	const uintptr_t esz = (uintptr_t) dtype_size(dt);
+	if (reinterpret_cast<uintptr_t>(X_q) % esz || reinterpret_cast<uintptr_t>(X_k) % esz || (reinterpret_cast<uintptr_t>(seq_positions) & 3u))
+		return set_error(DFB200_ERR_ARG, "%s: tensors must be aligned to their element size", op);
 	const int half = head_dim / 2;
-	if (half > ROPE_MAX_TABLE) return set_error(DFB200_ERR_ARG, "%s: head_dim %d too large", op, head_dim);
+	if (head_dim % E || !aligned16(X_q) || !aligned16(X_k) || half > ROPE_MAX_TABLE) {
+		const uint64_t n_pairs = (uint64_t) tokens * (uint64_t) (model_dim + kv_dim) / 2;
+		const uint64_t blocks = (n_pairs + ROPE_GENERAL_THREADS - 1) / ROPE_GENERAL_THREADS, cap = (uint64_t) (sm_count() > 0 ? sm_count() : 1) * 32;
+		DFB200_DISPATCH_DTYPE(dt, T,
+			(launch_pdl(rope_general_kernel<T, BWD>, dim3((unsigned) (blocks < cap ? blocks : cap)), dim3(ROPE_GENERAL_THREADS), 0, (cudaStream_t) stream, tokens,
+			            model_dim, kv_dim, head_dim, (float) theta, seq_positions, X_q, X_k)));
+		return check_launch(op);
+	}
 
 	// staged path: rows must be 16-byte multiples (bulk copies) and four stages of at least one token must fit
 	{

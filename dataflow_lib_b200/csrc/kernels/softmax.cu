@@ -447,6 +447,39 @@ softmax_rows_kernel(int n_rows, int n_cols, int slice_chunks, const void * __res
 	if constexpr (MULTI) cluster_wait_acquire();
 }
 
+// General shapes: any n_cols, tensors aligned to their element size only, rows of any length. The reference's structure itself
+// (src/ops/nvidia/loss/softmax.cu:273-407): one 1024-thread block per row, three passes over the row in global memory; warp w takes the
+// 32-element groups w, w + 32, ... (so thread t holds elements t, t + 1024, ...), its sum is rounded to the working type, the 32
+// rounded sums are added in the shuffle-tree order and the total rounded again. A ragged last group contributes what it has.
+template <typename F, typename B>
+__global__ void __launch_bounds__(1024)
+softmax_general_kernel(int n_rows, int n_cols, const void * __restrict__ X, void * __restrict__ out) {
+	__shared__ float s_warp[32];
+	__shared__ float s_row[2];
+	const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+	for (int row = blockIdx.x; row < n_rows; row += gridDim.x) {
+		const uint64_t base = (uint64_t) row * (uint64_t) n_cols;
+		float m = -CUDART_INF_F;
+		for (int i = tid; i < n_cols; i += 1024) m = fmaxf(m, load_one<F>(X, base + i));
+		m = warp_max(m);
+		if (lane == 0) s_warp[warp] = m;
+		__syncthreads();
+		if (warp == 0) { const float v = warp_max(s_warp[lane]); if (lane == 0) s_row[0] = v; }
+		__syncthreads();
+		const float row_max = s_row[0];
+		float part = 0.0f;
+		for (int i = tid; i < n_cols; i += 1024) part += fast_exp(round_to<B>(load_one<F>(X, base + i) - row_max));
+		part = warp_sum(part);
+		if (lane == 0) s_warp[warp] = round_to<B>(part);
+		__syncthreads();
+		if (warp == 0) { const float v = warp_sum(s_warp[lane]); if (lane == 0) s_row[1] = round_to<B>(v); }
+		__syncthreads();
+		const float inv_total = fast_rcp(s_row[1]);
+		for (int i = tid; i < n_cols; i += 1024) store_one<B>(out, base + i, fast_exp(round_to<B>(load_one<F>(X, base + i) - row_max)) * inv_total);
+		__syncthreads();                      // s_warp and s_row are reused by the next row
+	}
+}
+
 // pred[r, labels[r]] -= 1 in the tensor's own type (intended semantics of
 // src/ops/nvidia/loss/cross_entropy.cu:33-44, whose row index is always 0 as written).
 template <typename B>
@@ -668,6 +701,16 @@ using namespace dfb200;
 
 extern "C" int dfb200_softmax(int fwd_dt, int bwd_dt, int n_rows, int n_cols, const void * X, void * out, void * stream) {
 	SoftmaxGeometry g;
+	// rows that are not multiples of 8 elements, rows beyond the on-chip forms and tensors that are only element-aligned: the general kernel
+	if (valid_fwd_bwd_pair(fwd_dt, bwd_dt) && n_rows > 0 && n_cols > 0 && X && out &&
+	    (n_cols % E || !aligned16(X) || !aligned16(out) || n_cols > SOFTMAX_MAX_CLUSTER * SOFTMAX_MAX_THREADS * SOFTMAX_MAX_CPT * E)) {
+		if (reinterpret_cast<uintptr_t>(X) % (uintptr_t) dtype_size(fwd_dt) || reinterpret_cast<uintptr_t>(out) % (uintptr_t) dtype_size(bwd_dt))
+			return set_error(DFB200_ERR_ARG, "softmax: tensors must be aligned to their element size");
+		const long long cap = (long long) (sm_count() > 0 ? sm_count() : 1) * 2;
+		const unsigned grid = (unsigned) (n_rows < cap ? n_rows : cap);
+		DFB200_DISPATCH_PAIR(fwd_dt, bwd_dt, F, B, (softmax_general_kernel<F, B><<<grid, 1024, 0, (cudaStream_t) stream>>>(n_rows, n_cols, X, out)));
+		return check_launch("softmax (general shape)");
+	}
 	int rc = check_softmax("softmax", fwd_dt, bwd_dt, n_rows, n_cols, X, out, &g);
 	if (rc || n_rows == 0) return rc;
 	rc = DFB200_ERR_DTYPE;

@@ -87,15 +87,52 @@ swiglu_bwd_x_kernel(uint64_t n_chunks, const void * __restrict__ x_w1, const voi
 	}
 }
 
-static int check_elementwise(const char * op, int num_rows, int num_cols, uint64_t * n_chunks, int n_ptrs, const void * const * ptrs) {
+// General shapes: any element count, tensors aligned to their element size only (what the reference's element-per-thread kernels
+// accept, src/ops/nvidia/activations/swiglu.cu:48-68). One element per thread, same arithmetic as the packet kernels.
+constexpr int GENERAL_THREADS = 256;
+
+template <typename F>
+__global__ void __launch_bounds__(GENERAL_THREADS)
+swiglu_fwd_general_kernel(uint64_t n, const void * __restrict__ x_w1, const void * __restrict__ x_w3, void * __restrict__ out) {
+	pdl_prologue();
+	for (uint64_t i = (uint64_t) blockIdx.x * GENERAL_THREADS + threadIdx.x; i < n; i += (uint64_t) gridDim.x * GENERAL_THREADS) {
+		float e;
+		store_one<F>(out, i, silu_and_e(load_one<F>(x_w1, i), e) * load_one<F>(x_w3, i));
+	}
+}
+
+template <typename F, typename B>
+__global__ void __launch_bounds__(GENERAL_THREADS)
+swiglu_bwd_x_general_kernel(uint64_t n, const void * __restrict__ x_w1, const void * __restrict__ x_w3, const void * __restrict__ upstream_dX,
+                            void * __restrict__ dX_w1, void * __restrict__ dX_w3) {
+	pdl_prologue();
+	for (uint64_t i = (uint64_t) blockIdx.x * GENERAL_THREADS + threadIdx.x; i < n; i += (uint64_t) gridDim.x * GENERAL_THREADS) {
+		float e;
+		const float x1 = load_one<F>(x_w1, i), x3 = load_one<F>(x_w3, i), g = load_one<B>(upstream_dX, i);
+		const float s = silu_and_e(x1, e), ope = 1.0f + e;
+		store_one<B>(dX_w3, i, g * s);
+		store_one<B>(dX_w1, i, g * __fdividef(x3 * (ope + x1 * e), ope * ope));
+	}
+}
+
+static unsigned general_grid(uint64_t n) {
+	const uint64_t blocks = (n + GENERAL_THREADS - 1) / GENERAL_THREADS, cap = (uint64_t) (sm_count() > 0 ? sm_count() : 1) * 32;
+	return (unsigned) (blocks < cap ? (blocks ? blocks : 1) : cap);
+}
+
+// *packets = true: every tensor is 16-byte aligned and the element count is a multiple of 8 (the packet kernels); false: the general kernels.
+static int check_elementwise(const char * op, int num_rows, int num_cols, uint64_t * n_elems, bool * packets, int n_ptrs, const void * const * ptrs,
+                             const int * elem_sizes) {
 	if (num_rows < 0 || num_cols < 0) return set_error(DFB200_ERR_ARG, "%s: negative shape %d x %d", op, num_rows, num_cols);
 	const uint64_t n = (uint64_t) num_rows * (uint64_t) num_cols;
-	if (n % E) return set_error(DFB200_ERR_ARG, "%s: num_rows*num_cols = %llu is not a multiple of %d", op, (unsigned long long) n, E);
+	*packets = n % E == 0;
 	for (int i = 0; i < n_ptrs; i++) {
 		if (n && !ptrs[i]) return set_error(DFB200_ERR_ARG, "%s: NULL tensor argument %d", op, i);
-		if (!aligned16(ptrs[i])) return set_error(DFB200_ERR_ARG, "%s: tensor argument %d is not 16-byte aligned", op, i);
+		if (reinterpret_cast<uintptr_t>(ptrs[i]) % (uintptr_t) elem_sizes[i])
+			return set_error(DFB200_ERR_ARG, "%s: tensor argument %d is not aligned to its element size", op, i);
+		if (!aligned16(ptrs[i])) *packets = false;
 	}
-	*n_chunks = n / E;
+	*n_elems = n;
 	return DFB200_OK;
 }
 
@@ -104,11 +141,20 @@ static int check_elementwise(const char * op, int num_rows, int num_cols, uint64
 using namespace dfb200;
 
 extern "C" int dfb200_swiglu(int fwd_dt, int num_rows, int num_cols, const void * x_w1, const void * x_w3, void * out, void * stream) {
-	if (!dtype_size(fwd_dt)) return set_error(DFB200_ERR_DTYPE, "swiglu: unsupported datatype %d", fwd_dt);
-	uint64_t n_chunks;
+	const int es = dtype_size(fwd_dt);
+	if (!es) return set_error(DFB200_ERR_DTYPE, "swiglu: unsupported datatype %d", fwd_dt);
+	uint64_t n;
+	bool packets;
 	const void * ptrs[3] = {x_w1, x_w3, out};
-	int rc = check_elementwise("swiglu", num_rows, num_cols, &n_chunks, 3, ptrs);
-	if (rc || n_chunks == 0) return rc;
+	const int sizes[3] = {es, es, es};
+	int rc = check_elementwise("swiglu", num_rows, num_cols, &n, &packets, 3, ptrs, sizes);
+	if (rc || n == 0) return rc;
+	if (!packets) {
+		DFB200_DISPATCH_DTYPE(fwd_dt, F,
+			(launch_pdl(swiglu_fwd_general_kernel<F>, dim3(general_grid(n)), dim3(GENERAL_THREADS), 0, (cudaStream_t) stream, n, x_w1, x_w3, out)));
+		return check_launch("swiglu (general shape)");
+	}
+	const uint64_t n_chunks = n / E;
 	constexpr int THREADS = SWIGLU_FWD_THREADS, UNROLL = SWIGLU_FWD_UNROLL;
 	const uint64_t blocks = (n_chunks + THREADS * UNROLL - 1) / (THREADS * UNROLL);
 	if (blocks > 0x7fffffffull) return set_error(DFB200_ERR_ARG, "swiglu: tensor too large");
@@ -120,10 +166,19 @@ extern "C" int dfb200_swiglu(int fwd_dt, int num_rows, int num_cols, const void 
 extern "C" int dfb200_swiglu_bwd_x(int fwd_dt, int bwd_dt, int num_rows, int num_cols, const void * x_w1, const void * x_w3,
                                    const void * upstream_dX, void * dX_w1, void * dX_w3, void * stream) {
 	if (!valid_fwd_bwd_pair(fwd_dt, bwd_dt)) return set_error(DFB200_ERR_DTYPE, "swiglu_bwd_x: unsupported datatype pair (%d, %d)", fwd_dt, bwd_dt);
-	uint64_t n_chunks;
+	uint64_t n;
+	bool packets;
 	const void * ptrs[5] = {x_w1, x_w3, upstream_dX, dX_w1, dX_w3};
-	int rc = check_elementwise("swiglu_bwd_x", num_rows, num_cols, &n_chunks, 5, ptrs);
-	if (rc || n_chunks == 0) return rc;
+	const int fs = dtype_size(fwd_dt), bs = dtype_size(bwd_dt);
+	const int sizes[5] = {fs, fs, bs, bs, bs};
+	int rc = check_elementwise("swiglu_bwd_x", num_rows, num_cols, &n, &packets, 5, ptrs, sizes);
+	if (rc || n == 0) return rc;
+	if (!packets) {
+		DFB200_DISPATCH_PAIR(fwd_dt, bwd_dt, F, B,
+			(launch_pdl(swiglu_bwd_x_general_kernel<F, B>, dim3(general_grid(n)), dim3(GENERAL_THREADS), 0, (cudaStream_t) stream, n, x_w1, x_w3, upstream_dX, dX_w1, dX_w3)));
+		return check_launch("swiglu_bwd_x (general shape)");
+	}
+	const uint64_t n_chunks = n / E;
 	constexpr int THREADS = SWIGLU_BWD_THREADS, UNROLL = SWIGLU_BWD_UNROLL;
 	const uint64_t blocks = (n_chunks + THREADS * UNROLL - 1) / (THREADS * UNROLL);
 	if (blocks > 0x7fffffffull) return set_error(DFB200_ERR_ARG, "swiglu_bwd_x: tensor too large");

@@ -246,18 +246,25 @@ def test_fused_softmax_cross_entropy(ops, pair, shape):
 # ------------------------------------------------------------------------------------------ argument checking
 
 def test_bad_arguments_are_rejected(ops):
+    import ctypes
+    from dataflow_lib_b200 import _lib
     x = torch.zeros(4, 64, dtype=torch.bfloat16, device="cuda")
     w = torch.ones(64, dtype=torch.bfloat16, device="cuda")
-    with pytest.raises(RuntimeError, match="multiple of 8"):
-        ops.rms_norm(4, 60, 1e-5, w, x, x.clone())
-    with pytest.raises(RuntimeError, match="aligned"):
-        ops.swiglu(1, 8, x.view(-1)[1:9], x.view(-1)[8:16], x.view(-1)[16:24])
-    with pytest.raises(RuntimeError, match="exceeds"):
-        ops.softmax(1, 8 * 40000, x, x)
+    pos = torch.zeros(4, dtype=torch.int32, device="cuda")
+    with pytest.raises(RuntimeError, match="must be even"):
+        ops.rope(4 * 63, 63, 63, 0, 10000, pos, x, x)                          # pairs need an even head_dim
     with pytest.raises(RuntimeError, match="datatype"):
         ops.swiglu_bwd_x(4, 64, x, x, x.float(), x.float(), x.float())
     with pytest.raises(RuntimeError, match="workspace"):
         ops.rms_norm_bwd_w(4, 64, 1e-5, torch.ones(4, device="cuda"), x, x, w.clone(), workspace=torch.empty(16, dtype=torch.uint8, device="cuda"))
+    with pytest.raises(RuntimeError, match="bad shape"):
+        ops.rms_norm(4, 0, 1e-5, w, x, x.clone())
+    # a pointer that is not even aligned to its element (an odd address for a 16-bit tensor) is refused before anything is launched
+    L, BF = _lib.lib, 5
+    odd = x.data_ptr() + 1
+    assert L.dfb200_swiglu(BF, 1, 8, odd, x.data_ptr(), x.data_ptr(), None) == -1 and "element size" in _lib.last_error()
+    assert L.dfb200_rms_norm(BF, 1, 8, ctypes.c_float(1e-5), w.data_ptr(), odd, x.data_ptr(), None, None, None) == -1
+    assert L.dfb200_softmax(BF, BF, 1, 8, odd, x.data_ptr(), None) == -1
     torch.cuda.synchronize()
 
 
