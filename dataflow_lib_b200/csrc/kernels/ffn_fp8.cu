@@ -833,6 +833,8 @@ static bool force_single_cta() {
 // Clusters of two CTAs of the pair kernel that fit on the current device at once (0 when the query fails); remembered per device.
 template <int MODE>
 static int max_resident_pairs() {
+	// plain host statics, not synchronised: two threads that race here both run the query and store the same value (the occupancy of
+	// a kernel on a device does not change), so the worst case is one redundant query
 	static int memo[64];
 	static bool known[64];
 	int dev = 0;

@@ -1,8 +1,9 @@
 """Times the REFERENCE's own kernels (oracle/_ref/cuda_kernels.cubin: its cuda_kernels.cu compiled unchanged for sm_100a with
 its own flags) beside this library's on the same B200, same shapes, same inputs: the 8192-token layer chain and a 4096-row
-slice of the 128256-column softmax. Not a test (pytest does not collect it); run as
+slice of the 128256-column softmax. Checker-side tooling (it launches the reference's kernels): it lives with the oracle and is
+what profiles/reference_kernels_vs_library_bf16_8192tok.md was made with; run as
 
-    python tests/time_reference_kernels.py [--iters 20]
+    python oracle/time_reference_kernels.py [--iters 20]
 
 Each op is launched `iters` times back to back between two CUDA events after one warm-up launch (inputs are far larger than
 L2). cross_entropy_loss is left out: the reference kernel only touches row 0. Prints a markdown table."""
@@ -12,8 +13,9 @@ import sys
 
 import torch
 
-sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
-sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+sys.path.insert(0, os.path.join(ROOT, "tests"))            # ref_kernels.py: the launcher of the reference cubin that the tests use
 
 from dataflow_lib_b200 import ops          # noqa: E402
 from ref_kernels import RefKernels, available   # noqa: E402

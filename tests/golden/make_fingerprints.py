@@ -57,7 +57,7 @@ for op, variants in FAMILIES.items():
 # struct layouts, from the reference's own headers
 import subprocess
 import tempfile
-REF = "/root/reference"
+REF = os.environ.get("REF", "/root/reference")          # the reference tree, as in oracle/Makefile (REF ?= ...)
 inc = [f"-I{REF}/include", f"-I{REF}/src/datatype/include", f"-I{REF}/src/table/include", f"-I{REF}/src/ops/include",
        f"-I{REF}/src/dataflow_handle/include", f"-I{REF}/src/dataflow_handle/nvidia/include", "-I/usr/local/cuda/include"]
 with tempfile.TemporaryDirectory() as td:
