@@ -1,6 +1,12 @@
 """FP8-weight SwiGLU FFN (tcgen05 GEMMs) against the CPU oracle. The reference has no such op, so the oracle's restatement
 is the contract (parity unpinned); it is cross-checked here against a plain fp32 matmul of the dequantised operands.
-Tolerance: bf16 outputs within 1e-2 of max(|ref|, rms(ref)); quantised codes and scales bit-exact."""
+Tolerance: bf16 outputs within 1e-2 of max(|ref|, rms(ref)); quantised codes and scales bit-exact.
+
+Where a pass re-quantises an intermediate that the device computed with the approximate exponential (the hidden activation, the
+gate / up gradients), a one-ulp bf16 difference from the oracle's intermediate can move an e4m3 code by one step, i.e. by 6-12 % of
+that element. Such passes are therefore checked in two ways: every GEMM at 1e-2 against the oracle's GEMM of the codes the DEVICE fed
+it (made again with the library's own row quantiser, which is deterministic), and the whole pass against the oracle's whole pass in
+the L2 norm (1e-2 relative)."""
 import numpy as np
 import pytest
 import torch
@@ -15,6 +21,11 @@ pytestmark = pytest.mark.gpu
 def ops():
     from dataflow_lib_b200 import ops as _ops
     return _ops
+
+
+def _rel_l2(got_bits, ref_bits):
+    got, ref = f32(got_bits, O.BF16).astype(np.float64), f32(ref_bits, O.BF16).astype(np.float64)
+    return float(np.linalg.norm(got - ref) / max(np.linalg.norm(ref), 1e-30))
 
 
 def _weights(n_out, n_in, seed):
@@ -89,8 +100,12 @@ def test_swiglu_ffn_fp8_forward(ops):
     torch.cuda.synchronize()
     assert check_lowp(to_host(G, O.BF16), ref_g, O.BF16, "saved gate pre-activation") > 0.99
     assert check_lowp(to_host(U, O.BF16), ref_u, O.BF16, "saved up pre-activation") > 0.99
-    # the hidden rows are re-quantised from bf16 values that may differ by one ulp from the oracle's: allow 2e-2 here
-    check_lowp(to_host(out, O.BF16), ref, O.BF16, "swiglu_ffn_fp8 out", rel=2e-2)
+    # the down projection at 1e-2 from the codes the device made of ITS g, u; the whole pass in the L2 norm
+    Hq, sh = torch.empty((T, f), dtype=torch.uint8, device="cuda"), torch.empty(T, device="cuda")
+    ops.swiglu_quantize_rows_e4m3(T, f, G, U, Hq, sh)
+    torch.cuda.synchronize()
+    check_lowp(to_host(out, O.BF16), O.gemm_e4m3(Hq.cpu().numpy(), sh.cpu().numpy(), Wd, sd), O.BF16, "down projection of the device's hidden codes")
+    assert _rel_l2(to_host(out, O.BF16), ref) < 1e-2
     # and against the unquantised-activation FFN the fp8 activations cost a few per cent of the output scale
     a32 = f32(A, O.BF16).astype(np.float64)
     wg, wu, wd = (f32(W, O.E4M3) * s[:, None] for W, s in ((Wg, sg), (Wu, su), (Wd, sd)))
@@ -120,8 +135,17 @@ def test_swiglu_ffn_fp8_backward(ops, shape):
     # backward from the ORACLE's saved pre-activations, so that the comparison isolates the backward kernels
     ops.swiglu_ffn_fp8_bwd(T, d, f, to_dev(dOut, O.BF16), to_dev(g, O.BF16), to_dev(u, O.BF16), WdT, t(sd), WguT, t(np.concatenate([sg, su])), dA)
     torch.cuda.synchronize()
-    # gate/up gradients are re-quantised from bf16 values that can differ from the oracle's by one ulp: 2e-2
-    check_lowp(to_host(dA, O.BF16), ref, O.BF16, f"swiglu_ffn_fp8_bwd dA {shape}", rel=2e-2)
+    # the last GEMM at 1e-2 from the codes of the device's own gate | up gradients; the whole pass in the L2 norm
+    dGU = torch.empty((T, 2 * f), dtype=torch.bfloat16, device="cuda")
+    dA2 = torch.empty_like(dA)
+    sgu = t(np.concatenate([sg, su]))
+    ops.swiglu_ffn_fp8_bwd(T, d, f, to_dev(dOut, O.BF16), to_dev(g, O.BF16), to_dev(u, O.BF16), WdT, t(sd), WguT, sgu, dA2, dgate_dup=dGU)
+    dGUq, s2 = torch.empty((T, 2 * f), dtype=torch.uint8, device="cuda"), torch.empty(T, device="cuda")
+    ops.quantize_rows_e4m3(T, 2 * f, dGU, dGUq, s2, col_factors=sgu)
+    torch.cuda.synchronize()
+    assert torch.equal(dA2, dA)
+    check_lowp(to_host(dA, O.BF16), O.gemm_e4m3(dGUq.cpu().numpy(), s2.cpu().numpy(), WguT.cpu().numpy(), None), O.BF16, f"input gradient from the device's codes {shape}")
+    assert _rel_l2(to_host(dA, O.BF16), ref) < 1e-2
     # against autograd of the dequantised-weight FFN in fp64 the fp8 gradients cost a few per cent of the gradient's scale
     a64 = torch.tensor(f32(A, O.BF16), dtype=torch.float64, requires_grad=True)
     wg, wu, wd = (torch.tensor(f32(W, O.E4M3) * s[:, None], dtype=torch.float64) for W, s in ((Wg, sg), (Wu, su), (Wd, sd)))
@@ -231,7 +255,7 @@ def test_ffn_through_the_handle(ops):
     torch.cuda.synchronize()
     assert torch.equal(out0, out1) and torch.equal(G0, G1) and torch.equal(U0, U1) and torch.equal(dA0, dA1)
     ref, _, _ = O.swiglu_ffn_fp8(A, Wg, sg, Wu, su, Wd, sd)
-    check_lowp(to_host(out2, O.BF16), ref, O.BF16, "swiglu_ffn_fp8 through the handle", rel=2e-2)
+    assert _rel_l2(to_host(out2, O.BF16), ref) < 1e-2
     h.close()
 
 
@@ -269,10 +293,22 @@ def test_swiglu_ffn_fp8_wgrad(ops):
     dWg, dWu, dWd = bf(f, d), bf(f, d), bf(d, f)
     ops.swiglu_ffn_fp8_wgrad(T, d, f, to_dev(A, O.BF16), to_dev(dOut, O.BF16), to_dev(g, O.BF16), to_dev(u, O.BF16), to_dev(dGU, O.BF16), dWg, dWu, dWd)
     torch.cuda.synchronize()
-    # H is recomputed on the device with the approximate exponential: a one-ulp bf16 difference can move a code, hence 2e-2
-    check_lowp(to_host(dWd, O.BF16), ref_d, O.BF16, "dWdown", rel=2e-2)
-    check_lowp(to_host(dWg, O.BF16), ref_g, O.BF16, "dWgate", rel=2e-2)
-    check_lowp(to_host(dWu, O.BF16), ref_u, O.BF16, "dWup", rel=2e-2)
+    # dWgate and dWup are made from exact inputs (A, the given gate | up gradients): 1e-2 against the oracle. dWdown uses H, which the
+    # device recomputes with the approximate exponential: its GEMM at 1e-2 from the device's own transposed codes, the pass in the L2 norm
+    check_lowp(to_host(dWg, O.BF16), ref_g, O.BF16, "dWgate")
+    check_lowp(to_host(dWu, O.BF16), ref_u, O.BF16, "dWup")
+    H = torch.empty((T, f), dtype=torch.bfloat16, device="cuda")
+    ops.swiglu(T, f, to_dev(g, O.BF16), to_dev(u, O.BF16), H)
+    def transposed(X, cols):
+        amax, Qt, sc = torch.empty(cols, device="cuda"), torch.empty((cols, T), dtype=torch.uint8, device="cuda"), torch.empty(cols, device="cuda")
+        ops.col_amax_bf16(T, cols, X, amax)
+        ops.transpose_quantize_e4m3(T, cols, X, amax, Qt, sc)
+        torch.cuda.synchronize()
+        return Qt.cpu().numpy(), sc.cpu().numpy()
+    dOt, s_do = transposed(to_dev(dOut, O.BF16), d)
+    Ht, s_h = transposed(H, f)
+    check_lowp(to_host(dWd, O.BF16), O.gemm_e4m3(dOt, s_do, Ht, s_h), O.BF16, "dWdown from the device's transposed codes")
+    assert _rel_l2(to_host(dWd, O.BF16), ref_d) < 1e-2
     # against fp64 autograd of the dequantised-weight FFN the fp8 operands cost a few per cent of the gradient's scale
     a64 = torch.tensor(f32(A, O.BF16), dtype=torch.float64)
     wg, wu, wd = (torch.tensor(f32(W, O.E4M3) * s[:, None], dtype=torch.float64, requires_grad=True) for W, s in ((Wg, sg), (Wu, su), (Wd, sd)))
@@ -300,4 +336,9 @@ def test_ffn_bwd_stores_gate_up_gradients(ops):
     dOq, s1 = O.quantize_rows_e4m3(dOut, sd)
     dH = O.gemm_e4m3(dOq, s1, np.ascontiguousarray(Wd.T), None)
     dg, du = O.swiglu_bwd_x(O.BF16, O.BF16, g, u, dH)
-    check_lowp(to_host(dGU, O.BF16), np.concatenate([dg, du], axis=1), O.BF16, "gate|up gradients kept by the backward pass", rel=2e-2)
+    # dH (a bf16 GEMM output) enters the SwiGLU gradient as an input: where the device's dH and the oracle's round to different bf16
+    # neighbours (two fp32 sums in different orders) the product moves by that unit on top of its own rounding. Those elements are few:
+    got, want = to_host(dGU, O.BF16), np.concatenate([dg, du], axis=1)
+    err = np.abs(f32(got, O.BF16).astype(np.float64) - f32(want, O.BF16))
+    tol = 1e-2 * np.maximum(np.abs(f32(want, O.BF16)), np.sqrt((f32(want, O.BF16).astype(np.float64) ** 2).mean()))
+    assert (err > tol).mean() < 1e-3 and (err <= 2 * tol).all(), "gate|up gradients kept by the backward pass"
