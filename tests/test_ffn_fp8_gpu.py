@@ -192,17 +192,17 @@ def test_ffn_waits_completed(ops):
 def _check_codes(Q, sc, q_ref, s_ref, what):
     """Quantised rows against the oracle when the values being quantised come from approximate device arithmetic: a one-ulp
     bf16 difference can move a code by one step (or, on a row's largest element, the row's scale by < 1 %), so: scales within
-    1 %, >= 98 % of the codes identical, and every dequantised value within one e4m3 step (12.5 %, floor: the row's smallest
-    normal step) of the oracle's."""
+    1 %, >= 98 % of the codes identical, and every dequantised value within one e4m3 step plus that 1 % of scale (13.5 %, floor: the
+    row's smallest normal step) of the oracle's."""
     Q, sc = Q.cpu().numpy(), sc.cpu().numpy()
     assert np.allclose(sc, s_ref, rtol=1e-2), what
     assert (Q == q_ref).mean() >= 0.98, (what, (Q == q_ref).mean())
     got, ref = f32(Q, O.E4M3) * sc[:, None], f32(q_ref, O.E4M3) * s_ref[:, None]
-    tol = 0.125 * np.maximum(np.abs(ref), (s_ref * 2.0 ** -6)[:, None] * 8)
+    tol = 0.135 * np.maximum(np.abs(ref), (s_ref * 2.0 ** -6)[:, None] * 8)
     assert (np.abs(got - ref) <= tol).all(), what
 
 
-@pytest.mark.parametrize("shape", [(64, 14336), (37, 1000 // 8 * 8), (3, 8), (20, 32768)], ids=str)
+@pytest.mark.parametrize("shape", [(64, 14336), (37, 1000 // 8 * 8), (3, 8), (20, 32768), (1200, 14336), (700, 1008)], ids=str)
 def test_swiglu_quantize_rows(ops, shape):
     T, f = shape
     g, u = O.fill_normal(O.BF16, shape, 51), O.fill_normal(O.BF16, shape, 52)
@@ -213,7 +213,7 @@ def test_swiglu_quantize_rows(ops, shape):
     _check_codes(Q, sc, q_ref, s_ref, f"swiglu_quantize_rows {shape}")
 
 
-@pytest.mark.parametrize("shape", [(64, 14336), (37, 1008), (3, 16), (10, 16384)], ids=str)
+@pytest.mark.parametrize("shape", [(64, 14336), (37, 1008), (3, 16), (10, 16384), (1200, 14336), (700, 1008)], ids=str)
 @pytest.mark.parametrize("with_factors", [True, False])
 def test_swiglu_bwd_quantize_rows(ops, shape, with_factors):
     T, f = shape
@@ -222,10 +222,12 @@ def test_swiglu_bwd_quantize_rows(ops, shape, with_factors):
     dg, du = O.swiglu_bwd_x(O.BF16, O.BF16, g, u, dh)
     q_ref, s_ref = O.quantize_rows_e4m3(np.ascontiguousarray(np.concatenate([dg, du], axis=1)), cf)
     Q, sc = torch.empty((T, 2 * f), dtype=torch.uint8, device="cuda"), torch.empty(T, device="cuda")
+    kept = torch.full((T, 2 * f), float("nan"), dtype=torch.bfloat16, device="cuda")
     ops.swiglu_bwd_quantize_rows_e4m3(T, f, to_dev(g, O.BF16), to_dev(u, O.BF16), to_dev(dh, O.BF16), Q, sc,
-                                      col_factors=None if cf is None else torch.from_numpy(cf).cuda())
+                                      col_factors=None if cf is None else torch.from_numpy(cf).cuda(), dgate_dup=kept)
     torch.cuda.synchronize()
     _check_codes(Q, sc, q_ref, s_ref, f"swiglu_bwd_quantize_rows {shape}")
+    assert check_lowp(to_host(kept, O.BF16), np.concatenate([dg, du], axis=1), O.BF16, "gate | up gradients kept in bf16") > 0.99
 
 
 def test_ffn_through_the_handle(ops):
