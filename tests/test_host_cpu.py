@@ -199,11 +199,14 @@ def test_handle_api_fails_cleanly_without_a_device(L, capfd):
     assert L.register_native_ops(C.byref(abi.DataflowHandleStruct()), None, None) == -1
     # the kernel launchers validate arguments before touching CUDA
     assert L.dfb200_swiglu(5, 1, 7, None, None, None, None) == -1
-    assert b"multiple of 8" in L.dfb200_last_error()
+    assert b"NULL tensor argument" in L.dfb200_last_error()
+    assert L.dfb200_swiglu(5, 1, 7, 0x1001, 0x1000, 0x1000, None) == -1       # an odd address for a 16-bit tensor
+    assert b"not aligned to its element size" in L.dfb200_last_error()
+    assert L.dfb200_rope(5, 63 * 4, 63, 63, 0, 10000, 0x1000, 0x2000, 0x3000, None) == -1 and b"must be even" in L.dfb200_last_error()
     assert L.dfb200_rms_norm(1, 1, 8, 1e-5, None, None, None, None, None, None) == -2
-    # the softmax row limit holds in every datatype (the long-row geometries must not widen it silently)
+    # the fused op keeps the on-chip forms' row limit in every datatype (the long-row geometries must not widen it silently)
     for dt in (3, 4, 5, 6):
-        assert L.dfb200_softmax(dt, 5 if dt == 6 else dt, 1, 8 * 40000, 0x1000, 0x2000, None) != 0
+        assert L.dfb200_softmax_cross_entropy(dt, 5 if dt == 6 else dt, 1, 8 * 40000, 0x1000, 0x3000, 0x2000, None, None, None, 0, None) != 0
         assert b"exceeds the supported maximum of 262144" in L.dfb200_last_error()
 
 
