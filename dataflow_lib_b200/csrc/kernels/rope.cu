@@ -144,9 +144,12 @@ rope_staged_kernel(int tokens, int model_dim, int kv_dim, int head_dim, int tok_
 	unsigned char * ring = smem;                                                        // [STAGES][stage_bytes]
 	// cos and sin in separate arrays: a thread reads 4 consecutive cos and 4 consecutive sin (two 16-byte loads),
 	// and consecutive threads read consecutive 16-byte slots, which is free of bank conflicts
-	float * tab_cos = reinterpret_cast<float *>(smem + ROPE_STAGES * stage_bytes);      // [tok_per_stage * half]
-	float * tab_sin = tab_cos + tok_per_stage * half;                                   // [tok_per_stage * half]
-	float * inv_freq = tab_sin + tok_per_stage * half;                                  // [half]
+	// Two table buffers: the table of stage it + 1 is built while stage it is rotated, so one CTA barrier per stage serves both
+	// "rotated rows ready for the write-back" and "next table ready".
+	const int table_len = tok_per_stage * half;
+	float * tab_cos = reinterpret_cast<float *>(smem + ROPE_STAGES * stage_bytes);      // [2][tok_per_stage * half]
+	float * tab_sin = tab_cos + 2 * table_len;                                          // [2][tok_per_stage * half]
+	float * inv_freq = tab_sin + 2 * table_len;                                         // [half]
 	uint64_t * full = reinterpret_cast<uint64_t *>(inv_freq + ((half + 3) & ~3));       // [STAGES]
 	const int tid = threadIdx.x;
 
@@ -176,6 +179,21 @@ rope_staged_kernel(int tokens, int model_dim, int kv_dim, int head_dim, int tok_
 	};
 	if (tid == 0)
 		for (int it = 0; it < ROPE_STAGES - 1 && it < my_iters; it++) issue_load(it);
+	// (cos, sin) of one stage's tokens into table buffer it & 1
+	auto build_table = [&](int it) {
+		if (it >= my_iters) return;
+		const int tok0 = tok0_of(it), n_tok = min(tok_per_stage, tokens - tok0);
+		float * tc = tab_cos + (it & 1) * table_len, * ts = tab_sin + (it & 1) * table_len;
+		for (int e = tid; e < n_tok * half; e += ROPE_STAGED_THREADS) {
+			const int t = e / half, j = e - t * half;
+			float sn, cs;
+			sincosf((float) __ldg(seq_positions + tok0 + t) * inv_freq[j], &sn, &cs);
+			tc[e] = cs;
+			ts[e] = BWD ? -sn : sn;
+		}
+	};
+	build_table(0);
+	__syncthreads();
 
 	const int q_chunks = model_dim / E, k_chunks = kv_dim / E, row_chunks = q_chunks + k_chunks;
 	const int chunks_per_head = head_dim / E;
@@ -183,27 +201,18 @@ rope_staged_kernel(int tokens, int model_dim, int kv_dim, int head_dim, int tok_
 	bool ok = true;
 	for (int it = 0; it < my_iters && ok; it++) {
 		const int s = it % ROPE_STAGES, tok0 = tok0_of(it), n_tok = min(tok_per_stage, tokens - tok0);
-		// (cos, sin) of this stage's tokens, while the copy is still in flight
-		for (int e = tid; e < n_tok * half; e += ROPE_STAGED_THREADS) {
-			const int t = e / half, j = e - t * half;
-			float sn, cs;
-			sincosf((float) __ldg(seq_positions + tok0 + t) * inv_freq[j], &sn, &cs);
-			tab_cos[e] = cs;
-			tab_sin[e] = BWD ? -sn : sn;
-		}
-		ok = mbar_wait_bounded(&full[s], (uint32_t) (it / ROPE_STAGES) & 1u, status, 0x100u + (unsigned) s);
-		ok = __syncthreads_and(ok);            // table visible; everyone agrees on whether to go on
-		if (!ok) break;
+		// every thread waits for the stage's copy itself; a thread whose wait gave up skips the rotation, and the barrier below tells all
+		const bool arrived = mbar_wait_bounded(&full[s], (uint32_t) (it / ROPE_STAGES) & 1u, status, 0x100u + (unsigned) s);
 
 		// Rotate in place in shared memory. Token-major outer loop, chunk-strided inner loop: a chunk's
 		// slot in the (cos, sin) table depends only on its position inside its head, which for Q and K
 		// alike is (c mod chunks_per_head) because both sections hold whole heads -- no division in the
 		// inner loop when chunks_per_head is a power of two.
 		unsigned char * stage = ring + (size_t) s * stage_bytes;
-		for (int t = 0; t < n_tok; t++) {
+		for (int t = 0; t < n_tok && arrived; t++) {
 			unsigned char * q_row = stage + (size_t) t * model_dim * ESIZE;
 			unsigned char * k_row = stage + q_stage_bytes + (size_t) t * kv_dim * ESIZE - (size_t) q_chunks * E * ESIZE;
-			const float * cos_t = tab_cos + t * half, * sin_t = tab_sin + t * half;
+			const float * cos_t = tab_cos + (it & 1) * table_len + t * half, * sin_t = tab_sin + (it & 1) * table_len + t * half;
 			for (int c = tid; c < row_chunks; c += ROPE_STAGED_THREADS) {
 				uint32_t * p = reinterpret_cast<uint32_t *>((c < q_chunks ? q_row : k_row) + (size_t) c * E * ESIZE);
 				const int in_head = head_mask >= 0 ? (c & head_mask) : (c % chunks_per_head);
@@ -236,8 +245,10 @@ rope_staged_kernel(int tokens, int model_dim, int kv_dim, int head_dim, int tok_
 				}
 			}
 		}
+		build_table(it + 1);                   // the other buffer: its last readers passed the previous iteration's barrier
 		fence_async_smem();                    // rotated values must be visible to the bulk store
-		__syncthreads();
+		ok = __syncthreads_and(arrived);       // rows rotated, next table visible; everyone agrees on whether to go on
+		if (!ok) break;
 		if (tid == 0) {
 			const uint32_t qb = (uint32_t) n_tok * model_dim * ESIZE, kb = (uint32_t) n_tok * kv_dim * ESIZE;
 			bulk_store(reinterpret_cast<unsigned char *>(X_q) + (size_t) tok0 * model_dim * ESIZE, stage, qb);
@@ -322,7 +333,7 @@ static int launch_rope(const char * op, int dt, uint64_t N, int model_dim, int h
 		unsigned int * status = kernel_status_word(STATUS_ROPE);
 		if (copyable && tok >= 1 && status) {
 			const size_t stage_bytes = ((size_t) tok * row_bytes + 127) & ~(size_t) 127;
-			const size_t smem = ROPE_STAGES * stage_bytes + (size_t) tok * half * sizeof(float2) + (((size_t) half + 3) & ~(size_t) 3) * sizeof(float)
+			const size_t smem = ROPE_STAGES * stage_bytes + 2 * (size_t) tok * half * sizeof(float2) + (((size_t) half + 3) & ~(size_t) 3) * sizeof(float)
 			                    + ROPE_STAGES * sizeof(uint64_t);
 			int rc = DFB200_ERR_DTYPE;
 			DFB200_DISPATCH_DTYPE(dt, T, {
