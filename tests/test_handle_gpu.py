@@ -75,9 +75,11 @@ def test_same_op_on_two_streams_keeps_separate_scratch():
         X, dY, rms, dW = data[s]
         exact = (dY.float() * X.float() * rms[:, None]).double().sum(0)
         assert ((dW.double() - exact).abs() <= 2.0 ** -8 * exact.abs() + 2e-3).all(), f"stream {s}"
+    torch.cuda.synchronize()
+    before_close = torch.cuda.mem_get_info()[0]
     h.close()
     torch.cuda.synchronize()
-    assert torch.cuda.mem_get_info()[0] > free1                # destroy released the blocks
+    assert torch.cuda.mem_get_info()[0] > before_close         # destroy released the blocks
 
 
 def test_unreserved_scratch_grows_on_demand_and_matches_the_oracle():
