@@ -9,8 +9,10 @@
 One step = one pass over one batch of 8192 tokens per GPU (weak scaling, token-sharded, no data-path collective;
 the RMSNorm weight gradient is all-reduced over NCCL at N > 1):
     fwd  RMSNorm(d=4096) -> RoPE on Q [32 x 128] and K [8 x 128], theta 500000, positions 0..8191 -> SwiGLU [8192 x 14336]
-    bwd  SwiGLU bwd_x -> RoPE bwd_x -> RMSNorm bwd_x -> RMSNorm bwd_w
-submitted through the Dataflow_Handle API (submit_* -> registry lookup -> external op -> C-ABI launcher -> kernel).
+    bwd  SwiGLU bwd_x -> RoPE bwd_x -> RMSNorm bwd_x and bwd_w
+The two gradients of the norm run as this library's one-pass op rms_norm_bwd_x_w (X and dY read once; dX bit-identical to
+rms_norm_bwd_x); --separate-norm-bwd runs the reference's two identities instead, and either way one region of the other form is
+timed in the same run (`norm_backward.other_form`). All ops are submitted through the Dataflow_Handle API (submit_* -> registry lookup -> external op -> C-ABI launcher -> kernel).
 Synthetic seeded inputs (N(0,1); weight N(1, 0.02)). The working set of a step (1.7 GiB) is 13x the 126 MB L2.
 
 `value`   tokens/s with inputs resident in HBM, CUDA events on the handle's stream, max over ranks.
@@ -43,8 +45,12 @@ BYTES_PER_TOKEN = {
     "rms_norm": 2 * D_MODEL * 2 + 8, "rope": 2 * (N_HEADS + N_KV) * HEAD_DIM * 2 + 4, "swiglu": 3 * FFN * 2,
     "swiglu_bwd_x": 5 * FFN * 2, "rope_bwd_x": 2 * (N_HEADS + N_KV) * HEAD_DIM * 2 + 4,
     "rms_norm_bwd_x": 4 * D_MODEL * 2 + 8, "rms_norm_bwd_w": 2 * D_MODEL * 2 + 4,
+    "rms_norm_bwd_x_w": 4 * D_MODEL * 2 + 8,        # both gradients of the norm in one pass: X, dY and dX read once, dX written
 }
-KERNEL_LAUNCHES_PER_STEP = 8          # 7 ops; rms_norm_bwd_w is two launches
+# The backward of the norm runs as this library's one-pass op (rms_norm_bwd_x_w: 4 d e bytes per token) unless --separate-norm-bwd asks
+# for the reference's two identities (rms_norm_bwd_x, then rms_norm_bwd_w reading X and dY again: 6 d e bytes per token).
+CHAIN_OPS = ["rms_norm", "rope", "swiglu", "swiglu_bwd_x", "rope_bwd_x", "rms_norm_bwd_x_w"]
+CHAIN_OPS_SEPARATE = ["rms_norm", "rope", "swiglu", "swiglu_bwd_x", "rope_bwd_x", "rms_norm_bwd_x", "rms_norm_bwd_w"]
 DOMINANT = "swiglu_bwd_x"
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from the ncu capture summarised in
 # profiles/swiglu_bwd_x_bf16_2048x14336.md: reads scale with the rows and equal the algorithmic 704.6 MB; DRAM writes are
@@ -391,33 +397,41 @@ def run_gpu_arm(args):
         for k, a in host.items():
             assert h.submit_inbound_transfer(stream_id, dev[k], a.ctypes.data, a.nbytes) == 0
 
-    op_names = ["rms_norm", "rope", "swiglu", "swiglu_bwd_x", "rope_bwd_x", "rms_norm_bwd_x", "rms_norm_bwd_w"]
+    op_names = CHAIN_OPS_SEPARATE if args.separate_norm_bwd else CHAIN_OPS
+    launches_per_step = len(op_names) + 1      # the weight gradient of the norm is two launches (partial sums, final sum) in both forms
     DOM = op_names.index(DOMINANT)
     N = T * N_HEADS * HEAD_DIM
 
-    def bind(dev):
+    def bind(dev, separate):
         """The submissions of one step on input set `dev`, bound once: the C entry points (submit_* of include/dataflow_api.h) with plain
         integer pointers, so that the per-step host work is the C path (skeleton + SHA-256 + table lookup + launch)."""
         P = {k: v.data_ptr() for k, v in dev.items()}
+        grad = packed.dW[0].data_ptr() if world > 1 else dW.data_ptr()
         calls = [
             lambda: L.submit_rms_norm(hp, S0, BF, T, D_MODEL, EPS, P["w"], P["X"], Y.data_ptr(), ws.data_ptr(), rms.data_ptr()),
             lambda: L.submit_rope(hp, S0, BF, N, N_HEADS * HEAD_DIM, HEAD_DIM, N_KV, THETA, P["pos"], P["Q"], P["K"]),
             lambda: L.submit_swiglu(hp, S0, BF, T, FFN, P["gate"], P["up"], S.data_ptr()),
             lambda: L.submit_swiglu_bwd_x(hp, S0, BF, BF, T, FFN, P["gate"], P["up"], P["dS"], d1.data_ptr(), d3.data_ptr()),
             lambda: L.submit_rope_bwd_x(hp, S0, BF, N, N_HEADS * HEAD_DIM, HEAD_DIM, N_KV, THETA, P["pos"], P["Q"], P["K"]),
-            lambda: L.submit_rms_norm_bwd_x(hp, S0, BF, BF, T, D_MODEL, EPS, ws.data_ptr(), rms.data_ptr(), P["w"], P["X"], P["dY"], dX.data_ptr()),
         ]
-        if world > 1:       # the weight gradient as fp32 column sums in its slot of the packed buffer (overwritten every step)
-            calls.append(lambda: L.submit_rms_norm_bwd_w_sums(hp, S0, BF, BF, T, D_MODEL, EPS, rms.data_ptr(), P["X"], P["dY"], packed.dW[0].data_ptr()))
-        else:               # the reference's identity: accumulates into the bf16 dW
-            calls.append(lambda: L.submit_rms_norm_bwd_w(hp, S0, BF, BF, T, D_MODEL, EPS, rms.data_ptr(), P["X"], P["dY"], dW.data_ptr()))
+        # The weight gradient: at N > 1 fp32 column sums in their slot of the packed buffer (overwritten every step), at N = 1 the
+        # reference's form, accumulated into the bf16 dW.
+        norm_args = (hp, S0, BF, BF, T, D_MODEL, EPS, ws.data_ptr(), rms.data_ptr(), P["w"], P["X"], P["dY"], dX.data_ptr())
+        if separate:
+            calls.append(lambda: L.submit_rms_norm_bwd_x(*norm_args))
+            bwd_w = L.submit_rms_norm_bwd_w_sums if world > 1 else L.submit_rms_norm_bwd_w
+            calls.append(lambda: bwd_w(hp, S0, BF, BF, T, D_MODEL, EPS, rms.data_ptr(), P["X"], P["dY"], grad))
+        else:
+            bwd_x_w = L.submit_rms_norm_bwd_x_w_sums if world > 1 else L.submit_rms_norm_bwd_x_w
+            calls.append(lambda: bwd_x_w(*norm_args, grad))
         return calls
-    bound = [bind(sets[0]), bind(sets[1])]
+    bound = [bind(sets[0], args.separate_norm_bwd), bind(sets[1], args.separate_norm_bwd)]
+    bound_other = bind(sets[0], not args.separate_norm_bwd)        # the other form of the norm's backward, for one comparison region
     exchange_pending = [False]
 
-    def chain(events=None, only=None, which=0):
+    def chain(events=None, only=None, which=0, calls=None):
         """One step on input set `which`. `events[i] = (start, end)` are recorded around op i (all ops, or just op `only`)."""
-        calls = bound[which]
+        calls = calls or bound[which]
         for i, call in enumerate(calls):
             timed = events is not None and (only is None or only == i)
             if world > 1 and i == len(calls) - 1 and exchange_pending[0]:
@@ -430,7 +444,7 @@ def run_gpu_arm(args):
             if timed:
                 events[i][1].record(stream)
             if rc != 0:
-                raise RuntimeError(f"submit of {op_names[i]} failed")
+                raise RuntimeError(f"submit of op {i} of the chain failed")
         if world > 1:
             # the data-parallel exchange (one in-place fp32 all-reduce of 16 KB, issued from C) runs on the handle's second stream behind
             # a dependency on the compute stream, so that it overlaps the next step's kernels
@@ -496,6 +510,23 @@ def run_gpu_arm(args):
     barrier()
     dom_alone_ms = iso[0].elapsed_time(iso[1]) / 20
 
+    # ---- one region of the OTHER form of the norm's backward (separate identities when the timed regions ran the one-pass op, and
+    # the other way round), for a like-for-like step time in the same run
+    for _ in range(3):
+        chain(calls=bound_other)
+    join_exchange(); barrier()
+    o0, o1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    o0.record(stream)
+    for s in range(args.steps):
+        chain(calls=bound_other)
+    join_exchange()
+    o1.record(stream)
+    barrier()
+    other_ms = torch.tensor([o0.elapsed_time(o1)], device="cuda", dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(other_ms, op=dist.ReduceOp.MAX)
+    other_form_ms_per_step = other_ms.item() / args.steps
+
     # ---- untimed pass: every op bracketed, for the per-op table (event-to-event times include launch latency)
     prof_steps = min(args.steps, 50)
     evp = [new_events() for _ in range(prof_steps)]
@@ -511,7 +542,12 @@ def run_gpu_arm(args):
     if world > 1:
         local_sums = torch.empty(D_MODEL, device="cuda")
         with torch.cuda.stream(stream):
-            assert L.submit_rms_norm_bwd_w_sums(hp, S0, BF, BF, T, D_MODEL, EPS, rms.data_ptr(), sets[0]["X"].data_ptr(), sets[0]["dY"].data_ptr(), local_sums.data_ptr()) == 0
+            if args.separate_norm_bwd:
+                assert L.submit_rms_norm_bwd_w_sums(hp, S0, BF, BF, T, D_MODEL, EPS, rms.data_ptr(), sets[0]["X"].data_ptr(), sets[0]["dY"].data_ptr(), local_sums.data_ptr()) == 0
+            else:       # the same one-pass op the step runs (its summation order is its own), on a scratch dX
+                scratch_dX = torch.zeros_like(dX)
+                assert L.submit_rms_norm_bwd_x_w_sums(hp, S0, BF, BF, T, D_MODEL, EPS, ws.data_ptr(), rms.data_ptr(), sets[0]["w"].data_ptr(), sets[0]["X"].data_ptr(),
+                                                      sets[0]["dY"].data_ptr(), scratch_dX.data_ptr(), local_sums.data_ptr()) == 0
         chain(); join_exchange()
         barrier()
         want = local_sums.clone()
@@ -583,7 +619,9 @@ def run_gpu_arm(args):
         achieved, alone = dom_bytes / (dom_ms * 1e-3) / 1e9, dom_bytes / (dom_alone_ms * 1e-3) / 1e9
         ops_report = {name: {"ms": per_op_ms[name], "GB/s": BYTES_PER_TOKEN[name] * T / (per_op_ms[name] * 1e-3) / 1e9,
                              "frac_of_peak": BYTES_PER_TOKEN[name] * T / (per_op_ms[name] * 1e-3) / 1e9 / peak} for name in op_names}
-        step_bytes = sum(BYTES_PER_TOKEN.values()) * T
+        step_bytes = sum(BYTES_PER_TOKEN[name] for name in op_names) * T
+        other_names = CHAIN_OPS if args.separate_norm_bwd else CHAIN_OPS_SEPARATE
+        other_bytes = sum(BYTES_PER_TOKEN[name] for name in other_names) * T
         cpu = cpu_baseline() if world == 1 else None
         others = other_configs(peak) if (world == 1 and not args.no_other_configs) else {}
         if c5 is not None:
@@ -607,13 +645,18 @@ def run_gpu_arm(args):
                                  "them from the end: the ~126 MB that swiglu left in L2 are not re-read from DRAM, so frac can pass 1; `alone` is the "
                                  "distance to the DRAM roofline"},
             "ops_event_bracketed": ops_report,
+            "norm_backward": {"form": "separate rms_norm_bwd_x + rms_norm_bwd_w (the reference's identities)" if args.separate_norm_bwd
+                                      else "one pass: rms_norm_bwd_x_w (dX bit-identical to rms_norm_bwd_x, dW summed in fp32)",
+                              "other_form": {"ops": other_names, "ms_per_step": other_form_ms_per_step, "algorithmic_bytes": other_bytes,
+                                             "tokens_per_s": world * T / (other_form_ms_per_step * 1e-3),
+                                             "what": f"one region of {args.steps} steps with the other form of the norm's backward, same run"}},
             "e2e": {"value": world * T * e2e_steps / (ms_e2e * 1e-3), "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "steps": e2e_steps, "ms_per_step": ms_e2e / e2e_steps, "regions_ms": e2e_ms, "reported": "median of 3 regions",
                     "copy_ms": copy_ms, "compute_ms": ms_total / args.steps,
                     "h2d_GBps_per_rank": h2d / (copy_ms * 1e-3) / 1e9, "h2d_GBps_all_ranks": world * h2d / (copy_ms * 1e-3) / 1e9,
                     "note": "uploads of step s + 1 run on stream 1 beside the kernels of step s; copy_ms is the upload of one step alone with all "
                             "ranks copying at once (slowest rank): the host-side ceiling of this region"},
-            "gpu_launches": KERNEL_LAUNCHES_PER_STEP * args.steps * len(region_ms),
+            "gpu_launches": launches_per_step * args.steps * len(region_ms),
             "host_enqueue_ms_per_step": host_enqueue_ms,
             "clocks": clocks,
         }
@@ -809,6 +852,8 @@ def main():
                     help="chain (default): the elementwise op chain the headline metric is quoted on; stack: the 4-layer token-sharded training step")
     ap.add_argument("--tokens", type=int, default=0, help="stack workload only: tokens per GPU (default 16384)")
     ap.add_argument("--repeats", type=int, default=7, help="chain workload: timed regions of --steps steps each; the median region is reported")
+    ap.add_argument("--separate-norm-bwd", action="store_true",
+                    help="chain workload: run the norm's backward as the reference's two identities (rms_norm_bwd_x, rms_norm_bwd_w) instead of the one-pass op")
     ap.add_argument("--no-stack", action="store_true", help="chain workload: skip the 4-layer stack step (other_configs.c5_stack_4layer)")
     ap.add_argument("--no-other-configs", action="store_true", help="chain workload, N = 1: skip configurations C1, C3 and C4")
     args = ap.parse_args()

@@ -29,6 +29,8 @@ KERNEL_ABI = {
     "dfb200_rms_norm_bwd_w_workspace_bytes": (_u64, [_i, _i]),
     "dfb200_rms_norm_bwd_w": (_i, [_i, _i, _i, _i, _f, _vp, _vp, _vp, _vp, _vp, _u64, _vp]),
     "dfb200_rms_norm_bwd_w_sums": (_i, [_i, _i, _i, _i, _f, _vp, _vp, _vp, _vp, _vp, _u64, _vp]),
+    "dfb200_rms_norm_bwd_x_w": (_i, [_i, _i, _i, _i, _f, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _u64, _vp]),
+    "dfb200_rms_norm_bwd_x_w_sums": (_i, [_i, _i, _i, _i, _f, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _u64, _vp]),
     "dfb200_rms_norm_bwd_w_static": (_i, [_i, _i, _i, _i, _f, _vp, _vp, _vp, _vp, _vp]),
     "dfb200_rope": (_i, [_i, _u64, _i, _i, _i, _i, _vp, _vp, _vp, _vp]),
     "dfb200_rope_bwd_x": (_i, [_i, _u64, _i, _i, _i, _i, _vp, _vp, _vp, _vp]),
@@ -94,6 +96,8 @@ HOST_ABI = {
     "set_native_rms_norm_bwd_x_skeleton": (None, [_SK, _i, _i]),
     "set_native_rms_norm_bwd_w_skeleton": (None, [_SK, _i, _i]),
     "set_native_rms_norm_bwd_w_sums_skeleton": (None, [_SK, _i, _i]),
+    "set_native_rms_norm_bwd_x_w_skeleton": (None, [_SK, _i, _i]),
+    "set_native_rms_norm_bwd_x_w_sums_skeleton": (None, [_SK, _i, _i]),
     "set_native_rope_skeleton": (None, [_SK, _i]),
     "set_native_rope_bwd_x_skeleton": (None, [_SK, _i]),
     "set_native_copy_to_seq_context_skeleton": (None, [_SK, _i]),
@@ -116,6 +120,8 @@ HOST_ABI = {
     "submit_rms_norm_bwd_x": (_i, [_H, _i, _i, _i, _i, _i, _f, _vp, _vp, _vp, _vp, _vp, _vp]),
     "submit_rms_norm_bwd_w": (_i, [_H, _i, _i, _i, _i, _i, _f, _vp, _vp, _vp, _vp]),
     "submit_rms_norm_bwd_w_sums": (_i, [_H, _i, _i, _i, _i, _i, _f, _vp, _vp, _vp, _vp]),
+    "submit_rms_norm_bwd_x_w": (_i, [_H, _i, _i, _i, _i, _i, _f, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
+    "submit_rms_norm_bwd_x_w_sums": (_i, [_H, _i, _i, _i, _i, _i, _f, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
     "submit_rope": (_i, [_H, _i, _i, _u64, _i, _i, _i, _i, _vp, _vp, _vp]),
     "submit_rope_bwd_x": (_i, [_H, _i, _i, _u64, _i, _i, _i, _i, _vp, _vp, _vp]),
     "submit_swiglu": (_i, [_H, _i, _i, _i, _i, _vp, _vp, _vp]),
@@ -154,6 +160,8 @@ HOST_ABI = {
     "dataflow_b200_rms_norm_bwd_x": (_i, [_H, _i, _vp, _vp]),
     "dataflow_b200_rms_norm_bwd_w": (_i, [_H, _i, _vp, _vp]),
     "dataflow_b200_rms_norm_bwd_w_sums": (_i, [_H, _i, _vp, _vp]),
+    "dataflow_b200_rms_norm_bwd_x_w": (_i, [_H, _i, _vp, _vp]),
+    "dataflow_b200_rms_norm_bwd_x_w_sums": (_i, [_H, _i, _vp, _vp]),
     "dataflow_b200_rope": (_i, [_H, _i, _vp, _vp]),
     "dataflow_b200_rope_bwd_x": (_i, [_H, _i, _vp, _vp]),
     "dataflow_b200_swiglu": (_i, [_H, _i, _vp, _vp]),

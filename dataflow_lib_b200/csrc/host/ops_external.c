@@ -58,6 +58,8 @@ static Ws_Block * ensure_workspace(Op_Workspace * all, int stream_id, uint64_t b
 
 int dataflow_b200_rms_norm_bwd_w(Dataflow_Handle * h, int stream_id, Op * op, void * op_extra);
 int dataflow_b200_rms_norm_bwd_w_sums(Dataflow_Handle * h, int stream_id, Op * op, void * op_extra);
+int dataflow_b200_rms_norm_bwd_x_w(Dataflow_Handle * h, int stream_id, Op * op, void * op_extra);
+int dataflow_b200_rms_norm_bwd_x_w_sums(Dataflow_Handle * h, int stream_id, Op * op, void * op_extra);
 int dataflow_b200_softmax_cross_entropy(Dataflow_Handle * h, int stream_id, Op * op, void * op_extra);
 int dataflow_b200_swiglu_ffn_fp8(Dataflow_Handle * h, int stream_id, Op * op, void * op_extra);
 int dataflow_b200_swiglu_ffn_fp8_bwd(Dataflow_Handle * h, int stream_id, Op * op, void * op_extra);
@@ -65,6 +67,7 @@ int dataflow_b200_swiglu_ffn_fp8_bwd(Dataflow_Handle * h, int stream_id, Op * op
 static int owns_workspace(const Cuda_Function * fn) {
 	return fn && !fn->is_native && fn->op_extra &&
 	       (fn->cuda_external_func == dataflow_b200_rms_norm_bwd_w || fn->cuda_external_func == dataflow_b200_rms_norm_bwd_w_sums ||
+	        fn->cuda_external_func == dataflow_b200_rms_norm_bwd_x_w || fn->cuda_external_func == dataflow_b200_rms_norm_bwd_x_w_sums ||
 	        fn->cuda_external_func == dataflow_b200_softmax_cross_entropy ||
 	        fn->cuda_external_func == dataflow_b200_swiglu_ffn_fp8 || fn->cuda_external_func == dataflow_b200_swiglu_ffn_fp8_bwd);
 }
@@ -124,6 +127,25 @@ int dataflow_b200_rms_norm_bwd_w_sums(Dataflow_Handle * h, int stream_id, Op * o
 	if (!ws) return -1;
 	return finish(dfb200_rms_norm_bwd_w_sums(DT(op, 4), DT(op, 5), n_rows, n_cols, ARG(op, 2, float), ARG(op, 3, float *), ARG(op, 4, void *),
 	                                         ARG(op, 5, void *), ARG(op, 6, float *), ws->ptr, ws->bytes, stream_of(h, stream_id)), "rms_norm_bwd_w_sums");
+}
+
+/* args: n_rows, n_cols, eps, fwd_weighted_sums, fwd_rms_vals, rms_weight, X_inp, upstream_dX, dX, dW (or fp32 column_sums) */
+int dataflow_b200_rms_norm_bwd_x_w(Dataflow_Handle * h, int stream_id, Op * op, void * op_extra) {
+	const int n_rows = ARG(op, 0, int), n_cols = ARG(op, 1, int);
+	Ws_Block * ws = ensure_workspace((Op_Workspace *) op_extra, stream_id, dfb200_rms_norm_bwd_w_workspace_bytes(n_rows, n_cols));
+	if (!ws) return -1;
+	return finish(dfb200_rms_norm_bwd_x_w(DT(op, 5), DT(op, 7), n_rows, n_cols, ARG(op, 2, float), ARG(op, 3, float *), ARG(op, 4, float *),
+	                                      ARG(op, 5, void *), ARG(op, 6, void *), ARG(op, 7, void *), ARG(op, 8, void *), ARG(op, 9, void *), ws->ptr,
+	                                      ws->bytes, stream_of(h, stream_id)), "rms_norm_bwd_x_w");
+}
+
+int dataflow_b200_rms_norm_bwd_x_w_sums(Dataflow_Handle * h, int stream_id, Op * op, void * op_extra) {
+	const int n_rows = ARG(op, 0, int), n_cols = ARG(op, 1, int);
+	Ws_Block * ws = ensure_workspace((Op_Workspace *) op_extra, stream_id, dfb200_rms_norm_bwd_w_workspace_bytes(n_rows, n_cols));
+	if (!ws) return -1;
+	return finish(dfb200_rms_norm_bwd_x_w_sums(DT(op, 5), DT(op, 7), n_rows, n_cols, ARG(op, 2, float), ARG(op, 3, float *), ARG(op, 4, float *),
+	                                           ARG(op, 5, void *), ARG(op, 6, void *), ARG(op, 7, void *), ARG(op, 8, void *), ARG(op, 9, float *),
+	                                           ws->ptr, ws->bytes, stream_of(h, stream_id)), "rms_norm_bwd_x_w_sums");
 }
 
 int dataflow_b200_rope(Dataflow_Handle * h, int stream_id, Op * op, void * op_extra) {

@@ -49,6 +49,24 @@ int submit_rms_norm_bwd_w_sums(Dataflow_Handle * handle, int stream_id, Dataflow
 	return submit(handle, &op, stream_id, "rms norm bwd w (fp32 column sums)");
 }
 
+int submit_rms_norm_bwd_x_w(Dataflow_Handle * handle, int stream_id, DataflowDatatype fwd_dt, DataflowDatatype bwd_dt,
+                            int n_rows, int n_cols, float eps, float * fwd_weighted_sums, float * fwd_rms_vals,
+                            void * rms_weight, void * X_inp, void * upstream_dX, void * dX, void * dW) {
+	Op op;
+	set_native_rms_norm_bwd_x_w_skeleton(&op.op_skeleton, fwd_dt, bwd_dt);
+	ARGS(op, &n_rows, &n_cols, &eps, &fwd_weighted_sums, &fwd_rms_vals, &rms_weight, &X_inp, &upstream_dX, &dX, &dW);
+	return submit(handle, &op, stream_id, "rms norm bwd x and w");
+}
+
+int submit_rms_norm_bwd_x_w_sums(Dataflow_Handle * handle, int stream_id, DataflowDatatype fwd_dt, DataflowDatatype bwd_dt,
+                                 int n_rows, int n_cols, float eps, float * fwd_weighted_sums, float * fwd_rms_vals,
+                                 void * rms_weight, void * X_inp, void * upstream_dX, void * dX, float * column_sums) {
+	Op op;
+	set_native_rms_norm_bwd_x_w_sums_skeleton(&op.op_skeleton, fwd_dt, bwd_dt);
+	ARGS(op, &n_rows, &n_cols, &eps, &fwd_weighted_sums, &fwd_rms_vals, &rms_weight, &X_inp, &upstream_dX, &dX, &column_sums);
+	return submit(handle, &op, stream_id, "rms norm bwd x and w (fp32 column sums)");
+}
+
 int submit_rope(Dataflow_Handle * handle, int stream_id, DataflowDatatype fwd_dt, uint64_t N, int model_dim, int head_dim,
                 int num_kv_heads, int theta, int * seq_positions, void * X_q, void * X_k) {
 	Op op;

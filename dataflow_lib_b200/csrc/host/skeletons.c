@@ -71,6 +71,14 @@ void set_native_rms_norm_bwd_w_sums_skeleton(Op_Skeleton * skeleton, DataflowDat
 	char nick[MAX_OP_NICKNAME_SIZE];   /* n_rows, n_cols, eps, rms_vals, X, dY, column sums (fp32) */
 	build_skeleton(skeleton, nick2(nick, "rms_norm_bwd_w_sums", fwd, bwd), I_S, I_S, F_S, DATAFLOW_FP32, fwd, bwd, DATAFLOW_FP32, END);
 }
+void set_native_rms_norm_bwd_x_w_skeleton(Op_Skeleton * skeleton, DataflowDatatype fwd, DataflowDatatype bwd) {
+	char nick[MAX_OP_NICKNAME_SIZE];   /* n_rows, n_cols, eps, weighted_sums, rms_vals, weight, X, dY, dX, dW */
+	build_skeleton(skeleton, nick2(nick, "rms_norm_bwd_x_w", fwd, bwd), I_S, I_S, F_S, DATAFLOW_FP32, DATAFLOW_FP32, fwd, fwd, bwd, bwd, bwd, END);
+}
+void set_native_rms_norm_bwd_x_w_sums_skeleton(Op_Skeleton * skeleton, DataflowDatatype fwd, DataflowDatatype bwd) {
+	char nick[MAX_OP_NICKNAME_SIZE];   /* n_rows, n_cols, eps, weighted_sums, rms_vals, weight, X, dY, dX, column sums (fp32) */
+	build_skeleton(skeleton, nick2(nick, "rms_norm_bwd_x_w_sums", fwd, bwd), I_S, I_S, F_S, DATAFLOW_FP32, DATAFLOW_FP32, fwd, fwd, bwd, bwd, DATAFLOW_FP32, END);
+}
 void set_native_rope_skeleton(Op_Skeleton * skeleton, DataflowDatatype fwd) {
 	char nick[MAX_OP_NICKNAME_SIZE];   /* N, model_dim, head_dim, num_kv_heads, theta, seq_positions, X_q, X_k */
 	build_skeleton(skeleton, nick1(nick, "rope", fwd), U64_S, I_S, I_S, I_S, I_S, DATAFLOW_INT, fwd, fwd, END);
@@ -149,6 +157,8 @@ int set_native_op_skeleton(Op_Skeleton * skeleton, char * op_name, DataflowDatat
 	else if (!strcmp(op_name, "rms_norm_bwd_x")) set_native_rms_norm_bwd_x_skeleton(skeleton, fwd_dt, bwd_dt);
 	else if (!strcmp(op_name, "rms_norm_bwd_w")) set_native_rms_norm_bwd_w_skeleton(skeleton, fwd_dt, bwd_dt);
 	else if (!strcmp(op_name, "rms_norm_bwd_w_sums")) set_native_rms_norm_bwd_w_sums_skeleton(skeleton, fwd_dt, bwd_dt);
+	else if (!strcmp(op_name, "rms_norm_bwd_x_w")) set_native_rms_norm_bwd_x_w_skeleton(skeleton, fwd_dt, bwd_dt);
+	else if (!strcmp(op_name, "rms_norm_bwd_x_w_sums")) set_native_rms_norm_bwd_x_w_sums_skeleton(skeleton, fwd_dt, bwd_dt);
 	else if (!strcmp(op_name, "rope")) set_native_rope_skeleton(skeleton, fwd_dt);
 	else if (!strcmp(op_name, "rope_bwd_x")) set_native_rope_bwd_x_skeleton(skeleton, bwd_dt);
 	else if (!strcmp(op_name, "copy_to_seq_context")) set_native_copy_to_seq_context_skeleton(skeleton, fwd_dt);
@@ -182,12 +192,14 @@ typedef struct {
 /* The reference registers 54 identities (set_native_op_skeletons.c:13-39): all of them are here. Added: the 5
  * copy_to_seq_context identities (the reference has the skeleton, the wrapper and the kernels but leaves them out of
  * its registration list), 5 select_experts identities (kernels only in the reference) and the 7 datatype pairs of
- * the fused softmax+cross-entropy op, 2 softmax_argmax identities (fp16 / bf16 -> fp32), the FP8 FFN forward and backward, and the 7
- * pairs of rms_norm_bwd_w_sums (the weight gradient written as fp32 column sums for a data-parallel exchange): 82 in total. */
+ * the fused softmax+cross-entropy op, 2 softmax_argmax identities (fp16 / bf16 -> fp32), the FP8 FFN forward and backward, the 7
+ * pairs of rms_norm_bwd_w_sums (the weight gradient written as fp32 column sums for a data-parallel exchange), and the 7 + 7 pairs of
+ * rms_norm_bwd_x_w and rms_norm_bwd_x_w_sums (input and weight gradient of the norm in one pass over X and dY): 96 in total. */
 static const Op_Family FAMILIES[] = {
 	{"embedding", KEY_FWD, false},      {"copy_to_seq_context", KEY_FWD, false}, {"select_experts", KEY_FWD, false},
 	{"rms_norm", KEY_FWD, false},       {"rms_norm_bwd_x", KEY_PAIR, false}, {"rms_norm_bwd_w", KEY_PAIR, true},
 	{"rms_norm_bwd_w_sums", KEY_PAIR, true},
+	{"rms_norm_bwd_x_w", KEY_PAIR, true}, {"rms_norm_bwd_x_w_sums", KEY_PAIR, true},
 	{"rope", KEY_FWD, false},           {"rope_bwd_x", KEY_BWD, false},
 	{"swiglu", KEY_FWD, false},         {"swiglu_bwd_x", KEY_PAIR, false},
 	{"softmax", KEY_PAIR, false},       {"cross_entropy_loss", KEY_BWD, false},
@@ -201,7 +213,7 @@ static const DataflowDatatype BWD_DTS[3] = {DATAFLOW_FP32, DATAFLOW_FP16, DATAFL
 static const DataflowDatatype PAIR_FWD[7] = {DATAFLOW_FP32, DATAFLOW_FP16, DATAFLOW_BF16, DATAFLOW_FP8E4M3, DATAFLOW_FP8E4M3, DATAFLOW_FP8E5M2, DATAFLOW_FP8E5M2};
 static const DataflowDatatype PAIR_BWD[7] = {DATAFLOW_FP32, DATAFLOW_FP16, DATAFLOW_BF16, DATAFLOW_FP16, DATAFLOW_BF16, DATAFLOW_FP16, DATAFLOW_BF16};
 
-#define MAX_REGISTERED 96
+#define MAX_REGISTERED 128
 
 int register_native_ops(Dataflow_Handle * dataflow_handle, char * native_function_code_filename, char * native_function_config_filename) {
 	(void) native_function_config_filename;

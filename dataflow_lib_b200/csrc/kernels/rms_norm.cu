@@ -8,6 +8,8 @@
 // requested before the current row is reduced, so each thread keeps 2*VPT (fwd), up to 6*VPT
 // (bwd_x) loads in flight.
 #include "common.cuh"
+#include "tma.cuh"
+#include <math_constants.h>
 
 namespace dfb200 {
 
@@ -304,6 +306,263 @@ rms_norm_bwd_w_partial_kernel(int n_rows, int n_cols, int group_threads, const f
 	}
 }
 
+// ----------------------------------------------------------------------------------------
+// backward-x and backward-w stage 1 in ONE pass over X and dY (no reference counterpart: the reference launches the two kernels
+// above one after the other, and the second reads X and dY again). Geometry of backward-w stage 1: one CTA per SM, GROUPS row
+// groups of `group_threads` threads, group g taking rows blockIdx.x*GROUPS + g, + gridDim.x*GROUPS, ... . Per row a thread does
+// what rms_norm_bwd_x_kernel does to its packets of dX (same arithmetic, same roundings: the dX it writes is bit-identical) and
+// adds f32(dY)*f32(x)*r to its fp32 column sums, which leave the CTA the way rms_norm_bwd_w_partial_kernel's do. There is no
+// barrier in the row loop, so the warps of a CTA drift apart and one warp's loads overlap another's arithmetic; all packets of a
+// row are requested before the first is used (6*VPT 16-byte loads per thread in flight).
+// ----------------------------------------------------------------------------------------
+template <typename F, typename B, int VPT>
+__global__ void __launch_bounds__(bwd_w_max_threads(VPT))
+rms_norm_bwd_xw_partial_kernel(int n_rows, int n_cols, int group_threads, const float * __restrict__ fwd_weighted_sums,
+                               const float * __restrict__ fwd_rms_vals, const void * __restrict__ weight, const void * __restrict__ X,
+                               const void * __restrict__ dY, void * dX, float * __restrict__ partials) {
+	constexpr int BEPW = Word<B>::EPW, BW = E / BEPW;
+	extern __shared__ float group_sums[];      // [groups - 1][n_cols]
+	pdl_prologue();                            // also lets stage 2 be scheduled: it waits for this grid in its own prologue
+	const int n_chunks = n_cols / E;
+	const int groups = blockDim.x / group_threads;
+	const int g = threadIdx.x / group_threads;
+	const int tid = threadIdx.x - g * group_threads;
+	const float n_cols_f = (float) n_cols;
+
+	float acc[VPT][E];
+	RawChunk<F> wr[VPT];
+	#pragma unroll
+	for (int v = 0; v < VPT; v++) {
+		#pragma unroll
+		for (int i = 0; i < E; i++) acc[v][i] = 0.0f;
+		const int c = tid + v * group_threads;
+		if (c < n_chunks) ld_words<E / Word<F>::EPW, Hint::KEEP>(reinterpret_cast<const char *>(weight) + (size_t) c * E * (4 / Word<F>::EPW), wr[v].w);
+	}
+
+	const int row_stride = gridDim.x * groups;
+	for (int row = blockIdx.x * groups + g; row < n_rows; row += row_stride) {
+		RawChunk<F> xr[VPT];
+		RawChunk<B> gr[VPT], dr[VPT];
+		#pragma unroll
+		for (int v = 0; v < VPT; v++) {
+			const int c = tid + v * group_threads;
+			if (c < n_chunks) {
+				const uint64_t off = (uint64_t) row * n_cols + (uint64_t) c * E;
+				ld_raw<F>(X, off, xr[v]);
+				ld_raw<B>(dY, off, gr[v]);
+				ld_raw<B>(dX, off, dr[v]);
+			}
+		}
+		const float r = __ldg(fwd_rms_vals + row);
+		const float ws = __ldg(fwd_weighted_sums + row);
+		const float r3 = r * r * r;
+		#pragma unroll
+		for (int v = 0; v < VPT; v++) {
+			const int c = tid + v * group_threads;
+			if (c < n_chunks) {
+				float x[E], w[E], gy[E], deriv[E];
+				to_f32<F>(xr[v], x); to_f32<F>(wr[v], w); to_f32<B>(gr[v], gy);
+				#pragma unroll
+				for (int i = 0; i < E; i++) {
+					deriv[i] = (w[i] * r) - (__fdividef(x[i] * r3, n_cols_f) * ws);
+					acc[v][i] += gy[i] * x[i] * r;
+				}
+				uint32_t o[BW];
+				#pragma unroll
+				for (int k = 0; k < BW; k++) o[k] = FusedUpdate<B>::apply(dr[v].w[k], gr[v].w[k], &deriv[k * BEPW]);
+				st_words<BW>(reinterpret_cast<char *>(dX) + ((uint64_t) row * n_cols + (uint64_t) c * E) * (4 / BEPW), o);
+			}
+		}
+	}
+
+	if (g > 0) {
+		#pragma unroll
+		for (int v = 0; v < VPT; v++) {
+			const int c = tid + v * group_threads;
+			if (c < n_chunks) {
+				float4 * dst = reinterpret_cast<float4 *>(group_sums + (size_t) (g - 1) * n_cols + (size_t) c * E);
+				dst[0] = make_float4(acc[v][0], acc[v][1], acc[v][2], acc[v][3]);
+				dst[1] = make_float4(acc[v][4], acc[v][5], acc[v][6], acc[v][7]);
+			}
+		}
+	}
+	__syncthreads();
+	if (g == 0) {
+		#pragma unroll
+		for (int v = 0; v < VPT; v++) {
+			const int c = tid + v * group_threads;
+			if (c < n_chunks) {
+				for (int o = 0; o < groups - 1; o++) {
+					const float4 * src = reinterpret_cast<const float4 *>(group_sums + (size_t) o * n_cols + (size_t) c * E);
+					const float4 a = src[0], b = src[1];
+					acc[v][0] += a.x; acc[v][1] += a.y; acc[v][2] += a.z; acc[v][3] += a.w;
+					acc[v][4] += b.x; acc[v][5] += b.y; acc[v][6] += b.z; acc[v][7] += b.w;
+				}
+				float4 * dst = reinterpret_cast<float4 *>(partials + (size_t) blockIdx.x * n_cols + (size_t) c * E);
+				dst[0] = make_float4(acc[v][0], acc[v][1], acc[v][2], acc[v][3]);
+				dst[1] = make_float4(acc[v][4], acc[v][5], acc[v][6], acc[v][7]);
+			}
+		}
+	}
+}
+
+// ----------------------------------------------------------------------------------------
+// The same fused pass with the rows STAGED through shared memory by bulk asynchronous copies. A thread of the register kernel above
+// has at most 6*VPT packets in flight and then stops requesting while it computes; what a whole SM keeps in flight (96 KB at 1024
+// threads) is what limits it (5.0 TB/s at 8192 x 4096 bf16). Here each row group owns a ring of `stages` row slots [X | dY | dX] that
+// its thread 0 refills with three bulk copies as soon as the group has consumed a slot, so an SM has up to 8 rows (192 KB at
+// d = 4096 bf16) in flight whatever the threads are doing, and the registers hold only the weights and the column sums.
+// Waits are bounded: a group whose copy does not arrive records it in *status, the CTA's partial sums become NaN (so does dW) and
+// the rows it did not reach keep their dX.
+// ----------------------------------------------------------------------------------------
+constexpr int XW_STAGED_THREADS = 512, XW_MAX_STAGES = 4;
+constexpr size_t XW_RING_BUDGET = 200 * 1024;
+
+template <int NW> __device__ __forceinline__ void lds_words(const unsigned char * p, uint32_t (&w)[NW]) {
+	static_assert(NW == 2 || NW == 4 || NW == 8, "a chunk of 8 elements is 8, 16 or 32 bytes");
+	if constexpr (NW == 2) {
+		const uint2 v = *reinterpret_cast<const uint2 *>(p);
+		w[0] = v.x; w[1] = v.y;
+	} else {
+		#pragma unroll
+		for (int q = 0; q < NW / 4; q++) {
+			const uint4 v = reinterpret_cast<const uint4 *>(p)[q];
+			w[4 * q] = v.x; w[4 * q + 1] = v.y; w[4 * q + 2] = v.z; w[4 * q + 3] = v.w;
+		}
+	}
+}
+
+template <typename F, typename B, int VPT>
+__global__ void __launch_bounds__(XW_STAGED_THREADS)
+rms_norm_bwd_xw_staged_kernel(int n_rows, int n_cols, int group_threads, int stages, const float * __restrict__ fwd_weighted_sums,
+                              const float * __restrict__ fwd_rms_vals, const void * __restrict__ weight, const void * X, const void * dY, void * dX,
+                              float * __restrict__ partials, unsigned int * status) {
+	constexpr int FW = E / Word<F>::EPW, BEPW = Word<B>::EPW, BW = E / BEPW;
+	constexpr uint32_t FSIZE = 4 / Word<F>::EPW, BSIZE = 4 / BEPW;
+	extern __shared__ __align__(128) unsigned char xw_smem[];
+	__shared__ int s_failed;
+	const int n_chunks = n_cols / E;
+	const int groups = blockDim.x / group_threads;
+	const int g = threadIdx.x / group_threads;
+	const int tid = threadIdx.x - g * group_threads;
+	const float n_cols_f = (float) n_cols;
+	const uint32_t xb = (uint32_t) n_cols * FSIZE, gb = (uint32_t) n_cols * BSIZE, stage_bytes = xb + 2 * gb;
+	unsigned char * ring = xw_smem + (size_t) g * stages * stage_bytes;                                         // this group's [stages][X | dY | dX]
+	uint64_t * full = reinterpret_cast<uint64_t *>(xw_smem + (size_t) groups * stages * stage_bytes) + g * stages;
+
+	cudaTriggerProgrammaticLaunchCompletion();       // see pdl_prologue(): the set-up below needs no global memory
+	if (threadIdx.x == 0) s_failed = 0;
+	if (tid == 0) {
+		for (int s = 0; s < stages; s++) mbar_init(&full[s], 1);
+		mbar_fence_init();
+	}
+	float acc[VPT][E];
+	#pragma unroll
+	for (int v = 0; v < VPT; v++)
+		#pragma unroll
+		for (int i = 0; i < E; i++) acc[v][i] = 0.0f;
+	__syncthreads();
+	cudaGridDependencySynchronize();
+
+	const int row_stride = gridDim.x * groups, first = blockIdx.x * groups + g;
+	const int my_iters = first < n_rows ? (n_rows - first + row_stride - 1) / row_stride : 0;
+	auto issue = [&](int k) {                        // thread 0 of the group only
+		const int s = k % stages;
+		const uint64_t row = (uint64_t) (first + k * row_stride);
+		unsigned char * dst = ring + (size_t) s * stage_bytes;
+		mbar_arrive_expect_tx(&full[s], stage_bytes);
+		bulk_load(dst, reinterpret_cast<const unsigned char *>(X) + row * xb, xb, &full[s]);
+		bulk_load(dst + xb, reinterpret_cast<const unsigned char *>(dY) + row * gb, gb, &full[s]);
+		bulk_load(dst + xb + gb, reinterpret_cast<const unsigned char *>(dX) + row * gb, gb, &full[s]);
+	};
+	if (tid == 0)
+		for (int k = 0; k < stages && k < my_iters; k++) issue(k);
+
+	RawChunk<F> wr[VPT];
+	#pragma unroll
+	for (int v = 0; v < VPT; v++) {
+		const int c = tid + v * group_threads;
+		if (c < n_chunks) ld_words<FW, Hint::KEEP>(reinterpret_cast<const char *>(weight) + (size_t) c * E * FSIZE, wr[v].w);
+	}
+
+	for (int k = 0; k < my_iters; k++) {
+		const int s = k % stages, row = first + k * row_stride;
+		const bool arrived = mbar_wait_bounded(&full[s], (uint32_t) (k / stages) & 1u, status, 0x300u + (unsigned) s);
+		if (arrived) {
+			const unsigned char * slot = ring + (size_t) s * stage_bytes;
+			const float r = __ldg(fwd_rms_vals + row);
+			const float ws = __ldg(fwd_weighted_sums + row);
+			const float r3 = r * r * r;
+			#pragma unroll
+			for (int v = 0; v < VPT; v++) {
+				const int c = tid + v * group_threads;
+				if (c < n_chunks) {
+					RawChunk<F> xr;
+					RawChunk<B> gr, dr;
+					lds_words<FW>(slot + (size_t) c * E * FSIZE, xr.w);
+					lds_words<BW>(slot + xb + (size_t) c * E * BSIZE, gr.w);
+					lds_words<BW>(slot + xb + gb + (size_t) c * E * BSIZE, dr.w);
+					float x[E], w[E], gy[E], deriv[E];
+					to_f32<F>(xr, x); to_f32<F>(wr[v], w); to_f32<B>(gr, gy);
+					#pragma unroll
+					for (int i = 0; i < E; i++) {
+						deriv[i] = (w[i] * r) - (__fdividef(x[i] * r3, n_cols_f) * ws);
+						acc[v][i] += gy[i] * x[i] * r;
+					}
+					uint32_t o[BW];
+					#pragma unroll
+					for (int q = 0; q < BW; q++) o[q] = FusedUpdate<B>::apply(dr.w[q], gr.w[q], &deriv[q * BEPW]);
+					st_words<BW>(reinterpret_cast<char *>(dX) + ((uint64_t) row * n_cols + (uint64_t) c * E) * BSIZE, o);
+				}
+			}
+		} else {
+			*reinterpret_cast<volatile int *>(&s_failed) = 1;
+		}
+		// the group's own barrier (ids 1 .. groups): every thread of the group has read the slot, and a failure flag set above is visible
+		asm volatile("bar.sync %0, %1;" :: "r"(1 + g), "r"(group_threads) : "memory");
+		if (*reinterpret_cast<volatile int *>(&s_failed)) break;
+		if (tid == 0 && k + stages < my_iters) issue(k + stages);
+	}
+	__syncthreads();                                 // every group has left its loop
+	const bool failed = *reinterpret_cast<volatile int *>(&s_failed) != 0;
+	if (failed) {
+		// copies may still be in flight into the ring: leave it alone, and poison what this CTA contributes
+		for (int c = threadIdx.x; c < n_cols; c += blockDim.x) partials[(size_t) blockIdx.x * n_cols + c] = CUDART_NAN_F;
+		return;
+	}
+	// every copy that was issued has been waited for, so the ring can carry the groups' column sums now
+	float * group_sums = reinterpret_cast<float *>(xw_smem);   // [groups - 1][n_cols]
+	if (g > 0) {
+		#pragma unroll
+		for (int v = 0; v < VPT; v++) {
+			const int c = tid + v * group_threads;
+			if (c < n_chunks) {
+				float4 * dst = reinterpret_cast<float4 *>(group_sums + (size_t) (g - 1) * n_cols + (size_t) c * E);
+				dst[0] = make_float4(acc[v][0], acc[v][1], acc[v][2], acc[v][3]);
+				dst[1] = make_float4(acc[v][4], acc[v][5], acc[v][6], acc[v][7]);
+			}
+		}
+	}
+	__syncthreads();
+	if (g == 0) {
+		#pragma unroll
+		for (int v = 0; v < VPT; v++) {
+			const int c = tid + v * group_threads;
+			if (c < n_chunks) {
+				for (int o = 0; o < groups - 1; o++) {
+					const float4 * src = reinterpret_cast<const float4 *>(group_sums + (size_t) o * n_cols + (size_t) c * E);
+					const float4 a = src[0], b = src[1];
+					acc[v][0] += a.x; acc[v][1] += a.y; acc[v][2] += a.z; acc[v][3] += a.w;
+					acc[v][4] += b.x; acc[v][5] += b.y; acc[v][6] += b.z; acc[v][7] += b.w;
+				}
+				float4 * dst = reinterpret_cast<float4 *>(partials + (size_t) blockIdx.x * n_cols + (size_t) c * E);
+				dst[0] = make_float4(acc[v][0], acc[v][1], acc[v][2], acc[v][3]);
+				dst[1] = make_float4(acc[v][4], acc[v][5], acc[v][6], acc[v][7]);
+			}
+		}
+	}
+}
+
 // backward-w, stage 2: dW[c] = B( f32(dW[c]) + sum_p partials[p][c] ). A CTA covers 32
 // columns with 32 slices of the partial rows (every thread a handful of independent loads);
 // slices are combined in slice order. Launched as a programmatic dependent of stage 1: its CTAs
@@ -552,6 +811,24 @@ extern "C" uint64_t dfb200_rms_norm_bwd_w_workspace_bytes(int n_rows, int n_cols
 	return (uint64_t) sms * (uint64_t) n_cols * sizeof(float);
 }
 
+// Stage 2 of backward-w as a programmatic dependent of the stage-1 launch before it.
+static int launch_bwd_w_final(const char * op, bool sums, int fwd_dt, int bwd_dt, int n_cols, int n_partials, const float * partials, void * dW, cudaStream_t s) {
+	cudaLaunchConfig_t cfg = {};
+	cfg.gridDim = dim3((n_cols + 31) / 32, 1, 1);
+	cfg.blockDim = dim3(1024, 1, 1);
+	cfg.stream = s;
+	cudaLaunchAttribute attr[1];
+	attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+	attr[0].val.programmaticStreamSerializationAllowed = 1;
+	cfg.attrs = attr; cfg.numAttrs = 1;
+	cudaError_t e = cudaErrorInvalidValue;
+	DFB200_DISPATCH_PAIR(fwd_dt, bwd_dt, F, B,
+		e = (sums ? cudaLaunchKernelEx(&cfg, rms_norm_bwd_w_final_kernel<B, true>, n_cols, n_partials, partials, dW)
+		          : cudaLaunchKernelEx(&cfg, rms_norm_bwd_w_final_kernel<B, false>, n_cols, n_partials, partials, dW)));
+	if (e != cudaSuccess) { cudaGetLastError(); return set_error(DFB200_ERR_CUDA, "%s: %s", op, cudaGetErrorString(e)); }
+	return DFB200_OK;
+}
+
 static int launch_rms_norm_bwd_w(bool sums, int fwd_dt, int bwd_dt, int n_rows, int n_cols, const float * fwd_rms_vals, const void * X_inp,
                                  const void * upstream_dX, void * dW, void * workspace, uint64_t workspace_bytes, void * stream) {
 	if (!valid_fwd_bwd_pair(fwd_dt, bwd_dt)) return set_error(DFB200_ERR_DTYPE, "rms_norm_bwd_w: unsupported datatype pair (%d, %d)", fwd_dt, bwd_dt);
@@ -591,23 +868,92 @@ static int launch_rms_norm_bwd_w(bool sums, int fwd_dt, int bwd_dt, int n_rows, 
 	}
 	rc = check_launch("rms_norm_bwd_w (partial sums)");
 	if (rc) return rc;
-	{
-		cudaLaunchConfig_t cfg = {};
-		cfg.gridDim = dim3((n_cols + 31) / 32, 1, 1);
-		cfg.blockDim = dim3(1024, 1, 1);
-		cfg.stream = s;
-		cudaLaunchAttribute attr[1];
-		attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-		attr[0].val.programmaticStreamSerializationAllowed = 1;
-		cfg.attrs = attr; cfg.numAttrs = 1;
-		const float * cpartials = partials;
-		cudaError_t e = cudaErrorInvalidValue;
-		DFB200_DISPATCH_PAIR(fwd_dt, bwd_dt, F, B,
-			e = (sums ? cudaLaunchKernelEx(&cfg, rms_norm_bwd_w_final_kernel<B, true>, n_cols, grid, cpartials, dW)
-			          : cudaLaunchKernelEx(&cfg, rms_norm_bwd_w_final_kernel<B, false>, n_cols, grid, cpartials, dW)));
-		if (e != cudaSuccess) { cudaGetLastError(); return set_error(DFB200_ERR_CUDA, "rms_norm_bwd_w (final sum): %s", cudaGetErrorString(e)); }
+	return launch_bwd_w_final("rms_norm_bwd_w (final sum)", sums, fwd_dt, bwd_dt, n_cols, grid, partials, dW, s);
+}
+
+// rms_norm_bwd_x and rms_norm_bwd_w in one call: one pass over X and dY (rms_norm_bwd_xw_partial_kernel) where the row length and
+// the alignment allow the packet kernels, the two separate general-shape paths otherwise. dX is what rms_norm_bwd_x gives, bit for
+// bit; dW differs from rms_norm_bwd_w's only by the order of the fp32 additions (rows are dealt to the row groups in another order).
+static int launch_rms_norm_bwd_xw(bool sums, int fwd_dt, int bwd_dt, int n_rows, int n_cols, float eps, const float * fwd_weighted_sums,
+                                  const float * fwd_rms_vals, const void * rms_weight, const void * X_inp, const void * upstream_dX, void * dX,
+                                  void * dW, void * workspace, uint64_t workspace_bytes, void * stream) {
+	const char * op = sums ? "rms_norm_bwd_x_w_sums" : "rms_norm_bwd_x_w";
+	if (!valid_fwd_bwd_pair(fwd_dt, bwd_dt)) return set_error(DFB200_ERR_DTYPE, "%s: unsupported datatype pair (%d, %d)", op, fwd_dt, bwd_dt);
+	RowGeometry geo;
+	bool packets;
+	int rc = check_rows(op, n_rows, n_cols, BWD_W_ROW_THREADS, &geo, &packets);
+	if (rc) return rc;
+	if (n_rows == 0 && !sums) return DFB200_OK;
+	packets = packets && n_rows > 0 && aligned16(rms_weight) && aligned16(X_inp) && aligned16(upstream_dX) && aligned16(dX);
+	int groups = 1, grid = 1;
+	if (packets) bwd_w_geometry(n_rows, geo, &groups, &grid);
+	const size_t smem = (size_t) (groups - 1) * n_cols * sizeof(float);
+	if (!packets || smem > 200 * 1024) {
+		rc = dfb200_rms_norm_bwd_x(fwd_dt, bwd_dt, n_rows, n_cols, eps, fwd_weighted_sums, fwd_rms_vals, rms_weight, X_inp, upstream_dX, dX, stream);
+		if (rc) return rc;
+		return sums ? dfb200_rms_norm_bwd_w_sums(fwd_dt, bwd_dt, n_rows, n_cols, eps, fwd_rms_vals, X_inp, upstream_dX, static_cast<float *>(dW), workspace, workspace_bytes, stream)
+		            : dfb200_rms_norm_bwd_w(fwd_dt, bwd_dt, n_rows, n_cols, eps, fwd_rms_vals, X_inp, upstream_dX, dW, workspace, workspace_bytes, stream);
 	}
-	return DFB200_OK;
+	if (!fwd_weighted_sums || !fwd_rms_vals || !rms_weight || !X_inp || !upstream_dX || !dX || !dW) return set_error(DFB200_ERR_ARG, "%s: NULL tensor argument", op);
+	if (!elem_aligned(dW, sums ? DATAFLOW_FP32 : bwd_dt)) return set_error(DFB200_ERR_ARG, "%s: tensors must be aligned to their element size", op);
+	// one fp32 row of partial sums per CTA, and neither form launches more CTAs than SMs or rows
+	const uint64_t need = (uint64_t) (sm_count() < n_rows ? (sm_count() > 0 ? sm_count() : 1) : n_rows) * (uint64_t) n_cols * sizeof(float);
+	if (!workspace || workspace_bytes < need || !aligned16(workspace))
+		return set_error(DFB200_ERR_WORKSPACE, "%s: needs %llu bytes of 16-byte aligned workspace, got %llu", op, (unsigned long long) need,
+		                 (unsigned long long) workspace_bytes);
+	cudaStream_t s = (cudaStream_t) stream;
+	float * partials = reinterpret_cast<float *>(workspace);
+	// Staged form: rows are multiples of 16 bytes in both types (bulk copies), the row group fits 512 threads, and at least two row
+	// slots per group fit the ring.
+	{
+		const size_t stage_bytes = (size_t) n_cols * (dtype_size(fwd_dt) + 2 * dtype_size(bwd_dt));
+		unsigned int * status = kernel_status_word(STATUS_RMS);
+		int sgroups = XW_STAGED_THREADS / geo.threads;
+		if (sgroups > 8) sgroups = 8;                            // the groups synchronise on named barriers 1 .. groups
+		while (sgroups > 1 && (sgroups > n_rows || XW_RING_BUDGET / (sgroups * stage_bytes) < 2)) sgroups /= 2;
+		int stages = sgroups >= 1 ? (int) (XW_RING_BUDGET / ((size_t) sgroups * stage_bytes)) : 0;
+		if (stages > XW_MAX_STAGES) stages = XW_MAX_STAGES;
+		if (status && sgroups >= 1 && stages >= 2 && ((size_t) n_cols * dtype_size(fwd_dt)) % 16 == 0 && ((size_t) n_cols * dtype_size(bwd_dt)) % 16 == 0 &&
+		    geo.threads <= XW_STAGED_THREADS && aligned16(X_inp) && aligned16(upstream_dX) && aligned16(dX)) {
+			long long sgrid = sm_count();
+			const long long needed = ((long long) n_rows + sgroups - 1) / sgroups;
+			if (sgrid > needed) sgrid = needed;
+			if (sgrid < 1) sgrid = 1;
+			const size_t ssmem = (size_t) sgroups * stages * stage_bytes + (size_t) sgroups * stages * sizeof(uint64_t);
+			DFB200_DISPATCH_PAIR(fwd_dt, bwd_dt, F, B, DFB200_DISPATCH_VPT(geo.vpt, VPT, {
+				auto kernel = rms_norm_bwd_xw_staged_kernel<F, B, VPT>;
+				allow_dyn_smem(reinterpret_cast<const void *>(kernel), ssmem);
+				launch_pdl(kernel, dim3((unsigned) sgrid), dim3(sgroups * geo.threads), ssmem, s, n_rows, n_cols, geo.threads, stages, fwd_weighted_sums, fwd_rms_vals,
+				           rms_weight, X_inp, upstream_dX, dX, partials, status);
+			}));
+			rc = check_launch(op);
+			if (rc) return rc;
+			return launch_bwd_w_final(op, sums, fwd_dt, bwd_dt, n_cols, (int) sgrid, partials, dW, s);
+		}
+	}
+	DFB200_DISPATCH_PAIR(fwd_dt, bwd_dt, F, B, DFB200_DISPATCH_VPT(geo.vpt, VPT, {
+		auto kernel = rms_norm_bwd_xw_partial_kernel<F, B, VPT>;
+		allow_dyn_smem(reinterpret_cast<const void *>(kernel), smem);
+		launch_pdl(kernel, dim3(grid), dim3(groups * geo.threads), smem, s, n_rows, n_cols, geo.threads, fwd_weighted_sums, fwd_rms_vals, rms_weight, X_inp,
+		           upstream_dX, dX, partials);
+	}));
+	rc = check_launch(op);
+	if (rc) return rc;
+	return launch_bwd_w_final(op, sums, fwd_dt, bwd_dt, n_cols, grid, partials, dW, s);
+}
+
+extern "C" int dfb200_rms_norm_bwd_x_w(int fwd_dt, int bwd_dt, int n_rows, int n_cols, float eps, const float * fwd_weighted_sums,
+                                       const float * fwd_rms_vals, const void * rms_weight, const void * X_inp, const void * upstream_dX,
+                                       void * dX, void * dW, void * workspace, uint64_t workspace_bytes, void * stream) {
+	return launch_rms_norm_bwd_xw(false, fwd_dt, bwd_dt, n_rows, n_cols, eps, fwd_weighted_sums, fwd_rms_vals, rms_weight, X_inp, upstream_dX, dX, dW, workspace,
+	                              workspace_bytes, stream);
+}
+
+extern "C" int dfb200_rms_norm_bwd_x_w_sums(int fwd_dt, int bwd_dt, int n_rows, int n_cols, float eps, const float * fwd_weighted_sums,
+                                            const float * fwd_rms_vals, const void * rms_weight, const void * X_inp, const void * upstream_dX,
+                                            void * dX, float * column_sums, void * workspace, uint64_t workspace_bytes, void * stream) {
+	return launch_rms_norm_bwd_xw(true, fwd_dt, bwd_dt, n_rows, n_cols, eps, fwd_weighted_sums, fwd_rms_vals, rms_weight, X_inp, upstream_dX, dX, column_sums,
+	                              workspace, workspace_bytes, stream);
 }
 
 extern "C" int dfb200_rms_norm_bwd_w(int fwd_dt, int bwd_dt, int n_rows, int n_cols, float eps, const float * fwd_rms_vals,

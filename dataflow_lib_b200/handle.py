@@ -95,6 +95,13 @@ class DataflowHandle:
         return _L.submit_rms_norm_bwd_w_sums(C.byref(self.h), stream_id, int(fwd_dt), int(bwd_dt), n_rows, n_cols, eps, _p(fwd_rms_vals), _p(X_inp),
                                              _p(upstream_dX), _p(column_sums))
 
+    def submit_rms_norm_bwd_x_w(self, stream_id, fwd_dt, bwd_dt, n_rows, n_cols, eps, fwd_weighted_sums, fwd_rms_vals, rms_weight, X_inp, upstream_dX, dX, dW,
+                                sums=False):
+        """rms_norm_bwd_x and rms_norm_bwd_w in one pass; sums=True: dW is the fp32 column-sums array of submit_rms_norm_bwd_w_sums."""
+        fn = _L.submit_rms_norm_bwd_x_w_sums if sums else _L.submit_rms_norm_bwd_x_w
+        return fn(C.byref(self.h), stream_id, int(fwd_dt), int(bwd_dt), n_rows, n_cols, eps, _p(fwd_weighted_sums), _p(fwd_rms_vals), _p(rms_weight),
+                  _p(X_inp), _p(upstream_dX), _p(dX), _p(dW))
+
     def submit_rope(self, stream_id, fwd_dt, N, model_dim, head_dim, num_kv_heads, theta, seq_positions, X_q, X_k):
         return _L.submit_rope(C.byref(self.h), stream_id, int(fwd_dt), N, model_dim, head_dim, num_kv_heads, theta, _p(seq_positions), _p(X_q), _p(X_k))
 

@@ -8,9 +8,9 @@ the ops this library provides:
                rope(h as Q, k)                               in place
                x_{l+1} = swiglu_ffn_fp8(h) + x_l             FP8 weights, residual added in the down projection's epilogue
     head    :  h = rms_norm(x_L, w_head);  logits = h @ W_vocab^T (library bf16 GEMM);  fused softmax + cross entropy
-    backward:  d h = dlogits @ W_vocab (library GEMM);  rms_norm_bwd_w / rms_norm_bwd_x (dx += ...) for the head, then per
-               layer in reverse: FFN input gradient, rope_bwd_x, rms_norm_bwd_w, rms_norm_bwd_x accumulating into dx,
-               which carries the residual branch.
+    backward:  d h = dlogits @ W_vocab (library GEMM);  rms_norm_bwd_x_w (dx += ..., weight gradient as fp32 column sums, one
+               pass over x and d h) for the head, then per layer in reverse: FFN input gradient, rope_bwd_x, rms_norm_bwd_x_w
+               accumulating into dx, which carries the residual branch.
     exchange:  [loss sum, valid rows | dW_0 .. dW_L], one packed fp32 buffer that the loss kernel and the weight-gradient kernels
                write directly (sharding.PackedReduction), summed over the ranks by the library's C exchange
                (include/dataflow_b200_exchange.h: NCCL called from C) on a stream of the step's handle.
@@ -164,8 +164,7 @@ class OpStackStep:
         torch.matmul(self.dlogits, self.W_vocab, out=self.dh)
         self._mark("vocabulary GEMMs (library)")
         self.dx.zero_()
-        ops.rms_norm_bwd_w_sums(T, d, self.eps, self.rms[L], self.x[L], self.dh, self.dW[L])
-        ops.rms_norm_bwd_x(T, d, self.eps, self.ws[L], self.rms[L], self.w_norm[L], self.x[L], self.dh, self.dx)
+        ops.rms_norm_bwd_x_w(T, d, self.eps, self.ws[L], self.rms[L], self.w_norm[L], self.x[L], self.dh, self.dx, self.dW[L], sums=True)
         self.dk.zero_()                                           # nothing consumes K in this stack: its upstream gradient is zero
         self._mark("rms_norm_bwd + rope_bwd")
         for l in reversed(range(L)):
@@ -173,8 +172,7 @@ class OpStackStep:
                                    workspace=self.ffn_ws)
             self._mark("swiglu_ffn_fp8_bwd")
             ops.rope_bwd_x(T * d, d, self.hd, self.n_kv, self.theta, self.pos, self.dA, self.dk)
-            ops.rms_norm_bwd_w_sums(T, d, self.eps, self.rms[l], self.x[l], self.dA, self.dW[l])
-            ops.rms_norm_bwd_x(T, d, self.eps, self.ws[l], self.rms[l], self.w_norm[l], self.x[l], self.dA, self.dx)
+            ops.rms_norm_bwd_x_w(T, d, self.eps, self.ws[l], self.rms[l], self.w_norm[l], self.x[l], self.dA, self.dx, self.dW[l], sums=True)
             self._mark("rms_norm_bwd + rope_bwd")
 
     def _the_exchange(self, group):
@@ -230,6 +228,6 @@ class OpStackStep:
             self._exchange = None
 
     # launches of this library's kernels in one step (for accounting): per layer fwd rms 1 + rope 1 + ffn 5 (2 row passes, 3 GEMMs),
-    # bwd ffn 4 + rope 1 + bwd_w 2 + bwd_x 1; head rms 1 + softmax/CE 2 (rows + loss sum) + bwd_w 2 + bwd_x 1
+    # bwd ffn 4 + rope 1 + norm bwd_x_w 2 (one pass + final sum); head rms 1 + softmax/CE 2 (rows + loss sum) + norm bwd_x_w 2
     def library_launches_per_step(self):
-        return self.L * (1 + 1 + 5 + 4 + 1 + 2 + 1) + (1 + 2 + 2 + 1)
+        return self.L * (1 + 1 + 5 + 4 + 1 + 2) + (1 + 2 + 2)

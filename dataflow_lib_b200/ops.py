@@ -93,6 +93,17 @@ def rms_norm_bwd_w_sums(n_rows, n_cols, eps, fwd_rms_vals, X_inp, upstream_dX, c
            "rms_norm_bwd_w_sums")
 
 
+def rms_norm_bwd_x_w(n_rows, n_cols, eps, fwd_weighted_sums, fwd_rms_vals, rms_weight, X_inp, upstream_dX, dX, dW, stream=None, workspace=None, sums=False):
+    """rms_norm_bwd_x and rms_norm_bwd_w in one pass over X and dY. sums=True: dW is an fp32 array that receives the column sums
+    (the form of rms_norm_bwd_w_sums) instead of a gradient in dX's type that is accumulated into."""
+    need = _lib_.dfb200_rms_norm_bwd_w_workspace_bytes(n_rows, n_cols)
+    ws = workspace if workspace is not None else _workspace(X_inp.device, need)
+    fn = _lib_.dfb200_rms_norm_bwd_x_w_sums if sums else _lib_.dfb200_rms_norm_bwd_x_w
+    _check(fn(dt_of(X_inp), dt_of(dX), n_rows, n_cols, eps, _ptr(fwd_weighted_sums), _ptr(fwd_rms_vals), _ptr(rms_weight), _ptr(X_inp),
+              _ptr(upstream_dX), _ptr(dX), _ptr(dW), _ptr(ws), ws.numel() * ws.element_size(), _stream(stream)),
+           "rms_norm_bwd_x_w_sums" if sums else "rms_norm_bwd_x_w")
+
+
 def rope(N, model_dim, head_dim, num_kv_heads, theta, seq_positions, X_q, X_k, stream=None):
     _check(_lib_.dfb200_rope(dt_of(X_q), N, model_dim, head_dim, num_kv_heads, theta, _ptr(seq_positions), _ptr(X_q), _ptr(X_k),
                              _stream(stream)), "rope")

@@ -16,7 +16,7 @@ D, NH, NKV, HD, F, V = 4096, 32, 8, 128, 14336, 128256
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("op", choices=["rms_norm", "rms_norm_bwd_x", "rms_norm_bwd_w", "rope", "rope_bwd_x", "swiglu", "swiglu_bwd_x",
+    ap.add_argument("op", choices=["rms_norm", "rms_norm_bwd_x", "rms_norm_bwd_w", "rms_norm_bwd_x_w", "rope", "rope_bwd_x", "swiglu", "swiglu_bwd_x",
                                    "softmax", "softmax_cross_entropy", "swiglu_ffn_fp8", "swiglu_ffn_fp8_bwd", "swiglu_ffn_fp8_wgrad", "gemm_e4m3_swiglu", "gemm_e4m3",
                                    "fp8_peak"])
     ap.add_argument("--tokens", type=int, default=2048)
@@ -108,8 +108,9 @@ def main():
         ops.rms_norm(T, D, 1e-5, w, X, Y, ws, rms)
         fn = {"rms_norm": lambda: ops.rms_norm(T, D, 1e-5, w, X, Y, ws, rms),
               "rms_norm_bwd_x": lambda: ops.rms_norm_bwd_x(T, D, 1e-5, ws, rms, w, X, dY, dX),
-              "rms_norm_bwd_w": lambda: ops.rms_norm_bwd_w(T, D, 1e-5, rms, X, dY, dW)}[a.op]
-        nbytes = T * D * {"rms_norm": 2 * es, "rms_norm_bwd_x": es + 3 * bes, "rms_norm_bwd_w": es + bes}[a.op]
+              "rms_norm_bwd_w": lambda: ops.rms_norm_bwd_w(T, D, 1e-5, rms, X, dY, dW),
+              "rms_norm_bwd_x_w": lambda: ops.rms_norm_bwd_x_w(T, D, 1e-5, ws, rms, w, X, dY, dX, dW)}[a.op]
+        nbytes = T * D * {"rms_norm": 2 * es, "rms_norm_bwd_x": es + 3 * bes, "rms_norm_bwd_w": es + bes, "rms_norm_bwd_x_w": es + 3 * bes}[a.op]
     elif a.op.startswith("rope"):
         rdt = dt if a.op == "rope" else bdt                      # the backward op works on gradients
         Q, K = (torch.randn(T, n * HD, device="cuda", generator=g).to(rdt) for n in (NH, NKV))

@@ -89,6 +89,10 @@ void set_native_rms_norm_bwd_x_skeleton(Op_Skeleton * skeleton, DataflowDatatype
 void set_native_rms_norm_bwd_w_skeleton(Op_Skeleton * skeleton, DataflowDatatype fwd_datatype, DataflowDatatype bwd_datatype);
 /* Not in the reference: "rms_norm_bwd_w_sums_<F>_<B>", the RMSNorm weight gradient written as fp32 column sums (dfb200_rms_norm_bwd_w_sums). */
 void set_native_rms_norm_bwd_w_sums_skeleton(Op_Skeleton * skeleton, DataflowDatatype fwd_datatype, DataflowDatatype bwd_datatype);
+/* Not in the reference: "rms_norm_bwd_x_w_<F>_<B>" and "rms_norm_bwd_x_w_sums_<F>_<B>", rms_norm_bwd_x and rms_norm_bwd_w (or its
+ * fp32-sums form) in one pass over X and dY (dfb200_rms_norm_bwd_x_w, dfb200_rms_norm_bwd_x_w_sums). */
+void set_native_rms_norm_bwd_x_w_skeleton(Op_Skeleton * skeleton, DataflowDatatype fwd_datatype, DataflowDatatype bwd_datatype);
+void set_native_rms_norm_bwd_x_w_sums_skeleton(Op_Skeleton * skeleton, DataflowDatatype fwd_datatype, DataflowDatatype bwd_datatype);
 void set_native_rope_skeleton(Op_Skeleton * skeleton, DataflowDatatype fwd_datatype);
 void set_native_rope_bwd_x_skeleton(Op_Skeleton * skeleton, DataflowDatatype bwd_datatype);
 void set_native_copy_to_seq_context_skeleton(Op_Skeleton * skeleton, DataflowDatatype fwd_datatype);
@@ -137,6 +141,17 @@ int submit_rms_norm_bwd_w(Dataflow_Handle * handle, int stream_id, DataflowDatat
 int submit_rms_norm_bwd_w_sums(Dataflow_Handle * handle, int stream_id, DataflowDatatype fwd_dt, DataflowDatatype bwd_dt,
                                int n_rows, int n_cols, float eps,
                                float * fwd_rms_vals, void * X_inp, void * upstream_dX, float * column_sums);
+/* Not in the reference (it submits rms_norm_bwd_x, then rms_norm_bwd_w, each reading X and dY): both gradients of the norm in one
+ * pass. dX gets what submit_rms_norm_bwd_x gives, bit for bit; dW what submit_rms_norm_bwd_w gives up to the order of the fp32
+ * additions over the rows; the _sums form writes the fp32 column sums like submit_rms_norm_bwd_w_sums. */
+int submit_rms_norm_bwd_x_w(Dataflow_Handle * handle, int stream_id, DataflowDatatype fwd_dt, DataflowDatatype bwd_dt,
+                            int n_rows, int n_cols, float eps,
+                            float * fwd_weighted_sums, float * fwd_rms_vals,
+                            void * rms_weight, void * X_inp, void * upstream_dX, void * dX, void * dW);
+int submit_rms_norm_bwd_x_w_sums(Dataflow_Handle * handle, int stream_id, DataflowDatatype fwd_dt, DataflowDatatype bwd_dt,
+                                 int n_rows, int n_cols, float eps,
+                                 float * fwd_weighted_sums, float * fwd_rms_vals,
+                                 void * rms_weight, void * X_inp, void * upstream_dX, void * dX, float * column_sums);
 int submit_rope(Dataflow_Handle * handle, int stream_id, DataflowDatatype fwd_dt,
                 uint64_t N, int model_dim, int head_dim, int num_kv_heads, int theta,
                 int * seq_positions, void * X_q, void * X_k);

@@ -85,6 +85,21 @@ int dfb200_rms_norm_bwd_w_sums(int fwd_dt, int bwd_dt, int n_rows, int n_cols, f
                                const void * upstream_dX, float * column_sums,
                                void * workspace, uint64_t workspace_bytes, void * stream);
 
+/* No counterpart in the reference, which launches rms_norm_bwd_x and rms_norm_bwd_w one after the other, each reading X and dY
+ * (src/dataflow_models/dataflow_transformer/src/dataflow_transformer.c: the backward of every norm): both in ONE pass over X and
+ * dY -- 4 * n_cols elements of traffic per row instead of 6. dX is what dfb200_rms_norm_bwd_x writes, bit for bit; dW (the
+ * accumulating form) or column_sums (the fp32 form of dfb200_rms_norm_bwd_w_sums) differ from the separate op's only by the order
+ * of the fp32 additions over the rows. Same workspace as dfb200_rms_norm_bwd_w. Row lengths or alignments the 16-byte packet
+ * kernels cannot take run as the two separate general-shape passes. */
+int dfb200_rms_norm_bwd_x_w(int fwd_dt, int bwd_dt, int n_rows, int n_cols, float eps,
+                            const float * fwd_weighted_sums, const float * fwd_rms_vals,
+                            const void * rms_weight, const void * X_inp, const void * upstream_dX,
+                            void * dX, void * dW, void * workspace, uint64_t workspace_bytes, void * stream);
+int dfb200_rms_norm_bwd_x_w_sums(int fwd_dt, int bwd_dt, int n_rows, int n_cols, float eps,
+                                 const float * fwd_weighted_sums, const float * fwd_rms_vals,
+                                 const void * rms_weight, const void * X_inp, const void * upstream_dX,
+                                 void * dX, float * column_sums, void * workspace, uint64_t workspace_bytes, void * stream);
+
 /* No counterpart in the reference. rms_norm_bwd_w for callers that cannot allocate device memory or pass a
  * workspace: a program whose own arena already owns the whole device (one bulk alloc_mem at start-up), or a step
  * loop that must not hit cudaMalloc's device-wide synchronisation. Same results as dfb200_rms_norm_bwd_w; the

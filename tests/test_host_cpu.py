@@ -225,6 +225,14 @@ def test_own_op_identities_are_stable(L):
                                                         "00bf0355dfb6b3de7356d47462035a81c77a2c8541b5f4721b14bd6834c9e97c"),
         ("set_native_softmax_cross_entropy_skeleton", (5, 5)): ("softmax_cross_entropy_BF16_BF16", [26, 26, 5, 9, 5, 3, 3],
                                                                 "e769fbd45e29682394e79ad43293bd5d087f6af5cacea9039631b052b9377975"),
+        ("set_native_rms_norm_bwd_w_sums_skeleton", (5, 5)): ("rms_norm_bwd_w_sums_BF16_BF16", [26, 26, 16, 3, 5, 5, 3],
+                                                              "5a19551fe3c12e4ee113b9b1c15ddb8fe120304066491a8172d3027234afdec6"),
+        ("set_native_rms_norm_bwd_x_w_skeleton", (5, 5)): ("rms_norm_bwd_x_w_BF16_BF16", [26, 26, 16, 3, 3, 5, 5, 5, 5, 5],
+                                                           "2a16dacd8e5d5d29ec0f6d84674816de4944caa6ca9f5dfd8d3379ba3da61616"),
+        ("set_native_rms_norm_bwd_x_w_skeleton", (6, 4)): ("rms_norm_bwd_x_w_FP8E4M3_FP16", [26, 26, 16, 3, 3, 6, 6, 4, 4, 4],
+                                                           "7c45bab4018365bb664dd1a3984fbb530765aca83bf9a76064031b4ecbafd5dd"),
+        ("set_native_rms_norm_bwd_x_w_sums_skeleton", (5, 5)): ("rms_norm_bwd_x_w_sums_BF16_BF16", [26, 26, 16, 3, 3, 5, 5, 5, 5, 3],
+                                                                "24bd0572d6d2ae63bb6059c51c9063f3be724592c00386c3bdc8e8d0bf91e665"),
     }
     for (fn, args), (nick, dts, digest) in want.items():
         sk = abi.OpSkeleton()
@@ -320,6 +328,12 @@ def test_external_op_wrappers_build_the_reference_argument_lists(L):
                                   0xB0, 0xC0, 0xD0, 0xE0, 88, 0xF0) == 0
     assert seen["nick"] == "flash3_attention_bwd"
     assert seen["vals"] == [BF16, 2, 100, 120, 0x10, 0x20, 60, 0x30, 0x40, 70, 32, 8, 128, 0x50, 0x60, 0x70, 0x80, 0x90, 0xB0, 0xC0, 0xD0, 0xE0, 88, 0xF0]
+    # this library's fused norm backward: the argument list of rms_norm_bwd_x with the weight gradient appended
+    assert L.submit_rms_norm_bwd_x_w(C.byref(h), 2, BF16, BF16, 100, 4096, 1e-5, 0x10, 0x20, 0x30, 0x40, 0x50, 0x60, 0x70) == 0
+    assert seen["nick"] == "rms_norm_bwd_x_w_BF16_BF16" and seen["stream"] == 2
+    assert seen["vals"][:2] == [100, 4096] and abs(seen["vals"][2] - 1e-5) < 1e-12 and seen["vals"][3:] == [0x10, 0x20, 0x30, 0x40, 0x50, 0x60, 0x70]
+    assert L.submit_rms_norm_bwd_x_w_sums(C.byref(h), 0, BF16, BF16, 7, 64, 1e-5, 0x10, 0x20, 0x30, 0x40, 0x50, 0x60, 0x70) == 0
+    assert seen["nick"] == "rms_norm_bwd_x_w_sums_BF16_BF16" and seen["vals"][3:] == [0x10, 0x20, 0x30, 0x40, 0x50, 0x60, 0x70]
     seen["rc"] = -1
     assert L.submit_matmul(C.byref(h), 0, BF16, BF16, NONE, BF16, FP32, 0, 0, 8, 8, 8, 1.0, 0.0, None, None, None, None, 0, None) == -1
 
@@ -344,12 +358,12 @@ def test_register_native_ops_with_the_reference_callers_arguments(L, capfd, tmp_
     cubin.write_bytes(b"\x7fELF not a shared object")
     for arg in (b"lib/cuda_kernels.cubin", str(cubin).encode(), b"libm.so.6"):       # missing file, not loadable, loadable but without the ops
         seen.clear()
-        assert L.register_native_ops(C.byref(h), arg, b"lib/cuda_kernels_config.so") == 82
-        assert os.path.realpath(seen["path"]) == own and seen["n"] == 82 and "dataflow_b200_rms_norm" in seen["symbols"]
+        assert L.register_native_ops(C.byref(h), arg, b"lib/cuda_kernels_config.so") == 96
+        assert os.path.realpath(seen["path"]) == own and seen["n"] == 96 and "dataflow_b200_rms_norm" in seen["symbols"]
         assert "registering them from this library instead" in capfd.readouterr().err
     for arg in (None, own.encode()):                                                  # the documented forms: no notice
         seen.clear()
-        assert L.register_native_ops(C.byref(h), arg, None) == 82
+        assert L.register_native_ops(C.byref(h), arg, None) == 96
         assert os.path.realpath(seen["path"]) == own
         assert "Notice" not in capfd.readouterr().err
 

@@ -86,7 +86,7 @@ def test_stack_matches_oracle_composition():
     assert _rel_l2(f32(to_host(st.dx, O.BF16), O.BF16), f32(dx, O.BF16)) < 6e-2
     for l in range(L + 1):                                     # the stack keeps the weight gradients as fp32 column sums in its packed buffer
         assert _rel_l2(st.dW[l].cpu().numpy(), f32(dW[l], O.BF16)) < 6e-2, l
-    assert st.library_launches_per_step() == L * 15 + 6
+    assert st.library_launches_per_step() == L * 14 + 5
     st.close()
 
 

@@ -101,6 +101,44 @@ def test_rms_norm_bwd_w(ops, pair, shape):
     assert np.array_equal(to_host(dW2, bdt), got)
 
 
+@pytest.mark.parametrize("pair", PAIRS, ids=lambda p: f"{DT_NAME[p[0]]}_{DT_NAME[p[1]]}")
+@pytest.mark.parametrize("shape", [(4096, 4096), (17, 1024), (3, 16), (1000, 8192), (64, 16384), (2, 32768), (777, 512), (301, 2056), (37, 4100)], ids=str)
+@pytest.mark.parametrize("sums", [False, True], ids=["dW", "sums"])
+def test_rms_norm_bwd_x_w(ops, pair, shape, sums):
+    """Both gradients of the norm in one pass over X and dY (no reference counterpart): dX must be what rms_norm_bwd_x gives, bit for
+    bit, and dW (or the fp32 column sums) what the oracle's rms_norm_bwd_w gives within the tolerance of the separate op. The shapes
+    cover the staged kernel (rows of 16-byte multiples that fit the shared-memory ring with 1, 2 or 4 row groups), the register kernel
+    (32768 columns: a row slot does not fit twice) and the general-shape fallback (4100 columns)."""
+    fdt, bdt = pair
+    n_rows, n_cols = shape
+    X, w = fill(fdt, shape, 1), fill(fdt, (n_cols,), 2, 1.0, 0.02)
+    dY, dX0 = fill(bdt, shape, 3), fill(bdt, shape, 4)
+    _, ws, rms = O.rms_norm(fdt, 1e-5, w, X)
+    wsd, rmsd, wd, Xd, dYd = torch.from_numpy(ws).cuda(), torch.from_numpy(rms).cuda(), to_dev(w, fdt), to_dev(X, fdt), to_dev(dY, bdt)
+    dX_sep, dX = to_dev(dX0, bdt), to_dev(dX0, bdt)
+    ops.rms_norm_bwd_x(n_rows, n_cols, 1e-5, wsd, rmsd, wd, Xd, dYd, dX_sep)
+    dW0 = fill(bdt, (n_cols,), 5)
+    if sums:
+        dW = torch.full((n_cols,), float("nan"), device="cuda")                  # overwritten, nothing read
+    else:
+        dW = to_dev(dW0, bdt)
+        ref = O.rms_norm_bwd_w(fdt, bdt, rms, X, dY, dW0, n_blocks=0)
+    ops.rms_norm_bwd_x_w(n_rows, n_cols, 1e-5, wsd, rmsd, wd, Xd, dYd, dX, dW, sums=sums)
+    torch.cuda.synchronize()
+    assert torch.equal(dX.view(torch.uint8), dX_sep.view(torch.uint8)), "dX differs from rms_norm_bwd_x"
+    if sums:
+        exact = (f32(dY, bdt).astype(np.float64) * f32(X, fdt).astype(np.float64) * rms.astype(np.float64)[:, None]).sum(0)
+        got = dW.cpu().numpy()
+        assert np.all(np.abs(got - exact) <= 2e-5 * np.maximum(np.abs(exact), np.sqrt(n_rows))), float(np.abs(got - exact).max())
+    else:
+        check_lowp(to_host(dW, bdt), ref, bdt, "rms_norm_bwd_x_w dW", rel=rel_for(bdt) if bdt != O.FP32 else 2e-5, scale=float(np.sqrt(n_rows)))
+    # deterministic: a second run gives identical bits
+    dX2, dW2 = to_dev(dX0, bdt), (torch.empty_like(dW) if sums else to_dev(dW0, bdt))
+    ops.rms_norm_bwd_x_w(n_rows, n_cols, 1e-5, wsd, rmsd, wd, Xd, dYd, dX2, dW2, sums=sums)
+    torch.cuda.synchronize()
+    assert torch.equal(dW2.view(torch.uint8), dW.view(torch.uint8)) and torch.equal(dX2.view(torch.uint8), dX.view(torch.uint8))
+
+
 # ------------------------------------------------------------------------------------------ RoPE
 
 ROPE_CASES = [  # tokens, n_heads, n_kv_heads, head_dim, theta, max_pos
