@@ -215,13 +215,18 @@ def other_configs(hbm_peak):
         ops.rms_norm(R, C, EPS, w, X, Y, ws, rms)
         ops.rms_norm_bwd_x(R, C, EPS, ws, rms, w, X, dY, dX)
         ops.rms_norm_bwd_w(R, C, EPS, rms, X, dY, dW)
+    def c1_one_pass_sequence():
+        ops.rms_norm(R, C, EPS, w, X, Y, ws, rms)
+        ops.rms_norm_bwd_x_w(R, C, EPS, ws, rms, w, X, dY, dX, dW)
     out["c1_rms_norm_4096x4096"] = {
         "fwd": hbm(2 * R * C * 2, timed(lambda: ops.rms_norm(R, C, EPS, w, X, Y, ws, rms))),
         "bwd_x": hbm(4 * R * C * 2, timed(lambda: ops.rms_norm_bwd_x(R, C, EPS, ws, rms, w, X, dY, dX))),
         "bwd_w": hbm(2 * R * C * 2, timed(lambda: ops.rms_norm_bwd_w(R, C, EPS, rms, X, dY, dW))),
+        "bwd_x_w": hbm(4 * R * C * 2, timed(lambda: ops.rms_norm_bwd_x_w(R, C, EPS, ws, rms, w, X, dY, dX, dW))),
         "fwd_bwd_x_bwd_w_sequence": hbm(8 * R * C * 2, timed(c1_sequence, 20)),
+        "fwd_bwd_x_w_sequence": hbm(6 * R * C * 2, timed(c1_one_pass_sequence, 20)),
         "note": "the configuration as it is run: forward, input gradient and weight gradient back to back (4 launches, programmatic dependent "
-                "launches), 256 MiB algorithmic per sequence; the whole working set (4 x 32 MiB) is of the order of the 126 MB L2, so single ops "
+                "launches), 256 MiB algorithmic per sequence -- or, with both gradients in one pass over X and dY (bwd_x_w: same outputs), 3 launches and 192 MiB; the whole working set (4 x 32 MiB) is of the order of the 126 MB L2, so single ops "
                 "repeated in isolation partly hit L2 and can read above the DRAM ceiling"}
     del X, dY, Y, dX
     # C3: fused softmax + cross entropy 16384 x 128256

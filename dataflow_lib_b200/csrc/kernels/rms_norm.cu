@@ -236,6 +236,7 @@ rms_norm_bwd_w_partial_kernel(int n_rows, int n_cols, int group_threads, const f
 	RawChunk<F> xr[VPT], xn[VPT];
 	RawChunk<B> gr[VPT], gn[VPT];
 	int row = blockIdx.x * groups + g;
+	float r_next = 0.0f;                             // the row's rms value travels with its packets, one row ahead
 	if (row < n_rows) {
 		#pragma unroll
 		for (int v = 0; v < VPT; v++) {
@@ -246,10 +247,13 @@ rms_norm_bwd_w_partial_kernel(int n_rows, int n_cols, int group_threads, const f
 				ld_raw<B>(dY, off, gr[v]);
 			}
 		}
+		r_next = __ldg(fwd_rms_vals + (n_rows - 1 - row));
 	}
 	for (; row < n_rows; row += row_stride) {
 		const int next_row = row + row_stride;
+		const float r = r_next;
 		if (next_row < n_rows) {                     // next row's packets are requested before this row is consumed
+			r_next = __ldg(fwd_rms_vals + (n_rows - 1 - next_row));
 			#pragma unroll
 			for (int v = 0; v < VPT; v++) {
 				const int c = tid + v * group_threads;
@@ -260,7 +264,6 @@ rms_norm_bwd_w_partial_kernel(int n_rows, int n_cols, int group_threads, const f
 				}
 			}
 		}
-		const float r = __ldg(fwd_rms_vals + (n_rows - 1 - row));
 		#pragma unroll
 		for (int v = 0; v < VPT; v++) {
 			const int c = tid + v * group_threads;
@@ -433,7 +436,7 @@ template <int NW> __device__ __forceinline__ void lds_words(const unsigned char 
 }
 
 template <typename F, typename B, int VPT>
-__global__ void __launch_bounds__(XW_STAGED_THREADS)
+__global__ void __launch_bounds__(XW_STAGED_THREADS, 1)
 rms_norm_bwd_xw_staged_kernel(int n_rows, int n_cols, int group_threads, int stages, const float * __restrict__ fwd_weighted_sums,
                               const float * __restrict__ fwd_rms_vals, const void * __restrict__ weight, const void * X, const void * dY, void * dX,
                               float * __restrict__ partials, unsigned int * status) {
@@ -485,13 +488,17 @@ rms_norm_bwd_xw_staged_kernel(int n_rows, int n_cols, int group_threads, int sta
 		if (c < n_chunks) ld_words<FW, Hint::KEEP>(reinterpret_cast<const char *>(weight) + (size_t) c * E * FSIZE, wr[v].w);
 	}
 
+	// the two statistics of a row are requested one row ahead: a scalar load issued when the row is due would put a trip to L2 on
+	// every row's critical path
+	float r_next = 0.0f, ws_next = 0.0f;
+	if (my_iters > 0) { r_next = __ldg(fwd_rms_vals + first); ws_next = __ldg(fwd_weighted_sums + first); }
 	for (int k = 0; k < my_iters; k++) {
 		const int s = k % stages, row = first + k * row_stride;
+		const float r = r_next, ws = ws_next;
+		if (k + 1 < my_iters) { r_next = __ldg(fwd_rms_vals + row + row_stride); ws_next = __ldg(fwd_weighted_sums + row + row_stride); }
 		const bool arrived = mbar_wait_bounded(&full[s], (uint32_t) (k / stages) & 1u, status, 0x300u + (unsigned) s);
 		if (arrived) {
 			const unsigned char * slot = ring + (size_t) s * stage_bytes;
-			const float r = __ldg(fwd_rms_vals + row);
-			const float ws = __ldg(fwd_weighted_sums + row);
 			const float r3 = r * r * r;
 			#pragma unroll
 			for (int v = 0; v < VPT; v++) {

@@ -121,18 +121,20 @@ rope_kernel(int tokens, int model_dim, int kv_dim, int head_dim, int tok_per_ite
 // ----------------------------------------------------------------------------------------
 // staged kernel
 // ----------------------------------------------------------------------------------------
+// Ring geometry, measured on B200 at 8192 / 16384 tokens x (4096 + 1024) bf16 (10 KB per token), 512 threads, launches back to back:
+// 3 tokens x 3 stages 28.8 / 57.2 us (5.9 TB/s); 2 x 4: 30.4 / 59.4; 2 x 5: 30.3 / 60.3; 4 x 2: - / 68.6; geometries that leave
+// one CTA per SM (3 x 4, 4 x 3, 2 x 6, 1 x 8) 70 - 90 us at 16384 tokens. 320 to 512 threads per CTA are within 2 % of each other.
 #ifndef DFB200_ROPE_STAGES
-#define DFB200_ROPE_STAGES 4
+#define DFB200_ROPE_STAGES 3
 #endif
 #ifndef DFB200_ROPE_STAGE_BUDGET
-#define DFB200_ROPE_STAGE_BUDGET 24576
+#define DFB200_ROPE_STAGE_BUDGET 32768
 #endif
-constexpr int ROPE_STAGES = DFB200_ROPE_STAGES;
 constexpr int ROPE_STAGED_THREADS = 512;
 
 template <typename T, bool BWD>
 __global__ void __launch_bounds__(ROPE_STAGED_THREADS)
-rope_staged_kernel(int tokens, int model_dim, int kv_dim, int head_dim, int tok_per_stage, float theta,
+rope_staged_kernel(int tokens, int model_dim, int kv_dim, int head_dim, int tok_per_stage, int stages, float theta,
                    const int * __restrict__ seq_positions, void * X_q, void * X_k, unsigned int * status) {
 	constexpr int ESIZE = 4 / Word<T>::EPW;              // bytes per element
 	constexpr int CW = E / Word<T>::EPW;                 // 32-bit words per chunk
@@ -147,18 +149,18 @@ rope_staged_kernel(int tokens, int model_dim, int kv_dim, int head_dim, int tok_
 	// Two table buffers: the table of stage it + 1 is built while stage it is rotated, so one CTA barrier per stage serves both
 	// "rotated rows ready for the write-back" and "next table ready".
 	const int table_len = tok_per_stage * half;
-	float * tab_cos = reinterpret_cast<float *>(smem + ROPE_STAGES * stage_bytes);      // [2][tok_per_stage * half]
+	float * tab_cos = reinterpret_cast<float *>(smem + stages * stage_bytes);      // [2][tok_per_stage * half]
 	float * tab_sin = tab_cos + 2 * table_len;                                          // [2][tok_per_stage * half]
 	float * inv_freq = tab_sin + 2 * table_len;                                         // [half]
 	uint64_t * full = reinterpret_cast<uint64_t *>(inv_freq + ((half + 3) & ~3));       // [STAGES]
-	const int tid = threadIdx.x;
+	const int tid = threadIdx.x, nthr = blockDim.x;
 
 	cudaTriggerProgrammaticLaunchCompletion();       // see pdl_prologue(): barrier setup and the frequencies need no global memory,
 	if (tid == 0) {
-		for (int s = 0; s < ROPE_STAGES; s++) mbar_init(&full[s], 1);
+		for (int s = 0; s < stages; s++) mbar_init(&full[s], 1);
 		mbar_fence_init();
 	}
-	for (int j = tid; j < half; j += ROPE_STAGED_THREADS) {
+	for (int j = tid; j < half; j += nthr) {
 		const float expo = -1.0f * ((float) (2 * j) / (float) head_dim);
 		inv_freq[j] = (float) pow((double) theta, (double) expo);
 	}
@@ -170,7 +172,7 @@ rope_staged_kernel(int tokens, int model_dim, int kv_dim, int head_dim, int tok_
 	const int my_iters = blockIdx.x < n_blocks ? (n_blocks - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
 	auto tok0_of = [&](int it) { return (blockIdx.x + it * (int) gridDim.x) * tok_per_stage; };
 	auto issue_load = [&](int it) {          // thread 0 only
-		const int s = it % ROPE_STAGES, tok0 = tok0_of(it), n_tok = min(tok_per_stage, tokens - tok0);
+		const int s = it % stages, tok0 = tok0_of(it), n_tok = min(tok_per_stage, tokens - tok0);
 		const uint32_t qb = (uint32_t) n_tok * model_dim * ESIZE, kb = (uint32_t) n_tok * kv_dim * ESIZE;
 		unsigned char * dst = ring + (size_t) s * stage_bytes;
 		mbar_arrive_expect_tx(&full[s], qb + kb);
@@ -178,13 +180,13 @@ rope_staged_kernel(int tokens, int model_dim, int kv_dim, int head_dim, int tok_
 		if (kb) bulk_load(dst + q_stage_bytes, reinterpret_cast<const unsigned char *>(X_k) + (size_t) tok0 * kv_dim * ESIZE, kb, &full[s]);
 	};
 	if (tid == 0)
-		for (int it = 0; it < ROPE_STAGES - 1 && it < my_iters; it++) issue_load(it);
+		for (int it = 0; it < stages - 1 && it < my_iters; it++) issue_load(it);
 	// (cos, sin) of one stage's tokens into table buffer it & 1
 	auto build_table = [&](int it) {
 		if (it >= my_iters) return;
 		const int tok0 = tok0_of(it), n_tok = min(tok_per_stage, tokens - tok0);
 		float * tc = tab_cos + (it & 1) * table_len, * ts = tab_sin + (it & 1) * table_len;
-		for (int e = tid; e < n_tok * half; e += ROPE_STAGED_THREADS) {
+		for (int e = tid; e < n_tok * half; e += nthr) {
 			const int t = e / half, j = e - t * half;
 			float sn, cs;
 			sincosf((float) __ldg(seq_positions + tok0 + t) * inv_freq[j], &sn, &cs);
@@ -200,22 +202,27 @@ rope_staged_kernel(int tokens, int model_dim, int kv_dim, int head_dim, int tok_
 	const int head_mask = (chunks_per_head & (chunks_per_head - 1)) == 0 ? chunks_per_head - 1 : -1;
 	bool ok = true;
 	for (int it = 0; it < my_iters && ok; it++) {
-		const int s = it % ROPE_STAGES, tok0 = tok0_of(it), n_tok = min(tok_per_stage, tokens - tok0);
+		const int s = it % stages, tok0 = tok0_of(it), n_tok = min(tok_per_stage, tokens - tok0);
 		// every thread waits for the stage's copy itself; a thread whose wait gave up skips the rotation, and the barrier below tells all
-		const bool arrived = mbar_wait_bounded(&full[s], (uint32_t) (it / ROPE_STAGES) & 1u, status, 0x100u + (unsigned) s);
+		const bool arrived = mbar_wait_bounded(&full[s], (uint32_t) (it / stages) & 1u, status, 0x100u + (unsigned) s);
 
-		// Rotate in place in shared memory. Token-major outer loop, chunk-strided inner loop: a chunk's
-		// slot in the (cos, sin) table depends only on its position inside its head, which for Q and K
-		// alike is (c mod chunks_per_head) because both sections hold whole heads -- no division in the
-		// inner loop when chunks_per_head is a power of two.
+		// Rotate in place in shared memory. The stage holds the Q rows of its tokens back to back, then the K rows, so it is ONE flat
+		// list of n_tok * (q_chunks + k_chunks) chunks that the threads share evenly (a per-token loop would leave most warps idle
+		// when a row has fewer chunks than two rounds of the CTA). A chunk's slot in the (cos, sin) table depends only on its
+		// position inside its head, which is its flat index within its section modulo chunks_per_head because both sections hold
+		// whole heads; its token is found by comparisons (a stage has at most 8 tokens).
 		unsigned char * stage = ring + (size_t) s * stage_bytes;
-		for (int t = 0; t < n_tok && arrived; t++) {
-			unsigned char * q_row = stage + (size_t) t * model_dim * ESIZE;
-			unsigned char * k_row = stage + q_stage_bytes + (size_t) t * kv_dim * ESIZE - (size_t) q_chunks * E * ESIZE;
-			const float * cos_t = tab_cos + (it & 1) * table_len + t * half, * sin_t = tab_sin + (it & 1) * table_len + t * half;
-			for (int c = tid; c < row_chunks; c += ROPE_STAGED_THREADS) {
-				uint32_t * p = reinterpret_cast<uint32_t *>((c < q_chunks ? q_row : k_row) + (size_t) c * E * ESIZE);
-				const int in_head = head_mask >= 0 ? (c & head_mask) : (c % chunks_per_head);
+		const int nq = n_tok * q_chunks, work = arrived ? n_tok * row_chunks : 0;
+		const float * cos_s = tab_cos + (it & 1) * table_len, * sin_s = tab_sin + (it & 1) * table_len;
+		{
+			for (int i = tid; i < work; i += nthr) {
+				const bool is_q = i < nq;
+				const int j = is_q ? i : i - nq, per_tok = is_q ? q_chunks : k_chunks;     // flat chunk index within the section
+				int t = 0;
+				for (int u = 1; u < n_tok; u++) t += j >= u * per_tok;
+				uint32_t * p = reinterpret_cast<uint32_t *>(stage + (is_q ? 0u : q_stage_bytes) + (size_t) j * E * ESIZE);
+				const int in_head = head_mask >= 0 ? (j & head_mask) : (j % chunks_per_head);
+				const float * cos_t = cos_s + t * half, * sin_t = sin_s + t * half;
 				uint32_t w[CW];
 				if constexpr (CW == 2) { const uint2 v = *reinterpret_cast<const uint2 *>(p); w[0] = v.x; w[1] = v.y; }
 				else {
@@ -254,7 +261,7 @@ rope_staged_kernel(int tokens, int model_dim, int kv_dim, int head_dim, int tok_
 			bulk_store(reinterpret_cast<unsigned char *>(X_q) + (size_t) tok0 * model_dim * ESIZE, stage, qb);
 			if (kb) bulk_store(reinterpret_cast<unsigned char *>(X_k) + (size_t) tok0 * kv_dim * ESIZE, stage + q_stage_bytes, kb);
 			bulk_commit();
-			const int next = it + ROPE_STAGES - 1;       // refills the stage written back in the previous iteration
+			const int next = it + stages - 1;            // refills the stage written back in the previous iteration
 			if (next < my_iters) {
 				bulk_wait_read<1>();                     // ... once that write-back no longer reads it
 				issue_load(next);
@@ -328,23 +335,25 @@ static int launch_rope(const char * op, int dt, uint64_t N, int model_dim, int h
 		const size_t row_bytes = ((size_t) model_dim + kv_dim) * esize;
 		const bool copyable = (model_dim * esize) % 16 == 0 && (kv_dim * esize) % 16 == 0;
 		int tok = (int) (DFB200_ROPE_STAGE_BUDGET / row_bytes);
+		int stages = DFB200_ROPE_STAGES;
+		const int sthreads = ROPE_STAGED_THREADS;
 		if (tok > 8) tok = 8;
 		if (tok > tokens) tok = tokens;
 		unsigned int * status = kernel_status_word(STATUS_ROPE);
 		if (copyable && tok >= 1 && status) {
 			const size_t stage_bytes = ((size_t) tok * row_bytes + 127) & ~(size_t) 127;
-			const size_t smem = ROPE_STAGES * stage_bytes + 2 * (size_t) tok * half * sizeof(float2) + (((size_t) half + 3) & ~(size_t) 3) * sizeof(float)
-			                    + ROPE_STAGES * sizeof(uint64_t);
+			const size_t smem = stages * stage_bytes + 2 * (size_t) tok * half * sizeof(float2) + (((size_t) half + 3) & ~(size_t) 3) * sizeof(float)
+			                    + stages * sizeof(uint64_t);
 			int rc = DFB200_ERR_DTYPE;
 			DFB200_DISPATCH_DTYPE(dt, T, {
 				auto kernel = rope_staged_kernel<T, BWD>;
 				allow_dyn_smem(reinterpret_cast<const void *>(kernel), smem);
-				const int per_sm = ctas_per_sm(reinterpret_cast<const void *>(kernel), ROPE_STAGED_THREADS, smem);
+				const int per_sm = ctas_per_sm(reinterpret_cast<const void *>(kernel), sthreads, smem);
 				long long g = (long long) sm_count() * per_sm;
 				const long long blocks = ((long long) tokens + tok - 1) / tok;
 				if (g > blocks) g = blocks;
-				launch_pdl(kernel, dim3((unsigned) (g < 1 ? 1 : g)), dim3(ROPE_STAGED_THREADS), smem, (cudaStream_t) stream, tokens, model_dim, kv_dim, head_dim, tok,
-				           (float) theta, seq_positions, X_q, X_k, status);
+				launch_pdl(kernel, dim3((unsigned) (g < 1 ? 1 : g)), dim3(sthreads), smem, (cudaStream_t) stream, tokens, model_dim, kv_dim, head_dim, tok,
+				           stages, (float) theta, seq_positions, X_q, X_k, status);
 				rc = check_launch(op);
 			});
 			return rc;
