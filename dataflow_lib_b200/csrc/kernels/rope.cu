@@ -121,9 +121,10 @@ rope_kernel(int tokens, int model_dim, int kv_dim, int head_dim, int tok_per_ite
 // ----------------------------------------------------------------------------------------
 // staged kernel
 // ----------------------------------------------------------------------------------------
-// Ring geometry, measured on B200 at 8192 / 16384 tokens x (4096 + 1024) bf16 (10 KB per token), 512 threads, launches back to back:
-// 3 tokens x 3 stages 28.8 / 57.2 us (5.9 TB/s); 2 x 4: 30.4 / 59.4; 2 x 5: 30.3 / 60.3; 4 x 2: - / 68.6; geometries that leave
-// one CTA per SM (3 x 4, 4 x 3, 2 x 6, 1 x 8) 70 - 90 us at 16384 tokens. 320 to 512 threads per CTA are within 2 % of each other.
+// Ring geometry, measured on B200 at 8192 / 16384 tokens x (4096 + 1024) bf16 (10 KB per token, 320 threads per CTA), launches back to
+// back, and as the step of the Llama-3-8B layer chain that holds two RoPE launches (bench.py): 3 tokens x 3 stages 25.3 / 56.0 us,
+// step 0.407 ms; 2 x 3: 24.0 / 56.5, 0.408; 2 x 4: 26.3 / 56.3, 0.412; 1 x 4: 30.4 / 58.9, 0.413; 3 x 2: 30.5 / 59.9, 0.415;
+// 4 x 2: 32.9 / 65.7, 0.422. Geometries that leave one CTA per SM (3 x 4, 4 x 3, 2 x 6, 1 x 8) take 70 - 90 us at 16384 tokens.
 #ifndef DFB200_ROPE_STAGES
 #define DFB200_ROPE_STAGES 3
 #endif
@@ -206,23 +207,19 @@ rope_staged_kernel(int tokens, int model_dim, int kv_dim, int head_dim, int tok_
 		// every thread waits for the stage's copy itself; a thread whose wait gave up skips the rotation, and the barrier below tells all
 		const bool arrived = mbar_wait_bounded(&full[s], (uint32_t) (it / stages) & 1u, status, 0x100u + (unsigned) s);
 
-		// Rotate in place in shared memory. The stage holds the Q rows of its tokens back to back, then the K rows, so it is ONE flat
-		// list of n_tok * (q_chunks + k_chunks) chunks that the threads share evenly (a per-token loop would leave most warps idle
-		// when a row has fewer chunks than two rounds of the CTA). A chunk's slot in the (cos, sin) table depends only on its
-		// position inside its head, which is its flat index within its section modulo chunks_per_head because both sections hold
-		// whole heads; its token is found by comparisons (a stage has at most 8 tokens).
+		// Rotate in place in shared memory. Token-major outer loop, chunk-strided inner loop: a chunk's slot in the (cos, sin) table
+		// depends only on its position inside its head, which for Q and K alike is (c mod chunks_per_head) because both sections hold
+		// whole heads -- no division in the inner loop when chunks_per_head is a power of two. The launcher sizes the CTA so that a
+		// row's chunks divide evenly among the threads (640 chunks: 320 threads x 2), or else most warps would idle through the
+		// second round of every token.
 		unsigned char * stage = ring + (size_t) s * stage_bytes;
-		const int nq = n_tok * q_chunks, work = arrived ? n_tok * row_chunks : 0;
-		const float * cos_s = tab_cos + (it & 1) * table_len, * sin_s = tab_sin + (it & 1) * table_len;
-		{
-			for (int i = tid; i < work; i += nthr) {
-				const bool is_q = i < nq;
-				const int j = is_q ? i : i - nq, per_tok = is_q ? q_chunks : k_chunks;     // flat chunk index within the section
-				int t = 0;
-				for (int u = 1; u < n_tok; u++) t += j >= u * per_tok;
-				uint32_t * p = reinterpret_cast<uint32_t *>(stage + (is_q ? 0u : q_stage_bytes) + (size_t) j * E * ESIZE);
-				const int in_head = head_mask >= 0 ? (j & head_mask) : (j % chunks_per_head);
-				const float * cos_t = cos_s + t * half, * sin_t = sin_s + t * half;
+		for (int t = 0; t < n_tok && arrived; t++) {
+			unsigned char * q_row = stage + (size_t) t * model_dim * ESIZE;
+			unsigned char * k_row = stage + q_stage_bytes + (size_t) t * kv_dim * ESIZE - (size_t) q_chunks * E * ESIZE;
+			const float * cos_t = tab_cos + (it & 1) * table_len + t * half, * sin_t = tab_sin + (it & 1) * table_len + t * half;
+			for (int c = tid; c < row_chunks; c += nthr) {
+				uint32_t * p = reinterpret_cast<uint32_t *>((c < q_chunks ? q_row : k_row) + (size_t) c * E * ESIZE);
+				const int in_head = head_mask >= 0 ? (c & head_mask) : (c % chunks_per_head);
 				uint32_t w[CW];
 				if constexpr (CW == 2) { const uint2 v = *reinterpret_cast<const uint2 *>(p); w[0] = v.x; w[1] = v.y; }
 				else {
@@ -336,7 +333,11 @@ static int launch_rope(const char * op, int dt, uint64_t N, int model_dim, int h
 		const bool copyable = (model_dim * esize) % 16 == 0 && (kv_dim * esize) % 16 == 0;
 		int tok = (int) (DFB200_ROPE_STAGE_BUDGET / row_bytes);
 		int stages = DFB200_ROPE_STAGES;
-		const int sthreads = ROPE_STAGED_THREADS;
+		// threads per CTA: the fewest rounds over a row's chunks that 512 threads allow, then as few threads as do it in that many
+		// rounds (a multiple of 32), so that every thread has the same number of chunks per token
+		const int row_chunks = (model_dim + kv_dim) / E, rounds = (row_chunks + ROPE_STAGED_THREADS - 1) / ROPE_STAGED_THREADS;
+		int sthreads = ((row_chunks + rounds - 1) / rounds + 31) / 32 * 32;
+		if (sthreads < 64) sthreads = 64;
 		if (tok > 8) tok = 8;
 		if (tok > tokens) tok = tokens;
 		unsigned int * status = kernel_status_word(STATUS_ROPE);
