@@ -432,7 +432,15 @@ def run_gpu_arm(args):
         return calls
     bound = [bind(sets[0], args.separate_norm_bwd), bind(sets[1], args.separate_norm_bwd)]
     bound_other = bind(sets[0], not args.separate_norm_bwd)        # the other form of the norm's backward, for one comparison region
-    exchange_pending = [False]
+    exchange_pending, exchange_due = [False], [False]
+    AFTER_OP = op_names.index("rope")          # the exchange of step s is issued behind this op of step s + 1: beside `swiglu`
+
+    def issue_exchange():
+        """The data-parallel exchange (one in-place fp32 all-reduce of 16 KB, issued from C) on the handle's second stream, behind a
+        dependency on what the compute stream holds so far."""
+        assert h.submit_dependency(S1, h.get_stream_state(S0)) == 0
+        assert exchange.all_reduce(S1, packed) == 0
+        exchange_due[0], exchange_pending[0] = False, True
 
     def chain(events=None, only=None, which=0, calls=None):
         """One step on input set `which`. `events[i] = (start, end)` are recorded around op i (all ops, or just op `only`)."""
@@ -450,14 +458,18 @@ def run_gpu_arm(args):
                 events[i][1].record(stream)
             if rc != 0:
                 raise RuntimeError(f"submit of op {i} of the chain failed")
+            if i == AFTER_OP and exchange_due[0]:
+                # The previous step's exchange runs beside this step's `swiglu`, a flat grid of short CTAs that gives up a few SMs for
+                # the collective's 30 - 50 us at no measurable cost. Beside a persistent grid (rms_norm, rope: every CTA resident for the
+                # whole kernel) the CTAs that the collective displaces run as a second wave: rope 36 -> 47 us at N = 8 when the
+                # exchange was issued right after the step.
+                issue_exchange()
         if world > 1:
-            # the data-parallel exchange (one in-place fp32 all-reduce of 16 KB, issued from C) runs on the handle's second stream behind
-            # a dependency on the compute stream, so that it overlaps the next step's kernels
-            assert h.submit_dependency(S1, h.get_stream_state(S0)) == 0
-            assert exchange.all_reduce(S1, packed) == 0
-            exchange_pending[0] = True
+            exchange_due[0] = True
 
     def join_exchange():
+        if world > 1 and exchange_due[0]:
+            issue_exchange()
         if world > 1 and exchange_pending[0]:
             assert h.submit_dependency(S0, h.get_stream_state(S1)) == 0
             exchange_pending[0] = False
