@@ -514,7 +514,15 @@ def run_gpu_arm(args):
     region_ms = regions.tolist()
     ms_total = statistics.median(region_ms)
     dom_ms = statistics.median(dom_ms_all)
-    host_enqueue_ms = statistics.median(enqueue_ms)
+    host_enqueue_ms = statistics.median(enqueue_ms)      # includes waiting for room in the launch queue once the region outruns it
+    # the host's own cost of submitting a step: 40 steps (under 300 launches, well inside the queue) submitted to an idle device
+    barrier()
+    host_t0 = time.perf_counter()
+    for s in range(40):
+        chain()
+    host_submit_ms = 1e3 * (time.perf_counter() - host_t0) / 40
+    join_exchange()
+    barrier()
 
     # ---- untimed: the dominant kernel alone, back to back (every launch re-reads its 0.7 GB of inputs from DRAM: it walks the tensors
     # from the end, so what the previous launch left in L2 is the part it reads last)
@@ -675,6 +683,10 @@ def run_gpu_arm(args):
                             "ranks copying at once (slowest rank): the host-side ceiling of this region"},
             "gpu_launches": launches_per_step * args.steps * len(region_ms),
             "host_enqueue_ms_per_step": host_enqueue_ms,
+            "host_submit_ms_per_step": host_submit_ms,
+            "host_note": "host_submit = wall time per step of submitting 40 steps to an idle device (the C path: skeleton, SHA-256, table lookup, "
+                         "launch, through ctypes); host_enqueue = the same inside the timed regions, where the host runs a full launch queue ahead "
+                         "of the device and mostly waits for room in it",
             "clocks": clocks,
         }
         if exchange_check is not None:

@@ -211,7 +211,7 @@ rope_staged_kernel(int tokens, int model_dim, int kv_dim, int head_dim, int tok_
 		// depends only on its position inside its head, which for Q and K alike is (c mod chunks_per_head) because both sections hold
 		// whole heads -- no division in the inner loop when chunks_per_head is a power of two. The launcher sizes the CTA so that a
 		// row's chunks divide evenly among the threads (640 chunks: 320 threads x 2), or else most warps would idle through the
-		// second round of every token.
+		// second pass over every token's chunks.
 		unsigned char * stage = ring + (size_t) s * stage_bytes;
 		for (int t = 0; t < n_tok && arrived; t++) {
 			unsigned char * q_row = stage + (size_t) t * model_dim * ESIZE;
@@ -333,10 +333,10 @@ static int launch_rope(const char * op, int dt, uint64_t N, int model_dim, int h
 		const bool copyable = (model_dim * esize) % 16 == 0 && (kv_dim * esize) % 16 == 0;
 		int tok = (int) (DFB200_ROPE_STAGE_BUDGET / row_bytes);
 		int stages = DFB200_ROPE_STAGES;
-		// threads per CTA: the fewest rounds over a row's chunks that 512 threads allow, then as few threads as do it in that many
-		// rounds (a multiple of 32), so that every thread has the same number of chunks per token
-		const int row_chunks = (model_dim + kv_dim) / E, rounds = (row_chunks + ROPE_STAGED_THREADS - 1) / ROPE_STAGED_THREADS;
-		int sthreads = ((row_chunks + rounds - 1) / rounds + 31) / 32 * 32;
+		// threads per CTA: the fewest passes over a row's chunks that 512 threads allow, then as few threads as do it in that many
+		// passes (a multiple of 32), so that every thread has the same number of chunks per token
+		const int row_chunks = (model_dim + kv_dim) / E, passes = (row_chunks + ROPE_STAGED_THREADS - 1) / ROPE_STAGED_THREADS;
+		int sthreads = ((row_chunks + passes - 1) / passes + 31) / 32 * 32;
 		if (sthreads < 64) sthreads = 64;
 		if (tok > 8) tok = 8;
 		if (tok > tokens) tok = tokens;
