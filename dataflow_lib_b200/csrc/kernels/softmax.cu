@@ -548,19 +548,36 @@ constexpr int SOFTMAX_SPT_16BIT = 8, SOFTMAX_SPT_FP32 = 4;
 // packet_bytes = bytes of one 8-element chunk in the input type (8 for fp8, 16 for fp16 / bf16, 32 for fp32)
 static bool softmax_geometry(int n_chunks, int packet_bytes, SoftmaxGeometry * g) {
 	g->spt = 0;
-	// Long rows of 16- and 32-bit elements: CTAs of up to 512 threads with half of their packets in registers and half in shared memory
-	// (two CTAs per SM). 16-bit: one CTA for rows of up to 65536 elements, a cluster of two up to 131072, of four up to 262144; fp32: one
-	// CTA up to 32768 elements, clusters of two, four and eight up to 262144. Shorter rows (<= 32 words per thread) stay in registers.
+	// Long rows of 16- and 32-bit elements: CTAs of up to 512 threads with half of their packets in registers and half in shared memory.
+	// The smallest cluster that holds the row -- 16-bit: one CTA for rows of up to 65536 elements, two up to 131072, four up to 262144;
+	// fp32: one CTA up to 32768 elements, clusters of two, four and eight up to 262144 -- is then widened to more, smaller CTAs (below).
+	// Shorter rows (<= 32 words per thread) stay in registers.
 	const int half = packet_bytes == 16 ? SOFTMAX_SPT_16BIT : packet_bytes == 32 ? SOFTMAX_SPT_FP32 : 0;
 	if (half && n_chunks > SOFTMAX_MAX_THREADS * half && n_chunks <= SOFTMAX_MAX_CLUSTER * SOFTMAX_MAX_THREADS * 2 * half &&
 	    SOFTMAX_MAX_CPT == 8 && SOFTMAX_MAX_THREADS == 512) {
 		const int per_cta = SOFTMAX_MAX_THREADS * 2 * half;
 		int cluster = 1;
 		while (cluster * per_cta < n_chunks) cluster *= 2;
-		int slice = (n_chunks + cluster - 1) / cluster;
-		slice = (slice + SLICE_ALIGN_CHUNKS - 1) / SLICE_ALIGN_CHUNKS * SLICE_ALIGN_CHUNKS;
-		int threads = (slice + 2 * half - 1) / (2 * half);
-		threads = (threads + 127) / 128 * 128;
+		auto shape_of = [&](int cl, int * slice_out, int * threads_out) {
+			int sl = (n_chunks + cl - 1) / cl;
+			sl = (sl + SLICE_ALIGN_CHUNKS - 1) / SLICE_ALIGN_CHUNKS * SLICE_ALIGN_CHUNKS;
+			int th = (sl + 2 * half - 1) / (2 * half);
+			th = (th + 127) / 128 * 128;
+			*slice_out = sl; *threads_out = th;
+		};
+		int slice, threads;
+		shape_of(cluster, &slice, &threads);
+		// More, smaller CTAs per row: eight 128-thread CTAs on an SM interleave their load / exponential / store phases more finely than
+		// two of 512 threads (16384 x 128256 bf16, fused cross entropy: clusters of 2 x 512 threads 1468 us, 4 x 256 1403 us, 8 x 128
+		// 1391 us). The cluster is widened while the CTAs keep at least 128 threads and the thread slots that the 128-thread
+		// granularity leaves empty do not grow beyond a tenth of the row.
+		while (cluster * 2 <= SOFTMAX_MAX_CLUSTER && threads > 128) {
+			int slice2, threads2;
+			shape_of(cluster * 2, &slice2, &threads2);
+			const double slots = (double) cluster * threads * 2 * half / n_chunks, slots2 = (double) cluster * 2 * threads2 * 2 * half / n_chunks;
+			if (slots2 > (slots > 1.1 ? slots : 1.1)) break;
+			cluster *= 2; slice = slice2; threads = threads2;
+		}
 		if (cluster <= SOFTMAX_MAX_CLUSTER && threads <= SOFTMAX_MAX_THREADS) {
 			g->cluster = cluster; g->threads = threads; g->cpt = half; g->slice_chunks = slice;
 			g->spt = half;
