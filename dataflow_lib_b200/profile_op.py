@@ -21,6 +21,7 @@ def main():
                                    "fp8_peak"])
     ap.add_argument("--tokens", type=int, default=2048)
     ap.add_argument("--iters", type=int, default=3)
+    ap.add_argument("--vocab", type=int, default=V, help="softmax ops: columns per row (default: the Llama-3 vocabulary)")
     ap.add_argument("--dtype", default="bf16", choices=["bf16", "fp16", "fp32", "fp8e4m3", "fp8e5m2"],
                     help="datatype of the forward tensors; with an fp8 type the gradients are bf16 (the registered fp8 x bf16 pairs)")
     a = ap.parse_args()
@@ -124,12 +125,13 @@ def main():
         fn = (lambda: ops.swiglu(T, F, x1, x3, out)) if a.op == "swiglu" else (lambda: ops.swiglu_bwd_x(T, F, x1, x3, dY, d1, d3))
         nbytes = T * F * (3 * es if a.op == "swiglu" else 2 * es + 3 * bes)
     else:
-        L = (2 * torch.randn(T, V, device="cuda", generator=g)).to(dt)
-        out = torch.empty(T, V, device="cuda", dtype=bdt)
-        labels = torch.randint(0, V, (T,), device="cuda", generator=g, dtype=torch.int32)
+        vocab = a.vocab
+        L = (2 * torch.randn(T, vocab, device="cuda", generator=g)).to(dt)
+        out = torch.empty(T, vocab, device="cuda", dtype=bdt)
+        labels = torch.randint(0, vocab, (T,), device="cuda", generator=g, dtype=torch.int32)
         loss = torch.zeros(2, device="cuda")
-        fn = (lambda: ops.softmax(T, V, L, out)) if a.op == "softmax" else (lambda: ops.softmax_cross_entropy(T, V, L, labels, out, None, loss))
-        nbytes = T * V * (es + bes)
+        fn = (lambda: ops.softmax(T, vocab, L, out)) if a.op == "softmax" else (lambda: ops.softmax_cross_entropy(T, vocab, L, labels, out, None, loss))
+        nbytes = T * vocab * (es + bes)
     fn()
     torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
