@@ -1,5 +1,6 @@
 """The token-sharded step's collective on real GPUs: include/dataflow_b200_exchange.h (NCCL called from C on a stream of each rank's
-handle) with rms_norm_bwd_w_sums writing its fp32 column sums straight into the packed buffer. One process per GPU, the communicator
+handle) with rms_norm_bwd_w_sums -- and, in the last step, the one-pass rms_norm_bwd_x_w_sums -- writing the fp32 column sums straight
+into the packed buffer. One process per GPU, the communicator
 id carried by a gloo process group (any channel will do); needs at least two GPUs, so it is skipped on a single-GPU box. No rank
 leaves before all collectives have completed, NVLS off for the test (plain ring / tree paths)."""
 import os
@@ -41,7 +42,11 @@ def _rank(rank, world, port, out):
     for step in range(3):                                        # the buffer is overwritten, not accumulated: every step gives the same sums
         packed.loss.copy_(torch.tensor([float(rank + 1), float(ROWS)], device="cuda"))
         torch.cuda.synchronize()
-        assert h.submit_rms_norm_bwd_w_sums(0, BF, BF, ROWS, COLS, 1e-5, rms, X, dY, packed.dW[0]) == 0
+        if step < 2:
+            assert h.submit_rms_norm_bwd_w_sums(0, BF, BF, ROWS, COLS, 1e-5, rms, X, dY, packed.dW[0]) == 0
+        else:        # the same sums from the op that also does the input gradient (its own summation order over the rows)
+            ws, w, dX = torch.zeros(ROWS, device="cuda"), torch.ones(COLS, device="cuda").bfloat16(), torch.zeros_like(X)
+            assert h.submit_rms_norm_bwd_x_w(0, BF, BF, ROWS, COLS, 1e-5, ws, rms, w, X, dY, dX, packed.dW[0], sums=True) == 0
         assert h.submit_dependency(1, h.get_stream_state(0)) == 0
         assert ex.all_reduce(1, packed) == 0
         assert h.sync_stream(1) == 0
