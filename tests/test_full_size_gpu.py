@@ -65,6 +65,20 @@ def test_c1_rms_norm_fwd_bwd(ops):
     dW3 = dW.clone()
     ops.rms_norm_bwd_w(R, C, eps, rms, X, dY, dW3)
     assert ((dW3.double() - 2 * exact).abs() <= 2.0 ** -7 * exact.abs() * 2 + 4e-3).all()
+    # both gradients in one pass over X and dY (rms_norm_bwd_x_w): dX is the separate op's bit for bit, the weight gradient is the same
+    # exact column sum within bf16 rounding, its fp32 form (written, not accumulated) within 2e-5; linear in dY like the separate op
+    dX0 = _randn((R, C), 3)
+    dX_sep, dX_one, dX_sums = dX0.clone(), dX0.clone(), dX0.clone()
+    ops.rms_norm_bwd_x(R, C, eps, ws, rms, w, X, dY, dX_sep)
+    dW4, sums = torch.zeros_like(dW), torch.full((C,), float("nan"), device="cuda")
+    ops.rms_norm_bwd_x_w(R, C, eps, ws, rms, w, X, dY, dX_one, dW4)
+    ops.rms_norm_bwd_x_w(R, C, eps, ws, rms, w, X, dY, dX_sums, sums, sums=True)
+    assert torch.equal(dX_one.view(torch.int16), dX_sep.view(torch.int16)) and torch.equal(dX_sums.view(torch.int16), dX_sep.view(torch.int16))
+    assert ((dW4.double() - exact).abs() <= 2.0 ** -8 * exact.abs() + 2e-3).all()
+    assert ((sums.double() - exact).abs() <= 2e-5 * exact.abs() + 2e-5 * R ** 0.5).all()
+    dW5, scratch = torch.zeros_like(dW), dX0.clone()
+    ops.rms_norm_bwd_x_w(R, C, eps, ws, rms, w, X, (dY.float() * 2).bfloat16(), scratch, dW5)
+    assert torch.equal(dW5.float(), dW4.float() * 2)
 
 
 def test_c2_rope_roundtrip_and_swiglu(ops):
