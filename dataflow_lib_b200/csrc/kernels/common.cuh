@@ -48,6 +48,11 @@ static inline void launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, s
 	(void) cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);      // a failure stays readable through cudaGetLastError (check_launch)
 }
 #ifdef __CUDACC__
+// Asks L2 for the line that holds *p. Legal before cudaGridDependencySynchronize() whatever the previous kernel of the stream writes:
+// nothing reaches a register, and a line that the previous kernel still writes stays coherent in the one L2. A kernel that waits for
+// its predecessor's last CTAs uses the wait to have its own first loads hit L2 instead of starting a trip to DRAM afterwards.
+__device__ __forceinline__ void prefetch_l2(const void * p) { asm volatile("prefetch.global.L2 [%0];" :: "l"(p)); }
+
 __device__ __forceinline__ void pdl_prologue() {
 	cudaTriggerProgrammaticLaunchCompletion();       // the next kernel of the stream may be scheduled; it still waits for this one to finish
 	cudaGridDependencySynchronize();                 // the previous kernel of the stream has finished and its writes are visible

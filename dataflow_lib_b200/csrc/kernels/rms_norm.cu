@@ -66,9 +66,17 @@ __global__ void __launch_bounds__(fwd_max_threads(VPT))
 rms_norm_fwd_kernel(int n_rows, int n_cols, float eps, const void * __restrict__ weight, const void * __restrict__ X,
                     void * __restrict__ out, float * __restrict__ weighted_sums, float * __restrict__ rms_vals) {
 	__shared__ float red[2][2][32];
-	pdl_prologue();
 	const int n_chunks = n_cols / E;
 	const int tid = threadIdx.x, nthr = blockDim.x;
+	cudaTriggerProgrammaticLaunchCompletion();
+	if ((int) blockIdx.x < n_rows) {                 // while the previous kernel of the stream drains: the first row's lines on their way to L2
+		#pragma unroll
+		for (int v = 0; v < VPT; v++) {
+			const int c = tid + v * nthr;
+			if (c < n_chunks) prefetch_l2(reinterpret_cast<const char *>(X) + ((uint64_t) blockIdx.x * n_cols + (uint64_t) c * E) * (4 / Word<T>::EPW));
+		}
+	}
+	cudaGridDependencySynchronize();
 
 	RawChunk<T> wr[VPT], cur[VPT], nxt[VPT];     // packed: 4 registers per chunk for 16-bit types
 	#pragma unroll
@@ -456,6 +464,14 @@ rms_norm_bwd_xw_staged_kernel(int n_rows, int n_cols, int group_threads, int sta
 	cudaTriggerProgrammaticLaunchCompletion();       // see pdl_prologue(): the set-up below needs no global memory
 	if (threadIdx.x == 0) s_failed = 0;
 	if (tid == 0) {
+		// while the previous kernel of the stream drains: this group's first rows on their way to L2
+		for (int k = 0; k < stages; k++) {
+			const uint64_t row = (uint64_t) blockIdx.x * groups + g + (uint64_t) k * gridDim.x * groups;
+			if (row >= (uint64_t) n_rows) break;
+			bulk_prefetch_l2(reinterpret_cast<const unsigned char *>(X) + row * xb, xb);
+			bulk_prefetch_l2(reinterpret_cast<const unsigned char *>(dY) + row * gb, gb);
+			bulk_prefetch_l2(reinterpret_cast<const unsigned char *>(dX) + row * gb, gb);
+		}
 		for (int s = 0; s < stages; s++) mbar_init(&full[s], 1);
 		mbar_fence_init();
 	}

@@ -158,6 +158,15 @@ rope_staged_kernel(int tokens, int model_dim, int kv_dim, int head_dim, int tok_
 
 	cudaTriggerProgrammaticLaunchCompletion();       // see pdl_prologue(): barrier setup and the frequencies need no global memory,
 	if (tid == 0) {
+		// while the previous kernel of the stream drains: this CTA's first stages on their way to L2
+		const int n_blocks0 = (tokens + tok_per_stage - 1) / tok_per_stage;
+		for (int it = 0; it < stages - 1; it++) {
+			const int blk = (int) blockIdx.x + it * (int) gridDim.x;
+			if (blk >= n_blocks0) break;
+			const int tok0 = blk * tok_per_stage, n_tok = min(tok_per_stage, tokens - tok0);
+			bulk_prefetch_l2(reinterpret_cast<const unsigned char *>(X_q) + (size_t) tok0 * model_dim * ESIZE, (uint32_t) n_tok * model_dim * ESIZE);
+			if (kv_dim) bulk_prefetch_l2(reinterpret_cast<const unsigned char *>(X_k) + (size_t) tok0 * kv_dim * ESIZE, (uint32_t) n_tok * kv_dim * ESIZE);
+		}
 		for (int s = 0; s < stages; s++) mbar_init(&full[s], 1);
 		mbar_fence_init();
 	}

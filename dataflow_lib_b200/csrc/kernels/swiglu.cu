@@ -53,10 +53,20 @@ template <typename F, typename B, int THREADS, int UNROLL>
 __global__ void __launch_bounds__(THREADS)
 swiglu_bwd_x_kernel(uint64_t n_chunks, const void * __restrict__ x_w1, const void * __restrict__ x_w3,
                     const void * __restrict__ upstream_dX, void * __restrict__ dX_w1, void * __restrict__ dX_w3) {
-	pdl_prologue();
 	// The tensors are walked from their END: in a layer's forward-then-backward sequence the tail of x_w1 and x_w3 is what the forward
 	// kernel left in L2.
 	const uint64_t first = (uint64_t) blockIdx.x * (THREADS * UNROLL) + threadIdx.x, last = n_chunks - 1;
+	cudaTriggerProgrammaticLaunchCompletion();
+	#pragma unroll
+	for (int u = 0; u < UNROLL; u++) {                 // while the previous kernel of the stream drains: this thread's lines on their way to L2
+		const uint64_t c = last - (first + (uint64_t) u * THREADS);
+		if (c < n_chunks) {
+			prefetch_l2(reinterpret_cast<const char *>(x_w1) + c * (E * (4 / Word<F>::EPW)));
+			prefetch_l2(reinterpret_cast<const char *>(x_w3) + c * (E * (4 / Word<F>::EPW)));
+			prefetch_l2(reinterpret_cast<const char *>(upstream_dX) + c * (E * (4 / Word<B>::EPW)));
+		}
+	}
+	cudaGridDependencySynchronize();
 	float a[UNROLL][E], b[UNROLL][E], g[UNROLL][E];
 	#pragma unroll
 	for (int u = 0; u < UNROLL; u++) {

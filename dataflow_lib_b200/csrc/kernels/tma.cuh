@@ -66,6 +66,11 @@ __device__ __forceinline__ void bulk_load(void * smem_dst, const void * gmem_src
 	asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
 	             :: "r"(smem_u32(smem_dst)), "l"(gmem_src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
 }
+// Asks L2 for `bytes` of global memory (multiples of 16, address 16-byte aligned); nothing reaches shared memory or registers, so it is
+// legal before the wait for the previous kernel of the stream (see prefetch_l2 in common.cuh).
+__device__ __forceinline__ void bulk_prefetch_l2(const void * gmem_src, uint32_t bytes) {
+	asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" :: "l"(gmem_src), "r"(bytes) : "memory");
+}
 // this CTA's shared memory -> global, tracked by the thread's bulk-group.
 __device__ __forceinline__ void bulk_store(void * gmem_dst, const void * smem_src, uint32_t bytes) {
 	asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" :: "l"(gmem_dst), "r"(smem_u32(smem_src)), "r"(bytes) : "memory");
