@@ -329,6 +329,54 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(sm)}
 
 
+def host_memory_near_gpu(device_index):
+    """Multi-rank runs: prefer this process's host memory on the NUMA node its GPU hangs off, and run on that node's CPUs where the
+    allowed CPU set has any, so that eight ranks' pinned buffers are not all served by one socket's memory. Linux only
+    (set_mempolicy(MPOL_PREFERRED) for this process; nothing outside it is touched); every failure leaves things as they were. Returns
+    what was found and done, for the JSON line."""
+    import ctypes
+    import platform
+    info = {"gpu_numa_node": None, "mempolicy": "unchanged", "cpu_affinity": "unchanged"}
+    try:
+        import torch
+        p = torch.cuda.get_device_properties(device_index)
+        if hasattr(p, "pci_bus_id"):
+            bus = "%04x:%02x:%02x.0" % (getattr(p, "pci_domain_id", 0), p.pci_bus_id, getattr(p, "pci_device_id", 0))
+        else:
+            import pynvml
+            pynvml.nvmlInit()
+            raw = pynvml.nvmlDeviceGetPciInfo(pynvml.nvmlDeviceGetHandleByIndex(device_index)).busId
+            raw = raw.decode() if isinstance(raw, bytes) else raw
+            bus = raw.lower()[-12:]
+        with open(f"/sys/bus/pci/devices/{bus}/numa_node") as f:
+            node = int(f.read())
+        info["gpu_numa_node"] = node
+        nodes = [d for d in os.listdir("/sys/devices/system/node") if d.startswith("node") and d[4:].isdigit()]
+        info["host_numa_nodes"] = len(nodes)
+        if node < 0 or len(nodes) < 2:
+            return info
+        if platform.machine() == "x86_64" and node < 63:
+            mask = ctypes.c_ulong(1 << node)
+            libc = ctypes.CDLL(None, use_errno=True)
+            rc = libc.syscall(238, 1, ctypes.byref(mask), ctypes.c_ulong(64))          # set_mempolicy(MPOL_PREFERRED, {node})
+            info["mempolicy"] = f"preferred node {node}" if rc == 0 else f"refused (errno {ctypes.get_errno()})"
+        cpus = set()
+        with open(f"/sys/devices/system/node/node{node}/cpulist") as f:
+            for part in f.read().strip().split(","):
+                if part:
+                    lo, _, hi = part.partition("-")
+                    cpus.update(range(int(lo), int(hi or lo) + 1))
+        both = os.sched_getaffinity(0) & cpus
+        if both:
+            os.sched_setaffinity(0, both)
+            info["cpu_affinity"] = f"{len(both)} allowed CPUs of node {node}"
+        else:
+            info["cpu_affinity"] = f"none of node {node}'s CPUs is in the allowed set"
+    except Exception as e:                                   # placement is an optimisation: report and carry on
+        info["error"] = repr(e)
+    return info
+
+
 def seeded_inputs(rank):
     """Host inputs of the chain: seed 0 + rank for the data, identical weights on all ranks. numpy normals rounded to bf16 by torch on the
     CPU; returned as raw 16-bit arrays (what the handle's transfers move)."""
@@ -365,6 +413,9 @@ def run_gpu_arm(args):
     rank, world, local = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1")), int(os.environ.get("LOCAL_RANK", "0"))
     assert world == args.gpus, f"--gpus {args.gpus} but WORLD_SIZE={world} (launch N > 1 with torchrun)"
     torch.cuda.set_device(local)
+    host_numa = host_memory_near_gpu(local) if world > 1 else None      # before any host buffer of this rank exists
+    if host_numa is not None:
+        print(f"rank {rank}: host memory placement {host_numa}", file=sys.stderr)
     if world > 1:
         quiet_nccl_banner()
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
@@ -691,6 +742,8 @@ def run_gpu_arm(args):
         }
         if exchange_check is not None:
             line["exchange_check"] = exchange_check
+        if host_numa is not None:
+            line["host_numa"] = host_numa
         if cpu is not None:
             line["cpu_baseline"] = cpu
         if others:
