@@ -54,9 +54,9 @@ CHAIN_OPS_SEPARATE = ["rms_norm", "rope", "swiglu", "swiglu_bwd_x", "rope_bwd_x"
 DOMINANT = "swiglu_bwd_x"
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from the ncu capture summarised in
 # profiles/swiglu_bwd_x_bf16_2048x14336.md: reads scale with the rows and equal the algorithmic 704.6 MB; DRAM writes are
-# the algorithmic 469.8 MB minus ~41.6 MB that is still dirty in L2 when the kernel ends (size-independent residue). (Inside the
+# the algorithmic 469.8 MB minus ~51.6 MB that is still dirty in L2 when the kernel ends (size-independent residue). (Inside the
 # chain the kernel starts with the tail of x_w1 and x_w3 already in L2, left there by swiglu: up to ~126 MB fewer DRAM reads.)
-DOMINANT_DRAM_TRAFFIC_BYTES = 1_132_800_000
+DOMINANT_DRAM_TRAFFIC_BYTES = 1_122_800_000
 
 
 def quiet_nccl_banner():
@@ -716,7 +716,7 @@ def run_gpu_arm(args):
                          "alone": {"achieved": alone, "frac": alone / peak, "ms": dom_alone_ms,
                                    "what": "the same kernel launched 20 times back to back by itself in this run: every byte comes from DRAM"},
                          "traffic_source": "profiles/swiglu_bwd_x_bf16_2048x14336.md: ncu capture of the kernel alone at 2048 rows, reads scaled by the rows "
-                                           "(x4), writes less the size-independent ~42 MB still dirty in L2 at kernel end",
+                                           "(x4), writes less the size-independent ~52 MB still dirty in L2 at kernel end",
                          "note": "achieved / frac are measured inside the chain, where the kernel follows swiglu on the same x_w1, x_w3 and walks "
                                  "them from the end: the ~126 MB that swiglu left in L2 are not re-read from DRAM, so frac can pass 1; `alone` is the "
                                  "distance to the DRAM roofline"},
