@@ -63,7 +63,7 @@ int main(int argc, char ** argv) {
 	for (long i = 0; i < (long) rows * ffn; i++) { hG[i] = solo_fp32_to_bf16(3.0f * uniform(&st)); hU[i] = solo_fp32_to_bf16(2.0f * uniform(&st)); }
 
 	/* one allocation, sub-allocated by the caller (256-byte aligned pieces), as the reference's programs do */
-	const size_t total = 2 * xb + 3 * gb + 4096 + 2 * (size_t) rows * 4 + 8 * 256;
+	const size_t total = 3 * xb + 3 * gb + 2 * 4096 + 2 * (size_t) rows * 4 + 10 * 256;
 	char * base = handle.alloc_mem(&handle, total);
 	if (!base) { fprintf(stderr, "alloc_mem failed\n"); return 1; }
 	size_t off = 0;
@@ -71,6 +71,8 @@ int main(int argc, char ** argv) {
 	void * dX = TAKE(xb); void * dY = TAKE(xb); void * dW = TAKE(cols * 2);
 	void * dG = TAKE(gb); void * dU = TAKE(gb); void * dS = TAKE(gb);
 	float * d_ws = (float *) TAKE(rows * 4); float * d_rms = (float *) TAKE(rows * 4);
+	void * dXg = TAKE(xb); void * dWg = TAKE(cols * 2);                       /* gradients of the norm's input and weight */
+	uint16_t * hXg = calloc(1, xb), * hWg = calloc(1, cols * 2);
 
 	int rc = 0;
 	rc |= handle.submit_inbound_transfer(&handle, 0, dX, hX, xb);
@@ -79,12 +81,19 @@ int main(int argc, char ** argv) {
 	rc |= handle.submit_inbound_transfer(&handle, 0, dU, hU, gb);
 	rc |= submit_rms_norm(&handle, 0, DATAFLOW_BF16, rows, cols, eps, dW, dX, dY, d_ws, d_rms);
 	rc |= submit_swiglu(&handle, 0, DATAFLOW_BF16, rows, ffn, dG, dU, dS);
+	/* the norm's backward in one pass (this library's rms_norm_bwd_x_w), with the norm's own output standing in for the upstream
+	 * gradient; both gradient buffers start at zero */
+	rc |= handle.submit_inbound_transfer(&handle, 0, dXg, hXg, xb);
+	rc |= handle.submit_inbound_transfer(&handle, 0, dWg, hWg, cols * 2);
+	rc |= submit_rms_norm_bwd_x_w(&handle, 0, DATAFLOW_BF16, DATAFLOW_BF16, rows, cols, eps, d_ws, d_rms, dW, dX, dY, dXg, dWg);
 	/* results leave on the second stream, behind a dependency on the compute stream */
 	rc |= handle.submit_dependency(&handle, 1, handle.get_stream_state(&handle, 0));
 	rc |= handle.submit_outbound_transfer(&handle, 1, hY, dY, xb);
 	rc |= handle.submit_outbound_transfer(&handle, 1, hS, dS, gb);
 	rc |= handle.submit_outbound_transfer(&handle, 1, h_rms, d_rms, rows * 4);
 	rc |= handle.submit_outbound_transfer(&handle, 1, h_ws, d_ws, rows * 4);
+	rc |= handle.submit_outbound_transfer(&handle, 1, hXg, dXg, xb);
+	rc |= handle.submit_outbound_transfer(&handle, 1, hWg, dWg, cols * 2);
 	rc |= handle.sync_stream(&handle, 1);
 	if (rc) { fprintf(stderr, "a submission failed\n"); return 1; }
 
@@ -98,6 +107,21 @@ int main(int argc, char ** argv) {
 		if (fabs(h_rms[r] - rinv) > 1e-5 * rinv || fabs(h_ws[r] - wsum) > 1e-4 * fmax(fabs(wsum), 1.0)) { fprintf(stderr, "row %d statistics: %g %g, expected %g %g\n", r, h_rms[r], h_ws[r], rinv, wsum); bad = 1; break; }
 	}
 	bad |= check("rms_norm", hY, ref, (long) rows * cols);
+	{	/* dW[c] = sum_r dY[r,c] x[r,c] r_r and dX[r,c] = dY[r,c] (w_c r_r - x[r,c] r_r^3 ws_r / n), from the device's own Y, rms and ws */
+		double * dw = calloc(cols, sizeof(double)), * dx = malloc((size_t) rows * cols * sizeof(double));
+		for (int r = 0; r < rows; r++)
+			for (int c = 0; c < cols; c++) {
+				const double x = solo_bf16_to_fp32(hX[(long) r * cols + c]), g = solo_bf16_to_fp32(hY[(long) r * cols + c]), rr = h_rms[r];
+				dw[c] += g * x * rr;
+				dx[(long) r * cols + c] = g * (solo_bf16_to_fp32(hW[c]) * rr - x * rr * rr * rr / cols * h_ws[r]);
+			}
+		bad |= check("rms_norm_bwd_x_w dX", hXg, dx, (long) rows * cols);
+		double scale = 0.0;
+		for (int c = 0; c < cols; c++) scale = fmax(scale, fabs(dw[c]));
+		for (int c = 0; c < cols && !bad; c++)
+			if (fabs(solo_bf16_to_fp32(hWg[c]) - dw[c]) > 1e-2 * fmax(fabs(dw[c]), 0.05 * scale)) { fprintf(stderr, "rms_norm_bwd_x_w dW[%d]: %g, expected %g\n", c, solo_bf16_to_fp32(hWg[c]), dw[c]); bad = 1; }
+		free(dw); free(dx);
+	}
 	for (long i = 0; i < (long) rows * ffn; i++) { const double g = solo_bf16_to_fp32(hG[i]); ref[i] = g / (1.0 + exp(-g)) * solo_bf16_to_fp32(hU[i]); }
 	bad |= check("swiglu", hS, ref, (long) rows * ffn);
 
